@@ -1,0 +1,245 @@
+/*
+ * turbofieldfare_cuda.h — C ABI of the B200 (sm_100a) routed-expert library.
+ *
+ * One entry point per reference operator on the routed-expert path. The
+ * reference (drumih/turbo-fieldfare) has no FFI for this path: its operators
+ * are Swift classes that encode Metal compute passes onto a command buffer.
+ * Each function below names the Swift method it replaces (path relative to the
+ * reference repository root) and keeps that method's argument meaning:
+ *
+ *   (MTLBuffer, byteOffset)  ->  (device pointer, byte offset)
+ *   MTLCommandBuffer         ->  cudaStream_t (void* here; work is enqueued,
+ *                                the call returns immediately)
+ *   precondition / throw     ->  non-zero tf_status + tf_last_error()
+ *
+ * Conventions
+ *   - every data pointer is a DEVICE pointer unless its name says host;
+ *   - *_off are byte offsets added to the pointer before use;
+ *   - the caller owns every buffer, scratch included, and keeps it alive until
+ *     the stream has passed the call (as with a committed command buffer);
+ *   - no entry point allocates device memory except the *_create functions;
+ *   - there is no CPU fallback: without a CUDA device every call fails.
+ *
+ * Weight format (unchanged from the .gturbo files): MLX affine, group 64.
+ *   int4: N/2 bytes per row, low nibble = even column; int8: N bytes per row;
+ *   one 16-bit scale and one 16-bit bias per group, w = q * scale + bias.
+ *   The planes are BF16 in the format (TF_BF16); TF_FP16 planes are accepted
+ *   by the stand-alone GEMVs only.
+ */
+#ifndef TURBOFIELDFARE_CUDA_H
+#define TURBOFIELDFARE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TF_ABI_VERSION 1
+#define TF_GROUP_SIZE 64
+#define TF_MAX_TOP_K 8          /* MoE.maxStreamedExperts, Kernels/MoE/MoE.swift:32 */
+#define TF_MAX_ROUTER_EXPERTS 256
+#define TF_MAX_TILE_EXPERTS 16  /* PrefillMoEGrouping.swift:113 */
+
+typedef int tf_status;
+enum {
+    TF_OK = 0,
+    TF_ERR_INVALID_ARGUMENT = 1,   /* a Swift precondition would have trapped */
+    TF_ERR_UNSUPPORTED = 2,
+    TF_ERR_CUDA = 3,               /* a CUDA runtime call failed; see tf_last_error */
+    TF_ERR_ALIGNMENT = 4,
+    TF_ERR_OUT_OF_MEMORY = 5,      /* PrefillGroupedRoutedMoEError.allocationFailed */
+    TF_ERR_SCRATCH_TOO_SMALL = 6,  /* SharedExpertError.scratchTooSmall */
+    TF_ERR_DIMENSION_MISMATCH = 7, /* SharedExpertError.dimensionMismatch */
+    TF_ERR_NO_DEVICE = 8,          /* MetalError.noDevice */
+    /* PrefillMoEGroupingError cases, in declaration order
+       (Kernels/Prefill/MoE/PrefillMoEGrouping.swift:52-62) */
+    TF_ERR_GROUPING_INVALID_QUERY_COUNT = 101,
+    TF_ERR_GROUPING_INVALID_TOP_K = 102,
+    TF_ERR_GROUPING_INVALID_NUM_EXPERTS = 103,
+    TF_ERR_GROUPING_INVALID_TILE_EXPERT_COUNT = 104,
+    TF_ERR_GROUPING_PAIR_COUNT_MISMATCH = 105,
+    TF_ERR_GROUPING_TOKEN_OUT_OF_RANGE = 106,
+    TF_ERR_GROUPING_RANK_OUT_OF_RANGE = 107,
+    TF_ERR_GROUPING_EXPERT_OUT_OF_RANGE = 108,
+    TF_ERR_GROUPING_DUPLICATE_TOKEN_RANK = 109,
+    TF_ERR_GROUPING_SORT_KEY_COUNT_MISMATCH = 110
+};
+
+typedef enum { TF_BF16 = 0, TF_FP16 = 1 } tf_dtype;
+
+/* Nine byte offsets into one expert blob: gate{W,S,B} | up{W,S,B} | down{W,S,B}.
+ * Replaces MoEExpertOffsets (Kernels/MoE/MoE.swift:4-29) and the MSL
+ * ExpertOffsets (Metal/MoE/moe.metal:62-72); same field order, 36 bytes. */
+typedef struct tf_expert_offsets {
+    uint32_t gate_w_off, gate_s_off, gate_b_off;
+    uint32_t up_w_off, up_s_off, up_b_off;
+    uint32_t down_w_off, down_s_off, down_b_off;
+} tf_expert_offsets;
+
+/* One quantised projection: three planes + shape. Replaces
+ * SharedExpertProjection (Kernels/MoE/SharedExpertInt8.swift:9-31). */
+typedef struct tf_projection {
+    const void* weights; uint64_t weights_off;
+    const void* scales;  uint64_t scales_off;
+    const void* biases;  uint64_t biases_off;
+    uint32_t rows, cols;
+} tf_projection;
+
+/* 16-byte route pair. Replaces PrefillTokenExpertPair
+ * (Kernels/Prefill/MoE/PrefillRouter.swift:5-28); layout pinned by
+ * Tests/TurboFieldfare/Core/Kernels/Prefill/PrefillRouterTests.swift:12-19. */
+typedef struct tf_pair {
+    uint32_t token, expert, rank, weight_bits_and_reserved;
+} tf_pair;
+
+/* PrefillMoEGroup / PrefillMoETile (PrefillMoEGrouping.swift:4-31). */
+typedef struct tf_group { uint32_t expert, pair_start, pair_count; } tf_group;
+typedef struct tf_tile { uint32_t group_start, group_count, pair_start, pair_count; } tf_tile;
+
+typedef struct tf_context tf_context;
+
+/* ---- context: replaces MetalContext (Infrastructure/Metal/MetalContext.swift:51-214) ---- */
+tf_status tf_context_create(int device, tf_context** out);
+void tf_context_destroy(tf_context* ctx);
+/* Message of the last failing call on this context (or of the last failing
+ * context-less call when ctx is NULL). Never NULL. */
+const char* tf_last_error(tf_context* ctx);
+int tf_abi_version(void);
+/* Number of kernels this context has enqueued since creation (for callers that
+ * need to show that work ran on the GPU). */
+uint64_t tf_launch_count(tf_context* ctx);
+
+/* ---- stand-alone GEMVs ---- */
+/* y[m] = deq4(W[m,n]) . x[n]; x, y fp16; fp32 accumulation.
+ * Replaces DequantInt4GEMV.encode (Kernels/Quant/DequantInt4GEMV.swift:44-87):
+ * requires n % 64 == 0 and an even weights offset (:57-62). */
+tf_status tf_int4_gemv(tf_context* ctx, void* stream,
+                       const void* weights, uint64_t weights_off,
+                       const void* scales, uint64_t scales_off,
+                       const void* biases, uint64_t biases_off,
+                       const void* x, uint64_t x_off, void* y, uint64_t y_off,
+                       uint32_t m, uint32_t n, tf_dtype sb_dtype);
+/* Replaces DequantInt8GEMV.encode (Kernels/Quant/DequantInt8GEMV.swift:50-81). */
+tf_status tf_int8_gemv(tf_context* ctx, void* stream,
+                       const void* weights, uint64_t weights_off,
+                       const void* scales, uint64_t scales_off,
+                       const void* biases, uint64_t biases_off,
+                       const void* x, uint64_t x_off, void* y, uint64_t y_off,
+                       uint32_t m, uint32_t n, tf_dtype sb_dtype);
+
+/* ---- router ---- */
+/* logits = deq8(W) . (hidden * effective_scale); top-8, ties to the lower
+ * index; weights = softmax(top-8 logits) * per_expert_scale -> fp16. The ids
+ * stay on the device. Replaces MoE.encodeRouterGemma4
+ * (Kernels/MoE/MoE.swift:109-159): d % 64 == 0, num_experts <= 256, top_k == 8.
+ * out_logits (fp32 [num_experts], device) may be NULL. */
+tf_status tf_router_gemma4(tf_context* ctx, void* stream,
+                           const void* weights, uint64_t weights_off,
+                           const void* scales, uint64_t scales_off,
+                           const void* biases, uint64_t biases_off,
+                           const void* hidden,
+                           const void* effective_scale, uint64_t effective_scale_off,
+                           const void* per_expert_scale, uint64_t per_expert_scale_off,
+                           uint32_t* out_indices, void* out_weights, float* out_logits,
+                           uint32_t num_experts, uint32_t d, uint32_t top_k);
+/* The same for query_count rows with a row stride. Replaces
+ * PrefillRouter.encodeGemma4Block (Kernels/Prefill/MoE/PrefillRouter.swift:37-89):
+ * query_count > 0, num_experts <= 256, 1 <= top_k <= 64 (this library: <= 8),
+ * hidden_stride_elements >= d. hidden_dtype selects fp16 or bf16 rows.
+ * logit_bias (fp32 [num_experts], device, may be NULL) is added to the logits
+ * before selection (used to skew synthetic routing); out_logits may be NULL. */
+tf_status tf_router_gemma4_block(tf_context* ctx, void* stream,
+                                 const void* weights, uint64_t weights_off,
+                                 const void* scales, uint64_t scales_off,
+                                 const void* biases, uint64_t biases_off,
+                                 const void* hidden, uint64_t hidden_off, tf_dtype hidden_dtype,
+                                 const void* effective_scale, uint64_t effective_scale_off,
+                                 const void* per_expert_scale, uint64_t per_expert_scale_off,
+                                 const float* logit_bias,
+                                 uint32_t* out_indices, uint64_t out_indices_off,
+                                 void* out_weights, uint64_t out_weights_off, float* out_logits,
+                                 uint32_t query_count, uint32_t num_experts, uint32_t d,
+                                 uint32_t top_k, uint32_t hidden_stride_elements);
+
+/* ---- decode routed experts ---- */
+/* acts[k*f + j] = half(gelu_tanh(gate_k[j,:].x) * (up_k[j,:].x)) for the top_k
+ * blobs in the DEVICE table blobs[top_k]. Replaces
+ * MoE.encodeRoutedPersistentPhase1U16Load (Kernels/MoE/MoE.swift:180-213). */
+tf_status tf_moe_phase1(tf_context* ctx, void* stream,
+                        const void* const* blobs, const tf_expert_offsets* offsets,
+                        const void* x, void* acts, uint32_t d, uint32_t f, uint32_t top_k);
+/* Same over active_slots[active_count] (device u32). Replaces
+ * MoE.encodeRoutedPersistentPhase1SubsetU16Load (MoE.swift:215-258). */
+tf_status tf_moe_phase1_subset(tf_context* ctx, void* stream,
+                               const void* const* blobs, const tf_expert_offsets* offsets,
+                               const void* x, void* acts, uint32_t d, uint32_t f, uint32_t top_k,
+                               const uint32_t* active_slots, uint32_t active_count);
+/* y[d] = half(residual[d] + sum_k w_k * (down_k[d,:] . acts_k)), slot order.
+ * Replaces MoE.encodeRoutedPersistentPhase2Reduce (MoE.swift:260-295). */
+tf_status tf_moe_phase2_reduce(tf_context* ctx, void* stream,
+                               const void* const* blobs, const tf_expert_offsets* offsets,
+                               const void* acts, const void* routing_weights,
+                               const void* residual, void* y,
+                               uint32_t d, uint32_t f, uint32_t top_k);
+/* Fills the device table blobs[t*top_k + r] = pool_base + indices[t*top_k+r] * stride
+ * without a host round trip. Replaces Model.routedExpertBuffers /
+ * routedExpertOffsets (Runtime/Inference/ModelExpertIO.swift:21-142), whose
+ * CPU read-back of the ids exists only because experts lived on SSD. */
+tf_status tf_expert_table_from_indices(tf_context* ctx, void* stream,
+                                       const void* pool_layer_base, uint64_t expert_stride,
+                                       const uint32_t* indices, uint32_t count, uint32_t num_experts,
+                                       const void** blobs_out);
+
+/* ---- shared expert ---- */
+/* y = down(half(gelu(half(gate.x)) * half(up.x))). Replaces
+ * SharedExpertInt4.encode (Kernels/MoE/SharedExpertInt4.swift:30-93). The
+ * *_bytes arguments are the sizes of the buffers behind x, y and the three
+ * scratch pointers, checked as the reference checks MTLBuffer.length. */
+tf_status tf_shared_expert_int4(tf_context* ctx, void* stream,
+                                const void* x, uint64_t x_off, uint64_t x_bytes,
+                                const tf_projection* gate, const tf_projection* up,
+                                const tf_projection* down,
+                                void* y, uint64_t y_off, uint64_t y_bytes,
+                                void* scratch_gate, uint64_t scratch_gate_off, uint64_t scratch_gate_bytes,
+                                void* scratch_up, uint64_t scratch_up_off, uint64_t scratch_up_bytes,
+                                void* scratch_act, uint64_t scratch_act_off, uint64_t scratch_act_bytes);
+
+/* ---- routing metadata (host) ---- */
+/* Replaces PrefillRouter.makeTokenExpertPairs (PrefillRouter.swift:91-111). HOST arrays. */
+tf_status tf_make_token_expert_pairs(const uint32_t* host_indices, const uint16_t* host_weights_f16,
+                                     uint32_t query_count, uint32_t top_k, tf_pair* host_pairs_out);
+/* Validate, sort by (sort key, expert, token, rank), build offsets (UINT32_MAX
+ * when unused), counts, groups and tiles. HOST arrays; outputs sized
+ * pair_count / num_experts / pair_count / pair_count. Replaces
+ * PrefillMoEGrouping.groupTokenExpertPairs (PrefillMoEGrouping.swift:91-193). */
+tf_status tf_group_pairs(const tf_pair* host_pairs, uint32_t pair_count,
+                         int32_t query_count, int32_t top_k, int32_t num_experts,
+                         int32_t tile_expert_count,
+                         const uint64_t* host_expert_sort_keys, uint32_t sort_key_count,
+                         tf_pair* sorted_out, uint32_t* per_expert_offsets, uint32_t* per_expert_counts,
+                         tf_group* groups_out, uint32_t* group_count_out,
+                         tf_tile* tiles_out, uint32_t* tile_count_out);
+
+/* ---- norms ---- */
+/* y = half(x * rsqrt(mean(x^2) + eps) * w_bf16); weight NULL = no-scale form.
+ * Replaces RMSNorm.encode and the block form PrefillRMSNorm
+ * (Metal/Primitives/rmsnorm.metal:32-93,153-175; Metal/Prefill/prefill.metal:54-111). */
+tf_status tf_rmsnorm(tf_context* ctx, void* stream,
+                     const void* x, uint64_t x_off, const void* weight_bf16, uint64_t weight_off,
+                     void* y, uint64_t y_off, uint32_t rows, uint32_t d,
+                     uint32_t stride_elements, float eps, tf_dtype act_dtype);
+/* hidden = (hidden + rms(h1 + rms(h2) * w2) * w) * layer_scalar with fp16
+ * rounding at each stage. Replaces FusedLayerTail / PrefillLayerTail
+ * (Metal/Fusions/fused.metal:271-375; Metal/Prefill/prefill.metal:255-334). */
+tf_status tf_layer_tail(tf_context* ctx, void* stream,
+                        const void* h2, const void* h1, void* hidden,
+                        const void* w_postffn2_bf16, const void* w_postffn_bf16,
+                        uint32_t rows, uint32_t d, uint32_t stride_elements,
+                        float eps, float layer_scalar);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TURBOFIELDFARE_CUDA_H */

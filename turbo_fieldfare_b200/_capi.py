@@ -1,0 +1,97 @@
+"""ctypes binding of ``libtfcuda.so`` (declared in ``include/turbofieldfare_cuda.h``).
+
+There is no CPU fallback and no JIT: if the in-tree shared library is missing
+the import fails with an instruction to build it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+LIB_PATH = PKG / "_lib" / "libtfcuda.so"
+HEADER_PATH = PKG.parent / "include" / "turbofieldfare_cuda.h"
+
+TF_BF16, TF_FP16 = 0, 1
+TF_MAX_TOP_K = 8
+
+vp, u32, u64, i32, f32 = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int32, C.c_float
+
+
+class ExpertOffsets(C.Structure):
+    """tf_expert_offsets: nine byte offsets (MoEExpertOffsets, Kernels/MoE/MoE.swift:4-29)."""
+    _fields_ = [(n, u32) for n in ("gate_w_off", "gate_s_off", "gate_b_off", "up_w_off", "up_s_off", "up_b_off",
+                                   "down_w_off", "down_s_off", "down_b_off")]
+
+
+class Projection(C.Structure):
+    """tf_projection (SharedExpertProjection, Kernels/MoE/SharedExpertInt8.swift:9-31)."""
+    _fields_ = [("weights", vp), ("weights_off", u64), ("scales", vp), ("scales_off", u64),
+                ("biases", vp), ("biases_off", u64), ("rows", u32), ("cols", u32)]
+
+
+class Pair(C.Structure):
+    """tf_pair (PrefillTokenExpertPair, Kernels/Prefill/MoE/PrefillRouter.swift:5-28)."""
+    _fields_ = [("token", u32), ("expert", u32), ("rank", u32), ("weight_bits_and_reserved", u32)]
+
+
+class Group(C.Structure):
+    _fields_ = [("expert", u32), ("pair_start", u32), ("pair_count", u32)]
+
+
+class Tile(C.Structure):
+    _fields_ = [("group_start", u32), ("group_count", u32), ("pair_start", u32), ("pair_count", u32)]
+
+
+_PLANES = [vp, u64, vp, u64, vp, u64]   # weights, scales, biases with offsets
+
+SIGNATURES = {
+    "tf_abi_version": (C.c_int, []),
+    "tf_context_create": (C.c_int, [C.c_int, C.POINTER(vp)]),
+    "tf_context_destroy": (None, [vp]),
+    "tf_last_error": (C.c_char_p, [vp]),
+    "tf_launch_count": (u64, [vp]),
+    "tf_int4_gemv": (C.c_int, [vp, vp, *_PLANES, vp, u64, vp, u64, u32, u32, C.c_int]),
+    "tf_int8_gemv": (C.c_int, [vp, vp, *_PLANES, vp, u64, vp, u64, u32, u32, C.c_int]),
+    "tf_router_gemma4": (C.c_int, [vp, vp, *_PLANES, vp, vp, u64, vp, u64, vp, vp, vp, u32, u32, u32]),
+    "tf_router_gemma4_block": (C.c_int, [vp, vp, *_PLANES, vp, u64, C.c_int, vp, u64, vp, u64, vp,
+                                         vp, u64, vp, u64, vp, u32, u32, u32, u32, u32]),
+    "tf_moe_phase1": (C.c_int, [vp, vp, vp, C.POINTER(ExpertOffsets), vp, vp, u32, u32, u32]),
+    "tf_moe_phase1_subset": (C.c_int, [vp, vp, vp, C.POINTER(ExpertOffsets), vp, vp, u32, u32, u32, vp, u32]),
+    "tf_moe_phase2_reduce": (C.c_int, [vp, vp, vp, C.POINTER(ExpertOffsets), vp, vp, vp, vp, u32, u32, u32]),
+    "tf_expert_table_from_indices": (C.c_int, [vp, vp, vp, u64, vp, u32, u32, vp]),
+    "tf_shared_expert_int4": (C.c_int, [vp, vp, vp, u64, u64, C.POINTER(Projection), C.POINTER(Projection),
+                                        C.POINTER(Projection), vp, u64, u64, vp, u64, u64, vp, u64, u64, vp, u64, u64]),
+    "tf_make_token_expert_pairs": (C.c_int, [vp, vp, u32, u32, vp]),
+    "tf_group_pairs": (C.c_int, [vp, u32, i32, i32, i32, i32, vp, u32, vp, vp, vp, vp, C.POINTER(u32), vp, C.POINTER(u32)]),
+    "tf_rmsnorm": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, u32, u32, u32, f32, C.c_int]),
+    "tf_layer_tail": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, f32, f32]),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Load the in-tree library and attach the signatures. Raises if it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m turbo_fieldfare_b200.build` "
+            "(nvcc, sm_100a). There is no CPU or PyTorch fallback for this library.")
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        fn = getattr(lib, name)   # AttributeError if the symbol is not exported
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def declared_functions() -> list[str]:
+    """Names of every function declared in the public header."""
+    import re
+    text = HEADER_PATH.read_text()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(tf_[a-z0-9_]+)\s*\(", text)))

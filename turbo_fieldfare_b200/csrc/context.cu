@@ -1,0 +1,102 @@
+// Context and error reporting. Replaces the device/queue/pipeline-cache role of
+// MetalContext (Infrastructure/Metal/MetalContext.swift:51-214): CUDA kernels
+// are compiled ahead of time, so the context only pins a device, owns the small
+// router scratch and records errors.
+#include "tf_common.cuh"
+
+namespace tf {
+
+std::string& global_error() {
+    static std::string s;
+    return s;
+}
+
+static std::mutex& err_mutex() {
+    static std::mutex m;
+    return m;
+}
+
+void set_global_error(const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    std::lock_guard<std::mutex> lock(err_mutex());
+    global_error() = buf;
+}
+
+tf_status fail(tf_context* ctx, tf_status code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    std::lock_guard<std::mutex> lock(err_mutex());
+    if (ctx) ctx->last_error = buf;
+    global_error() = buf;
+    return code;
+}
+
+tf_status check_launch(tf_context* ctx, const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(ctx, TF_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
+    if (ctx) ctx->launches += 1;
+    return TF_OK;
+}
+
+}  // namespace tf
+
+extern "C" {
+
+int tf_abi_version(void) { return TF_ABI_VERSION; }
+
+tf_status tf_context_create(int device, tf_context** out) {
+    if (!out) return tf::fail(nullptr, TF_ERR_INVALID_ARGUMENT, "tf_context_create: out is NULL");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0)
+        return tf::fail(nullptr, TF_ERR_NO_DEVICE, "no CUDA device: %s (this library has no CPU fallback)",
+                        e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+    if (device < 0 || device >= count)
+        return tf::fail(nullptr, TF_ERR_INVALID_ARGUMENT, "device %d out of range (0..%d)", device, count - 1);
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return tf::fail(nullptr, TF_ERR_CUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+    if (prop.major != 10)
+        return tf::fail(nullptr, TF_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only",
+                        device, prop.major, prop.minor);
+    e = cudaSetDevice(device);
+    if (e != cudaSuccess) return tf::fail(nullptr, TF_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
+    tf_context* ctx = new tf_context();
+    ctx->device = device;
+    ctx->sm_count = prop.multiProcessorCount;
+    e = cudaMalloc(&ctx->router_logits, sizeof(float) * tf::kRouterSplitRows * TF_MAX_ROUTER_EXPERTS);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->router_tickets, sizeof(unsigned int) * tf::kRouterSplitRows);
+    if (e == cudaSuccess) e = cudaMemset(ctx->router_tickets, 0, sizeof(unsigned int) * tf::kRouterSplitRows);
+    if (e != cudaSuccess) {
+        tf_status s = tf::fail(nullptr, TF_ERR_OUT_OF_MEMORY, "context scratch: %s", cudaGetErrorString(e));
+        tf_context_destroy(ctx);
+        return s;
+    }
+    *out = ctx;
+    return TF_OK;
+}
+
+void tf_context_destroy(tf_context* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->router_logits) cudaFree(ctx->router_logits);
+    if (ctx->router_tickets) cudaFree(ctx->router_tickets);
+    delete ctx;
+}
+
+const char* tf_last_error(tf_context* ctx) {
+    if (ctx) return ctx->last_error.c_str();
+    return tf::global_error().c_str();
+}
+
+uint64_t tf_launch_count(tf_context* ctx) { return ctx ? ctx->launches : 0; }
+
+}  // extern "C"

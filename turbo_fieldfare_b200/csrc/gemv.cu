@@ -1,0 +1,112 @@
+// Stand-alone affine GEMVs: y[m] = deq(W[m,n]) . x[n], fp16 in/out, fp32 accumulate.
+// Replaces dequant_int4_gemv_simd / dequant_int8_gemv_simd
+// (Metal/Quant/dequant_int4.metal:93-191, Metal/Quant/dequant_int8.metal:57-97).
+//
+// One warp per row, rows strided over a grid sized to the SM count; x is staged
+// once per block in shared memory; packed weights stream through 128-bit
+// non-allocating loads when the plane is 16-byte aligned, 16-bit loads otherwise.
+#include "rowdot.cuh"
+
+namespace tf {
+
+constexpr int kGemvThreads = 256;
+constexpr int kGemvWarps = kGemvThreads / kWarp;
+
+template <int BITS, bool SB_FP16, bool A16>
+__global__ void __launch_bounds__(kGemvThreads)
+affine_gemv_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, const uint16_t* __restrict__ B,
+                   const uint16_t* __restrict__ x, uint16_t* __restrict__ y, uint32_t m, uint32_t n, bool a4) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint16_t* xs = reinterpret_cast<uint16_t*>(smem);
+    float* xsum16 = xsum_ptr(xs, (int)n);
+    stage_x<false>(x, xs, xsum16, (int)n);
+
+    const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const uint32_t groups = n / kGroup;
+    const size_t row_bytes = BITS == 4 ? n / 2 : n;
+    for (uint32_t row = blockIdx.x * kGemvWarps + warp; row < m; row += gridDim.x * kGemvWarps) {
+        const uint8_t* Wrow = W + (size_t)row * row_bytes;
+        const uint16_t* s_row = S + (size_t)row * groups;
+        const uint16_t* b_row = B + (size_t)row * groups;
+        float acc;
+        if constexpr (BITS == 4) {
+            if constexpr (A16) acc = int4_row_partial_a16<SB_FP16, false>(Wrow, s_row, b_row, xs, xsum16, (int)n, lane);
+            else acc = int4_row_partial_a2<SB_FP16, false>(Wrow, s_row, b_row, xs, (int)n, lane);
+        } else {
+            acc = int8_row_partial<SB_FP16, false>(Wrow, s_row, b_row, xs, (int)n, lane, a4);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) y[row] = __half_as_ushort(__float2half_rn(acc));
+    }
+}
+
+template <int BITS>
+static tf_status launch_gemv(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off,
+                             const void* scales, uint64_t scales_off, const void* biases, uint64_t biases_off,
+                             const void* x, uint64_t x_off, void* y, uint64_t y_off, uint32_t m, uint32_t n,
+                             tf_dtype sb_dtype, const char* name) {
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, weights && scales && biases && x && y, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, m > 0 && n > 0, TF_ERR_INVALID_ARGUMENT, "%s: m and n must be positive", name);
+    TF_REQUIRE(ctx, n % kGroup == 0, TF_ERR_INVALID_ARGUMENT, "%s: N=%u must be a multiple of %d", name, n, kGroup);
+    TF_REQUIRE(ctx, sb_dtype == TF_BF16 || sb_dtype == TF_FP16, TF_ERR_INVALID_ARGUMENT, "%s: bad sb_dtype", name);
+    const uint8_t* W = byte_ptr(weights, weights_off);
+    const uint8_t* S = byte_ptr(scales, scales_off);
+    const uint8_t* Bp = byte_ptr(biases, biases_off);
+    const uint8_t* xp = byte_ptr(x, x_off);
+    uint8_t* yp = byte_ptr(y, y_off);
+    if (BITS == 4)
+        TF_REQUIRE(ctx, aligned(W, 2), TF_ERR_ALIGNMENT, "%s: weightsOffset must be even", name);
+    TF_REQUIRE(ctx, aligned(S, 2) && aligned(Bp, 2) && aligned(xp, 2) && aligned(yp, 2), TF_ERR_ALIGNMENT,
+               "%s: scale/bias/x/y planes must be 2-byte aligned", name);
+    const size_t smem = stage_x_bytes((int)n);
+    TF_REQUIRE(ctx, smem <= 96 * 1024, TF_ERR_UNSUPPORTED, "%s: N=%u too large for the staged-x kernel", name, n);
+
+    const size_t row_bytes = BITS == 4 ? n / 2 : n;
+    const bool a16 = aligned(W, 16) && row_bytes % 16 == 0;
+    const bool a4 = aligned(W, 4) && row_bytes % 4 == 0;
+    const uint32_t blocks_needed = (m + kGemvWarps - 1) / kGemvWarps;
+    const uint32_t grid = blocks_needed < (uint32_t)ctx->sm_count * 8u ? blocks_needed : (uint32_t)ctx->sm_count * 8u;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool fp16 = sb_dtype == TF_FP16;
+
+#define TF_GEMV_LAUNCH(SB, A)                                                                          \
+    do {                                                                                               \
+        auto k = affine_gemv_kernel<BITS, SB, A>;                                                      \
+        if (smem > 48 * 1024) TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        k<<<grid, kGemvThreads, smem, st>>>(W, reinterpret_cast<const uint16_t*>(S),                   \
+                                            reinterpret_cast<const uint16_t*>(Bp),                      \
+                                            reinterpret_cast<const uint16_t*>(xp),                      \
+                                            reinterpret_cast<uint16_t*>(yp), m, n, a4);                 \
+    } while (0)
+
+    if (BITS == 4 && a16) {
+        if (fp16) TF_GEMV_LAUNCH(true, true); else TF_GEMV_LAUNCH(false, true);
+    } else {
+        if (fp16) TF_GEMV_LAUNCH(true, false); else TF_GEMV_LAUNCH(false, false);
+    }
+#undef TF_GEMV_LAUNCH
+    return check_launch(ctx, name);
+}
+
+}  // namespace tf
+
+extern "C" {
+
+tf_status tf_int4_gemv(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off,
+                       const void* scales, uint64_t scales_off, const void* biases, uint64_t biases_off,
+                       const void* x, uint64_t x_off, void* y, uint64_t y_off,
+                       uint32_t m, uint32_t n, tf_dtype sb_dtype) {
+    return tf::launch_gemv<4>(ctx, stream, weights, weights_off, scales, scales_off, biases, biases_off,
+                              x, x_off, y, y_off, m, n, sb_dtype, "tf_int4_gemv");
+}
+
+tf_status tf_int8_gemv(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off,
+                       const void* scales, uint64_t scales_off, const void* biases, uint64_t biases_off,
+                       const void* x, uint64_t x_off, void* y, uint64_t y_off,
+                       uint32_t m, uint32_t n, tf_dtype sb_dtype) {
+    return tf::launch_gemv<8>(ctx, stream, weights, weights_off, scales, scales_off, biases, biases_off,
+                              x, x_off, y, y_off, m, n, sb_dtype, "tf_int8_gemv");
+}
+
+}  // extern "C"

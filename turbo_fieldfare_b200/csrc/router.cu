@@ -1,0 +1,263 @@
+// Router: 8-bit affine GEMV + top-k + softmax in ONE launch, ids stay on the device.
+// Replaces router_gemv_gemma4_r4 + router_topk_select_k8 (Metal/MoE/moe.metal:78-185)
+// and prefill_router_gemma4_block (Metal/Prefill/prefill.metal:478-573).
+//
+// Logit arithmetic is canonical so that a CPU emulation reproduces every bit
+// (top-k indices must match exactly):
+//   xf[i]  = fmul(float(hidden[i]), float(effective_scale[i]))
+//   lane l, group g: i0 = 64 g + 2 l
+//     p   = fma(q1, xf[i0+1], fmul(q0, xf[i0]))
+//     acc = fma(s, p, acc);  acc = fma(b, fadd(xf[i0], xf[i0+1]), acc)
+//   logit = xor-butterfly sum over the 32 lanes (offsets 16, 8, 4, 2, 1)
+// which is the reference kernel's per-lane element assignment with the
+// contraction and reduction order fixed.
+#include "tf_common.cuh"
+
+namespace tf {
+
+constexpr int kSplitExpertsPerBlock = 4;
+constexpr int kSplitThreads = kSplitExpertsPerBlock * kWarp;
+constexpr int kBlockRouterThreads = 256;
+
+template <bool X_BF16>
+__device__ __forceinline__ void stage_router_x(const uint16_t* __restrict__ hidden, const uint16_t* __restrict__ eff,
+                                               float* xf, uint32_t d) {
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+        const float h = X_BF16 ? bf16_bits_to_float(hidden[i]) : f16_bits_to_float(hidden[i]);
+        xf[i] = __fmul_rn(h, bf16_bits_to_float(eff[i]));
+    }
+    __syncthreads();
+}
+
+__device__ __forceinline__ float router_row_logit(const uint8_t* __restrict__ Wrow, const uint16_t* __restrict__ s_row,
+                                                  const uint16_t* __restrict__ b_row, const float* xf,
+                                                  uint32_t groups, int lane, bool a2) {
+    float acc = 0.0f;
+    for (uint32_t g = 0; g < groups; ++g) {
+        const uint32_t i0 = g * kGroup + lane * 2;
+        uint32_t w;
+        if (a2) w = *reinterpret_cast<const uint16_t*>(Wrow + i0);
+        else w = (uint32_t)Wrow[i0] | ((uint32_t)Wrow[i0 + 1] << 8);
+        const float q0 = (float)(w & 0xFFu), q1 = (float)(w >> 8);
+        const float2 xv = *reinterpret_cast<const float2*>(xf + i0);
+        const float s = bf16_bits_to_float(s_row[g]);
+        const float b = bf16_bits_to_float(b_row[g]);
+        const float p = __fmaf_rn(q1, xv.y, __fmul_rn(q0, xv.x));
+        acc = __fmaf_rn(s, p, acc);
+        acc = __fmaf_rn(b, __fadd_rn(xv.x, xv.y), acc);
+    }
+    return warp_sum(acc);
+}
+
+// Warp-parallel top-k over logits in shared memory: k rounds of arg-max with
+// ties to the lower index, i.e. the first k entries of the order
+// (score desc, index asc) — the result of the reference's insertion scan
+// (moe.metal:152-166). Then softmax over the selected scores times the
+// per-expert gain, rounded to fp16 (moe.metal:168-184). Called by warp 0.
+__device__ __forceinline__ void warp_select_topk(float* scores /*shared, clobbered*/, uint32_t num_experts, uint32_t top_k,
+                                                 const uint16_t* __restrict__ per_expert_scale,
+                                                 uint32_t* __restrict__ out_idx, uint16_t* __restrict__ out_w, int lane) {
+    float sel_score[TF_MAX_TOP_K];
+    uint32_t sel_idx[TF_MAX_TOP_K];
+    for (uint32_t r = 0; r < top_k; ++r) {
+        float best = -INFINITY;
+        uint32_t best_e = 0xFFFFFFFFu;
+        for (uint32_t e = lane; e < num_experts; e += kWarp) {
+            const float s = scores[e];
+            if (s > best || (s == best && e < best_e)) { best = s; best_e = e; }
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float os = __shfl_xor_sync(kFullMask, best, off);
+            const uint32_t oe = __shfl_xor_sync(kFullMask, best_e, off);
+            if (os > best || (os == best && oe < best_e)) { best = os; best_e = oe; }
+        }
+        if (best_e == 0xFFFFFFFFu) best_e = 0;   // fewer finite candidates than top_k
+        sel_score[r] = best;
+        sel_idx[r] = best_e;
+        if (lane == 0 && best_e < num_experts) scores[best_e] = -INFINITY;   // NaN-free inputs: -inf never wins again before real scores
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const float max_s = sel_score[0];
+        float exps[TF_MAX_TOP_K];
+        float sum_exp = 0.0f;
+        for (uint32_t r = 0; r < top_k; ++r) { exps[r] = expf(sel_score[r] - max_s); sum_exp += exps[r]; }
+        for (uint32_t r = 0; r < top_k; ++r) {
+            const float w = exps[r] / sum_exp * bf16_bits_to_float(per_expert_scale[sel_idx[r]]);
+            out_idx[r] = sel_idx[r];
+            out_w[r] = __half_as_ushort(__float2half_rn(w));
+        }
+    }
+}
+
+// Few rows (decode): grid (rows, experts/4); the last block to finish a row
+// (self-resetting ticket) runs the selection, so one launch does everything.
+template <bool X_BF16>
+__global__ void __launch_bounds__(kSplitThreads)
+router_split_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, const uint16_t* __restrict__ B,
+                    const uint16_t* __restrict__ hidden, uint32_t hidden_stride,
+                    const uint16_t* __restrict__ eff, const uint16_t* __restrict__ per_expert_scale,
+                    const float* __restrict__ logit_bias,
+                    uint32_t* __restrict__ out_idx, uint16_t* __restrict__ out_w, float* __restrict__ out_logits,
+                    float* scratch_logits, unsigned int* tickets,
+                    uint32_t num_experts, uint32_t d, uint32_t top_k, bool a2) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    float* xf = reinterpret_cast<float*>(smem);
+    __shared__ float scores[TF_MAX_ROUTER_EXPERTS];
+    __shared__ bool is_last;
+    const uint32_t row = blockIdx.x;
+    stage_router_x<X_BF16>(hidden + (size_t)row * hidden_stride, eff, xf, d);
+
+    const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const uint32_t groups = d / kGroup;
+    const uint32_t e = blockIdx.y * kSplitExpertsPerBlock + warp;
+    if (e < num_experts) {
+        float logit = router_row_logit(W + (size_t)e * d, S + (size_t)e * groups, B + (size_t)e * groups, xf, groups, lane, a2);
+        if (logit_bias) logit = __fadd_rn(logit, logit_bias[e]);
+        if (lane == 0) scratch_logits[(size_t)row * TF_MAX_ROUTER_EXPERTS + e] = logit;
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int t = atomicAdd(&tickets[row], 1u);
+        is_last = (t == gridDim.y - 1);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (uint32_t i = threadIdx.x; i < num_experts; i += blockDim.x) {
+        const float v = __ldcg(&scratch_logits[(size_t)row * TF_MAX_ROUTER_EXPERTS + i]);
+        scores[i] = v;
+        if (out_logits) out_logits[(size_t)row * num_experts + i] = v;
+    }
+    if (threadIdx.x == 0) tickets[row] = 0;   // ready for the next launch on this stream
+    __syncthreads();
+    if (warp == 0)
+        warp_select_topk(scores, num_experts, top_k, per_expert_scale, out_idx + (size_t)row * top_k,
+                         out_w + (size_t)row * top_k, lane);
+}
+
+// Many rows (batched decode, prefill): one block per row.
+template <bool X_BF16>
+__global__ void __launch_bounds__(kBlockRouterThreads)
+router_block_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, const uint16_t* __restrict__ B,
+                    const uint16_t* __restrict__ hidden, uint32_t hidden_stride,
+                    const uint16_t* __restrict__ eff, const uint16_t* __restrict__ per_expert_scale,
+                    const float* __restrict__ logit_bias,
+                    uint32_t* __restrict__ out_idx, uint16_t* __restrict__ out_w, float* __restrict__ out_logits,
+                    uint32_t num_experts, uint32_t d, uint32_t top_k, bool a2) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    float* xf = reinterpret_cast<float*>(smem);
+    __shared__ float scores[TF_MAX_ROUTER_EXPERTS];
+    const uint32_t row = blockIdx.x;
+    stage_router_x<X_BF16>(hidden + (size_t)row * hidden_stride, eff, xf, d);
+    const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const uint32_t groups = d / kGroup;
+    for (uint32_t e = warp; e < num_experts; e += kBlockRouterThreads / kWarp) {
+        float logit = router_row_logit(W + (size_t)e * d, S + (size_t)e * groups, B + (size_t)e * groups, xf, groups, lane, a2);
+        if (logit_bias) logit = __fadd_rn(logit, logit_bias[e]);
+        if (lane == 0) {
+            scores[e] = logit;
+            if (out_logits) out_logits[(size_t)row * num_experts + e] = logit;
+        }
+    }
+    __syncthreads();
+    if (warp == 0)
+        warp_select_topk(scores, num_experts, top_k, per_expert_scale, out_idx + (size_t)row * top_k,
+                         out_w + (size_t)row * top_k, lane);
+}
+
+static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, const uint8_t* S, const uint8_t* B,
+                               const uint8_t* hidden, tf_dtype hidden_dtype, const uint8_t* eff, const uint8_t* pes,
+                               const float* logit_bias, uint32_t* out_idx, uint8_t* out_w, float* out_logits,
+                               uint32_t rows, uint32_t num_experts, uint32_t d, uint32_t top_k, uint32_t stride,
+                               const char* name) {
+    TF_REQUIRE(ctx, aligned(S, 2) && aligned(B, 2) && aligned(hidden, 2) && aligned(eff, 2) && aligned(pes, 2) &&
+                        aligned(out_w, 2) && aligned(out_idx, 4),
+               TF_ERR_ALIGNMENT, "%s: 16-bit planes must be 2-byte aligned, indices 4-byte aligned", name);
+    const bool a2 = aligned(W, 2);
+    const size_t smem = (size_t)d * sizeof(float);
+    TF_REQUIRE(ctx, smem <= 160 * 1024, TF_ERR_UNSUPPORTED, "%s: D=%u too large", name, d);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const bool bf = hidden_dtype == TF_BF16;
+    auto Sp = reinterpret_cast<const uint16_t*>(S);
+    auto Bp = reinterpret_cast<const uint16_t*>(B);
+    auto hp = reinterpret_cast<const uint16_t*>(hidden);
+    auto ep = reinterpret_cast<const uint16_t*>(eff);
+    auto pp = reinterpret_cast<const uint16_t*>(pes);
+    auto wp = reinterpret_cast<uint16_t*>(out_w);
+    if (rows <= (uint32_t)kRouterSplitRows) {
+        dim3 grid(rows, (num_experts + kSplitExpertsPerBlock - 1) / kSplitExpertsPerBlock);
+        auto k = bf ? router_split_kernel<true> : router_split_kernel<false>;
+        if (smem > 40 * 1024) TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<grid, kSplitThreads, smem, st>>>(W, Sp, Bp, hp, stride, ep, pp, logit_bias, out_idx, wp, out_logits,
+                                             ctx->router_logits, ctx->router_tickets, num_experts, d, top_k, a2);
+    } else {
+        auto k = bf ? router_block_kernel<true> : router_block_kernel<false>;
+        if (smem > 40 * 1024) TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k<<<rows, kBlockRouterThreads, smem, st>>>(W, Sp, Bp, hp, stride, ep, pp, logit_bias, out_idx, wp, out_logits,
+                                                   num_experts, d, top_k, a2);
+    }
+    return check_launch(ctx, name);
+}
+
+}  // namespace tf
+
+extern "C" {
+
+tf_status tf_router_gemma4(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off,
+                           const void* scales, uint64_t scales_off, const void* biases, uint64_t biases_off,
+                           const void* hidden, const void* effective_scale, uint64_t effective_scale_off,
+                           const void* per_expert_scale, uint64_t per_expert_scale_off,
+                           uint32_t* out_indices, void* out_weights, float* out_logits,
+                           uint32_t num_experts, uint32_t d, uint32_t top_k) {
+    const char* name = "tf_router_gemma4";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, weights && scales && biases && hidden && effective_scale && per_expert_scale && out_indices && out_weights,
+               TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, d > 0 && d % tf::kGroup == 0, TF_ERR_INVALID_ARGUMENT, "%s: D=%u must be a multiple of 64", name, d);
+    TF_REQUIRE(ctx, num_experts > 0 && num_experts <= TF_MAX_ROUTER_EXPERTS, TF_ERR_INVALID_ARGUMENT,
+               "%s: numExperts=%u must be in 1...256", name, num_experts);
+    TF_REQUIRE(ctx, top_k == TF_MAX_TOP_K, TF_ERR_INVALID_ARGUMENT, "%s: topK must be 8, got %u", name, top_k);
+    TF_REQUIRE(ctx, num_experts >= top_k, TF_ERR_INVALID_ARGUMENT, "%s: numExperts < topK", name);
+    return tf::launch_router(ctx, stream, tf::byte_ptr(weights, weights_off), tf::byte_ptr(scales, scales_off),
+                             tf::byte_ptr(biases, biases_off), static_cast<const uint8_t*>(hidden), TF_FP16,
+                             tf::byte_ptr(effective_scale, effective_scale_off),
+                             tf::byte_ptr(per_expert_scale, per_expert_scale_off), nullptr, out_indices,
+                             static_cast<uint8_t*>(out_weights), out_logits, 1, num_experts, d, top_k, d, name);
+}
+
+tf_status tf_router_gemma4_block(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off,
+                                 const void* scales, uint64_t scales_off, const void* biases, uint64_t biases_off,
+                                 const void* hidden, uint64_t hidden_off, tf_dtype hidden_dtype,
+                                 const void* effective_scale, uint64_t effective_scale_off,
+                                 const void* per_expert_scale, uint64_t per_expert_scale_off,
+                                 const float* logit_bias,
+                                 uint32_t* out_indices, uint64_t out_indices_off,
+                                 void* out_weights, uint64_t out_weights_off, float* out_logits,
+                                 uint32_t query_count, uint32_t num_experts, uint32_t d,
+                                 uint32_t top_k, uint32_t hidden_stride_elements) {
+    const char* name = "tf_router_gemma4_block";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, weights && scales && biases && hidden && effective_scale && per_expert_scale && out_indices && out_weights,
+               TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, query_count > 0, TF_ERR_INVALID_ARGUMENT, "%s: queryCount must be positive", name);
+    TF_REQUIRE(ctx, num_experts > 0 && num_experts <= TF_MAX_ROUTER_EXPERTS, TF_ERR_INVALID_ARGUMENT,
+               "%s: numExperts > 256 is not supported", name);
+    TF_REQUIRE(ctx, top_k > 0 && top_k <= TF_MAX_TOP_K, TF_ERR_INVALID_ARGUMENT,
+               "%s: topK must be in 1...%d, got %u", name, TF_MAX_TOP_K, top_k);
+    TF_REQUIRE(ctx, num_experts >= top_k, TF_ERR_INVALID_ARGUMENT, "%s: numExperts < topK", name);
+    TF_REQUIRE(ctx, d > 0 && d % tf::kGroup == 0, TF_ERR_INVALID_ARGUMENT, "%s: D must be a multiple of 64", name);
+    TF_REQUIRE(ctx, hidden_stride_elements >= d, TF_ERR_INVALID_ARGUMENT, "%s: hidden stride is too small", name);
+    TF_REQUIRE(ctx, hidden_dtype == TF_FP16 || hidden_dtype == TF_BF16, TF_ERR_INVALID_ARGUMENT, "%s: bad hidden dtype", name);
+    return tf::launch_router(ctx, stream, tf::byte_ptr(weights, weights_off), tf::byte_ptr(scales, scales_off),
+                             tf::byte_ptr(biases, biases_off), tf::byte_ptr(hidden, hidden_off), hidden_dtype,
+                             tf::byte_ptr(effective_scale, effective_scale_off),
+                             tf::byte_ptr(per_expert_scale, per_expert_scale_off), logit_bias,
+                             reinterpret_cast<uint32_t*>(tf::byte_ptr(static_cast<void*>(out_indices), out_indices_off)),
+                             tf::byte_ptr(out_weights, out_weights_off), out_logits, query_count, num_experts, d, top_k,
+                             hidden_stride_elements, name);
+}
+
+}  // extern "C"

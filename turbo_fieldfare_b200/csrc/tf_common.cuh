@@ -1,0 +1,100 @@
+// Shared device/host helpers for the sm_100a routed-expert kernels.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+#include <string>
+
+#include "turbofieldfare_cuda.h"
+
+namespace tf {
+
+constexpr int kGroup = TF_GROUP_SIZE;
+constexpr int kWarp = 32;
+constexpr unsigned kFullMask = 0xFFFFFFFFu;
+constexpr int kRouterSplitRows = 64;   // rows served by the multi-block decode router
+
+// ---------------------------------------------------------------------------
+// host side: context and error plumbing
+// ---------------------------------------------------------------------------
+
+std::string& global_error();
+void set_global_error(const char* fmt, ...);
+
+}  // namespace tf
+
+struct tf_context {
+    int device = 0;
+    int sm_count = 0;
+    uint64_t launches = 0;
+    std::string last_error;
+    // Router scratch owned by the context, like the 1 KiB logits buffer the
+    // reference's MoE wrapper owns (Kernels/MoE/MoE.swift:92-106).
+    float* router_logits = nullptr;        // [kRouterSplitRows, 256]
+    unsigned int* router_tickets = nullptr;  // [kRouterSplitRows], self-resetting
+};
+
+namespace tf {
+
+tf_status fail(tf_context* ctx, tf_status code, const char* fmt, ...);
+tf_status check_launch(tf_context* ctx, const char* what);
+
+#define TF_REQUIRE(ctx, cond, code, ...)                      \
+    do {                                                      \
+        if (!(cond)) return ::tf::fail((ctx), (code), __VA_ARGS__); \
+    } while (0)
+
+#define TF_CUDA(ctx, expr)                                                          \
+    do {                                                                            \
+        cudaError_t _e = (expr);                                                    \
+        if (_e != cudaSuccess)                                                      \
+            return ::tf::fail((ctx), TF_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(_e)); \
+    } while (0)
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+inline const uint8_t* byte_ptr(const void* p, uint64_t off) { return static_cast<const uint8_t*>(p) + off; }
+inline uint8_t* byte_ptr(void* p, uint64_t off) { return static_cast<uint8_t*>(p) + off; }
+
+// ---------------------------------------------------------------------------
+// device helpers
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ float bf16_bits_to_float(uint16_t b) { return __uint_as_float(static_cast<uint32_t>(b) << 16); }
+__device__ __forceinline__ float f16_bits_to_float(uint16_t b) { return __half2float(__ushort_as_half(b)); }
+
+template <bool SB_FP16>
+__device__ __forceinline__ float sb_to_float(uint16_t b) {
+    if constexpr (SB_FP16) return f16_bits_to_float(b);
+    else return bf16_bits_to_float(b);
+}
+
+// Fixed xor-butterfly: every lane ends with the same bits, and the order is the
+// one the CPU oracle emulates for the router logits.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(kFullMask, v, off));
+    return v;
+}
+
+// tanh GELU with the inner argument clamped to +-20 (Metal/MoE/moe.metal:53-60).
+__device__ __forceinline__ float gelu_tanh(float x) {
+    const float x3 = x * x * x;
+    float inner = 0.7978845608028654f * (x + 0.044715f * x3);
+    inner = fminf(fmaxf(inner, -20.0f), 20.0f);
+    return 0.5f * x * (1.0f + tanhf(inner));
+}
+
+__device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+}  // namespace tf

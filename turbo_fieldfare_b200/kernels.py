@@ -1,0 +1,310 @@
+"""Host-side mirror of the reference's operator classes over the C ABI.
+
+Class and method names follow the Swift wrappers in
+``Sources/TurboFieldfare/Kernels`` (``MoE.encodeRouterGemma4``,
+``DequantInt4GEMV.encode`` ...). A ``torch.Tensor`` on the CUDA device stands in
+for an ``MTLBuffer`` and a CUDA stream for the command buffer; every call only
+enqueues work. Errors the reference raises as preconditions or thrown enums
+arrive as :class:`TFError` carrying the C status code.
+
+torch is used for device memory and streams only; no torch operator computes
+anything on this path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from . import _capi
+from ._capi import ExpertOffsets, Projection, TF_BF16, TF_FP16
+
+
+class TFError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"[tf_status {status}] {message}")
+        self.status = status
+        self.message = message
+
+
+def _ptr(t) -> int | None:
+    if t is None:
+        return None
+    if isinstance(t, torch.Tensor):
+        return t.data_ptr()
+    return int(t)
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, torch.cuda.Stream):
+        return stream.cuda_stream
+    return int(stream)
+
+
+class TurboContext:
+    """Replaces ``MetalContext`` (Infrastructure/Metal/MetalContext.swift:51-214)."""
+
+    def __init__(self, device: int = 0):
+        self.lib = _capi.load()
+        handle = C.c_void_p()
+        status = self.lib.tf_context_create(device, C.byref(handle))
+        if status != 0:
+            raise TFError(status, self.lib.tf_last_error(None).decode())
+        self.handle = handle
+        self.device = device
+
+    def check(self, status: int) -> None:
+        if status != 0:
+            raise TFError(status, self.lib.tf_last_error(self.handle).decode())
+
+    @property
+    def launch_count(self) -> int:
+        return int(self.lib.tf_launch_count(self.handle))
+
+    def close(self) -> None:
+        if getattr(self, "handle", None):
+            self.lib.tf_context_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+@dataclass
+class SharedExpertProjection:
+    """(weights, scales, biases) buffers + byte offsets + shape (SharedExpertInt8.swift:9-31)."""
+    weights: torch.Tensor
+    scales: torch.Tensor
+    biases: torch.Tensor
+    rows: int
+    cols: int
+    weights_offset: int = 0
+    scales_offset: int = 0
+    biases_offset: int = 0
+
+    def c_struct(self) -> Projection:
+        return Projection(_ptr(self.weights), self.weights_offset, _ptr(self.scales), self.scales_offset,
+                          _ptr(self.biases), self.biases_offset, self.rows, self.cols)
+
+
+class DequantInt4GEMV:
+    """``DequantInt4GEMV`` (Kernels/Quant/DequantInt4GEMV.swift:5-88)."""
+    _fn = "tf_int4_gemv"
+
+    def __init__(self, context: TurboContext):
+        self.context = context
+
+    def encode(self, weights, scales, biases, x, y, m: int, n: int, *, weights_offset=0, scales_offset=0,
+               biases_offset=0, x_offset=0, y_offset=0, sb_dtype=TF_BF16, stream=None) -> None:
+        ctx = self.context
+        fn = getattr(ctx.lib, self._fn)
+        ctx.check(fn(ctx.handle, _stream(stream), _ptr(weights), weights_offset, _ptr(scales), scales_offset,
+                     _ptr(biases), biases_offset, _ptr(x), x_offset, _ptr(y), y_offset, m, n, sb_dtype))
+
+
+class DequantInt8GEMV(DequantInt4GEMV):
+    """``DequantInt8GEMV`` (Kernels/Quant/DequantInt8GEMV.swift:16-82)."""
+    _fn = "tf_int8_gemv"
+
+
+class MoE:
+    """``MoE`` (Kernels/MoE/MoE.swift:31-313): router + decode routed phases."""
+    max_streamed_experts = 8
+
+    def __init__(self, context: TurboContext):
+        self.context = context
+
+    def encode_router_gemma4(self, weights, scales, biases, hidden, effective_scale, per_expert_scale,
+                             out_indices, out_weights, num_experts: int, d: int, top_k: int, *,
+                             weights_offset=0, scales_offset=0, biases_offset=0, effective_scale_offset=0,
+                             per_expert_scale_offset=0, out_logits=None, stream=None) -> None:
+        ctx = self.context
+        ctx.check(ctx.lib.tf_router_gemma4(
+            ctx.handle, _stream(stream), _ptr(weights), weights_offset, _ptr(scales), scales_offset,
+            _ptr(biases), biases_offset, _ptr(hidden), _ptr(effective_scale), effective_scale_offset,
+            _ptr(per_expert_scale), per_expert_scale_offset, _ptr(out_indices), _ptr(out_weights),
+            _ptr(out_logits), num_experts, d, top_k))
+
+    def encode_routed_phase1(self, blobs, offsets: ExpertOffsets, x, acts, d: int, f: int, top_k: int, *, stream=None):
+        ctx = self.context
+        ctx.check(ctx.lib.tf_moe_phase1(ctx.handle, _stream(stream), _ptr(blobs), C.byref(offsets), _ptr(x),
+                                        _ptr(acts), d, f, top_k))
+
+    def encode_routed_phase1_subset(self, blobs, offsets: ExpertOffsets, x, acts, d: int, f: int, top_k: int,
+                                    active_slots, active_count: int, *, stream=None):
+        ctx = self.context
+        ctx.check(ctx.lib.tf_moe_phase1_subset(ctx.handle, _stream(stream), _ptr(blobs), C.byref(offsets), _ptr(x),
+                                               _ptr(acts), d, f, top_k, _ptr(active_slots), active_count))
+
+    def encode_routed_phase2_reduce(self, blobs, offsets: ExpertOffsets, acts, routing_weights, residual, y,
+                                    d: int, f: int, top_k: int, *, stream=None):
+        ctx = self.context
+        ctx.check(ctx.lib.tf_moe_phase2_reduce(ctx.handle, _stream(stream), _ptr(blobs), C.byref(offsets), _ptr(acts),
+                                               _ptr(routing_weights), _ptr(residual), _ptr(y), d, f, top_k))
+
+    def encode_expert_table(self, pool_layer_base, expert_stride: int, indices, count: int, num_experts: int,
+                            blobs_out, *, stream=None):
+        ctx = self.context
+        ctx.check(ctx.lib.tf_expert_table_from_indices(ctx.handle, _stream(stream), _ptr(pool_layer_base),
+                                                       expert_stride, _ptr(indices), count, num_experts,
+                                                       _ptr(blobs_out)))
+
+
+class SharedExpertInt4:
+    """``SharedExpertInt4`` (Kernels/MoE/SharedExpertInt4.swift:21-95)."""
+
+    def __init__(self, context: TurboContext):
+        self.context = context
+
+    def encode(self, x, gate: SharedExpertProjection, up: SharedExpertProjection, down: SharedExpertProjection, y,
+               scratch_gate, scratch_up, scratch_act, *, x_offset=0, y_offset=0, scratch_gate_offset=0,
+               scratch_up_offset=0, scratch_act_offset=0, stream=None) -> None:
+        ctx = self.context
+        nbytes = lambda t: t.numel() * t.element_size()
+        g, u, dn = gate.c_struct(), up.c_struct(), down.c_struct()
+        ctx.check(ctx.lib.tf_shared_expert_int4(
+            ctx.handle, _stream(stream), _ptr(x), x_offset, nbytes(x), C.byref(g), C.byref(u), C.byref(dn),
+            _ptr(y), y_offset, nbytes(y), _ptr(scratch_gate), scratch_gate_offset, nbytes(scratch_gate),
+            _ptr(scratch_up), scratch_up_offset, nbytes(scratch_up), _ptr(scratch_act), scratch_act_offset,
+            nbytes(scratch_act)))
+
+
+class PrefillRouter:
+    """``PrefillRouter`` (Kernels/Prefill/MoE/PrefillRouter.swift:30-112)."""
+
+    def __init__(self, context: TurboContext):
+        self.context = context
+
+    def encode_gemma4_block(self, weights, scales, biases, hidden, effective_scale, per_expert_scale, out_indices,
+                            out_weights, query_count: int, num_experts: int, d: int, top_k: int,
+                            hidden_stride_elements: int, *, weights_offset=0, scales_offset=0, biases_offset=0,
+                            hidden_offset=0, hidden_dtype=TF_FP16, effective_scale_offset=0,
+                            per_expert_scale_offset=0, out_indices_offset=0, out_weights_offset=0,
+                            logit_bias=None, out_logits=None, stream=None) -> None:
+        ctx = self.context
+        ctx.check(ctx.lib.tf_router_gemma4_block(
+            ctx.handle, _stream(stream), _ptr(weights), weights_offset, _ptr(scales), scales_offset,
+            _ptr(biases), biases_offset, _ptr(hidden), hidden_offset, hidden_dtype,
+            _ptr(effective_scale), effective_scale_offset, _ptr(per_expert_scale), per_expert_scale_offset,
+            _ptr(logit_bias), _ptr(out_indices), out_indices_offset, _ptr(out_weights), out_weights_offset,
+            _ptr(out_logits), query_count, num_experts, d, top_k, hidden_stride_elements))
+
+    @staticmethod
+    def make_token_expert_pairs(indices: np.ndarray, weights_f16_bits: np.ndarray, query_count: int, top_k: int):
+        """Host arrays in, structured array of 16-byte pairs out (PrefillRouter.swift:91-111)."""
+        lib = _capi.load()
+        indices = np.ascontiguousarray(indices, dtype=np.uint32)
+        weights = np.ascontiguousarray(weights_f16_bits, dtype=np.uint16)
+        if indices.size != query_count * top_k:
+            raise TFError(1, "indices count mismatch")
+        if weights.size != query_count * top_k:
+            raise TFError(1, "weights count mismatch")
+        out = np.zeros(query_count * top_k, dtype=PAIR_DTYPE)
+        status = lib.tf_make_token_expert_pairs(indices.ctypes.data, weights.ctypes.data, query_count, top_k,
+                                                out.ctypes.data)
+        if status:
+            raise TFError(status, lib.tf_last_error(None).decode())
+        return out
+
+
+PAIR_DTYPE = np.dtype([("token", "<u4"), ("expert", "<u4"), ("rank", "<u4"), ("weight_bits", "<u4")])
+GROUP_DTYPE = np.dtype([("expert", "<u4"), ("pair_start", "<u4"), ("pair_count", "<u4")])
+TILE_DTYPE = np.dtype([("group_start", "<u4"), ("group_count", "<u4"), ("pair_start", "<u4"), ("pair_count", "<u4")])
+
+GROUPING_ERROR_CASES = {
+    101: "invalidQueryCount", 102: "invalidTopK", 103: "invalidNumExperts", 104: "invalidTileExpertCount",
+    105: "pairCountMismatch", 106: "tokenOutOfRange", 107: "rankOutOfRange", 108: "expertOutOfRange",
+    109: "duplicateTokenRank", 110: "expertSortKeyCountMismatch",
+}
+
+
+class PrefillMoEGroupingError(TFError):
+    """``PrefillMoEGroupingError`` (PrefillMoEGrouping.swift:52-88)."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(status, message)
+        self.case = GROUPING_ERROR_CASES.get(status)
+
+
+@dataclass
+class PrefillMoEGroupedRoutes:
+    """``PrefillMoEGroupedRoutes`` (PrefillMoEGrouping.swift:33-50)."""
+    sorted_pairs: np.ndarray
+    per_expert_offsets: np.ndarray
+    per_expert_counts: np.ndarray
+    groups: np.ndarray
+    tiles: np.ndarray
+    query_count: int
+
+    @property
+    def max_pairs_per_expert(self) -> int:
+        return int(self.groups["pair_count"].max()) if len(self.groups) else 0
+
+    @property
+    def max_pairs_per_tile(self) -> int:
+        return int(self.tiles["pair_count"].max()) if len(self.tiles) else 0
+
+    @property
+    def max_live_experts_per_tile(self) -> int:
+        return int(self.tiles["group_count"].max()) if len(self.tiles) else 0
+
+
+class PrefillMoEGrouping:
+    """``PrefillMoEGrouping`` (PrefillMoEGrouping.swift:90-193)."""
+
+    @staticmethod
+    def group_token_expert_pairs(pairs: np.ndarray, query_count: int, top_k: int, num_experts: int,
+                                 tile_expert_count: int = 16, expert_sort_keys=None) -> PrefillMoEGroupedRoutes:
+        lib = _capi.load()
+        pairs = np.ascontiguousarray(pairs, dtype=PAIR_DTYPE)
+        n = int(pairs.shape[0])
+        sorted_out = np.zeros(max(n, 1), dtype=PAIR_DTYPE)
+        offs = np.zeros(max(num_experts, 1), dtype=np.uint32)
+        cnts = np.zeros(max(num_experts, 1), dtype=np.uint32)
+        groups = np.zeros(max(n, 1), dtype=GROUP_DTYPE)
+        tiles = np.zeros(max(n, 1), dtype=TILE_DTYPE)
+        ng, nt = C.c_uint32(0), C.c_uint32(0)
+        keys = None if expert_sort_keys is None else np.ascontiguousarray(expert_sort_keys, dtype=np.uint64)
+        status = lib.tf_group_pairs(pairs.ctypes.data, n, query_count, top_k, num_experts, tile_expert_count,
+                                    None if keys is None else keys.ctypes.data, 0 if keys is None else keys.shape[0],
+                                    sorted_out.ctypes.data, offs.ctypes.data, cnts.ctypes.data, groups.ctypes.data,
+                                    C.byref(ng), tiles.ctypes.data, C.byref(nt))
+        if status:
+            raise PrefillMoEGroupingError(status, lib.tf_last_error(None).decode())
+        return PrefillMoEGroupedRoutes(sorted_out[:n], offs[:num_experts], cnts[:num_experts],
+                                       groups[:ng.value], tiles[:nt.value], query_count)
+
+
+class RMSNorm:
+    """``RMSNorm`` / ``PrefillRMSNorm`` (Metal/Primitives/rmsnorm.metal:32-93,153-175)."""
+
+    def __init__(self, context: TurboContext):
+        self.context = context
+
+    def encode(self, x, weight, y, rows: int, d: int, stride_elements: int | None = None, eps: float = 1e-6,
+               act_dtype=TF_FP16, *, x_offset=0, weight_offset=0, y_offset=0, stream=None):
+        ctx = self.context
+        ctx.check(ctx.lib.tf_rmsnorm(ctx.handle, _stream(stream), _ptr(x), x_offset, _ptr(weight), weight_offset,
+                                     _ptr(y), y_offset, rows, d, d if stride_elements is None else stride_elements,
+                                     eps, act_dtype))
+
+
+class FusedLayerTail:
+    """``FusedLayerTail`` / ``PrefillLayerTail`` (Metal/Fusions/fused.metal:271-375)."""
+
+    def __init__(self, context: TurboContext):
+        self.context = context
+
+    def encode(self, h2, h1, hidden, w_postffn2, w_postffn, rows: int, d: int, stride_elements: int | None = None,
+               eps: float = 1e-6, layer_scalar: float = 1.0, *, stream=None):
+        ctx = self.context
+        ctx.check(ctx.lib.tf_layer_tail(ctx.handle, _stream(stream), _ptr(h2), _ptr(h1), _ptr(hidden), _ptr(w_postffn2),
+                                        _ptr(w_postffn), rows, d, d if stride_elements is None else stride_elements,
+                                        eps, layer_scalar))
