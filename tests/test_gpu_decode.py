@@ -1,0 +1,434 @@
+"""GPU parity of the decode-path entry points against the CPU oracle, through the
+C ABI. Seeds, shapes and tolerances are the reference's own where it has a test
+(cited per case); BASELINE configurations use numpy-seeded inputs."""
+import numpy as np
+import pytest
+
+from helpers import (blob_table, capi_offsets, config0_matrix, dev_zeros_u16, from_dev, quantized_blob, random_blob,
+                     to_dev)
+
+pytestmark = pytest.mark.gpu
+
+FP16_REDUCTION = 5e-3      # Tolerance.fp16Reduction
+FP16_CHAINED = 1e-2        # Tolerance.fp16ChainedReduction (also BASELINE's 1e-2 relative L2)
+
+
+def _run_gemv(tf_ctx, o, mat, x16, offset=0, bits=4):
+    import torch
+    from turbo_fieldfare_b200.kernels import DequantInt4GEMV, DequantInt8GEMV
+    raw = mat.packed.reshape(-1)
+    padded = np.zeros(raw.size + offset + 16, dtype=np.uint8)
+    padded[offset:offset + raw.size] = raw
+    W, S, B, x = to_dev(padded), to_dev(mat.scales), to_dev(mat.biases), to_dev(x16)
+    guard = 8
+    y = dev_zeros_u16(mat.m + 2 * guard, fill=0x7BFF)        # poison: 65504
+    k = (DequantInt4GEMV if bits == 4 else DequantInt8GEMV)(tf_ctx)
+    k.encode(W, S, B, x, y, mat.m, mat.n, weights_offset=offset, y_offset=guard * 2, sb_dtype=mat.sb_dtype)
+    torch.cuda.synchronize()
+    out = from_dev(y, np.uint16)
+    assert np.all(out[:guard] == 0x7BFF) and np.all(out[-guard:] == 0x7BFF), "guard band overwritten"
+    return out[guard:-guard]
+
+
+@pytest.mark.parametrize("m,n,seed,label,offset", [
+    (128, 128, 0xC1, "int4-gemv-kernel-m128-n128", 0),
+    (1024, 2816, 0xC2, "int4-gemv-kernel-m1024-n2816", 0),
+    (64, 64, 0xC3, "int4-gemv-kernel-m64-n64", 0),
+    (128, 2816, 0xC4, "int4-gemv-kernel-m128-n2816-off2", 2),
+])
+def test_int4_gemv_reference_fixtures(tf_ctx, oracle, m, n, seed, label, offset):
+    # Tests/TurboFieldfare/Core/Kernels/Quant/DequantInt4GEMVTests.swift:41-121
+    o = oracle
+    rng = o.SeedTree(seed).key(label)
+    mat = o.quantize_rows(np.stack([rng.uniform_array(-0.5, 0.5, n) for _ in range(m)]), 4)
+    x16 = o.f32_to_f16(rng.uniform_array(-1.0, 1.0, n))
+    y = _run_gemv(tf_ctx, o, mat, x16, offset)
+    ref = o.gemv_ref(mat, o.f16_to_f32(x16))
+    assert o.rel_error(o.f16_to_f32(y), ref) < FP16_REDUCTION
+    assert o.rel_l2(o.f16_to_f32(y), ref) < 1e-3
+
+
+@pytest.mark.parametrize("m", [64, 65, 128, 129])
+@pytest.mark.parametrize("n", [64, 128, 192, 256, 320, 384, 448, 512])
+def test_int4_gemv_sweep(tf_ctx, oracle, m, n):
+    # DequantInt4GEMVTests.swift:123-128
+    o = oracle
+    seed = (m * 0x9E37 + n) & 0xFFFFFFFFFFFFFFFF
+    rng = o.SeedTree(seed).key(f"int4-gemv-kernel-m{m}-n{n}")
+    mat = o.quantize_rows(np.stack([rng.uniform_array(-0.5, 0.5, n) for _ in range(m)]), 4)
+    x16 = o.f32_to_f16(rng.uniform_array(-1.0, 1.0, n))
+    y = _run_gemv(tf_ctx, o, mat, x16)
+    assert o.rel_error(o.f16_to_f32(y), o.gemv_ref(mat, o.f16_to_f32(x16))) < FP16_REDUCTION
+
+
+@pytest.mark.parametrize("m,n,seed", [(128, 2816, 0x151), (1024, 2816, 0x152)])
+def test_int8_gemv_reference_fixtures(tf_ctx, oracle, m, n, seed):
+    # DequantInt8GEMVTests.swift:74-88
+    o = oracle
+    rng = o.SplitMix64(seed)
+    mat = o.quantize_rows(np.stack([rng.uniform_array(-0.5, 0.5, n) for _ in range(m)]), 8)
+    x16 = o.f32_to_f16(rng.uniform_array(-1.0, 1.0, n))
+    for offset in (0, 1):
+        y = _run_gemv(tf_ctx, o, mat, x16, offset=offset, bits=8)
+        assert o.rel_error(o.f16_to_f32(y), o.gemv_ref(mat, o.f16_to_f32(x16))) < FP16_REDUCTION
+
+
+@pytest.mark.parametrize("sb_dtype", [0, 1])
+def test_config0_gemv_704x2816(tf_ctx, oracle, sb_dtype):
+    """BASELINE config 0: 704 x 2816, uniform codes, scale/bias distributions, x ~ N(0,1) fp16."""
+    o = oracle
+    rng = np.random.default_rng(20260 + sb_dtype)
+    mat = config0_matrix(o, 704, 2816, rng, sb_dtype=sb_dtype)
+    x16 = o.f32_to_f16(rng.standard_normal(2816).astype(np.float32))
+    y = o.f16_to_f32(_run_gemv(tf_ctx, o, mat, x16))
+    ref = o.gemv_ref(mat, o.f16_to_f32(x16))
+    assert o.rel_l2(y, ref) < FP16_CHAINED
+    assert o.rel_error(y, ref) < FP16_REDUCTION
+
+
+def test_gemv_rejects_bad_arguments(tf_ctx, oracle):
+    from turbo_fieldfare_b200.kernels import DequantInt4GEMV, TFError
+    import torch
+    buf = torch.zeros(4096, dtype=torch.uint8, device="cuda")
+    k = DequantInt4GEMV(tf_ctx)
+    with pytest.raises(TFError) as e:
+        k.encode(buf, buf, buf, buf, buf, 4, 96)          # N % 64 != 0 (DequantInt4GEMV.swift:57-62)
+    assert e.value.status == 1
+    with pytest.raises(TFError) as e:
+        k.encode(buf, buf, buf, buf, buf, 4, 64, weights_offset=1)   # odd weights offset
+    assert e.value.status == 4
+
+
+# ---------------------------------------------------------------------------
+# router
+# ---------------------------------------------------------------------------
+
+def _run_router(tf_ctx, o, mat, hidden16, eff16, gain16, rows=None, stride=None, logit_bias=None, bf16_hidden=False):
+    import torch
+    from turbo_fieldfare_b200.kernels import MoE, PrefillRouter
+    E, D = mat.m, mat.n
+    W, S, B = to_dev(mat.packed), to_dev(mat.scales), to_dev(mat.biases)
+    eff, gain = to_dev(eff16), to_dev(gain16)
+    hid = to_dev(hidden16)
+    if rows is None:
+        idx = torch.full((8,), -1, dtype=torch.int32, device="cuda")
+        w = dev_zeros_u16(8)
+        logits = torch.zeros(E, dtype=torch.float32, device="cuda")
+        MoE(tf_ctx).encode_router_gemma4(W, S, B, hid, eff, gain, idx, w, E, D, 8, out_logits=logits)
+        torch.cuda.synchronize()
+        return from_dev(idx, np.uint32), from_dev(w, np.uint16), logits.cpu().numpy()
+    K = 8
+    idx = torch.full((rows, K), -1, dtype=torch.int32, device="cuda")
+    w = dev_zeros_u16(rows * K)
+    logits = torch.zeros((rows, E), dtype=torch.float32, device="cuda")
+    PrefillRouter(tf_ctx).encode_gemma4_block(W, S, B, hid, eff, gain, idx, w, rows, E, D, K, stride or D,
+                                              hidden_dtype=0 if bf16_hidden else 1,
+                                              logit_bias=None if logit_bias is None else to_dev(logit_bias),
+                                              out_logits=logits)
+    torch.cuda.synchronize()
+    return from_dev(idx, np.uint32).reshape(rows, K), from_dev(w, np.uint16).reshape(rows, K), logits.cpu().numpy()
+
+
+def test_router_reference_fixture(tf_ctx, oracle):
+    # Tests/TurboFieldfare/Core/Kernels/MoE/RouterTopKTests.swift:17-45
+    from test_oracle_pins import _router_fixture
+    o = oracle
+    weights, hidden, eff, gain = _router_fixture(o)
+    mat = o.quantize_rows(weights, 8)
+    h16, e16, g16 = o.f32_to_f16(hidden), o.f32_to_bf16(eff), o.f32_to_bf16(gain)
+    idx, w16, logits = _run_router(tf_ctx, o, mat, h16, e16, g16)
+    ref_logits = o.router_logits(mat, h16, e16)[0]
+    assert logits.tobytes() == ref_logits.tobytes(), "router logits are not bit-exact with the canonical order"
+    ridx, rw16, rw32 = o.router_select(ref_logits, g16, 8)
+    assert idx.tolist() == ridx[0].tolist()
+    assert np.max(np.abs(o.f16_to_f32(w16) - rw32[0])) < 5e-3
+    # and against the reference test's own CPU formulation
+    sidx, sw = o.router_select_sorted(o.gemv_ref(mat, (o.f16_to_f32(h16) * o.bf16_to_f32(e16)).astype(np.float32)),
+                                      o.bf16_to_f32(g16), 8)
+    assert idx.tolist() == sidx.tolist()
+    assert np.max(np.abs(o.f16_to_f32(w16) - sw)) < 5e-3
+
+
+def test_router_near_tie(tf_ctx, oracle):
+    # RouterTopKTests.swift:47-70
+    o = oracle
+    rng = o.SplitMix64(0x71E0F4A)
+    pattern = rng.uniform_array(0.2, 1.0, 128)
+    hidden = rng.uniform_array(0.5, 1.5, 128)
+    gains = np.zeros(16, dtype=np.float32)
+    for e in range(7):
+        gains[e] = np.float32(1.0) - np.float32(e) * np.float32(0.05)
+    gains[7] = 0.5
+    gains[8] = np.float32(0.5) * (np.float32(1.0) + np.float32(1e-4))
+    for e in range(9, 16):
+        gains[e] = np.float32(0.4) - np.float32(e - 9) * np.float32(0.02)
+    mat = o.quantize_rows(np.stack([pattern * g for g in gains]), 8)
+    ones_d, ones_e = o.f32_to_bf16(np.ones(128, dtype=np.float32)), o.f32_to_bf16(np.ones(16, dtype=np.float32))
+    h16 = o.f32_to_f16(hidden)
+    idx, _, logits = _run_router(tf_ctx, o, mat, h16, ones_d, ones_e)
+    ref_logits = o.router_logits(mat, h16, ones_d)[0]
+    assert logits.tobytes() == ref_logits.tobytes()
+    assert idx.tolist() == o.router_select(ref_logits, ones_e, 8)[0][0].tolist()
+    assert idx.tolist() == o.router_select_sorted(o.gemv_ref(mat, o.f16_to_f32(h16)), np.ones(16, np.float32), 8)[0].tolist()
+
+
+def test_router_exact_ties_lower_index_first(tf_ctx, oracle):
+    """Identical rows give identical logits: the selection must take the lower ids."""
+    o = oracle
+    rng = np.random.default_rng(5)
+    row = rng.uniform(-0.05, 0.05, 128).astype(np.float32)
+    weights = np.stack([row] * 12 + [row * 0.5] * 4)
+    mat = o.quantize_rows(weights, 8)
+    h16 = o.f32_to_f16(rng.uniform(0.5, 1.0, 128).astype(np.float32) * np.sign(row))
+    ones_d, ones_e = o.f32_to_bf16(np.ones(128, dtype=np.float32)), o.f32_to_bf16(np.ones(16, dtype=np.float32))
+    idx, w16, _ = _run_router(tf_ctx, o, mat, h16, ones_d, ones_e)
+    assert idx.tolist() == list(range(8))
+    assert np.allclose(o.f16_to_f32(w16), 0.125, atol=1e-3)
+
+
+@pytest.mark.parametrize("rows", [5, 64, 200])
+def test_block_router_strided_rows(tf_ctx, oracle, rows):
+    # Tests/TurboFieldfare/Core/Kernels/Prefill/PrefillRouterTests.swift:33-101: stride D+13, sentinel padding
+    o = oracle
+    E, D, stride = 16, 128, 128 + 13
+    rng = o.SplitMix64(0x9A7E2026)
+    mat = o.quantize_rows(np.stack([rng.uniform_array(-0.05, 0.05, D) + np.float32(e) * np.float32(0.01) for e in range(E)]), 8)
+    hidden = np.full((rows, stride), -31.0, dtype=np.float32)
+    for t in range(rows):
+        hidden[t, :D] = rng.uniform_array(-1.0, 1.0, D)
+    h16 = o.f32_to_f16(hidden)
+    e16 = o.f32_to_bf16(rng.uniform_array(0.5, 1.5, D) / np.sqrt(np.float32(D)))
+    g16 = o.f32_to_bf16(rng.uniform_array(0.6, 1.4, E))
+    idx, w16, logits = _run_router(tf_ctx, o, mat, h16, e16, g16, rows=rows, stride=stride)
+    ref_logits = o.router_logits(mat, h16, e16, stride=stride)
+    assert logits.tobytes() == ref_logits.tobytes()
+    ridx, rw16, rw32 = o.router_select(ref_logits, g16, 8)
+    assert np.array_equal(idx, ridx)
+    assert np.max(np.abs(o.f16_to_f32(w16) - rw32)) < 5e-3
+
+
+def test_production_router_128x2816_with_bias(tf_ctx, oracle):
+    """BASELINE configs 1-3: 128 experts, D=2816, top-8; Zipf(1.1) logit bias; fp16 and bf16 rows."""
+    o = oracle
+    rng = np.random.default_rng(31)
+    E, D, T = 128, 2816, 96
+    mat = config0_matrix(o, E, D, rng, bits=8)
+    eff = o.f32_to_bf16(np.full(D, 1.0 / np.sqrt(D), dtype=np.float32))
+    gain = o.f32_to_bf16(np.ones(E, dtype=np.float32))
+    ranks = rng.permutation(E) + 1
+    p = 1.0 / ranks ** 1.1
+    bias = np.log(p / p.sum()).astype(np.float32)
+    x = rng.standard_normal((T, D)).astype(np.float32)
+    for bf in (False, True):
+        h16 = o.f32_to_bf16(x) if bf else o.f32_to_f16(x)
+        idx, w16, logits = _run_router(tf_ctx, o, mat, h16, eff, gain, rows=T, logit_bias=bias, bf16_hidden=bf)
+        if bf:
+            # the oracle's logits take fp16 rows; for bf16 rows compare with the double-precision truth instead
+            xf = o.bf16_to_f32(h16).astype(np.float64) * o.bf16_to_f32(eff).astype(np.float64)
+            truth = xf @ o.dequantize(mat).astype(np.float64).T + bias
+            assert np.max(np.abs(logits - truth)) < 1e-4
+            order = np.argsort(-logits, axis=1, kind="stable")[:, :8]
+            assert np.array_equal(idx, order.astype(np.uint32))
+            continue
+        ref_logits = (o.router_logits(mat, h16, eff) + bias).astype(np.float32)
+        assert logits.tobytes() == ref_logits.tobytes()
+        ridx, _, rw32 = o.router_select(ref_logits, gain, 8)
+        assert np.array_equal(idx, ridx)
+        assert np.max(np.abs(o.f16_to_f32(w16) - rw32)) < 5e-3
+        # decode entry point on row 0 gives the same bits as the block entry point
+        idx1, w1, lg1 = _run_router(tf_ctx, o, mat, h16[0], eff, gain)
+        assert lg1.tobytes() == o.router_logits(mat, h16[0], eff)[0].tobytes()
+
+
+def test_router_preconditions(tf_ctx):
+    import torch
+    from turbo_fieldfare_b200.kernels import MoE, TFError
+    b = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    moe = MoE(tf_ctx)
+    for kwargs in (dict(num_experts=16, d=100, top_k=8), dict(num_experts=300, d=128, top_k=8),
+                   dict(num_experts=16, d=128, top_k=4)):          # MoE.swift:121-123
+        with pytest.raises(TFError) as e:
+            moe.encode_router_gemma4(b, b, b, b, b, b, b, b, **kwargs)
+        assert e.value.status == 1
+
+
+# ---------------------------------------------------------------------------
+# routed experts, decode
+# ---------------------------------------------------------------------------
+
+def _routed_fixture(o, D=128, F=64, K=8):
+    # Tests/TurboFieldfare/Core/Kernels/MoE/MoEFusedFFNTests.swift:17-159
+    rng = o.SeedTree(0x2D3).key("production-routed-moe")
+    off, payload, stride = o.blob_layout(D, F, align=256)
+    blobs = [quantized_blob(o, D, F, rng.uniform_array, off, stride)[0] for _ in range(K)]
+    x16 = o.f32_to_f16(rng.uniform_array(-1.0, 1.0, D))
+    w16 = o.f32_to_f16(np.array([0.04 + 0.015 * k for k in range(K)], dtype=np.float32))
+    return off, blobs, x16, w16
+
+
+def test_routed_decode_reference_fixture(tf_ctx, oracle):
+    import torch
+    from turbo_fieldfare_b200.kernels import MoE
+    o = oracle
+    D, F, K = 128, 64, 8
+    off, blobs, x16, w16 = _routed_fixture(o, D, F, K)
+    # poison prefix/suffix around every blob (PrefillGroupedRoutedMoETests.swift:80-106 style)
+    dev_blobs = []
+    for b in blobs:
+        buf = np.full(b.size + 512, 0xA5, dtype=np.uint8)
+        buf[256:256 + b.size] = b
+        dev_blobs.append(to_dev(buf))
+    table = torch.tensor([t.data_ptr() + 256 for t in dev_blobs], dtype=torch.int64, device="cuda")
+    x, w = to_dev(x16), to_dev(w16)
+    acts = dev_zeros_u16(K * F + 16, fill=0x7BFF)
+    y = dev_zeros_u16(D + 16, fill=0x7BFF)
+    res = dev_zeros_u16(D)
+    moe = MoE(tf_ctx)
+    coff = capi_offsets(off)
+    moe.encode_routed_phase1(table, coff, x, acts, D, F, K)
+    moe.encode_routed_phase2_reduce(table, coff, acts, w, res, y, D, F, K)
+    torch.cuda.synchronize()
+    acts_h, y_h = from_dev(acts, np.uint16), from_dev(y, np.uint16)
+    assert np.all(acts_h[K * F:] == 0x7BFF) and np.all(y_h[D:] == 0x7BFF)
+    y_truth16, y_truth, acts_truth = o.moe_routed_decode(blobs, off, x16, w16, from_dev(res, np.uint16), D, F, order=0)
+    assert o.rel_error(o.f16_to_f32(acts_h[:K * F]), o.f16_to_f32(acts_truth.reshape(-1))) < FP16_CHAINED
+    assert o.rel_error(o.f16_to_f32(y_h[:D]), y_truth) < FP16_CHAINED
+    assert o.rel_l2(o.f16_to_f32(y_h[:D]), y_truth) < FP16_CHAINED
+
+    # hit/miss split == full, bitwise (MoEFusedFFNTests.swift:154-156)
+    acts2 = dev_zeros_u16(K * F)
+    hits = to_dev(np.array([0, 3, 5], dtype=np.uint32))
+    misses = to_dev(np.array([1, 2, 4, 6, 7], dtype=np.uint32))
+    moe.encode_routed_phase1_subset(table, coff, x, acts2, D, F, K, hits, 3)
+    moe.encode_routed_phase1_subset(table, coff, x, acts2, D, F, K, misses, 5)
+    torch.cuda.synchronize()
+    assert from_dev(acts2, np.uint16).tobytes() == acts_h[:K * F].tobytes()
+
+    # a non-zero residual is added in fp32 before the single rounding (moe.metal:475-480)
+    res2 = to_dev(o.f32_to_f16(np.linspace(-1, 1, D).astype(np.float32)))
+    moe.encode_routed_phase2_reduce(table, coff, acts, w, res2, y, D, F, K)
+    torch.cuda.synchronize()
+    _, y_truth2, _ = o.moe_routed_decode(blobs, off, x16, w16, from_dev(res2, np.uint16), D, F, order=0)
+    assert o.rel_error(o.f16_to_f32(from_dev(y, np.uint16)[:D]), y_truth2) < FP16_CHAINED
+
+
+def test_routed_decode_production_shape_with_device_table(tf_ctx, oracle):
+    """BASELINE config 1 routed half: D=2816, F=704, 8 of 16 pooled experts chosen by ids on the device."""
+    import torch
+    from turbo_fieldfare_b200.kernels import MoE
+    o = oracle
+    D, F, K, E = 2816, 704, 8, 16
+    rng = np.random.default_rng(77)
+    off, payload, stride = o.blob_layout(D, F)
+    assert stride == 3358720
+    pool_h = np.zeros(E * stride, dtype=np.uint8)
+    for e in range(E):
+        pool_h[e * stride:(e + 1) * stride] = random_blob(o, D, F, rng, off, stride)[0]
+    pool = to_dev(pool_h)
+    ids = np.array([9, 2, 15, 0, 7, 11, 4, 200], dtype=np.uint32)       # 200 clamps to E-1
+    x16 = o.f32_to_f16(rng.standard_normal(D).astype(np.float32))
+    w16 = o.f32_to_f16(rng.dirichlet(np.ones(K)).astype(np.float32))
+    table = torch.zeros(K, dtype=torch.int64, device="cuda")
+    moe = MoE(tf_ctx)
+    moe.encode_expert_table(pool, stride, to_dev(ids), K, E, table)
+    acts, y = dev_zeros_u16(K * F), dev_zeros_u16(D)
+    coff = capi_offsets(off)
+    moe.encode_routed_phase1(table, coff, to_dev(x16), acts, D, F, K)
+    moe.encode_routed_phase2_reduce(table, coff, acts, to_dev(w16), None, y, D, F, K)
+    torch.cuda.synchronize()
+    clamped = np.minimum(ids, E - 1)
+    assert table.cpu().tolist() == [pool.data_ptr() + int(e) * stride for e in clamped]
+    blobs = [pool_h[int(e) * stride:(int(e) + 1) * stride] for e in clamped]
+    _, y_truth, acts_truth = o.moe_routed_decode(blobs, off, x16, w16, None, D, F, order=0)
+    assert o.rel_l2(o.f16_to_f32(from_dev(acts, np.uint16)), o.f16_to_f32(acts_truth.reshape(-1))) < FP16_CHAINED
+    assert o.rel_l2(o.f16_to_f32(from_dev(y, np.uint16)), y_truth) < FP16_CHAINED
+    assert o.rel_error(o.f16_to_f32(from_dev(y, np.uint16)), y_truth) < FP16_CHAINED
+
+
+# ---------------------------------------------------------------------------
+# shared expert, norms
+# ---------------------------------------------------------------------------
+
+def _shared_run(tf_ctx, o, gate, up, down, x16):
+    import torch
+    from turbo_fieldfare_b200.kernels import SharedExpertInt4, SharedExpertProjection
+    D, Fs = gate.n, gate.m
+    proj = lambda m: SharedExpertProjection(to_dev(m.packed), to_dev(m.scales), to_dev(m.biases), m.m, m.n)
+    y = dev_zeros_u16(D)
+    sg, su, sa = dev_zeros_u16(Fs), dev_zeros_u16(Fs), dev_zeros_u16(Fs)
+    SharedExpertInt4(tf_ctx).encode(to_dev(x16), proj(gate), proj(up), proj(down), y, sg, su, sa)
+    torch.cuda.synchronize()
+    return from_dev(y, np.uint16)
+
+
+def test_shared_expert_reference_fixture(tf_ctx, oracle):
+    # Tests/TurboFieldfare/Core/Kernels/MoE/SharedExpertInt4Tests.swift:11-52 (D=128, F=64, seed 0x604; rel < 6e-3)
+    o = oracle
+    D, Fs = 128, 64
+    rng = o.SplitMix64(0x604)
+    gate = o.quantize_rows(np.stack([rng.uniform_array(-0.5, 0.5, D) for _ in range(Fs)]), 4)
+    up = o.quantize_rows(np.stack([rng.uniform_array(-0.5, 0.5, D) for _ in range(Fs)]), 4)
+    down = o.quantize_rows(np.stack([rng.uniform_array(-0.5, 0.5, Fs) for _ in range(D)]), 4)
+    x16 = o.f32_to_f16(rng.uniform_array(-1.0, 1.0, D))
+    y = _shared_run(tf_ctx, o, gate, up, down, x16)
+    _, truth = o.shared_expert_int4(gate, up, down, x16, order=0)
+    assert o.rel_error(o.f16_to_f32(y), truth) < 6e-3
+
+
+def test_shared_expert_production_shape(tf_ctx, oracle):
+    o = oracle
+    rng = np.random.default_rng(99)
+    D, Fs = 2816, 2112
+    gate, up, down = config0_matrix(o, Fs, D, rng), config0_matrix(o, Fs, D, rng), config0_matrix(o, D, Fs, rng)
+    x16 = o.f32_to_f16(rng.standard_normal(D).astype(np.float32))
+    y = _shared_run(tf_ctx, o, gate, up, down, x16)
+    _, truth = o.shared_expert_int4(gate, up, down, x16, order=0)
+    assert o.rel_l2(o.f16_to_f32(y), truth) < FP16_CHAINED
+
+
+def test_shared_expert_errors(tf_ctx, oracle):
+    import torch
+    from turbo_fieldfare_b200.kernels import SharedExpertInt4, SharedExpertProjection, TFError
+    b = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    small = torch.zeros(8, dtype=torch.uint8, device="cuda")
+    p = lambda r, c: SharedExpertProjection(b, b, b, r, c)
+    k = SharedExpertInt4(tf_ctx)
+    with pytest.raises(TFError) as e:          # SharedExpertError.dimensionMismatch
+        k.encode(b, p(64, 128), p(64, 128), p(128, 128), b, b, b, b)
+    assert e.value.status == 7
+    with pytest.raises(TFError) as e:          # SharedExpertError.scratchTooSmall
+        k.encode(b, p(64, 128), p(64, 128), p(128, 64), b, small, b, b)
+    assert e.value.status == 6
+
+
+def test_rmsnorm_and_layer_tail(tf_ctx, oracle):
+    import torch
+    from turbo_fieldfare_b200.kernels import FusedLayerTail, RMSNorm
+    o = oracle
+    rng = np.random.default_rng(3)
+    T, D, stride = 5, 2816, 2816 + 8
+    x = np.zeros((T, stride), dtype=np.float32)
+    x[:, :D] = rng.standard_normal((T, D))
+    x16 = o.f32_to_f16(x)
+    w = o.f32_to_bf16((1 + 0.02 * rng.standard_normal(D)).astype(np.float32))
+    y = dev_zeros_u16(T * stride)
+    RMSNorm(tf_ctx).encode(to_dev(x16), to_dev(w), y, T, D, stride)
+    y0 = dev_zeros_u16(T * stride)
+    RMSNorm(tf_ctx).encode(to_dev(x16), None, y0, T, D, stride)
+    torch.cuda.synchronize()
+    got = o.f16_to_f32(from_dev(y, np.uint16).reshape(T, stride)[:, :D])
+    ref = o.f16_to_f32(o.rmsnorm(np.ascontiguousarray(x16[:, :D]), w))
+    assert o.rel_error(got, ref) < 2e-3
+    assert np.all(from_dev(y, np.uint16).reshape(T, stride)[:, D:] == 0)     # padding untouched
+    got0 = o.f16_to_f32(from_dev(y0, np.uint16).reshape(T, stride)[:, :D])
+    assert o.rel_error(got0, o.f16_to_f32(o.rmsnorm(np.ascontiguousarray(x16[:, :D]), None))) < 2e-3
+
+    h2 = o.f32_to_f16(rng.standard_normal((T, D)).astype(np.float32))
+    h1 = o.f32_to_f16(rng.standard_normal((T, D)).astype(np.float32))
+    hid = o.f32_to_f16(rng.standard_normal((T, D)).astype(np.float32))
+    w2 = o.f32_to_bf16((1 + 0.02 * rng.standard_normal(D)).astype(np.float32))
+    hd = to_dev(hid)
+    FusedLayerTail(tf_ctx).encode(to_dev(h2), to_dev(h1), hd, to_dev(w2), to_dev(w), T, D, D, 1e-6, 0.75)
+    torch.cuda.synchronize()
+    ref = o.f16_to_f32(o.layer_tail(h2, h1, hid, w2, w, 1e-6, 0.75))
+    assert o.rel_error(o.f16_to_f32(from_dev(hd, np.uint16).reshape(T, D)), ref) < 3e-3
