@@ -98,6 +98,24 @@ typedef struct tf_pair {
 typedef struct tf_group { uint32_t expert, pair_start, pair_count; } tf_group;
 typedef struct tf_tile { uint32_t group_start, group_count, pair_start, pair_count; } tf_tile;
 
+/* Device-resident routing metadata produced by tf_group_routes_device and
+ * consumed by tf_grouped_moe_batched. All pointers are DEVICE buffers the
+ * caller owns: sorted_pairs [T*K]; per_expert_offsets, per_expert_counts,
+ * groups, chunk_start [E]; chunk_group [T*K/16 + E]; counters [4] =
+ * {group count, chunk count, pair count, reserved}. A chunk is up to 16
+ * consecutive sorted pairs of one expert (one pass of the grouped kernels).
+ * Replaces PrefillMoEGroupedRoutes (PrefillMoEGrouping.swift:33-50), which the
+ * reference builds on the CPU after reading the router output back. */
+typedef struct tf_device_routes {
+    tf_pair* sorted_pairs;
+    uint32_t* per_expert_offsets;
+    uint32_t* per_expert_counts;
+    tf_group* groups;
+    uint32_t* chunk_group;
+    uint32_t* chunk_start;
+    uint32_t* counters;
+} tf_device_routes;
+
 typedef struct tf_context tf_context;
 
 /* ---- context: replaces MetalContext (Infrastructure/Metal/MetalContext.swift:51-214) ---- */
@@ -221,6 +239,49 @@ tf_status tf_group_pairs(const tf_pair* host_pairs, uint32_t pair_count,
                          tf_pair* sorted_out, uint32_t* per_expert_offsets, uint32_t* per_expert_counts,
                          tf_group* groups_out, uint32_t* group_count_out,
                          tf_tile* tiles_out, uint32_t* tile_count_out);
+
+/* ---- batched routing on the device ---- */
+/* Device form of groupTokenExpertPairs for router output that never leaves the
+ * GPU: order (expert, token, rank), ids clamped to num_experts-1 as the caller
+ * does (Runtime/Inference/RealForwardRunner.swift:955). No sort keys and no
+ * tiles: tiles exist in the reference only to bound SSD slots. Replaces the
+ * CPU stage PrefillRouter.makeTokenExpertPairs + PrefillMoEGrouping
+ * (RealForwardRunner.swift:945-979). */
+tf_status tf_group_routes_device(tf_context* ctx, void* stream,
+                                 const uint32_t* indices, const void* weights_f16,
+                                 uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                                 const tf_device_routes* routes);
+/* Per pair: act = half(gelu(gate.x) * (up.x)) into acts_scratch[pair, F] (sorted
+ * pair order), then down -> route_partials[(token*top_k + rank)*D + d], fp16
+ * (the reference) or fp32 when partials_f32 != 0. Experts are read from the
+ * HBM-resident pool: blob(e) = pool_layer_base + e * expert_stride. Replaces
+ * PrefillGroupedRoutedMoE.encodeStreamedBatched over all tiles
+ * (Kernels/Prefill/MoE/PrefillGroupedRoutedMoE.swift:386-461). */
+tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream,
+                                 const void* hidden, uint64_t hidden_off, uint32_t hidden_stride_elements,
+                                 const void* pool_layer_base, uint64_t expert_stride,
+                                 const tf_expert_offsets* offsets, const tf_device_routes* routes,
+                                 void* acts_scratch, void* route_partials, int partials_f32,
+                                 uint32_t query_count, uint32_t d, uint32_t f, uint32_t top_k);
+/* h2[t,d] = half(sum_r w[t,r] * partial[t,r,d] (+ residual[t,d])), rank order.
+ * Replaces PrefillMoE.encodeReduceTokenMajor (Kernels/Prefill/MoE/PrefillMoE.swift:11-39);
+ * residual may be NULL (the reference has none); with fp32 partials the order is
+ * the decode kernel's (Metal/MoE/moe.metal:473-480). */
+tf_status tf_moe_reduce_token_major(tf_context* ctx, void* stream,
+                                    const void* route_partials, int partials_f32,
+                                    const void* route_weights,
+                                    const void* residual, uint32_t residual_stride_elements,
+                                    void* h2, uint32_t h2_stride_elements,
+                                    uint32_t query_count, uint32_t top_k, uint32_t d);
+/* Shared expert for `rows` tokens at once (weights read once per 16 tokens).
+ * Replaces PrefillSharedExpert.encodeBlock (Kernels/Prefill/MoE/PrefillSharedExpert.swift:11-59),
+ * which loops SharedExpertInt4.encode over the rows. scratch_act: [rows, gate.rows] fp16. */
+tf_status tf_shared_expert_int4_block(tf_context* ctx, void* stream,
+                                      const void* x, uint64_t x_off, uint32_t x_stride_elements,
+                                      const tf_projection* gate, const tf_projection* up,
+                                      const tf_projection* down,
+                                      void* y, uint64_t y_off, uint32_t y_stride_elements,
+                                      void* scratch_act, uint32_t rows);
 
 /* ---- norms ---- */
 /* y = half(x * rsqrt(mean(x^2) + eps) * w_bf16); weight NULL = no-scale form.

@@ -43,6 +43,12 @@ class Tile(C.Structure):
     _fields_ = [("group_start", u32), ("group_count", u32), ("pair_start", u32), ("pair_count", u32)]
 
 
+class DeviceRoutes(C.Structure):
+    """tf_device_routes: device buffers of the grouped routing metadata."""
+    _fields_ = [(n, vp) for n in ("sorted_pairs", "per_expert_offsets", "per_expert_counts", "groups",
+                                  "chunk_group", "chunk_start", "counters")]
+
+
 _PLANES = [vp, u64, vp, u64, vp, u64]   # weights, scales, biases with offsets
 
 SIGNATURES = {
@@ -64,6 +70,12 @@ SIGNATURES = {
                                         C.POINTER(Projection), vp, u64, u64, vp, u64, u64, vp, u64, u64, vp, u64, u64]),
     "tf_make_token_expert_pairs": (C.c_int, [vp, vp, u32, u32, vp]),
     "tf_group_pairs": (C.c_int, [vp, u32, i32, i32, i32, i32, vp, u32, vp, vp, vp, vp, C.POINTER(u32), vp, C.POINTER(u32)]),
+    "tf_group_routes_device": (C.c_int, [vp, vp, vp, vp, u32, u32, u32, C.POINTER(DeviceRoutes)]),
+    "tf_grouped_moe_batched": (C.c_int, [vp, vp, vp, u64, u32, vp, u64, C.POINTER(ExpertOffsets), C.POINTER(DeviceRoutes),
+                                         vp, vp, C.c_int, u32, u32, u32, u32]),
+    "tf_moe_reduce_token_major": (C.c_int, [vp, vp, vp, C.c_int, vp, vp, u32, vp, u32, u32, u32, u32]),
+    "tf_shared_expert_int4_block": (C.c_int, [vp, vp, vp, u64, u32, C.POINTER(Projection), C.POINTER(Projection),
+                                              C.POINTER(Projection), vp, u64, u32, vp, u32]),
     "tf_rmsnorm": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, u32, u32, u32, f32, C.c_int]),
     "tf_layer_tail": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, f32, f32]),
 }

@@ -308,3 +308,90 @@ class FusedLayerTail:
         ctx.check(ctx.lib.tf_layer_tail(ctx.handle, _stream(stream), _ptr(h2), _ptr(h1), _ptr(hidden), _ptr(w_postffn2),
                                         _ptr(w_postffn), rows, d, d if stride_elements is None else stride_elements,
                                         eps, layer_scalar))
+
+
+class DeviceRoutes:
+    """Device buffers for the grouped routing metadata (``tf_device_routes``). Replaces the
+    CPU-built ``PrefillMoEGroupedRoutes`` + ``makeStreamedMetadataBuffers``
+    (Kernels/Prefill/MoE/PrefillGroupedRoutedMoE.swift:368-384)."""
+
+    def __init__(self, max_tokens: int, top_k: int, num_experts: int, device="cuda"):
+        n = max_tokens * top_k
+        i32 = dict(dtype=torch.int32, device=device)
+        self.max_tokens, self.top_k, self.num_experts = max_tokens, top_k, num_experts
+        self.sorted_pairs = torch.zeros(max(n, 1) * 4, **i32)
+        self.per_expert_offsets = torch.zeros(num_experts, **i32)
+        self.per_expert_counts = torch.zeros(num_experts, **i32)
+        self.groups = torch.zeros(num_experts * 3, **i32)
+        self.chunk_group = torch.zeros(n // 16 + num_experts + 1, **i32)
+        self.chunk_start = torch.zeros(num_experts, **i32)
+        self.counters = torch.zeros(4, **i32)
+        self.c_struct = _capi.DeviceRoutes(*[_ptr(t) for t in (self.sorted_pairs, self.per_expert_offsets,
+                                                               self.per_expert_counts, self.groups, self.chunk_group,
+                                                               self.chunk_start, self.counters)])
+
+    def to_host(self, query_count: int) -> PrefillMoEGroupedRoutes:
+        n = query_count * self.top_k
+        counters = self.counters.cpu().numpy().view(np.uint32)
+        ng = int(counters[0])
+        return PrefillMoEGroupedRoutes(
+            self.sorted_pairs.cpu().numpy().view(np.uint32)[:n * 4].copy().view(PAIR_DTYPE),
+            self.per_expert_offsets.cpu().numpy().view(np.uint32), self.per_expert_counts.cpu().numpy().view(np.uint32),
+            self.groups.cpu().numpy().view(np.uint32)[:ng * 3].copy().view(GROUP_DTYPE), np.zeros(0, dtype=TILE_DTYPE),
+            query_count)
+
+
+class PrefillGroupedRoutedMoE:
+    """``PrefillGroupedRoutedMoE`` (Kernels/Prefill/MoE/PrefillGroupedRoutedMoE.swift:339-463) over
+    HBM-resident experts, with the grouping done on the device."""
+
+    def __init__(self, context: TurboContext):
+        self.context = context
+
+    def encode_group_routes(self, indices, weights, query_count: int, top_k: int, num_experts: int,
+                            routes: DeviceRoutes, *, stream=None):
+        ctx = self.context
+        ctx.check(ctx.lib.tf_group_routes_device(ctx.handle, _stream(stream), _ptr(indices), _ptr(weights),
+                                                 query_count, top_k, num_experts, C.byref(routes.c_struct)))
+
+    def encode_streamed_batched(self, hidden, pool_layer_base, expert_stride: int, offsets: ExpertOffsets,
+                                routes: DeviceRoutes, acts_scratch, route_partials, query_count: int, d: int, f: int,
+                                top_k: int, *, hidden_offset=0, hidden_stride_elements=None, partials_f32=False,
+                                stream=None):
+        ctx = self.context
+        ctx.check(ctx.lib.tf_grouped_moe_batched(
+            ctx.handle, _stream(stream), _ptr(hidden), hidden_offset,
+            d if hidden_stride_elements is None else hidden_stride_elements, _ptr(pool_layer_base), expert_stride,
+            C.byref(offsets), C.byref(routes.c_struct), _ptr(acts_scratch), _ptr(route_partials),
+            1 if partials_f32 else 0, query_count, d, f, top_k))
+
+
+class PrefillMoE:
+    """``PrefillMoE`` (Kernels/Prefill/MoE/PrefillMoE.swift:4-40)."""
+
+    def __init__(self, context: TurboContext):
+        self.context = context
+
+    def encode_reduce_token_major(self, route_partials, route_weights, h2, query_count: int, top_k: int, d: int, *,
+                                  residual=None, residual_stride=None, h2_stride=None, partials_f32=False, stream=None):
+        ctx = self.context
+        ctx.check(ctx.lib.tf_moe_reduce_token_major(
+            ctx.handle, _stream(stream), _ptr(route_partials), 1 if partials_f32 else 0, _ptr(route_weights),
+            _ptr(residual), d if residual_stride is None else residual_stride, _ptr(h2),
+            d if h2_stride is None else h2_stride, query_count, top_k, d))
+
+
+class PrefillSharedExpert:
+    """``PrefillSharedExpert`` (Kernels/Prefill/MoE/PrefillSharedExpert.swift:4-60), batched over rows."""
+
+    def __init__(self, context: TurboContext):
+        self.context = context
+
+    def encode_block(self, x, gate: SharedExpertProjection, up: SharedExpertProjection, down: SharedExpertProjection,
+                     y, scratch_act, rows: int, *, x_offset=0, x_stride=None, y_offset=0, y_stride=None, stream=None):
+        ctx = self.context
+        g, u, dn = gate.c_struct(), up.c_struct(), down.c_struct()
+        ctx.check(ctx.lib.tf_shared_expert_int4_block(
+            ctx.handle, _stream(stream), _ptr(x), x_offset, gate.cols if x_stride is None else x_stride,
+            C.byref(g), C.byref(u), C.byref(dn), _ptr(y), y_offset, gate.cols if y_stride is None else y_stride,
+            _ptr(scratch_act), rows))
