@@ -283,6 +283,72 @@ tf_status tf_shared_expert_int4_block(tf_context* ctx, void* stream,
                                       void* y, uint64_t y_off, uint32_t y_stride_elements,
                                       void* scratch_act, uint32_t rows);
 
+/* ---- HBM-resident expert pool (replaces SSD streaming) ---- */
+/* One allocation of layers * experts blobs of `stride` bytes in the .gturbo blob
+ * layout. Replaces PreadExpertStreamer and its LFU slot cache
+ * (Infrastructure/Streaming/PreadExpertStreamer.swift:57-414) and
+ * Model.routedExpertOffsets / planRoutedExperts / fetchRoutedExperts
+ * (Runtime/Inference/ModelExpertIO.swift:21-142): every expert is resident, so a
+ * "fetch" is tf_expert_pool_ptr(). tf_expert_pool_create allocates device memory. */
+typedef struct tf_pool tf_pool;
+tf_status tf_expert_pool_create(tf_context* ctx, uint32_t layers, uint32_t experts, uint64_t stride,
+                                const tf_expert_offsets* offsets, tf_pool** out);
+void tf_expert_pool_destroy(tf_pool* pool);
+/* Device address of a blob; NULL when out of range. */
+const void* tf_expert_pool_ptr(const tf_pool* pool, uint32_t layer, uint32_t expert);
+uint64_t tf_expert_pool_bytes(const tf_pool* pool);
+/* Copy one blob (as stored in packed_experts/layer_XX.bin) from HOST memory. */
+tf_status tf_expert_pool_upload(tf_pool* pool, void* stream, uint32_t layer, uint32_t expert,
+                                const void* host_blob, uint64_t bytes);
+/* Seeded synthetic weights generated on the device: uniform codes, per-group
+ * scale |N(0,1)| * 0.004 (8-bit: / 16), bias -zero_point * scale + N(0, 1e-4), bf16. */
+tf_status tf_fill_affine_synthetic(tf_context* ctx, void* stream, void* weights, void* scales, void* biases,
+                                   uint32_t rows, uint32_t cols, uint32_t bits, uint64_t seed);
+tf_status tf_expert_pool_fill_synthetic(tf_pool* pool, void* stream, uint64_t seed, uint32_t d, uint32_t f);
+
+/* ---- fused MoE block and layer stack (new entry points; the reference spreads
+ * this over RealForwardRunner with two CPU round trips per layer) ---- */
+typedef struct tf_moe_layer {
+    tf_projection router;            /* 8-bit affine [num_experts, d] */
+    const void* effective_scale;     /* bf16 [d]  (RealForwardRunner.swift:352-376) */
+    const void* per_expert_scale;    /* bf16 [num_experts] */
+    const float* logit_bias;         /* fp32 [num_experts] or NULL */
+    const void* pool_layer_base;     /* tf_expert_pool_ptr(pool, layer, 0) */
+    uint64_t expert_stride;
+    tf_expert_offsets offsets;
+    tf_projection shared_gate, shared_up, shared_down;   /* 4-bit affine */
+    uint32_t num_experts, d, f, fs, top_k;
+} tf_moe_layer;
+
+/* Device scratch for up to max_tokens tokens (router output, routes, activations,
+ * partials). Replaces the runner-owned scratch buffers
+ * (RealForwardRunner.swift:176-199; Runtime/Prefill/PrefillChunkScratch.swift:79-152).
+ * Partials are fp32 when max_tokens <= 64 (decode arithmetic), fp16 otherwise
+ * (the prefill kernels' rounding). tf_workspace_create allocates device memory. */
+typedef struct tf_workspace tf_workspace;
+tf_status tf_workspace_create(tf_context* ctx, uint32_t max_tokens, uint32_t d, uint32_t f, uint32_t fs,
+                              uint32_t top_k, uint32_t num_experts, tf_workspace** out);
+void tf_workspace_destroy(tf_workspace* ws);
+uint64_t tf_workspace_bytes(const tf_workspace* ws);
+const uint32_t* tf_workspace_indices(const tf_workspace* ws);   /* device [tokens, top_k] of the last forward */
+const void* tf_workspace_weights(const tf_workspace* ws);        /* device fp16 [tokens, top_k] */
+const tf_device_routes* tf_workspace_routes(const tf_workspace* ws);
+
+/* y[t] = half(shared(x[t]) + sum_r w[t,r] * routed_{idx[t,r]}(x[t])) for `tokens`
+ * fp16 rows: router + top-8 + softmax, device grouping, grouped gate/up + GeGLU,
+ * grouped down, shared expert, weighted combine. No host synchronisation. */
+tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer* layer,
+                               const void* x, uint32_t x_stride_elements,
+                               void* y, uint32_t y_stride_elements, uint32_t tokens, tf_workspace* ws);
+
+/* A stack of MoE blocks with RMSNorm between layers and a residual stream:
+ * x = rmsnorm(h) * w_l; h = h + block_l(x). hidden is fp16 [tokens, d], in place. */
+typedef struct tf_stack tf_stack;
+tf_status tf_stack_create(tf_context* ctx, const tf_moe_layer* layers, const void* const* norm_weights_bf16,
+                          uint32_t layer_count, float eps, tf_stack** out);
+void tf_stack_destroy(tf_stack* stack);
+tf_status tf_stack_forward(tf_stack* stack, void* stream, void* hidden, uint32_t tokens, tf_workspace* ws);
+
 /* ---- norms ---- */
 /* y = half(x * rsqrt(mean(x^2) + eps) * w_bf16); weight NULL = no-scale form.
  * Replaces RMSNorm.encode and the block form PrefillRMSNorm

@@ -1,0 +1,161 @@
+"""GPU parity of the fused MoE block and the layer stack against the oracle applied per token
+(BASELINE configs 1 and 2, and a small-dimension stack)."""
+import numpy as np
+import pytest
+
+from helpers import from_dev, to_dev
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2     # BASELINE: outputs within 1e-2 relative L2 of the fp32-dequantised oracle
+
+
+def _affine_from(o, tensor):
+    packed, scales, biases = tensor.download()
+    return o.AffineMatrix(packed, scales, biases, tensor.bits, tensor.cols)
+
+
+def _oracle_offsets(o, coff):
+    return o.ExpertOffsets(coff.gate_w_off, coff.gate_s_off, coff.gate_b_off, coff.up_w_off, coff.up_s_off,
+                           coff.up_b_off, coff.down_w_off, coff.down_s_off, coff.down_b_off)
+
+
+def _oracle_block(o, layer, pool, x16_rows, tokens, logit_bias=None):
+    """Per-token oracle of one block. Returns (indices, y_f32 [T, D], w_f32)."""
+    router = _affine_from(o, layer.router)
+    sg, su, sd = (_affine_from(o, t) for t in (layer.shared_gate, layer.shared_up, layer.shared_down))
+    eff = from_dev(layer.effective_scale, np.uint16)
+    gain = from_dev(layer.per_expert_scale, np.uint16)
+    logits = o.router_logits(router, x16_rows, eff)
+    if logit_bias is not None:
+        logits = (logits + logit_bias.astype(np.float32)).astype(np.float32)
+    idx, w16, w32 = o.router_select(logits, gain, layer.top_k)
+    off = _oracle_offsets(o, pool.offsets)
+    cache = {}
+    ys = []
+    for t in tokens:
+        blobs = []
+        for e in idx[t]:
+            if int(e) not in cache:
+                cache[int(e)] = pool.download(layer.layer_index, int(e))
+            blobs.append(cache[int(e)])
+        shared16, _ = o.shared_expert_int4(sg, su, sd, x16_rows[t], order=0)
+        _, y32, _ = o.moe_routed_decode(blobs, off, x16_rows[t], w16[t], shared16, layer.d, layer.f, order=0)
+        ys.append(y32)
+    return idx, np.stack(ys), w32
+
+
+@pytest.fixture(scope="module")
+def production_layer(tf_ctx):
+    """One production-shaped layer: 128 experts of the .gturbo blob layout (430 MB)."""
+    import torch
+    from turbo_fieldfare_b200.stack import ExpertPool, MoEBlockLayer
+    pool = ExpertPool(tf_ctx, 1, 128, 2816, 704)
+    assert pool.stride == 3358720 and pool.nbytes == 429916160      # docs/SYSTEM_DESIGN.md:166
+    pool.fill_synthetic(11)
+    layer = MoEBlockLayer(tf_ctx, pool, 0, 2816, 704, 2112, 128, 8)
+    layer.fill_synthetic(12)
+    torch.cuda.synchronize()
+    yield layer, pool
+    pool.close()
+
+
+def test_synthetic_weights_follow_the_config_distributions(tf_ctx, oracle, production_layer):
+    o = oracle
+    layer, pool = production_layer
+    blob = pool.download(0, 5)
+    off = pool.offsets
+    codes = blob[off.gate_w_off:off.gate_w_off + 704 * 1408]
+    nib = np.concatenate([codes & 0xF, codes >> 4])
+    hist = np.bincount(nib, minlength=16) / nib.size
+    assert np.all(np.abs(hist - 1 / 16) < 0.002)                      # uniform 0..15
+    s = o.bf16_to_f32(blob[off.gate_s_off:off.gate_s_off + 704 * 44 * 2].view(np.uint16))
+    b = o.bf16_to_f32(blob[off.gate_b_off:off.gate_b_off + 704 * 44 * 2].view(np.uint16))
+    assert abs(s.mean() - 0.004 * np.sqrt(2 / np.pi)) < 2e-4 and s.min() >= 0      # |N(0,1)| * 0.004
+    assert np.abs(b + 8 * s).max() < 1e-3 + 8 * s.max() * 2 ** -8                # -8 * scale + N(0, 1e-4), bf16
+    assert np.any(blob[off.down_w_off:off.down_w_off + 64] != 0) and np.all(blob[pool.payload:] == 0)
+    other = pool.download(0, 6)
+    assert not np.array_equal(other[:4096], blob[:4096])
+
+
+@pytest.mark.parametrize("T", [1, 64])
+def test_block_forward_configs_1_and_2(tf_ctx, oracle, production_layer, T):
+    """Config 1 (one token) and config 2 (64 tokens): top-k indices bit-exact, outputs within tolerance."""
+    import torch
+    from turbo_fieldfare_b200.stack import MoEBlock, Workspace
+    o = oracle
+    layer, pool = production_layer
+    rng = np.random.default_rng(100 + T)
+    x16 = o.f32_to_f16(rng.standard_normal((T, 2816)).astype(np.float32))
+    ws = Workspace(tf_ctx, T, 2816, 704, 2112, 8, 128)
+    y = torch.zeros(T * 2816, dtype=torch.int16, device="cuda")
+    launches0 = tf_ctx.launch_count
+    MoEBlock(tf_ctx, layer).forward(to_dev(x16), y, T, ws)
+    torch.cuda.synchronize()
+    assert tf_ctx.launch_count - launches0 == 7
+    idx_gpu, w_gpu = ws.routing(T)
+    check = range(T) if T == 1 else (0, 13, 63)
+    idx_ref, y_ref, w_ref = _oracle_block(o, layer, pool, x16, check)
+    assert np.array_equal(idx_gpu, idx_ref), "top-k indices differ from the oracle"
+    assert np.max(np.abs(o.f16_to_f32(w_gpu) - w_ref)) < 5e-3
+    got = o.f16_to_f32(from_dev(y, np.uint16).reshape(T, 2816))
+    for i, t in enumerate(check):
+        assert o.rel_l2(got[t], y_ref[i]) < TOL, f"token {t}"
+    if T == 64:
+        counts = np.bincount(idx_gpu.reshape(-1), minlength=128)
+        assert counts.sum() == 512 and (counts > 0).sum() > 100        # near-uniform load touches most experts
+
+
+def test_block_forward_with_zipf_bias_and_fp16_partials(tf_ctx, oracle, production_layer):
+    """Config-3 routing skew at a test-sized token count; workspace > 64 tokens selects fp16 partials."""
+    import torch
+    from turbo_fieldfare_b200.stack import MoEBlock, Workspace
+    o = oracle
+    layer, pool = production_layer
+    rng = np.random.default_rng(7)
+    T = 96
+    p = 1.0 / (rng.permutation(128) + 1) ** 1.1
+    bias = np.log(p / p.sum()).astype(np.float32)
+    layer.set_logit_bias(bias)
+    try:
+        x16 = o.f32_to_f16(rng.standard_normal((T, 2816)).astype(np.float32))
+        ws = Workspace(tf_ctx, 128, 2816, 704, 2112, 8, 128)
+        y = torch.zeros(T * 2816, dtype=torch.int16, device="cuda")
+        MoEBlock(tf_ctx, layer).forward(to_dev(x16), y, T, ws)
+        torch.cuda.synchronize()
+        idx_gpu, _ = ws.routing(T)
+        check = (0, 50, 95)
+        idx_ref, y_ref, _ = _oracle_block(o, layer, pool, x16, check, logit_bias=bias)
+        assert np.array_equal(idx_gpu, idx_ref)
+        got = o.f16_to_f32(from_dev(y, np.uint16).reshape(T, 2816))
+        for i, t in enumerate(check):
+            assert o.rel_l2(got[t], y_ref[i]) < TOL
+        counts = np.bincount(idx_gpu.reshape(-1), minlength=128)
+        assert counts.max() > 4 * counts.mean()                          # the skew is real
+    finally:
+        layer.set_logit_bias(None)
+
+
+def test_small_stack_matches_oracle(tf_ctx, oracle):
+    """Config-4 structure at small dimensions: 3 layers, RMSNorm between layers, residual stream."""
+    import torch
+    from turbo_fieldfare_b200.stack import MoEStack
+    o = oracle
+    stack = MoEStack(tf_ctx, layers=3, d=256, f=128, fs=192, num_experts=16, top_k=8, seed=5, align=256)
+    T = 4
+    rng = np.random.default_rng(9)
+    h16 = o.f32_to_f16(rng.standard_normal((T, 256)).astype(np.float32))
+    hid = to_dev(h16.copy())
+    ws = stack.workspace(T)
+    stack.forward(hid, T, ws)
+    torch.cuda.synchronize()
+    got = o.f16_to_f32(from_dev(hid, np.uint16).reshape(T, 256))
+    # oracle: same recurrence with fp16 rounding at the same points
+    h = h16.copy()
+    for l, layer in enumerate(stack.layers):
+        x = o.rmsnorm(h, from_dev(stack.norm_weights[l], np.uint16))
+        _, y32, _ = _oracle_block(o, layer, stack.pool, x, range(T))
+        y16 = o.f32_to_f16(y32)
+        h = o.f32_to_f16(o.f16_to_f32(h) + o.f16_to_f32(y16))
+    ref = o.f16_to_f32(h)
+    assert o.rel_l2(got, ref) < TOL
+    stack.close()

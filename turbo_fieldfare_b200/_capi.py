@@ -43,6 +43,14 @@ class Tile(C.Structure):
     _fields_ = [("group_start", u32), ("group_count", u32), ("pair_start", u32), ("pair_count", u32)]
 
 
+class MoELayer(C.Structure):
+    """tf_moe_layer: device pointers and dimensions of one MoE block."""
+    _fields_ = [("router", Projection), ("effective_scale", vp), ("per_expert_scale", vp), ("logit_bias", vp),
+                ("pool_layer_base", vp), ("expert_stride", u64), ("offsets", ExpertOffsets),
+                ("shared_gate", Projection), ("shared_up", Projection), ("shared_down", Projection),
+                ("num_experts", u32), ("d", u32), ("f", u32), ("fs", u32), ("top_k", u32)]
+
+
 class DeviceRoutes(C.Structure):
     """tf_device_routes: device buffers of the grouped routing metadata."""
     _fields_ = [(n, vp) for n in ("sorted_pairs", "per_expert_offsets", "per_expert_counts", "groups",
@@ -76,6 +84,23 @@ SIGNATURES = {
     "tf_moe_reduce_token_major": (C.c_int, [vp, vp, vp, C.c_int, vp, vp, u32, vp, u32, u32, u32, u32]),
     "tf_shared_expert_int4_block": (C.c_int, [vp, vp, vp, u64, u32, C.POINTER(Projection), C.POINTER(Projection),
                                               C.POINTER(Projection), vp, u64, u32, vp, u32]),
+    "tf_expert_pool_create": (C.c_int, [vp, u32, u32, u64, C.POINTER(ExpertOffsets), C.POINTER(vp)]),
+    "tf_expert_pool_destroy": (None, [vp]),
+    "tf_expert_pool_ptr": (vp, [vp, u32, u32]),
+    "tf_expert_pool_bytes": (u64, [vp]),
+    "tf_expert_pool_upload": (C.c_int, [vp, vp, u32, u32, vp, u64]),
+    "tf_fill_affine_synthetic": (C.c_int, [vp, vp, vp, vp, vp, u32, u32, u32, u64]),
+    "tf_expert_pool_fill_synthetic": (C.c_int, [vp, vp, u64, u32, u32]),
+    "tf_workspace_create": (C.c_int, [vp, u32, u32, u32, u32, u32, u32, C.POINTER(vp)]),
+    "tf_workspace_destroy": (None, [vp]),
+    "tf_workspace_bytes": (u64, [vp]),
+    "tf_workspace_indices": (vp, [vp]),
+    "tf_workspace_weights": (vp, [vp]),
+    "tf_workspace_routes": (C.POINTER(DeviceRoutes), [vp]),
+    "tf_moe_block_forward": (C.c_int, [vp, vp, C.POINTER(MoELayer), vp, u32, vp, u32, u32, vp]),
+    "tf_stack_create": (C.c_int, [vp, C.POINTER(MoELayer), C.POINTER(vp), u32, f32, C.POINTER(vp)]),
+    "tf_stack_destroy": (None, [vp]),
+    "tf_stack_forward": (C.c_int, [vp, vp, vp, u32, vp]),
     "tf_rmsnorm": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, u32, u32, u32, f32, C.c_int]),
     "tf_layer_tail": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, f32, f32]),
 }

@@ -1,0 +1,347 @@
+// HBM-resident expert pool, fused MoE block and layer stack.
+//
+// Replaces, for a GPU whose memory holds every expert:
+//   - the expert buffer manager: PreadExpertStreamer's LFU slot cache and pread path
+//     (Infrastructure/Streaming/PreadExpertStreamer.swift:57-414) and
+//     Model.planRoutedExperts / fetchRoutedExperts / routedExpertOffsets
+//     (Runtime/Inference/ModelExpertIO.swift:21-142): "fetch" becomes
+//     base + layer * layer_bytes + expert * stride;
+//   - the MoE section of the forward runner (Runtime/Inference/RealForwardRunner.swift:902-1186
+//     prefill, :1449-1693 decode), whose two CPU<->GPU round trips per layer exist only to
+//     plan SSD reads: here router ids, grouping and expert addressing stay on the device.
+#include <vector>
+
+#include "tf_common.cuh"
+
+struct tf_pool {
+    tf_context* ctx;
+    uint8_t* base;
+    uint32_t layers, experts;
+    uint64_t stride;
+    tf_expert_offsets offsets;
+};
+
+struct tf_workspace {
+    tf_context* ctx;
+    uint32_t max_tokens, d, f, fs, top_k, num_experts;
+    uint8_t* base;          // one allocation
+    uint32_t* indices;      // [T, K]
+    uint16_t* weights;      // [T, K] fp16
+    tf_device_routes routes;
+    uint16_t* acts;         // [T*K, F] fp16
+    void* partials;         // [T, K, D] fp32 (T <= f32_tokens) or fp16
+    uint16_t* shared_act;   // [T, Fs]
+    uint16_t* shared_y;     // [T, D]
+    uint16_t* x_norm;       // [T, D] (stack)
+    uint16_t* y_block;      // [T, D] (stack)
+    uint64_t bytes;
+};
+
+struct tf_stack {
+    tf_context* ctx;
+    std::vector<tf_moe_layer> layers;
+    std::vector<const void*> norm_weights;   // bf16 [D] per layer
+    float eps;
+};
+
+namespace tf {
+
+constexpr uint32_t kF32PartialTokens = 64;   // decode-sized batches keep fp32 partials (decode kernel semantics)
+
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+
+__device__ __forceinline__ float unit_float(uint64_t r) { return ((float)(r >> 40) + 0.5f) * (1.0f / 16777216.0f); }
+
+// One thread per 64-column group: uniform codes, scale = |N(0,1)| * scale_mul,
+// bias = -zero_point * scale + N(0, bias_sigma), both rounded to bf16.
+__global__ void fill_affine_kernel(uint8_t* W, uint16_t* S, uint16_t* B, uint64_t groups_total, int bits,
+                                   uint64_t seed, float scale_mul, float zero_point, float bias_sigma) {
+    const uint64_t gid = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (gid >= groups_total) return;
+    uint64_t st = mix64(seed ^ (gid * 0xD1342543DE82EF95ull));
+    const int words = bits == 4 ? 4 : 8;            // 64-bit words of codes per group
+    uint64_t* wp = reinterpret_cast<uint64_t*>(W + gid * (bits == 4 ? 32 : 64));
+    for (int i = 0; i < words; ++i) { st = mix64(st); wp[i] = st; }
+    st = mix64(st);
+    const float u1 = unit_float(st);
+    st = mix64(st);
+    const float u2 = unit_float(st);
+    const float r = sqrtf(-2.0f * __logf(u1));
+    const float n1 = r * __cosf(6.2831853f * u2), n2 = r * __sinf(6.2831853f * u2);
+    const float scale = fabsf(n1) * scale_mul;
+    const float bias = -zero_point * scale + n2 * bias_sigma;
+    S[gid] = __bfloat16_as_ushort(__float2bfloat16_rn(scale));
+    B[gid] = __bfloat16_as_ushort(__float2bfloat16_rn(bias));
+}
+
+// h += y (fp16, one rounding), then x = half(rmsnorm(h) * w). One block per row.
+__global__ void __launch_bounds__(256)
+residual_rmsnorm_kernel(uint16_t* __restrict__ h, const uint16_t* __restrict__ y, const uint16_t* __restrict__ w,
+                        uint16_t* __restrict__ x, uint32_t d, float eps) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    float* hv = reinterpret_cast<float*>(smem);
+    __shared__ float red[8];
+    uint16_t* hr = h + (size_t)blockIdx.x * d;
+    float acc = 0.0f;
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+        float v = f16_bits_to_float(hr[i]);
+        if (y) {
+            v = __half2float(__float2half_rn(v + f16_bits_to_float(y[(size_t)blockIdx.x * d + i])));
+            hr[i] = __half_as_ushort(__float2half_rn(v));
+        }
+        hv[i] = v;
+        acc = fmaf(v, v, acc);
+    }
+    acc = warp_sum(acc);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    float tot = (threadIdx.x & 31) < 8 ? red[threadIdx.x & 31] : 0.0f;
+    tot = warp_sum(tot);
+    const float inv = rsqrtf(tot / (float)d + eps);
+    if (x)
+        for (uint32_t i = threadIdx.x; i < d; i += blockDim.x)
+            x[(size_t)blockIdx.x * d + i] = __half_as_ushort(__float2half_rn(hv[i] * inv * bf16_bits_to_float(w[i])));
+}
+
+}  // namespace tf
+
+extern "C" {
+
+// ---------------------------------------------------------------------------
+// pool
+// ---------------------------------------------------------------------------
+
+tf_status tf_expert_pool_create(tf_context* ctx, uint32_t layers, uint32_t experts, uint64_t stride,
+                                const tf_expert_offsets* offsets, tf_pool** out) {
+    const char* name = "tf_expert_pool_create";
+    TF_REQUIRE(ctx, ctx != nullptr && out != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    *out = nullptr;
+    TF_REQUIRE(ctx, layers > 0 && experts > 0 && stride > 0 && offsets, TF_ERR_INVALID_ARGUMENT, "%s: bad dimensions", name);
+    TF_REQUIRE(ctx, stride % 256 == 0, TF_ERR_ALIGNMENT, "%s: expert stride must be a multiple of 256 bytes", name);
+    uint8_t* base = nullptr;
+    const uint64_t bytes = (uint64_t)layers * experts * stride;
+    cudaError_t e = cudaMalloc(&base, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return tf::fail(ctx, TF_ERR_OUT_OF_MEMORY, "failed to allocate expert pool of %llu bytes: %s",
+                        (unsigned long long)bytes, cudaGetErrorString(e));
+    }
+    tf_pool* p = new tf_pool{ctx, base, layers, experts, stride, *offsets};
+    *out = p;
+    return TF_OK;
+}
+
+void tf_expert_pool_destroy(tf_pool* pool) {
+    if (!pool) return;
+    cudaFree(pool->base);
+    delete pool;
+}
+
+const void* tf_expert_pool_ptr(const tf_pool* pool, uint32_t layer, uint32_t expert) {
+    if (!pool || layer >= pool->layers || expert >= pool->experts) return nullptr;
+    return pool->base + ((uint64_t)layer * pool->experts + expert) * pool->stride;
+}
+
+uint64_t tf_expert_pool_bytes(const tf_pool* pool) {
+    return pool ? (uint64_t)pool->layers * pool->experts * pool->stride : 0;
+}
+
+tf_status tf_expert_pool_upload(tf_pool* pool, void* stream, uint32_t layer, uint32_t expert,
+                                const void* host_blob, uint64_t bytes) {
+    const char* name = "tf_expert_pool_upload";
+    TF_REQUIRE(nullptr, pool != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: pool is NULL", name);
+    tf_context* ctx = pool->ctx;
+    TF_REQUIRE(ctx, host_blob != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: blob is NULL", name);
+    TF_REQUIRE(ctx, layer < pool->layers && expert < pool->experts, TF_ERR_INVALID_ARGUMENT,
+               "%s: (layer %u, expert %u) out of range", name, layer, expert);
+    TF_REQUIRE(ctx, bytes <= pool->stride, TF_ERR_INVALID_ARGUMENT, "%s: blob of %llu bytes exceeds the stride %llu",
+               name, (unsigned long long)bytes, (unsigned long long)pool->stride);
+    TF_CUDA(ctx, cudaMemcpyAsync(const_cast<void*>(tf_expert_pool_ptr(pool, layer, expert)), host_blob, bytes,
+                                 cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+    return TF_OK;
+}
+
+tf_status tf_fill_affine_synthetic(tf_context* ctx, void* stream, void* weights, void* scales, void* biases,
+                                   uint32_t rows, uint32_t cols, uint32_t bits, uint64_t seed) {
+    const char* name = "tf_fill_affine_synthetic";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, weights && scales && biases, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, (bits == 4 || bits == 8) && cols % tf::kGroup == 0, TF_ERR_INVALID_ARGUMENT, "%s: bits must be 4 or 8, cols a multiple of 64", name);
+    TF_REQUIRE(ctx, tf::aligned(weights, 8) && tf::aligned(scales, 2) && tf::aligned(biases, 2), TF_ERR_ALIGNMENT, "%s: alignment", name);
+    const uint64_t groups = (uint64_t)rows * (cols / tf::kGroup);
+    if (groups == 0) return TF_OK;
+    const float scale_mul = bits == 4 ? 0.004f : 0.004f / 16.0f;
+    const float zero = bits == 4 ? 8.0f : 128.0f;
+    tf::fill_affine_kernel<<<(uint32_t)((groups + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint8_t*>(weights), static_cast<uint16_t*>(scales), static_cast<uint16_t*>(biases), groups,
+        (int)bits, seed, scale_mul, zero, 1e-4f);
+    return tf::check_launch(ctx, name);
+}
+
+tf_status tf_expert_pool_fill_synthetic(tf_pool* pool, void* stream, uint64_t seed, uint32_t d, uint32_t f) {
+    const char* name = "tf_expert_pool_fill_synthetic";
+    TF_REQUIRE(nullptr, pool != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: pool is NULL", name);
+    tf_context* ctx = pool->ctx;
+    const tf_expert_offsets& o = pool->offsets;
+    for (uint32_t l = 0; l < pool->layers; ++l)
+        for (uint32_t e = 0; e < pool->experts; ++e) {
+            uint8_t* b = const_cast<uint8_t*>(static_cast<const uint8_t*>(tf_expert_pool_ptr(pool, l, e)));
+            const uint64_t s0 = seed + ((uint64_t)l * pool->experts + e) * 3;
+            tf_status s = tf_fill_affine_synthetic(ctx, stream, b + o.gate_w_off, b + o.gate_s_off, b + o.gate_b_off, f, d, 4, s0);
+            if (!s) s = tf_fill_affine_synthetic(ctx, stream, b + o.up_w_off, b + o.up_s_off, b + o.up_b_off, f, d, 4, s0 + 1);
+            if (!s) s = tf_fill_affine_synthetic(ctx, stream, b + o.down_w_off, b + o.down_s_off, b + o.down_b_off, d, f, 4, s0 + 2);
+            if (s) return s;
+        }
+    return TF_OK;
+}
+
+// ---------------------------------------------------------------------------
+// workspace
+// ---------------------------------------------------------------------------
+
+tf_status tf_workspace_create(tf_context* ctx, uint32_t max_tokens, uint32_t d, uint32_t f, uint32_t fs,
+                              uint32_t top_k, uint32_t num_experts, tf_workspace** out) {
+    const char* name = "tf_workspace_create";
+    TF_REQUIRE(ctx, ctx != nullptr && out != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    *out = nullptr;
+    TF_REQUIRE(ctx, max_tokens > 0 && d > 0 && f > 0 && fs > 0 && top_k > 0 && num_experts > 0, TF_ERR_INVALID_ARGUMENT, "%s: bad dimensions", name);
+    const uint64_t T = max_tokens, K = top_k, E = num_experts;
+    auto up = [](uint64_t v) { return (v + 255) / 256 * 256; };
+    uint64_t off = 0;
+    auto take = [&](uint64_t bytes) { uint64_t o = off; off += up(bytes); return o; };
+    const uint64_t o_idx = take(T * K * 4), o_w = take(T * K * 2), o_pairs = take(T * K * 16), o_eoff = take(E * 4),
+                   o_ecnt = take(E * 4), o_groups = take(E * 12), o_cgroup = take((T * K / 16 + E + 1) * 4),
+                   o_cstart = take(E * 4), o_counters = take(16), o_acts = take(T * K * f * 2),
+                   o_partials = take(T * K * d * (T <= tf::kF32PartialTokens ? 4 : 2)), o_sact = take(T * fs * 2),
+                   o_sy = take(T * d * 2), o_xn = take(T * d * 2), o_yb = take(T * d * 2);
+    uint8_t* base = nullptr;
+    cudaError_t e = cudaMalloc(&base, off);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return tf::fail(ctx, TF_ERR_OUT_OF_MEMORY, "failed to allocate workspace of %llu bytes: %s", (unsigned long long)off, cudaGetErrorString(e));
+    }
+    cudaMemset(base, 0, off);
+    tf_workspace* w = new tf_workspace();
+    w->ctx = ctx; w->max_tokens = max_tokens; w->d = d; w->f = f; w->fs = fs; w->top_k = top_k; w->num_experts = num_experts;
+    w->base = base; w->bytes = off;
+    w->indices = reinterpret_cast<uint32_t*>(base + o_idx);
+    w->weights = reinterpret_cast<uint16_t*>(base + o_w);
+    w->routes.sorted_pairs = reinterpret_cast<tf_pair*>(base + o_pairs);
+    w->routes.per_expert_offsets = reinterpret_cast<uint32_t*>(base + o_eoff);
+    w->routes.per_expert_counts = reinterpret_cast<uint32_t*>(base + o_ecnt);
+    w->routes.groups = reinterpret_cast<tf_group*>(base + o_groups);
+    w->routes.chunk_group = reinterpret_cast<uint32_t*>(base + o_cgroup);
+    w->routes.chunk_start = reinterpret_cast<uint32_t*>(base + o_cstart);
+    w->routes.counters = reinterpret_cast<uint32_t*>(base + o_counters);
+    w->acts = reinterpret_cast<uint16_t*>(base + o_acts);
+    w->partials = base + o_partials;
+    w->shared_act = reinterpret_cast<uint16_t*>(base + o_sact);
+    w->shared_y = reinterpret_cast<uint16_t*>(base + o_sy);
+    w->x_norm = reinterpret_cast<uint16_t*>(base + o_xn);
+    w->y_block = reinterpret_cast<uint16_t*>(base + o_yb);
+    *out = w;
+    return TF_OK;
+}
+
+void tf_workspace_destroy(tf_workspace* ws) {
+    if (!ws) return;
+    cudaFree(ws->base);
+    delete ws;
+}
+
+uint64_t tf_workspace_bytes(const tf_workspace* ws) { return ws ? ws->bytes : 0; }
+
+// Device addresses of the routing results of the last block forward (for inspection by tests).
+const uint32_t* tf_workspace_indices(const tf_workspace* ws) { return ws ? ws->indices : nullptr; }
+const void* tf_workspace_weights(const tf_workspace* ws) { return ws ? ws->weights : nullptr; }
+const tf_device_routes* tf_workspace_routes(const tf_workspace* ws) { return ws ? &ws->routes : nullptr; }
+
+// ---------------------------------------------------------------------------
+// fused block and stack
+// ---------------------------------------------------------------------------
+
+tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer* layer,
+                               const void* x, uint32_t x_stride_elements,
+                               void* y, uint32_t y_stride_elements, uint32_t tokens, tf_workspace* ws) {
+    const char* name = "tf_moe_block_forward";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, layer && x && y && ws, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    TF_REQUIRE(ctx, tokens <= ws->max_tokens, TF_ERR_SCRATCH_TOO_SMALL, "%s: %u tokens exceed the workspace (%u)", name, tokens, ws->max_tokens);
+    TF_REQUIRE(ctx, layer->d == ws->d && layer->f == ws->f && layer->fs == ws->fs && layer->top_k == ws->top_k &&
+                        layer->num_experts == ws->num_experts,
+               TF_ERR_DIMENSION_MISMATCH, "%s: layer dimensions differ from the workspace", name);
+    TF_REQUIRE(ctx, layer->router.rows == layer->num_experts && layer->router.cols == layer->d, TF_ERR_DIMENSION_MISMATCH,
+               "%s: router is (%u,%u), expected (%u,%u)", name, layer->router.rows, layer->router.cols, layer->num_experts, layer->d);
+    if (tokens == 0) return TF_OK;
+    const uint32_t d = layer->d, f = layer->f, K = layer->top_k, E = layer->num_experts;
+    tf_status s = tf_router_gemma4_block(ctx, stream, layer->router.weights, layer->router.weights_off,
+                                         layer->router.scales, layer->router.scales_off,
+                                         layer->router.biases, layer->router.biases_off,
+                                         x, 0, TF_FP16, layer->effective_scale, 0, layer->per_expert_scale, 0,
+                                         layer->logit_bias, ws->indices, 0, ws->weights, 0, nullptr,
+                                         tokens, E, d, K, x_stride_elements);
+    if (s) return s;
+    s = tf_group_routes_device(ctx, stream, ws->indices, ws->weights, tokens, K, E, &ws->routes);
+    if (s) return s;
+    // The partial dtype follows the workspace's capacity so that one workspace
+    // always runs the same arithmetic whatever the call's token count.
+    const int f32 = ws->max_tokens <= tf::kF32PartialTokens ? 1 : 0;
+    s = tf_grouped_moe_batched(ctx, stream, x, 0, x_stride_elements, layer->pool_layer_base, layer->expert_stride,
+                               &layer->offsets, &ws->routes, ws->acts, ws->partials, f32, tokens, d, f, K);
+    if (s) return s;
+    s = tf_shared_expert_int4_block(ctx, stream, x, 0, x_stride_elements, &layer->shared_gate, &layer->shared_up,
+                                    &layer->shared_down, ws->shared_y, 0, d, ws->shared_act, tokens);
+    if (s) return s;
+    return tf_moe_reduce_token_major(ctx, stream, ws->partials, f32, ws->weights, ws->shared_y, d, y,
+                                     y_stride_elements, tokens, K, d);
+}
+
+tf_status tf_stack_create(tf_context* ctx, const tf_moe_layer* layers, const void* const* norm_weights_bf16,
+                          uint32_t layer_count, float eps, tf_stack** out) {
+    const char* name = "tf_stack_create";
+    TF_REQUIRE(ctx, ctx != nullptr && out != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    *out = nullptr;
+    TF_REQUIRE(ctx, layers && norm_weights_bf16 && layer_count > 0, TF_ERR_INVALID_ARGUMENT, "%s: no layers", name);
+    tf_stack* st = new tf_stack();
+    st->ctx = ctx;
+    st->eps = eps;
+    st->layers.assign(layers, layers + layer_count);
+    st->norm_weights.assign(norm_weights_bf16, norm_weights_bf16 + layer_count);
+    *out = st;
+    return TF_OK;
+}
+
+void tf_stack_destroy(tf_stack* st) { delete st; }
+
+// hidden [tokens, d] fp16, contiguous, updated in place:
+//   for each layer: x = rmsnorm(h) * w_l;  h = h + block_l(x)
+// (the residual add of layer l is fused into the norm of layer l+1; a final add closes the stack).
+tf_status tf_stack_forward(tf_stack* st, void* stream, void* hidden, uint32_t tokens, tf_workspace* ws) {
+    const char* name = "tf_stack_forward";
+    TF_REQUIRE(nullptr, st != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: stack is NULL", name);
+    tf_context* ctx = st->ctx;
+    TF_REQUIRE(ctx, hidden && ws, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    TF_REQUIRE(ctx, tokens <= ws->max_tokens, TF_ERR_SCRATCH_TOO_SMALL, "%s: %u tokens exceed the workspace (%u)", name, tokens, ws->max_tokens);
+    if (tokens == 0) return TF_OK;
+    const uint32_t d = ws->d;
+    const size_t smem = (size_t)d * sizeof(float);
+    TF_REQUIRE(ctx, smem <= 48 * 1024, TF_ERR_UNSUPPORTED, "%s: D too large", name);
+    cudaStream_t cs = static_cast<cudaStream_t>(stream);
+    uint16_t* h = static_cast<uint16_t*>(hidden);
+    for (size_t l = 0; l < st->layers.size(); ++l) {
+        tf::residual_rmsnorm_kernel<<<tokens, 256, smem, cs>>>(h, l == 0 ? nullptr : ws->y_block,
+                                                              static_cast<const uint16_t*>(st->norm_weights[l]),
+                                                              ws->x_norm, d, st->eps);
+        if (tf_status s = tf::check_launch(ctx, "residual_rmsnorm")) return s;
+        if (tf_status s = tf_moe_block_forward(ctx, stream, &st->layers[l], ws->x_norm, d, ws->y_block, d, tokens, ws)) return s;
+    }
+    tf::residual_rmsnorm_kernel<<<tokens, 256, smem, cs>>>(h, ws->y_block, nullptr, nullptr, d, st->eps);
+    return tf::check_launch(ctx, "residual_add");
+}
+
+}  // extern "C"
