@@ -1,0 +1,401 @@
+#!/usr/bin/env python
+"""Benchmark of the routed-expert hot path on B200: the synthetic 30-layer MoE stack of
+BASELINE.json (config 4): a 4096-token prefill followed by 256 decode steps at batch 1 and
+256 at batch 64, reported as whole-job tokens/s.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (CUDA, sm_100a)
+    python bench.py --impl reference ...                     # the CPU restatement on the host cores
+
+One "step" is one pass of the whole job. `value` is timed with the inputs resident in HBM;
+`e2e` runs the same job through the public Python API from pinned HOST buffers with the
+host<->device copies inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+D, F, FS, E, K, LAYERS = 2816, 704, 2112, 128, 8, 30
+PREFILL_TOKENS, DECODE_STEPS, DECODE_BATCH = 4096, 256, 64
+EXPERT_BYTES = 3345408            # gate + up + down planes of one expert
+SHARED_BYTES = 10036224           # shared expert, 4-bit, Fs = 2112
+ROUTER_BYTES = 382976             # 8-bit router 128 x 2816 with its planes
+METRIC = "moe_stack_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def tokens_per_job(prefill, steps, batch):
+    return prefill + steps * 1 + steps * batch
+
+
+class ClockSampler:
+    """nvidia-smi clock/throttle samples during the timed region."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu_index), "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        busy = [s for s in sm if s > 500] or sm
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------
+# CPU baseline: the oracle's restatement of the reference kernels, on the host cores
+# ---------------------------------------------------------------------------
+
+def cpu_sample(sample_tokens: int, threads: int | None = None):
+    """Time `sample_tokens` tokens through ONE layer (router, top-8, 8 routed experts in the
+    kernels' lane order, shared expert, combine) on the host and scale to the 30-layer stack.
+    Returns (tokens_per_s, cores, description, seconds)."""
+    from oracle import oracle as o
+    o.build()
+    if threads:
+        o.lib().tfo_set_num_threads(threads)
+    cores = o.num_threads()
+    rng = np.random.default_rng(0)
+    pool_experts = 16
+    off, payload, stride = o.blob_layout(D, F)
+
+    def rand_mat(m, n, bits=4):
+        codes = rng.integers(0, 256, size=(m, n // 2 if bits == 4 else n), dtype=np.uint8)
+        scale = (np.abs(rng.standard_normal((m, n // 64))) * (0.004 if bits == 4 else 0.00025)).astype(np.float32)
+        bias = (-(8.0 if bits == 4 else 128.0) * scale).astype(np.float32)
+        return o.AffineMatrix(codes, o.f32_to_bf16(scale), o.f32_to_bf16(bias), bits, n)
+
+    blobs = [o.pack_blob(rand_mat(F, D), rand_mat(F, D), rand_mat(D, F), off, stride) for _ in range(pool_experts)]
+    router = rand_mat(E, D, 8)
+    sg, su, sd = rand_mat(FS, D), rand_mat(FS, D), rand_mat(D, FS)
+    eff = o.f32_to_bf16(np.full(D, D ** -0.5, dtype=np.float32))
+    gain = o.f32_to_bf16(np.ones(E, dtype=np.float32))
+    x16 = o.f32_to_f16(rng.standard_normal((sample_tokens, D)).astype(np.float32))
+    t0 = time.perf_counter()
+    for t in range(sample_tokens):
+        logits = o.router_logits(router, x16[t], eff)
+        idx, w16, _ = o.router_select(logits, gain, K)
+        shared16, _ = o.shared_expert_int4(sg, su, sd, x16[t], order=1)
+        o.moe_routed_decode([blobs[int(e) % pool_experts] for e in idx[0]], off, x16[t], w16[0], shared16, D, F, order=1)
+    dt = time.perf_counter() - t0
+    per_token_stack = dt / sample_tokens * LAYERS
+    desc = (f"{sample_tokens} tokens x 1 layer (router + top-8 + 8 routed experts + shared expert, kernel lane order, "
+            f"scalar C -O2 with OpenMP row partitioning), scaled x{LAYERS} layers")
+    return 1.0 / per_token_stack, cores, desc, dt
+
+
+def run_reference(args):
+    """The reference has no CPU production path and its Swift/Metal code cannot run here; this arm
+    times the C restatement of its kernels (oracle/) with all host threads."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = 128
+    times, value, cores, desc = [], None, None, None
+    for i in range(args.warmup + args.steps):
+        v, cores, desc, dt = cpu_sample(sample)
+        if i >= args.warmup:
+            times.append(dt)
+    mean_dt = sum(times) / len(times)
+    value = sample / (mean_dt * LAYERS)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": mean_dt * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "config4: 30-layer MoE stack (128 experts, top-8, shared expert, D=2816)",
+                   "sample": desc},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this library has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from turbo_fieldfare_b200.kernels import PrefillGroupedRoutedMoE, PrefillRouter, TurboContext
+    from turbo_fieldfare_b200.stack import MoEStack
+
+    prefill_tokens, steps_dec, batch = args.prefill_tokens, args.decode_steps, args.decode_batch
+    ctx = TurboContext(local_rank)
+    stack = MoEStack(ctx, layers=args.layers, seed=2026 + rank)
+    if args.zipf:
+        rng = np.random.default_rng(17)
+        p = 1.0 / (rng.permutation(E) + 1) ** 1.1
+        stack.set_logit_bias(np.log(p / p.sum()).astype(np.float32))
+    ws_prefill, ws_b1, ws_bn = stack.workspace(prefill_tokens), stack.workspace(1), stack.workspace(batch)
+
+    gen = torch.Generator().manual_seed(1234 + rank)
+    host_prefill = torch.randn(prefill_tokens, D, generator=gen).half().pin_memory()
+    host_dec1 = torch.randn(steps_dec, 1, D, generator=gen).half().pin_memory()
+    host_decn = torch.randn(steps_dec, batch, D, generator=gen).half().pin_memory()
+    host_out_prefill = torch.empty_like(host_prefill).pin_memory()
+    host_out_dec1 = torch.empty_like(host_dec1).pin_memory()
+    host_out_decn = torch.empty_like(host_decn).pin_memory()
+    dev_prefill, dev_dec1, dev_decn = host_prefill.cuda(), host_dec1.cuda(), host_decn.cuda()
+    work_prefill = torch.empty_like(dev_prefill)
+    out_dec1, out_decn = torch.empty_like(dev_dec1), torch.empty_like(dev_decn)
+    h1 = torch.zeros(1, D, dtype=torch.float16, device="cuda")
+    hn = torch.zeros(batch, D, dtype=torch.float16, device="cuda")
+
+    # one CUDA graph per decode batch size: 30 layers of launches replayed per step
+    stream = torch.cuda.Stream()
+    launches = {}
+
+    def capture(h, tokens, ws):
+        with torch.cuda.stream(stream):
+            stack.forward(h, tokens, ws, stream=stream)           # warm-up: sets kernel attributes
+            stream.synchronize()
+            before = ctx.launch_count
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                stack.forward(h, tokens, ws, stream=torch.cuda.current_stream())
+            launches[tokens] = ctx.launch_count - before
+        return g
+
+    use_graphs = not args.no_graphs
+    g1 = capture(h1, 1, ws_b1) if use_graphs else None
+    gn = capture(hn, batch, ws_bn) if use_graphs else None
+    counters = {"launches": 0}
+
+    def job(from_host: bool):
+        """One whole job on the current stream."""
+        cs = torch.cuda.current_stream()
+        if from_host:
+            dev_prefill.copy_(host_prefill, non_blocking=True)
+            dev_dec1.copy_(host_dec1, non_blocking=True)
+            dev_decn.copy_(host_decn, non_blocking=True)
+        work_prefill.copy_(dev_prefill)
+        before = ctx.launch_count
+        stack.forward(work_prefill, prefill_tokens, ws_prefill, stream=cs)
+        counters["launches"] += ctx.launch_count - before
+        for h, dev_in, dev_out, g, ws, tok in ((h1, dev_dec1, out_dec1, g1, ws_b1, 1), (hn, dev_decn, out_decn, gn, ws_bn, batch)):
+            for i in range(steps_dec):
+                h.copy_(dev_in[i])
+                if g is not None:
+                    g.replay()
+                    counters["launches"] += launches[tok]
+                else:
+                    before = ctx.launch_count
+                    stack.forward(h, tok, ws, stream=cs)
+                    counters["launches"] += ctx.launch_count - before
+                dev_out[i].copy_(h)
+        if from_host:
+            host_out_prefill.copy_(work_prefill, non_blocking=True)
+            host_out_dec1.copy_(out_dec1, non_blocking=True)
+            host_out_decn.copy_(out_decn, non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(from_host: bool, steps: int, warmup: int):
+        for _ in range(warmup):
+            job(from_host)
+        barrier()
+        counters["launches"] = 0
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        start.record()
+        for _ in range(steps):
+            job(from_host)
+        end.record()
+        barrier()
+        clocks = sampler.stop() if rank == 0 else None
+        ms = start.elapsed_time(end)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps, clocks, counters["launches"]
+
+    ms_step, clocks, n_launches = timed(False, args.steps, args.warmup)
+    ms_e2e, _, _ = timed(True, max(1, min(args.steps, 2)), 1)
+    tokens = tokens_per_job(prefill_tokens, steps_dec, batch) * world
+    value = tokens / (ms_step * 1e-3)
+    e2e_value = tokens / (ms_e2e * 1e-3)
+    io_bytes = int(host_prefill.numel() + host_dec1.numel() + host_decn.numel()) * 2
+
+    # phase breakdown (informative)
+    def phase_ms(fn, reps=2):
+        fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(reps):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / reps
+
+    cs = torch.cuda.current_stream()
+    ms_prefill = phase_ms(lambda: stack.forward(work_prefill, prefill_tokens, ws_prefill, stream=cs))
+    ms_dec1 = phase_ms(lambda: g1.replay() if g1 else stack.forward(h1, 1, ws_b1, stream=cs), 20)
+    ms_decn = phase_ms(lambda: gn.replay() if gn else stack.forward(hn, batch, ws_bn, stream=cs), 20)
+
+    # roofline of the dominant kernel: the grouped tensor-core expert kernel at decode batch 64
+    # (gate/up launch + down launch of one layer timed as a pair, distinct layers back to back so
+    # that nothing is re-read from L2).
+    roofline = measure_roofline(torch, ctx, stack, ws_bn, hn, batch, PrefillRouter, PrefillGroupedRoutedMoE)
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": f"config4: {args.layers}-layer MoE stack (128 experts int4 g64, top-8, shared expert, "
+                               f"RMSNorm between layers, attention omitted): {prefill_tokens}-token prefill + "
+                               f"{steps_dec} decode steps at batch 1 + {steps_dec} at batch {batch}",
+                   "tokens_per_step": tokens, "routing": "zipf(1.1) logit bias" if args.zipf else "computed logits",
+                   "l2": "every step streams 13.2 GB of distinct layer weights (>> 126 MB L2)",
+                   "cuda_graphs": use_graphs, "parallelism": "replicas" if world > 1 else "single GPU",
+                   "phase_ms": {"prefill": ms_prefill, "decode_b1_per_step": ms_dec1, f"decode_b{batch}_per_step": ms_decn},
+                   "phase_tokens_per_s": {"prefill": prefill_tokens / ms_prefill * 1e3, "decode_b1": 1e3 / ms_dec1,
+                                          f"decode_b{batch}": batch / ms_decn * 1e3}},
+        "clocks": clocks,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
+                "ms_per_step": ms_e2e},
+        "gpu_launches": n_launches,
+        "roofline": roofline,
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            v, cores, desc, dt = cpu_sample(args.cpu_sample_tokens)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc, "seconds": dt}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def measure_roofline(torch, ctx, stack, ws, h, batch, PrefillRouter, PrefillGroupedRoutedMoE):
+    peaks_path = ROOT / "MEASURED_PEAKS.json"
+    if peaks_path.exists():
+        peak, peak_src = float(json.loads(peaks_path.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    from turbo_fieldfare_b200.kernels import DeviceRoutes
+    moe = PrefillGroupedRoutedMoE(ctx)
+    router = PrefillRouter(ctx)
+    x = torch.randn(batch, D, device="cuda").half()
+    layers = stack.layers
+    idx = torch.zeros(batch, K, dtype=torch.int32, device="cuda")
+    w = torch.zeros(batch, K, dtype=torch.int16, device="cuda")
+    routes = [DeviceRoutes(batch, K, E) for _ in layers]
+    acts = torch.zeros(batch * K * F, dtype=torch.int16, device="cuda")
+    partials = torch.zeros(batch * K * D, dtype=torch.float32, device="cuda")
+    touched = []
+    for l, layer in enumerate(layers):
+        r = layer.router
+        router.encode_gemma4_block(r.buffer, r.buffer, r.buffer, x, layer.effective_scale, layer.per_expert_scale, idx, w,
+                                   batch, E, D, K, D, scales_offset=r.s_off, biases_offset=r.b_off, hidden_dtype=1)
+        moe.encode_group_routes(idx, w, batch, K, E, routes[l])
+        torch.cuda.synchronize()
+        touched.append(int(routes[l].counters.cpu().numpy().view(np.uint32)[0]))
+
+    def run_all():
+        for l, layer in enumerate(layers):
+            moe.encode_streamed_batched(x, layer.pool.ptr(layer.layer_index, 0), layer.pool.stride, layer.pool.offsets,
+                                        routes[l], acts, partials, batch, D, F, K, partials_f32=True)
+    for _ in range(3):
+        run_all()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    s.record()
+    for _ in range(reps):
+        run_all()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / reps
+    launches = 2 * len(layers)
+    bytes_total = sum(touched) * EXPERT_BYTES + len(layers) * batch * (D * 2 + K * D * 4)   # weights + activations in/out
+    achieved = bytes_total / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": "grouped_mma_kernel (gate/up and down launches of one layer, batch 64)",
+            "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
+            "traffic": None, "bytes_per_launch": bytes_total / launches, "us_per_launch": ms * 1e3 / launches,
+            "experts_touched_per_layer": sum(touched) / len(touched)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS)
+    ap.add_argument("--decode-steps", type=int, default=DECODE_STEPS)
+    ap.add_argument("--decode-batch", type=int, default=DECODE_BATCH)
+    ap.add_argument("--zipf", action="store_true", help="add the Zipf(1.1) router logit bias of config 3")
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-sample-tokens", type=int, default=256)
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "b200":
+        print(f"note: warmup {args.warmup} < 3 breaks the timing rules; use it for smoke runs only", file=sys.stderr)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -512,11 +512,17 @@ static tf_status launch_grouped(tf_context* ctx, void* stream, const GroupedArgs
     const SmemLayout<NMAT> lay{warps, ng};
     const size_t smem = lay.total();
     auto kern = grouped_mma_kernel<NMAT, DENSE, OUT_MODE>;
-    TF_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    int per_sm = 1;
-    TF_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, (int)(warps * kWarp), smem));
-    if (per_sm < 1) per_sm = 1;
-    if (per_sm > 8) per_sm = 8;
+    // Attribute and occupancy are queried once per (instantiation, warp count) and cached,
+    // so steady-state calls are a bare launch (and safe inside stream capture).
+    static int cached_per_sm[kMaxGroupedWarps + 1] = {0};
+    int per_sm = cached_per_sm[warps];
+    if (per_sm == 0) {
+        TF_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        TF_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, (int)(warps * kWarp), smem));
+        if (per_sm < 1) per_sm = 1;
+        if (per_sm > 8) per_sm = 8;
+        cached_per_sm[warps] = per_sm;
+    }
     uint32_t grid = (uint32_t)ctx->sm_count * (uint32_t)per_sm;
     if (DENSE) {
         const uint64_t items = (uint64_t)((args.dense_tokens + kChunkTokens - 1) / kChunkTokens) * (args.rows / kTileRows);

@@ -1,0 +1,56 @@
+"""Small, self-contained GPU cases for profiling one kernel at a time under ncu.
+
+    python -m turbo_fieldfare_b200.profile_cases block --tokens 64 --layers 2 --iters 3
+    python -m turbo_fieldfare_b200.profile_cases gemv --rows 262144 --iters 3
+
+Each case holds well under a few GB on the device, streams more than the 126 MB L2 per
+launch (one layer of experts is 430 MB), and launches only a handful of kernels, so that a
+capture of one to three launches ends by itself.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from .kernels import DequantInt4GEMV, TurboContext
+from .stack import AffineTensor, MoEStack
+
+
+def case_block(args) -> None:
+    ctx = TurboContext(0)
+    stack = MoEStack(ctx, layers=args.layers, seed=3)
+    ws = stack.workspace(args.tokens)
+    h = torch.randn(args.tokens, 2816, device="cuda").half()
+    for _ in range(args.iters):
+        stack.forward(h, args.tokens, ws)
+    torch.cuda.synchronize()
+    print(f"block case done: tokens={args.tokens} layers={args.layers} iters={args.iters} launches={ctx.launch_count}")
+
+
+def case_gemv(args) -> None:
+    ctx = TurboContext(0)
+    mat = AffineTensor(args.rows, 2816, 4)
+    mat.fill_synthetic(ctx, 5)
+    x = torch.randn(2816, device="cuda").half()
+    y = torch.zeros(args.rows, dtype=torch.float16, device="cuda")
+    k = DequantInt4GEMV(ctx)
+    for _ in range(args.iters):
+        k.encode(mat.buffer, mat.buffer, mat.buffer, x, y, args.rows, 2816, scales_offset=mat.s_off, biases_offset=mat.b_off)
+    torch.cuda.synchronize()
+    print(f"gemv case done: rows={args.rows} bytes={mat.w_bytes + 2 * mat.sb_bytes}")
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["block", "gemv"])
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--layers", type=int, default=2)
+    ap.add_argument("--rows", type=int, default=262144)
+    ap.add_argument("--iters", type=int, default=3)
+    args = ap.parse_args()
+    {"block": case_block, "gemv": case_gemv}[args.case](args)
+
+
+if __name__ == "__main__":
+    main()
