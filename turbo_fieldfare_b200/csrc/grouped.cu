@@ -10,17 +10,20 @@
 //   - the per-row shared-expert loop (Kernels/Prefill/MoE/PrefillSharedExpert.swift:11-59).
 //
 // Kernel design (memory-bound; HBM roofline): weights are the B operand of
-// mma.sync.m16n8k16 (8 weight rows per warp tile), up to 16 tokens are the A
-// operand. A 4-bit code q placed in the low mantissa bits of an fp16 IS the
-// subnormal q * 2^-24, so "dequantisation" is one AND per two codes and the
+// mma.sync.m16n8k16 (8 weight rows per warp tile), up to 8 tokens are rows 0..7
+// of the A operand. A 4-bit code q placed in the low mantissa bits of an fp16 IS
+// the subnormal q * 2^-24, so "dequantisation" is one AND per two codes and the
 // tensor core multiplies exact integers by fp16 activations with fp32
 // accumulation. Scale and bias are applied per 64-column group after the MMAs:
 //     y += (s * 2^24) * acc + b * sum_k x_k
 // i.e. the reference's group factoring (Metal/Quant/dequant_int4.metal:14-19).
-// K is split across the warps of a CTA (4 groups each); activations live in
-// registers as MMA fragments; packed weights and the scale planes stream
-// through a cp.async ring (16-byte copies, 4 stages); warp partials are summed
-// in warp order through shared memory, so results are deterministic.
+// The activations of a chunk (<= 8 tokens of one expert) are staged once per
+// CTA in shared memory, already permuted into MMA fragment order; every warp
+// then streams whole 8-row tiles on its own: packed codes and scale rows come
+// straight from global memory into registers, prefetched one step (4 groups)
+// ahead, with no block-wide barrier in the steady state. For very small
+// batches a tile is split along K over `ks` warps that meet at a named barrier
+// and are summed in warp order, so results stay deterministic.
 #include "tf_common.cuh"
 
 namespace tf {
@@ -31,9 +34,9 @@ namespace tf {
 
 constexpr int kGroupThreads = 256;
 constexpr int kGroupPerThread = 4;
-constexpr int kChunkTokens = 16;      // tokens per work chunk of the grouped kernels
+constexpr int kChunkTokens = 8;       // tokens per work chunk of the grouped kernels (rows 0..7 of the MMA's A operand)
 
-// counters: [0] group count, [1] total chunks (sum over groups of ceil(count/16)), [2] pair count
+// counters: [0] group count, [1] total chunks (sum over groups of ceil(count/8)), [2] pair count
 __global__ void __launch_bounds__(kGroupThreads)
 group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __restrict__ weights,
                     uint32_t T, uint32_t K, uint32_t E,
@@ -124,12 +127,12 @@ group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __rest
 // grouped small-batch expert kernels
 // ---------------------------------------------------------------------------
 
-constexpr int kGPW = 4;            // 64-column groups per warp
-constexpr int kStages = 4;         // cp.async ring depth
-constexpr int kTileRows = 8;       // weight rows per MMA tile (the n of m16n8k16)
+constexpr int kStep = 4;               // 64-column groups per prefetch step
+constexpr int kTileRows = 8;           // weight rows per MMA tile (the n of m16n8k16)
 constexpr float kTwo24 = 16777216.0f;
-constexpr int kMaxGroupedWarps = 12;   // K <= 12 * 4 * 64 = 3072 columns
-constexpr int kMaxGroupedThreads = kMaxGroupedWarps * kWarp;
+constexpr int kStreamWarps = 16;       // warps per CTA
+constexpr int kStreamThreads = kStreamWarps * kWarp;
+constexpr int kMaxKSplit = 8;
 
 struct MatPlanes {
     const uint8_t* W;
@@ -161,310 +164,307 @@ struct GroupedArgs {
     uint32_t k;                // columns (D for gate/up, F for down)
     uint32_t top_k;
     uint32_t dense_tokens;     // dense mode: number of tokens
+    uint32_t ks;               // warps that share one tile along K (1, 2, 4 or 8)
 };
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
-    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
-    const int sz = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(sz) : "memory");
+// rows 8..15 of A (a1, a3) are zero: a chunk holds at most 8 tokens, so only c0, c1 are used.
+// First MMA of a group: C is the constant zero, so no accumulator has to be cleared.
+__device__ __forceinline__ void mma16816_first(float& c0, float& c1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float d2, d3;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%9,%9,%9,%9};"
+                 : "=f"(c0), "=f"(c1), "=f"(d2), "=f"(d3)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.0f));
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                         uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+__device__ __forceinline__ void mma16816_acc(float& c0, float& c1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float d2, d3;
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%9,%9};"
+                 : "+f"(c0), "+f"(c1), "=f"(d2), "=f"(d3)
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.0f));
 }
-
-// Activation fragments of one token for one 64-column group, as held by lane
-// (g, t): 16 consecutive values starting at 16 * pi(t), pi = (0, 2, 1, 3),
-// rearranged to the operand order of the four MMAs; odd columns pre-scaled by
-// 1/16 because their codes sit four mantissa bits higher.
-struct XFrag {
-    uint32_t a[8];
-    float sum;       // full 64-column sum of the token's activations (quad-reduced)
-};
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t r;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
     return r;
 }
-
 __device__ __forceinline__ uint32_t hmul2_sixteenth(uint32_t v) {
     const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&v), __half2half2(__float2half_rn(0.0625f)));
     return *reinterpret_cast<const uint32_t*>(&r);
 }
-
-__device__ __forceinline__ void load_xfrag(XFrag& f, const uint16_t* __restrict__ row /* null = zero token */,
-                                           uint32_t group, int t) {
-    uint32_t r[8];
-    if (row) {
-        const int piece = ((t & 1) << 1) | (t >> 1);
-        const uint4* p = reinterpret_cast<const uint4*>(row + group * kGroup + piece * 16);
-        const uint4 lo = __ldg(p), hi = __ldg(p + 1);
-        r[0] = lo.x; r[1] = lo.y; r[2] = lo.z; r[3] = lo.w;
-        r[4] = hi.x; r[5] = hi.y; r[6] = hi.z; r[7] = hi.w;
-    } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) r[i] = 0;
-    }
-    float s = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&r[i]));
-        s += v.x + v.y;
-    }
-    s += __shfl_xor_sync(kFullMask, s, 1);
-    s += __shfl_xor_sync(kFullMask, s, 2);
-    f.sum = s;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        f.a[4 * h + 0] = prmt(r[4 * h + 0], r[4 * h + 2], 0x5410);                    // (x0, x4)
-        f.a[4 * h + 1] = prmt(r[4 * h + 1], r[4 * h + 3], 0x5410);                    // (x2, x6)
-        f.a[4 * h + 2] = hmul2_sixteenth(prmt(r[4 * h + 0], r[4 * h + 2], 0x7632));   // (x1, x5) / 16
-        f.a[4 * h + 3] = hmul2_sixteenth(prmt(r[4 * h + 1], r[4 * h + 3], 0x7632));   // (x3, x7) / 16
-    }
+__device__ __forceinline__ uint2 ldg_nc_u2(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// Four MMAs of one 64-column group: piece = this lane's 16 codes (two words).
-template <bool HI>
-__device__ __forceinline__ void group_mma(float (&c)[4], uint32_t w0, uint32_t w1, const XFrag& lo, const XFrag& hi) {
+// Four MMAs of one 64-column group. (w0, w1) = this lane's 16 codes (bytes [8t, 8t+8) of the row's
+// group); xl, xh = the token's 16 activations at the same columns, already in operand order:
+//   xl = {(x0,x4), (x2,x6), (x1,x5)/16, (x3,x7)/16}, xh the same for x8..x15.
+// Odd columns are pre-scaled by 1/16 because their codes sit four mantissa bits higher.
+__device__ __forceinline__ void group_mma(float& c0, float& c1, uint32_t w0, uint32_t w1, const uint4& xl, const uint4& xh) {
     const uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
-    mma16816(c, lo.a[0], HI ? hi.a[0] : 0u, lo.a[1], HI ? hi.a[1] : 0u, w0 & 0x000F000Fu, w0s & 0x000F000Fu);
-    mma16816(c, lo.a[2], HI ? hi.a[2] : 0u, lo.a[3], HI ? hi.a[3] : 0u, w0 & 0x00F000F0u, w0s & 0x00F000F0u);
-    mma16816(c, lo.a[4], HI ? hi.a[4] : 0u, lo.a[5], HI ? hi.a[5] : 0u, w1 & 0x000F000Fu, w1s & 0x000F000Fu);
-    mma16816(c, lo.a[6], HI ? hi.a[6] : 0u, lo.a[7], HI ? hi.a[7] : 0u, w1 & 0x00F000F0u, w1s & 0x00F000F0u);
+    mma16816_first(c0, c1, xl.x, xl.y, w0 & 0x000F000Fu, w0s & 0x000F000Fu);
+    mma16816_acc(c0, c1, xl.z, xl.w, w0 & 0x00F000F0u, w0s & 0x00F000F0u);
+    mma16816_acc(c0, c1, xh.x, xh.y, w1 & 0x000F000Fu, w1s & 0x000F000Fu);
+    mma16816_acc(c0, c1, xh.z, xh.w, w1 & 0x00F000F0u, w1s & 0x00F000F0u);
 }
 
 enum OutMode { kOutActs = 0, kOutPartialF16 = 1, kOutPartialF32 = 2, kOutDenseF16 = 3 };
 
-// Shared-memory layout per CTA:
-//   ring[stage][warp][mat][step][lane] uint4      (packed codes, warp private)
-//   sb[stage][mat][2][8 * NG] uint16              (scale and bias rows of the tile)
-//   red[warp][mat][16 * 8] float                  (warp partials)
+// Shared memory: xlo[ng][32] uint4 | xhi[ng][32] uint4 | xsum[ng][8] float | red[2][warps][NMAT][64] float
+__host__ __device__ inline size_t stream_smem_bytes(uint32_t ng, int nmat) {
+    return (size_t)ng * 32 * 16 * 2 + (size_t)ng * 8 * 4 + (size_t)2 * kStreamWarps * nmat * 64 * 4;
+}
+
+// What one step (up to kStep groups of one 8-row tile) needs from global memory.
 template <int NMAT>
-struct SmemLayout {
-    uint32_t warps, ng;
-    __host__ __device__ size_t ring_bytes() const { return (size_t)kStages * warps * NMAT * (kGPW / 2) * kWarp * 16; }
-    __host__ __device__ size_t sb_stage_bytes() const { return (size_t)NMAT * 2 * kTileRows * ng * 2; }
-    __host__ __device__ size_t sb_bytes() const { return (size_t)kStages * sb_stage_bytes(); }
-    __host__ __device__ size_t red_bytes() const { return (size_t)warps * NMAT * 128 * sizeof(float); }
-    __host__ __device__ size_t total() const { return ring_bytes() + sb_bytes() + red_bytes(); }
+struct StepRegs {
+    uint2 w[NMAT][kStep];          // this lane's 16 codes of each group (row g)
+    uint2 s0[NMAT], s1[NMAT];      // 4 consecutive bf16 scales of rows 2t and 2t+1
+    uint2 b0[NMAT], b1[NMAT];      // and biases
 };
 
+__device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+
 template <int NMAT, bool DENSE, int OUT_MODE>
-__global__ void __launch_bounds__(kMaxGroupedThreads)
-grouped_mma_kernel(const GroupedArgs args) {
+__global__ void __launch_bounds__(kStreamThreads)
+grouped_stream_kernel(const GroupedArgs args) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t warps = blockDim.x / kWarp;
     const uint32_t ng = args.k / kGroup;
-    const SmemLayout<NMAT> lay{warps, ng};
-    uint4* ring = reinterpret_cast<uint4*>(smem);
-    uint16_t* sb = reinterpret_cast<uint16_t*>(smem + lay.ring_bytes());
-    float* red = reinterpret_cast<float*>(smem + lay.ring_bytes() + lay.sb_bytes());
+    const uint32_t ks = args.ks;
+    const uint32_t row_bytes = args.k / 2;
+    const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
+    const uint32_t xlo_addr = smem_base + lane * 16;
+    const uint32_t xhi_addr = xlo_addr + ng * 512;
+    const uint32_t xsum_addr = smem_base + ng * 1024 + g * 4;
+    uint4* xlo = reinterpret_cast<uint4*>(smem);
+    uint4* xhi = xlo + ng * 32;
+    float* xsum = reinterpret_cast<float*>(smem + (size_t)ng * 1024);
+    float* red = xsum + ng * 8;
 
     const uint32_t tiles = args.rows / kTileRows;
     const uint32_t total_chunks = DENSE ? (args.dense_tokens + kChunkTokens - 1) / kChunkTokens : args.counters[1];
-    const uint64_t total_items = (uint64_t)total_chunks * tiles;
-    // contiguous item range per CTA so that consecutive items share the chunk (activations stay in registers)
-    const uint64_t item_begin = total_items * blockIdx.x / gridDim.x;
-    const uint64_t item_end = total_items * (blockIdx.x + 1) / gridDim.x;
-    if (item_begin >= item_end) return;
+    const uint32_t total_items = total_chunks * tiles;
+    // contiguous item range per CTA: consecutive items share the chunk whose activations sit in shared memory
+    uint32_t item = (uint32_t)((uint64_t)total_items * blockIdx.x / gridDim.x);
+    const uint32_t item_end = (uint32_t)((uint64_t)total_items * (blockIdx.x + 1) / gridDim.x);
 
-    const uint32_t g0 = warp * kGPW;                                   // first group of this warp
-    const uint32_t ngw = g0 < ng ? (ng - g0 < (uint32_t)kGPW ? ng - g0 : (uint32_t)kGPW) : 0u;
-    const size_t row_bytes = args.k / 2;
+    // K split: warp group `grp` of ks warps shares a tile; warp `kw` of the group owns groups [k_begin, k_end)
+    const uint32_t ngroups = kStreamWarps / ks;
+    const uint32_t grp = warp / ks, kw = warp % ks;
+    const uint32_t steps_total = (ng + kStep - 1) / kStep;
+    const uint32_t steps_per_warp = (steps_total + ks - 1) / ks;
+    const uint32_t k_begin = kw * steps_per_warp * kStep < ng ? kw * steps_per_warp * kStep : ng;
+    const uint32_t k_end = (kw + 1) * steps_per_warp * kStep < ng ? (kw + 1) * steps_per_warp * kStep : ng;
+    const bool sb_vec = (ng % 4) == 0;        // 4 consecutive bf16 of a scale row are 8-byte aligned
 
-    // per-chunk state
-    uint32_t cur_chunk = 0xFFFFFFFFu;
-    MatPlanes planes[NMAT];
-    uint32_t ntok = 0, row_base = 0;          // routed: first sorted-pair index; dense: first token
-    XFrag xlo[kGPW], xhi[kGPW];
-
-    auto resolve_chunk = [&](uint32_t chunk, MatPlanes (&pl)[NMAT], uint32_t& ntok_o, uint32_t& base_o) {
+    while (item < item_end) {
+        // ---- segment: the items of this CTA that belong to one chunk ----
+        const uint32_t chunk = item / tiles;
+        const uint32_t tile_begin = item % tiles;
+        const uint32_t seg_items = (item_end - item) < (tiles - tile_begin) ? (item_end - item) : (tiles - tile_begin);
+        MatPlanes pl[NMAT];
+        uint32_t ntok, row_base;
         if constexpr (DENSE) {
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) pl[m] = args.dense[m];
-            base_o = chunk * kChunkTokens;
-            const uint32_t left = args.dense_tokens - base_o;
-            ntok_o = left < (uint32_t)kChunkTokens ? left : (uint32_t)kChunkTokens;
+            row_base = chunk * kChunkTokens;
+            const uint32_t left = args.dense_tokens - row_base;
+            ntok = left < (uint32_t)kChunkTokens ? left : (uint32_t)kChunkTokens;
         } else {
             const uint32_t gi = args.chunk_group[chunk];
-            const tf_group grp = args.groups[gi];
+            const tf_group grpinfo = args.groups[gi];
             const uint32_t cin = chunk - args.chunk_start[gi];
-            const uint8_t* blob = args.pool_base + (uint64_t)grp.expert * args.expert_stride;
+            const uint8_t* blob = args.pool_base + (uint64_t)grpinfo.expert * args.expert_stride;
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
                 pl[m].W = blob + args.w_off[m];
                 pl[m].S = reinterpret_cast<const uint16_t*>(blob + args.s_off[m]);
                 pl[m].B = reinterpret_cast<const uint16_t*>(blob + args.b_off[m]);
             }
-            base_o = grp.pair_start + cin * kChunkTokens;
-            const uint32_t left = grp.pair_count - cin * kChunkTokens;
-            ntok_o = left < (uint32_t)kChunkTokens ? left : (uint32_t)kChunkTokens;
+            row_base = grpinfo.pair_start + cin * kChunkTokens;
+            const uint32_t left = grpinfo.pair_count - cin * kChunkTokens;
+            ntok = left < (uint32_t)kChunkTokens ? left : (uint32_t)kChunkTokens;
         }
-    };
 
-    // issue the cp.async copies of one item into a ring stage
-    auto issue = [&](uint64_t item, int stage) {
-        if (item < item_end) {
-            const uint32_t chunk = (uint32_t)(item / tiles), tile = (uint32_t)(item % tiles);
-            MatPlanes pl[NMAT];
-            uint32_t nt, rb;
-            resolve_chunk(chunk, pl, nt, rb);
-            const uint32_t row = tile * kTileRows + g;
+        __syncthreads();        // every warp is done with the previous chunk's fragments
+        // stage the chunk's activations as MMA fragments: entry (G, lane) holds token g = lane/4,
+        // columns 64 G + 16 t .. + 15 (t = lane%4)
+        for (uint32_t idx = threadIdx.x; idx < ng * 32; idx += blockDim.x) {
+            const uint32_t G = idx >> 5, ln = idx & 31, tg = ln >> 2, tt = ln & 3;
+            uint32_t r[8];
+            if (tg < ntok) {
+                const uint32_t rr = (DENSE || NMAT == 1) ? row_base + tg : args.sorted_pairs[row_base + tg].token;
+                const uint4* p = reinterpret_cast<const uint4*>(args.x + (size_t)rr * args.x_stride + G * kGroup + tt * 16);
+                const uint4 lo = __ldg(p), hi = __ldg(p + 1);
+                r[0] = lo.x; r[1] = lo.y; r[2] = lo.z; r[3] = lo.w;
+                r[4] = hi.x; r[5] = hi.y; r[6] = hi.z; r[7] = hi.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) r[i] = 0;
+            }
+            float sum = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&r[i]));
+                sum += v.x + v.y;
+            }
+            sum += __shfl_xor_sync(kFullMask, sum, 1);
+            sum += __shfl_xor_sync(kFullMask, sum, 2);
+            xlo[idx] = make_uint4(prmt(r[0], r[2], 0x5410), prmt(r[1], r[3], 0x5410),
+                                  hmul2_sixteenth(prmt(r[0], r[2], 0x7632)), hmul2_sixteenth(prmt(r[1], r[3], 0x7632)));
+            xhi[idx] = make_uint4(prmt(r[4], r[6], 0x5410), prmt(r[5], r[7], 0x5410),
+                                  hmul2_sixteenth(prmt(r[4], r[6], 0x7632)), hmul2_sixteenth(prmt(r[5], r[7], 0x7632)));
+            if (tt == 0) xsum[G * 8 + tg] = sum;
+        }
+        __syncthreads();
+
+        // ---- this warp group's tiles of the segment: tile_begin + grp, + ngroups, ... ----
+        const bool tok_valid = (uint32_t)g < ntok;
+        const uint32_t my_tiles = grp < seg_items ? (seg_items - grp + ngroups - 1) / ngroups : 0;
+        const uint32_t nsteps = k_end > k_begin ? (k_end - k_begin + kStep - 1) / kStep : 0;
+
+        auto load_step = [&](StepRegs<NMAT>& sr, uint32_t tile, uint32_t g_first) {
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
+                const uint8_t* wrow = pl[m].W + (size_t)(tile * kTileRows + g) * row_bytes + g_first * 32 + t * 8;
 #pragma unroll
-                for (int s = 0; s < kGPW / 2; ++s) {
-                    const uint32_t grp = g0 + 2 * s + (t >> 1);
-                    const bool valid = (2u * s + (t >> 1)) < ngw;
-                    const uint8_t* src = pl[m].W + (size_t)row * row_bytes + (size_t)(g0 + 2 * s) * 32 + t * 16;
-                    uint4* dst = ring + ((((size_t)stage * warps + warp) * NMAT + m) * (kGPW / 2) + s) * kWarp + lane;
-                    cp_async16(dst, valid ? src : pl[m].W, valid);
-                    (void)grp;
+                for (int i = 0; i < kStep; ++i)
+                    sr.w[m][i] = (g_first + i < k_end) ? ldg_nc_u2(wrow + i * 32) : make_uint2(0u, 0u);
+                const uint16_t* s_r0 = pl[m].S + (size_t)(tile * kTileRows + 2 * t) * ng + g_first;
+                const uint16_t* b_r0 = pl[m].B + (size_t)(tile * kTileRows + 2 * t) * ng + g_first;
+                if (sb_vec) {
+                    sr.s0[m] = __ldg(reinterpret_cast<const uint2*>(s_r0));
+                    sr.s1[m] = __ldg(reinterpret_cast<const uint2*>(s_r0 + ng));
+                    sr.b0[m] = __ldg(reinterpret_cast<const uint2*>(b_r0));
+                    sr.b1[m] = __ldg(reinterpret_cast<const uint2*>(b_r0 + ng));
+                } else {
+                    uint32_t v[4][4];
+#pragma unroll
+                    for (int i = 0; i < kStep; ++i) {
+                        const bool ok = g_first + i < k_end;
+                        v[0][i] = ok ? s_r0[i] : 0u; v[1][i] = ok ? s_r0[ng + i] : 0u;
+                        v[2][i] = ok ? b_r0[i] : 0u; v[3][i] = ok ? b_r0[ng + i] : 0u;
+                    }
+                    sr.s0[m] = make_uint2(v[0][0] | (v[0][1] << 16), v[0][2] | (v[0][3] << 16));
+                    sr.s1[m] = make_uint2(v[1][0] | (v[1][1] << 16), v[1][2] | (v[1][3] << 16));
+                    sr.b0[m] = make_uint2(v[2][0] | (v[2][1] << 16), v[2][2] | (v[2][3] << 16));
+                    sr.b1[m] = make_uint2(v[3][0] | (v[3][1] << 16), v[3][2] | (v[3][3] << 16));
                 }
             }
-            // scale / bias rows of the tile: 8 * ng 16-bit values per plane = ng 16-byte copies
-            const uint32_t copies = NMAT * 2 * ng;
-            for (uint32_t c = threadIdx.x; c < copies; c += blockDim.x) {
-                const uint32_t m = c / (2 * ng), rest = c % (2 * ng), which = rest / ng, j = rest % ng;
-                const uint16_t* plane = which == 0 ? pl[m].S : pl[m].B;
-                const uint8_t* src = reinterpret_cast<const uint8_t*>(plane + (size_t)tile * kTileRows * ng) + j * 16;
-                uint8_t* dst = reinterpret_cast<uint8_t*>(sb) + (size_t)stage * lay.sb_stage_bytes() +
-                               ((size_t)(m * 2 + which) * kTileRows * ng) * 2 + j * 16;
-                cp_async16(dst, src, true);
-            }
-        }
-        cp_async_commit();
-    };
+        };
 
+        StepRegs<NMAT> cur;
+        if (my_tiles > 0 && nsteps > 0) load_step(cur, tile_begin + grp, k_begin);
+        for (uint32_t ti = 0; ti < my_tiles; ++ti) {
+            const uint32_t tile = tile_begin + grp + ti * ngroups;
+            float ya[NMAT][2], yb[NMAT][2];
 #pragma unroll
-    for (int p = 0; p < kStages - 1; ++p) issue(item_begin + p, p);
-
-    for (uint64_t item = item_begin; item < item_end; ++item) {
-        const int stage = (int)((item - item_begin) % kStages);
-        issue(item + kStages - 1, (int)((item - item_begin + kStages - 1) % kStages));
-        cp_async_wait<kStages - 1>();
-        __syncthreads();
-
-        const uint32_t chunk = (uint32_t)(item / tiles), tile = (uint32_t)(item % tiles);
-        if (chunk != cur_chunk) {
-            cur_chunk = chunk;
-            resolve_chunk(chunk, planes, ntok, row_base);
+            for (int m = 0; m < NMAT; ++m) { ya[m][0] = ya[m][1] = yb[m][0] = yb[m][1] = 0.0f; }
+            for (uint32_t st = 0; st < nsteps; ++st) {
+                const uint32_t g_first = k_begin + st * kStep;
+                // prefetch the next step (of this tile, or the first step of this warp's next tile)
+                StepRegs<NMAT> nxt;
+                const bool last_step = st + 1 == nsteps;
+                const bool has_next = !last_step || ti + 1 < my_tiles;
+                if (has_next) load_step(nxt, last_step ? tile + ngroups : tile, last_step ? k_begin : g_first + kStep);
 #pragma unroll
-            for (int i = 0; i < kGPW; ++i) {
-                const bool gv = (uint32_t)i < ngw;
-                const uint16_t* rlo = nullptr;
-                const uint16_t* rhi = nullptr;
-                if (gv && (uint32_t)g < ntok) {
-                    const uint32_t r = DENSE || NMAT == 1 ? row_base + g : args.sorted_pairs[row_base + g].token;
-                    rlo = args.x + (size_t)r * args.x_stride;
-                }
-                if (gv && (uint32_t)(g + 8) < ntok) {
-                    const uint32_t r = DENSE || NMAT == 1 ? row_base + g + 8 : args.sorted_pairs[row_base + g + 8].token;
-                    rhi = args.x + (size_t)r * args.x_stride;
-                }
-                load_xfrag(xlo[i], rlo, g0 + i, t);
-                load_xfrag(xhi[i], rhi, g0 + i, t);
-            }
-        }
-
-        float y[NMAT][4];
+                for (int i = 0; i < kStep; ++i) {
+                    if (g_first + i < k_end) {          // warp-uniform
+                        const uint32_t G = g_first + i;
+                        uint4 xl = make_uint4(0u, 0u, 0u, 0u), xh = make_uint4(0u, 0u, 0u, 0u);
+                        float xs = 0.0f;
+                        if (tok_valid) {
+                            xl = lds128(xlo_addr + G * 512);
+                            xh = lds128(xhi_addr + G * 512);
+                            xs = lds_f32(xsum_addr + G * 32);
+                        }
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m) { y[m][0] = y[m][1] = y[m][2] = y[m][3] = 0.0f; }
-        const bool hi_tokens = ntok > 8;
-        const uint16_t* sb_stage = reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(sb) +
-                                                                     (size_t)stage * lay.sb_stage_bytes());
-#pragma unroll
-        for (int m = 0; m < NMAT; ++m) {
-            const uint16_t* sm_s = sb_stage + (size_t)(m * 2 + 0) * kTileRows * ng;
-            const uint16_t* sm_b = sb_stage + (size_t)(m * 2 + 1) * kTileRows * ng;
-#pragma unroll
-            for (int s = 0; s < kGPW / 2; ++s) {
-                if (2u * s >= ngw) break;
-                const uint4 v = ring[((((size_t)stage * warps + warp) * NMAT + m) * (kGPW / 2) + s) * kWarp + lane];
-                // quad exchange: lanes t<2 hold two pieces of the even group, t>=2 of the odd group
-                const bool low = t < 2;
-                const uint32_t sx = low ? v.z : v.x, sy = low ? v.w : v.y;
-                const uint32_t rx = __shfl_xor_sync(kFullMask, sx, 2), ry = __shfl_xor_sync(kFullMask, sy, 2);
-                const uint32_t e0 = low ? v.x : rx, e1 = low ? v.y : ry;      // even group piece
-                const uint32_t o0 = low ? rx : v.z, o1 = low ? ry : v.w;      // odd group piece
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const int gi = 2 * s + half;
-                    if ((uint32_t)gi >= ngw) break;
-                    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                    if (hi_tokens) group_mma<true>(c, half ? o0 : e0, half ? o1 : e1, xlo[gi], xhi[gi]);
-                    else group_mma<false>(c, half ? o0 : e0, half ? o1 : e1, xlo[gi], xhi[gi]);
-                    const uint32_t grp = g0 + gi;
-                    const float s0 = bf16_bits_to_float(sm_s[(2 * t) * ng + grp]) * kTwo24;
-                    const float s1 = bf16_bits_to_float(sm_s[(2 * t + 1) * ng + grp]) * kTwo24;
-                    const float b0 = bf16_bits_to_float(sm_b[(2 * t) * ng + grp]);
-                    const float b1 = bf16_bits_to_float(sm_b[(2 * t + 1) * ng + grp]);
-                    y[m][0] = fmaf(s0, c[0], y[m][0]); y[m][0] = fmaf(b0, xlo[gi].sum, y[m][0]);
-                    y[m][1] = fmaf(s1, c[1], y[m][1]); y[m][1] = fmaf(b1, xlo[gi].sum, y[m][1]);
-                    if (hi_tokens) {
-                        y[m][2] = fmaf(s0, c[2], y[m][2]); y[m][2] = fmaf(b0, xhi[gi].sum, y[m][2]);
-                        y[m][3] = fmaf(s1, c[3], y[m][3]); y[m][3] = fmaf(b1, xhi[gi].sum, y[m][3]);
+                        for (int m = 0; m < NMAT; ++m) {
+                            float c0, c1;
+                            group_mma(c0, c1, cur.w[m][i].x, cur.w[m][i].y, xl, xh);
+                            const uint32_t sv0 = i < 2 ? cur.s0[m].x : cur.s0[m].y, sv1 = i < 2 ? cur.s1[m].x : cur.s1[m].y;
+                            const uint32_t bv0 = i < 2 ? cur.b0[m].x : cur.b0[m].y, bv1 = i < 2 ? cur.b1[m].x : cur.b1[m].y;
+                            const float s0 = (i & 1) ? bf16_hi(sv0) : bf16_lo(sv0), s1 = (i & 1) ? bf16_hi(sv1) : bf16_lo(sv1);
+                            const float b0 = (i & 1) ? bf16_hi(bv0) : bf16_lo(bv0), b1 = (i & 1) ? bf16_hi(bv1) : bf16_lo(bv1);
+                            ya[m][0] = fmaf(s0, c0, ya[m][0]); yb[m][0] = fmaf(b0, xs, yb[m][0]);
+                            ya[m][1] = fmaf(s1, c1, ya[m][1]); yb[m][1] = fmaf(b1, xs, yb[m][1]);
+                        }
                     }
                 }
+                if (has_next) cur = nxt;
             }
-        }
-        // warp partials -> shared, index = token * 8 + row
+            float y[NMAT][2];
 #pragma unroll
-        for (int m = 0; m < NMAT; ++m) {
-            float* r = red + ((size_t)warp * NMAT + m) * 128;
-            r[g * 8 + 2 * t] = y[m][0];
-            r[g * 8 + 2 * t + 1] = y[m][1];
-            r[(g + 8) * 8 + 2 * t] = y[m][2];
-            r[(g + 8) * 8 + 2 * t + 1] = y[m][3];
-        }
-        __syncthreads();
-        for (uint32_t oi = threadIdx.x; oi < 128; oi += blockDim.x) {
-            const uint32_t tok = oi >> 3, row = oi & 7;
-            if (tok < ntok) {
-                float acc[NMAT];
+            for (int m = 0; m < NMAT; ++m) {
+                y[m][0] = fmaf(ya[m][0], kTwo24, yb[m][0]);
+                y[m][1] = fmaf(ya[m][1], kTwo24, yb[m][1]);
+            }
+            if (ks > 1) {
+                // partial sums of the group's warps, added in warp order by the group's first warp
+                float* rb = red + (size_t)(ti & 1) * (kStreamWarps * NMAT * 64);
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m) {
-                    float a = 0.0f;
-                    for (uint32_t w2 = 0; w2 < warps; ++w2) a += red[((size_t)w2 * NMAT + m) * 128 + oi];
-                    acc[m] = a;
+                for (int m = 0; m < NMAT; ++m)
+                    *reinterpret_cast<float2*>(rb + ((size_t)warp * NMAT + m) * 64 + g * 8 + 2 * t) = make_float2(y[m][0], y[m][1]);
+                named_barrier(1 + grp, ks * kWarp);
+                if (kw == 0) {
+#pragma unroll
+                    for (int m = 0; m < NMAT; ++m) {
+                        float2 acc = make_float2(0.0f, 0.0f);
+                        for (uint32_t w2 = 0; w2 < ks; ++w2) {
+                            const float2 v = *reinterpret_cast<const float2*>(rb + ((size_t)(warp + w2) * NMAT + m) * 64 + g * 8 + 2 * t);
+                            acc.x += v.x; acc.y += v.y;
+                        }
+                        y[m][0] = acc.x; y[m][1] = acc.y;
+                    }
                 }
-                const uint32_t out_row = tile * kTileRows + row;
+                // `red` is double buffered by tile parity: a buffer is rewritten two tiles later, after another
+                // pass through this barrier, which the reading warp reaches only once it has finished reading.
+            }
+            if (kw == 0 && tok_valid) {
+                const uint32_t out_row = tile * kTileRows + 2 * t;
                 if constexpr (OUT_MODE == kOutActs) {
-                    uint16_t* o = static_cast<uint16_t*>(args.out);
-                    float gt = acc[0], up = acc[NMAT - 1];
+                    float g0v = y[0][0], g1v = y[0][1], u0 = y[NMAT - 1][0], u1 = y[NMAT - 1][1];
                     if constexpr (DENSE) {
                         // shared expert: gate and up are stored as fp16 before the activation
                         // (Kernels/MoE/SharedExpertInt4.swift:62-93; Metal/Primitives/utility.metal:15-17)
-                        gt = __half2float(__float2half_rn(gt));
-                        up = __half2float(__float2half_rn(up));
+                        g0v = __half2float(__float2half_rn(g0v)); g1v = __half2float(__float2half_rn(g1v));
+                        u0 = __half2float(__float2half_rn(u0)); u1 = __half2float(__float2half_rn(u1));
                     }
                     // routed: act = half(gelu_tanh(gate) * up), gate and up in fp32 (prefill.metal:634-636; moe.metal:368)
-                    o[(size_t)(row_base + tok) * args.out_stride + out_row] = __half_as_ushort(__float2half_rn(gelu_tanh(gt) * up));
+                    const __half2 h = __floats2half2_rn(gelu_tanh(g0v) * u0, gelu_tanh(g1v) * u1);
+                    *reinterpret_cast<__half2*>(static_cast<uint16_t*>(args.out) + (size_t)(row_base + g) * args.out_stride + out_row) = h;
                 } else if constexpr (OUT_MODE == kOutDenseF16) {
-                    uint16_t* o = static_cast<uint16_t*>(args.out);
-                    o[(size_t)(row_base + tok) * args.out_stride + out_row] = __half_as_ushort(__float2half_rn(acc[0]));
+                    *reinterpret_cast<__half2*>(static_cast<uint16_t*>(args.out) + (size_t)(row_base + g) * args.out_stride + out_row) =
+                        __floats2half2_rn(y[0][0], y[0][1]);
                 } else {
-                    const tf_pair pr = args.sorted_pairs[row_base + tok];
+                    const tf_pair pr = args.sorted_pairs[row_base + g];
                     const size_t idx = ((size_t)pr.token * args.top_k + pr.rank) * args.out_stride + out_row;
-                    if constexpr (OUT_MODE == kOutPartialF16)
-                        static_cast<uint16_t*>(args.out)[idx] = __half_as_ushort(__float2half_rn(acc[0]));   // prefill.metal:666-669
+                    if constexpr (OUT_MODE == kOutPartialF16)      // prefill.metal:666-669
+                        *reinterpret_cast<__half2*>(static_cast<uint16_t*>(args.out) + idx) = __floats2half2_rn(y[0][0], y[0][1]);
                     else
-                        static_cast<float*>(args.out)[idx] = acc[0];
+                        *reinterpret_cast<float2*>(static_cast<float*>(args.out) + idx) = make_float2(y[0][0], y[0][1]);
                 }
             }
         }
-        // the next iteration's first barrier orders these reads before the next writes of `red`
+        item += seg_items;
     }
-    cp_async_wait<0>();
 }
 
 }  // namespace tf
@@ -502,34 +502,38 @@ __global__ void reduce_token_major_kernel(const void* __restrict__ partials, con
     out[(size_t)t * out_stride + d] = __half_as_ushort(__float2half_rn(acc));
 }
 
+// Picks the K split: enough warp-tiles to occupy every warp of every CTA a few times over.
+static uint32_t choose_ksplit(uint64_t expected_items, uint32_t sm_count, uint32_t ng) {
+    uint32_t ks = 1;
+    const uint32_t steps = (ng + kStep - 1) / kStep;
+    while (ks < (uint32_t)kMaxKSplit && ks * 2 <= steps && expected_items * ks < (uint64_t)sm_count * kStreamWarps * 3) ks *= 2;
+    return ks;
+}
+
 template <int NMAT, bool DENSE, int OUT_MODE>
-static tf_status launch_grouped(tf_context* ctx, void* stream, const GroupedArgs& args, const char* name) {
+static tf_status launch_grouped(tf_context* ctx, void* stream, GroupedArgs& args, uint64_t expected_chunks, const char* name) {
     const uint32_t ng = args.k / kGroup;
-    const uint32_t warps = (ng + kGPW - 1) / kGPW;
-    TF_REQUIRE(ctx, warps >= 1 && warps <= (uint32_t)kMaxGroupedWarps, TF_ERR_UNSUPPORTED,
-               "%s: K=%u outside the supported range (64..3072)", name, args.k);
+    TF_REQUIRE(ctx, ng >= 1 && args.k % kGroup == 0, TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);
     TF_REQUIRE(ctx, args.rows % kTileRows == 0, TF_ERR_UNSUPPORTED, "%s: row count %u must be a multiple of 8", name, args.rows);
-    const SmemLayout<NMAT> lay{warps, ng};
-    const size_t smem = lay.total();
-    auto kern = grouped_mma_kernel<NMAT, DENSE, OUT_MODE>;
-    // Attribute and occupancy are queried once per (instantiation, warp count) and cached,
-    // so steady-state calls are a bare launch (and safe inside stream capture).
-    static int cached_per_sm[kMaxGroupedWarps + 1] = {0};
-    int per_sm = cached_per_sm[warps];
-    if (per_sm == 0) {
+    const size_t smem = stream_smem_bytes(ng, NMAT);
+    TF_REQUIRE(ctx, smem <= 200 * 1024, TF_ERR_UNSUPPORTED, "%s: K=%u needs %zu bytes of shared memory (limit 200 KB)", name, args.k, smem);
+    auto kern = grouped_stream_kernel<NMAT, DENSE, OUT_MODE>;
+    // The attribute is set once per instantiation, so steady-state calls are a bare launch
+    // (and safe inside stream capture).
+    static bool configured = false;
+    if (!configured) {
         TF_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        TF_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, (int)(warps * kWarp), smem));
-        if (per_sm < 1) per_sm = 1;
-        if (per_sm > 8) per_sm = 8;
-        cached_per_sm[warps] = per_sm;
+        configured = true;
     }
-    uint32_t grid = (uint32_t)ctx->sm_count * (uint32_t)per_sm;
+    const uint64_t items = expected_chunks * (args.rows / kTileRows);
+    args.ks = choose_ksplit(items, (uint32_t)ctx->sm_count, ng);
+    uint32_t grid = (uint32_t)ctx->sm_count;
     if (DENSE) {
-        const uint64_t items = (uint64_t)((args.dense_tokens + kChunkTokens - 1) / kChunkTokens) * (args.rows / kTileRows);
         if (items == 0) return TF_OK;
-        if (items < grid) grid = (uint32_t)items;
+        const uint64_t want = (items * args.ks + kStreamWarps - 1) / kStreamWarps;
+        if (want < grid) grid = (uint32_t)want;
     }
-    kern<<<grid, warps * kWarp, smem, static_cast<cudaStream_t>(stream)>>>(args);
+    kern<<<grid, kStreamThreads, smem, static_cast<cudaStream_t>(stream)>>>(args);
     return check_launch(ctx, name);
 }
 
@@ -583,6 +587,10 @@ tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream, const void* hidd
     TF_REQUIRE(ctx, tf::aligned(hp, 16) && (hidden_stride_elements * 2) % 16 == 0 && tf::aligned(acts_scratch, 16),
                TF_ERR_ALIGNMENT, "%s: hidden rows and acts scratch must be 16-byte aligned", name);
     if (query_count == 0) return TF_OK;
+    // The chunk count lives on the device; the K split only needs its order of magnitude:
+    // every pair its own expert (at most num pairs, bounded by the pool) or 8 pairs per chunk.
+    const uint64_t pairs = (uint64_t)query_count * top_k;
+    const uint64_t expected_chunks = pairs < 1024 ? pairs : pairs / tf::kChunkTokens;
 
     tf::GroupedArgs a{};
     a.pool_base = static_cast<const uint8_t*>(pool_layer_base);
@@ -593,7 +601,7 @@ tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream, const void* hidd
     a.chunk_start = routes->chunk_start; a.counters = routes->counters;
     a.x = reinterpret_cast<const uint16_t*>(hp); a.x_stride = hidden_stride_elements;
     a.out = acts_scratch; a.out_stride = f; a.rows = f; a.k = d; a.top_k = top_k;
-    tf_status s = tf::launch_grouped<2, false, tf::kOutActs>(ctx, stream, a, "tf_grouped_moe_batched(gate/up)");
+    tf_status s = tf::launch_grouped<2, false, tf::kOutActs>(ctx, stream, a, expected_chunks, "tf_grouped_moe_batched(gate/up)");
     if (s) return s;
 
     tf::GroupedArgs b{};
@@ -603,8 +611,8 @@ tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream, const void* hidd
     b.chunk_start = routes->chunk_start; b.counters = routes->counters;
     b.x = static_cast<const uint16_t*>(acts_scratch); b.x_stride = f;
     b.out = route_partials; b.out_stride = d; b.rows = d; b.k = f; b.top_k = top_k;
-    if (partials_f32) return tf::launch_grouped<1, false, tf::kOutPartialF32>(ctx, stream, b, "tf_grouped_moe_batched(down)");
-    return tf::launch_grouped<1, false, tf::kOutPartialF16>(ctx, stream, b, "tf_grouped_moe_batched(down)");
+    if (partials_f32) return tf::launch_grouped<1, false, tf::kOutPartialF32>(ctx, stream, b, expected_chunks, "tf_grouped_moe_batched(down)");
+    return tf::launch_grouped<1, false, tf::kOutPartialF16>(ctx, stream, b, expected_chunks, "tf_grouped_moe_batched(down)");
 }
 
 tf_status tf_moe_reduce_token_major(tf_context* ctx, void* stream, const void* route_partials, int partials_f32,
@@ -659,13 +667,13 @@ tf_status tf_shared_expert_int4_block(tf_context* ctx, void* stream, const void*
     a.dense[0] = mp[0]; a.dense[1] = mp[1];
     a.x = reinterpret_cast<const uint16_t*>(xp); a.x_stride = x_stride_elements;
     a.out = scratch_act; a.out_stride = fs; a.rows = fs; a.k = d; a.dense_tokens = rows;
-    tf_status s = tf::launch_grouped<2, true, tf::kOutActs>(ctx, stream, a, "tf_shared_expert_int4_block(gate/up)");
+    tf_status s = tf::launch_grouped<2, true, tf::kOutActs>(ctx, stream, a, (rows + tf::kChunkTokens - 1) / tf::kChunkTokens, "tf_shared_expert_int4_block(gate/up)");
     if (s) return s;
     tf::GroupedArgs b{};
     b.dense[0] = mp[2];
     b.x = static_cast<const uint16_t*>(scratch_act); b.x_stride = fs;
     b.out = tf::byte_ptr(y, y_off); b.out_stride = y_stride_elements; b.rows = d; b.k = fs; b.dense_tokens = rows;
-    return tf::launch_grouped<1, true, tf::kOutDenseF16>(ctx, stream, b, "tf_shared_expert_int4_block(down)");
+    return tf::launch_grouped<1, true, tf::kOutDenseF16>(ctx, stream, b, (rows + tf::kChunkTokens - 1) / tf::kChunkTokens, "tf_shared_expert_int4_block(down)");
 }
 
 }  // extern "C"
