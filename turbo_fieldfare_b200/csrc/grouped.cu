@@ -10,14 +10,14 @@
 //   - the per-row shared-expert loop (Kernels/Prefill/MoE/PrefillSharedExpert.swift:11-59).
 //
 // Kernel design (memory-bound; HBM roofline): weights are the B operand of
-// mma.sync.m16n8k16 (8 weight rows per warp tile), up to 8 tokens are rows 0..7
-// of the A operand. A 4-bit code q placed in the low mantissa bits of an fp16 IS
+// mma.sync.m16n8k16 (8 weight rows per warp tile), up to 16 tokens are the A
+// operand. A 4-bit code q placed in the low mantissa bits of an fp16 IS
 // the subnormal q * 2^-24, so "dequantisation" is one AND per two codes and the
 // tensor core multiplies exact integers by fp16 activations with fp32
 // accumulation. Scale and bias are applied per 64-column group after the MMAs:
 //     y += (s * 2^24) * acc + b * sum_k x_k
 // i.e. the reference's group factoring (Metal/Quant/dequant_int4.metal:14-19).
-// The activations of a chunk (<= 8 tokens of one expert) are staged once per
+// The activations of a chunk (<= 16 tokens of one expert) are staged once per
 // CTA in shared memory, already permuted into MMA fragment order; every warp
 // then streams whole 8-row tiles on its own: packed codes and scale rows come
 // straight from global memory into registers, prefetched one step (4 groups)
@@ -34,9 +34,9 @@ namespace tf {
 
 constexpr int kGroupThreads = 256;
 constexpr int kGroupPerThread = 4;
-constexpr int kChunkTokens = 8;       // tokens per work chunk of the grouped kernels (rows 0..7 of the MMA's A operand)
+constexpr int kChunkTokens = 16;      // tokens per work chunk of the grouped kernels (the m of m16n8k16)
 
-// counters: [0] group count, [1] total chunks (sum over groups of ceil(count/8)), [2] pair count
+// counters: [0] group count, [1] total chunks (sum over groups of ceil(count/16)), [2] pair count
 __global__ void __launch_bounds__(kGroupThreads)
 group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __restrict__ weights,
                     uint32_t T, uint32_t K, uint32_t E,
@@ -167,19 +167,18 @@ struct GroupedArgs {
     uint32_t ks;               // warps that share one tile along K (1, 2, 4 or 8)
 };
 
-// rows 8..15 of A (a1, a3) are zero: a chunk holds at most 8 tokens, so only c0, c1 are used.
-// First MMA of a group: C is the constant zero, so no accumulator has to be cleared.
-__device__ __forceinline__ void mma16816_first(float& c0, float& c1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    float d2, d3;
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%9,%9,%9,%9};"
-                 : "=f"(c0), "=f"(c1), "=f"(d2), "=f"(d3)
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.0f));
+// D = A * B + C with C either the constant zero (first MMA of a group) or D itself. The four A
+// registers and the four accumulators are always real fragments (tokens g and g + 8), so the
+// operands need no marshalling moves.
+__device__ __forceinline__ void mma16816_first(float (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+                 : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1), "f"(0.0f));
 }
-__device__ __forceinline__ void mma16816_acc(float& c0, float& c1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    float d2, d3;
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%9,%9};"
-                 : "+f"(c0), "+f"(c1), "=f"(d2), "=f"(d3)
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1), "f"(0.0f));
+__device__ __forceinline__ void mma16816_acc(float (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
 }
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -201,44 +200,40 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ float lds_f32(uint32_t addr) {
-    float v;
-    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+__device__ __forceinline__ float2 lds_f32x2(uint32_t addr) {
+    float2 v;
+    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// Four MMAs of one 64-column group. (w0, w1) = this lane's 16 codes (bytes [8t, 8t+8) of the row's
-// group); xl, xh = the token's 16 activations at the same columns, already in operand order:
-//   xl = {(x0,x4), (x2,x6), (x1,x5)/16, (x3,x7)/16}, xh the same for x8..x15.
-// Odd columns are pre-scaled by 1/16 because their codes sit four mantissa bits higher.
-__device__ __forceinline__ void group_mma(float& c0, float& c1, uint32_t w0, uint32_t w1, const uint4& xl, const uint4& xh) {
-    const uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
-    mma16816_first(c0, c1, xl.x, xl.y, w0 & 0x000F000Fu, w0s & 0x000F000Fu);
-    mma16816_acc(c0, c1, xl.z, xl.w, w0 & 0x00F000F0u, w0s & 0x00F000F0u);
-    mma16816_acc(c0, c1, xh.x, xh.y, w1 & 0x000F000Fu, w1s & 0x000F000Fu);
-    mma16816_acc(c0, c1, xh.z, xh.w, w1 & 0x00F000F0u, w1s & 0x00F000F0u);
-}
-
 enum OutMode { kOutActs = 0, kOutPartialF16 = 1, kOutPartialF32 = 2, kOutDenseF16 = 3 };
 
-// Shared memory: xlo[ng][32] uint4 | xhi[ng][32] uint4 | xsum[ng][8] float | red[2][warps][NMAT][64] float
+// Shared memory:
+//   xq[ng][4][32] uint4    A fragments: entry (G, j, lane) = {a0, a1, a2, a3} of MMA j of group G for lane (g, t):
+//                          tokens g (a0, a2) and g + 8 (a1, a3), this lane's columns 64 G + 16 t + {..}
+//   xsum[ng][8] float2     fp32 sums of the 64 activations of group G for tokens g and g + 8
+//   red[2][warps][NMAT][128] float   K-split partials, double buffered
 __host__ __device__ inline size_t stream_smem_bytes(uint32_t ng, int nmat) {
-    return (size_t)ng * 32 * 16 * 2 + (size_t)ng * 8 * 4 + (size_t)2 * kStreamWarps * nmat * 64 * 4;
+    return (size_t)ng * 4 * 32 * 16 + (size_t)ng * 8 * 8 + (size_t)2 * kStreamWarps * nmat * 128 * 4;
 }
 
 // What one step (up to kStep groups of one 8-row tile) needs from global memory.
 template <int NMAT>
 struct StepRegs {
-    uint2 w[NMAT][kStep];          // this lane's 16 codes of each group (row g)
+    uint2 w[NMAT][kStep];          // this lane's 16 codes of each group (row g, bytes [8t, 8t+8) of the group)
     uint2 s0[NMAT], s1[NMAT];      // 4 consecutive bf16 scales of rows 2t and 2t+1
     uint2 b0[NMAT], b1[NMAT];      // and biases
 };
 
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
+// bf16 scale times 2^24 (the codes enter the MMA as q * 2^-24): add 24 to the exponent field.
+// A zero scale becomes 2^-103, whose product with the accumulator is far below fp32 resolution.
+__device__ __forceinline__ float bf16_lo_x2p24(uint32_t v) { return __uint_as_float((v << 16) + 0x0C000000u); }
+__device__ __forceinline__ float bf16_hi_x2p24(uint32_t v) { return __uint_as_float((v & 0xFFFF0000u) + 0x0C000000u); }
 
 template <int NMAT, bool DENSE, int OUT_MODE>
 __global__ void __launch_bounds__(kStreamThreads)
@@ -250,13 +245,11 @@ grouped_stream_kernel(const GroupedArgs args) {
     const uint32_t ks = args.ks;
     const uint32_t row_bytes = args.k / 2;
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t xlo_addr = smem_base + lane * 16;
-    const uint32_t xhi_addr = xlo_addr + ng * 512;
-    const uint32_t xsum_addr = smem_base + ng * 1024 + g * 4;
-    uint4* xlo = reinterpret_cast<uint4*>(smem);
-    uint4* xhi = xlo + ng * 32;
-    float* xsum = reinterpret_cast<float*>(smem + (size_t)ng * 1024);
-    float* red = xsum + ng * 8;
+    const uint32_t xq_addr = smem_base + lane * 16;                    // + G * 2048 + j * 512
+    const uint32_t xsum_addr = smem_base + ng * 2048 + g * 8;          // + G * 64
+    uint4* xq = reinterpret_cast<uint4*>(smem);
+    float2* xsum = reinterpret_cast<float2*>(smem + (size_t)ng * 2048);
+    float* red = reinterpret_cast<float*>(smem + (size_t)ng * 2048 + (size_t)ng * 64);
 
     const uint32_t tiles = args.rows / kTileRows;
     const uint32_t total_chunks = DENSE ? (args.dense_tokens + kChunkTokens - 1) / kChunkTokens : args.counters[1];
@@ -272,7 +265,9 @@ grouped_stream_kernel(const GroupedArgs args) {
     const uint32_t steps_per_warp = (steps_total + ks - 1) / ks;
     const uint32_t k_begin = kw * steps_per_warp * kStep < ng ? kw * steps_per_warp * kStep : ng;
     const uint32_t k_end = (kw + 1) * steps_per_warp * kStep < ng ? (kw + 1) * steps_per_warp * kStep : ng;
+    const uint32_t nsteps = k_end > k_begin ? (k_end - k_begin + kStep - 1) / kStep : 0;
     const bool sb_vec = (ng % 4) == 0;        // 4 consecutive bf16 of a scale row are 8-byte aligned
+    const uint32_t out_stride = args.out_stride, top_k = args.top_k;
 
     while (item < item_end) {
         // ---- segment: the items of this CTA that belong to one chunk ----
@@ -304,13 +299,15 @@ grouped_stream_kernel(const GroupedArgs args) {
         }
 
         __syncthreads();        // every warp is done with the previous chunk's fragments
-        // stage the chunk's activations as MMA fragments: entry (G, lane) holds token g = lane/4,
-        // columns 64 G + 16 t .. + 15 (t = lane%4)
-        for (uint32_t idx = threadIdx.x; idx < ng * 32; idx += blockDim.x) {
-            const uint32_t G = idx >> 5, ln = idx & 31, tg = ln >> 2, tt = ln & 3;
+        // Stage the chunk's activations as MMA A fragments. Work item (G, half, lane): token g + 8 * half,
+        // columns 64 G + 16 t .. + 15. The 16 values x0..x15 feed four MMAs:
+        //   j = 0: (x0,x4),(x2,x6)   j = 1: (x1,x5)/16,(x3,x7)/16   j = 2, 3: the same for x8..x15.
+        // Odd columns are pre-scaled by 1/16 because their codes sit four mantissa bits higher.
+        for (uint32_t idx = threadIdx.x; idx < ng * 64; idx += blockDim.x) {
+            const uint32_t G = idx >> 6, half = (idx >> 5) & 1, ln = idx & 31, tok = (ln >> 2) + 8 * half, tt = ln & 3;
             uint32_t r[8];
-            if (tg < ntok) {
-                const uint32_t rr = (DENSE || NMAT == 1) ? row_base + tg : args.sorted_pairs[row_base + tg].token;
+            if (tok < ntok) {
+                const uint32_t rr = (DENSE || NMAT == 1) ? row_base + tok : args.sorted_pairs[row_base + tok].token;
                 const uint4* p = reinterpret_cast<const uint4*>(args.x + (size_t)rr * args.x_stride + G * kGroup + tt * 16);
                 const uint4 lo = __ldg(p), hi = __ldg(p + 1);
                 r[0] = lo.x; r[1] = lo.y; r[2] = lo.z; r[3] = lo.w;
@@ -327,40 +324,53 @@ grouped_stream_kernel(const GroupedArgs args) {
             }
             sum += __shfl_xor_sync(kFullMask, sum, 1);
             sum += __shfl_xor_sync(kFullMask, sum, 2);
-            xlo[idx] = make_uint4(prmt(r[0], r[2], 0x5410), prmt(r[1], r[3], 0x5410),
-                                  hmul2_sixteenth(prmt(r[0], r[2], 0x7632)), hmul2_sixteenth(prmt(r[1], r[3], 0x7632)));
-            xhi[idx] = make_uint4(prmt(r[4], r[6], 0x5410), prmt(r[5], r[7], 0x5410),
-                                  hmul2_sixteenth(prmt(r[4], r[6], 0x7632)), hmul2_sixteenth(prmt(r[5], r[7], 0x7632)));
-            if (tt == 0) xsum[G * 8 + tg] = sum;
+            uint32_t* q = reinterpret_cast<uint32_t*>(xq + (size_t)G * 128 + ln) + half;     // a0/a1 slot; a2/a3 at +2
+            q[0 * 128 + 0] = prmt(r[0], r[2], 0x5410);                      q[0 * 128 + 2] = prmt(r[1], r[3], 0x5410);
+            q[1 * 128 + 0] = hmul2_sixteenth(prmt(r[0], r[2], 0x7632));     q[1 * 128 + 2] = hmul2_sixteenth(prmt(r[1], r[3], 0x7632));
+            q[2 * 128 + 0] = prmt(r[4], r[6], 0x5410);                      q[2 * 128 + 2] = prmt(r[5], r[7], 0x5410);
+            q[3 * 128 + 0] = hmul2_sixteenth(prmt(r[4], r[6], 0x7632));     q[3 * 128 + 2] = hmul2_sixteenth(prmt(r[5], r[7], 0x7632));
+            if (tt == 0) reinterpret_cast<float*>(xsum + G * 8 + (ln >> 2))[half] = sum;
         }
         __syncthreads();
 
         // ---- this warp group's tiles of the segment: tile_begin + grp, + ngroups, ... ----
-        const bool tok_valid = (uint32_t)g < ntok;
         const uint32_t my_tiles = grp < seg_items ? (seg_items - grp + ngroups - 1) / ngroups : 0;
-        const uint32_t nsteps = k_end > k_begin ? (k_end - k_begin + kStep - 1) / kStep : 0;
+        const uint32_t total_steps = my_tiles * nsteps;
 
-        auto load_step = [&](StepRegs<NMAT>& sr, uint32_t tile, uint32_t g_first) {
+        // lane pointers at (first tile, k_begin); a step advances them by kStep groups, a tile change rewinds K
+        const uint8_t* wp[NMAT];
+        const uint16_t* sp[NMAT];
+        const uint16_t* bp[NMAT];
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) {
+            const uint32_t tile0 = tile_begin + grp;
+            wp[m] = pl[m].W + (size_t)(tile0 * kTileRows + g) * row_bytes + k_begin * 32 + t * 8;
+            sp[m] = pl[m].S + (size_t)(tile0 * kTileRows + 2 * t) * ng + k_begin;
+            bp[m] = pl[m].B + (size_t)(tile0 * kTileRows + 2 * t) * ng + k_begin;
+        }
+        const uint32_t w_tile_jump = ngroups * kTileRows * row_bytes - (nsteps - 1) * kStep * 32;   // last step -> next tile's first
+        const uint32_t sb_tile_jump = ngroups * kTileRows * ng - (nsteps - 1) * kStep;
+        uint32_t load_st = 0;       // step index (within the tile) of the next load
+
+        auto load_step = [&](StepRegs<NMAT>& sr) {
+            const uint32_t g_first = k_begin + load_st * kStep;
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
-                const uint8_t* wrow = pl[m].W + (size_t)(tile * kTileRows + g) * row_bytes + g_first * 32 + t * 8;
 #pragma unroll
                 for (int i = 0; i < kStep; ++i)
-                    sr.w[m][i] = (g_first + i < k_end) ? ldg_nc_u2(wrow + i * 32) : make_uint2(0u, 0u);
-                const uint16_t* s_r0 = pl[m].S + (size_t)(tile * kTileRows + 2 * t) * ng + g_first;
-                const uint16_t* b_r0 = pl[m].B + (size_t)(tile * kTileRows + 2 * t) * ng + g_first;
+                    sr.w[m][i] = (g_first + i < k_end) ? ldg_nc_u2(wp[m] + i * 32) : make_uint2(0u, 0u);
                 if (sb_vec) {
-                    sr.s0[m] = __ldg(reinterpret_cast<const uint2*>(s_r0));
-                    sr.s1[m] = __ldg(reinterpret_cast<const uint2*>(s_r0 + ng));
-                    sr.b0[m] = __ldg(reinterpret_cast<const uint2*>(b_r0));
-                    sr.b1[m] = __ldg(reinterpret_cast<const uint2*>(b_r0 + ng));
+                    sr.s0[m] = __ldg(reinterpret_cast<const uint2*>(sp[m]));
+                    sr.s1[m] = __ldg(reinterpret_cast<const uint2*>(sp[m] + ng));
+                    sr.b0[m] = __ldg(reinterpret_cast<const uint2*>(bp[m]));
+                    sr.b1[m] = __ldg(reinterpret_cast<const uint2*>(bp[m] + ng));
                 } else {
                     uint32_t v[4][4];
 #pragma unroll
                     for (int i = 0; i < kStep; ++i) {
                         const bool ok = g_first + i < k_end;
-                        v[0][i] = ok ? s_r0[i] : 0u; v[1][i] = ok ? s_r0[ng + i] : 0u;
-                        v[2][i] = ok ? b_r0[i] : 0u; v[3][i] = ok ? b_r0[ng + i] : 0u;
+                        v[0][i] = ok ? sp[m][i] : 0u; v[1][i] = ok ? sp[m][ng + i] : 0u;
+                        v[2][i] = ok ? bp[m][i] : 0u; v[3][i] = ok ? bp[m][ng + i] : 0u;
                     }
                     sr.s0[m] = make_uint2(v[0][0] | (v[0][1] << 16), v[0][2] | (v[0][3] << 16));
                     sr.s1[m] = make_uint2(v[1][0] | (v[1][1] << 16), v[1][2] | (v[1][3] << 16));
@@ -368,100 +378,152 @@ grouped_stream_kernel(const GroupedArgs args) {
                     sr.b1[m] = make_uint2(v[3][0] | (v[3][1] << 16), v[3][2] | (v[3][3] << 16));
                 }
             }
+            if (++load_st == nsteps) {
+                load_st = 0;
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m) { wp[m] += w_tile_jump; sp[m] += sb_tile_jump; bp[m] += sb_tile_jump; }
+            } else {
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m) { wp[m] += kStep * 32; sp[m] += kStep; bp[m] += kStep; }
+            }
         };
 
-        StepRegs<NMAT> cur;
-        if (my_tiles > 0 && nsteps > 0) load_step(cur, tile_begin + grp, k_begin);
-        for (uint32_t ti = 0; ti < my_tiles; ++ti) {
-            const uint32_t tile = tile_begin + grp + ti * ngroups;
-            float ya[NMAT][2], yb[NMAT][2];
+        float ya[NMAT][4];
 #pragma unroll
-            for (int m = 0; m < NMAT; ++m) { ya[m][0] = ya[m][1] = yb[m][0] = yb[m][1] = 0.0f; }
-            for (uint32_t st = 0; st < nsteps; ++st) {
-                const uint32_t g_first = k_begin + st * kStep;
-                // prefetch the next step (of this tile, or the first step of this warp's next tile)
-                StepRegs<NMAT> nxt;
-                const bool last_step = st + 1 == nsteps;
-                const bool has_next = !last_step || ti + 1 < my_tiles;
-                if (has_next) load_step(nxt, last_step ? tile + ngroups : tile, last_step ? k_begin : g_first + kStep);
+        for (int m = 0; m < NMAT; ++m) {
 #pragma unroll
-                for (int i = 0; i < kStep; ++i) {
-                    if (g_first + i < k_end) {          // warp-uniform
-                        const uint32_t G = g_first + i;
-                        uint4 xl = make_uint4(0u, 0u, 0u, 0u), xh = make_uint4(0u, 0u, 0u, 0u);
-                        float xs = 0.0f;
-                        if (tok_valid) {
-                            xl = lds128(xlo_addr + G * 512);
-                            xh = lds128(xhi_addr + G * 512);
-                            xs = lds_f32(xsum_addr + G * 32);
-                        }
+            for (int j = 0; j < 4; ++j) ya[m][j] = 0.0f;
+        }
+        uint32_t comp_st = 0, comp_tile = tile_begin + grp, comp_ti = 0;
+
+        auto compute_step = [&](const StepRegs<NMAT>& sr) {
+            const uint32_t g_first = k_begin + comp_st * kStep;
 #pragma unroll
-                        for (int m = 0; m < NMAT; ++m) {
-                            float c0, c1;
-                            group_mma(c0, c1, cur.w[m][i].x, cur.w[m][i].y, xl, xh);
-                            const uint32_t sv0 = i < 2 ? cur.s0[m].x : cur.s0[m].y, sv1 = i < 2 ? cur.s1[m].x : cur.s1[m].y;
-                            const uint32_t bv0 = i < 2 ? cur.b0[m].x : cur.b0[m].y, bv1 = i < 2 ? cur.b1[m].x : cur.b1[m].y;
-                            const float s0 = (i & 1) ? bf16_hi(sv0) : bf16_lo(sv0), s1 = (i & 1) ? bf16_hi(sv1) : bf16_lo(sv1);
-                            const float b0 = (i & 1) ? bf16_hi(bv0) : bf16_lo(bv0), b1 = (i & 1) ? bf16_hi(bv1) : bf16_lo(bv1);
-                            ya[m][0] = fmaf(s0, c0, ya[m][0]); yb[m][0] = fmaf(b0, xs, yb[m][0]);
-                            ya[m][1] = fmaf(s1, c1, ya[m][1]); yb[m][1] = fmaf(b1, xs, yb[m][1]);
-                        }
+            for (int i = 0; i < kStep; ++i) {
+                if (g_first + i < k_end) {          // warp-uniform
+                    const uint32_t G = g_first + i;
+                    const uint4 a0 = lds128(xq_addr + G * 2048), a1 = lds128(xq_addr + G * 2048 + 512);
+                    const uint4 a2 = lds128(xq_addr + G * 2048 + 1024), a3 = lds128(xq_addr + G * 2048 + 1536);
+                    const float2 xs = lds_f32x2(xsum_addr + G * 64);
+#pragma unroll
+                    for (int m = 0; m < NMAT; ++m) {
+                        const uint32_t w0 = sr.w[m][i].x, w1 = sr.w[m][i].y, w0s = w0 >> 8, w1s = w1 >> 8;
+                        float c[4];
+                        mma16816_first(c, a0, w0 & 0x000F000Fu, w0s & 0x000F000Fu);
+                        mma16816_acc(c, a1, w0 & 0x00F000F0u, w0s & 0x00F000F0u);
+                        mma16816_acc(c, a2, w1 & 0x000F000Fu, w1s & 0x000F000Fu);
+                        mma16816_acc(c, a3, w1 & 0x00F000F0u, w1s & 0x00F000F0u);
+                        const uint32_t sv0 = i < 2 ? sr.s0[m].x : sr.s0[m].y, sv1 = i < 2 ? sr.s1[m].x : sr.s1[m].y;
+                        const uint32_t bv0 = i < 2 ? sr.b0[m].x : sr.b0[m].y, bv1 = i < 2 ? sr.b1[m].x : sr.b1[m].y;
+                        const float s0 = (i & 1) ? bf16_hi_x2p24(sv0) : bf16_lo_x2p24(sv0);
+                        const float s1 = (i & 1) ? bf16_hi_x2p24(sv1) : bf16_lo_x2p24(sv1);
+                        const float b0 = (i & 1) ? bf16_hi(bv0) : bf16_lo(bv0), b1 = (i & 1) ? bf16_hi(bv1) : bf16_lo(bv1);
+                        // c0, c1: token g, rows 2t, 2t+1; c2, c3: token g + 8
+                        ya[m][0] = fmaf(s0, c[0], fmaf(b0, xs.x, ya[m][0]));
+                        ya[m][1] = fmaf(s1, c[1], fmaf(b1, xs.x, ya[m][1]));
+                        ya[m][2] = fmaf(s0, c[2], fmaf(b0, xs.y, ya[m][2]));
+                        ya[m][3] = fmaf(s1, c[3], fmaf(b1, xs.y, ya[m][3]));
                     }
                 }
-                if (has_next) cur = nxt;
             }
-            float y[NMAT][2];
+            if (++comp_st < nsteps) return;
+            // ---- last step of the tile: combine, reduce over the K split, store ----
+            comp_st = 0;
+            float y[NMAT][4];
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
-                y[m][0] = fmaf(ya[m][0], kTwo24, yb[m][0]);
-                y[m][1] = fmaf(ya[m][1], kTwo24, yb[m][1]);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    y[m][j] = ya[m][j];
+                    ya[m][j] = 0.0f;
+                }
             }
             if (ks > 1) {
                 // partial sums of the group's warps, added in warp order by the group's first warp
-                float* rb = red + (size_t)(ti & 1) * (kStreamWarps * NMAT * 64);
+                float* rb = red + (size_t)(comp_ti & 1) * (kStreamWarps * NMAT * 128);
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m)
-                    *reinterpret_cast<float2*>(rb + ((size_t)warp * NMAT + m) * 64 + g * 8 + 2 * t) = make_float2(y[m][0], y[m][1]);
+                for (int m = 0; m < NMAT; ++m) {
+                    float* r = rb + ((size_t)warp * NMAT + m) * 128;
+                    *reinterpret_cast<float2*>(r + g * 8 + 2 * t) = make_float2(y[m][0], y[m][1]);
+                    *reinterpret_cast<float2*>(r + (g + 8) * 8 + 2 * t) = make_float2(y[m][2], y[m][3]);
+                }
                 named_barrier(1 + grp, ks * kWarp);
                 if (kw == 0) {
 #pragma unroll
                     for (int m = 0; m < NMAT; ++m) {
-                        float2 acc = make_float2(0.0f, 0.0f);
+                        float2 lo = make_float2(0.0f, 0.0f), hi = make_float2(0.0f, 0.0f);
                         for (uint32_t w2 = 0; w2 < ks; ++w2) {
-                            const float2 v = *reinterpret_cast<const float2*>(rb + ((size_t)(warp + w2) * NMAT + m) * 64 + g * 8 + 2 * t);
-                            acc.x += v.x; acc.y += v.y;
+                            const float* r = rb + ((size_t)(warp + w2) * NMAT + m) * 128;
+                            const float2 v0 = *reinterpret_cast<const float2*>(r + g * 8 + 2 * t);
+                            const float2 v1 = *reinterpret_cast<const float2*>(r + (g + 8) * 8 + 2 * t);
+                            lo.x += v0.x; lo.y += v0.y; hi.x += v1.x; hi.y += v1.y;
                         }
-                        y[m][0] = acc.x; y[m][1] = acc.y;
+                        y[m][0] = lo.x; y[m][1] = lo.y; y[m][2] = hi.x; y[m][3] = hi.y;
                     }
                 }
                 // `red` is double buffered by tile parity: a buffer is rewritten two tiles later, after another
                 // pass through this barrier, which the reading warp reaches only once it has finished reading.
             }
-            if (kw == 0 && tok_valid) {
-                const uint32_t out_row = tile * kTileRows + 2 * t;
-                if constexpr (OUT_MODE == kOutActs) {
-                    float g0v = y[0][0], g1v = y[0][1], u0 = y[NMAT - 1][0], u1 = y[NMAT - 1][1];
-                    if constexpr (DENSE) {
-                        // shared expert: gate and up are stored as fp16 before the activation
-                        // (Kernels/MoE/SharedExpertInt4.swift:62-93; Metal/Primitives/utility.metal:15-17)
-                        g0v = __half2float(__float2half_rn(g0v)); g1v = __half2float(__float2half_rn(g1v));
-                        u0 = __half2float(__float2half_rn(u0)); u1 = __half2float(__float2half_rn(u1));
+            if (kw == 0) {
+                const uint32_t out_row = comp_tile * kTileRows + 2 * t;
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const uint32_t tok = g + 8 * hh;
+                    if (tok < ntok) {
+                        const float v0 = y[0][2 * hh], v1 = y[0][2 * hh + 1];
+                        if constexpr (OUT_MODE == kOutActs) {
+                            float g0v = v0, g1v = v1, u0 = y[NMAT - 1][2 * hh], u1 = y[NMAT - 1][2 * hh + 1];
+                            if constexpr (DENSE) {
+                                // shared expert: gate and up are stored as fp16 before the activation
+                                // (Kernels/MoE/SharedExpertInt4.swift:62-93; Metal/Primitives/utility.metal:15-17)
+                                g0v = __half2float(__float2half_rn(g0v)); g1v = __half2float(__float2half_rn(g1v));
+                                u0 = __half2float(__float2half_rn(u0)); u1 = __half2float(__float2half_rn(u1));
+                            }
+                            // routed: act = half(gelu_tanh(gate) * up), gate and up in fp32 (prefill.metal:634-636; moe.metal:368)
+                            *reinterpret_cast<__half2*>(static_cast<uint16_t*>(args.out) + (size_t)(row_base + tok) * out_stride + out_row) =
+                                __floats2half2_rn(gelu_tanh(g0v) * u0, gelu_tanh(g1v) * u1);
+                        } else if constexpr (OUT_MODE == kOutDenseF16) {
+                            *reinterpret_cast<__half2*>(static_cast<uint16_t*>(args.out) + (size_t)(row_base + tok) * out_stride + out_row) =
+                                __floats2half2_rn(v0, v1);
+                        } else {
+                            const tf_pair pr = args.sorted_pairs[row_base + tok];
+                            const size_t idx = ((size_t)pr.token * top_k + pr.rank) * out_stride + out_row;
+                            if constexpr (OUT_MODE == kOutPartialF16)      // prefill.metal:666-669
+                                *reinterpret_cast<__half2*>(static_cast<uint16_t*>(args.out) + idx) = __floats2half2_rn(v0, v1);
+                            else
+                                *reinterpret_cast<float2*>(static_cast<float*>(args.out) + idx) = make_float2(v0, v1);
+                        }
                     }
-                    // routed: act = half(gelu_tanh(gate) * up), gate and up in fp32 (prefill.metal:634-636; moe.metal:368)
-                    const __half2 h = __floats2half2_rn(gelu_tanh(g0v) * u0, gelu_tanh(g1v) * u1);
-                    *reinterpret_cast<__half2*>(static_cast<uint16_t*>(args.out) + (size_t)(row_base + g) * args.out_stride + out_row) = h;
-                } else if constexpr (OUT_MODE == kOutDenseF16) {
-                    *reinterpret_cast<__half2*>(static_cast<uint16_t*>(args.out) + (size_t)(row_base + g) * args.out_stride + out_row) =
-                        __floats2half2_rn(y[0][0], y[0][1]);
-                } else {
-                    const tf_pair pr = args.sorted_pairs[row_base + g];
-                    const size_t idx = ((size_t)pr.token * args.top_k + pr.rank) * args.out_stride + out_row;
-                    if constexpr (OUT_MODE == kOutPartialF16)      // prefill.metal:666-669
-                        *reinterpret_cast<__half2*>(static_cast<uint16_t*>(args.out) + idx) = __floats2half2_rn(y[0][0], y[0][1]);
-                    else
-                        *reinterpret_cast<float2*>(static_cast<float*>(args.out) + idx) = make_float2(y[0][0], y[0][1]);
                 }
             }
+            comp_tile += ngroups;
+            ++comp_ti;
+        };
+
+        if (ks > 1 && nsteps == 0) {
+            // a warp of a K-split group whose K range is empty still has to meet its group at every tile
+            for (uint32_t ti = 0; ti < my_tiles; ++ti) {
+                float* rb = red + (size_t)(ti & 1) * (kStreamWarps * NMAT * 128);
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m) {
+                    float* r = rb + ((size_t)warp * NMAT + m) * 128;
+                    *reinterpret_cast<float2*>(r + g * 8 + 2 * t) = make_float2(0.0f, 0.0f);
+                    *reinterpret_cast<float2*>(r + (g + 8) * 8 + 2 * t) = make_float2(0.0f, 0.0f);
+                }
+                named_barrier(1 + grp, ks * kWarp);
+            }
+        } else if (total_steps > 0) {
+            // ping-pong register prefetch: while one step's registers are consumed the next step's loads are in flight
+            StepRegs<NMAT> ra, rb2;
+            load_step(ra);
+            uint32_t gs = 0;
+            for (; gs + 2 <= total_steps; gs += 2) {
+                load_step(rb2);
+                compute_step(ra);
+                if (gs + 2 < total_steps) load_step(ra);
+                compute_step(rb2);
+            }
+            if (gs < total_steps) compute_step(ra);
         }
         item += seg_items;
     }
