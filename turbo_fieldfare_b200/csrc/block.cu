@@ -79,33 +79,68 @@ __global__ void fill_affine_kernel(uint8_t* W, uint16_t* S, uint16_t* B, uint64_
     B[gid] = __bfloat16_as_ushort(__float2bfloat16_rn(bias));
 }
 
-// h += y (fp16, one rounding), then x = half(rmsnorm(h) * w). One block per row.
-__global__ void __launch_bounds__(256)
+// h += y (fp16, one rounding), then x = half(rmsnorm(h) * w). One block per row; each thread keeps
+// its 8-element slices in registers (128-bit loads and stores), so the row is read once.
+constexpr int kRrnThreads = 128;
+constexpr int kRrnMaxSlices = 4;          // d <= 128 * 8 * 4 = 4096
+__global__ void __launch_bounds__(kRrnThreads)
 residual_rmsnorm_kernel(uint16_t* __restrict__ h, const uint16_t* __restrict__ y, const uint16_t* __restrict__ w,
                         uint16_t* __restrict__ x, uint32_t d, float eps) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    float* hv = reinterpret_cast<float*>(smem);
-    __shared__ float red[8];
+    __shared__ float red[kRrnThreads / kWarp];
     uint16_t* hr = h + (size_t)blockIdx.x * d;
+    const uint32_t vecs = d / 8;
+    float v[kRrnMaxSlices][8];
     float acc = 0.0f;
-    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
-        float v = f16_bits_to_float(hr[i]);
-        if (y) {
-            v = __half2float(__float2half_rn(v + f16_bits_to_float(y[(size_t)blockIdx.x * d + i])));
-            hr[i] = __half_as_ushort(__float2half_rn(v));
+#pragma unroll
+    for (int s = 0; s < kRrnMaxSlices; ++s) {
+        const uint32_t i = threadIdx.x + s * kRrnThreads;
+        if (i < vecs) {
+            const uint4 hv = *reinterpret_cast<const uint4*>(hr + i * 8);
+            const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+            uint32_t yw[4] = {0u, 0u, 0u, 0u};
+            if (y) {
+                const uint4 yv = __ldg(reinterpret_cast<const uint4*>(y + (size_t)blockIdx.x * d + i * 8));
+                yw[0] = yv.x; yw[1] = yv.y; yw[2] = yv.z; yw[3] = yv.w;
+            }
+            uint32_t ow[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 a = __half22float2(*reinterpret_cast<const __half2*>(&hw[j]));
+                if (y) {
+                    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&yw[j]));
+                    const __half2 r = __floats2half2_rn(a.x + b.x, a.y + b.y);
+                    ow[j] = *reinterpret_cast<const uint32_t*>(&r);
+                    a = __half22float2(r);
+                }
+                v[s][2 * j] = a.x; v[s][2 * j + 1] = a.y;
+                acc = fmaf(a.x, a.x, acc); acc = fmaf(a.y, a.y, acc);
+            }
+            if (y) *reinterpret_cast<uint4*>(hr + i * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
         }
-        hv[i] = v;
-        acc = fmaf(v, v, acc);
     }
     acc = warp_sum(acc);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = acc;
     __syncthreads();
-    float tot = (threadIdx.x & 31) < 8 ? red[threadIdx.x & 31] : 0.0f;
+    float tot = (threadIdx.x & 31) < (kRrnThreads / kWarp) ? red[threadIdx.x & 31] : 0.0f;
     tot = warp_sum(tot);
+    if (!x) return;
     const float inv = rsqrtf(tot / (float)d + eps);
-    if (x)
-        for (uint32_t i = threadIdx.x; i < d; i += blockDim.x)
-            x[(size_t)blockIdx.x * d + i] = __half_as_ushort(__float2half_rn(hv[i] * inv * bf16_bits_to_float(w[i])));
+#pragma unroll
+    for (int s = 0; s < kRrnMaxSlices; ++s) {
+        const uint32_t i = threadIdx.x + s * kRrnThreads;
+        if (i < vecs) {
+            const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w + i * 8));
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+            uint32_t ow[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const __half2 r = __floats2half2_rn(v[s][2 * j] * inv * bf16_bits_to_float((uint16_t)(ww[j] & 0xFFFFu)),
+                                                    v[s][2 * j + 1] * inv * bf16_bits_to_float((uint16_t)(ww[j] >> 16)));
+                ow[j] = *reinterpret_cast<const uint32_t*>(&r);
+            }
+            *reinterpret_cast<uint4*>(x + (size_t)blockIdx.x * d + i * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+        }
+    }
 }
 
 }  // namespace tf
@@ -329,18 +364,20 @@ tf_status tf_stack_forward(tf_stack* st, void* stream, void* hidden, uint32_t to
     TF_REQUIRE(ctx, tokens <= ws->max_tokens, TF_ERR_SCRATCH_TOO_SMALL, "%s: %u tokens exceed the workspace (%u)", name, tokens, ws->max_tokens);
     if (tokens == 0) return TF_OK;
     const uint32_t d = ws->d;
-    const size_t smem = (size_t)d * sizeof(float);
-    TF_REQUIRE(ctx, smem <= 48 * 1024, TF_ERR_UNSUPPORTED, "%s: D too large", name);
+    const size_t smem = 0;
+    TF_REQUIRE(ctx, d % 8 == 0 && d <= 8u * tf::kRrnThreads * tf::kRrnMaxSlices, TF_ERR_UNSUPPORTED,
+               "%s: D must be a multiple of 8 and at most %d", name, 8 * tf::kRrnThreads * tf::kRrnMaxSlices);
+    TF_REQUIRE(ctx, tf::aligned(hidden, 16), TF_ERR_ALIGNMENT, "%s: hidden must be 16-byte aligned", name);
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     uint16_t* h = static_cast<uint16_t*>(hidden);
     for (size_t l = 0; l < st->layers.size(); ++l) {
-        tf::residual_rmsnorm_kernel<<<tokens, 256, smem, cs>>>(h, l == 0 ? nullptr : ws->y_block,
+        tf::residual_rmsnorm_kernel<<<tokens, tf::kRrnThreads, smem, cs>>>(h, l == 0 ? nullptr : ws->y_block,
                                                               static_cast<const uint16_t*>(st->norm_weights[l]),
                                                               ws->x_norm, d, st->eps);
         if (tf_status s = tf::check_launch(ctx, "residual_rmsnorm")) return s;
         if (tf_status s = tf_moe_block_forward(ctx, stream, &st->layers[l], ws->x_norm, d, ws->y_block, d, tokens, ws)) return s;
     }
-    tf::residual_rmsnorm_kernel<<<tokens, 256, smem, cs>>>(h, ws->y_block, nullptr, nullptr, d, st->eps);
+    tf::residual_rmsnorm_kernel<<<tokens, tf::kRrnThreads, smem, cs>>>(h, ws->y_block, nullptr, nullptr, d, st->eps);
     return tf::check_launch(ctx, "residual_add");
 }
 

@@ -205,6 +205,7 @@ __device__ __forceinline__ float2 lds_f32x2(uint32_t addr) {
     asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
     return v;
 }
+__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -352,8 +353,35 @@ grouped_stream_kernel(const GroupedArgs args) {
         const uint32_t sb_tile_jump = ngroups * kTileRows * ng - (nsteps - 1) * kStep;
         uint32_t load_st = 0;       // step index (within the tile) of the next load
 
+        // L2 prefetch of one whole tile (this warp's K range of the 8 rows, and the scale rows): issued
+        // one tile ahead so that DRAM latency is paid long before the register loads need the data.
+        const uint32_t pf_line0 = (k_begin * 32) / 128, pf_line1 = (k_end * 32 + 127) / 128;
+        const uint32_t pf_lines = (pf_line1 - pf_line0) * kTileRows;
+        const uint32_t sb_lines = (kTileRows * ng * 2 + 127) / 128;
+        uint32_t load_tile = tile_begin + grp;
+        auto prefetch_tile = [&](uint32_t tile) {
+            if (tile >= tile_begin + seg_items) return;
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+                const uint8_t* wt = pl[m].W + (size_t)tile * kTileRows * row_bytes;
+                for (uint32_t l = lane; l < pf_lines; l += kWarp) {
+                    const uint32_t r = l / (pf_line1 - pf_line0), c = pf_line0 + l % (pf_line1 - pf_line0);
+                    prefetch_l2(wt + (size_t)r * row_bytes + c * 128);
+                }
+                if (kw == 0 && lane < sb_lines) {
+                    prefetch_l2(reinterpret_cast<const uint8_t*>(pl[m].S + (size_t)tile * kTileRows * ng) + lane * 128);
+                    prefetch_l2(reinterpret_cast<const uint8_t*>(pl[m].B + (size_t)tile * kTileRows * ng) + lane * 128);
+                }
+            }
+        };
+        if (my_tiles > 0 && nsteps > 0) prefetch_tile(load_tile);
+
         auto load_step = [&](StepRegs<NMAT>& sr) {
             const uint32_t g_first = k_begin + load_st * kStep;
+            if (load_st == 0) {
+                prefetch_tile(load_tile + ngroups);
+                load_tile += ngroups;
+            }
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
 #pragma unroll

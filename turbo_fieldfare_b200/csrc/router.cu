@@ -91,8 +91,30 @@ __device__ __forceinline__ void warp_select_topk(float* scores /*shared, clobber
     }
 }
 
-// Few rows (decode): grid (rows, experts/4); the last block to finish a row
-// (self-resetting ticket) runs the selection, so one launch does everything.
+// Canonical logit of one expert row whose bytes, scales and biases sit in shared memory
+// (same arithmetic and order as router_row_logit; only the operand source differs).
+__device__ __forceinline__ float router_row_logit_smem(const uint8_t* Wrow, const uint16_t* s_row, const uint16_t* b_row,
+                                                       const float* xf, uint32_t groups, int lane) {
+    float acc = 0.0f;
+#pragma unroll 4
+    for (uint32_t g = 0; g < groups; ++g) {
+        const uint32_t i0 = g * kGroup + lane * 2;
+        const uint32_t w = *reinterpret_cast<const uint16_t*>(Wrow + i0);
+        const float q0 = (float)(w & 0xFFu), q1 = (float)(w >> 8);
+        const float2 xv = *reinterpret_cast<const float2*>(xf + i0);
+        const float s = bf16_bits_to_float(s_row[g]);
+        const float b = bf16_bits_to_float(b_row[g]);
+        const float p = __fmaf_rn(q1, xv.y, __fmul_rn(q0, xv.x));
+        acc = __fmaf_rn(s, p, acc);
+        acc = __fmaf_rn(b, __fadd_rn(xv.x, xv.y), acc);
+    }
+    return warp_sum(acc);
+}
+
+// Few rows (decode): grid (rows, experts/4); the block first copies its four expert rows into
+// shared memory with coalesced loads (the per-lane access pattern of the canonical order would
+// otherwise be a chain of 2-byte global loads); the last block to finish a row (self-resetting
+// ticket) runs the selection, so one launch does everything.
 template <bool X_BF16>
 __global__ void __launch_bounds__(kSplitThreads)
 router_split_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, const uint16_t* __restrict__ B,
@@ -103,25 +125,46 @@ router_split_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
                     float* scratch_logits, unsigned int* tickets,
                     uint32_t num_experts, uint32_t d, uint32_t top_k, bool a2) {
     extern __shared__ __align__(16) uint8_t smem[];
-    float* xf = reinterpret_cast<float*>(smem);
+    float* xf = reinterpret_cast<float*>(smem);                                   // [d]
+    uint8_t* wrows = smem + (size_t)d * 4;                                        // [4][d]
+    const uint32_t groups = d / kGroup;
+    uint16_t* srows = reinterpret_cast<uint16_t*>(wrows + (size_t)kSplitExpertsPerBlock * d);   // [4][groups]
+    uint16_t* brows = srows + kSplitExpertsPerBlock * groups;
     __shared__ float scores[TF_MAX_ROUTER_EXPERTS];
     __shared__ bool is_last;
     const uint32_t row = blockIdx.x;
-    stage_router_x<X_BF16>(hidden + (size_t)row * hidden_stride, eff, xf, d);
+    const uint32_t e0 = blockIdx.y * kSplitExpertsPerBlock;
+    const uint32_t ne = num_experts - e0 < (uint32_t)kSplitExpertsPerBlock ? num_experts - e0 : (uint32_t)kSplitExpertsPerBlock;
+    // the four rows are contiguous in every plane
+    const uint8_t* wsrc = W + (size_t)e0 * d;
+    const bool a16 = (reinterpret_cast<uintptr_t>(wsrc) & 15) == 0 && (d & 15) == 0;
+    if (a16) {
+        for (uint32_t i = threadIdx.x; i < ne * d / 16; i += blockDim.x)
+            reinterpret_cast<uint4*>(wrows)[i] = ldg_nc_u4(wsrc + (size_t)i * 16);
+    } else if (a2) {
+        for (uint32_t i = threadIdx.x; i < ne * d / 2; i += blockDim.x)
+            reinterpret_cast<uint16_t*>(wrows)[i] = reinterpret_cast<const uint16_t*>(wsrc)[i];
+    } else {
+        for (uint32_t i = threadIdx.x; i < ne * d; i += blockDim.x) wrows[i] = wsrc[i];
+    }
+    for (uint32_t i = threadIdx.x; i < ne * groups; i += blockDim.x) {
+        srows[i] = S[(size_t)e0 * groups + i];
+        brows[i] = B[(size_t)e0 * groups + i];
+    }
+    stage_router_x<X_BF16>(hidden + (size_t)row * hidden_stride, eff, xf, d);     // ends with a barrier
 
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
-    const uint32_t groups = d / kGroup;
-    const uint32_t e = blockIdx.y * kSplitExpertsPerBlock + warp;
+    const uint32_t e = e0 + warp;
     if (e < num_experts) {
-        float logit = router_row_logit(W + (size_t)e * d, S + (size_t)e * groups, B + (size_t)e * groups, xf, groups, lane, a2);
+        float logit = router_row_logit_smem(wrows + (size_t)warp * d, srows + warp * groups, brows + warp * groups, xf, groups, lane);
         if (logit_bias) logit = __fadd_rn(logit, logit_bias[e]);
         if (lane == 0) scratch_logits[(size_t)row * TF_MAX_ROUTER_EXPERTS + e] = logit;
     }
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
-        const unsigned int t = atomicAdd(&tickets[row], 1u);
-        is_last = (t == gridDim.y - 1);
+        const unsigned int tk = atomicAdd(&tickets[row], 1u);
+        is_last = (tk == gridDim.y - 1);
     }
     __syncthreads();
     if (!is_last) return;
@@ -190,8 +233,10 @@ static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, 
     if (rows <= (uint32_t)kRouterSplitRows) {
         dim3 grid(rows, (num_experts + kSplitExpertsPerBlock - 1) / kSplitExpertsPerBlock);
         auto k = bf ? router_split_kernel<true> : router_split_kernel<false>;
-        if (smem > 40 * 1024) TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<grid, kSplitThreads, smem, st>>>(W, Sp, Bp, hp, stride, ep, pp, logit_bias, out_idx, wp, out_logits,
+        const size_t smem_split = (size_t)d * 4 + (size_t)kSplitExpertsPerBlock * d + (size_t)kSplitExpertsPerBlock * (d / kGroup) * 4;
+        TF_REQUIRE(ctx, smem_split <= 200 * 1024, TF_ERR_UNSUPPORTED, "%s: D=%u too large", name, d);
+        if (smem_split > 40 * 1024) TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_split));
+        k<<<grid, kSplitThreads, smem_split, st>>>(W, Sp, Bp, hp, stride, ep, pp, logit_bias, out_idx, wp, out_logits,
                                              ctx->router_logits, ctx->router_tickets, num_experts, d, top_k, a2);
     } else {
         auto k = bf ? router_block_kernel<true> : router_block_kernel<false>;
