@@ -128,6 +128,11 @@ int tf_abi_version(void);
 /* Number of kernels this context has enqueued since creation (for callers that
  * need to show that work ran on the GPU). */
 uint64_t tf_launch_count(tf_context* ctx);
+/* Synchronises the device and reports whether any kernel abandoned one of its bounded waits
+ * (mbarrier / flag polls never spin for ever: on expiry the kernel records a code and returns).
+ * Replaces the command-buffer error check (Infrastructure/Metal/MetalContext.swift:22-26).
+ * *code_out is 0 when healthy; a non-zero code also returns TF_ERR_CUDA and clears the word. */
+tf_status tf_device_status(tf_context* ctx, uint32_t* code_out);
 
 /* ---- stand-alone GEMVs ---- */
 /* y[m] = deq4(W[m,n]) . x[n]; x, y fp16; fp32 accumulation.

@@ -76,6 +76,7 @@ def _run_batched(tf_ctx, o, pool_h, off, stride, hidden16, idx, w16, D, F, K, E,
     moe.encode_streamed_batched(to_dev(hidden16), pool, stride, capi_offsets(off), routes, acts, partials, T, D, F, K,
                                 partials_f32=partials_f32)
     torch.cuda.synchronize()
+    assert tf_ctx.device_status() == 0, "a kernel abandoned a bounded wait"
     if partials_f32:
         return partials.cpu().numpy().reshape(T, K, D), routes
     return from_dev(partials, np.uint16).reshape(T, K, D), routes

@@ -65,6 +65,7 @@ SIGNATURES = {
     "tf_context_destroy": (None, [vp]),
     "tf_last_error": (C.c_char_p, [vp]),
     "tf_launch_count": (u64, [vp]),
+    "tf_device_status": (C.c_int, [vp, C.POINTER(u32)]),
     "tf_int4_gemv": (C.c_int, [vp, vp, *_PLANES, vp, u64, vp, u64, u32, u32, C.c_int]),
     "tf_int8_gemv": (C.c_int, [vp, vp, *_PLANES, vp, u64, vp, u64, u32, u32, C.c_int]),
     "tf_router_gemma4": (C.c_int, [vp, vp, *_PLANES, vp, vp, u64, vp, u64, vp, vp, vp, u32, u32, u32]),

@@ -75,6 +75,8 @@ tf_status tf_context_create(int device, tf_context** out) {
     e = cudaMalloc(&ctx->router_logits, sizeof(float) * tf::kRouterSplitRows * TF_MAX_ROUTER_EXPERTS);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->router_tickets, sizeof(unsigned int) * tf::kRouterSplitRows);
     if (e == cudaSuccess) e = cudaMemset(ctx->router_tickets, 0, sizeof(unsigned int) * tf::kRouterSplitRows);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->device_error, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(ctx->device_error, 0, sizeof(uint32_t));
     if (e != cudaSuccess) {
         tf_status s = tf::fail(nullptr, TF_ERR_OUT_OF_MEMORY, "context scratch: %s", cudaGetErrorString(e));
         tf_context_destroy(ctx);
@@ -89,6 +91,7 @@ void tf_context_destroy(tf_context* ctx) {
     cudaSetDevice(ctx->device);
     if (ctx->router_logits) cudaFree(ctx->router_logits);
     if (ctx->router_tickets) cudaFree(ctx->router_tickets);
+    if (ctx->device_error) cudaFree(ctx->device_error);
     delete ctx;
 }
 
@@ -98,5 +101,17 @@ const char* tf_last_error(tf_context* ctx) {
 }
 
 uint64_t tf_launch_count(tf_context* ctx) { return ctx ? ctx->launches : 0; }
+
+tf_status tf_device_status(tf_context* ctx, uint32_t* code_out) {
+    TF_REQUIRE(ctx, ctx != nullptr && code_out != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_device_status: NULL argument");
+    TF_CUDA(ctx, cudaDeviceSynchronize());
+    TF_CUDA(ctx, cudaMemcpy(code_out, ctx->device_error, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    if (*code_out != 0) {
+        const uint32_t code = *code_out;
+        TF_CUDA(ctx, cudaMemset(ctx->device_error, 0, sizeof(uint32_t)));
+        return tf::fail(ctx, TF_ERR_CUDA, "a kernel gave up a bounded wait (device code 0x%08x)", code);
+    }
+    return TF_OK;
+}
 
 }  // extern "C"

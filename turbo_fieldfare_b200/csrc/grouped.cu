@@ -10,20 +10,25 @@
 //   - the per-row shared-expert loop (Kernels/Prefill/MoE/PrefillSharedExpert.swift:11-59).
 //
 // Kernel design (memory-bound; HBM roofline): weights are the B operand of
-// mma.sync.m16n8k16 (8 weight rows per warp tile), up to 16 tokens are the A
-// operand. A 4-bit code q placed in the low mantissa bits of an fp16 IS
-// the subnormal q * 2^-24, so "dequantisation" is one AND per two codes and the
-// tensor core multiplies exact integers by fp16 activations with fp32
-// accumulation. Scale and bias are applied per 64-column group after the MMAs:
+// mma.sync.m16n8k16 (8 weight rows per tile), up to 16 tokens are the A operand.
+// A 4-bit code q placed in the low mantissa bits of an fp16 IS the subnormal
+// q * 2^-24, so "dequantisation" is one AND per two codes and the tensor core
+// multiplies exact integers by fp16 activations with fp32 accumulation. Scale
+// and bias are applied per 64-column group after the MMAs:
 //     y += (s * 2^24) * acc + b * sum_k x_k
 // i.e. the reference's group factoring (Metal/Quant/dequant_int4.metal:14-19).
-// The activations of a chunk (<= 16 tokens of one expert) are staged once per
-// CTA in shared memory, already permuted into MMA fragment order; every warp
-// then streams whole 8-row tiles on its own: packed codes and scale rows come
-// straight from global memory into registers, prefetched one step (4 groups)
-// ahead, with no block-wide barrier in the steady state. For very small
-// batches a tile is split along K over `ks` warps that meet at a named barrier
-// and are summed in warp order, so results stay deterministic.
+//
+// A CTA is K-split: compute warp w owns columns [256 w, 256 w + 256) and keeps the
+// activations of the current chunk (<= 16 tokens of one expert) for those columns in
+// registers, already in MMA fragment order. A loader warp streams whole 8-row tiles
+// (packed codes of every matrix plus their scale/bias rows) into a shared ring with
+// bulk asynchronous copies (cp.async.bulk, one full row or one contiguous tile per
+// copy, mbarrier completion; rows are padded so that the fragment loads are free of
+// bank conflicts). After each tile a compute warp stores its partial sums and
+// arrives on an mbarrier; two reducer warps add the partials in warp order
+// (deterministic), apply the epilogue and store. No warp ever meets another at a
+// block-wide barrier in the steady state. Every mbarrier wait is bounded: on expiry
+// the kernel records an error code and returns.
 #include "tf_common.cuh"
 
 namespace tf {
@@ -127,12 +132,19 @@ group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __rest
 // grouped small-batch expert kernels
 // ---------------------------------------------------------------------------
 
-constexpr int kStep = 4;               // 64-column groups per prefetch step
-constexpr int kTileRows = 8;           // weight rows per MMA tile (the n of m16n8k16)
-constexpr float kTwo24 = 16777216.0f;
-constexpr int kStreamWarps = 16;       // warps per CTA
-constexpr int kStreamThreads = kStreamWarps * kWarp;
-constexpr int kMaxKSplit = 8;
+constexpr int kGPW = 4;                 // 64-column groups per compute warp
+constexpr int kWStages = 4;             // ring depth (items) of the packed-code and scale rings
+constexpr int kReducers = 2;            // reducer warps; reducer q owns the items and the partial buffer of parity q
+constexpr int kRedStages = kReducers;   // partial-sum buffers
+constexpr int kTileRows = 8;            // weight rows per MMA tile (the n of m16n8k16)
+constexpr int kMaxComputeWarps = 12;    // K <= 12 * 256 = 3072 columns
+constexpr uint32_t kSpinLimit = 1u << 21;
+constexpr uint32_t kErrTimeoutCodes = 0x7F000001u;   // device error words
+constexpr uint32_t kErrTimeoutScales = 0x7F000002u;
+constexpr uint32_t kErrTimeoutPartials = 0x7F000003u;
+constexpr uint32_t kErrTimeoutRedFree = 0x7F000004u;
+constexpr uint32_t kErrTimeoutStageFree = 0x7F000005u;
+constexpr int kExtraWarps = kReducers + 1;   // reducers + loader
 
 struct MatPlanes {
     const uint8_t* W;
@@ -164,12 +176,11 @@ struct GroupedArgs {
     uint32_t k;                // columns (D for gate/up, F for down)
     uint32_t top_k;
     uint32_t dense_tokens;     // dense mode: number of tokens
-    uint32_t ks;               // warps that share one tile along K (1, 2, 4 or 8)
+    uint32_t* error;           // device word: 0, or the code of the wait that gave up
 };
 
 // D = A * B + C with C either the constant zero (first MMA of a group) or D itself. The four A
-// registers and the four accumulators are always real fragments (tokens g and g + 8), so the
-// operands need no marshalling moves.
+// registers and the four accumulators are always real fragments (tokens g and g + 8).
 __device__ __forceinline__ void mma16816_first(float (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                  : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
@@ -190,44 +201,111 @@ __device__ __forceinline__ uint32_t hmul2_sixteenth(uint32_t v) {
     const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&v), __half2half2(__float2half_rn(0.0625f)));
     return *reinterpret_cast<const uint32_t*>(&r);
 }
-__device__ __forceinline__ uint2 ldg_nc_u2(const void* p) {
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
     uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ float2 lds_f32x2(uint32_t addr) {
-    float2 v;
-    asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+__device__ __forceinline__ float4 lds_f32x4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ void prefetch_l2(const void* p) { asm volatile("prefetch.global.L2 [%0];" ::"l"(p)); }
-__device__ __forceinline__ void named_barrier(uint32_t id, uint32_t threads) {
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+__device__ __forceinline__ void sts_f32x2(uint32_t addr, float a, float b) {
+    asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
 }
+
+// ---- mbarrier and bulk-copy primitives (all waits are bounded) ----
+__device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t addr) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t addr, uint32_t bytes) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t smem_dst, const void* gmem_src, uint32_t bytes, uint32_t mbar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(mbar) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 enum OutMode { kOutActs = 0, kOutPartialF16 = 1, kOutPartialF32 = 2, kOutDenseF16 = 3 };
 
-// Shared memory:
-//   xq[ng][4][32] uint4    A fragments: entry (G, j, lane) = {a0, a1, a2, a3} of MMA j of group G for lane (g, t):
-//                          tokens g (a0, a2) and g + 8 (a1, a3), this lane's columns 64 G + 16 t + {..}
-//   xsum[ng][8] float2     fp32 sums of the 64 activations of group G for tokens g and g + 8
-//   red[2][warps][NMAT][128] float   K-split partials, double buffered
-__host__ __device__ inline size_t stream_smem_bytes(uint32_t ng, int nmat) {
-    return (size_t)ng * 4 * 32 * 16 + (size_t)ng * 8 * 8 + (size_t)2 * kStreamWarps * nmat * 128 * 4;
+// Ring row stride: rows of a tile must start on different banks for the 8-rows-by-8-bytes fragment
+// loads. A stride of 8 (mod 32) words does that for each half warp; strides that already satisfy it
+// (or 24 mod 32) are kept, so the whole tile is one contiguous copy.
+__host__ __device__ inline uint32_t ring_row_stride(uint32_t row_bytes) {
+    const uint32_t words = (row_bytes / 4) % 32;
+    if (words == 8 || words == 24) return row_bytes;
+    return row_bytes + ((8 + 32 - words) % 32) * 4;
 }
 
-// What one step (up to kStep groups of one 8-row tile) needs from global memory.
+// Shared-memory layout of a CTA with `cw` compute warps.
 template <int NMAT>
-struct StepRegs {
-    uint2 w[NMAT][kStep];          // this lane's 16 codes of each group (row g, bytes [8t, 8t+8) of the group)
-    uint2 s0[NMAT], s1[NMAT];      // 4 consecutive bf16 scales of rows 2t and 2t+1
-    uint2 b0[NMAT], b1[NMAT];      // and biases
+struct KSplitSmem {
+    uint32_t cw, ng, row_bytes;
+    __host__ __device__ uint32_t row_stride() const { return ring_row_stride(row_bytes); }
+    __host__ __device__ uint32_t mat_bytes() const { return kTileRows * row_stride(); }
+    __host__ __device__ uint32_t sb_plane_bytes() const { return kTileRows * ng * 2; }                            // multiple of 16
+    __host__ __device__ uint32_t stage_bytes() const { return NMAT * mat_bytes() + NMAT * 2 * sb_plane_bytes(); } // codes, then scales
+    __host__ __device__ uint32_t off_sb_in_stage() const { return NMAT * mat_bytes(); }
+    __host__ __device__ uint32_t ring_bytes() const { return kWStages * stage_bytes(); }
+    __host__ __device__ uint32_t red_stage_bytes() const { return cw * NMAT * 128 * 4; }
+    __host__ __device__ uint32_t red_bytes() const { return kRedStages * red_stage_bytes(); }
+    __host__ __device__ uint32_t bar_count() const { return 2 * kWStages + 2 * kRedStages; }
+    __host__ __device__ uint32_t off_red() const { return ring_bytes(); }
+    __host__ __device__ uint32_t off_bar() const { return off_red() + red_bytes(); }
+    __host__ __device__ size_t total() const { return (size_t)off_bar() + (size_t)bar_count() * 8; }
 };
+
+// Where a warp is in its CTA's item sequence and what the chunk resolves to.
+template <int NMAT>
+struct ItemCursor {
+    uint32_t chunk, tile;
+    MatPlanes pl[NMAT];
+    uint32_t ntok, row_base;
+};
+
+template <int NMAT, bool DENSE>
+__device__ __forceinline__ void resolve_chunk(const GroupedArgs& args, ItemCursor<NMAT>& c) {
+    if constexpr (DENSE) {
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) c.pl[m] = args.dense[m];
+        c.row_base = c.chunk * kChunkTokens;
+        const uint32_t left = args.dense_tokens - c.row_base;
+        c.ntok = left < (uint32_t)kChunkTokens ? left : (uint32_t)kChunkTokens;
+    } else {
+        const uint32_t gi = args.chunk_group[c.chunk];
+        const tf_group grp = args.groups[gi];
+        const uint32_t cin = c.chunk - args.chunk_start[gi];
+        const uint8_t* blob = args.pool_base + (uint64_t)grp.expert * args.expert_stride;
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) {
+            c.pl[m].W = blob + args.w_off[m];
+            c.pl[m].S = reinterpret_cast<const uint16_t*>(blob + args.s_off[m]);
+            c.pl[m].B = reinterpret_cast<const uint16_t*>(blob + args.b_off[m]);
+        }
+        c.row_base = grp.pair_start + cin * kChunkTokens;
+        const uint32_t left = grp.pair_count - cin * kChunkTokens;
+        c.ntok = left < (uint32_t)kChunkTokens ? left : (uint32_t)kChunkTokens;
+    }
+}
 
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
@@ -237,323 +315,335 @@ __device__ __forceinline__ float bf16_lo_x2p24(uint32_t v) { return __uint_as_fl
 __device__ __forceinline__ float bf16_hi_x2p24(uint32_t v) { return __uint_as_float((v & 0xFFFF0000u) + 0x0C000000u); }
 
 template <int NMAT, bool DENSE, int OUT_MODE>
-__global__ void __launch_bounds__(kStreamThreads)
-grouped_stream_kernel(const GroupedArgs args) {
+__global__ void __launch_bounds__((kMaxComputeWarps + kExtraWarps) * kWarp)
+grouped_ksplit_kernel(const GroupedArgs args) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const int g = lane >> 2, t = lane & 3;
+    const uint32_t cw = blockDim.x / kWarp - kExtraWarps;  // compute warps; then kReducers reducer warps; the last warp loads
     const uint32_t ng = args.k / kGroup;
-    const uint32_t ks = args.ks;
     const uint32_t row_bytes = args.k / 2;
+    const KSplitSmem<NMAT> lay{cw, ng, row_bytes};
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
-    const uint32_t xq_addr = smem_base + lane * 16;                    // + G * 2048 + j * 512
-    const uint32_t xsum_addr = smem_base + ng * 2048 + g * 8;          // + G * 64
-    uint4* xq = reinterpret_cast<uint4*>(smem);
-    float2* xsum = reinterpret_cast<float2*>(smem + (size_t)ng * 2048);
-    float* red = reinterpret_cast<float*>(smem + (size_t)ng * 2048 + (size_t)ng * 64);
+    const uint32_t red_base = smem_base + lay.off_red();
+    const uint32_t bar_base = smem_base + lay.off_bar();
+    // mbarriers: full[stage] | empty[stage] | part_full[r] | red_free[r]
+    auto bar_full = [&](uint32_t st) { return bar_base + st * 8; };
+    auto bar_empty = [&](uint32_t st) { return bar_base + (kWStages + st) * 8; };
+    auto bar_part_full = [&](uint32_t r) { return bar_base + (2 * kWStages + r) * 8; };
+    auto bar_red_free = [&](uint32_t r) { return bar_base + (2 * kWStages + kRedStages + r) * 8; };
 
     const uint32_t tiles = args.rows / kTileRows;
     const uint32_t total_chunks = DENSE ? (args.dense_tokens + kChunkTokens - 1) / kChunkTokens : args.counters[1];
     const uint32_t total_items = total_chunks * tiles;
-    // contiguous item range per CTA: consecutive items share the chunk whose activations sit in shared memory
-    uint32_t item = (uint32_t)((uint64_t)total_items * blockIdx.x / gridDim.x);
+    // contiguous item range per CTA: consecutive items share the chunk, whose activations stay in registers
+    const uint32_t item_begin = (uint32_t)((uint64_t)total_items * blockIdx.x / gridDim.x);
     const uint32_t item_end = (uint32_t)((uint64_t)total_items * (blockIdx.x + 1) / gridDim.x);
+    if (item_begin >= item_end) return;
+    const uint32_t n_items = item_end - item_begin;
 
-    // K split: warp group `grp` of ks warps shares a tile; warp `kw` of the group owns groups [k_begin, k_end)
-    const uint32_t ngroups = kStreamWarps / ks;
-    const uint32_t grp = warp / ks, kw = warp % ks;
-    const uint32_t steps_total = (ng + kStep - 1) / kStep;
-    const uint32_t steps_per_warp = (steps_total + ks - 1) / ks;
-    const uint32_t k_begin = kw * steps_per_warp * kStep < ng ? kw * steps_per_warp * kStep : ng;
-    const uint32_t k_end = (kw + 1) * steps_per_warp * kStep < ng ? (kw + 1) * steps_per_warp * kStep : ng;
-    const uint32_t nsteps = k_end > k_begin ? (k_end - k_begin + kStep - 1) / kStep : 0;
-    const bool sb_vec = (ng % 4) == 0;        // 4 consecutive bf16 of a scale row are 8-byte aligned
-    const uint32_t out_stride = args.out_stride, top_k = args.top_k;
+    if (threadIdx.x == 0) {
+        for (uint32_t st = 0; st < (uint32_t)kWStages; ++st) { mbar_init(bar_full(st), 1); mbar_init(bar_empty(st), cw); }
+        for (uint32_t r = 0; r < (uint32_t)kRedStages; ++r) { mbar_init(bar_part_full(r), cw); mbar_init(bar_red_free(r), 1); }
+        fence_proxy_async();
+    }
+    __syncthreads();
 
-    while (item < item_end) {
-        // ---- segment: the items of this CTA that belong to one chunk ----
-        const uint32_t chunk = item / tiles;
-        const uint32_t tile_begin = item % tiles;
-        const uint32_t seg_items = (item_end - item) < (tiles - tile_begin) ? (item_end - item) : (tiles - tile_begin);
-        MatPlanes pl[NMAT];
-        uint32_t ntok, row_base;
-        if constexpr (DENSE) {
-#pragma unroll
-            for (int m = 0; m < NMAT; ++m) pl[m] = args.dense[m];
-            row_base = chunk * kChunkTokens;
-            const uint32_t left = args.dense_tokens - row_base;
-            ntok = left < (uint32_t)kChunkTokens ? left : (uint32_t)kChunkTokens;
-        } else {
-            const uint32_t gi = args.chunk_group[chunk];
-            const tf_group grpinfo = args.groups[gi];
-            const uint32_t cin = chunk - args.chunk_start[gi];
-            const uint8_t* blob = args.pool_base + (uint64_t)grpinfo.expert * args.expert_stride;
-#pragma unroll
-            for (int m = 0; m < NMAT; ++m) {
-                pl[m].W = blob + args.w_off[m];
-                pl[m].S = reinterpret_cast<const uint16_t*>(blob + args.s_off[m]);
-                pl[m].B = reinterpret_cast<const uint16_t*>(blob + args.b_off[m]);
-            }
-            row_base = grpinfo.pair_start + cin * kChunkTokens;
-            const uint32_t left = grpinfo.pair_count - cin * kChunkTokens;
-            ntok = left < (uint32_t)kChunkTokens ? left : (uint32_t)kChunkTokens;
+    auto advance = [&](ItemCursor<NMAT>& c) {
+        if (++c.tile == tiles) {
+            c.tile = 0;
+            ++c.chunk;
+            if (c.chunk < total_chunks) resolve_chunk<NMAT, DENSE>(args, c);
         }
+    };
 
-        __syncthreads();        // every warp is done with the previous chunk's fragments
-        // Stage the chunk's activations as MMA A fragments. Work item (G, half, lane): token g + 8 * half,
-        // columns 64 G + 16 t .. + 15. The 16 values x0..x15 feed four MMAs:
-        //   j = 0: (x0,x4),(x2,x6)   j = 1: (x1,x5)/16,(x3,x7)/16   j = 2, 3: the same for x8..x15.
-        // Odd columns are pre-scaled by 1/16 because their codes sit four mantissa bits higher.
-        for (uint32_t idx = threadIdx.x; idx < ng * 64; idx += blockDim.x) {
-            const uint32_t G = idx >> 6, half = (idx >> 5) & 1, ln = idx & 31, tok = (ln >> 2) + 8 * half, tt = ln & 3;
-            uint32_t r[8];
-            if (tok < ntok) {
-                const uint32_t rr = (DENSE || NMAT == 1) ? row_base + tok : args.sorted_pairs[row_base + tok].token;
-                const uint4* p = reinterpret_cast<const uint4*>(args.x + (size_t)rr * args.x_stride + G * kGroup + tt * 16);
-                const uint4 lo = __ldg(p), hi = __ldg(p + 1);
-                r[0] = lo.x; r[1] = lo.y; r[2] = lo.z; r[3] = lo.w;
-                r[4] = hi.x; r[5] = hi.y; r[6] = hi.z; r[7] = hi.w;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) r[i] = 0;
-            }
-            float sum = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&r[i]));
-                sum += v.x + v.y;
-            }
-            sum += __shfl_xor_sync(kFullMask, sum, 1);
-            sum += __shfl_xor_sync(kFullMask, sum, 2);
-            uint32_t* q = reinterpret_cast<uint32_t*>(xq + (size_t)G * 128 + ln) + half;     // a0/a1 slot; a2/a3 at +2
-            q[0 * 128 + 0] = prmt(r[0], r[2], 0x5410);                      q[0 * 128 + 2] = prmt(r[1], r[3], 0x5410);
-            q[1 * 128 + 0] = hmul2_sixteenth(prmt(r[0], r[2], 0x7632));     q[1 * 128 + 2] = hmul2_sixteenth(prmt(r[1], r[3], 0x7632));
-            q[2 * 128 + 0] = prmt(r[4], r[6], 0x5410);                      q[2 * 128 + 2] = prmt(r[5], r[7], 0x5410);
-            q[3 * 128 + 0] = hmul2_sixteenth(prmt(r[4], r[6], 0x7632));     q[3 * 128 + 2] = hmul2_sixteenth(prmt(r[5], r[7], 0x7632));
-            if (tt == 0) reinterpret_cast<float*>(xsum + G * 8 + (ln >> 2))[half] = sum;
-        }
-        __syncthreads();
+    auto advance_by = [&](ItemCursor<NMAT>& c, uint32_t n) {
+        for (uint32_t i = 0; i < n; ++i) advance(c);
+    };
 
-        // ---- this warp group's tiles of the segment: tile_begin + grp, + ngroups, ... ----
-        const uint32_t my_tiles = grp < seg_items ? (seg_items - grp + ngroups - 1) / ngroups : 0;
-        const uint32_t total_steps = my_tiles * nsteps;
+    if ((uint32_t)warp < cw) {
+        // =========================== compute warp ===========================
+        const uint32_t g0 = warp * kGPW;
+        const uint32_t ngw = ng - g0 < (uint32_t)kGPW ? ng - g0 : (uint32_t)kGPW;     // g0 < ng by construction
+        const bool sb_vec = (ng % 4) == 0;
+        const uint32_t sb_row0 = ((2 * t) * ng + g0) * 2, sb_row1 = ((2 * t + 1) * ng + g0) * 2;
+        const uint32_t lane_code_off = g * lay.row_stride() + g0 * 32 + t * 8;          // this lane's codes within a matrix tile
 
-        // lane pointers at (first tile, k_begin); a step advances them by kStep groups, a tile change rewinds K
-        const uint8_t* wp[NMAT];
-        const uint16_t* sp[NMAT];
-        const uint16_t* bp[NMAT];
-#pragma unroll
-        for (int m = 0; m < NMAT; ++m) {
-            const uint32_t tile0 = tile_begin + grp;
-            wp[m] = pl[m].W + (size_t)(tile0 * kTileRows + g) * row_bytes + k_begin * 32 + t * 8;
-            sp[m] = pl[m].S + (size_t)(tile0 * kTileRows + 2 * t) * ng + k_begin;
-            bp[m] = pl[m].B + (size_t)(tile0 * kTileRows + 2 * t) * ng + k_begin;
-        }
-        const uint32_t w_tile_jump = ngroups * kTileRows * row_bytes - (nsteps - 1) * kStep * 32;   // last step -> next tile's first
-        const uint32_t sb_tile_jump = ngroups * kTileRows * ng - (nsteps - 1) * kStep;
-        uint32_t load_st = 0;       // step index (within the tile) of the next load
+        ItemCursor<NMAT> cur;
+        cur.chunk = item_begin / tiles;
+        cur.tile = item_begin % tiles;
+        resolve_chunk<NMAT, DENSE>(args, cur);
 
-        // L2 prefetch of one whole tile (this warp's K range of the 8 rows, and the scale rows): issued
-        // one tile ahead so that DRAM latency is paid long before the register loads need the data.
-        const uint32_t pf_line0 = (k_begin * 32) / 128, pf_line1 = (k_end * 32 + 127) / 128;
-        const uint32_t pf_lines = (pf_line1 - pf_line0) * kTileRows;
-        const uint32_t sb_lines = (kTileRows * ng * 2 + 127) / 128;
-        uint32_t load_tile = tile_begin + grp;
-        auto prefetch_tile = [&](uint32_t tile) {
-            if (tile >= tile_begin + seg_items) return;
-#pragma unroll
-            for (int m = 0; m < NMAT; ++m) {
-                const uint8_t* wt = pl[m].W + (size_t)tile * kTileRows * row_bytes;
-                for (uint32_t l = lane; l < pf_lines; l += kWarp) {
-                    const uint32_t r = l / (pf_line1 - pf_line0), c = pf_line0 + l % (pf_line1 - pf_line0);
-                    prefetch_l2(wt + (size_t)r * row_bytes + c * 128);
-                }
-                if (kw == 0 && lane < sb_lines) {
-                    prefetch_l2(reinterpret_cast<const uint8_t*>(pl[m].S + (size_t)tile * kTileRows * ng) + lane * 128);
-                    prefetch_l2(reinterpret_cast<const uint8_t*>(pl[m].B + (size_t)tile * kTileRows * ng) + lane * 128);
-                }
-            }
-        };
-        if (my_tiles > 0 && nsteps > 0) prefetch_tile(load_tile);
+        uint4 xa[kGPW][4];
+        float2 xsum[kGPW];
+        uint32_t loaded_chunk = 0xFFFFFFFFu;
+        uint32_t fail = 0;
 
-        auto load_step = [&](StepRegs<NMAT>& sr) {
-            const uint32_t g_first = k_begin + load_st * kStep;
-            if (load_st == 0) {
-                prefetch_tile(load_tile + ngroups);
-                load_tile += ngroups;
-            }
+        for (uint32_t li = 0; li < n_items; ++li) {
+            const uint32_t st = li % kWStages, use = li / kWStages;
+            if (cur.chunk != loaded_chunk) {
+                // activations of this warp's columns for the chunk's tokens g and g + 8, in MMA operand order:
+                // the 16 values x0..x15 at columns 64 G + 16 t feed four MMAs,
+                //   j = 0: (x0,x4),(x2,x6)   j = 1: (x1,x5)/16,(x3,x7)/16   j = 2, 3: the same for x8..x15;
+                // odd columns are pre-scaled by 1/16 because their codes sit four mantissa bits higher.
+                loaded_chunk = cur.chunk;
 #pragma unroll
-            for (int m = 0; m < NMAT; ++m) {
+                for (int i = 0; i < kGPW; ++i) {
+                    uint32_t r[2][8];
 #pragma unroll
-                for (int i = 0; i < kStep; ++i)
-                    sr.w[m][i] = (g_first + i < k_end) ? ldg_nc_u2(wp[m] + i * 32) : make_uint2(0u, 0u);
-                if (sb_vec) {
-                    sr.s0[m] = __ldg(reinterpret_cast<const uint2*>(sp[m]));
-                    sr.s1[m] = __ldg(reinterpret_cast<const uint2*>(sp[m] + ng));
-                    sr.b0[m] = __ldg(reinterpret_cast<const uint2*>(bp[m]));
-                    sr.b1[m] = __ldg(reinterpret_cast<const uint2*>(bp[m] + ng));
-                } else {
-                    uint32_t v[4][4];
+                    for (int hh = 0; hh < 2; ++hh) {
+                        const uint32_t tok = g + 8 * hh;
+                        if ((uint32_t)i < ngw && tok < cur.ntok) {
+                            const uint32_t rr = (DENSE || NMAT == 1) ? cur.row_base + tok : args.sorted_pairs[cur.row_base + tok].token;
+                            const uint4* p = reinterpret_cast<const uint4*>(args.x + (size_t)rr * args.x_stride + (g0 + i) * kGroup + t * 16);
+                            const uint4 lo = __ldg(p), hi = __ldg(p + 1);
+                            r[hh][0] = lo.x; r[hh][1] = lo.y; r[hh][2] = lo.z; r[hh][3] = lo.w;
+                            r[hh][4] = hi.x; r[hh][5] = hi.y; r[hh][6] = hi.z; r[hh][7] = hi.w;
+                        } else {
 #pragma unroll
-                    for (int i = 0; i < kStep; ++i) {
-                        const bool ok = g_first + i < k_end;
-                        v[0][i] = ok ? sp[m][i] : 0u; v[1][i] = ok ? sp[m][ng + i] : 0u;
-                        v[2][i] = ok ? bp[m][i] : 0u; v[3][i] = ok ? bp[m][ng + i] : 0u;
+                            for (int q = 0; q < 8; ++q) r[hh][q] = 0;
+                        }
                     }
-                    sr.s0[m] = make_uint2(v[0][0] | (v[0][1] << 16), v[0][2] | (v[0][3] << 16));
-                    sr.s1[m] = make_uint2(v[1][0] | (v[1][1] << 16), v[1][2] | (v[1][3] << 16));
-                    sr.b0[m] = make_uint2(v[2][0] | (v[2][1] << 16), v[2][2] | (v[2][3] << 16));
-                    sr.b1[m] = make_uint2(v[3][0] | (v[3][1] << 16), v[3][2] | (v[3][3] << 16));
-                }
-            }
-            if (++load_st == nsteps) {
-                load_st = 0;
+                    float s0 = 0.0f, s1 = 0.0f;
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m) { wp[m] += w_tile_jump; sp[m] += sb_tile_jump; bp[m] += sb_tile_jump; }
-            } else {
+                    for (int q = 0; q < 8; ++q) {
+                        const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&r[0][q]));
+                        const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&r[1][q]));
+                        s0 += v0.x + v0.y; s1 += v1.x + v1.y;
+                    }
+                    s0 += __shfl_xor_sync(kFullMask, s0, 1); s0 += __shfl_xor_sync(kFullMask, s0, 2);
+                    s1 += __shfl_xor_sync(kFullMask, s1, 1); s1 += __shfl_xor_sync(kFullMask, s1, 2);
+                    xsum[i] = make_float2(s0, s1);
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m) { wp[m] += kStep * 32; sp[m] += kStep; bp[m] += kStep; }
-            }
-        };
-
-        float ya[NMAT][4];
-#pragma unroll
-        for (int m = 0; m < NMAT; ++m) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) ya[m][j] = 0.0f;
-        }
-        uint32_t comp_st = 0, comp_tile = tile_begin + grp, comp_ti = 0;
-
-        auto compute_step = [&](const StepRegs<NMAT>& sr) {
-            const uint32_t g_first = k_begin + comp_st * kStep;
-#pragma unroll
-            for (int i = 0; i < kStep; ++i) {
-                if (g_first + i < k_end) {          // warp-uniform
-                    const uint32_t G = g_first + i;
-                    const uint4 a0 = lds128(xq_addr + G * 2048), a1 = lds128(xq_addr + G * 2048 + 512);
-                    const uint4 a2 = lds128(xq_addr + G * 2048 + 1024), a3 = lds128(xq_addr + G * 2048 + 1536);
-                    const float2 xs = lds_f32x2(xsum_addr + G * 64);
-#pragma unroll
-                    for (int m = 0; m < NMAT; ++m) {
-                        const uint32_t w0 = sr.w[m][i].x, w1 = sr.w[m][i].y, w0s = w0 >> 8, w1s = w1 >> 8;
-                        float c[4];
-                        mma16816_first(c, a0, w0 & 0x000F000Fu, w0s & 0x000F000Fu);
-                        mma16816_acc(c, a1, w0 & 0x00F000F0u, w0s & 0x00F000F0u);
-                        mma16816_acc(c, a2, w1 & 0x000F000Fu, w1s & 0x000F000Fu);
-                        mma16816_acc(c, a3, w1 & 0x00F000F0u, w1s & 0x00F000F0u);
-                        const uint32_t sv0 = i < 2 ? sr.s0[m].x : sr.s0[m].y, sv1 = i < 2 ? sr.s1[m].x : sr.s1[m].y;
-                        const uint32_t bv0 = i < 2 ? sr.b0[m].x : sr.b0[m].y, bv1 = i < 2 ? sr.b1[m].x : sr.b1[m].y;
-                        const float s0 = (i & 1) ? bf16_hi_x2p24(sv0) : bf16_lo_x2p24(sv0);
-                        const float s1 = (i & 1) ? bf16_hi_x2p24(sv1) : bf16_lo_x2p24(sv1);
-                        const float b0 = (i & 1) ? bf16_hi(bv0) : bf16_lo(bv0), b1 = (i & 1) ? bf16_hi(bv1) : bf16_lo(bv1);
-                        // c0, c1: token g, rows 2t, 2t+1; c2, c3: token g + 8
-                        ya[m][0] = fmaf(s0, c[0], fmaf(b0, xs.x, ya[m][0]));
-                        ya[m][1] = fmaf(s1, c[1], fmaf(b1, xs.x, ya[m][1]));
-                        ya[m][2] = fmaf(s0, c[2], fmaf(b0, xs.y, ya[m][2]));
-                        ya[m][3] = fmaf(s1, c[3], fmaf(b1, xs.y, ya[m][3]));
+                    for (int h2 = 0; h2 < 2; ++h2) {
+                        const int o = 4 * h2;
+                        xa[i][2 * h2] = make_uint4(prmt(r[0][o], r[0][o + 2], 0x5410), prmt(r[1][o], r[1][o + 2], 0x5410),
+                                                   prmt(r[0][o + 1], r[0][o + 3], 0x5410), prmt(r[1][o + 1], r[1][o + 3], 0x5410));
+                        xa[i][2 * h2 + 1] = make_uint4(hmul2_sixteenth(prmt(r[0][o], r[0][o + 2], 0x7632)),
+                                                       hmul2_sixteenth(prmt(r[1][o], r[1][o + 2], 0x7632)),
+                                                       hmul2_sixteenth(prmt(r[0][o + 1], r[0][o + 3], 0x7632)),
+                                                       hmul2_sixteenth(prmt(r[1][o + 1], r[1][o + 3], 0x7632)));
                     }
                 }
             }
-            if (++comp_st < nsteps) return;
-            // ---- last step of the tile: combine, reduce over the K split, store ----
-            comp_st = 0;
+            if (!mbar_wait(bar_full(st), use & 1)) { fail = kErrTimeoutCodes; break; }
+
+            const uint32_t ring_item = smem_base + st * lay.stage_bytes() + lane_code_off;
+            const uint32_t sb_item = smem_base + st * lay.stage_bytes() + lay.off_sb_in_stage();
+            // All codes of the item first, then the MMAs interleaved over the (matrix, group) pairs: the four
+            // MMAs of one group form a dependent chain through its accumulator, so consecutive instructions
+            // always belong to different chains and the tensor pipe stays full.
+            uint2 wv[NMAT][kGPW];
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+                for (int i = 0; i < kGPW; ++i)
+                    wv[m][i] = (uint32_t)i < ngw ? lds64(ring_item + m * lay.mat_bytes() + i * 32) : make_uint2(0u, 0u);
+            }
+            float c[NMAT][kGPW][4];
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+                for (int i = 0; i < kGPW; ++i) mma16816_first(c[m][i], xa[i][0], wv[m][i].x & 0x000F000Fu, (wv[m][i].x >> 8) & 0x000F000Fu);
+            }
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+                for (int i = 0; i < kGPW; ++i) mma16816_acc(c[m][i], xa[i][1], wv[m][i].x & 0x00F000F0u, (wv[m][i].x >> 8) & 0x00F000F0u);
+            }
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+                for (int i = 0; i < kGPW; ++i) mma16816_acc(c[m][i], xa[i][2], wv[m][i].y & 0x000F000Fu, (wv[m][i].y >> 8) & 0x000F000Fu);
+            }
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+#pragma unroll
+                for (int i = 0; i < kGPW; ++i) mma16816_acc(c[m][i], xa[i][3], wv[m][i].y & 0x00F000F0u, (wv[m][i].y >> 8) & 0x00F000F0u);
+            }
             float y[NMAT][4];
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
+                const uint32_t sm_s = sb_item + (m * 2) * lay.sb_plane_bytes(), sm_b = sm_s + lay.sb_plane_bytes();
+                uint2 vs0, vs1, vb0, vb1;
+                if (sb_vec) {
+                    vs0 = lds64(sm_s + sb_row0); vs1 = lds64(sm_s + sb_row1);
+                    vb0 = lds64(sm_b + sb_row0); vb1 = lds64(sm_b + sb_row1);
+                } else {
+                    uint32_t v[4][4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    y[m][j] = ya[m][j];
-                    ya[m][j] = 0.0f;
-                }
-            }
-            if (ks > 1) {
-                // partial sums of the group's warps, added in warp order by the group's first warp
-                float* rb = red + (size_t)(comp_ti & 1) * (kStreamWarps * NMAT * 128);
-#pragma unroll
-                for (int m = 0; m < NMAT; ++m) {
-                    float* r = rb + ((size_t)warp * NMAT + m) * 128;
-                    *reinterpret_cast<float2*>(r + g * 8 + 2 * t) = make_float2(y[m][0], y[m][1]);
-                    *reinterpret_cast<float2*>(r + (g + 8) * 8 + 2 * t) = make_float2(y[m][2], y[m][3]);
-                }
-                named_barrier(1 + grp, ks * kWarp);
-                if (kw == 0) {
-#pragma unroll
-                    for (int m = 0; m < NMAT; ++m) {
-                        float2 lo = make_float2(0.0f, 0.0f), hi = make_float2(0.0f, 0.0f);
-                        for (uint32_t w2 = 0; w2 < ks; ++w2) {
-                            const float* r = rb + ((size_t)(warp + w2) * NMAT + m) * 128;
-                            const float2 v0 = *reinterpret_cast<const float2*>(r + g * 8 + 2 * t);
-                            const float2 v1 = *reinterpret_cast<const float2*>(r + (g + 8) * 8 + 2 * t);
-                            lo.x += v0.x; lo.y += v0.y; hi.x += v1.x; hi.y += v1.y;
-                        }
-                        y[m][0] = lo.x; y[m][1] = lo.y; y[m][2] = hi.x; y[m][3] = hi.y;
+                    for (int i = 0; i < kGPW; ++i) {
+                        const bool ok = (uint32_t)i < ngw;
+                        v[0][i] = ok ? lds16(sm_s + sb_row0 + i * 2) : 0u; v[1][i] = ok ? lds16(sm_s + sb_row1 + i * 2) : 0u;
+                        v[2][i] = ok ? lds16(sm_b + sb_row0 + i * 2) : 0u; v[3][i] = ok ? lds16(sm_b + sb_row1 + i * 2) : 0u;
                     }
+                    vs0 = make_uint2(v[0][0] | (v[0][1] << 16), v[0][2] | (v[0][3] << 16));
+                    vs1 = make_uint2(v[1][0] | (v[1][1] << 16), v[1][2] | (v[1][3] << 16));
+                    vb0 = make_uint2(v[2][0] | (v[2][1] << 16), v[2][2] | (v[2][3] << 16));
+                    vb1 = make_uint2(v[3][0] | (v[3][1] << 16), v[3][2] | (v[3][3] << 16));
                 }
-                // `red` is double buffered by tile parity: a buffer is rewritten two tiles later, after another
-                // pass through this barrier, which the reading warp reaches only once it has finished reading.
-            }
-            if (kw == 0) {
-                const uint32_t out_row = comp_tile * kTileRows + 2 * t;
+                float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const uint32_t tok = g + 8 * hh;
-                    if (tok < ntok) {
-                        const float v0 = y[0][2 * hh], v1 = y[0][2 * hh + 1];
-                        if constexpr (OUT_MODE == kOutActs) {
-                            float g0v = v0, g1v = v1, u0 = y[NMAT - 1][2 * hh], u1 = y[NMAT - 1][2 * hh + 1];
-                            if constexpr (DENSE) {
-                                // shared expert: gate and up are stored as fp16 before the activation
-                                // (Kernels/MoE/SharedExpertInt4.swift:62-93; Metal/Primitives/utility.metal:15-17)
-                                g0v = __half2float(__float2half_rn(g0v)); g1v = __half2float(__float2half_rn(g1v));
-                                u0 = __half2float(__float2half_rn(u0)); u1 = __half2float(__float2half_rn(u1));
-                            }
-                            // routed: act = half(gelu_tanh(gate) * up), gate and up in fp32 (prefill.metal:634-636; moe.metal:368)
-                            *reinterpret_cast<__half2*>(static_cast<uint16_t*>(args.out) + (size_t)(row_base + tok) * out_stride + out_row) =
-                                __floats2half2_rn(gelu_tanh(g0v) * u0, gelu_tanh(g1v) * u1);
-                        } else if constexpr (OUT_MODE == kOutDenseF16) {
-                            *reinterpret_cast<__half2*>(static_cast<uint16_t*>(args.out) + (size_t)(row_base + tok) * out_stride + out_row) =
-                                __floats2half2_rn(v0, v1);
-                        } else {
-                            const tf_pair pr = args.sorted_pairs[row_base + tok];
-                            const size_t idx = ((size_t)pr.token * top_k + pr.rank) * out_stride + out_row;
-                            if constexpr (OUT_MODE == kOutPartialF16)      // prefill.metal:666-669
-                                *reinterpret_cast<__half2*>(static_cast<uint16_t*>(args.out) + idx) = __floats2half2_rn(v0, v1);
-                            else
-                                *reinterpret_cast<float2*>(static_cast<float*>(args.out) + idx) = make_float2(v0, v1);
-                        }
-                    }
+                for (int i = 0; i < kGPW; ++i) {
+                    // groups beyond this warp's range carry zero codes and zero activations; their scale words are
+                    // zeroed above (or belong to the next warp's group and multiply a zero accumulator and a zero sum)
+                    const uint32_t sv0 = i < 2 ? vs0.x : vs0.y, sv1 = i < 2 ? vs1.x : vs1.y;
+                    const uint32_t bv0 = i < 2 ? vb0.x : vb0.y, bv1 = i < 2 ? vb1.x : vb1.y;
+                    const float s0 = (i & 1) ? bf16_hi_x2p24(sv0) : bf16_lo_x2p24(sv0);
+                    const float s1 = (i & 1) ? bf16_hi_x2p24(sv1) : bf16_lo_x2p24(sv1);
+                    const float b0 = (i & 1) ? bf16_hi(bv0) : bf16_lo(bv0), b1 = (i & 1) ? bf16_hi(bv1) : bf16_lo(bv1);
+                    // c0, c1: token g, rows 2t, 2t+1; c2, c3: token g + 8
+                    acc[0] = fmaf(s0, c[m][i][0], fmaf(b0, xsum[i].x, acc[0]));
+                    acc[1] = fmaf(s1, c[m][i][1], fmaf(b1, xsum[i].x, acc[1]));
+                    acc[2] = fmaf(s0, c[m][i][2], fmaf(b0, xsum[i].y, acc[2]));
+                    acc[3] = fmaf(s1, c[m][i][3], fmaf(b1, xsum[i].y, acc[3]));
                 }
-            }
-            comp_tile += ngroups;
-            ++comp_ti;
-        };
-
-        if (ks > 1 && nsteps == 0) {
-            // a warp of a K-split group whose K range is empty still has to meet its group at every tile
-            for (uint32_t ti = 0; ti < my_tiles; ++ti) {
-                float* rb = red + (size_t)(ti & 1) * (kStreamWarps * NMAT * 128);
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m) {
-                    float* r = rb + ((size_t)warp * NMAT + m) * 128;
-                    *reinterpret_cast<float2*>(r + g * 8 + 2 * t) = make_float2(0.0f, 0.0f);
-                    *reinterpret_cast<float2*>(r + (g + 8) * 8 + 2 * t) = make_float2(0.0f, 0.0f);
-                }
-                named_barrier(1 + grp, ks * kWarp);
+                for (int j = 0; j < 4; ++j) y[m][j] = acc[j];
             }
-        } else if (total_steps > 0) {
-            // ping-pong register prefetch: while one step's registers are consumed the next step's loads are in flight
-            StepRegs<NMAT> ra, rb2;
-            load_step(ra);
-            uint32_t gs = 0;
-            for (; gs + 2 <= total_steps; gs += 2) {
-                load_step(rb2);
-                compute_step(ra);
-                if (gs + 2 < total_steps) load_step(ra);
-                compute_step(rb2);
+            // this warp is done with the stage (codes and scales are in registers or consumed)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty(st));
+            // hand the partial sums to the reducer
+            const uint32_t r = li % kRedStages, ruse = li / kRedStages;
+            if (!mbar_wait(bar_red_free(r), (ruse & 1) ^ 1)) { fail = kErrTimeoutRedFree; break; }
+            const uint32_t red_w = red_base + r * lay.red_stage_bytes() + (warp * NMAT) * 512 + (g * 8 + 2 * t) * 4;
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+                sts_f32x2(red_w + m * 512, y[m][0], y[m][1]);
+                sts_f32x2(red_w + m * 512 + 256, y[m][2], y[m][3]);      // token g + 8: index (g + 8) * 8 + 2t
             }
-            if (gs < total_steps) compute_step(ra);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_part_full(r));
+            if (li + 1 < n_items) advance(cur);
         }
-        item += seg_items;
+        if (fail && lane == 0) atomicCAS(args.error, 0u, fail);
+    } else if ((uint32_t)warp == cw + kReducers) {
+        // =========================== loader warp ===========================
+        ItemCursor<NMAT> iss;
+        iss.chunk = item_begin / tiles;
+        iss.tile = item_begin % tiles;
+        resolve_chunk<NMAT, DENSE>(args, iss);
+        const uint32_t plane_bytes = lay.sb_plane_bytes();
+        const bool contiguous = lay.row_stride() == row_bytes;       // the 8 rows of a tile land as one copy
+        const uint32_t tx_bytes = NMAT * kTileRows * row_bytes + NMAT * 2 * plane_bytes;
+        uint32_t fail = 0, issued = 0;
+        for (uint32_t li = 0; li < n_items; ++li) {
+            const uint32_t st = li % kWStages, use = li / kWStages;
+            if (use > 0 && !mbar_wait(bar_empty(st), (use - 1) & 1)) { fail = kErrTimeoutStageFree; break; }
+            const uint32_t mbar = bar_full(st);
+            const uint32_t stage = smem_base + st * lay.stage_bytes();
+            if (lane == 0) {
+                fence_proxy_async();          // the stage was last read through the generic proxy
+                mbar_arrive_expect_tx(mbar, tx_bytes);
+            }
+            __syncwarp();
+            if (contiguous) {
+                if (lane < NMAT) {
+                    const MatPlanes& mp = lane ? iss.pl[NMAT - 1] : iss.pl[0];
+                    bulk_copy_g2s(stage + lane * lay.mat_bytes(), mp.W + (size_t)iss.tile * kTileRows * row_bytes,
+                                  kTileRows * row_bytes, mbar);
+                }
+            } else if (lane < NMAT * kTileRows) {
+                const uint32_t m = lane / kTileRows, r = lane % kTileRows;
+                const MatPlanes& mp = m ? iss.pl[NMAT - 1] : iss.pl[0];
+                bulk_copy_g2s(stage + m * lay.mat_bytes() + r * lay.row_stride(),
+                              mp.W + (size_t)(iss.tile * kTileRows + r) * row_bytes, row_bytes, mbar);
+            }
+            if (lane >= 16 && lane < 16 + NMAT * 2) {
+                const uint32_t j = lane - 16, m = j >> 1, which = j & 1;
+                const MatPlanes& mp = m ? iss.pl[NMAT - 1] : iss.pl[0];
+                const uint16_t* plane = which ? mp.B : mp.S;
+                bulk_copy_g2s(stage + lay.off_sb_in_stage() + j * plane_bytes, plane + (size_t)iss.tile * kTileRows * ng,
+                              plane_bytes, mbar);
+            }
+            ++issued;
+            if (li + 1 < n_items) advance(iss);
+        }
+        if (fail) {
+            if (lane == 0) atomicCAS(args.error, 0u, fail);
+            // let the copies already issued land before the CTA's shared memory goes away (bounded)
+            for (uint32_t st = 0; st < (uint32_t)kWStages && st < issued; ++st)
+                for (uint32_t par = 0; par < 2; ++par) mbar_wait(bar_full(st), par);
+        }
+    } else {
+        // =========================== reducer warp q ===========================
+        // Reducer q handles the items of parity q (and with them partial buffer q and scale stages q, q + 2).
+        const uint32_t q = warp - cw;
+        ItemCursor<NMAT> cur;
+        cur.chunk = item_begin / tiles;
+        cur.tile = item_begin % tiles;
+        resolve_chunk<NMAT, DENSE>(args, cur);
+        if (q < n_items) advance_by(cur, q);
+        uint32_t fail = 0;
+        const uint32_t tok = lane >> 1, row4 = (lane & 1) * 4;      // this lane sums 4 consecutive rows of one token
+        const uint32_t red_q = red_base + q * lay.red_stage_bytes() + lane * 16;
+        uint32_t pair_chunk = 0xFFFFFFFFu;
+        tf_pair pr = tf_pair{0u, 0u, 0u, 0u};
+        for (uint32_t li = q; li < n_items; li += kReducers) {
+            const uint32_t ruse = li / kRedStages;
+            if (OUT_MODE == kOutPartialF16 || OUT_MODE == kOutPartialF32) {
+                if (cur.chunk != pair_chunk) {       // the pair of a token is the same for every tile of the chunk
+                    pair_chunk = cur.chunk;
+                    if (tok < cur.ntok) pr = args.sorted_pairs[cur.row_base + tok];
+                }
+            }
+            if (!mbar_wait(bar_part_full(q), ruse & 1)) { fail = kErrTimeoutPartials; break; }
+            float4 acc[NMAT];
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+                // independent loads first, then the sum in warp order (deterministic)
+                float4 v[kMaxComputeWarps];
+#pragma unroll
+                for (int w2 = 0; w2 < kMaxComputeWarps; ++w2)
+                    v[w2] = (uint32_t)w2 < cw ? lds_f32x4(red_q + (w2 * NMAT + m) * 512) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                acc[m] = v[0];
+#pragma unroll
+                for (int w2 = 1; w2 < kMaxComputeWarps; ++w2) {
+                    if ((uint32_t)w2 < cw) { acc[m].x += v[w2].x; acc[m].y += v[w2].y; acc[m].z += v[w2].z; acc[m].w += v[w2].w; }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_red_free(q));
+            if (tok < cur.ntok) {
+                const uint32_t out_row = cur.tile * kTileRows + row4;
+                if constexpr (OUT_MODE == kOutActs) {
+                    float gt[4] = {acc[0].x, acc[0].y, acc[0].z, acc[0].w};
+                    float up[4] = {acc[NMAT - 1].x, acc[NMAT - 1].y, acc[NMAT - 1].z, acc[NMAT - 1].w};
+                    uint32_t o[2];
+#pragma unroll
+                    for (int j = 0; j < 2; ++j) {
+                        float g0v = gt[2 * j], g1v = gt[2 * j + 1], u0 = up[2 * j], u1 = up[2 * j + 1];
+                        if constexpr (DENSE) {
+                            // shared expert: gate and up are stored as fp16 before the activation
+                            // (Kernels/MoE/SharedExpertInt4.swift:62-93; Metal/Primitives/utility.metal:15-17)
+                            g0v = __half2float(__float2half_rn(g0v)); g1v = __half2float(__float2half_rn(g1v));
+                            u0 = __half2float(__float2half_rn(u0)); u1 = __half2float(__float2half_rn(u1));
+                        }
+                        // routed: act = half(gelu_tanh(gate) * up), gate and up in fp32 (prefill.metal:634-636; moe.metal:368)
+                        const __half2 h = __floats2half2_rn(gelu_tanh(g0v) * u0, gelu_tanh(g1v) * u1);
+                        o[j] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                    *reinterpret_cast<uint2*>(static_cast<uint16_t*>(args.out) + (size_t)(cur.row_base + tok) * args.out_stride + out_row) =
+                        make_uint2(o[0], o[1]);
+                } else if constexpr (OUT_MODE == kOutDenseF16) {
+                    const __half2 h0 = __floats2half2_rn(acc[0].x, acc[0].y), h1 = __floats2half2_rn(acc[0].z, acc[0].w);
+                    *reinterpret_cast<uint2*>(static_cast<uint16_t*>(args.out) + (size_t)(cur.row_base + tok) * args.out_stride + out_row) =
+                        make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+                } else {
+                    const size_t idx = ((size_t)pr.token * args.top_k + pr.rank) * args.out_stride + out_row;
+                    if constexpr (OUT_MODE == kOutPartialF16) {       // prefill.metal:666-669
+                        const __half2 h0 = __floats2half2_rn(acc[0].x, acc[0].y), h1 = __floats2half2_rn(acc[0].z, acc[0].w);
+                        *reinterpret_cast<uint2*>(static_cast<uint16_t*>(args.out) + idx) =
+                            make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+                    } else {
+                        *reinterpret_cast<float4*>(static_cast<float*>(args.out) + idx) = acc[0];
+                    }
+                }
+            }
+            if (li + kReducers < n_items) advance_by(cur, kReducers);
+        }
+        if (fail && lane == 0) atomicCAS(args.error, 0u, fail);
     }
 }
 
@@ -592,38 +682,36 @@ __global__ void reduce_token_major_kernel(const void* __restrict__ partials, con
     out[(size_t)t * out_stride + d] = __half_as_ushort(__float2half_rn(acc));
 }
 
-// Picks the K split: enough warp-tiles to occupy every warp of every CTA a few times over.
-static uint32_t choose_ksplit(uint64_t expected_items, uint32_t sm_count, uint32_t ng) {
-    uint32_t ks = 1;
-    const uint32_t steps = (ng + kStep - 1) / kStep;
-    while (ks < (uint32_t)kMaxKSplit && ks * 2 <= steps && expected_items * ks < (uint64_t)sm_count * kStreamWarps * 3) ks *= 2;
-    return ks;
-}
-
 template <int NMAT, bool DENSE, int OUT_MODE>
-static tf_status launch_grouped(tf_context* ctx, void* stream, GroupedArgs& args, uint64_t expected_chunks, const char* name) {
+static tf_status launch_grouped(tf_context* ctx, void* stream, GroupedArgs& args, const char* name) {
     const uint32_t ng = args.k / kGroup;
     TF_REQUIRE(ctx, ng >= 1 && args.k % kGroup == 0, TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);
+    const uint32_t cw = (ng + kGPW - 1) / kGPW;
+    TF_REQUIRE(ctx, cw <= (uint32_t)kMaxComputeWarps, TF_ERR_UNSUPPORTED, "%s: K=%u outside the supported range (64..3072)", name, args.k);
     TF_REQUIRE(ctx, args.rows % kTileRows == 0, TF_ERR_UNSUPPORTED, "%s: row count %u must be a multiple of 8", name, args.rows);
-    const size_t smem = stream_smem_bytes(ng, NMAT);
+    const KSplitSmem<NMAT> lay{cw, ng, args.k / 2};
+    const size_t smem = lay.total();
     TF_REQUIRE(ctx, smem <= 200 * 1024, TF_ERR_UNSUPPORTED, "%s: K=%u needs %zu bytes of shared memory (limit 200 KB)", name, args.k, smem);
-    auto kern = grouped_stream_kernel<NMAT, DENSE, OUT_MODE>;
-    // The attribute is set once per instantiation, so steady-state calls are a bare launch
-    // (and safe inside stream capture).
-    static bool configured = false;
-    if (!configured) {
+    auto kern = grouped_ksplit_kernel<NMAT, DENSE, OUT_MODE>;
+    // Attribute and occupancy are queried once per (instantiation, warp count) and cached, so
+    // steady-state calls are a bare launch (and safe inside stream capture).
+    static int cached_per_sm[kMaxComputeWarps + 1] = {0};
+    int per_sm = cached_per_sm[cw];
+    if (per_sm == 0) {
         TF_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        configured = true;
+        TF_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, (int)((cw + kExtraWarps) * kWarp), smem));
+        if (per_sm < 1) per_sm = 1;
+        if (per_sm > 8) per_sm = 8;
+        cached_per_sm[cw] = per_sm;
     }
-    const uint64_t items = expected_chunks * (args.rows / kTileRows);
-    args.ks = choose_ksplit(items, (uint32_t)ctx->sm_count, ng);
-    uint32_t grid = (uint32_t)ctx->sm_count;
+    args.error = ctx->device_error;
+    uint32_t grid = (uint32_t)ctx->sm_count * (uint32_t)per_sm;
     if (DENSE) {
+        const uint64_t items = (uint64_t)((args.dense_tokens + kChunkTokens - 1) / kChunkTokens) * (args.rows / kTileRows);
         if (items == 0) return TF_OK;
-        const uint64_t want = (items * args.ks + kStreamWarps - 1) / kStreamWarps;
-        if (want < grid) grid = (uint32_t)want;
+        if (items < grid) grid = (uint32_t)items;
     }
-    kern<<<grid, kStreamThreads, smem, static_cast<cudaStream_t>(stream)>>>(args);
+    kern<<<grid, (cw + kExtraWarps) * kWarp, smem, static_cast<cudaStream_t>(stream)>>>(args);
     return check_launch(ctx, name);
 }
 
@@ -677,11 +765,6 @@ tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream, const void* hidd
     TF_REQUIRE(ctx, tf::aligned(hp, 16) && (hidden_stride_elements * 2) % 16 == 0 && tf::aligned(acts_scratch, 16),
                TF_ERR_ALIGNMENT, "%s: hidden rows and acts scratch must be 16-byte aligned", name);
     if (query_count == 0) return TF_OK;
-    // The chunk count lives on the device; the K split only needs its order of magnitude:
-    // every pair its own expert (at most num pairs, bounded by the pool) or 8 pairs per chunk.
-    const uint64_t pairs = (uint64_t)query_count * top_k;
-    const uint64_t expected_chunks = pairs < 1024 ? pairs : pairs / tf::kChunkTokens;
-
     tf::GroupedArgs a{};
     a.pool_base = static_cast<const uint8_t*>(pool_layer_base);
     a.expert_stride = expert_stride;
@@ -691,7 +774,7 @@ tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream, const void* hidd
     a.chunk_start = routes->chunk_start; a.counters = routes->counters;
     a.x = reinterpret_cast<const uint16_t*>(hp); a.x_stride = hidden_stride_elements;
     a.out = acts_scratch; a.out_stride = f; a.rows = f; a.k = d; a.top_k = top_k;
-    tf_status s = tf::launch_grouped<2, false, tf::kOutActs>(ctx, stream, a, expected_chunks, "tf_grouped_moe_batched(gate/up)");
+    tf_status s = tf::launch_grouped<2, false, tf::kOutActs>(ctx, stream, a, "tf_grouped_moe_batched(gate/up)");
     if (s) return s;
 
     tf::GroupedArgs b{};
@@ -701,8 +784,8 @@ tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream, const void* hidd
     b.chunk_start = routes->chunk_start; b.counters = routes->counters;
     b.x = static_cast<const uint16_t*>(acts_scratch); b.x_stride = f;
     b.out = route_partials; b.out_stride = d; b.rows = d; b.k = f; b.top_k = top_k;
-    if (partials_f32) return tf::launch_grouped<1, false, tf::kOutPartialF32>(ctx, stream, b, expected_chunks, "tf_grouped_moe_batched(down)");
-    return tf::launch_grouped<1, false, tf::kOutPartialF16>(ctx, stream, b, expected_chunks, "tf_grouped_moe_batched(down)");
+    if (partials_f32) return tf::launch_grouped<1, false, tf::kOutPartialF32>(ctx, stream, b, "tf_grouped_moe_batched(down)");
+    return tf::launch_grouped<1, false, tf::kOutPartialF16>(ctx, stream, b, "tf_grouped_moe_batched(down)");
 }
 
 tf_status tf_moe_reduce_token_major(tf_context* ctx, void* stream, const void* route_partials, int partials_f32,
@@ -757,13 +840,13 @@ tf_status tf_shared_expert_int4_block(tf_context* ctx, void* stream, const void*
     a.dense[0] = mp[0]; a.dense[1] = mp[1];
     a.x = reinterpret_cast<const uint16_t*>(xp); a.x_stride = x_stride_elements;
     a.out = scratch_act; a.out_stride = fs; a.rows = fs; a.k = d; a.dense_tokens = rows;
-    tf_status s = tf::launch_grouped<2, true, tf::kOutActs>(ctx, stream, a, (rows + tf::kChunkTokens - 1) / tf::kChunkTokens, "tf_shared_expert_int4_block(gate/up)");
+    tf_status s = tf::launch_grouped<2, true, tf::kOutActs>(ctx, stream, a, "tf_shared_expert_int4_block(gate/up)");
     if (s) return s;
     tf::GroupedArgs b{};
     b.dense[0] = mp[2];
     b.x = static_cast<const uint16_t*>(scratch_act); b.x_stride = fs;
     b.out = tf::byte_ptr(y, y_off); b.out_stride = y_stride_elements; b.rows = d; b.k = fs; b.dense_tokens = rows;
-    return tf::launch_grouped<1, true, tf::kOutDenseF16>(ctx, stream, b, (rows + tf::kChunkTokens - 1) / tf::kChunkTokens, "tf_shared_expert_int4_block(down)");
+    return tf::launch_grouped<1, true, tf::kOutDenseF16>(ctx, stream, b, "tf_shared_expert_int4_block(down)");
 }
 
 }  // extern "C"

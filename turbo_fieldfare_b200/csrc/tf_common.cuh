@@ -38,6 +38,8 @@ struct tf_context {
     // reference's MoE wrapper owns (Kernels/MoE/MoE.swift:92-106).
     float* router_logits = nullptr;        // [kRouterSplitRows, 256]
     unsigned int* router_tickets = nullptr;  // [kRouterSplitRows], self-resetting
+    // One device word that kernels with bounded waits set when a wait gives up (0 = healthy).
+    uint32_t* device_error = nullptr;
 };
 
 namespace tf {
@@ -83,11 +85,15 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // tanh GELU with the inner argument clamped to +-20 (Metal/MoE/moe.metal:53-60).
+// tanh(u) = 1 - 2 / (exp(2u) + 1) with the hardware exp2: relative error about 1e-6, far below
+// the fp16 rounding of the activation, at a fraction of tanhf's instruction count.
 __device__ __forceinline__ float gelu_tanh(float x) {
     const float x3 = x * x * x;
     float inner = 0.7978845608028654f * (x + 0.044715f * x3);
     inner = fminf(fmaxf(inner, -20.0f), 20.0f);
-    return 0.5f * x * (1.0f + tanhf(inner));
+    const float e = __expf(2.0f * inner);
+    const float th = 1.0f - __fdividef(2.0f, e + 1.0f);
+    return 0.5f * x * (1.0f + th);
 }
 
 __device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {

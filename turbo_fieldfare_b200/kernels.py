@@ -61,6 +61,12 @@ class TurboContext:
         if status != 0:
             raise TFError(status, self.lib.tf_last_error(self.handle).decode())
 
+    def device_status(self) -> int:
+        """Synchronise and return the device error word (0 = healthy); raises TFError when a kernel gave up a wait."""
+        code = C.c_uint32(0)
+        self.check(self.lib.tf_device_status(self.handle, C.byref(code)))
+        return int(code.value)
+
     @property
     def launch_count(self) -> int:
         return int(self.lib.tf_launch_count(self.handle))
