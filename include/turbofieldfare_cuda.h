@@ -101,8 +101,8 @@ typedef struct tf_tile { uint32_t group_start, group_count, pair_start, pair_cou
 /* Device-resident routing metadata produced by tf_group_routes_device and
  * consumed by tf_grouped_moe_batched. All pointers are DEVICE buffers the
  * caller owns: sorted_pairs [T*K]; per_expert_offsets, per_expert_counts,
- * groups, chunk_start [E]; chunk_group [T*K/16 + E]; counters [4] =
- * {group count, chunk count, pair count, reserved}. A chunk is up to 16
+ * groups, chunk_start [E]; chunk_group [T*K/8 + E]; counters [4] =
+ * {group count, chunk count, pair count, reserved}. A chunk is up to 8
  * consecutive sorted pairs of one expert (one pass of the grouped kernels).
  * Replaces PrefillMoEGroupedRoutes (PrefillMoEGrouping.swift:33-50), which the
  * reference builds on the CPU after reading the router output back. */
@@ -278,7 +278,7 @@ tf_status tf_moe_reduce_token_major(tf_context* ctx, void* stream,
                                     const void* residual, uint32_t residual_stride_elements,
                                     void* h2, uint32_t h2_stride_elements,
                                     uint32_t query_count, uint32_t top_k, uint32_t d);
-/* Shared expert for `rows` tokens at once (weights read from HBM once; one pass per 16 tokens).
+/* Shared expert for `rows` tokens at once (weights read from HBM once; one pass per 8 tokens).
  * Replaces PrefillSharedExpert.encodeBlock (Kernels/Prefill/MoE/PrefillSharedExpert.swift:11-59),
  * which loops SharedExpertInt4.encode over the rows. scratch_act: [rows, gate.rows] fp16. */
 tf_status tf_shared_expert_int4_block(tf_context* ctx, void* stream,

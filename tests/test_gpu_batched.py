@@ -41,7 +41,7 @@ def test_device_grouping_matches_oracle(tf_ctx, oracle, T, K, E, zipf):
     assert got.groups.tobytes() == ref.groups.tobytes()
     counters = routes.counters.cpu().numpy().view(np.uint32)
     assert counters[0] == len(ref.groups) and counters[2] == T * K
-    assert counters[1] == sum((int(c) + 15) // 16 for c in ref.per_expert_counts)
+    assert counters[1] == sum((int(c) + 7) // 8 for c in ref.per_expert_counts)
 
 
 def _closed_form_pool(o, E, D, F):
@@ -99,7 +99,7 @@ def test_grouped_moe_closed_form_fixture(tf_ctx, oracle):
 
 @pytest.mark.parametrize("T,D,F,E,K", [(1, 128, 64, 16, 8), (5, 128, 64, 16, 8), (40, 256, 128, 8, 4), (64, 2816, 704, 16, 8)])
 def test_grouped_moe_random_vs_oracle(tf_ctx, oracle, T, D, F, E, K):
-    """Config-2 style: T tokens scattered over E experts (up to 64 x 8 pairs on 16 experts: chunks of 16 and ragged tails)."""
+    """Config-2 style: T tokens scattered over E experts (up to 64 x 8 pairs on 16 experts: chunks of 8 and ragged tails)."""
     o = oracle
     rng = np.random.default_rng(T + D)
     off, payload, stride = o.blob_layout(D, F, align=256 if D < 2816 else 16384)

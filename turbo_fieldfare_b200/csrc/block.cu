@@ -250,7 +250,7 @@ tf_status tf_workspace_create(tf_context* ctx, uint32_t max_tokens, uint32_t d, 
     uint64_t off = 0;
     auto take = [&](uint64_t bytes) { uint64_t o = off; off += up(bytes); return o; };
     const uint64_t o_idx = take(T * K * 4), o_w = take(T * K * 2), o_pairs = take(T * K * 16), o_eoff = take(E * 4),
-                   o_ecnt = take(E * 4), o_groups = take(E * 12), o_cgroup = take((T * K / 16 + E + 1) * 4),
+                   o_ecnt = take(E * 4), o_groups = take(E * 12), o_cgroup = take((T * K / 8 + E + 1) * 4),
                    o_cstart = take(E * 4), o_counters = take(16), o_acts = take(T * K * f * 2),
                    o_partials = take(T * K * d * (T <= tf::kF32PartialTokens ? 4 : 2)), o_sact = take(T * fs * 2),
                    o_sy = take(T * d * 2), o_xn = take(T * d * 2), o_yb = take(T * d * 2);

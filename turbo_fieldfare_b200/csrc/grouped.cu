@@ -9,8 +9,9 @@
 //     (Metal/MoE/moe.metal:248-482);
 //   - the per-row shared-expert loop (Kernels/Prefill/MoE/PrefillSharedExpert.swift:11-59).
 //
-// Kernel design (memory-bound; HBM roofline): weights are the B operand of
-// mma.sync.m16n8k16 (8 weight rows per tile), up to 16 tokens are the A operand.
+// Kernel design (memory-bound; HBM roofline): weights are the A operand of
+// mma.sync.m16n8k16 (16 weight rows per tile), up to 8 tokens are the B operand
+// (decode-sized batches put few tokens on an expert, so the tokens take the narrow side).
 // A 4-bit code q placed in the low mantissa bits of an fp16 IS the subnormal
 // q * 2^-24, so "dequantisation" is one AND per two codes and the tensor core
 // multiplies exact integers by fp16 activations with fp32 accumulation. Scale
@@ -19,8 +20,8 @@
 // i.e. the reference's group factoring (Metal/Quant/dequant_int4.metal:14-19).
 //
 // A CTA is K-split: compute warp w owns columns [256 w, 256 w + 256) and keeps the
-// activations of the current chunk (<= 16 tokens of one expert) for those columns in
-// registers, already in MMA fragment order. A loader warp streams whole 8-row tiles
+// activations of the current chunk (<= 8 tokens of one expert) for those columns in
+// registers, already in MMA fragment order. A loader warp streams whole 16-row tiles
 // (packed codes of every matrix plus their scale/bias rows) into a shared ring with
 // bulk asynchronous copies (cp.async.bulk, one full row or one contiguous tile per
 // copy, mbarrier completion; rows are padded so that the fragment loads are free of
@@ -39,9 +40,9 @@ namespace tf {
 
 constexpr int kGroupThreads = 256;
 constexpr int kGroupPerThread = 4;
-constexpr int kChunkTokens = 16;      // tokens per work chunk of the grouped kernels (the m of m16n8k16)
+constexpr int kChunkTokens = 8;       // tokens per work chunk of the grouped kernels (the n of m16n8k16)
 
-// counters: [0] group count, [1] total chunks (sum over groups of ceil(count/16)), [2] pair count
+// counters: [0] group count, [1] total chunks (sum over groups of ceil(count/8)), [2] pair count
 __global__ void __launch_bounds__(kGroupThreads)
 group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __restrict__ weights,
                     uint32_t T, uint32_t K, uint32_t E,
@@ -133,10 +134,10 @@ group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __rest
 // ---------------------------------------------------------------------------
 
 constexpr int kGPW = 4;                 // 64-column groups per compute warp
-constexpr int kWStages = 4;             // ring depth (items) of the packed-code and scale rings
+constexpr int kWStages = 3;             // ring depth (items) of the tile ring (codes + scales)
 constexpr int kReducers = 2;            // reducer warps; reducer q owns the items and the partial buffer of parity q
 constexpr int kRedStages = kReducers;   // partial-sum buffers
-constexpr int kTileRows = 8;            // weight rows per MMA tile (the n of m16n8k16)
+constexpr int kTileRows = 16;           // weight rows per MMA tile (the m of m16n8k16)
 constexpr int kMaxComputeWarps = 12;    // K <= 12 * 256 = 3072 columns
 constexpr uint32_t kSpinLimit = 1u << 21;
 constexpr uint32_t kErrTimeoutCodes = 0x7F000001u;   // device error words
@@ -179,17 +180,17 @@ struct GroupedArgs {
     uint32_t* error;           // device word: 0, or the code of the wait that gave up
 };
 
-// D = A * B + C with C either the constant zero (first MMA of a group) or D itself. The four A
-// registers and the four accumulators are always real fragments (tokens g and g + 8).
-__device__ __forceinline__ void mma16816_first(float (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+// D = A * B + C with C either the constant zero (first MMA of a group) or D itself.
+// A = codes of weight rows g (a0, a2) and g + 8 (a1, a3); B = activations of token g.
+__device__ __forceinline__ void mma16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, const uint2& b) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
                  : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1), "f"(0.0f));
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y), "f"(0.0f));
 }
-__device__ __forceinline__ void mma16816_acc(float (&c)[4], const uint4& a, uint32_t b0, uint32_t b1) {
+__device__ __forceinline__ void mma16816_acc(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, const uint2& b) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y));
 }
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
@@ -366,63 +367,56 @@ grouped_ksplit_kernel(const GroupedArgs args) {
         const uint32_t g0 = warp * kGPW;
         const uint32_t ngw = ng - g0 < (uint32_t)kGPW ? ng - g0 : (uint32_t)kGPW;     // g0 < ng by construction
         const bool sb_vec = (ng % 4) == 0;
-        const uint32_t sb_row0 = ((2 * t) * ng + g0) * 2, sb_row1 = ((2 * t + 1) * ng + g0) * 2;
-        const uint32_t lane_code_off = g * lay.row_stride() + g0 * 32 + t * 8;          // this lane's codes within a matrix tile
+        const uint32_t sb_row0 = (g * ng + g0) * 2, sb_row1 = ((g + 8) * ng + g0) * 2;     // scale rows of weight rows g, g + 8
+        const uint32_t lane_code_off = g * lay.row_stride() + g0 * 32 + t * 8;          // this lane's codes of row g within a matrix tile
+        const uint32_t row8_off = 8 * lay.row_stride();                                 // row g + 8
 
         ItemCursor<NMAT> cur;
         cur.chunk = item_begin / tiles;
         cur.tile = item_begin % tiles;
         resolve_chunk<NMAT, DENSE>(args, cur);
 
-        uint4 xa[kGPW][4];
-        float2 xsum[kGPW];
+        uint2 xb[kGPW][4];          // B fragments of token g: [group][MMA j] = {b0, b1}
+        float2 xsum[kGPW];          // fp32 sums of the 64 activations of the group for tokens 2t and 2t + 1
         uint32_t loaded_chunk = 0xFFFFFFFFu;
         uint32_t fail = 0;
 
         for (uint32_t li = 0; li < n_items; ++li) {
             const uint32_t st = li % kWStages, use = li / kWStages;
             if (cur.chunk != loaded_chunk) {
-                // activations of this warp's columns for the chunk's tokens g and g + 8, in MMA operand order:
-                // the 16 values x0..x15 at columns 64 G + 16 t feed four MMAs,
+                // activations of this warp's columns for the chunk's token g, in MMA operand order: the 16 values
+                // x0..x15 at columns 64 G + 16 t feed four MMAs,
                 //   j = 0: (x0,x4),(x2,x6)   j = 1: (x1,x5)/16,(x3,x7)/16   j = 2, 3: the same for x8..x15;
                 // odd columns are pre-scaled by 1/16 because their codes sit four mantissa bits higher.
                 loaded_chunk = cur.chunk;
 #pragma unroll
                 for (int i = 0; i < kGPW; ++i) {
-                    uint32_t r[2][8];
+                    uint32_t r[8];
+                    if ((uint32_t)i < ngw && (uint32_t)g < cur.ntok) {
+                        const uint32_t rr = (DENSE || NMAT == 1) ? cur.row_base + g : args.sorted_pairs[cur.row_base + g].token;
+                        const uint4* p = reinterpret_cast<const uint4*>(args.x + (size_t)rr * args.x_stride + (g0 + i) * kGroup + t * 16);
+                        const uint4 lo = __ldg(p), hi = __ldg(p + 1);
+                        r[0] = lo.x; r[1] = lo.y; r[2] = lo.z; r[3] = lo.w;
+                        r[4] = hi.x; r[5] = hi.y; r[6] = hi.z; r[7] = hi.w;
+                    } else {
 #pragma unroll
-                    for (int hh = 0; hh < 2; ++hh) {
-                        const uint32_t tok = g + 8 * hh;
-                        if ((uint32_t)i < ngw && tok < cur.ntok) {
-                            const uint32_t rr = (DENSE || NMAT == 1) ? cur.row_base + tok : args.sorted_pairs[cur.row_base + tok].token;
-                            const uint4* p = reinterpret_cast<const uint4*>(args.x + (size_t)rr * args.x_stride + (g0 + i) * kGroup + t * 16);
-                            const uint4 lo = __ldg(p), hi = __ldg(p + 1);
-                            r[hh][0] = lo.x; r[hh][1] = lo.y; r[hh][2] = lo.z; r[hh][3] = lo.w;
-                            r[hh][4] = hi.x; r[hh][5] = hi.y; r[hh][6] = hi.z; r[hh][7] = hi.w;
-                        } else {
-#pragma unroll
-                            for (int q = 0; q < 8; ++q) r[hh][q] = 0;
-                        }
+                        for (int q = 0; q < 8; ++q) r[q] = 0;
                     }
-                    float s0 = 0.0f, s1 = 0.0f;
+                    float sum = 0.0f;
 #pragma unroll
                     for (int q = 0; q < 8; ++q) {
-                        const float2 v0 = __half22float2(*reinterpret_cast<const __half2*>(&r[0][q]));
-                        const float2 v1 = __half22float2(*reinterpret_cast<const __half2*>(&r[1][q]));
-                        s0 += v0.x + v0.y; s1 += v1.x + v1.y;
+                        const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&r[q]));
+                        sum += v.x + v.y;
                     }
-                    s0 += __shfl_xor_sync(kFullMask, s0, 1); s0 += __shfl_xor_sync(kFullMask, s0, 2);
-                    s1 += __shfl_xor_sync(kFullMask, s1, 1); s1 += __shfl_xor_sync(kFullMask, s1, 2);
-                    xsum[i] = make_float2(s0, s1);
+                    sum += __shfl_xor_sync(kFullMask, sum, 1);
+                    sum += __shfl_xor_sync(kFullMask, sum, 2);        // every lane of quad g holds token g's group sum
+                    xsum[i] = make_float2(__shfl_sync(kFullMask, sum, 8 * t), __shfl_sync(kFullMask, sum, 8 * t + 4));
 #pragma unroll
                     for (int h2 = 0; h2 < 2; ++h2) {
                         const int o = 4 * h2;
-                        xa[i][2 * h2] = make_uint4(prmt(r[0][o], r[0][o + 2], 0x5410), prmt(r[1][o], r[1][o + 2], 0x5410),
-                                                   prmt(r[0][o + 1], r[0][o + 3], 0x5410), prmt(r[1][o + 1], r[1][o + 3], 0x5410));
-                        xa[i][2 * h2 + 1] = make_uint4(hmul2_sixteenth(prmt(r[0][o], r[0][o + 2], 0x7632)),
-                                                       hmul2_sixteenth(prmt(r[1][o], r[1][o + 2], 0x7632)),
-                                                       hmul2_sixteenth(prmt(r[0][o + 1], r[0][o + 3], 0x7632)),
-                                                       hmul2_sixteenth(prmt(r[1][o + 1], r[1][o + 3], 0x7632)));
+                        xb[i][2 * h2] = make_uint2(prmt(r[o], r[o + 2], 0x5410), prmt(r[o + 1], r[o + 3], 0x5410));
+                        xb[i][2 * h2 + 1] = make_uint2(hmul2_sixteenth(prmt(r[o], r[o + 2], 0x7632)),
+                                                       hmul2_sixteenth(prmt(r[o + 1], r[o + 3], 0x7632)));
                     }
                 }
             }
@@ -433,33 +427,44 @@ grouped_ksplit_kernel(const GroupedArgs args) {
             // All codes of the item first, then the MMAs interleaved over the (matrix, group) pairs: the four
             // MMAs of one group form a dependent chain through its accumulator, so consecutive instructions
             // always belong to different chains and the tensor pipe stays full.
-            uint2 wv[NMAT][kGPW];
+            uint2 wa[NMAT][kGPW], wb[NMAT][kGPW];          // codes of rows g and g + 8
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
 #pragma unroll
-                for (int i = 0; i < kGPW; ++i)
-                    wv[m][i] = (uint32_t)i < ngw ? lds64(ring_item + m * lay.mat_bytes() + i * 32) : make_uint2(0u, 0u);
+                for (int i = 0; i < kGPW; ++i) {
+                    const bool v = (uint32_t)i < ngw;
+                    wa[m][i] = v ? lds64(ring_item + m * lay.mat_bytes() + i * 32) : make_uint2(0u, 0u);
+                    wb[m][i] = v ? lds64(ring_item + m * lay.mat_bytes() + row8_off + i * 32) : make_uint2(0u, 0u);
+                }
             }
             float c[NMAT][kGPW][4];
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
 #pragma unroll
-                for (int i = 0; i < kGPW; ++i) mma16816_first(c[m][i], xa[i][0], wv[m][i].x & 0x000F000Fu, (wv[m][i].x >> 8) & 0x000F000Fu);
+                for (int i = 0; i < kGPW; ++i)
+                    mma16816_first(c[m][i], wa[m][i].x & 0x000F000Fu, wb[m][i].x & 0x000F000Fu,
+                                   (wa[m][i].x >> 8) & 0x000F000Fu, (wb[m][i].x >> 8) & 0x000F000Fu, xb[i][0]);
             }
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
 #pragma unroll
-                for (int i = 0; i < kGPW; ++i) mma16816_acc(c[m][i], xa[i][1], wv[m][i].x & 0x00F000F0u, (wv[m][i].x >> 8) & 0x00F000F0u);
+                for (int i = 0; i < kGPW; ++i)
+                    mma16816_acc(c[m][i], wa[m][i].x & 0x00F000F0u, wb[m][i].x & 0x00F000F0u,
+                                 (wa[m][i].x >> 8) & 0x00F000F0u, (wb[m][i].x >> 8) & 0x00F000F0u, xb[i][1]);
             }
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
 #pragma unroll
-                for (int i = 0; i < kGPW; ++i) mma16816_acc(c[m][i], xa[i][2], wv[m][i].y & 0x000F000Fu, (wv[m][i].y >> 8) & 0x000F000Fu);
+                for (int i = 0; i < kGPW; ++i)
+                    mma16816_acc(c[m][i], wa[m][i].y & 0x000F000Fu, wb[m][i].y & 0x000F000Fu,
+                                 (wa[m][i].y >> 8) & 0x000F000Fu, (wb[m][i].y >> 8) & 0x000F000Fu, xb[i][2]);
             }
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
 #pragma unroll
-                for (int i = 0; i < kGPW; ++i) mma16816_acc(c[m][i], xa[i][3], wv[m][i].y & 0x00F000F0u, (wv[m][i].y >> 8) & 0x00F000F0u);
+                for (int i = 0; i < kGPW; ++i)
+                    mma16816_acc(c[m][i], wa[m][i].y & 0x00F000F0u, wb[m][i].y & 0x00F000F0u,
+                                 (wa[m][i].y >> 8) & 0x00F000F0u, (wb[m][i].y >> 8) & 0x00F000F0u, xb[i][3]);
             }
             float y[NMAT][4];
 #pragma unroll
@@ -492,10 +497,10 @@ grouped_ksplit_kernel(const GroupedArgs args) {
                     const float s0 = (i & 1) ? bf16_hi_x2p24(sv0) : bf16_lo_x2p24(sv0);
                     const float s1 = (i & 1) ? bf16_hi_x2p24(sv1) : bf16_lo_x2p24(sv1);
                     const float b0 = (i & 1) ? bf16_hi(bv0) : bf16_lo(bv0), b1 = (i & 1) ? bf16_hi(bv1) : bf16_lo(bv1);
-                    // c0, c1: token g, rows 2t, 2t+1; c2, c3: token g + 8
+                    // c0, c1: weight row g, tokens 2t, 2t+1; c2, c3: weight row g + 8 (scale words 0 / 1)
                     acc[0] = fmaf(s0, c[m][i][0], fmaf(b0, xsum[i].x, acc[0]));
-                    acc[1] = fmaf(s1, c[m][i][1], fmaf(b1, xsum[i].x, acc[1]));
-                    acc[2] = fmaf(s0, c[m][i][2], fmaf(b0, xsum[i].y, acc[2]));
+                    acc[1] = fmaf(s0, c[m][i][1], fmaf(b0, xsum[i].y, acc[1]));
+                    acc[2] = fmaf(s1, c[m][i][2], fmaf(b1, xsum[i].x, acc[2]));
                     acc[3] = fmaf(s1, c[m][i][3], fmaf(b1, xsum[i].y, acc[3]));
                 }
 #pragma unroll
@@ -511,7 +516,7 @@ grouped_ksplit_kernel(const GroupedArgs args) {
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
                 sts_f32x2(red_w + m * 512, y[m][0], y[m][1]);
-                sts_f32x2(red_w + m * 512 + 256, y[m][2], y[m][3]);      // token g + 8: index (g + 8) * 8 + 2t
+                sts_f32x2(red_w + m * 512 + 256, y[m][2], y[m][3]);      // weight row g + 8: index (g + 8) * 8 + 2t
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_part_full(r));
@@ -544,17 +549,19 @@ grouped_ksplit_kernel(const GroupedArgs args) {
                     bulk_copy_g2s(stage + lane * lay.mat_bytes(), mp.W + (size_t)iss.tile * kTileRows * row_bytes,
                                   kTileRows * row_bytes, mbar);
                 }
-            } else if (lane < NMAT * kTileRows) {
-                const uint32_t m = lane / kTileRows, r = lane % kTileRows;
-                const MatPlanes& mp = m ? iss.pl[NMAT - 1] : iss.pl[0];
-                bulk_copy_g2s(stage + m * lay.mat_bytes() + r * lay.row_stride(),
-                              mp.W + (size_t)(iss.tile * kTileRows + r) * row_bytes, row_bytes, mbar);
+            } else {
+                for (uint32_t j = lane; j < (uint32_t)(NMAT * kTileRows); j += kWarp) {
+                    const uint32_t m = j / kTileRows, r = j % kTileRows;
+                    const MatPlanes& mp = m ? iss.pl[NMAT - 1] : iss.pl[0];
+                    bulk_copy_g2s(stage + m * lay.mat_bytes() + r * lay.row_stride(),
+                                  mp.W + (size_t)(iss.tile * kTileRows + r) * row_bytes, row_bytes, mbar);
+                }
             }
-            if (lane >= 16 && lane < 16 + NMAT * 2) {
-                const uint32_t j = lane - 16, m = j >> 1, which = j & 1;
+            if (lane < NMAT * 2) {
+                const uint32_t m = lane >> 1, which = lane & 1;
                 const MatPlanes& mp = m ? iss.pl[NMAT - 1] : iss.pl[0];
                 const uint16_t* plane = which ? mp.B : mp.S;
-                bulk_copy_g2s(stage + lay.off_sb_in_stage() + j * plane_bytes, plane + (size_t)iss.tile * kTileRows * ng,
+                bulk_copy_g2s(stage + lay.off_sb_in_stage() + lane * plane_bytes, plane + (size_t)iss.tile * kTileRows * ng,
                               plane_bytes, mbar);
             }
             ++issued;
@@ -576,16 +583,22 @@ grouped_ksplit_kernel(const GroupedArgs args) {
         resolve_chunk<NMAT, DENSE>(args, cur);
         if (q < n_items) advance_by(cur, q);
         uint32_t fail = 0;
-        const uint32_t tok = lane >> 1, row4 = (lane & 1) * 4;      // this lane sums 4 consecutive rows of one token
+        const uint32_t row = lane >> 1, tok4 = (lane & 1) * 4;      // this lane sums one weight row for 4 consecutive tokens
         const uint32_t red_q = red_base + q * lay.red_stage_bytes() + lane * 16;
         uint32_t pair_chunk = 0xFFFFFFFFu;
-        tf_pair pr = tf_pair{0u, 0u, 0u, 0u};
+        uint32_t pair_base[4] = {0u, 0u, 0u, 0u};                   // (token * top_k + rank) of this lane's 4 tokens
         for (uint32_t li = q; li < n_items; li += kReducers) {
             const uint32_t ruse = li / kRedStages;
             if (OUT_MODE == kOutPartialF16 || OUT_MODE == kOutPartialF32) {
                 if (cur.chunk != pair_chunk) {       // the pair of a token is the same for every tile of the chunk
                     pair_chunk = cur.chunk;
-                    if (tok < cur.ntok) pr = args.sorted_pairs[cur.row_base + tok];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (tok4 + j < cur.ntok) {
+                            const tf_pair pr = args.sorted_pairs[cur.row_base + tok4 + j];
+                            pair_base[j] = pr.token * args.top_k + pr.rank;
+                        }
+                    }
                 }
             }
             if (!mbar_wait(bar_part_full(q), ruse & 1)) { fail = kErrTimeoutPartials; break; }
@@ -605,39 +618,33 @@ grouped_ksplit_kernel(const GroupedArgs args) {
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_red_free(q));
-            if (tok < cur.ntok) {
-                const uint32_t out_row = cur.tile * kTileRows + row4;
-                if constexpr (OUT_MODE == kOutActs) {
-                    float gt[4] = {acc[0].x, acc[0].y, acc[0].z, acc[0].w};
-                    float up[4] = {acc[NMAT - 1].x, acc[NMAT - 1].y, acc[NMAT - 1].z, acc[NMAT - 1].w};
-                    uint32_t o[2];
+            const uint32_t out_row = cur.tile * kTileRows + row;
+            const float o0[4] = {acc[0].x, acc[0].y, acc[0].z, acc[0].w};
+            const float o1[4] = {acc[NMAT - 1].x, acc[NMAT - 1].y, acc[NMAT - 1].z, acc[NMAT - 1].w};
 #pragma unroll
-                    for (int j = 0; j < 2; ++j) {
-                        float g0v = gt[2 * j], g1v = gt[2 * j + 1], u0 = up[2 * j], u1 = up[2 * j + 1];
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t tok = tok4 + j;
+                if (tok < cur.ntok) {
+                    if constexpr (OUT_MODE == kOutActs) {
+                        float gt = o0[j], up = o1[j];
                         if constexpr (DENSE) {
                             // shared expert: gate and up are stored as fp16 before the activation
                             // (Kernels/MoE/SharedExpertInt4.swift:62-93; Metal/Primitives/utility.metal:15-17)
-                            g0v = __half2float(__float2half_rn(g0v)); g1v = __half2float(__float2half_rn(g1v));
-                            u0 = __half2float(__float2half_rn(u0)); u1 = __half2float(__float2half_rn(u1));
+                            gt = __half2float(__float2half_rn(gt));
+                            up = __half2float(__float2half_rn(up));
                         }
                         // routed: act = half(gelu_tanh(gate) * up), gate and up in fp32 (prefill.metal:634-636; moe.metal:368)
-                        const __half2 h = __floats2half2_rn(gelu_tanh(g0v) * u0, gelu_tanh(g1v) * u1);
-                        o[j] = *reinterpret_cast<const uint32_t*>(&h);
-                    }
-                    *reinterpret_cast<uint2*>(static_cast<uint16_t*>(args.out) + (size_t)(cur.row_base + tok) * args.out_stride + out_row) =
-                        make_uint2(o[0], o[1]);
-                } else if constexpr (OUT_MODE == kOutDenseF16) {
-                    const __half2 h0 = __floats2half2_rn(acc[0].x, acc[0].y), h1 = __floats2half2_rn(acc[0].z, acc[0].w);
-                    *reinterpret_cast<uint2*>(static_cast<uint16_t*>(args.out) + (size_t)(cur.row_base + tok) * args.out_stride + out_row) =
-                        make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
-                } else {
-                    const size_t idx = ((size_t)pr.token * args.top_k + pr.rank) * args.out_stride + out_row;
-                    if constexpr (OUT_MODE == kOutPartialF16) {       // prefill.metal:666-669
-                        const __half2 h0 = __floats2half2_rn(acc[0].x, acc[0].y), h1 = __floats2half2_rn(acc[0].z, acc[0].w);
-                        *reinterpret_cast<uint2*>(static_cast<uint16_t*>(args.out) + idx) =
-                            make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
+                        static_cast<uint16_t*>(args.out)[(size_t)(cur.row_base + tok) * args.out_stride + out_row] =
+                            __half_as_ushort(__float2half_rn(gelu_tanh(gt) * up));
+                    } else if constexpr (OUT_MODE == kOutDenseF16) {
+                        static_cast<uint16_t*>(args.out)[(size_t)(cur.row_base + tok) * args.out_stride + out_row] =
+                            __half_as_ushort(__float2half_rn(o0[j]));
                     } else {
-                        *reinterpret_cast<float4*>(static_cast<float*>(args.out) + idx) = acc[0];
+                        const size_t idx = (size_t)pair_base[j] * args.out_stride + out_row;
+                        if constexpr (OUT_MODE == kOutPartialF16)       // prefill.metal:666-669
+                            static_cast<uint16_t*>(args.out)[idx] = __half_as_ushort(__float2half_rn(o0[j]));
+                        else
+                            static_cast<float*>(args.out)[idx] = o0[j];
                     }
                 }
             }
@@ -688,7 +695,7 @@ static tf_status launch_grouped(tf_context* ctx, void* stream, GroupedArgs& args
     TF_REQUIRE(ctx, ng >= 1 && args.k % kGroup == 0, TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);
     const uint32_t cw = (ng + kGPW - 1) / kGPW;
     TF_REQUIRE(ctx, cw <= (uint32_t)kMaxComputeWarps, TF_ERR_UNSUPPORTED, "%s: K=%u outside the supported range (64..3072)", name, args.k);
-    TF_REQUIRE(ctx, args.rows % kTileRows == 0, TF_ERR_UNSUPPORTED, "%s: row count %u must be a multiple of 8", name, args.rows);
+    TF_REQUIRE(ctx, args.rows % kTileRows == 0, TF_ERR_UNSUPPORTED, "%s: row count %u must be a multiple of 16", name, args.rows);
     const KSplitSmem<NMAT> lay{cw, ng, args.k / 2};
     const size_t smem = lay.total();
     TF_REQUIRE(ctx, smem <= 200 * 1024, TF_ERR_UNSUPPORTED, "%s: K=%u needs %zu bytes of shared memory (limit 200 KB)", name, args.k, smem);

@@ -329,7 +329,7 @@ class DeviceRoutes:
         self.per_expert_offsets = torch.zeros(num_experts, **i32)
         self.per_expert_counts = torch.zeros(num_experts, **i32)
         self.groups = torch.zeros(num_experts * 3, **i32)
-        self.chunk_group = torch.zeros(n // 16 + num_experts + 1, **i32)
+        self.chunk_group = torch.zeros(n // 8 + num_experts + 1, **i32)
         self.chunk_start = torch.zeros(num_experts, **i32)
         self.counters = torch.zeros(4, **i32)
         self.c_struct = _capi.DeviceRoutes(*[_ptr(t) for t in (self.sorted_pairs, self.per_expert_offsets,
