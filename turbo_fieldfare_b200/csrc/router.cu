@@ -137,21 +137,65 @@ router_split_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
     const uint32_t ne = num_experts - e0 < (uint32_t)kSplitExpertsPerBlock ? num_experts - e0 : (uint32_t)kSplitExpertsPerBlock;
     // the four rows are contiguous in every plane
     const uint8_t* wsrc = W + (size_t)e0 * d;
+    const uint16_t* hrow = hidden + (size_t)row * hidden_stride;
     const bool a16 = (reinterpret_cast<uintptr_t>(wsrc) & 15) == 0 && (d & 15) == 0;
-    if (a16) {
-        for (uint32_t i = threadIdx.x; i < ne * d / 16; i += blockDim.x)
-            reinterpret_cast<uint4*>(wrows)[i] = ldg_nc_u4(wsrc + (size_t)i * 16);
-    } else if (a2) {
-        for (uint32_t i = threadIdx.x; i < ne * d / 2; i += blockDim.x)
-            reinterpret_cast<uint16_t*>(wrows)[i] = reinterpret_cast<const uint16_t*>(wsrc)[i];
+    const bool x16 = (reinterpret_cast<uintptr_t>(hrow) & 15) == 0 && (reinterpret_cast<uintptr_t>(eff) & 15) == 0 && (d & 7) == 0;
+    if (a16 && x16 && ne * d <= kSplitThreads * 16 * 6 && d <= kSplitThreads * 8 * 3) {
+        // latency path: every load of the block is issued before the first one is consumed
+        uint4 wv[6], hv[3], ev[3];
+#pragma unroll
+        for (int j = 0; j < 6; ++j) {
+            const uint32_t i = threadIdx.x + j * kSplitThreads;
+            wv[j] = i < ne * d / 16 ? ldg_nc_u4(wsrc + (size_t)i * 16) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            const uint32_t i = threadIdx.x + j * kSplitThreads;
+            const bool ok = i < d / 8;
+            hv[j] = ok ? __ldg(reinterpret_cast<const uint4*>(hrow) + i) : make_uint4(0u, 0u, 0u, 0u);
+            ev[j] = ok ? __ldg(reinterpret_cast<const uint4*>(eff) + i) : make_uint4(0u, 0u, 0u, 0u);
+        }
+        for (uint32_t i = threadIdx.x; i < ne * groups; i += blockDim.x) {
+            srows[i] = S[(size_t)e0 * groups + i];
+            brows[i] = B[(size_t)e0 * groups + i];
+        }
+#pragma unroll
+        for (int j = 0; j < 6; ++j) {
+            const uint32_t i = threadIdx.x + j * kSplitThreads;
+            if (i < ne * d / 16) reinterpret_cast<uint4*>(wrows)[i] = wv[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+            const uint32_t i = threadIdx.x + j * kSplitThreads;
+            if (i < d / 8) {
+                const uint32_t hw[4] = {hv[j].x, hv[j].y, hv[j].z, hv[j].w}, ew[4] = {ev[j].x, ev[j].y, ev[j].z, ev[j].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const uint16_t h0 = (uint16_t)(hw[q] & 0xFFFFu), h1 = (uint16_t)(hw[q] >> 16);
+                    const float f0 = X_BF16 ? bf16_bits_to_float(h0) : f16_bits_to_float(h0);
+                    const float f1 = X_BF16 ? bf16_bits_to_float(h1) : f16_bits_to_float(h1);
+                    xf[i * 8 + 2 * q] = __fmul_rn(f0, bf16_bits_to_float((uint16_t)(ew[q] & 0xFFFFu)));
+                    xf[i * 8 + 2 * q + 1] = __fmul_rn(f1, bf16_bits_to_float((uint16_t)(ew[q] >> 16)));
+                }
+            }
+        }
+        __syncthreads();
     } else {
-        for (uint32_t i = threadIdx.x; i < ne * d; i += blockDim.x) wrows[i] = wsrc[i];
+        if (a16) {
+            for (uint32_t i = threadIdx.x; i < ne * d / 16; i += blockDim.x)
+                reinterpret_cast<uint4*>(wrows)[i] = ldg_nc_u4(wsrc + (size_t)i * 16);
+        } else if (a2) {
+            for (uint32_t i = threadIdx.x; i < ne * d / 2; i += blockDim.x)
+                reinterpret_cast<uint16_t*>(wrows)[i] = reinterpret_cast<const uint16_t*>(wsrc)[i];
+        } else {
+            for (uint32_t i = threadIdx.x; i < ne * d; i += blockDim.x) wrows[i] = wsrc[i];
+        }
+        for (uint32_t i = threadIdx.x; i < ne * groups; i += blockDim.x) {
+            srows[i] = S[(size_t)e0 * groups + i];
+            brows[i] = B[(size_t)e0 * groups + i];
+        }
+        stage_router_x<X_BF16>(hrow, eff, xf, d);     // ends with a barrier
     }
-    for (uint32_t i = threadIdx.x; i < ne * groups; i += blockDim.x) {
-        srows[i] = S[(size_t)e0 * groups + i];
-        brows[i] = B[(size_t)e0 * groups + i];
-    }
-    stage_router_x<X_BF16>(hidden + (size_t)row * hidden_stride, eff, xf, d);     // ends with a barrier
 
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t e = e0 + warp;
