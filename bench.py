@@ -174,12 +174,22 @@ def run_gpu(args):
 
     prefill_tokens, steps_dec, batch = args.prefill_tokens, args.decode_steps, args.decode_batch
     ctx = TurboContext(local_rank)
-    stack = MoEStack(ctx, layers=args.layers, seed=2026 + rank)
+    ep = world > 1
+    if ep:
+        # experts sharded 128/N per GPU, per-rank token counts fixed (weak scaling), all-to-all dispatch and combine
+        from turbo_fieldfare_b200.ep import ExpertParallelStack
+        stack = ExpertParallelStack(ctx, layers=args.layers, seed=2026)
+    else:
+        stack = MoEStack(ctx, layers=args.layers, seed=2026)
     if args.zipf:
         rng = np.random.default_rng(17)
         p = 1.0 / (rng.permutation(E) + 1) ** 1.1
         stack.set_logit_bias(np.log(p / p.sum()).astype(np.float32))
-    ws_prefill, ws_b1, ws_bn = stack.workspace(prefill_tokens), stack.workspace(1), stack.workspace(batch)
+    if ep:
+        ws_prefill = stack.buffers(prefill_tokens, fixed_capacity=False)
+        ws_b1, ws_bn = stack.buffers(1, fixed_capacity=True), stack.buffers(batch, fixed_capacity=True)
+    else:
+        ws_prefill, ws_b1, ws_bn = stack.workspace(prefill_tokens), stack.workspace(1), stack.workspace(batch)
 
     gen = torch.Generator().manual_seed(1234 + rank)
     host_prefill = torch.randn(prefill_tokens, D, generator=gen).half().pin_memory()
@@ -209,7 +219,8 @@ def run_gpu(args):
             launches[tokens] = ctx.launch_count - before
         return g
 
-    use_graphs = not args.no_graphs
+    # the expert-parallel path interleaves NCCL collectives with the kernels and runs eagerly
+    use_graphs = not args.no_graphs and not ep
     g1 = capture(h1, 1, ws_b1) if use_graphs else None
     gn = capture(hn, batch, ws_bn) if use_graphs else None
     counters = {"launches": 0}
@@ -295,7 +306,8 @@ def run_gpu(args):
     # roofline of the dominant kernel: the grouped tensor-core expert kernel at decode batch 64
     # (gate/up launch + down launch of one layer timed as a pair, distinct layers back to back so
     # that nothing is re-read from L2).
-    roofline = measure_roofline(torch, ctx, stack, ws_bn, hn, batch, PrefillRouter, PrefillGroupedRoutedMoE)
+    roofline = None if ep else measure_roofline(torch, ctx, stack, ws_bn, hn, batch, PrefillRouter, PrefillGroupedRoutedMoE)
+    device_code = ctx.device_status()          # 0 unless a kernel abandoned a bounded wait
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -306,7 +318,8 @@ def run_gpu(args):
                                f"{steps_dec} decode steps at batch 1 + {steps_dec} at batch {batch}",
                    "tokens_per_step": tokens, "routing": "zipf(1.1) logit bias" if args.zipf else "computed logits",
                    "l2": "every step streams 13.2 GB of distinct layer weights (>> 126 MB L2)",
-                   "cuda_graphs": use_graphs, "parallelism": "replicas" if world > 1 else "single GPU",
+                   "cuda_graphs": use_graphs, "device_status": device_code,
+                   "parallelism": f"ep{world}: experts sharded {E // world} per GPU, NCCL all-to-all dispatch + combine" if ep else "single GPU",
                    "phase_ms": {"prefill": ms_prefill, "decode_b1_per_step": ms_dec1, f"decode_b{batch}_per_step": ms_decn},
                    "phase_tokens_per_s": {"prefill": prefill_tokens / ms_prefill * 1e3, "decode_b1": 1e3 / ms_dec1,
                                           f"decode_b{batch}": batch / ms_decn * 1e3}},

@@ -248,7 +248,8 @@ tf_status tf_group_pairs(const tf_pair* host_pairs, uint32_t pair_count,
 /* ---- batched routing on the device ---- */
 /* Device form of groupTokenExpertPairs for router output that never leaves the
  * GPU: order (expert, token, rank), ids clamped to num_experts-1 as the caller
- * does (Runtime/Inference/RealForwardRunner.swift:955). No sort keys and no
+ * does (Runtime/Inference/RealForwardRunner.swift:955); an id of UINT32_MAX marks an
+ * empty slot and is skipped. No sort keys and no
  * tiles: tiles exist in the reference only to bound SSD slots. Replaces the
  * CPU stage PrefillRouter.makeTokenExpertPairs + PrefillMoEGrouping
  * (RealForwardRunner.swift:945-979). */
@@ -309,7 +310,10 @@ tf_status tf_expert_pool_upload(tf_pool* pool, void* stream, uint32_t layer, uin
  * scale |N(0,1)| * 0.004 (8-bit: / 16), bias -zero_point * scale + N(0, 1e-4), bf16. */
 tf_status tf_fill_affine_synthetic(tf_context* ctx, void* stream, void* weights, void* scales, void* biases,
                                    uint32_t rows, uint32_t cols, uint32_t bits, uint64_t seed);
-tf_status tf_expert_pool_fill_synthetic(tf_pool* pool, void* stream, uint64_t seed, uint32_t d, uint32_t f);
+/* The pool may be a shard [expert_offset, expert_offset + experts) of global_experts experts (0 = not
+ * sharded); blobs are seeded by the global expert id, so shards hold the bytes of the whole pool. */
+tf_status tf_expert_pool_fill_synthetic(tf_pool* pool, void* stream, uint64_t seed, uint32_t d, uint32_t f,
+                                        uint32_t global_experts, uint32_t expert_offset);
 
 /* ---- fused MoE block and layer stack (new entry points; the reference spreads
  * this over RealForwardRunner with two CPU round trips per layer) ---- */
@@ -353,6 +357,41 @@ tf_status tf_stack_create(tf_context* ctx, const tf_moe_layer* layers, const voi
                           uint32_t layer_count, float eps, tf_stack** out);
 void tf_stack_destroy(tf_stack* stack);
 tf_status tf_stack_forward(tf_stack* stack, void* stream, void* hidden, uint32_t tokens, tf_workspace* ws);
+
+/* h += y (one fp16 rounding; y may be NULL), then x_out = half(rmsnorm(h) * w) (x_out may be NULL).
+ * The residual add of one stack layer fused with the norm of the next; contiguous fp16 rows. */
+tf_status tf_residual_rmsnorm(tf_context* ctx, void* stream, void* hidden, const void* y, const void* weight_bf16,
+                              void* x_out, uint32_t rows, uint32_t d, float eps);
+
+/* ---- expert parallelism (new; the reference is single-GPU: MetalContext.swift:51-71) ---- */
+/* Gather each sorted pair's activation row into the send buffer in (destination rank, expert, token,
+ * rank) order, with the expert id local to its owner, and record inverse_perm[token*top_k + rank] = slot.
+ * capacity == 0: exact layout, slot = sorted pair index (split sizes come from per_expert_counts).
+ * capacity > 0: fixed layout [ranks][capacity] with unused slots marked id = UINT32_MAX (no host
+ * synchronisation; an overflowing destination sets the context's device error word). */
+tf_status tf_ep_pack(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off, uint32_t hidden_stride_elements,
+                     const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                     uint32_t experts_per_rank, uint32_t capacity, uint32_t d,
+                     void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm);
+/* The three phases of one expert-parallel layer; the caller runs the all-to-all exchanges between them
+ * (rows and expert ids out, result rows back).
+ *   tf_ep_dispatch: router + top-k + device grouping over the GLOBAL experts + tf_ep_pack;
+ *   tf_ep_experts:  on the owner: group the received rows by local expert and run gate/up/GeGLU/down;
+ *                   out_rows[slot] is the fp16 expert output of the row received in that slot;
+ *   tf_ep_finish:   shared expert on the local tokens + tf_ep_combine of the returned rows. */
+tf_status tf_ep_dispatch(tf_context* ctx, void* stream, const tf_moe_layer* layer, const void* x, uint32_t tokens,
+                         tf_workspace* ws, uint32_t experts_per_rank, uint32_t capacity,
+                         void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm);
+tf_status tf_ep_experts(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
+                        const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
+                        uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
+                        const void* zero_weights, void* acts_scratch, void* out_rows, uint32_t d, uint32_t f);
+tf_status tf_ep_finish(tf_context* ctx, void* stream, const tf_moe_layer* layer, const void* x, uint32_t tokens,
+                       tf_workspace* ws, const void* returned_rows, const uint32_t* inverse_perm, void* y);
+/* out[t] = half(sum_r w[t,r] * returned_rows[inverse_perm[t*top_k + r]] + residual[t]), rank order. */
+tf_status tf_ep_combine(tf_context* ctx, void* stream, const void* returned_rows, const void* route_weights,
+                        const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
+                        void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d);
 
 /* ---- norms ---- */
 /* y = half(x * rsqrt(mean(x^2) + eps) * w_bf16); weight NULL = no-scale form.

@@ -1,0 +1,44 @@
+"""One rank of the 2-GPU expert-parallel check (launched by tests/test_gpu_ep.py with torchrun): every rank
+runs its own tokens through the expert-parallel stack and through a private single-GPU stack with the
+same seeds, and writes the relative L2 difference."""
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+
+def main(out_dir: str) -> None:
+    rank, local = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from turbo_fieldfare_b200.ep import ExpertParallelStack
+    from turbo_fieldfare_b200.kernels import TurboContext
+    from turbo_fieldfare_b200.stack import MoEStack
+    ctx = TurboContext(local)
+    dims = dict(layers=2, d=256, f=128, fs=192, num_experts=16, top_k=8, seed=5, align=256)
+    ep_stack = ExpertParallelStack(ctx, **dims)
+    ref_stack = MoEStack(ctx, **dims)
+    worst = 0.0
+    for T, fixed in ((6, True), (70, False)):
+        g = torch.Generator().manual_seed(17 + rank + T)
+        h = torch.randn(T, 256, generator=g).half().cuda()
+        h_ep, h_ref = h.clone(), h.clone()
+        ep_stack.forward(h_ep, T, ep_stack.buffers(T, fixed))
+        ref_stack.forward(h_ref, T, ref_stack.workspace(T))
+        torch.cuda.synchronize()
+        a, b = h_ref.float(), h_ep.float()
+        worst = max(worst, float((a - b).norm() / a.norm()))
+    assert ctx.device_status() == 0
+    np.save(os.path.join(out_dir, f"err_{rank}.npy"), np.array(worst))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main(sys.argv[1])

@@ -1,0 +1,86 @@
+"""GPU tests of the expert-parallel path: the pack kernel against the numpy plan, the single-rank EP
+stack against the fused single-GPU stack, and (when two GPUs are visible) a 2-rank NCCL run against
+the single-GPU result."""
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from helpers import from_dev, to_dev
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.mark.parametrize("T,capacity", [(5, 0), (64, 0), (64, 64 * 8), (1, 8)])
+def test_pack_matches_numpy_plan(tf_ctx, oracle, T, capacity):
+    import ctypes as C
+    import torch
+    from turbo_fieldfare_b200.ep import plan_dispatch
+    from turbo_fieldfare_b200.kernels import DeviceRoutes, PrefillGroupedRoutedMoE
+    K, E, D, world = 8, 128, 256, 4
+    epr = E // world
+    rng = np.random.default_rng(T + capacity)
+    idx = np.stack([rng.permutation(E)[:K] for _ in range(T)]).astype(np.uint32)
+    w16 = rng.integers(0, 0x3C00, size=(T, K)).astype(np.uint16)
+    x16 = rng.integers(0, 0x7BFF, size=(T, D)).astype(np.uint16)
+    routes = DeviceRoutes(T, K, E)
+    PrefillGroupedRoutedMoE(tf_ctx).encode_group_routes(to_dev(idx), to_dev(w16), T, K, E, routes)
+    slots = world * capacity if capacity else T * K
+    send_rows = torch.full((slots * D,), -1, dtype=torch.int16, device="cuda")
+    send_ids = torch.full((slots,), 7, dtype=torch.int32, device="cuda")
+    inverse = torch.zeros(T * K, dtype=torch.int32, device="cuda")
+    tf_ctx.check(tf_ctx.lib.tf_ep_pack(tf_ctx.handle, torch.cuda.current_stream().cuda_stream, to_dev(x16).data_ptr(), 0, D,
+                                       C.byref(routes.c_struct), T, K, E, epr, capacity, D, send_rows.data_ptr(),
+                                       send_ids.data_ptr(), inverse.data_ptr()))
+    torch.cuda.synchronize()
+    assert tf_ctx.device_status() == 0
+    tok, eloc, inv, _ = plan_dispatch(idx, epr, world, capacity)
+    assert np.array_equal(from_dev(send_ids, np.uint32), eloc)
+    assert np.array_equal(from_dev(inverse, np.uint32), inv)
+    rows = from_dev(send_rows, np.uint16).reshape(slots, D)
+    valid = tok >= 0
+    assert np.array_equal(rows[valid], x16[tok[valid]])
+
+
+@pytest.mark.parametrize("T,fixed", [(1, True), (6, True), (70, False)])
+def test_single_rank_ep_stack_matches_fused_stack(tf_ctx, oracle, T, fixed):
+    import torch
+    from turbo_fieldfare_b200.ep import ExpertParallelStack
+    from turbo_fieldfare_b200.stack import MoEStack
+    o = oracle
+    dims = dict(layers=2, d=256, f=128, fs=192, num_experts=16, top_k=8, seed=5, align=256)
+    ref_stack = MoEStack(tf_ctx, **dims)
+    ep_stack = ExpertParallelStack(tf_ctx, **dims)
+    rng = np.random.default_rng(T)
+    h16 = o.f32_to_f16(rng.standard_normal((T, 256)).astype(np.float32))
+    h_ref, h_ep = to_dev(h16.copy()), to_dev(h16.copy())
+    ref_stack.forward(h_ref, T, ref_stack.workspace(T))
+    ep_stack.forward(h_ep, T, ep_stack.buffers(T, fixed))
+    torch.cuda.synchronize()
+    assert tf_ctx.device_status() == 0
+    a = o.f16_to_f32(from_dev(h_ref, np.uint16))
+    b = o.f16_to_f32(from_dev(h_ep, np.uint16))
+    assert o.rel_l2(b, a) < 3e-3          # fp16 result rows over the wire instead of fp32 partials
+    ref_stack.close()
+    ep_stack.close()
+
+
+def test_two_rank_nccl_matches_single_gpu(tmp_path):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(ROOT / "tests" / "ep_rank_main.py"), str(tmp_path)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    errs = [float(np.load(tmp_path / f"err_{r}.npy")) for r in range(2)]
+    assert max(errs) < 3e-3, errs

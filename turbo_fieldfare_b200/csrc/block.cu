@@ -218,15 +218,20 @@ tf_status tf_fill_affine_synthetic(tf_context* ctx, void* stream, void* weights,
     return tf::check_launch(ctx, name);
 }
 
-tf_status tf_expert_pool_fill_synthetic(tf_pool* pool, void* stream, uint64_t seed, uint32_t d, uint32_t f) {
+tf_status tf_expert_pool_fill_synthetic(tf_pool* pool, void* stream, uint64_t seed, uint32_t d, uint32_t f,
+                                        uint32_t global_experts, uint32_t expert_offset) {
     const char* name = "tf_expert_pool_fill_synthetic";
     TF_REQUIRE(nullptr, pool != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: pool is NULL", name);
     tf_context* ctx = pool->ctx;
+    if (global_experts == 0) global_experts = pool->experts;
+    TF_REQUIRE(ctx, expert_offset + pool->experts <= global_experts, TF_ERR_INVALID_ARGUMENT,
+               "%s: shard [%u, %u) exceeds %u experts", name, expert_offset, expert_offset + pool->experts, global_experts);
     const tf_expert_offsets& o = pool->offsets;
     for (uint32_t l = 0; l < pool->layers; ++l)
         for (uint32_t e = 0; e < pool->experts; ++e) {
             uint8_t* b = const_cast<uint8_t*>(static_cast<const uint8_t*>(tf_expert_pool_ptr(pool, l, e)));
-            const uint64_t s0 = seed + ((uint64_t)l * pool->experts + e) * 3;
+            // seeded by the GLOBAL expert id, so a shard holds the same bytes as the unsharded pool
+            const uint64_t s0 = seed + ((uint64_t)l * global_experts + expert_offset + e) * 3;
             tf_status s = tf_fill_affine_synthetic(ctx, stream, b + o.gate_w_off, b + o.gate_s_off, b + o.gate_b_off, f, d, 4, s0);
             if (!s) s = tf_fill_affine_synthetic(ctx, stream, b + o.up_w_off, b + o.up_s_off, b + o.up_b_off, f, d, 4, s0 + 1);
             if (!s) s = tf_fill_affine_synthetic(ctx, stream, b + o.down_w_off, b + o.down_s_off, b + o.down_b_off, d, f, 4, s0 + 2);
@@ -334,6 +339,76 @@ tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer
     if (s) return s;
     return tf_moe_reduce_token_major(ctx, stream, ws->partials, f32, ws->weights, ws->shared_y, d, y,
                                      y_stride_elements, tokens, K, d);
+}
+
+tf_status tf_residual_rmsnorm(tf_context* ctx, void* stream, void* hidden, const void* y, const void* weight_bf16,
+                              void* x_out, uint32_t rows, uint32_t d, float eps) {
+    const char* name = "tf_residual_rmsnorm";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, hidden != nullptr && (x_out == nullptr || weight_bf16 != nullptr), TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, d % 8 == 0 && d <= 8u * tf::kRrnThreads * tf::kRrnMaxSlices, TF_ERR_UNSUPPORTED,
+               "%s: D must be a multiple of 8 and at most %d", name, 8 * tf::kRrnThreads * tf::kRrnMaxSlices);
+    TF_REQUIRE(ctx, tf::aligned(hidden, 16) && tf::aligned(y, 16) && tf::aligned(weight_bf16, 16) && tf::aligned(x_out, 16),
+               TF_ERR_ALIGNMENT, "%s: buffers must be 16-byte aligned", name);
+    if (rows == 0) return TF_OK;
+    tf::residual_rmsnorm_kernel<<<rows, tf::kRrnThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint16_t*>(hidden), static_cast<const uint16_t*>(y), static_cast<const uint16_t*>(weight_bf16),
+        static_cast<uint16_t*>(x_out), d, eps);
+    return tf::check_launch(ctx, name);
+}
+
+// ---------------------------------------------------------------------------
+// expert-parallel layer phases (the collectives between them are the caller's)
+// ---------------------------------------------------------------------------
+
+tf_status tf_ep_dispatch(tf_context* ctx, void* stream, const tf_moe_layer* layer, const void* x, uint32_t tokens,
+                         tf_workspace* ws, uint32_t experts_per_rank, uint32_t capacity,
+                         void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm) {
+    const char* name = "tf_ep_dispatch";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, layer && x && ws, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    TF_REQUIRE(ctx, tokens <= ws->max_tokens, TF_ERR_SCRATCH_TOO_SMALL, "%s: %u tokens exceed the workspace (%u)", name, tokens, ws->max_tokens);
+    if (tokens == 0) return TF_OK;
+    const uint32_t d = layer->d, K = layer->top_k, E = layer->num_experts;
+    tf_status s = tf_router_gemma4_block(ctx, stream, layer->router.weights, layer->router.weights_off,
+                                         layer->router.scales, layer->router.scales_off,
+                                         layer->router.biases, layer->router.biases_off,
+                                         x, 0, TF_FP16, layer->effective_scale, 0, layer->per_expert_scale, 0,
+                                         layer->logit_bias, ws->indices, 0, ws->weights, 0, nullptr, tokens, E, d, K, d);
+    if (s) return s;
+    s = tf_group_routes_device(ctx, stream, ws->indices, ws->weights, tokens, K, E, &ws->routes);
+    if (s) return s;
+    return tf_ep_pack(ctx, stream, x, 0, d, &ws->routes, tokens, K, E, experts_per_rank, capacity, d, send_rows,
+                      send_expert_ids, inverse_perm);
+}
+
+tf_status tf_ep_experts(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
+                        const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
+                        uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
+                        const void* zero_weights, void* acts_scratch, void* out_rows, uint32_t d, uint32_t f) {
+    const char* name = "tf_ep_experts";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, pool_layer_base && offsets && recv_rows && recv_expert_ids && recv_routes && zero_weights && acts_scratch && out_rows,
+               TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    if (recv_slots == 0) return TF_OK;
+    // every received row is one (token = slot, rank 0) pair of a local expert; empty slots carry UINT32_MAX
+    tf_status s = tf_group_routes_device(ctx, stream, recv_expert_ids, zero_weights, recv_slots, 1, local_experts, recv_routes);
+    if (s) return s;
+    return tf_grouped_moe_batched(ctx, stream, recv_rows, 0, d, pool_layer_base, expert_stride, offsets, recv_routes,
+                                  acts_scratch, out_rows, 0, recv_slots, d, f, 1);
+}
+
+tf_status tf_ep_finish(tf_context* ctx, void* stream, const tf_moe_layer* layer, const void* x, uint32_t tokens,
+                       tf_workspace* ws, const void* returned_rows, const uint32_t* inverse_perm, void* y) {
+    const char* name = "tf_ep_finish";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, layer && x && ws && returned_rows && inverse_perm && y, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    if (tokens == 0) return TF_OK;
+    const uint32_t d = layer->d;
+    tf_status s = tf_shared_expert_int4_block(ctx, stream, x, 0, d, &layer->shared_gate, &layer->shared_up, &layer->shared_down,
+                                              ws->shared_y, 0, d, ws->shared_act, tokens);
+    if (s) return s;
+    return tf_ep_combine(ctx, stream, returned_rows, ws->weights, inverse_perm, ws->shared_y, d, y, d, tokens, layer->top_k, d);
 }
 
 tf_status tf_stack_create(tf_context* ctx, const tf_moe_layer* layers, const void* const* norm_weights_bf16,

@@ -1,0 +1,128 @@
+// Expert-parallel dispatch and combine: the data movement either side of the all-to-all.
+//
+// The reference has no multi-GPU path (one MTLDevice, one queue:
+// Infrastructure/Metal/MetalContext.swift:51-71). With experts sharded 128/N per GPU, a layer is
+//   route locally -> pack rows by destination rank (this file) -> all-to-all -> grouped experts on
+//   the owner (grouped.cu) -> all-to-all back -> weighted combine in rank order (this file).
+// The pack kernel gathers each pair's activation row straight into the send buffer in
+// (destination, expert, token, rank) order, which is the order the device grouping already produced,
+// and records where each (token, rank) went; the combine kernel gathers the returned rows through
+// that record, so no row is copied twice and the summation order is fixed (rank 0..K-1).
+#include "tf_common.cuh"
+
+namespace tf {
+
+constexpr int kPackThreads = 256;
+
+// One warp per send slot. Fixed-capacity mode: slot = dst * capacity + pos. Exact mode (n_dst == 1):
+// slot = sorted pair index.
+__global__ void __launch_bounds__(kPackThreads)
+ep_pack_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride, const tf_pair* __restrict__ sorted_pairs,
+               const uint32_t* __restrict__ per_expert_counts, uint32_t n_pairs, uint32_t top_k, uint32_t num_experts,
+               uint32_t experts_per_rank, uint32_t n_dst, uint32_t capacity, uint32_t d,
+               uint16_t* __restrict__ send_rows, uint32_t* __restrict__ send_ids, uint32_t* __restrict__ inverse_perm,
+               uint32_t* __restrict__ overflow) {
+    __shared__ uint32_t dst_base[257], dst_count[256];
+    if (n_dst > 1) {
+        // pairs are sorted by expert, experts are contiguous per rank: dst_base = prefix of the counts
+        if (threadIdx.x == 0) {
+            uint32_t run = 0;
+            for (uint32_t r = 0; r < n_dst; ++r) {
+                dst_base[r] = run;
+                uint32_t c = 0;
+                for (uint32_t e = r * experts_per_rank; e < (r + 1) * experts_per_rank && e < num_experts; ++e) c += per_expert_counts[e];
+                dst_count[r] = c;
+                run += c;
+                if (c > capacity && blockIdx.x == 0) atomicMax(overflow, c);
+            }
+        }
+        __syncthreads();
+    }
+    const uint32_t warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const uint32_t slot = blockIdx.x * (kPackThreads / kWarp) + warp;
+    const uint32_t slots = n_dst > 1 ? n_dst * capacity : n_pairs;
+    if (slot >= slots) return;
+    uint32_t p;
+    if (n_dst > 1) {
+        const uint32_t dst = slot / capacity, pos = slot % capacity;
+        if (pos >= dst_count[dst]) {
+            if (lane == 0) send_ids[slot] = 0xFFFFFFFFu;
+            return;
+        }
+        p = dst_base[dst] + pos;
+    } else {
+        p = slot;
+    }
+    const tf_pair pr = sorted_pairs[p];
+    if (lane == 0) {
+        send_ids[slot] = pr.expert % experts_per_rank;
+        inverse_perm[pr.token * top_k + pr.rank] = slot;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)pr.token * hidden_stride);
+    uint4* dst_row = reinterpret_cast<uint4*>(send_rows + (size_t)slot * d);
+    for (uint32_t i = lane; i < d / 8; i += kWarp) dst_row[i] = __ldg(src + i);
+}
+
+// y[t,d] = half(sum_r fma(w[t,r], partial[inverse[t*K+r]][d], acc) + residual[t,d]), rank order.
+__global__ void ep_combine_kernel(const uint16_t* __restrict__ rows, const uint16_t* __restrict__ weights,
+                                  const uint32_t* __restrict__ inverse_perm, const uint16_t* __restrict__ residual,
+                                  uint32_t residual_stride, uint16_t* __restrict__ out, uint32_t out_stride,
+                                  uint32_t T, uint32_t K, uint32_t D) {
+    const uint32_t d = blockIdx.x * blockDim.x + threadIdx.x;
+    const uint32_t t = blockIdx.y;
+    if (d >= D || t >= T) return;
+    float acc = 0.0f;
+    for (uint32_t r = 0; r < K; ++r) {
+        const uint32_t slot = inverse_perm[(size_t)t * K + r];
+        acc = fmaf(f16_bits_to_float(weights[(size_t)t * K + r]), f16_bits_to_float(rows[(size_t)slot * D + d]), acc);
+    }
+    if (residual) acc += f16_bits_to_float(residual[(size_t)t * residual_stride + d]);
+    out[(size_t)t * out_stride + d] = __half_as_ushort(__float2half_rn(acc));
+}
+
+}  // namespace tf
+
+extern "C" {
+
+tf_status tf_ep_pack(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off, uint32_t hidden_stride_elements,
+                     const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                     uint32_t experts_per_rank, uint32_t capacity, uint32_t d,
+                     void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm) {
+    const char* name = "tf_ep_pack";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, hidden && routes && send_rows && send_expert_ids && inverse_perm, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    TF_REQUIRE(ctx, experts_per_rank > 0 && num_experts % experts_per_rank == 0 && num_experts <= TF_MAX_ROUTER_EXPERTS,
+               TF_ERR_INVALID_ARGUMENT, "%s: experts (%u) must divide evenly over ranks (%u per rank)", name, num_experts, experts_per_rank);
+    TF_REQUIRE(ctx, d % 8 == 0 && hidden_stride_elements >= d, TF_ERR_INVALID_ARGUMENT, "%s: D must be a multiple of 8", name);
+    const uint8_t* hp = tf::byte_ptr(hidden, hidden_off);
+    TF_REQUIRE(ctx, tf::aligned(hp, 16) && (hidden_stride_elements * 2) % 16 == 0 && tf::aligned(send_rows, 16), TF_ERR_ALIGNMENT,
+               "%s: rows must be 16-byte aligned", name);
+    const uint32_t n_pairs = query_count * top_k;
+    if (n_pairs == 0) return TF_OK;
+    const uint32_t n_dst = capacity > 0 ? num_experts / experts_per_rank : 1;
+    const uint32_t slots = capacity > 0 ? n_dst * capacity : n_pairs;
+    const uint32_t per_block = tf::kPackThreads / tf::kWarp;
+    tf::ep_pack_kernel<<<(slots + per_block - 1) / per_block, tf::kPackThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const uint16_t*>(hp), hidden_stride_elements, routes->sorted_pairs, routes->per_expert_counts, n_pairs,
+        top_k, num_experts, experts_per_rank, n_dst, capacity, d, static_cast<uint16_t*>(send_rows), send_expert_ids,
+        inverse_perm, ctx->device_error);
+    return tf::check_launch(ctx, name);
+}
+
+tf_status tf_ep_combine(tf_context* ctx, void* stream, const void* returned_rows, const void* route_weights,
+                        const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
+                        void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d) {
+    const char* name = "tf_ep_combine";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, returned_rows && route_weights && inverse_perm && out, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, top_k > 0 && d > 0 && out_stride_elements >= d, TF_ERR_INVALID_ARGUMENT, "%s: bad dimensions", name);
+    if (query_count == 0) return TF_OK;
+    dim3 grid((d + 255) / 256, query_count);
+    tf::ep_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(returned_rows), static_cast<const uint16_t*>(route_weights), inverse_perm,
+        static_cast<const uint16_t*>(residual), residual_stride_elements, static_cast<uint16_t*>(out), out_stride_elements,
+        query_count, top_k, d);
+    return tf::check_launch(ctx, name);
+}
+
+}  // extern "C"

@@ -59,6 +59,7 @@ group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __rest
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
         uint32_t ex = indices[i];
+        if (ex == 0xFFFFFFFFu) continue;    // empty slot of a fixed-capacity exchange buffer
         if (ex >= E) ex = E - 1;            // min(id, E-1): Runtime/Inference/RealForwardRunner.swift:955
         atomicAdd(&hist[ex], 1u);
     }
@@ -99,7 +100,7 @@ group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __rest
             const uint32_t i = first + j;
             if (i < n) {
                 uint32_t ex = indices[i];
-                if (ex >= E) ex = E - 1;
+                if (ex != 0xFFFFFFFFu && ex >= E) ex = E - 1;
                 if (ex == e) { flags |= 1u << j; ++cnt; }
             }
         }

@@ -76,9 +76,11 @@ class ExpertPool:
                                                                   blob.ctypes.data, blob.size))
         torch.cuda.current_stream().synchronize()    # the host array may be freed by the caller
 
-    def fill_synthetic(self, seed: int, stream=None) -> None:
+    def fill_synthetic(self, seed: int, stream=None, global_experts: int = 0, expert_offset: int = 0) -> None:
+        """Seeded synthetic blobs; a shard passes the global expert count and its first expert id so that
+        it holds the same bytes as the corresponding slice of the unsharded pool."""
         self.context.check(self.context.lib.tf_expert_pool_fill_synthetic(self.handle, _stream(stream), seed,
-                                                                          self.d, self.f))
+                                                                          self.d, self.f, global_experts, expert_offset))
 
     def download(self, layer: int, expert: int) -> np.ndarray:
         """Copy one blob back to the host (tests use this to feed the oracle the exact bytes)."""
