@@ -289,6 +289,39 @@ tf_status tf_shared_expert_int4_block(tf_context* ctx, void* stream,
                                       void* y, uint64_t y_off, uint32_t y_stride_elements,
                                       void* scratch_act, uint32_t rows);
 
+/* ---- tensor-core (tcgen05 / TMEM) kernels for prefill-sized batches ---- */
+/* Y[M,N] = X[M,K] . dequant(W[N,K])^T, fp16 in/out, fp32 accumulation; the weight tile is staged as
+ * half(q*s+b) and multiplied on the matrix unit. Replaces MPPPrefillInt4QMM.encode
+ * (Kernels/TensorCore/MPPPrefillInt4QMM.swift:34-78; Metal/TensorCore/tensorops.metal:13-105).
+ * K % 64 == 0 as there; M and N are free (the reference wants M % 32 == 0 and N % 64 == 0). */
+tf_status tf_int4_qmm(tf_context* ctx, void* stream,
+                      const void* weights, uint64_t weights_off,
+                      const void* scales, uint64_t scales_off,
+                      const void* biases, uint64_t biases_off,
+                      const void* x, uint64_t x_off, void* y, uint64_t y_off,
+                      uint32_t m, uint32_t n, uint32_t k);
+/* Routed experts over expert-sorted rows: x_sorted[x_rows, D] holds the gathered hidden row of every
+ * (token, expert) pair in the order of routes->sorted_pairs (tf_ep_pack makes it);
+ * acts_scratch[x_rows, F] = half(gelu(gate.x) * (up.x)); out_rows[x_rows, D] = half(down.act), still in
+ * sorted order (tf_ep_combine folds them back per token). Same mathematics as tf_grouped_moe_batched with
+ * the weights rounded to half(q*s+b) first, the matrix-unit convention of tensorops.metal:60-75. Replaces
+ * PrefillGroupedRoutedMoE.encodeStreamedBatched (Kernels/Prefill/MoE/PrefillGroupedRoutedMoE.swift:386-461)
+ * for batches large enough to fill 128-token tiles. */
+tf_status tf_grouped_moe_tensorcore(tf_context* ctx, void* stream,
+                                    const void* x_sorted, uint32_t x_rows,
+                                    const void* pool_layer_base, uint64_t expert_stride,
+                                    const tf_expert_offsets* offsets, const tf_device_routes* routes,
+                                    void* acts_scratch, void* out_rows, uint32_t d, uint32_t f);
+/* Shared expert for `rows` tokens on the matrix unit; gate and up are rounded to fp16 before the activation
+ * like the row kernel (Kernels/MoE/SharedExpertInt4.swift:62-93). Replaces PrefillSharedExpert.encodeBlock
+ * (Kernels/Prefill/MoE/PrefillSharedExpert.swift:11-59) for prefill-sized blocks. */
+tf_status tf_shared_expert_int4_tensorcore(tf_context* ctx, void* stream,
+                                           const void* x, uint32_t x_stride_elements,
+                                           const tf_projection* gate, const tf_projection* up,
+                                           const tf_projection* down,
+                                           void* y, uint32_t y_stride_elements,
+                                           void* scratch_act, uint32_t rows);
+
 /* ---- HBM-resident expert pool (replaces SSD streaming) ---- */
 /* One allocation of layers * experts blobs of `stride` bytes in the .gturbo blob
  * layout. Replaces PreadExpertStreamer and its LFU slot cache

@@ -77,6 +77,8 @@ tf_status tf_context_create(int device, tf_context** out) {
     if (e == cudaSuccess) e = cudaMemset(ctx->router_tickets, 0, sizeof(unsigned int) * tf::kRouterSplitRows);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->device_error, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->device_error, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_groups, 64 * (TF_MAX_ROUTER_EXPERTS + 1));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_totals, 2 * sizeof(uint32_t));
     if (e != cudaSuccess) {
         tf_status s = tf::fail(nullptr, TF_ERR_OUT_OF_MEMORY, "context scratch: %s", cudaGetErrorString(e));
         tf_context_destroy(ctx);
@@ -92,6 +94,8 @@ void tf_context_destroy(tf_context* ctx) {
     if (ctx->router_logits) cudaFree(ctx->router_logits);
     if (ctx->router_tickets) cudaFree(ctx->router_tickets);
     if (ctx->device_error) cudaFree(ctx->device_error);
+    if (ctx->qmm_groups) cudaFree(ctx->qmm_groups);
+    if (ctx->qmm_totals) cudaFree(ctx->qmm_totals);
     delete ctx;
 }
 

@@ -1,0 +1,523 @@
+// Grouped int4 GEMM on the 5th-generation tensor cores for prefill-sized batches.
+//
+// Replaces mpp_prefill_affine_threadgroup_f16 (Metal/TensorCore/tensorops.metal:13-105; wrapper
+// Kernels/TensorCore/MPPPrefillInt4QMM.swift:34-78), the reference's "dequantise a weight tile to half
+// in threadgroup memory, then matrix-unit MMA with an fp32 accumulator" kernel, and the routed prefill
+// kernels prefill_grouped_routed_moe_batched_phase1 / _down (Metal/Prefill/prefill.metal:598-670),
+// which the reference runs as scalar per-thread dot products.
+//
+//   D[128 weight rows x 128 tokens] += W_tile[128 x 64] . X_tile[128 x 64]^T      per 64-column group
+//
+// Weights are the A operand (M = 128), tokens the B operand (N = 128), both K-major in shared memory
+// with the 128-byte swizzle. Per 64-column step:
+//   - one elected thread issues a TMA tile load (cp.async.bulk.tensor.2d) of the activations;
+//   - 128 dequantiser threads (one per weight row) read their row's 32 packed bytes and group
+//     scale/bias and write w = half(q * s + b), the reference's staged value (tensorops.metal:60-75),
+//     as one swizzled 128-byte row of the A tile;
+//   - one elected thread issues four tcgen05.mma (K = 16 each) per matrix into TMEM accumulators and
+//     commits the stage back to the producers through an mbarrier.
+// After the last step four epilogue warps read the accumulators with tcgen05.ld, apply GeGLU (gate and
+// up accumulate side by side in TMEM) or a plain fp16 store, masked to the group's real tokens.
+// A persistent grid walks (group, token tile, weight-row tile) work items derived on the device from the
+// routing metadata. Every mbarrier wait is bounded; on expiry the kernel records a code and leaves.
+#include <cuda.h>
+
+#include "tf_common.cuh"
+
+namespace tf {
+
+constexpr int kQmmTokens = 128;        // N of the MMA: tokens per tile
+constexpr int kQmmRows = 128;          // M of the MMA: weight rows per tile
+constexpr int kQmmK = 64;              // columns per step = one quantisation group = one 128-byte swizzle row
+constexpr int kQmmStages = 4;
+constexpr int kQmmThreads = 384;       // warp 0: TMA, warp 1: MMA, warps 2-3 idle, 4-7: dequantise, 8-11: epilogue
+constexpr uint32_t kQmmSpin = 1u << 22;
+constexpr uint32_t kErrQmmTimeout = 0x7E000000u;
+constexpr uint32_t kMaxQmmGroups = TF_MAX_ROUTER_EXPERTS + 1;   // rows of the context's group table
+
+struct QmmGroup {
+    const uint8_t* W[2];
+    const uint16_t* S[2];
+    const uint16_t* B[2];
+    uint32_t row_start;     // first row of the group in the (sorted) activation matrix
+    uint32_t count;         // tokens of the group
+    uint32_t tile_start;    // first token tile of the group in the global tile order
+    uint32_t pad;
+};
+
+struct QmmArgs {
+    QmmGroup* groups;       // device array, filled by qmm_prepare_kernel
+    uint32_t* totals;       // device: [0] group count, [1] token tiles
+    // routed source (prepare kernel)
+    const uint8_t* pool_base;
+    uint64_t expert_stride;
+    uint32_t w_off[2], s_off[2], b_off[2];
+    const tf_group* route_groups;
+    const uint32_t* route_counters;
+    // dense source
+    const uint8_t* dense_W[2];
+    const uint16_t* dense_S[2];
+    const uint16_t* dense_B[2];
+    uint32_t dense_tokens;
+    // problem
+    uint32_t rows;          // weight rows (output features)
+    uint32_t k;             // columns (input features)
+    uint16_t* out;          // [tokens, out_stride] fp16
+    uint32_t out_stride;
+    uint32_t round_gate_up; // shared expert: gate and up rounded to fp16 before the activation
+    uint32_t* error;
+};
+
+// ---- PTX wrappers ----
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void q_mbar_init(uint32_t addr, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(count) : "memory");
+}
+__device__ __forceinline__ void q_mbar_arrive(uint32_t addr) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(addr) : "memory");
+}
+__device__ __forceinline__ void q_mbar_expect_tx(uint32_t addr, uint32_t bytes) {
+    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(addr), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool q_mbar_wait(uint32_t addr, uint32_t parity) {
+    for (uint32_t i = 0; i < kQmmSpin; ++i) {
+        uint32_t ok;
+        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int c0, int c1, uint32_t mbar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(smem_dst), "l"(map), "r"(c0), "r"(c1), "r"(mbar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void q_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t mbar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                   "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                   "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major operand tile with the 128-byte swizzle: rows of 128 bytes, 8-row atoms of 1024 bytes.
+__device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16, fp16 x fp16 -> fp32, both operands K-major, M = 128, N = kQmmTokens.
+constexpr uint32_t kQmmIdesc = (1u << 4) | ((uint32_t)(kQmmTokens >> 3) << 17) | ((uint32_t)(kQmmRows >> 4) << 24);
+
+// Builds the group table on the device: routed groups from the routing metadata, or one dense group.
+__global__ void qmm_prepare_kernel(QmmArgs a, int nmat, int dense) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    uint32_t ng, tiles = 0;
+    if (dense) {
+        ng = 1;
+        QmmGroup g{};
+        for (int m = 0; m < nmat; ++m) { g.W[m] = a.dense_W[m]; g.S[m] = a.dense_S[m]; g.B[m] = a.dense_B[m]; }
+        g.row_start = 0; g.count = a.dense_tokens; g.tile_start = 0;
+        a.groups[0] = g;
+        tiles = (a.dense_tokens + kQmmTokens - 1) / kQmmTokens;
+    } else {
+        ng = a.route_counters[0];
+        for (uint32_t i = 0; i < ng; ++i) {
+            const tf_group rg = a.route_groups[i];
+            const uint8_t* blob = a.pool_base + (uint64_t)rg.expert * a.expert_stride;
+            QmmGroup g{};
+            for (int m = 0; m < nmat; ++m) {
+                g.W[m] = blob + a.w_off[m];
+                g.S[m] = reinterpret_cast<const uint16_t*>(blob + a.s_off[m]);
+                g.B[m] = reinterpret_cast<const uint16_t*>(blob + a.b_off[m]);
+            }
+            g.row_start = rg.pair_start; g.count = rg.pair_count; g.tile_start = tiles;
+            a.groups[i] = g;
+            tiles += (rg.pair_count + kQmmTokens - 1) / kQmmTokens;
+        }
+    }
+    a.totals[0] = ng;
+    a.totals[1] = tiles;
+}
+
+template <int NMAT>
+struct QmmSmem {
+    static constexpr uint32_t kATile = kQmmRows * 128;                 // 16 KB
+    static constexpr uint32_t kBTile = kQmmTokens * 128;               // 16 KB
+    static constexpr uint32_t kStage = NMAT * kATile + kBTile;
+    static constexpr uint32_t kRing = kQmmStages * kStage;
+    static constexpr uint32_t kBars = kRing;                           // full_a[S] full_b[S] empty[S] acc_full acc_empty, tmem ptr
+    static constexpr uint32_t kTotal = kRing + 256 + 1024;             // + barriers + slack for 1024-byte alignment
+};
+
+// 16 packed codes (two 32-bit words) of one row -> 16 fp16 weights in column order, w = half(q * s + b).
+// (w & 0x000F000F) | 0x6400 is the fp16 1024 + q, (w & 0x00F000F0) | 0x6400 is 1024 + 16 q; both are exact,
+// the subtraction of 1024 is exact, and the final fma rounds once (tensorops.metal:60-75 stores half(fma(q, s, b))).
+__device__ __forceinline__ void dequant8(uint32_t w, __half2 s, __half2 s16, __half2 b, uint32_t (&out)[4]) {
+    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+    uint32_t t0 = (w & 0x000F000Fu) | 0x64006400u, t1 = (w & 0x00F000F0u) | 0x64006400u;
+    const uint32_t ws = w >> 8;
+    uint32_t t2 = (ws & 0x000F000Fu) | 0x64006400u, t3 = (ws & 0x00F000F0u) | 0x64006400u;
+    __half2 h0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1024), s, b);      // (k0, k4)
+    __half2 h1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1024), s16, b);    // (k1, k5)
+    __half2 h2 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t2), k1024), s, b);      // (k2, k6)
+    __half2 h3 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t3), k1024), s16, b);    // (k3, k7)
+    const uint32_t u0 = *reinterpret_cast<uint32_t*>(&h0), u1 = *reinterpret_cast<uint32_t*>(&h1);
+    const uint32_t u2 = *reinterpret_cast<uint32_t*>(&h2), u3 = *reinterpret_cast<uint32_t*>(&h3);
+    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out[0]) : "r"(u0), "r"(u1));   // (k0, k1)
+    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out[1]) : "r"(u2), "r"(u3));   // (k2, k3)
+    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out[2]) : "r"(u0), "r"(u1));   // (k4, k5)
+    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out[3]) : "r"(u2), "r"(u3));   // (k6, k7)
+}
+
+template <int NMAT>
+__global__ void __launch_bounds__(kQmmThreads, 1)
+qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args) {
+    extern __shared__ uint8_t smem_raw[];
+    using L = QmmSmem<NMAT>;
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;                      // swizzle atoms need 1024-byte alignment
+    uint8_t* base_ptr = smem_raw + (base - raw);
+    const uint32_t bars = base + L::kBars;
+    auto bar_full_a = [&](uint32_t s) { return bars + s * 8; };
+    auto bar_full_b = [&](uint32_t s) { return bars + (kQmmStages + s) * 8; };
+    auto bar_empty = [&](uint32_t s) { return bars + (2 * kQmmStages + s) * 8; };
+    const uint32_t bar_acc_full = bars + 3 * kQmmStages * 8, bar_acc_empty = bar_acc_full + 8;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kBars + 3 * kQmmStages * 8 + 16);
+
+    const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const uint32_t ksteps = args.k / kQmmK;
+    const uint32_t groups_per_row = args.k / kGroup;
+    const uint32_t row_bytes = args.k / 2;
+    const uint32_t wrow_tiles = (args.rows + kQmmRows - 1) / kQmmRows;
+    const uint32_t ngroups = args.totals[0];
+    const uint32_t total_tiles = args.totals[1] * wrow_tiles;
+    constexpr uint32_t kTmemCols = NMAT * kQmmTokens;                  // 128 or 256: a power of two >= 32
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < (uint32_t)kQmmStages; ++s) {
+            q_mbar_init(bar_full_a(s), 4);      // one arrival per dequantiser warp
+            q_mbar_init(bar_full_b(s), 1);      // the TMA thread's expect_tx
+            q_mbar_init(bar_empty(s), 1);       // tcgen05.commit
+        }
+        q_mbar_init(bar_acc_full, 1);           // tcgen05.commit after the last step
+        q_mbar_init(bar_acc_empty, 4);          // one arrival per epilogue warp
+        q_fence_async_smem();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // maps a work item to (group, token tile within the group, weight-row tile)
+    auto locate = [&](uint32_t tile, uint32_t& gi, uint32_t& tt, uint32_t& wt) {
+        const uint32_t tglob = tile / wrow_tiles;
+        wt = tile % wrow_tiles;
+        uint32_t lo = 0, hi = ngroups;                                 // last group with tile_start <= tglob
+        while (hi - lo > 1) {
+            const uint32_t mid = (lo + hi) >> 1;
+            if (args.groups[mid].tile_start <= tglob) lo = mid; else hi = mid;
+        }
+        gi = lo;
+        tt = tglob - args.groups[lo].tile_start;
+    };
+
+    uint32_t fail = 0;
+    uint32_t it = 0;         // running k-step index over all of this CTA's tiles (ring position)
+    uint32_t local_tile = 0; // tiles done by this CTA (accumulator barrier phase)
+
+    if (warp == 0) {
+        // ===================== TMA producer: activation tiles =====================
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
+            uint32_t gi, tt, wt;
+            locate(tile, gi, tt, wt);
+            const uint32_t row0 = args.groups[gi].row_start + tt * kQmmTokens;
+            for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                const uint32_t s = it % kQmmStages, use = it / kQmmStages;
+                if (use > 0 && !q_mbar_wait(bar_empty(s), (use - 1) & 1)) { fail = kErrQmmTimeout | 1; break; }
+                if (lane == 0) {
+                    q_mbar_expect_tx(bar_full_b(s), L::kBTile);
+                    tma_load_2d(base + s * L::kStage + NMAT * L::kATile, &x_map, (int)(ks * kQmmK), (int)row0, bar_full_b(s));
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp == 1) {
+        // ===================== MMA issuer =====================
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x, ++local_tile) {
+            if (local_tile > 0 && !q_mbar_wait(bar_acc_empty, (local_tile - 1) & 1)) { fail = kErrQmmTimeout | 2; break; }
+            tc_fence_after();
+            for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                const uint32_t s = it % kQmmStages, use = it / kQmmStages;
+                if (!q_mbar_wait(bar_full_a(s), use & 1) || !q_mbar_wait(bar_full_b(s), use & 1)) { fail = kErrQmmTimeout | 3; break; }
+                tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t stage = base + s * L::kStage;
+                    const uint64_t b_desc = umma_smem_desc(stage + NMAT * L::kATile);
+#pragma unroll
+                    for (int m = 0; m < NMAT; ++m) {
+                        const uint64_t a_desc = umma_smem_desc(stage + m * L::kATile);
+#pragma unroll
+                        for (int j = 0; j < kQmmK / 16; ++j)      // 16 columns = 32 bytes along K per MMA
+                            tc_mma_f16(tmem_base + m * kQmmTokens, a_desc + (uint64_t)(j * 2), b_desc + (uint64_t)(j * 2), kQmmIdesc,
+                                       (ks > 0 || j > 0) ? 1u : 0u);
+                    }
+                    tc_commit(bar_empty(s));                      // the stage is free once these MMAs have read it
+                    if (ks + 1 == ksteps) tc_commit(bar_acc_full);
+                }
+                __syncwarp();
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ===================== dequantisers: one weight row per thread =====================
+        const uint32_t r = (warp - 4) * kWarp + lane;            // row within the tile
+        const uint32_t row_off = (r >> 3) * 1024 + (r & 7) * 128, sw = r & 7;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
+            uint32_t gi, tt, wt;
+            locate(tile, gi, tt, wt);
+            const QmmGroup grp = args.groups[gi];
+            const uint32_t wrow = wt * kQmmRows + r;
+            const bool valid = wrow < args.rows;
+            for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                const uint32_t s = it % kQmmStages, use = it / kQmmStages;
+                // fetch this step's codes and scale before waiting for the stage
+                uint4 codes[NMAT][2];
+                uint32_t sb[NMAT][2];
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m) {
+                    if (valid) {
+                        const uint4* wp = reinterpret_cast<const uint4*>(grp.W[m] + (size_t)wrow * row_bytes + ks * 32);
+                        codes[m][0] = __ldg(wp); codes[m][1] = __ldg(wp + 1);
+                        sb[m][0] = grp.S[m][(size_t)wrow * groups_per_row + ks];
+                        sb[m][1] = grp.B[m][(size_t)wrow * groups_per_row + ks];
+                    } else {
+                        codes[m][0] = codes[m][1] = make_uint4(0u, 0u, 0u, 0u);
+                        sb[m][0] = sb[m][1] = 0u;
+                    }
+                }
+                if (use > 0 && !q_mbar_wait(bar_empty(s), (use - 1) & 1)) { fail = kErrQmmTimeout | 4; break; }
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m) {
+                    const float sf = bf16_bits_to_float((uint16_t)sb[m][0]), bf = bf16_bits_to_float((uint16_t)sb[m][1]);
+                    const __half2 s2 = __float2half2_rn(sf), s16 = __float2half2_rn(sf * 0.0625f), b2 = __float2half2_rn(bf);
+                    uint8_t* arow = base_ptr + s * L::kStage + m * L::kATile + row_off;
+                    const uint32_t w[8] = {codes[m][0].x, codes[m][0].y, codes[m][0].z, codes[m][0].w,
+                                           codes[m][1].x, codes[m][1].y, codes[m][1].z, codes[m][1].w};
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {                 // 8 codes -> 16 bytes = one swizzle chunk
+                        uint32_t o[4];
+                        dequant8(w[c], s2, s16, b2, o);
+                        *reinterpret_cast<uint4*>(arow + ((c ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+                q_fence_async_smem();                             // generic writes -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) q_mbar_arrive(bar_full_a(s));
+            }
+        }
+    } else if (warp >= 8) {
+        // ===================== epilogue: TMEM -> registers -> global =====================
+        const uint32_t q = warp & 3;                              // TMEM lane quarter this warp may read
+        const uint32_t r = q * kWarp + lane;                      // weight row within the tile = TMEM lane
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x, ++local_tile) {
+            uint32_t gi, tt, wt;
+            locate(tile, gi, tt, wt);
+            const QmmGroup grp = args.groups[gi];
+            const uint32_t wrow = wt * kQmmRows + r;
+            const uint32_t tok0 = tt * kQmmTokens;
+            const uint32_t ntok = grp.count - tok0 < (uint32_t)kQmmTokens ? grp.count - tok0 : (uint32_t)kQmmTokens;
+            if (!q_mbar_wait(bar_acc_full, local_tile & 1)) { fail = kErrQmmTimeout | 5; break; }
+            tc_fence_after();
+            for (uint32_t c0 = 0; c0 < (uint32_t)kQmmTokens; c0 += 32) {
+                uint32_t v0[32], v1[32];
+                tc_ld32(tmem_base + ((q * kWarp) << 16) + c0, v0);
+                if (NMAT == 2) tc_ld32(tmem_base + ((q * kWarp) << 16) + kQmmTokens + c0, v1);
+                tc_wait_ld();
+                if (wrow < args.rows) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t tok = c0 + j;
+                        if (tok < ntok) {
+                            float y = __uint_as_float(v0[j]);
+                            if (NMAT == 2) {
+                                float gt = y, up = __uint_as_float(v1[j]);
+                                if (args.round_gate_up) {          // Kernels/MoE/SharedExpertInt4.swift:62-93
+                                    gt = __half2float(__float2half_rn(gt));
+                                    up = __half2float(__float2half_rn(up));
+                                }
+                                y = gelu_tanh(gt) * up;            // prefill.metal:634-636
+                            }
+                            args.out[(size_t)(grp.row_start + tok0 + tok) * args.out_stride + wrow] = __half_as_ushort(__float2half_rn(y));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) q_mbar_arrive(bar_acc_empty);
+        }
+    }
+    if (fail && lane == 0) atomicCAS(args.error, 0u, fail);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- host side ----
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// fp16 matrix [rows, k] with a row stride: box = 64 columns x 128 rows, 128-byte swizzle, zero fill outside.
+static tf_status make_x_map(tf_context* ctx, CUtensorMap* map, const void* x, uint64_t rows, uint32_t k, uint32_t stride_elems,
+                            const char* name) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    TF_REQUIRE(ctx, fn != nullptr, TF_ERR_UNSUPPORTED, "%s: cuTensorMapEncodeTiled is not available in this driver", name);
+    const cuuint64_t dims[2] = {k, rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)stride_elems * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kQmmK, (cuuint32_t)kQmmTokens};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TF_REQUIRE(ctx, r == CUDA_SUCCESS, TF_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed (%d)", name, (int)r);
+    return TF_OK;
+}
+
+template <int NMAT>
+static tf_status launch_qmm(tf_context* ctx, void* stream, QmmArgs& a, const void* x, uint64_t x_rows, uint32_t x_stride,
+                            bool dense, const char* name) {
+    TF_REQUIRE(ctx, a.k % kQmmK == 0 && a.k >= (uint32_t)kQmmK, TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);
+    TF_REQUIRE(ctx, aligned(x, 16) && (x_stride * 2) % 16 == 0, TF_ERR_ALIGNMENT, "%s: activation rows must be 16-byte aligned", name);
+    TF_REQUIRE(ctx, ctx->qmm_groups != nullptr, TF_ERR_OUT_OF_MEMORY, "%s: context scratch missing", name);
+    CUtensorMap map;
+    if (tf_status s = make_x_map(ctx, &map, x, x_rows, a.k, x_stride, name)) return s;
+    a.groups = static_cast<QmmGroup*>(ctx->qmm_groups);
+    a.totals = ctx->qmm_totals;
+    a.error = ctx->device_error;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    qmm_prepare_kernel<<<1, 32, 0, st>>>(a, NMAT, dense ? 1 : 0);
+    if (tf_status s = check_launch(ctx, "qmm_prepare")) return s;
+    auto kern = qmm_tcgen05_kernel<NMAT>;
+    static bool configured = false;
+    if (!configured) {
+        TF_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QmmSmem<NMAT>::kTotal));
+        configured = true;
+    }
+    kern<<<ctx->sm_count, kQmmThreads, QmmSmem<NMAT>::kTotal, st>>>(map, a);
+    return check_launch(ctx, name);
+}
+
+}  // namespace tf
+
+extern "C" {
+
+tf_status tf_grouped_moe_tensorcore(tf_context* ctx, void* stream, const void* x_sorted, uint32_t x_rows,
+                                    const void* pool_layer_base, uint64_t expert_stride, const tf_expert_offsets* offsets,
+                                    const tf_device_routes* routes, void* acts_scratch, void* out_rows,
+                                    uint32_t d, uint32_t f) {
+    const char* name = "tf_grouped_moe_tensorcore";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, x_sorted && pool_layer_base && offsets && routes && acts_scratch && out_rows, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    TF_REQUIRE(ctx, d % 64 == 0 && f % 64 == 0 && d > 0 && f > 0, TF_ERR_INVALID_ARGUMENT, "%s: D and F must be positive multiples of 64", name);
+    const uint32_t all[9] = {offsets->gate_w_off, offsets->gate_s_off, offsets->gate_b_off, offsets->up_w_off, offsets->up_s_off,
+                             offsets->up_b_off, offsets->down_w_off, offsets->down_s_off, offsets->down_b_off};
+    for (uint32_t v : all) TF_REQUIRE(ctx, v % 16 == 0, TF_ERR_ALIGNMENT, "%s: blob sub-tensor offset %u is not a multiple of 16 bytes", name, v);
+    TF_REQUIRE(ctx, tf::aligned(pool_layer_base, 16) && expert_stride % 16 == 0, TF_ERR_ALIGNMENT, "%s: pool must be 16-byte aligned", name);
+    if (x_rows == 0) return TF_OK;
+    tf::QmmArgs a{};
+    a.pool_base = static_cast<const uint8_t*>(pool_layer_base); a.expert_stride = expert_stride;
+    a.w_off[0] = offsets->gate_w_off; a.s_off[0] = offsets->gate_s_off; a.b_off[0] = offsets->gate_b_off;
+    a.w_off[1] = offsets->up_w_off;   a.s_off[1] = offsets->up_s_off;   a.b_off[1] = offsets->up_b_off;
+    a.route_groups = routes->groups; a.route_counters = routes->counters;
+    a.rows = f; a.k = d; a.out = static_cast<uint16_t*>(acts_scratch); a.out_stride = f; a.round_gate_up = 0;
+    if (tf_status s = tf::launch_qmm<2>(ctx, stream, a, x_sorted, x_rows, d, false, "tf_grouped_moe_tensorcore(gate/up)")) return s;
+    tf::QmmArgs b{};
+    b.pool_base = a.pool_base; b.expert_stride = expert_stride;
+    b.w_off[0] = offsets->down_w_off; b.s_off[0] = offsets->down_s_off; b.b_off[0] = offsets->down_b_off;
+    b.route_groups = routes->groups; b.route_counters = routes->counters;
+    b.rows = d; b.k = f; b.out = static_cast<uint16_t*>(out_rows); b.out_stride = d;
+    return tf::launch_qmm<1>(ctx, stream, b, acts_scratch, x_rows, f, false, "tf_grouped_moe_tensorcore(down)");
+}
+
+tf_status tf_int4_qmm(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off, const void* scales,
+                      uint64_t scales_off, const void* biases, uint64_t biases_off, const void* x, uint64_t x_off,
+                      void* y, uint64_t y_off, uint32_t m, uint32_t n, uint32_t k) {
+    const char* name = "tf_int4_qmm";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, weights && scales && biases && x && y, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, k % 64 == 0 && k > 0, TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);   // MPPPrefillInt4QMM.swift:43-55
+    if (m == 0 || n == 0) return TF_OK;
+    tf::QmmArgs a{};
+    a.dense_W[0] = tf::byte_ptr(weights, weights_off);
+    a.dense_S[0] = reinterpret_cast<const uint16_t*>(tf::byte_ptr(scales, scales_off));
+    a.dense_B[0] = reinterpret_cast<const uint16_t*>(tf::byte_ptr(biases, biases_off));
+    TF_REQUIRE(ctx, tf::aligned(a.dense_W[0], 16) && tf::aligned(a.dense_S[0], 2) && tf::aligned(a.dense_B[0], 2) && (k / 2) % 16 == 0,
+               TF_ERR_ALIGNMENT, "%s: packed rows must be 16-byte aligned", name);
+    a.dense_tokens = m; a.rows = n; a.k = k;
+    a.out = reinterpret_cast<uint16_t*>(tf::byte_ptr(y, y_off)); a.out_stride = n;
+    return tf::launch_qmm<1>(ctx, stream, a, tf::byte_ptr(x, x_off), m, k, true, name);
+}
+
+tf_status tf_shared_expert_int4_tensorcore(tf_context* ctx, void* stream, const void* x, uint32_t x_stride_elements,
+                                           const tf_projection* gate, const tf_projection* up, const tf_projection* down,
+                                           void* y, uint32_t y_stride_elements, void* scratch_act, uint32_t rows) {
+    const char* name = "tf_shared_expert_int4_tensorcore";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, x && gate && up && down && y && scratch_act, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    TF_REQUIRE(ctx, gate->rows == up->rows && gate->cols == up->cols && down->rows == gate->cols && down->cols == gate->rows,
+               TF_ERR_DIMENSION_MISMATCH, "SharedExpert dimension mismatch: gate=(%u,%u) up=(%u,%u) down=(%u,%u)",
+               gate->rows, gate->cols, up->rows, up->cols, down->rows, down->cols);
+    if (rows == 0) return TF_OK;
+    const uint32_t fs = gate->rows, d = gate->cols;
+    const tf_projection* ps[3] = {gate, up, down};
+    const uint8_t* W[3]; const uint16_t* S[3]; const uint16_t* B[3];
+    for (int i = 0; i < 3; ++i) {
+        W[i] = tf::byte_ptr(ps[i]->weights, ps[i]->weights_off);
+        S[i] = reinterpret_cast<const uint16_t*>(tf::byte_ptr(ps[i]->scales, ps[i]->scales_off));
+        B[i] = reinterpret_cast<const uint16_t*>(tf::byte_ptr(ps[i]->biases, ps[i]->biases_off));
+        TF_REQUIRE(ctx, tf::aligned(W[i], 16) && tf::aligned(S[i], 2) && tf::aligned(B[i], 2), TF_ERR_ALIGNMENT, "%s: planes must be 16-byte aligned", name);
+    }
+    tf::QmmArgs a{};
+    a.dense_W[0] = W[0]; a.dense_S[0] = S[0]; a.dense_B[0] = B[0];
+    a.dense_W[1] = W[1]; a.dense_S[1] = S[1]; a.dense_B[1] = B[1];
+    a.dense_tokens = rows; a.rows = fs; a.k = d; a.out = static_cast<uint16_t*>(scratch_act); a.out_stride = fs; a.round_gate_up = 1;
+    if (tf_status s = tf::launch_qmm<2>(ctx, stream, a, x, rows, x_stride_elements, true, "tf_shared_expert_int4_tensorcore(gate/up)")) return s;
+    tf::QmmArgs b{};
+    b.dense_W[0] = W[2]; b.dense_S[0] = S[2]; b.dense_B[0] = B[2];
+    b.dense_tokens = rows; b.rows = d; b.k = fs; b.out = static_cast<uint16_t*>(y); b.out_stride = y_stride_elements;
+    return tf::launch_qmm<1>(ctx, stream, b, scratch_act, rows, fs, true, "tf_shared_expert_int4_tensorcore(down)");
+}
+
+}  // extern "C"

@@ -40,6 +40,9 @@ struct tf_context {
     unsigned int* router_tickets = nullptr;  // [kRouterSplitRows], self-resetting
     // One device word that kernels with bounded waits set when a wait gives up (0 = healthy).
     uint32_t* device_error = nullptr;
+    // Group table and tile totals of the tensor-core grouped GEMM (filled on the device per launch).
+    void* qmm_groups = nullptr;
+    uint32_t* qmm_totals = nullptr;
 };
 
 namespace tf {

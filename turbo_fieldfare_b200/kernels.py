@@ -372,6 +372,30 @@ class PrefillGroupedRoutedMoE:
             1 if partials_f32 else 0, query_count, d, f, top_k))
 
 
+    def encode_tensorcore(self, x_sorted, x_rows: int, pool_layer_base, expert_stride: int, offsets: ExpertOffsets,
+                          routes: DeviceRoutes, acts_scratch, out_rows, d: int, f: int, *, stream=None):
+        """Same operator on the tcgen05 tensor cores over expert-sorted rows (``tf_grouped_moe_tensorcore``)."""
+        ctx = self.context
+        ctx.check(ctx.lib.tf_grouped_moe_tensorcore(
+            ctx.handle, _stream(stream), _ptr(x_sorted), x_rows, _ptr(pool_layer_base), expert_stride,
+            C.byref(offsets), C.byref(routes.c_struct), _ptr(acts_scratch), _ptr(out_rows), d, f))
+
+
+class MPPPrefillInt4QMM:
+    """``MPPPrefillInt4QMM`` (Kernels/TensorCore/MPPPrefillInt4QMM.swift:4-79): Y[M,N] = X[M,K] . deq4(W[N,K])^T with
+    the weight tile staged as half and multiplied on the matrix unit (tcgen05 here, TensorOps there)."""
+
+    def __init__(self, context: TurboContext):
+        self.context = context
+
+    def encode(self, weights, scales, biases, x, y, m: int, n: int, k: int, *, weights_offset=0, scales_offset=0,
+               biases_offset=0, x_offset=0, y_offset=0, stream=None):
+        ctx = self.context
+        ctx.check(ctx.lib.tf_int4_qmm(ctx.handle, _stream(stream), _ptr(weights), weights_offset, _ptr(scales),
+                                      scales_offset, _ptr(biases), biases_offset, _ptr(x), x_offset, _ptr(y), y_offset,
+                                      m, n, k))
+
+
 class PrefillMoE:
     """``PrefillMoE`` (Kernels/Prefill/MoE/PrefillMoE.swift:4-40)."""
 
@@ -400,4 +424,15 @@ class PrefillSharedExpert:
         ctx.check(ctx.lib.tf_shared_expert_int4_block(
             ctx.handle, _stream(stream), _ptr(x), x_offset, gate.cols if x_stride is None else x_stride,
             C.byref(g), C.byref(u), C.byref(dn), _ptr(y), y_offset, gate.cols if y_stride is None else y_stride,
+            _ptr(scratch_act), rows))
+
+    def encode_block_tensorcore(self, x, gate: SharedExpertProjection, up: SharedExpertProjection,
+                                down: SharedExpertProjection, y, scratch_act, rows: int, *, x_stride=None, y_stride=None,
+                                stream=None):
+        """The block on the tcgen05 tensor cores (``tf_shared_expert_int4_tensorcore``), for prefill-sized blocks."""
+        ctx = self.context
+        g, u, dn = gate.c_struct(), up.c_struct(), down.c_struct()
+        ctx.check(ctx.lib.tf_shared_expert_int4_tensorcore(
+            ctx.handle, _stream(stream), _ptr(x), gate.cols if x_stride is None else x_stride,
+            C.byref(g), C.byref(u), C.byref(dn), _ptr(y), gate.cols if y_stride is None else y_stride,
             _ptr(scratch_act), rows))
