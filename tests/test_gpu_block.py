@@ -135,6 +135,41 @@ def test_block_forward_with_zipf_bias_and_fp16_partials(tf_ctx, oracle, producti
         layer.set_logit_bias(None)
 
 
+@pytest.mark.parametrize("T,zipf", [(256, False), (1000, True)])
+def test_block_forward_prefill_sized_runs_on_tensor_cores(tf_ctx, oracle, production_layer, T, zipf):
+    """From 256 tokens the block runs pack -> tcgen05 grouped GEMMs -> combine; same router decisions, outputs
+    within the same 1e-2 relative L2 of the per-token oracle."""
+    import torch
+    from turbo_fieldfare_b200.stack import MoEBlock, Workspace
+    o = oracle
+    layer, pool = production_layer
+    rng = np.random.default_rng(70 + T)
+    bias = None
+    if zipf:
+        p = 1.0 / (rng.permutation(128) + 1) ** 1.1
+        bias = np.log(p / p.sum()).astype(np.float32)
+    layer.set_logit_bias(bias)
+    try:
+        x16 = o.f32_to_f16(rng.standard_normal((T, 2816)).astype(np.float32))
+        ws = Workspace(tf_ctx, T, 2816, 704, 2112, 8, 128)
+        y = torch.zeros(T * 2816, dtype=torch.int16, device="cuda")
+        before = tf_ctx.launch_count
+        MoEBlock(tf_ctx, layer).forward(to_dev(x16), y, T, ws)
+        torch.cuda.synchronize()
+        assert tf_ctx.device_status() == 0
+        assert tf_ctx.launch_count - before == 12     # router, grouping, pack, 3 x (prepare + GEMM) ... combine
+        idx_gpu, _ = ws.routing(T)
+        check = (0, T // 2, T - 1)
+        idx_ref, y_ref, _ = _oracle_block(o, layer, pool, x16, check, logit_bias=bias)
+        assert np.array_equal(idx_gpu[list(check)], idx_ref[list(check)])
+        got = o.f16_to_f32(from_dev(y, np.uint16).reshape(T, 2816))
+        assert np.isfinite(got).all()
+        for i, t in enumerate(check):
+            assert o.rel_l2(got[t], y_ref[i]) < TOL, f"token {t}"
+    finally:
+        layer.set_logit_bias(None)
+
+
 def test_small_stack_matches_oracle(tf_ctx, oracle):
     """Config-4 structure at small dimensions: 3 layers, RMSNorm between layers, residual stream."""
     import torch

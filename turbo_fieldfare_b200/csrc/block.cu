@@ -34,6 +34,9 @@ struct tf_workspace {
     uint16_t* shared_y;     // [T, D]
     uint16_t* x_norm;       // [T, D] (stack)
     uint16_t* y_block;      // [T, D] (stack)
+    uint16_t* x_sorted;     // [T*K, D] expert-sorted activation rows (tensor-core path; NULL for small workspaces)
+    uint32_t* inverse_perm; // [T*K] sorted row of every (token, rank)
+    uint32_t* pack_ids;     // [T*K]
     uint64_t bytes;
 };
 
@@ -47,6 +50,10 @@ struct tf_stack {
 namespace tf {
 
 constexpr uint32_t kF32PartialTokens = 64;   // decode-sized batches keep fp32 partials (decode kernel semantics)
+// From this many tokens a block forward runs the expert GEMMs on the tensor cores (128-token tiles per expert:
+// 256 tokens x top-8 over 128 experts is 16 pairs per expert on average, where a 128-wide tile already beats
+// eight-token CUDA-core chunks because the weight tile is dequantised once instead of twice).
+constexpr uint32_t kTensorCoreTokens = 256;
 
 __device__ __forceinline__ uint64_t mix64(uint64_t z) {
     z += 0x9E3779B97F4A7C15ull;
@@ -259,6 +266,9 @@ tf_status tf_workspace_create(tf_context* ctx, uint32_t max_tokens, uint32_t d, 
                    o_cstart = take(E * 4), o_counters = take(16), o_acts = take(T * K * f * 2),
                    o_partials = take(T * K * d * (T <= tf::kF32PartialTokens ? 4 : 2)), o_sact = take(T * fs * 2),
                    o_sy = take(T * d * 2), o_xn = take(T * d * 2), o_yb = take(T * d * 2);
+    const bool tensor_path = T >= tf::kTensorCoreTokens && d % 64 == 0 && f % 64 == 0 && fs % 64 == 0;
+    const uint64_t o_xs = tensor_path ? take(T * K * d * 2) : 0, o_inv = tensor_path ? take(T * K * 4) : 0,
+                   o_pid = tensor_path ? take(T * K * 4) : 0;
     uint8_t* base = nullptr;
     cudaError_t e = cudaMalloc(&base, off);
     if (e != cudaSuccess) {
@@ -284,6 +294,9 @@ tf_status tf_workspace_create(tf_context* ctx, uint32_t max_tokens, uint32_t d, 
     w->shared_y = reinterpret_cast<uint16_t*>(base + o_sy);
     w->x_norm = reinterpret_cast<uint16_t*>(base + o_xn);
     w->y_block = reinterpret_cast<uint16_t*>(base + o_yb);
+    w->x_sorted = tensor_path ? reinterpret_cast<uint16_t*>(base + o_xs) : nullptr;
+    w->inverse_perm = tensor_path ? reinterpret_cast<uint32_t*>(base + o_inv) : nullptr;
+    w->pack_ids = tensor_path ? reinterpret_cast<uint32_t*>(base + o_pid) : nullptr;
     *out = w;
     return TF_OK;
 }
@@ -328,6 +341,21 @@ tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer
     if (s) return s;
     s = tf_group_routes_device(ctx, stream, ws->indices, ws->weights, tokens, K, E, &ws->routes);
     if (s) return s;
+    if (tokens >= tf::kTensorCoreTokens && ws->x_sorted != nullptr) {
+        // Prefill-sized block: gather the rows into expert order, run gate/up/GeGLU/down and the shared expert as
+        // tcgen05 GEMMs, then fold the sorted rows back per token in rank order.
+        s = tf_ep_pack(ctx, stream, x, 0, x_stride_elements, &ws->routes, tokens, K, E, E, 0, d, ws->x_sorted, ws->pack_ids,
+                       ws->inverse_perm);
+        if (s) return s;
+        s = tf_grouped_moe_tensorcore(ctx, stream, ws->x_sorted, tokens * K, layer->pool_layer_base, layer->expert_stride,
+                                      &layer->offsets, &ws->routes, ws->acts, ws->partials, d, f);
+        if (s) return s;
+        s = tf_shared_expert_int4_tensorcore(ctx, stream, x, x_stride_elements, &layer->shared_gate, &layer->shared_up,
+                                             &layer->shared_down, ws->shared_y, d, ws->shared_act, tokens);
+        if (s) return s;
+        return tf_ep_combine(ctx, stream, ws->partials, ws->weights, ws->inverse_perm, ws->shared_y, d, y, y_stride_elements,
+                             tokens, K, d);
+    }
     // The partial dtype follows the workspace's capacity so that one workspace
     // always runs the same arithmetic whatever the call's token count.
     const int f32 = ws->max_tokens <= tf::kF32PartialTokens ? 1 : 0;

@@ -22,10 +22,20 @@ def case_block(args) -> None:
     stack = MoEStack(ctx, layers=args.layers, seed=3)
     ws = stack.workspace(args.tokens)
     h = torch.randn(args.tokens, 2816, device="cuda").half()
+    if args.zipf > 0:
+        import numpy as np
+        p = 1.0 / (np.random.default_rng(0).permutation(128) + 1) ** args.zipf
+        stack.set_logit_bias(np.log(p / p.sum()).astype(np.float32))
+    times = []
     for _ in range(args.iters):
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
         stack.forward(h, args.tokens, ws)
-    torch.cuda.synchronize()
-    print(f"block case done: tokens={args.tokens} layers={args.layers} iters={args.iters} launches={ctx.launch_count}")
+        t1.record()
+        torch.cuda.synchronize()
+        times.append(t0.elapsed_time(t1))
+    print(f"block case done: tokens={args.tokens} layers={args.layers} iters={args.iters} launches={ctx.launch_count} "
+          f"status={ctx.device_status()} ms_per_forward={[round(t, 3) for t in times]}")
 
 
 def case_gemv(args) -> None:
@@ -48,6 +58,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--rows", type=int, default=262144)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--zipf", type=float, default=0.0, help="router logit bias log(p), p ~ 1/rank^zipf (0 = none)")
     args = ap.parse_args()
     {"block": case_block, "gemv": case_gemv}[args.case](args)
 
