@@ -300,10 +300,18 @@ tf_status tf_int4_qmm(tf_context* ctx, void* stream,
                       const void* biases, uint64_t biases_off,
                       const void* x, uint64_t x_off, void* y, uint64_t y_off,
                       uint32_t m, uint32_t n, uint32_t k);
-/* Routed experts over expert-sorted rows: x_sorted[x_rows, D] holds the gathered hidden row of every
- * (token, expert) pair in the order of routes->sorted_pairs (tf_ep_pack makes it);
- * acts_scratch[x_rows, F] = half(gelu(gate.x) * (up.x)); out_rows[x_rows, D] = half(down.act), still in
- * sorted order (tf_ep_combine folds them back per token). Same mathematics as tf_grouped_moe_batched with
+/* Gathers the hidden row of every (token, expert) pair into x_sorted[T*top_k, D] in the order of
+ * routes->sorted_pairs, with every eight columns stored in the order (0,4,1,5,2,6,3,7) that
+ * tf_grouped_moe_tensorcore reads, and records inverse_perm[token*top_k + rank] = sorted row.
+ * row_expert_ids[T*top_k] receives each row's expert. Replaces the per-pair hidden gather inside
+ * prefill_grouped_routed_moe_batched_phase1 (Metal/Prefill/prefill.metal:598-640). */
+tf_status tf_pack_sorted_rows(tf_context* ctx, void* stream, const void* hidden, uint32_t hidden_stride_elements,
+                              const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                              uint32_t d, void* x_sorted, uint32_t* row_expert_ids, uint32_t* inverse_perm);
+/* Routed experts over expert-sorted rows: x_sorted[x_rows, D] from tf_pack_sorted_rows;
+ * acts_scratch[x_rows, F] = half(gelu(gate.x) * (up.x)) (scratch, same permuted column order);
+ * out_rows[x_rows, D] = half(down.act) in natural column order, still in sorted row order
+ * (tf_ep_combine folds them back per token). Same mathematics as tf_grouped_moe_batched with
  * the weights rounded to half(q*s+b) first, the matrix-unit convention of tensorops.metal:60-75. Replaces
  * PrefillGroupedRoutedMoE.encodeStreamedBatched (Kernels/Prefill/MoE/PrefillGroupedRoutedMoE.swift:386-461)
  * for batches large enough to fill 128-token tiles. */

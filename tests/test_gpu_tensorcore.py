@@ -73,7 +73,16 @@ def test_grouped_tensorcore_vs_oracle_and_cuda_cores(tf_ctx, oracle, T, D, F, E,
     host = routes.to_host(T)
     tok = host.sorted_pairs["token"].astype(np.int64)
     rank = host.sorted_pairs["rank"].astype(np.int64)
-    x_sorted = to_dev(np.ascontiguousarray(h16[tok]))
+    x_sorted = dev_zeros_u16(T * K * D)
+    row_ids = torch.zeros(T * K, dtype=torch.int32, device="cuda")
+    inverse = torch.zeros(T * K, dtype=torch.int32, device="cuda")
+    moe.encode_pack_sorted_rows(to_dev(h16), routes, T, K, E, D, x_sorted, row_ids, inverse)
+    torch.cuda.synchronize()
+    # the pack stores every eight columns as (0,4,1,5,2,6,3,7) and records where each (token, rank) went
+    packed = from_dev(x_sorted, np.uint16).reshape(T * K, D // 8, 8)
+    assert np.array_equal(packed, h16[tok].reshape(T * K, D // 8, 8)[:, :, [0, 4, 1, 5, 2, 6, 3, 7]])
+    assert np.array_equal(from_dev(row_ids, np.uint32), host.sorted_pairs["expert"])
+    assert np.array_equal(from_dev(inverse, np.uint32).reshape(T, K)[tok, rank], np.arange(T * K))
     pool = to_dev(pool_h)
     acts = dev_zeros_u16(T * K * F)
     out_rows = dev_zeros_u16(T * K * D, fill=0x7E00)

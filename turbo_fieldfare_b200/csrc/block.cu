@@ -344,8 +344,8 @@ tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer
     if (tokens >= tf::kTensorCoreTokens && ws->x_sorted != nullptr) {
         // Prefill-sized block: gather the rows into expert order, run gate/up/GeGLU/down and the shared expert as
         // tcgen05 GEMMs, then fold the sorted rows back per token in rank order.
-        s = tf_ep_pack(ctx, stream, x, 0, x_stride_elements, &ws->routes, tokens, K, E, E, 0, d, ws->x_sorted, ws->pack_ids,
-                       ws->inverse_perm);
+        s = tf_pack_sorted_rows(ctx, stream, x, x_stride_elements, &ws->routes, tokens, K, E, d, ws->x_sorted, ws->pack_ids,
+                                ws->inverse_perm);
         if (s) return s;
         s = tf_grouped_moe_tensorcore(ctx, stream, ws->x_sorted, tokens * K, layer->pool_layer_base, layer->expert_stride,
                                       &layer->offsets, &ws->routes, ws->acts, ws->partials, d, f);

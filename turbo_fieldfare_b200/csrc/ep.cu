@@ -15,7 +15,9 @@ namespace tf {
 constexpr int kPackThreads = 256;
 
 // One warp per send slot. Fixed-capacity mode: slot = dst * capacity + pos. Exact mode (n_dst == 1):
-// slot = sorted pair index.
+// slot = sorted pair index. PERMUTE_K8 stores every eight columns in the order (0,4,1,5,2,6,3,7), the
+// activation layout of the tensor-core grouped GEMM.
+template <bool PERMUTE_K8>
 __global__ void __launch_bounds__(kPackThreads)
 ep_pack_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride, const tf_pair* __restrict__ sorted_pairs,
                const uint32_t* __restrict__ per_expert_counts, uint32_t n_pairs, uint32_t top_k, uint32_t num_experts,
@@ -60,7 +62,18 @@ ep_pack_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride, cons
     }
     const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)pr.token * hidden_stride);
     uint4* dst_row = reinterpret_cast<uint4*>(send_rows + (size_t)slot * d);
-    for (uint32_t i = lane; i < d / 8; i += kWarp) dst_row[i] = __ldg(src + i);
+    for (uint32_t i = lane; i < d / 8; i += kWarp) {
+        uint4 v = __ldg(src + i);
+        if (PERMUTE_K8) {
+            uint4 o;
+            asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(o.x) : "r"(v.x), "r"(v.z));   // (k0, k4)
+            asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(o.y) : "r"(v.x), "r"(v.z));   // (k1, k5)
+            asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(o.z) : "r"(v.y), "r"(v.w));   // (k2, k6)
+            asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(o.w) : "r"(v.y), "r"(v.w));   // (k3, k7)
+            v = o;
+        }
+        dst_row[i] = v;
+    }
 }
 
 // y[t,d] = half(sum_r fma(w[t,r], partial[inverse[t*K+r]][d], acc) + residual[t,d]), rank order.
@@ -84,11 +97,10 @@ __global__ void ep_combine_kernel(const uint16_t* __restrict__ rows, const uint1
 
 extern "C" {
 
-tf_status tf_ep_pack(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off, uint32_t hidden_stride_elements,
-                     const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
-                     uint32_t experts_per_rank, uint32_t capacity, uint32_t d,
-                     void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm) {
-    const char* name = "tf_ep_pack";
+static tf_status pack_rows(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off, uint32_t hidden_stride_elements,
+                           const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                           uint32_t experts_per_rank, uint32_t capacity, uint32_t d,
+                           void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm, bool permute_k8, const char* name) {
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, hidden && routes && send_rows && send_expert_ids && inverse_perm, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
     TF_REQUIRE(ctx, experts_per_rank > 0 && num_experts % experts_per_rank == 0 && num_experts <= TF_MAX_ROUTER_EXPERTS,
@@ -102,11 +114,27 @@ tf_status tf_ep_pack(tf_context* ctx, void* stream, const void* hidden, uint64_t
     const uint32_t n_dst = capacity > 0 ? num_experts / experts_per_rank : 1;
     const uint32_t slots = capacity > 0 ? n_dst * capacity : n_pairs;
     const uint32_t per_block = tf::kPackThreads / tf::kWarp;
-    tf::ep_pack_kernel<<<(slots + per_block - 1) / per_block, tf::kPackThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+    auto kern = permute_k8 ? tf::ep_pack_kernel<true> : tf::ep_pack_kernel<false>;
+    kern<<<(slots + per_block - 1) / per_block, tf::kPackThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const uint16_t*>(hp), hidden_stride_elements, routes->sorted_pairs, routes->per_expert_counts, n_pairs,
         top_k, num_experts, experts_per_rank, n_dst, capacity, d, static_cast<uint16_t*>(send_rows), send_expert_ids,
         inverse_perm, ctx->device_error);
     return tf::check_launch(ctx, name);
+}
+
+tf_status tf_ep_pack(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off, uint32_t hidden_stride_elements,
+                     const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                     uint32_t experts_per_rank, uint32_t capacity, uint32_t d,
+                     void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm) {
+    return pack_rows(ctx, stream, hidden, hidden_off, hidden_stride_elements, routes, query_count, top_k, num_experts,
+                     experts_per_rank, capacity, d, send_rows, send_expert_ids, inverse_perm, false, "tf_ep_pack");
+}
+
+tf_status tf_pack_sorted_rows(tf_context* ctx, void* stream, const void* hidden, uint32_t hidden_stride_elements,
+                              const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                              uint32_t d, void* x_sorted, uint32_t* row_expert_ids, uint32_t* inverse_perm) {
+    return pack_rows(ctx, stream, hidden, 0, hidden_stride_elements, routes, query_count, top_k, num_experts, num_experts, 0, d,
+                     x_sorted, row_expert_ids, inverse_perm, true, "tf_pack_sorted_rows");
 }
 
 tf_status tf_ep_combine(tf_context* ctx, void* stream, const void* returned_rows, const void* route_weights,

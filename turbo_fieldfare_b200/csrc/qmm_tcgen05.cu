@@ -6,34 +6,45 @@
 // kernels prefill_grouped_routed_moe_batched_phase1 / _down (Metal/Prefill/prefill.metal:598-670),
 // which the reference runs as scalar per-thread dot products.
 //
-//   D[128 weight rows x 128 tokens] += W_tile[128 x 64] . X_tile[128 x 64]^T      per 64-column group
+//   D[128 weight rows x N tokens] += W_tile[128 x 64] . X_tile[N x 64]^T      per 64-column group, N <= 256
 //
-// Weights are the A operand (M = 128), tokens the B operand (N = 128), both K-major in shared memory
-// with the 128-byte swizzle. Per 64-column step:
-//   - one elected thread issues a TMA tile load (cp.async.bulk.tensor.2d) of the activations;
-//   - 128 dequantiser threads (one per weight row) read their row's 32 packed bytes and group
-//     scale/bias and write w = half(q * s + b), the reference's staged value (tensorops.metal:60-75),
-//     as one swizzled 128-byte row of the A tile;
+// Weights are the A operand (M = 128), tokens the B operand (N = the tile's token count rounded up to 16,
+// carried in the instruction descriptor), both K-major in shared memory with the 128-byte swizzle. Per step:
+//   - one elected thread issues TMA tile loads (cp.async.bulk.tensor.2d, 64 rows each) of the activations;
+//   - 256 dequantiser threads (two per weight row) read 16 packed bytes and the group's scale and bias and
+//     write w = half(q * s + b), the reference's staged value (tensorops.metal:60-75), into the swizzled A tile;
 //   - one elected thread issues four tcgen05.mma (K = 16 each) per matrix into TMEM accumulators and
 //     commits the stage back to the producers through an mbarrier.
-// After the last step four epilogue warps read the accumulators with tcgen05.ld, apply GeGLU (gate and
-// up accumulate side by side in TMEM) or a plain fp16 store, masked to the group's real tokens.
+// After the last step eight epilogue warps read the accumulators with tcgen05.ld and apply GeGLU (gate and
+// up accumulate side by side in TMEM) or a plain fp16 store, masked to the group's real tokens. The single
+// matrix form double-buffers its accumulator so that the epilogue of one tile overlaps the next tile's MMAs.
 // A persistent grid walks (group, token tile, weight-row tile) work items derived on the device from the
 // routing metadata. Every mbarrier wait is bounded; on expiry the kernel records a code and leaves.
+//
+// Column order. The cheapest nibble extraction yields the eight codes of a 32-bit word in the order
+// (0,4,1,5,2,6,3,7). A dot product does not care about the order as long as both operands agree, so the
+// routed path stores its activations (the gathered rows and the GeGLU output) in that order within every
+// eight columns (PERMUTED_K) and skips the four byte-permutes per word; the dense entry points take
+// caller-owned activations in natural order and pay them.
 #include <cuda.h>
 
 #include "tf_common.cuh"
 
 namespace tf {
 
-constexpr int kQmmTokens = 128;        // N of the MMA: tokens per tile
+constexpr int kQmmTokMax = 256;        // largest N of one MMA: tokens per tile
+constexpr int kQmmBoxRows = 64;        // activation rows per TMA box
 constexpr int kQmmRows = 128;          // M of the MMA: weight rows per tile
 constexpr int kQmmK = 64;              // columns per step = one quantisation group = one 128-byte swizzle row
-constexpr int kQmmStages = 4;
-constexpr int kQmmThreads = 384;       // warp 0: TMA, warp 1: MMA, warps 2-3 idle, 4-7: dequantise, 8-11: epilogue
+constexpr int kQmmStages = 3;
+constexpr int kQmmDequantWarps = 8, kQmmEpilogueWarps = 8;
+constexpr int kQmmFirstDequantWarp = 4, kQmmFirstEpilogueWarp = kQmmFirstDequantWarp + kQmmDequantWarps;
+constexpr int kQmmThreads = (kQmmFirstEpilogueWarp + kQmmEpilogueWarps) * 32;   // warp 0: TMA, warp 1: MMA, 2-3 idle
+constexpr int kQmmTmemCols = 512;      // the whole tensor memory: 2 x 256 accumulator columns
 constexpr uint32_t kQmmSpin = 1u << 22;
 constexpr uint32_t kErrQmmTimeout = 0x7E000000u;
-constexpr uint32_t kMaxQmmGroups = TF_MAX_ROUTER_EXPERTS + 1;   // rows of the context's group table
+
+static_assert(kQmmFirstEpilogueWarp % 4 == 0, "epilogue warp w reads TMEM lanes 32 * (w % 4)");
 
 struct QmmGroup {
     const uint8_t* W[2];
@@ -44,6 +55,8 @@ struct QmmGroup {
     uint32_t tile_start;    // first token tile of the group in the global tile order
     uint32_t pad;
 };
+
+static_assert(sizeof(QmmGroup) == 64, "the context allocates 64 bytes per group-table row");
 
 struct QmmArgs {
     QmmGroup* groups;       // device array, filled by qmm_prepare_kernel
@@ -103,13 +116,11 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-                   "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-                   "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                  : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
@@ -118,8 +129,10 @@ __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
     return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
-// kind::f16, fp16 x fp16 -> fp32, both operands K-major, M = 128, N = kQmmTokens.
-constexpr uint32_t kQmmIdesc = (1u << 4) | ((uint32_t)(kQmmTokens >> 3) << 17) | ((uint32_t)(kQmmRows >> 4) << 24);
+// kind::f16, fp16 x fp16 -> fp32, both operands K-major, M = 128, N = n (a multiple of 16, at most 256).
+__device__ __forceinline__ uint32_t qmm_idesc(uint32_t n) {
+    return (1u << 4) | ((n >> 3) << 17) | ((uint32_t)(kQmmRows >> 4) << 24);
+}
 
 // Builds the group table on the device: routed groups from the routing metadata, or one dense group.
 __global__ void qmm_prepare_kernel(QmmArgs a, int nmat, int dense) {
@@ -131,7 +144,7 @@ __global__ void qmm_prepare_kernel(QmmArgs a, int nmat, int dense) {
         for (int m = 0; m < nmat; ++m) { g.W[m] = a.dense_W[m]; g.S[m] = a.dense_S[m]; g.B[m] = a.dense_B[m]; }
         g.row_start = 0; g.count = a.dense_tokens; g.tile_start = 0;
         a.groups[0] = g;
-        tiles = (a.dense_tokens + kQmmTokens - 1) / kQmmTokens;
+        tiles = (a.dense_tokens + kQmmTokMax - 1) / kQmmTokMax;
     } else {
         ng = a.route_counters[0];
         for (uint32_t i = 0; i < ng; ++i) {
@@ -145,7 +158,7 @@ __global__ void qmm_prepare_kernel(QmmArgs a, int nmat, int dense) {
             }
             g.row_start = rg.pair_start; g.count = rg.pair_count; g.tile_start = tiles;
             a.groups[i] = g;
-            tiles += (rg.pair_count + kQmmTokens - 1) / kQmmTokens;
+            tiles += (rg.pair_count + kQmmTokMax - 1) / kQmmTokMax;
         }
     }
     a.totals[0] = ng;
@@ -155,38 +168,58 @@ __global__ void qmm_prepare_kernel(QmmArgs a, int nmat, int dense) {
 template <int NMAT>
 struct QmmSmem {
     static constexpr uint32_t kATile = kQmmRows * 128;                 // 16 KB
-    static constexpr uint32_t kBTile = kQmmTokens * 128;               // 16 KB
-    static constexpr uint32_t kStage = NMAT * kATile + kBTile;
+    static constexpr uint32_t kBTile = kQmmTokMax * 128;               // 32 KB
+    static constexpr uint32_t kStage = NMAT * kATile + kBTile;         // 64 KB / 48 KB
     static constexpr uint32_t kRing = kQmmStages * kStage;
-    static constexpr uint32_t kBars = kRing;                           // full_a[S] full_b[S] empty[S] acc_full acc_empty, tmem ptr
+    static constexpr uint32_t kBars = kRing;                           // barriers and the TMEM address
     static constexpr uint32_t kTotal = kRing + 256 + 1024;             // + barriers + slack for 1024-byte alignment
+    static constexpr int kAccBufs = NMAT == 1 ? 2 : 1;                 // 512 TMEM columns / (NMAT * 256)
 };
 
-// 16 packed codes (two 32-bit words) of one row -> 16 fp16 weights in column order, w = half(q * s + b).
-// (w & 0x000F000F) | 0x6400 is the fp16 1024 + q, (w & 0x00F000F0) | 0x6400 is 1024 + 16 q; both are exact,
-// the subtraction of 1024 is exact, and the final fma rounds once (tensorops.metal:60-75 stores half(fma(q, s, b))).
-__device__ __forceinline__ void dequant8(uint32_t w, __half2 s, __half2 s16, __half2 b, uint32_t (&out)[4]) {
-    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
-    uint32_t t0 = (w & 0x000F000Fu) | 0x64006400u, t1 = (w & 0x00F000F0u) | 0x64006400u;
-    const uint32_t ws = w >> 8;
-    uint32_t t2 = (ws & 0x000F000Fu) | 0x64006400u, t3 = (ws & 0x00F000F0u) | 0x64006400u;
-    __half2 h0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1024), s, b);      // (k0, k4)
-    __half2 h1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1024), s16, b);    // (k1, k5)
-    __half2 h2 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t2), k1024), s, b);      // (k2, k6)
-    __half2 h3 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t3), k1024), s16, b);    // (k3, k7)
+// Eight packed codes (one 32-bit word) -> eight fp16 weights w = half(q * s + b).
+// Fast form: a nibble moved to bits 4..7 of a half is the subnormal q * 2^-20, so one HFMA2 with s * 2^20
+// gives fma(q, s, b) rounded once (tensorops.metal:60-75 stores half(fma(q, s, b))); s * 2^20 is exact in
+// fp16 (s is a bf16) while |s| < 2^-5. Larger scales take the two-step form (1024 + q) - 1024.
+// Output order: PERMUTED (k0,k4,k1,k5,k2,k6,k3,k7), otherwise natural.
+template <bool NATURAL_K>
+__device__ __forceinline__ uint4 dequant8(uint32_t w, __half2 s_fast, __half2 s, __half2 b, bool fast) {
+    uint32_t t0, t1, t2, t3;
+    __half2 h0, h1, h2, h3;
+    if (fast) {
+        t0 = (w << 4) & 0x00F000F0u; t1 = w & 0x00F000F0u; t2 = (w >> 4) & 0x00F000F0u; t3 = (w >> 8) & 0x00F000F0u;
+        h0 = __hfma2(*reinterpret_cast<__half2*>(&t0), s_fast, b);     // (k0, k4)
+        h1 = __hfma2(*reinterpret_cast<__half2*>(&t1), s_fast, b);     // (k1, k5)
+        h2 = __hfma2(*reinterpret_cast<__half2*>(&t2), s_fast, b);     // (k2, k6)
+        h3 = __hfma2(*reinterpret_cast<__half2*>(&t3), s_fast, b);     // (k3, k7)
+    } else {
+        const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+        t0 = (w & 0x000F000Fu) | 0x64006400u; t1 = ((w >> 4) & 0x000F000Fu) | 0x64006400u;
+        t2 = ((w >> 8) & 0x000F000Fu) | 0x64006400u; t3 = ((w >> 12) & 0x000F000Fu) | 0x64006400u;
+        h0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1024), s, b);
+        h1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1024), s, b);
+        h2 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t2), k1024), s, b);
+        h3 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t3), k1024), s, b);
+    }
     const uint32_t u0 = *reinterpret_cast<uint32_t*>(&h0), u1 = *reinterpret_cast<uint32_t*>(&h1);
     const uint32_t u2 = *reinterpret_cast<uint32_t*>(&h2), u3 = *reinterpret_cast<uint32_t*>(&h3);
-    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out[0]) : "r"(u0), "r"(u1));   // (k0, k1)
-    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(out[1]) : "r"(u2), "r"(u3));   // (k2, k3)
-    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out[2]) : "r"(u0), "r"(u1));   // (k4, k5)
-    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(out[3]) : "r"(u2), "r"(u3));   // (k6, k7)
+    if (!NATURAL_K) return make_uint4(u0, u1, u2, u3);
+    uint4 o;
+    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(o.x) : "r"(u0), "r"(u1));   // (k0, k1)
+    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(o.y) : "r"(u2), "r"(u3));   // (k2, k3)
+    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(o.z) : "r"(u0), "r"(u1));   // (k4, k5)
+    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(o.w) : "r"(u2), "r"(u3));   // (k6, k7)
+    return o;
 }
 
-template <int NMAT>
+// Position of column k within its eight-column block in the PERMUTED order.
+__device__ __forceinline__ uint32_t permuted_col(uint32_t k) { return (k & ~7u) | ((k & 3u) << 1) | ((k >> 2) & 1u); }
+
+template <int NMAT, bool NATURAL_K>
 __global__ void __launch_bounds__(kQmmThreads, 1)
 qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args) {
     extern __shared__ uint8_t smem_raw[];
     using L = QmmSmem<NMAT>;
+    constexpr int kAccBufs = L::kAccBufs;
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                      // swizzle atoms need 1024-byte alignment
     uint8_t* base_ptr = smem_raw + (base - raw);
@@ -194,8 +227,9 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
     auto bar_full_a = [&](uint32_t s) { return bars + s * 8; };
     auto bar_full_b = [&](uint32_t s) { return bars + (kQmmStages + s) * 8; };
     auto bar_empty = [&](uint32_t s) { return bars + (2 * kQmmStages + s) * 8; };
-    const uint32_t bar_acc_full = bars + 3 * kQmmStages * 8, bar_acc_empty = bar_acc_full + 8;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kBars + 3 * kQmmStages * 8 + 16);
+    auto bar_acc_full = [&](uint32_t b) { return bars + (3 * kQmmStages + b) * 8; };
+    auto bar_acc_empty = [&](uint32_t b) { return bars + (3 * kQmmStages + 2 + b) * 8; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kBars + (3 * kQmmStages + 4) * 8);
 
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t ksteps = args.k / kQmmK;
@@ -204,21 +238,22 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
     const uint32_t wrow_tiles = (args.rows + kQmmRows - 1) / kQmmRows;
     const uint32_t ngroups = args.totals[0];
     const uint32_t total_tiles = args.totals[1] * wrow_tiles;
-    constexpr uint32_t kTmemCols = NMAT * kQmmTokens;                  // 128 or 256: a power of two >= 32
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < (uint32_t)kQmmStages; ++s) {
-            q_mbar_init(bar_full_a(s), 4);      // one arrival per dequantiser warp
-            q_mbar_init(bar_full_b(s), 1);      // the TMA thread's expect_tx
-            q_mbar_init(bar_empty(s), 1);       // tcgen05.commit
+            q_mbar_init(bar_full_a(s), kQmmDequantWarps);   // one arrival per dequantiser warp
+            q_mbar_init(bar_full_b(s), 1);                  // the TMA thread's expect_tx
+            q_mbar_init(bar_empty(s), 1);                   // tcgen05.commit
         }
-        q_mbar_init(bar_acc_full, 1);           // tcgen05.commit after the last step
-        q_mbar_init(bar_acc_empty, 4);          // one arrival per epilogue warp
+        for (uint32_t b = 0; b < 2; ++b) {
+            q_mbar_init(bar_acc_full(b), 1);                // tcgen05.commit after the last step
+            q_mbar_init(bar_acc_empty(b), kQmmEpilogueWarps);
+        }
         q_fence_async_smem();
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"(kTmemCols) : "memory");
+                     ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"((uint32_t)kQmmTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -238,6 +273,11 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
         gi = lo;
         tt = tglob - args.groups[lo].tile_start;
     };
+    // tokens of a tile, and the MMA's N (rounded up to 16)
+    auto tile_tokens = [&](uint32_t count, uint32_t tt) {
+        const uint32_t left = count - tt * kQmmTokMax;
+        return left < (uint32_t)kQmmTokMax ? left : (uint32_t)kQmmTokMax;
+    };
 
     uint32_t fail = 0;
     uint32_t it = 0;         // running k-step index over all of this CTA's tiles (ring position)
@@ -248,13 +288,16 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
         for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
             uint32_t gi, tt, wt;
             locate(tile, gi, tt, wt);
-            const uint32_t row0 = args.groups[gi].row_start + tt * kQmmTokens;
+            const uint32_t row0 = args.groups[gi].row_start + tt * kQmmTokMax;
+            const uint32_t boxes = (tile_tokens(args.groups[gi].count, tt) + kQmmBoxRows - 1) / kQmmBoxRows;
             for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
                 const uint32_t s = it % kQmmStages, use = it / kQmmStages;
                 if (use > 0 && !q_mbar_wait(bar_empty(s), (use - 1) & 1)) { fail = kErrQmmTimeout | 1; break; }
                 if (lane == 0) {
-                    q_mbar_expect_tx(bar_full_b(s), L::kBTile);
-                    tma_load_2d(base + s * L::kStage + NMAT * L::kATile, &x_map, (int)(ks * kQmmK), (int)row0, bar_full_b(s));
+                    q_mbar_expect_tx(bar_full_b(s), boxes * kQmmBoxRows * 128);
+                    for (uint32_t b = 0; b < boxes; ++b)
+                        tma_load_2d(base + s * L::kStage + NMAT * L::kATile + b * kQmmBoxRows * 128, &x_map, (int)(ks * kQmmK),
+                                    (int)(row0 + b * kQmmBoxRows), bar_full_b(s));
                 }
                 __syncwarp();
             }
@@ -262,8 +305,14 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
     } else if (warp == 1) {
         // ===================== MMA issuer =====================
         for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x, ++local_tile) {
-            if (local_tile > 0 && !q_mbar_wait(bar_acc_empty, (local_tile - 1) & 1)) { fail = kErrQmmTimeout | 2; break; }
+            uint32_t gi, tt, wt;
+            locate(tile, gi, tt, wt);
+            const uint32_t n_mma = (tile_tokens(args.groups[gi].count, tt) + 15u) & ~15u;
+            const uint32_t idesc = qmm_idesc(n_mma);
+            const uint32_t buf = local_tile % kAccBufs, n = local_tile / kAccBufs;
+            if (n > 0 && !q_mbar_wait(bar_acc_empty(buf), (n - 1) & 1)) { fail = kErrQmmTimeout | 2; break; }
             tc_fence_after();
+            const uint32_t acc = tmem_base + buf * (NMAT * kQmmTokMax);
             for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
                 const uint32_t s = it % kQmmStages, use = it / kQmmStages;
                 if (!q_mbar_wait(bar_full_a(s), use & 1) || !q_mbar_wait(bar_full_b(s), use & 1)) { fail = kErrQmmTimeout | 3; break; }
@@ -276,18 +325,19 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
                         const uint64_t a_desc = umma_smem_desc(stage + m * L::kATile);
 #pragma unroll
                         for (int j = 0; j < kQmmK / 16; ++j)      // 16 columns = 32 bytes along K per MMA
-                            tc_mma_f16(tmem_base + m * kQmmTokens, a_desc + (uint64_t)(j * 2), b_desc + (uint64_t)(j * 2), kQmmIdesc,
+                            tc_mma_f16(acc + m * kQmmTokMax, a_desc + (uint64_t)(j * 2), b_desc + (uint64_t)(j * 2), idesc,
                                        (ks > 0 || j > 0) ? 1u : 0u);
                     }
                     tc_commit(bar_empty(s));                      // the stage is free once these MMAs have read it
-                    if (ks + 1 == ksteps) tc_commit(bar_acc_full);
+                    if (ks + 1 == ksteps) tc_commit(bar_acc_full(buf));
                 }
                 __syncwarp();
             }
         }
-    } else if (warp >= 4 && warp < 8) {
-        // ===================== dequantisers: one weight row per thread =====================
-        const uint32_t r = (warp - 4) * kWarp + lane;            // row within the tile
+    } else if (warp >= kQmmFirstDequantWarp && warp < kQmmFirstEpilogueWarp) {
+        // ===================== dequantisers: two threads per weight row =====================
+        const uint32_t idx = threadIdx.x - kQmmFirstDequantWarp * kWarp;
+        const uint32_t r = idx >> 1, hf = idx & 1;               // row within the tile, half of the 64 columns
         const uint32_t row_off = (r >> 3) * 1024 + (r & 7) * 128, sw = r & 7;
         for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
             uint32_t gi, tt, wt;
@@ -295,64 +345,72 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
             const QmmGroup grp = args.groups[gi];
             const uint32_t wrow = wt * kQmmRows + r;
             const bool valid = wrow < args.rows;
-            for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
-                const uint32_t s = it % kQmmStages, use = it / kQmmStages;
-                // fetch this step's codes and scale before waiting for the stage
-                uint4 codes[NMAT][2];
-                uint32_t sb[NMAT][2];
+            uint4 codes[NMAT];
+            uint32_t sb[NMAT];
+            auto fetch = [&](uint32_t ks) {
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m) {
                     if (valid) {
-                        const uint4* wp = reinterpret_cast<const uint4*>(grp.W[m] + (size_t)wrow * row_bytes + ks * 32);
-                        codes[m][0] = __ldg(wp); codes[m][1] = __ldg(wp + 1);
-                        sb[m][0] = grp.S[m][(size_t)wrow * groups_per_row + ks];
-                        sb[m][1] = grp.B[m][(size_t)wrow * groups_per_row + ks];
+                        codes[m] = __ldg(reinterpret_cast<const uint4*>(grp.W[m] + (size_t)wrow * row_bytes + ks * 32 + hf * 16));
+                        sb[m] = (uint32_t)__ldg(grp.S[m] + (size_t)wrow * groups_per_row + ks) |
+                                ((uint32_t)__ldg(grp.B[m] + (size_t)wrow * groups_per_row + ks) << 16);
                     } else {
-                        codes[m][0] = codes[m][1] = make_uint4(0u, 0u, 0u, 0u);
-                        sb[m][0] = sb[m][1] = 0u;
+                        codes[m] = make_uint4(0u, 0u, 0u, 0u);
+                        sb[m] = 0u;
                     }
                 }
+            };
+            fetch(0);
+            for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                const uint32_t s = it % kQmmStages, use = it / kQmmStages;
+                uint4 cur[NMAT];
+                uint32_t cur_sb[NMAT];
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m) { cur[m] = codes[m]; cur_sb[m] = sb[m]; }
+                if (ks + 1 < ksteps) fetch(ks + 1);               // next step's loads fly over this step's work
                 if (use > 0 && !q_mbar_wait(bar_empty(s), (use - 1) & 1)) { fail = kErrQmmTimeout | 4; break; }
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m) {
-                    const float sf = bf16_bits_to_float((uint16_t)sb[m][0]), bf = bf16_bits_to_float((uint16_t)sb[m][1]);
-                    const __half2 s2 = __float2half2_rn(sf), s16 = __float2half2_rn(sf * 0.0625f), b2 = __float2half2_rn(bf);
+                    const float sf = bf16_bits_to_float((uint16_t)(cur_sb[m] & 0xFFFFu)), bf = bf16_bits_to_float((uint16_t)(cur_sb[m] >> 16));
+                    const bool fast = fabsf(sf) < 0.03125f;
+                    const __half2 s_fast = __float2half2_rn(sf * 1048576.0f), s2 = __float2half2_rn(sf), b2 = __float2half2_rn(bf);
                     uint8_t* arow = base_ptr + s * L::kStage + m * L::kATile + row_off;
-                    const uint32_t w[8] = {codes[m][0].x, codes[m][0].y, codes[m][0].z, codes[m][0].w,
-                                           codes[m][1].x, codes[m][1].y, codes[m][1].z, codes[m][1].w};
+                    const uint32_t w[4] = {cur[m].x, cur[m].y, cur[m].z, cur[m].w};
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {                 // 8 codes -> 16 bytes = one swizzle chunk
-                        uint32_t o[4];
-                        dequant8(w[c], s2, s16, b2, o);
-                        *reinterpret_cast<uint4*>(arow + ((c ^ sw) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-                    }
+                    for (int c = 0; c < 4; ++c)                   // 8 codes -> 16 bytes = one swizzle chunk
+                        *reinterpret_cast<uint4*>(arow + (((hf * 4 + c) ^ sw) << 4)) = dequant8<NATURAL_K>(w[c], s_fast, s2, b2, fast);
                 }
                 q_fence_async_smem();                             // generic writes -> visible to the tensor core's async proxy
                 __syncwarp();
                 if (lane == 0) q_mbar_arrive(bar_full_a(s));
             }
         }
-    } else if (warp >= 8) {
+    } else if (warp >= kQmmFirstEpilogueWarp) {
         // ===================== epilogue: TMEM -> registers -> global =====================
         const uint32_t q = warp & 3;                              // TMEM lane quarter this warp may read
+        const uint32_t chunk_par = (warp - kQmmFirstEpilogueWarp) >> 2;   // which 16-column chunks this warp takes
         const uint32_t r = q * kWarp + lane;                      // weight row within the tile = TMEM lane
         for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x, ++local_tile) {
             uint32_t gi, tt, wt;
             locate(tile, gi, tt, wt);
             const QmmGroup grp = args.groups[gi];
             const uint32_t wrow = wt * kQmmRows + r;
-            const uint32_t tok0 = tt * kQmmTokens;
-            const uint32_t ntok = grp.count - tok0 < (uint32_t)kQmmTokens ? grp.count - tok0 : (uint32_t)kQmmTokens;
-            if (!q_mbar_wait(bar_acc_full, local_tile & 1)) { fail = kErrQmmTimeout | 5; break; }
+            const uint32_t out_col = (NMAT == 2 && !NATURAL_K) ? permuted_col(wrow) : wrow;   // the GeGLU output feeds the down GEMM
+            const uint32_t tok0 = tt * kQmmTokMax;
+            const uint32_t ntok = tile_tokens(grp.count, tt);
+            const uint32_t buf = local_tile % kAccBufs, n = local_tile / kAccBufs;
+            if (!q_mbar_wait(bar_acc_full(buf), n & 1)) { fail = kErrQmmTimeout | 5; break; }
             tc_fence_after();
-            for (uint32_t c0 = 0; c0 < (uint32_t)kQmmTokens; c0 += 32) {
-                uint32_t v0[32], v1[32];
-                tc_ld32(tmem_base + ((q * kWarp) << 16) + c0, v0);
-                if (NMAT == 2) tc_ld32(tmem_base + ((q * kWarp) << 16) + kQmmTokens + c0, v1);
+            const uint32_t acc = tmem_base + ((q * kWarp) << 16) + buf * (NMAT * kQmmTokMax);
+            uint16_t* out_row = args.out + (size_t)(grp.row_start + tok0) * args.out_stride + out_col;
+            for (uint32_t c0 = chunk_par * 16; c0 < ntok; c0 += 32) {
+                uint32_t v0[16], v1[16];
+                tc_ld16(acc + c0, v0);
+                if (NMAT == 2) tc_ld16(acc + kQmmTokMax + c0, v1);
                 tc_wait_ld();
                 if (wrow < args.rows) {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
+                    for (int j = 0; j < 16; ++j) {
                         const uint32_t tok = c0 + j;
                         if (tok < ntok) {
                             float y = __uint_as_float(v0[j]);
@@ -364,14 +422,14 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
                                 }
                                 y = gelu_tanh(gt) * up;            // prefill.metal:634-636
                             }
-                            args.out[(size_t)(grp.row_start + tok0 + tok) * args.out_stride + wrow] = __half_as_ushort(__float2half_rn(y));
+                            out_row[(size_t)tok * args.out_stride] = __half_as_ushort(__float2half_rn(y));
                         }
                     }
                 }
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) q_mbar_arrive(bar_acc_empty);
+            if (lane == 0) q_mbar_arrive(bar_acc_empty(buf));
         }
     }
     if (fail && lane == 0) atomicCAS(args.error, 0u, fail);
@@ -379,7 +437,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
     __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kQmmTmemCols) : "memory");
     }
 }
 
@@ -399,14 +457,14 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// fp16 matrix [rows, k] with a row stride: box = 64 columns x 128 rows, 128-byte swizzle, zero fill outside.
+// fp16 matrix [rows, k] with a row stride: box = 64 columns x 64 rows, 128-byte swizzle, zero fill outside.
 static tf_status make_x_map(tf_context* ctx, CUtensorMap* map, const void* x, uint64_t rows, uint32_t k, uint32_t stride_elems,
                             const char* name) {
     EncodeTiledFn fn = encode_tiled_fn();
     TF_REQUIRE(ctx, fn != nullptr, TF_ERR_UNSUPPORTED, "%s: cuTensorMapEncodeTiled is not available in this driver", name);
     const cuuint64_t dims[2] = {k, rows};
     const cuuint64_t strides[1] = {(cuuint64_t)stride_elems * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kQmmK, (cuuint32_t)kQmmTokens};
+    const cuuint32_t box[2] = {(cuuint32_t)kQmmK, (cuuint32_t)kQmmBoxRows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -415,7 +473,7 @@ static tf_status make_x_map(tf_context* ctx, CUtensorMap* map, const void* x, ui
     return TF_OK;
 }
 
-template <int NMAT>
+template <int NMAT, bool NATURAL_K>
 static tf_status launch_qmm(tf_context* ctx, void* stream, QmmArgs& a, const void* x, uint64_t x_rows, uint32_t x_stride,
                             bool dense, const char* name) {
     TF_REQUIRE(ctx, a.k % kQmmK == 0 && a.k >= (uint32_t)kQmmK, TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);
@@ -429,7 +487,7 @@ static tf_status launch_qmm(tf_context* ctx, void* stream, QmmArgs& a, const voi
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     qmm_prepare_kernel<<<1, 32, 0, st>>>(a, NMAT, dense ? 1 : 0);
     if (tf_status s = check_launch(ctx, "qmm_prepare")) return s;
-    auto kern = qmm_tcgen05_kernel<NMAT>;
+    auto kern = qmm_tcgen05_kernel<NMAT, NATURAL_K>;
     static bool configured = false;
     if (!configured) {
         TF_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QmmSmem<NMAT>::kTotal));
@@ -462,13 +520,13 @@ tf_status tf_grouped_moe_tensorcore(tf_context* ctx, void* stream, const void* x
     a.w_off[1] = offsets->up_w_off;   a.s_off[1] = offsets->up_s_off;   a.b_off[1] = offsets->up_b_off;
     a.route_groups = routes->groups; a.route_counters = routes->counters;
     a.rows = f; a.k = d; a.out = static_cast<uint16_t*>(acts_scratch); a.out_stride = f; a.round_gate_up = 0;
-    if (tf_status s = tf::launch_qmm<2>(ctx, stream, a, x_sorted, x_rows, d, false, "tf_grouped_moe_tensorcore(gate/up)")) return s;
+    if (tf_status s = tf::launch_qmm<2, false>(ctx, stream, a, x_sorted, x_rows, d, false, "tf_grouped_moe_tensorcore(gate/up)")) return s;
     tf::QmmArgs b{};
     b.pool_base = a.pool_base; b.expert_stride = expert_stride;
     b.w_off[0] = offsets->down_w_off; b.s_off[0] = offsets->down_s_off; b.b_off[0] = offsets->down_b_off;
     b.route_groups = routes->groups; b.route_counters = routes->counters;
     b.rows = d; b.k = f; b.out = static_cast<uint16_t*>(out_rows); b.out_stride = d;
-    return tf::launch_qmm<1>(ctx, stream, b, acts_scratch, x_rows, f, false, "tf_grouped_moe_tensorcore(down)");
+    return tf::launch_qmm<1, false>(ctx, stream, b, acts_scratch, x_rows, f, false, "tf_grouped_moe_tensorcore(down)");
 }
 
 tf_status tf_int4_qmm(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off, const void* scales,
@@ -487,7 +545,7 @@ tf_status tf_int4_qmm(tf_context* ctx, void* stream, const void* weights, uint64
                TF_ERR_ALIGNMENT, "%s: packed rows must be 16-byte aligned", name);
     a.dense_tokens = m; a.rows = n; a.k = k;
     a.out = reinterpret_cast<uint16_t*>(tf::byte_ptr(y, y_off)); a.out_stride = n;
-    return tf::launch_qmm<1>(ctx, stream, a, tf::byte_ptr(x, x_off), m, k, true, name);
+    return tf::launch_qmm<1, true>(ctx, stream, a, tf::byte_ptr(x, x_off), m, k, true, name);
 }
 
 tf_status tf_shared_expert_int4_tensorcore(tf_context* ctx, void* stream, const void* x, uint32_t x_stride_elements,
@@ -513,11 +571,11 @@ tf_status tf_shared_expert_int4_tensorcore(tf_context* ctx, void* stream, const 
     a.dense_W[0] = W[0]; a.dense_S[0] = S[0]; a.dense_B[0] = B[0];
     a.dense_W[1] = W[1]; a.dense_S[1] = S[1]; a.dense_B[1] = B[1];
     a.dense_tokens = rows; a.rows = fs; a.k = d; a.out = static_cast<uint16_t*>(scratch_act); a.out_stride = fs; a.round_gate_up = 1;
-    if (tf_status s = tf::launch_qmm<2>(ctx, stream, a, x, rows, x_stride_elements, true, "tf_shared_expert_int4_tensorcore(gate/up)")) return s;
+    if (tf_status s = tf::launch_qmm<2, true>(ctx, stream, a, x, rows, x_stride_elements, true, "tf_shared_expert_int4_tensorcore(gate/up)")) return s;
     tf::QmmArgs b{};
     b.dense_W[0] = W[2]; b.dense_S[0] = S[2]; b.dense_B[0] = B[2];
     b.dense_tokens = rows; b.rows = d; b.k = fs; b.out = static_cast<uint16_t*>(y); b.out_stride = y_stride_elements;
-    return tf::launch_qmm<1>(ctx, stream, b, scratch_act, rows, fs, true, "tf_shared_expert_int4_tensorcore(down)");
+    return tf::launch_qmm<1, true>(ctx, stream, b, scratch_act, rows, fs, true, "tf_shared_expert_int4_tensorcore(down)");
 }
 
 }  // extern "C"

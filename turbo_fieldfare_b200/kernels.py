@@ -372,6 +372,15 @@ class PrefillGroupedRoutedMoE:
             1 if partials_f32 else 0, query_count, d, f, top_k))
 
 
+    def encode_pack_sorted_rows(self, hidden, routes: DeviceRoutes, query_count: int, top_k: int, num_experts: int, d: int,
+                                x_sorted, row_expert_ids, inverse_perm, *, hidden_stride_elements=None, stream=None):
+        """Gather every pair's hidden row into expert order for the tensor-core path (``tf_pack_sorted_rows``)."""
+        ctx = self.context
+        ctx.check(ctx.lib.tf_pack_sorted_rows(
+            ctx.handle, _stream(stream), _ptr(hidden), d if hidden_stride_elements is None else hidden_stride_elements,
+            C.byref(routes.c_struct), query_count, top_k, num_experts, d, _ptr(x_sorted), _ptr(row_expert_ids),
+            _ptr(inverse_perm)))
+
     def encode_tensorcore(self, x_sorted, x_rows: int, pool_layer_base, expert_stride: int, offsets: ExpertOffsets,
                           routes: DeviceRoutes, acts_scratch, out_rows, d: int, f: int, *, stream=None):
         """Same operator on the tcgen05 tensor cores over expert-sorted rows (``tf_grouped_moe_tensorcore``)."""
