@@ -36,7 +36,7 @@ constexpr int kQmmTokMax = 256;        // largest N of one MMA: tokens per tile
 constexpr int kQmmBoxRows = 64;        // activation rows per TMA box
 constexpr int kQmmRows = 128;          // M of the MMA: weight rows per tile
 constexpr int kQmmK = 64;              // columns per step = one quantisation group = one 128-byte swizzle row
-constexpr int kQmmStages = 3;
+constexpr int kQmmMaxStages = 4;       // ring depth: 3 with two weight matrices per stage (64 KB), 4 with one (48 KB)
 constexpr int kQmmDequantWarps = 8, kQmmEpilogueWarps = 8;
 constexpr int kQmmFirstDequantWarp = 4, kQmmFirstEpilogueWarp = kQmmFirstDequantWarp + kQmmDequantWarps;
 constexpr int kQmmThreads = (kQmmFirstEpilogueWarp + kQmmEpilogueWarps) * 32;   // warp 0: TMA, warp 1: MMA, 2-3 idle
@@ -170,10 +170,11 @@ struct QmmSmem {
     static constexpr uint32_t kATile = kQmmRows * 128;                 // 16 KB
     static constexpr uint32_t kBTile = kQmmTokMax * 128;               // 32 KB
     static constexpr uint32_t kStage = NMAT * kATile + kBTile;         // 64 KB / 48 KB
-    static constexpr uint32_t kRing = kQmmStages * kStage;
+    static constexpr int kStages = NMAT == 2 ? 3 : 4;
+    static constexpr int kPrefetch = NMAT == 2 ? 3 : 4;               // k-steps of packed codes a dequantiser thread keeps in flight
+    static constexpr uint32_t kRing = kStages * kStage;
     static constexpr uint32_t kBars = kRing;                           // barriers and the TMEM address
     static constexpr uint32_t kTotal = kRing + 256 + 1024;             // + barriers + slack for 1024-byte alignment
-    static constexpr int kAccBufs = NMAT == 1 ? 2 : 1;                 // 512 TMEM columns / (NMAT * 256)
 };
 
 // Eight packed codes (one 32-bit word) -> eight fp16 weights w = half(q * s + b).
@@ -214,22 +215,46 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __half2 s_fast, __half2 s,
 // Position of column k within its eight-column block in the PERMUTED order.
 __device__ __forceinline__ uint32_t permuted_col(uint32_t k) { return (k & ~7u) | ((k & 3u) << 1) | ((k >> 2) & 1u); }
 
+// Accumulator placement in the 512 TMEM columns, two buffers of 256. A tile whose accumulators fit one buffer
+// (one matrix, or two matrices of at most 128 tokens) takes the buffer used less often so far, so consecutive
+// tiles alternate and the epilogue of one overlaps the MMAs of the next; a two-matrix tile of more than 128
+// tokens takes both. The MMA issuer and the epilogue warps replay the same sequence, so they agree.
+struct AccPlan {
+    uint32_t uses0 = 0u, uses1 = 0u;
+    bool both = false;
+    uint32_t buf = 0, col0 = 0, mat_stride = 0;
+    template <int NMAT>
+    __device__ __forceinline__ void next(uint32_t n_mma) {
+        both = NMAT == 2 && n_mma > 128u;
+        buf = both ? 0u : (uses0 <= uses1 ? 0u : 1u);
+        col0 = buf * 256u;
+        mat_stride = both ? 256u : 128u;
+    }
+    __device__ __forceinline__ bool takes(uint32_t b) const { return both || b == buf; }
+    __device__ __forceinline__ uint32_t uses(uint32_t b) const { return b ? uses1 : uses0; }
+    __device__ __forceinline__ void done() {
+        if (both || buf == 0) ++uses0;
+        if (both || buf == 1) ++uses1;
+    }
+};
+
 template <int NMAT, bool NATURAL_K>
 __global__ void __launch_bounds__(kQmmThreads, 1)
 qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args) {
     extern __shared__ uint8_t smem_raw[];
     using L = QmmSmem<NMAT>;
-    constexpr int kAccBufs = L::kAccBufs;
+    constexpr int kQmmStages = L::kStages;
+    constexpr int kQmmPrefetch = L::kPrefetch;
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                      // swizzle atoms need 1024-byte alignment
     uint8_t* base_ptr = smem_raw + (base - raw);
     const uint32_t bars = base + L::kBars;
     auto bar_full_a = [&](uint32_t s) { return bars + s * 8; };
-    auto bar_full_b = [&](uint32_t s) { return bars + (kQmmStages + s) * 8; };
-    auto bar_empty = [&](uint32_t s) { return bars + (2 * kQmmStages + s) * 8; };
-    auto bar_acc_full = [&](uint32_t b) { return bars + (3 * kQmmStages + b) * 8; };
-    auto bar_acc_empty = [&](uint32_t b) { return bars + (3 * kQmmStages + 2 + b) * 8; };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kBars + (3 * kQmmStages + 4) * 8);
+    auto bar_full_b = [&](uint32_t s) { return bars + (kQmmMaxStages + s) * 8; };
+    auto bar_empty = [&](uint32_t s) { return bars + (2 * kQmmMaxStages + s) * 8; };
+    auto bar_acc_full = [&](uint32_t b) { return bars + (3 * kQmmMaxStages + b) * 8; };
+    auto bar_acc_empty = [&](uint32_t b) { return bars + (3 * kQmmMaxStages + 2 + b) * 8; };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kBars + (3 * kQmmMaxStages + 4) * 8);
 
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t ksteps = args.k / kQmmK;
@@ -281,7 +306,6 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
 
     uint32_t fail = 0;
     uint32_t it = 0;         // running k-step index over all of this CTA's tiles (ring position)
-    uint32_t local_tile = 0; // tiles done by this CTA (accumulator barrier phase)
 
     if (warp == 0) {
         // ===================== TMA producer: activation tiles =====================
@@ -304,15 +328,21 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
         }
     } else if (warp == 1) {
         // ===================== MMA issuer =====================
-        for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x, ++local_tile) {
+        AccPlan plan;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
             uint32_t gi, tt, wt;
             locate(tile, gi, tt, wt);
             const uint32_t n_mma = (tile_tokens(args.groups[gi].count, tt) + 15u) & ~15u;
             const uint32_t idesc = qmm_idesc(n_mma);
-            const uint32_t buf = local_tile % kAccBufs, n = local_tile / kAccBufs;
-            if (n > 0 && !q_mbar_wait(bar_acc_empty(buf), (n - 1) & 1)) { fail = kErrQmmTimeout | 2; break; }
+            plan.next<NMAT>(n_mma);
+#pragma unroll
+            for (uint32_t b = 0; b < 2; ++b) {
+                if (plan.takes(b) && plan.uses(b) > 0 && !q_mbar_wait(bar_acc_empty(b), (plan.uses(b) - 1) & 1))
+                    fail = kErrQmmTimeout | 2;
+            }
+            if (fail) break;
             tc_fence_after();
-            const uint32_t acc = tmem_base + buf * (NMAT * kQmmTokMax);
+            const uint32_t acc = tmem_base + plan.col0;
             for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
                 const uint32_t s = it % kQmmStages, use = it / kQmmStages;
                 if (!q_mbar_wait(bar_full_a(s), use & 1) || !q_mbar_wait(bar_full_b(s), use & 1)) { fail = kErrQmmTimeout | 3; break; }
@@ -325,57 +355,82 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
                         const uint64_t a_desc = umma_smem_desc(stage + m * L::kATile);
 #pragma unroll
                         for (int j = 0; j < kQmmK / 16; ++j)      // 16 columns = 32 bytes along K per MMA
-                            tc_mma_f16(acc + m * kQmmTokMax, a_desc + (uint64_t)(j * 2), b_desc + (uint64_t)(j * 2), idesc,
+                            tc_mma_f16(acc + m * plan.mat_stride, a_desc + (uint64_t)(j * 2), b_desc + (uint64_t)(j * 2), idesc,
                                        (ks > 0 || j > 0) ? 1u : 0u);
                     }
                     tc_commit(bar_empty(s));                      // the stage is free once these MMAs have read it
-                    if (ks + 1 == ksteps) tc_commit(bar_acc_full(buf));
+                    if (ks + 1 == ksteps) {
+                        if (plan.both || plan.buf == 0) tc_commit(bar_acc_full(0));
+                        if (plan.both || plan.buf == 1) tc_commit(bar_acc_full(1));
+                    }
                 }
                 __syncwarp();
             }
+            plan.done();
         }
     } else if (warp >= kQmmFirstDequantWarp && warp < kQmmFirstEpilogueWarp) {
         // ===================== dequantisers: two threads per weight row =====================
         const uint32_t idx = threadIdx.x - kQmmFirstDequantWarp * kWarp;
         const uint32_t r = idx >> 1, hf = idx & 1;               // row within the tile, half of the 64 columns
         const uint32_t row_off = (r >> 3) * 1024 + (r & 7) * 128, sw = r & 7;
-        for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
+        const uint32_t my_tiles = total_tiles > blockIdx.x ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+        const uint32_t total_steps = my_tiles * ksteps;
+        // The packed codes come straight from global memory, so each thread keeps a few k-steps of them in
+        // flight in registers (kPrefetch); the fetch cursor runs ahead of the processing loop and crosses tile boundaries.
+        uint32_t f_tile = blockIdx.x, f_ks = 0;
+        const uint8_t* f_w[NMAT];
+        const uint16_t* f_s[NMAT];
+        const uint16_t* f_b[NMAT];
+        bool f_valid = false;
+        auto f_resolve = [&]() {
             uint32_t gi, tt, wt;
-            locate(tile, gi, tt, wt);
-            const QmmGroup grp = args.groups[gi];
+            locate(f_tile, gi, tt, wt);
             const uint32_t wrow = wt * kQmmRows + r;
-            const bool valid = wrow < args.rows;
-            uint4 codes[NMAT];
-            uint32_t sb[NMAT];
-            auto fetch = [&](uint32_t ks) {
+            f_valid = wrow < args.rows;
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m) {
-                    if (valid) {
-                        codes[m] = __ldg(reinterpret_cast<const uint4*>(grp.W[m] + (size_t)wrow * row_bytes + ks * 32 + hf * 16));
-                        sb[m] = (uint32_t)__ldg(grp.S[m] + (size_t)wrow * groups_per_row + ks) |
-                                ((uint32_t)__ldg(grp.B[m] + (size_t)wrow * groups_per_row + ks) << 16);
-                    } else {
-                        codes[m] = make_uint4(0u, 0u, 0u, 0u);
-                        sb[m] = 0u;
-                    }
+            for (int m = 0; m < NMAT; ++m) {
+                f_w[m] = args.groups[gi].W[m] + (size_t)wrow * row_bytes + hf * 16;
+                f_s[m] = args.groups[gi].S[m] + (size_t)wrow * groups_per_row;
+                f_b[m] = args.groups[gi].B[m] + (size_t)wrow * groups_per_row;
+            }
+        };
+        uint4 codes[kQmmPrefetch][NMAT];
+        uint32_t sb[kQmmPrefetch][NMAT];
+        auto fetch = [&](uint4 (&c)[NMAT], uint32_t (&q)[NMAT]) {
+#pragma unroll
+            for (int m = 0; m < NMAT; ++m) {
+                if (f_valid) {
+                    c[m] = __ldg(reinterpret_cast<const uint4*>(f_w[m] + f_ks * 32));
+                    q[m] = (uint32_t)__ldg(f_s[m] + f_ks) | ((uint32_t)__ldg(f_b[m] + f_ks) << 16);
+                } else {
+                    c[m] = make_uint4(0u, 0u, 0u, 0u);
+                    q[m] = 0u;
                 }
-            };
-            fetch(0);
-            for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
-                const uint32_t s = it % kQmmStages, use = it / kQmmStages;
-                uint4 cur[NMAT];
-                uint32_t cur_sb[NMAT];
+            }
+            if (++f_ks == ksteps) {
+                f_ks = 0;
+                f_tile += gridDim.x;
+                if (f_tile < total_tiles) f_resolve();
+            }
+        };
+        if (total_steps) f_resolve();
 #pragma unroll
-                for (int m = 0; m < NMAT; ++m) { cur[m] = codes[m]; cur_sb[m] = sb[m]; }
-                if (ks + 1 < ksteps) fetch(ks + 1);               // next step's loads fly over this step's work
+        for (int p = 0; p < kQmmPrefetch; ++p)
+            if ((uint32_t)p < total_steps) fetch(codes[p], sb[p]);
+        for (uint32_t it0 = 0; it0 < total_steps && !fail; it0 += kQmmPrefetch) {
+#pragma unroll
+            for (int p = 0; p < kQmmPrefetch; ++p) {
+                const uint32_t itp = it0 + p;
+                if (itp >= total_steps) break;
+                const uint32_t s = itp % kQmmStages, use = itp / kQmmStages;
                 if (use > 0 && !q_mbar_wait(bar_empty(s), (use - 1) & 1)) { fail = kErrQmmTimeout | 4; break; }
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m) {
-                    const float sf = bf16_bits_to_float((uint16_t)(cur_sb[m] & 0xFFFFu)), bf = bf16_bits_to_float((uint16_t)(cur_sb[m] >> 16));
+                    const float sf = bf16_bits_to_float((uint16_t)(sb[p][m] & 0xFFFFu)), bf = bf16_bits_to_float((uint16_t)(sb[p][m] >> 16));
                     const bool fast = fabsf(sf) < 0.03125f;
                     const __half2 s_fast = __float2half2_rn(sf * 1048576.0f), s2 = __float2half2_rn(sf), b2 = __float2half2_rn(bf);
                     uint8_t* arow = base_ptr + s * L::kStage + m * L::kATile + row_off;
-                    const uint32_t w[4] = {cur[m].x, cur[m].y, cur[m].z, cur[m].w};
+                    const uint32_t w[4] = {codes[p][m].x, codes[p][m].y, codes[p][m].z, codes[p][m].w};
 #pragma unroll
                     for (int c = 0; c < 4; ++c)                   // 8 codes -> 16 bytes = one swizzle chunk
                         *reinterpret_cast<uint4*>(arow + (((hf * 4 + c) ^ sw) << 4)) = dequant8<NATURAL_K>(w[c], s_fast, s2, b2, fast);
@@ -383,6 +438,7 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
                 q_fence_async_smem();                             // generic writes -> visible to the tensor core's async proxy
                 __syncwarp();
                 if (lane == 0) q_mbar_arrive(bar_full_a(s));
+                if (itp + kQmmPrefetch < total_steps) fetch(codes[p], sb[p]);   // refill the slot just consumed
             }
         }
     } else if (warp >= kQmmFirstEpilogueWarp) {
@@ -390,7 +446,8 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
         const uint32_t q = warp & 3;                              // TMEM lane quarter this warp may read
         const uint32_t chunk_par = (warp - kQmmFirstEpilogueWarp) >> 2;   // which 16-column chunks this warp takes
         const uint32_t r = q * kWarp + lane;                      // weight row within the tile = TMEM lane
-        for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x, ++local_tile) {
+        AccPlan plan;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
             uint32_t gi, tt, wt;
             locate(tile, gi, tt, wt);
             const QmmGroup grp = args.groups[gi];
@@ -398,15 +455,19 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
             const uint32_t out_col = (NMAT == 2 && !NATURAL_K) ? permuted_col(wrow) : wrow;   // the GeGLU output feeds the down GEMM
             const uint32_t tok0 = tt * kQmmTokMax;
             const uint32_t ntok = tile_tokens(grp.count, tt);
-            const uint32_t buf = local_tile % kAccBufs, n = local_tile / kAccBufs;
-            if (!q_mbar_wait(bar_acc_full(buf), n & 1)) { fail = kErrQmmTimeout | 5; break; }
+            plan.next<NMAT>((ntok + 15u) & ~15u);
+#pragma unroll
+            for (uint32_t b = 0; b < 2; ++b) {
+                if (plan.takes(b) && !q_mbar_wait(bar_acc_full(b), plan.uses(b) & 1)) fail = kErrQmmTimeout | 5;
+            }
+            if (fail) break;
             tc_fence_after();
-            const uint32_t acc = tmem_base + ((q * kWarp) << 16) + buf * (NMAT * kQmmTokMax);
+            const uint32_t acc = tmem_base + ((q * kWarp) << 16) + plan.col0;
             uint16_t* out_row = args.out + (size_t)(grp.row_start + tok0) * args.out_stride + out_col;
             for (uint32_t c0 = chunk_par * 16; c0 < ntok; c0 += 32) {
                 uint32_t v0[16], v1[16];
                 tc_ld16(acc + c0, v0);
-                if (NMAT == 2) tc_ld16(acc + kQmmTokMax + c0, v1);
+                if (NMAT == 2) tc_ld16(acc + plan.mat_stride + c0, v1);
                 tc_wait_ld();
                 if (wrow < args.rows) {
 #pragma unroll
@@ -429,7 +490,11 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) q_mbar_arrive(bar_acc_empty(buf));
+            if (lane == 0) {
+                if (plan.both || plan.buf == 0) q_mbar_arrive(bar_acc_empty(0));
+                if (plan.both || plan.buf == 1) q_mbar_arrive(bar_acc_empty(1));
+            }
+            plan.done();
         }
     }
     if (fail && lane == 0) atomicCAS(args.error, 0u, fail);

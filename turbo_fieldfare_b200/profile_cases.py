@@ -2,6 +2,7 @@
 
     python -m turbo_fieldfare_b200.profile_cases block --tokens 64 --layers 2 --iters 3
     python -m turbo_fieldfare_b200.profile_cases gemv --rows 262144 --iters 3
+    python -m turbo_fieldfare_b200.profile_cases qmm --tokens 4096 --rows 4224 --iters 3
 
 Each case holds well under a few GB on the device, streams more than the 126 MB L2 per
 launch (one layer of experts is 430 MB), and launches only a handful of kernels, so that a
@@ -51,16 +52,47 @@ def case_gemv(args) -> None:
     print(f"gemv case done: rows={args.rows} bytes={mat.w_bytes + 2 * mat.sb_bytes}")
 
 
+def case_qmm(args) -> None:
+    """Dense int4 QMM on the tensor cores: --tokens rows of activations against a [--rows, 2816] weight matrix."""
+    from .kernels import MPPPrefillInt4QMM
+    ctx = TurboContext(0)
+    k = args.cols
+    mat = AffineTensor(args.rows, k, 4)
+    mat.fill_synthetic(ctx, 5)
+    x = torch.randn(args.tokens, k, device="cuda").half()
+    y = torch.zeros(args.tokens, args.rows, dtype=torch.float16, device="cuda")
+    op = MPPPrefillInt4QMM(ctx)
+    launch = lambda: op.encode(mat.buffer, mat.buffer, mat.buffer, x, y, args.tokens, args.rows, k,
+                               scales_offset=mat.s_off, biases_offset=mat.b_off)
+    for _ in range(args.warm):            # clocks ramp up only under sustained load
+        launch()
+    times = []
+    for _ in range(args.iters):           # each sample: 20 launches back to back, so the host's launch cost hides behind the GPU
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(20):
+            launch()
+        t1.record()
+        torch.cuda.synchronize()
+        times.append(t0.elapsed_time(t1) / 20)
+    nbytes = mat.w_bytes + 2 * mat.sb_bytes
+    best = min(times)
+    print(f"qmm case done: tokens={args.tokens} rows={args.rows} cols={k} weight_bytes={nbytes} status={ctx.device_status()} "
+          f"ms={[round(t, 4) for t in times]} weight_GBps={nbytes / best / 1e6:.0f} TFLOPs={2 * args.tokens * args.rows * k / best / 1e9:.0f}")
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["block", "gemv"])
+    ap.add_argument("case", choices=["block", "gemv", "qmm"])
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--rows", type=int, default=262144)
     ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--cols", type=int, default=2816)
+    ap.add_argument("--warm", type=int, default=0, help="untimed launches before the timed ones")
     ap.add_argument("--zipf", type=float, default=0.0, help="router logit bias log(p), p ~ 1/rank^zipf (0 = none)")
     args = ap.parse_args()
-    {"block": case_block, "gemv": case_gemv}[args.case](args)
+    {"block": case_block, "gemv": case_gemv, "qmm": case_qmm}[args.case](args)
 
 
 if __name__ == "__main__":
