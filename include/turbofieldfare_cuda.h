@@ -293,7 +293,7 @@ tf_status tf_shared_expert_int4_block(tf_context* ctx, void* stream,
 /* Y[M,N] = X[M,K] . dequant(W[N,K])^T, fp16 in/out, fp32 accumulation; the weight tile is staged as
  * half(q*s+b) and multiplied on the matrix unit. Replaces MPPPrefillInt4QMM.encode
  * (Kernels/TensorCore/MPPPrefillInt4QMM.swift:34-78; Metal/TensorCore/tensorops.metal:13-105).
- * K % 64 == 0 as there; M and N are free (the reference wants M % 32 == 0 and N % 64 == 0). */
+ * K % 64 == 0 as there; M is free and N % 8 == 0 (the reference wants M % 32 == 0 and N % 64 == 0). */
 tf_status tf_int4_qmm(tf_context* ctx, void* stream,
                       const void* weights, uint64_t weights_off,
                       const void* scales, uint64_t scales_off,
@@ -317,7 +317,7 @@ tf_status tf_pack_sorted_rows(tf_context* ctx, void* stream, const void* hidden,
  * for batches large enough to fill 128-token tiles. */
 tf_status tf_grouped_moe_tensorcore(tf_context* ctx, void* stream,
                                     const void* x_sorted, uint32_t x_rows,
-                                    const void* pool_layer_base, uint64_t expert_stride,
+                                    const void* pool_layer_base, uint64_t expert_stride, uint32_t num_experts,
                                     const tf_expert_offsets* offsets, const tf_device_routes* routes,
                                     void* acts_scratch, void* out_rows, uint32_t d, uint32_t f);
 /* Shared expert for `rows` tokens on the matrix unit; gate and up are rounded to fp16 before the activation

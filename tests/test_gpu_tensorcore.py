@@ -15,7 +15,7 @@ def _status_ok(tf_ctx):
     assert tf_ctx.device_status() == 0, "a kernel abandoned a bounded wait"
 
 
-@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (32, 128, 128), (128, 128, 256), (200, 130, 192), (129, 704, 2816),
+@pytest.mark.parametrize("M,N,K", [(1, 64, 64), (32, 128, 128), (128, 128, 256), (200, 136, 192), (129, 704, 2816),
                                    (512, 2816, 704)])
 def test_int4_qmm_vs_oracle(tf_ctx, oracle, M, N, K):
     import torch
@@ -86,7 +86,7 @@ def test_grouped_tensorcore_vs_oracle_and_cuda_cores(tf_ctx, oracle, T, D, F, E,
     pool = to_dev(pool_h)
     acts = dev_zeros_u16(T * K * F)
     out_rows = dev_zeros_u16(T * K * D, fill=0x7E00)
-    moe.encode_tensorcore(x_sorted, T * K, pool, stride, capi_offsets(off), routes, acts, out_rows, D, F)
+    moe.encode_tensorcore(x_sorted, T * K, pool, stride, E, capi_offsets(off), routes, acts, out_rows, D, F)
     torch.cuda.synchronize()
     _status_ok(tf_ctx)
     got_sorted = o.f16_to_f32(from_dev(out_rows, np.uint16).reshape(T * K, D))

@@ -87,8 +87,8 @@ SIGNATURES = {
                                               C.POINTER(Projection), vp, u64, u32, vp, u32]),
     "tf_int4_qmm": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, vp, u64, vp, u64, u32, u32, u32]),
     "tf_pack_sorted_rows": (C.c_int, [vp, vp, vp, u32, C.POINTER(DeviceRoutes), u32, u32, u32, u32, vp, vp, vp]),
-    "tf_grouped_moe_tensorcore": (C.c_int, [vp, vp, vp, u32, vp, u64, C.POINTER(ExpertOffsets), C.POINTER(DeviceRoutes),
-                                            vp, vp, u32, u32]),
+    "tf_grouped_moe_tensorcore": (C.c_int, [vp, vp, vp, u32, vp, u64, u32, C.POINTER(ExpertOffsets),
+                                            C.POINTER(DeviceRoutes), vp, vp, u32, u32]),
     "tf_shared_expert_int4_tensorcore": (C.c_int, [vp, vp, vp, u32, C.POINTER(Projection), C.POINTER(Projection),
                                                    C.POINTER(Projection), vp, u32, vp, u32]),
     "tf_expert_pool_create": (C.c_int, [vp, u32, u32, u64, C.POINTER(ExpertOffsets), C.POINTER(vp)]),

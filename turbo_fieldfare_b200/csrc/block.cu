@@ -347,7 +347,7 @@ tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer
         s = tf_pack_sorted_rows(ctx, stream, x, x_stride_elements, &ws->routes, tokens, K, E, d, ws->x_sorted, ws->pack_ids,
                                 ws->inverse_perm);
         if (s) return s;
-        s = tf_grouped_moe_tensorcore(ctx, stream, ws->x_sorted, tokens * K, layer->pool_layer_base, layer->expert_stride,
+        s = tf_grouped_moe_tensorcore(ctx, stream, ws->x_sorted, tokens * K, layer->pool_layer_base, layer->expert_stride, E,
                                       &layer->offsets, &ws->routes, ws->acts, ws->partials, d, f);
         if (s) return s;
         s = tf_shared_expert_int4_tensorcore(ctx, stream, x, x_stride_elements, &layer->shared_gate, &layer->shared_up,

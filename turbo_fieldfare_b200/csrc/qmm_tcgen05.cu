@@ -1,23 +1,28 @@
-// Grouped int4 GEMM on the 5th-generation tensor cores for prefill-sized batches.
+// Grouped int4 GEMM on the 5th-generation tensor cores (tcgen05 / TMEM) for batches of eight tokens and more.
 //
 // Replaces mpp_prefill_affine_threadgroup_f16 (Metal/TensorCore/tensorops.metal:13-105; wrapper
-// Kernels/TensorCore/MPPPrefillInt4QMM.swift:34-78), the reference's "dequantise a weight tile to half
-// in threadgroup memory, then matrix-unit MMA with an fp32 accumulator" kernel, and the routed prefill
-// kernels prefill_grouped_routed_moe_batched_phase1 / _down (Metal/Prefill/prefill.metal:598-670),
-// which the reference runs as scalar per-thread dot products.
+// Kernels/TensorCore/MPPPrefillInt4QMM.swift:34-78), the reference's "dequantise a weight tile to half,
+// then matrix-unit MMA with an fp32 accumulator" kernel, and the routed prefill kernels
+// prefill_grouped_routed_moe_batched_phase1 / _down (Metal/Prefill/prefill.metal:598-670), which the
+// reference runs as scalar per-thread dot products.
 //
-//   D[128 weight rows x N tokens] += W_tile[128 x 64] . X_tile[N x 64]^T      per 64-column group, N <= 256
+//   D[128 weight rows x N tokens] += W_tile[128 x 128] . X_tile[N x 128]^T     per step of two 64-column groups, N <= 128
 //
-// Weights are the A operand (M = 128), tokens the B operand (N = the tile's token count rounded up to 16,
-// carried in the instruction descriptor), both K-major in shared memory with the 128-byte swizzle. Per step:
-//   - one elected thread issues TMA tile loads (cp.async.bulk.tensor.2d, 64 rows each) of the activations;
-//   - 256 dequantiser threads (two per weight row) read 16 packed bytes and the group's scale and bias and
-//     write w = half(q * s + b), the reference's staged value (tensorops.metal:60-75), into the swizzled A tile;
-//   - one elected thread issues four tcgen05.mma (K = 16 each) per matrix into TMEM accumulators and
-//     commits the stage back to the producers through an mbarrier.
-// After the last step eight epilogue warps read the accumulators with tcgen05.ld and apply GeGLU (gate and
-// up accumulate side by side in TMEM) or a plain fp16 store, masked to the group's real tokens. The single
-// matrix form double-buffers its accumulator so that the epilogue of one tile overlaps the next tile's MMAs.
+// Weights are the A operand (M = 128) and are fed to the MMA from TENSOR MEMORY; tokens are the B operand
+// (N = the tile's token count rounded up to 16, carried in the instruction descriptor) in shared memory,
+// K-major with the 128-byte swizzle. Data path of the weights, which carry nearly all the bytes:
+//   HBM --TMA tile load--> shared memory (packed, 64 bytes per row and step)
+//       --LDS.128--> registers --one HFMA2 per two codes--> w = half(q * s + b)     (tensorops.metal:60-75)
+//       --tcgen05.st--> tensor memory --tcgen05.mma--> fp32 accumulators in tensor memory.
+// The dequantised tile never touches shared memory: an fp16 copy of the weights is four times the packed
+// bytes, and writing it to shared memory and reading it back for the MMA would cost more shared-memory
+// bandwidth than the whole HBM stream.
+// Roles of the 24 warps: warp 0 issues every asynchronous copy (packed codes per step, activation boxes of 16
+// rows per step, the tile's scale and bias planes as 1-D bulk copies); warp 1 issues the MMAs and commits
+// stages back through mbarriers; warps 4-19 dequantise (four threads per weight row); warps 20-23 read the
+// accumulators with tcgen05.ld and apply GeGLU (gate and up accumulate side by side) or a plain fp16 store,
+// masked to the group's real tokens. Accumulators of tiles with at most 64 tokens (one matrix: any tile)
+// alternate between two buffers so that the epilogue overlaps the next tile's MMAs.
 // A persistent grid walks (group, token tile, weight-row tile) work items derived on the device from the
 // routing metadata. Every mbarrier wait is bounded; on expiry the kernel records a code and leaves.
 //
@@ -32,30 +37,31 @@
 
 namespace tf {
 
-constexpr int kQmmTokMax = 256;        // largest N of one MMA: tokens per tile
-constexpr int kQmmBoxRows = 64;        // activation rows per TMA box
+constexpr int kQmmTokMax = 128;        // largest N of one MMA: tokens per tile
+constexpr int kQmmBoxRows = 16;        // activation rows per TMA box (2 KB per step)
 constexpr int kQmmRows = 128;          // M of the MMA: weight rows per tile
-constexpr int kQmmK = 64;              // columns per step = one quantisation group = one 128-byte swizzle row
-constexpr int kQmmMaxStages = 4;       // ring depth: 3 with two weight matrices per stage (64 KB), 4 with one (48 KB)
-constexpr int kQmmDequantWarps = 8, kQmmEpilogueWarps = 8;
-constexpr int kQmmFirstDequantWarp = 4, kQmmFirstEpilogueWarp = kQmmFirstDequantWarp + kQmmDequantWarps;
-constexpr int kQmmThreads = (kQmmFirstEpilogueWarp + kQmmEpilogueWarps) * 32;   // warp 0: TMA, warp 1: MMA, 2-3 idle
-constexpr int kQmmTmemCols = 512;      // the whole tensor memory: 2 x 256 accumulator columns
+constexpr int kQmmK = 128;             // columns per step: two quantisation groups, so that the per-step costs of the
+                                       // single-thread roles (waits, descriptors, commits) are paid once per 128 columns
+constexpr int kQmmRawStages = 4;       // ring of packed-code stages (NMAT x 8 KB each)
+constexpr int kQmmBSlots = 32;         // ring of activation slots (16 rows x 64 columns, 2 KB); a step takes 2, 4, 8 or 16
+constexpr int kQmmFirstDequantWarp = 4, kQmmDequantWarps = 16;      // four threads per weight row
+constexpr int kQmmFirstEpilogueWarp = 20, kQmmEpilogueWarps = 4;
+constexpr int kQmmThreads = (kQmmFirstEpilogueWarp + kQmmEpilogueWarps) * 32;
+constexpr int kQmmTmemCols = 512;      // columns 0..255: accumulators; 256..511: ring of dequantised weight stages
+constexpr int kQmmAccCols = 256;
 constexpr uint32_t kQmmSpin = 1u << 22;
 constexpr uint32_t kErrQmmTimeout = 0x7E000000u;
-
-static_assert(kQmmFirstEpilogueWarp % 4 == 0, "epilogue warp w reads TMEM lanes 32 * (w % 4)");
+static_assert(kQmmFirstEpilogueWarp % 4 == 0 && kQmmFirstDequantWarp % 4 == 0, "warp w touches TMEM lanes 32 * (w % 4)");
 
 struct QmmGroup {
-    const uint8_t* W[2];
-    const uint16_t* S[2];
+    const uint16_t* S[2];   // scale / bias planes of the group's matrices
     const uint16_t* B[2];
+    uint32_t expert;        // third coordinate of the weight tensor maps (0 for a dense matrix)
     uint32_t row_start;     // first row of the group in the (sorted) activation matrix
     uint32_t count;         // tokens of the group
     uint32_t tile_start;    // first token tile of the group in the global tile order
-    uint32_t pad;
+    uint32_t pad[4];
 };
-
 static_assert(sizeof(QmmGroup) == 64, "the context allocates 64 bytes per group-table row");
 
 struct QmmArgs {
@@ -64,11 +70,10 @@ struct QmmArgs {
     // routed source (prepare kernel)
     const uint8_t* pool_base;
     uint64_t expert_stride;
-    uint32_t w_off[2], s_off[2], b_off[2];
+    uint32_t s_off[2], b_off[2];
     const tf_group* route_groups;
     const uint32_t* route_counters;
     // dense source
-    const uint8_t* dense_W[2];
     const uint16_t* dense_S[2];
     const uint16_t* dense_B[2];
     uint32_t dense_tokens;
@@ -105,16 +110,32 @@ __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(smem_dst), "l"(map), "r"(c0), "r"(c1), "r"(mbar) : "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t smem_dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t mbar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(smem_dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(mbar) : "memory");
+}
+__device__ __forceinline__ void q_bulk_g2s(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t mbar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(mbar) : "memory");
+}
+// One lane of a converged warp; the address arithmetic around the elected instruction stays warp-uniform, so the
+// compiler keeps descriptors in uniform registers instead of moving them over for every instruction.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred = 0;
+    asm volatile("{\n\t.reg .pred px;\n\telect.sync _|px, 0xFFFFFFFF;\n\tselp.u32 %0, 1, 0, px;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void q_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_commit(uint32_t mbar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(mbar) : "memory");
 }
-__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem descriptor]
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
 }
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -124,6 +145,34 @@ __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
                  : "r"(taddr) : "memory");
 }
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// 16 consecutive 32-bit columns of this thread's TMEM lane <- 16 registers (four uint4)
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint4& a, const uint4& b, const uint4& c, const uint4& d) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w),
+                   "r"(c.x), "r"(c.y), "r"(c.z), "r"(c.w), "r"(d.x), "r"(d.y), "r"(d.z), "r"(d.w) : "memory");
+}
+// 8 consecutive 32-bit columns of this thread's TMEM lane <- 8 registers
+__device__ __forceinline__ void tc_st8(uint32_t taddr, const uint4& a, const uint4& b) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"r"(taddr), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ uint4 q_lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 q_lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t q_lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return v;
+}
 
 // K-major operand tile with the 128-byte swizzle: rows of 128 bytes, 8-row atoms of 1024 bytes.
 __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr) {
@@ -141,8 +190,8 @@ __global__ void qmm_prepare_kernel(QmmArgs a, int nmat, int dense) {
     if (dense) {
         ng = 1;
         QmmGroup g{};
-        for (int m = 0; m < nmat; ++m) { g.W[m] = a.dense_W[m]; g.S[m] = a.dense_S[m]; g.B[m] = a.dense_B[m]; }
-        g.row_start = 0; g.count = a.dense_tokens; g.tile_start = 0;
+        for (int m = 0; m < nmat; ++m) { g.S[m] = a.dense_S[m]; g.B[m] = a.dense_B[m]; }
+        g.expert = 0; g.row_start = 0; g.count = a.dense_tokens; g.tile_start = 0;
         a.groups[0] = g;
         tiles = (a.dense_tokens + kQmmTokMax - 1) / kQmmTokMax;
     } else {
@@ -152,11 +201,10 @@ __global__ void qmm_prepare_kernel(QmmArgs a, int nmat, int dense) {
             const uint8_t* blob = a.pool_base + (uint64_t)rg.expert * a.expert_stride;
             QmmGroup g{};
             for (int m = 0; m < nmat; ++m) {
-                g.W[m] = blob + a.w_off[m];
                 g.S[m] = reinterpret_cast<const uint16_t*>(blob + a.s_off[m]);
                 g.B[m] = reinterpret_cast<const uint16_t*>(blob + a.b_off[m]);
             }
-            g.row_start = rg.pair_start; g.count = rg.pair_count; g.tile_start = tiles;
+            g.expert = rg.expert; g.row_start = rg.pair_start; g.count = rg.pair_count; g.tile_start = tiles;
             a.groups[i] = g;
             tiles += (rg.pair_count + kQmmTokMax - 1) / kQmmTokMax;
         }
@@ -165,16 +213,20 @@ __global__ void qmm_prepare_kernel(QmmArgs a, int nmat, int dense) {
     a.totals[1] = tiles;
 }
 
+// Shared-memory plan (offsets from a 1024-byte aligned base).
 template <int NMAT>
 struct QmmSmem {
-    static constexpr uint32_t kATile = kQmmRows * 128;                 // 16 KB
-    static constexpr uint32_t kBTile = kQmmTokMax * 128;               // 32 KB
-    static constexpr uint32_t kStage = NMAT * kATile + kBTile;         // 64 KB / 48 KB
-    static constexpr int kStages = NMAT == 2 ? 3 : 4;
-    static constexpr int kPrefetch = NMAT == 2 ? 3 : 4;               // k-steps of packed codes a dequantiser thread keeps in flight
-    static constexpr uint32_t kRing = kStages * kStage;
-    static constexpr uint32_t kBars = kRing;                           // barriers and the TMEM address
-    static constexpr uint32_t kTotal = kRing + 256 + 1024;             // + barriers + slack for 1024-byte alignment
+    static constexpr uint32_t kRawMat = kQmmRows * (kQmmK / 2);              // 8 KB: 128 rows x 64 packed bytes
+    static constexpr uint32_t kRawStage = NMAT * kRawMat;
+    static constexpr uint32_t kOffRaw = 0;
+    static constexpr uint32_t kOffB = kOffRaw + kQmmRawStages * kRawStage;   // 32 slots x 2 KB
+    static constexpr uint32_t kOffScales = kOffB + kQmmBSlots * kQmmBoxRows * 128;
+    // scale and bias planes of a tile: 128 rows x (K / 64) bf16, two buffers, sized at launch
+    __host__ __device__ static uint32_t plane_bytes(uint32_t k) { return ((kQmmRows * (k / kGroup) * 2u) + 15u) & ~15u; }
+    __host__ __device__ static uint32_t scale_buf_bytes(uint32_t k) { return NMAT * 2 * plane_bytes(k); }
+    __host__ __device__ static uint32_t off_bars(uint32_t k) { return kOffScales + 2 * scale_buf_bytes(k); }
+    __host__ __device__ static uint32_t total(uint32_t k) { return off_bars(k) + 1024 /* barriers */ + 1024 /* alignment slack */; }
+    static constexpr int kAStages = 256 / (NMAT * (kQmmK / 2));              // TMEM ring of dequantised stages: 2 or 4
 };
 
 // Eight packed codes (one 32-bit word) -> eight fp16 weights w = half(q * s + b).
@@ -183,24 +235,7 @@ struct QmmSmem {
 // fp16 (s is a bf16) while |s| < 2^-5. Larger scales take the two-step form (1024 + q) - 1024.
 // Output order: PERMUTED (k0,k4,k1,k5,k2,k6,k3,k7), otherwise natural.
 template <bool NATURAL_K>
-__device__ __forceinline__ uint4 dequant8(uint32_t w, __half2 s_fast, __half2 s, __half2 b, bool fast) {
-    uint32_t t0, t1, t2, t3;
-    __half2 h0, h1, h2, h3;
-    if (fast) {
-        t0 = (w << 4) & 0x00F000F0u; t1 = w & 0x00F000F0u; t2 = (w >> 4) & 0x00F000F0u; t3 = (w >> 8) & 0x00F000F0u;
-        h0 = __hfma2(*reinterpret_cast<__half2*>(&t0), s_fast, b);     // (k0, k4)
-        h1 = __hfma2(*reinterpret_cast<__half2*>(&t1), s_fast, b);     // (k1, k5)
-        h2 = __hfma2(*reinterpret_cast<__half2*>(&t2), s_fast, b);     // (k2, k6)
-        h3 = __hfma2(*reinterpret_cast<__half2*>(&t3), s_fast, b);     // (k3, k7)
-    } else {
-        const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
-        t0 = (w & 0x000F000Fu) | 0x64006400u; t1 = ((w >> 4) & 0x000F000Fu) | 0x64006400u;
-        t2 = ((w >> 8) & 0x000F000Fu) | 0x64006400u; t3 = ((w >> 12) & 0x000F000Fu) | 0x64006400u;
-        h0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1024), s, b);
-        h1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1024), s, b);
-        h2 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t2), k1024), s, b);
-        h3 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t3), k1024), s, b);
-    }
+__device__ __forceinline__ uint4 order8(__half2 h0, __half2 h1, __half2 h2, __half2 h3) {
     const uint32_t u0 = *reinterpret_cast<uint32_t*>(&h0), u1 = *reinterpret_cast<uint32_t*>(&h1);
     const uint32_t u2 = *reinterpret_cast<uint32_t*>(&h2), u3 = *reinterpret_cast<uint32_t*>(&h3);
     if (!NATURAL_K) return make_uint4(u0, u1, u2, u3);
@@ -211,13 +246,31 @@ __device__ __forceinline__ uint4 dequant8(uint32_t w, __half2 s_fast, __half2 s,
     asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(o.w) : "r"(u2), "r"(u3));   // (k6, k7)
     return o;
 }
+template <bool NATURAL_K>
+__device__ __forceinline__ uint4 dequant8_fast(uint32_t w, __half2 s_fast, __half2 b) {
+    uint32_t t0 = (w << 4) & 0x00F000F0u, t1 = w & 0x00F000F0u, t2 = (w >> 4) & 0x00F000F0u, t3 = (w >> 8) & 0x00F000F0u;
+    return order8<NATURAL_K>(__hfma2(*reinterpret_cast<__half2*>(&t0), s_fast, b),      // (k0, k4)
+                             __hfma2(*reinterpret_cast<__half2*>(&t1), s_fast, b),      // (k1, k5)
+                             __hfma2(*reinterpret_cast<__half2*>(&t2), s_fast, b),      // (k2, k6)
+                             __hfma2(*reinterpret_cast<__half2*>(&t3), s_fast, b));     // (k3, k7)
+}
+template <bool NATURAL_K>
+__device__ __forceinline__ uint4 dequant8_wide(uint32_t w, __half2 s, __half2 b) {
+    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+    uint32_t t0 = (w & 0x000F000Fu) | 0x64006400u, t1 = ((w >> 4) & 0x000F000Fu) | 0x64006400u;
+    uint32_t t2 = ((w >> 8) & 0x000F000Fu) | 0x64006400u, t3 = ((w >> 12) & 0x000F000Fu) | 0x64006400u;
+    return order8<NATURAL_K>(__hfma2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1024), s, b),
+                             __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1024), s, b),
+                             __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t2), k1024), s, b),
+                             __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t3), k1024), s, b));
+}
 
 // Position of column k within its eight-column block in the PERMUTED order.
 __device__ __forceinline__ uint32_t permuted_col(uint32_t k) { return (k & ~7u) | ((k & 3u) << 1) | ((k >> 2) & 1u); }
 
-// Accumulator placement in the 512 TMEM columns, two buffers of 256. A tile whose accumulators fit one buffer
-// (one matrix, or two matrices of at most 128 tokens) takes the buffer used less often so far, so consecutive
-// tiles alternate and the epilogue of one overlaps the MMAs of the next; a two-matrix tile of more than 128
+// Accumulator placement in TMEM columns 0..255, two buffers of 128. A tile whose accumulators fit one buffer
+// (one matrix, or two matrices of at most 64 tokens) takes the buffer used less often so far, so consecutive
+// tiles alternate and the epilogue of one overlaps the MMAs of the next; a two-matrix tile of more than 64
 // tokens takes both. The MMA issuer and the epilogue warps replay the same sequence, so they agree.
 struct AccPlan {
     uint32_t uses0 = 0u, uses1 = 0u;
@@ -225,10 +278,10 @@ struct AccPlan {
     uint32_t buf = 0, col0 = 0, mat_stride = 0;
     template <int NMAT>
     __device__ __forceinline__ void next(uint32_t n_mma) {
-        both = NMAT == 2 && n_mma > 128u;
+        both = NMAT == 2 && n_mma > 64u;
         buf = both ? 0u : (uses0 <= uses1 ? 0u : 1u);
-        col0 = buf * 256u;
-        mat_stride = both ? 256u : 128u;
+        col0 = buf * 128u;
+        mat_stride = both ? 128u : 64u;
     }
     __device__ __forceinline__ bool takes(uint32_t b) const { return both || b == buf; }
     __device__ __forceinline__ uint32_t uses(uint32_t b) const { return b ? uses1 : uses0; }
@@ -240,51 +293,37 @@ struct AccPlan {
 
 template <int NMAT, bool NATURAL_K>
 __global__ void __launch_bounds__(kQmmThreads, 1)
-qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args) {
+qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map0,
+                   const __grid_constant__ CUtensorMap w_map1, const QmmArgs args) {
     extern __shared__ uint8_t smem_raw[];
     using L = QmmSmem<NMAT>;
-    constexpr int kQmmStages = L::kStages;
-    constexpr int kQmmPrefetch = L::kPrefetch;
+    constexpr int kAStages = L::kAStages;
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                      // swizzle atoms need 1024-byte alignment
     uint8_t* base_ptr = smem_raw + (base - raw);
-    const uint32_t bars = base + L::kBars;
-    auto bar_full_a = [&](uint32_t s) { return bars + s * 8; };
-    auto bar_full_b = [&](uint32_t s) { return bars + (kQmmMaxStages + s) * 8; };
-    auto bar_empty = [&](uint32_t s) { return bars + (2 * kQmmMaxStages + s) * 8; };
-    auto bar_acc_full = [&](uint32_t b) { return bars + (3 * kQmmMaxStages + b) * 8; };
-    auto bar_acc_empty = [&](uint32_t b) { return bars + (3 * kQmmMaxStages + 2 + b) * 8; };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::kBars + (3 * kQmmMaxStages + 4) * 8);
+    const uint32_t plane_bytes = L::plane_bytes(args.k);
+    const uint32_t scale_buf = L::scale_buf_bytes(args.k);
+    const uint32_t bars = base + L::off_bars(args.k);
+    // barrier map (8 bytes each)
+    auto bar_full_raw = [&](uint32_t s) { return bars + s * 8; };                            // 8: TMA tx
+    auto bar_empty_raw = [&](uint32_t s) { return bars + (8 + s) * 8; };                     // 8: dequant warps
+    auto bar_full_b = [&](uint32_t s) { return bars + (16 + s) * 8; };                       // 16: TMA tx
+    auto bar_empty_b = [&](uint32_t s) { return bars + (32 + s) * 8; };                      // 16: tcgen05.commit
+    auto bar_full_a = [&](uint32_t s) { return bars + (48 + s) * 8; };                       // 8: dequant warps
+    auto bar_empty_a = [&](uint32_t s) { return bars + (56 + s) * 8; };                      // 8: tcgen05.commit
+    auto bar_full_sc = [&](uint32_t b) { return bars + (64 + b) * 8; };                      // 2: TMA tx
+    auto bar_empty_sc = [&](uint32_t b) { return bars + (66 + b) * 8; };                     // 2: dequant warps
+    auto bar_acc_full = [&](uint32_t b) { return bars + (68 + b) * 8; };                     // 2: tcgen05.commit
+    auto bar_acc_empty = [&](uint32_t b) { return bars + (70 + b) * 8; };                    // 2: epilogue warps
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(base_ptr + L::off_bars(args.k) + 72 * 8);
+    volatile uint32_t* bslots_slot = tmem_slot + 1;
 
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
-    const uint32_t ksteps = args.k / kQmmK;
     const uint32_t groups_per_row = args.k / kGroup;
-    const uint32_t row_bytes = args.k / 2;
+    const uint32_t ksteps = (groups_per_row + 1) / 2;             // an odd last group is padded with zero columns
     const uint32_t wrow_tiles = (args.rows + kQmmRows - 1) / kQmmRows;
     const uint32_t ngroups = args.totals[0];
     const uint32_t total_tiles = args.totals[1] * wrow_tiles;
-
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < (uint32_t)kQmmStages; ++s) {
-            q_mbar_init(bar_full_a(s), kQmmDequantWarps);   // one arrival per dequantiser warp
-            q_mbar_init(bar_full_b(s), 1);                  // the TMA thread's expect_tx
-            q_mbar_init(bar_empty(s), 1);                   // tcgen05.commit
-        }
-        for (uint32_t b = 0; b < 2; ++b) {
-            q_mbar_init(bar_acc_full(b), 1);                // tcgen05.commit after the last step
-            q_mbar_init(bar_acc_empty(b), kQmmEpilogueWarps);
-        }
-        q_fence_async_smem();
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"((uint32_t)kQmmTmemCols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
 
     // maps a work item to (group, token tile within the group, weight-row tile)
     auto locate = [&](uint32_t tile, uint32_t& gi, uint32_t& tt, uint32_t& wt) {
@@ -298,37 +337,115 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
         gi = lo;
         tt = tglob - args.groups[lo].tile_start;
     };
-    // tokens of a tile, and the MMA's N (rounded up to 16)
     auto tile_tokens = [&](uint32_t count, uint32_t tt) {
         const uint32_t left = count - tt * kQmmTokMax;
         return left < (uint32_t)kQmmTokMax ? left : (uint32_t)kQmmTokMax;
     };
 
-    uint32_t fail = 0;
-    uint32_t it = 0;         // running k-step index over all of this CTA's tiles (ring position)
-
-    if (warp == 0) {
-        // ===================== TMA producer: activation tiles =====================
-        for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < 8; ++s) {
+            q_mbar_init(bar_full_raw(s), 1);
+            q_mbar_init(bar_empty_raw(s), kQmmDequantWarps);
+            q_mbar_init(bar_full_a(s), kQmmDequantWarps);
+            q_mbar_init(bar_empty_a(s), 1);
+        }
+        for (uint32_t s = 0; s < 16; ++s) { q_mbar_init(bar_full_b(s), 1); q_mbar_init(bar_empty_b(s), 1); }
+        for (uint32_t b = 0; b < 2; ++b) {
+            q_mbar_init(bar_full_sc(b), 1);
+            q_mbar_init(bar_empty_sc(b), kQmmDequantWarps);
+            q_mbar_init(bar_acc_full(b), 1);
+            q_mbar_init(bar_acc_empty(b), kQmmEpilogueWarps);
+        }
+        q_fence_async_smem();
+        // Activation slots per step, fixed for this CTA: the largest tile it will meet, rounded up to 1, 2, 4 or 8
+        // boxes of 16 rows, so that a step's rows are contiguous and the ring never has to be re-partitioned.
+        uint32_t max_tok = 1;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
             uint32_t gi, tt, wt;
             locate(tile, gi, tt, wt);
+            const uint32_t n = tile_tokens(args.groups[gi].count, tt);
+            max_tok = n > max_tok ? n : max_tok;
+        }
+        const uint32_t boxes = (max_tok + kQmmBoxRows - 1) / kQmmBoxRows;
+        *bslots_slot = boxes <= 1 ? 1u : boxes <= 2 ? 2u : boxes <= 4 ? 4u : 8u;
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"((uint32_t)kQmmTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t b_slots = *bslots_slot;                            // 16-row boxes per 64-column half of an activation stage
+    const uint32_t b_stages = kQmmBSlots / (2 * b_slots);             // 16, 8, 4 or 2
+    const uint32_t b_half_bytes = b_slots * kQmmBoxRows * 128;        // one 64-column half of a stage
+    const uint32_t a_ring = tmem_base + kQmmAccCols;
+
+    uint32_t fail = 0;
+    uint32_t it = 0;         // running k-step index over all of this CTA's tiles (ring positions)
+
+    if (warp == 0) {
+        // ===================== copy issuer: packed codes, activation boxes, scale planes =====================
+        uint32_t tile_idx = 0, sb = 0, ub = 0;                     // activation ring position and lap
+        auto issue_scales = [&](uint32_t tile, uint32_t idx) -> bool {
+            const uint32_t buf = idx & 1, n = idx >> 1;
+            if (n > 0 && !q_mbar_wait(bar_empty_sc(buf), (n - 1) & 1)) return false;
+            if (lane == 0) {
+                uint32_t gi, tt, wt;
+                locate(tile, gi, tt, wt);
+                const uint32_t row0 = wt * kQmmRows;
+                const uint32_t nrows = args.rows - row0 < (uint32_t)kQmmRows ? args.rows - row0 : (uint32_t)kQmmRows;
+                const uint32_t bytes = nrows * groups_per_row * 2;        // a multiple of 16: rows are a multiple of 8
+                q_mbar_expect_tx(bar_full_sc(buf), NMAT * 2 * bytes);
+                for (int m = 0; m < NMAT; ++m) {
+                    const uint32_t dst = base + L::kOffScales + buf * scale_buf + m * 2 * plane_bytes;
+                    q_bulk_g2s(dst, args.groups[gi].S[m] + (size_t)row0 * groups_per_row, bytes, bar_full_sc(buf));
+                    q_bulk_g2s(dst + plane_bytes, args.groups[gi].B[m] + (size_t)row0 * groups_per_row, bytes, bar_full_sc(buf));
+                }
+            }
+            __syncwarp();
+            return true;
+        };
+        if (blockIdx.x < total_tiles && !issue_scales(blockIdx.x, 0)) fail = kErrQmmTimeout | 6;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x, ++tile_idx) {
+            uint32_t gi, tt, wt;
+            locate(tile, gi, tt, wt);
+            const uint32_t expert = args.groups[gi].expert;
             const uint32_t row0 = args.groups[gi].row_start + tt * kQmmTokMax;
             const uint32_t boxes = (tile_tokens(args.groups[gi].count, tt) + kQmmBoxRows - 1) / kQmmBoxRows;
+            // the next tile's scale planes go out once the dequantisers are certainly done with the tile before
+            // this one (they have consumed this tile's first step when its ring slot comes round again)
+            const uint32_t scale_step = ksteps > (uint32_t)kQmmRawStages ? (uint32_t)kQmmRawStages : ksteps - 1;
             for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
-                const uint32_t s = it % kQmmStages, use = it / kQmmStages;
-                if (use > 0 && !q_mbar_wait(bar_empty(s), (use - 1) & 1)) { fail = kErrQmmTimeout | 1; break; }
-                if (lane == 0) {
-                    q_mbar_expect_tx(bar_full_b(s), boxes * kQmmBoxRows * 128);
-                    for (uint32_t b = 0; b < boxes; ++b)
-                        tma_load_2d(base + s * L::kStage + NMAT * L::kATile + b * kQmmBoxRows * 128, &x_map, (int)(ks * kQmmK),
-                                    (int)(row0 + b * kQmmBoxRows), bar_full_b(s));
+                const uint32_t sr = it % kQmmRawStages, ur = it / kQmmRawStages;
+                if (ur > 0 && !q_mbar_wait(bar_empty_raw(sr), (ur - 1) & 1)) { fail = kErrQmmTimeout | 1; break; }
+                const bool leader = elect_one();
+                if (leader) {
+                    q_mbar_expect_tx(bar_full_raw(sr), L::kRawStage);
+                    tma_load_3d(base + L::kOffRaw + sr * L::kRawStage, &w_map0, (int)(ks * (kQmmK / 2)), (int)(wt * kQmmRows), (int)expert, bar_full_raw(sr));
+                    if (NMAT == 2)
+                        tma_load_3d(base + L::kOffRaw + sr * L::kRawStage + L::kRawMat, &w_map1, (int)(ks * (kQmmK / 2)), (int)(wt * kQmmRows), (int)expert, bar_full_raw(sr));
+                }
+                if (ub > 0 && !q_mbar_wait(bar_empty_b(sb), (ub - 1) & 1)) { fail = kErrQmmTimeout | 7; break; }
+                if (leader) {
+                    q_mbar_expect_tx(bar_full_b(sb), 2 * boxes * kQmmBoxRows * 128);
+                    for (uint32_t h = 0; h < 2; ++h)              // columns past K (odd group count) read as zero
+                        for (uint32_t b = 0; b < boxes; ++b)
+                            tma_load_2d(base + L::kOffB + sb * 2 * b_half_bytes + h * b_half_bytes + b * kQmmBoxRows * 128, &x_map,
+                                        (int)(ks * kQmmK + h * 64), (int)(row0 + b * kQmmBoxRows), bar_full_b(sb));
                 }
                 __syncwarp();
+                if (++sb == b_stages) { sb = 0; ++ub; }
+                if (ks == scale_step && tile + gridDim.x < total_tiles && !issue_scales(tile + gridDim.x, tile_idx + 1)) { fail = kErrQmmTimeout | 6; break; }
             }
         }
     } else if (warp == 1) {
         // ===================== MMA issuer =====================
         AccPlan plan;
+        uint32_t sb = 0, ub = 0;                                  // activation ring position and lap
+        const uint64_t b_desc0 = umma_smem_desc(base + L::kOffB);
         for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
             uint32_t gi, tt, wt;
             locate(tile, gi, tt, wt);
@@ -344,107 +461,102 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
             tc_fence_after();
             const uint32_t acc = tmem_base + plan.col0;
             for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
-                const uint32_t s = it % kQmmStages, use = it / kQmmStages;
-                if (!q_mbar_wait(bar_full_a(s), use & 1) || !q_mbar_wait(bar_full_b(s), use & 1)) { fail = kErrQmmTimeout | 3; break; }
+                const uint32_t sa = it % kAStages, ua = it / kAStages;
+                if (!q_mbar_wait(bar_full_a(sa), ua & 1) || !q_mbar_wait(bar_full_b(sb), ub & 1)) { fail = kErrQmmTimeout | 3; break; }
                 tc_fence_after();
-                if (lane == 0) {
-                    const uint32_t stage = base + s * L::kStage;
-                    const uint64_t b_desc = umma_smem_desc(stage + NMAT * L::kATile);
+                const bool leader = elect_one();
+                const uint64_t b_desc = b_desc0 + (uint64_t)((sb * 2 * b_half_bytes) >> 4);
+                const uint32_t a_stage = a_ring + sa * (NMAT * 64);
+                const uint32_t nj = (2 * ks + 1 < groups_per_row) ? 8u : 4u;     // the padded half of an odd last step is skipped
 #pragma unroll
-                    for (int m = 0; m < NMAT; ++m) {
-                        const uint64_t a_desc = umma_smem_desc(stage + m * L::kATile);
+                for (int m = 0; m < NMAT; ++m) {
 #pragma unroll
-                        for (int j = 0; j < kQmmK / 16; ++j)      // 16 columns = 32 bytes along K per MMA
-                            tc_mma_f16(acc + m * plan.mat_stride, a_desc + (uint64_t)(j * 2), b_desc + (uint64_t)(j * 2), idesc,
-                                       (ks > 0 || j > 0) ? 1u : 0u);
+                    for (int j = 0; j < kQmmK / 16; ++j) {        // 16 columns of K: 8 TMEM columns of A, 32 bytes of B
+                        if ((uint32_t)j < nj && leader)
+                            tc_mma_f16_ts(acc + m * plan.mat_stride, a_stage + m * 64 + j * 8,
+                                          b_desc + (uint64_t)((j >> 2) * (b_half_bytes >> 4) + (j & 3) * 2), idesc, (ks > 0 || j > 0) ? 1u : 0u);
                     }
-                    tc_commit(bar_empty(s));                      // the stage is free once these MMAs have read it
+                }
+                if (leader) {
+                    tc_commit(bar_empty_a(sa));                   // both rings' stages are free once these MMAs have read them
+                    tc_commit(bar_empty_b(sb));
                     if (ks + 1 == ksteps) {
                         if (plan.both || plan.buf == 0) tc_commit(bar_acc_full(0));
                         if (plan.both || plan.buf == 1) tc_commit(bar_acc_full(1));
                     }
                 }
                 __syncwarp();
+                if (++sb == b_stages) { sb = 0; ++ub; }
             }
             plan.done();
         }
     } else if (warp >= kQmmFirstDequantWarp && warp < kQmmFirstEpilogueWarp) {
-        // ===================== dequantisers: two threads per weight row =====================
-        const uint32_t idx = threadIdx.x - kQmmFirstDequantWarp * kWarp;
-        const uint32_t r = idx >> 1, hf = idx & 1;               // row within the tile, half of the 64 columns
-        const uint32_t row_off = (r >> 3) * 1024 + (r & 7) * 128, sw = r & 7;
-        const uint32_t my_tiles = total_tiles > blockIdx.x ? (total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
-        const uint32_t total_steps = my_tiles * ksteps;
-        // The packed codes come straight from global memory, so each thread keeps a few k-steps of them in
-        // flight in registers (kPrefetch); the fetch cursor runs ahead of the processing loop and crosses tile boundaries.
-        uint32_t f_tile = blockIdx.x, f_ks = 0;
-        const uint8_t* f_w[NMAT];
-        const uint16_t* f_s[NMAT];
-        const uint16_t* f_b[NMAT];
-        bool f_valid = false;
-        auto f_resolve = [&]() {
-            uint32_t gi, tt, wt;
-            locate(f_tile, gi, tt, wt);
-            const uint32_t wrow = wt * kQmmRows + r;
-            f_valid = wrow < args.rows;
-#pragma unroll
-            for (int m = 0; m < NMAT; ++m) {
-                f_w[m] = args.groups[gi].W[m] + (size_t)wrow * row_bytes + hf * 16;
-                f_s[m] = args.groups[gi].S[m] + (size_t)wrow * groups_per_row;
-                f_b[m] = args.groups[gi].B[m] + (size_t)wrow * groups_per_row;
-            }
-        };
-        uint4 codes[kQmmPrefetch][NMAT];
-        uint32_t sb[kQmmPrefetch][NMAT];
-        auto fetch = [&](uint4 (&c)[NMAT], uint32_t (&q)[NMAT]) {
-#pragma unroll
-            for (int m = 0; m < NMAT; ++m) {
-                if (f_valid) {
-                    c[m] = __ldg(reinterpret_cast<const uint4*>(f_w[m] + f_ks * 32));
-                    q[m] = (uint32_t)__ldg(f_s[m] + f_ks) | ((uint32_t)__ldg(f_b[m] + f_ks) << 16);
-                } else {
-                    c[m] = make_uint4(0u, 0u, 0u, 0u);
-                    q[m] = 0u;
-                }
-            }
-            if (++f_ks == ksteps) {
-                f_ks = 0;
-                f_tile += gridDim.x;
-                if (f_tile < total_tiles) f_resolve();
-            }
-        };
-        if (total_steps) f_resolve();
-#pragma unroll
-        for (int p = 0; p < kQmmPrefetch; ++p)
-            if ((uint32_t)p < total_steps) fetch(codes[p], sb[p]);
-        for (uint32_t it0 = 0; it0 < total_steps && !fail; it0 += kQmmPrefetch) {
-#pragma unroll
-            for (int p = 0; p < kQmmPrefetch; ++p) {
-                const uint32_t itp = it0 + p;
-                if (itp >= total_steps) break;
-                const uint32_t s = itp % kQmmStages, use = itp / kQmmStages;
-                if (use > 0 && !q_mbar_wait(bar_empty(s), (use - 1) & 1)) { fail = kErrQmmTimeout | 4; break; }
+        // ===================== dequantisers: four threads per weight row =====================
+        const uint32_t dw = warp - kQmmFirstDequantWarp;
+        const uint32_t q = dw & 3, qc = dw >> 2;                 // TMEM lane quarter; quarter of the step's 128 columns
+        const uint32_t r = q * kWarp + lane;                     // row within the tile = TMEM lane
+        // packed codes of the row: 64 bytes whose 16-byte chunks sit at chunk ^ ((row / 2) % 4) (64-byte TMA swizzle)
+        const uint32_t raw_off = r * 64 + ((qc ^ ((r >> 1) & 3u)) << 4);
+        const uint32_t sc_off = r * groups_per_row * 2;
+        const uint32_t a_lane = a_ring + ((q * kWarp) << 16) + qc * 16;
+        uint32_t tile_idx = 0;
+        for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x, ++tile_idx) {
+            const uint32_t buf = tile_idx & 1;
+            if (!q_mbar_wait(bar_full_sc(buf), (tile_idx >> 1) & 1)) { fail = kErrQmmTimeout | 8; break; }
+            const uint32_t sc_base = base + L::kOffScales + buf * scale_buf + sc_off;
+            for (uint32_t ks = 0; ks < ksteps; ++ks, ++it) {
+                const uint32_t sr = it % kQmmRawStages, ur = it / kQmmRawStages;
+                const uint32_t sa = it % kAStages, ua = it / kAStages;
+                const uint32_t grp_idx = 2 * ks + (qc >> 1);      // this thread's 32 columns lie in one quantisation group
+                const bool real = grp_idx < groups_per_row;      // the padded group of an odd last step dequantises to zero
+                if (!q_mbar_wait(bar_full_raw(sr), ur & 1)) { fail = kErrQmmTimeout | 4; break; }
+                uint4 codes[NMAT];
+                float sf[NMAT], bf[NMAT];
+                bool fast = true;
 #pragma unroll
                 for (int m = 0; m < NMAT; ++m) {
-                    const float sf = bf16_bits_to_float((uint16_t)(sb[p][m] & 0xFFFFu)), bf = bf16_bits_to_float((uint16_t)(sb[p][m] >> 16));
-                    const bool fast = fabsf(sf) < 0.03125f;
-                    const __half2 s_fast = __float2half2_rn(sf * 1048576.0f), s2 = __float2half2_rn(sf), b2 = __float2half2_rn(bf);
-                    uint8_t* arow = base_ptr + s * L::kStage + m * L::kATile + row_off;
-                    const uint32_t w[4] = {codes[p][m].x, codes[p][m].y, codes[p][m].z, codes[p][m].w};
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)                   // 8 codes -> 16 bytes = one swizzle chunk
-                        *reinterpret_cast<uint4*>(arow + (((hf * 4 + c) ^ sw) << 4)) = dequant8<NATURAL_K>(w[c], s_fast, s2, b2, fast);
+                    codes[m] = q_lds128(base + L::kOffRaw + sr * L::kRawStage + m * L::kRawMat + raw_off);
+                    sf[m] = real ? bf16_bits_to_float((uint16_t)q_lds16(sc_base + m * 2 * plane_bytes + grp_idx * 2)) : 0.0f;
+                    bf[m] = real ? bf16_bits_to_float((uint16_t)q_lds16(sc_base + m * 2 * plane_bytes + plane_bytes + grp_idx * 2)) : 0.0f;
+                    fast = fast && fabsf(sf[m]) < 0.03125f;
                 }
-                q_fence_async_smem();                             // generic writes -> visible to the tensor core's async proxy
+                uint4 out[NMAT][4];
+                if (__all_sync(kFullMask, fast)) {                // one branch per warp and step, both arms straight-line
+#pragma unroll
+                    for (int m = 0; m < NMAT; ++m) {
+                        const __half2 s_fast = __float2half2_rn(sf[m] * 1048576.0f), b2 = __float2half2_rn(bf[m]);
+                        out[m][0] = dequant8_fast<NATURAL_K>(codes[m].x, s_fast, b2);
+                        out[m][1] = dequant8_fast<NATURAL_K>(codes[m].y, s_fast, b2);
+                        out[m][2] = dequant8_fast<NATURAL_K>(codes[m].z, s_fast, b2);
+                        out[m][3] = dequant8_fast<NATURAL_K>(codes[m].w, s_fast, b2);
+                    }
+                } else {
+#pragma unroll
+                    for (int m = 0; m < NMAT; ++m) {
+                        const __half2 s2 = __float2half2_rn(sf[m]), b2 = __float2half2_rn(bf[m]);
+                        out[m][0] = dequant8_wide<NATURAL_K>(codes[m].x, s2, b2);
+                        out[m][1] = dequant8_wide<NATURAL_K>(codes[m].y, s2, b2);
+                        out[m][2] = dequant8_wide<NATURAL_K>(codes[m].z, s2, b2);
+                        out[m][3] = dequant8_wide<NATURAL_K>(codes[m].w, s2, b2);
+                    }
+                }
                 __syncwarp();
-                if (lane == 0) q_mbar_arrive(bar_full_a(s));
-                if (itp + kQmmPrefetch < total_steps) fetch(codes[p], sb[p]);   // refill the slot just consumed
+                if (lane == 0) q_mbar_arrive(bar_empty_raw(sr));  // the codes are in registers
+                if (ua > 0 && !q_mbar_wait(bar_empty_a(sa), (ua - 1) & 1)) { fail = kErrQmmTimeout | 5; break; }
+                tc_fence_after();
+#pragma unroll
+                for (int m = 0; m < NMAT; ++m) tc_st16(a_lane + sa * (NMAT * 64) + m * 64, out[m][0], out[m][1], out[m][2], out[m][3]);
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) q_mbar_arrive(bar_full_a(sa));
             }
+            __syncwarp();
+            if (lane == 0) q_mbar_arrive(bar_empty_sc(buf));      // done with this tile's scale planes
         }
     } else if (warp >= kQmmFirstEpilogueWarp) {
         // ===================== epilogue: TMEM -> registers -> global =====================
         const uint32_t q = warp & 3;                              // TMEM lane quarter this warp may read
-        const uint32_t chunk_par = (warp - kQmmFirstEpilogueWarp) >> 2;   // which 16-column chunks this warp takes
         const uint32_t r = q * kWarp + lane;                      // weight row within the tile = TMEM lane
         AccPlan plan;
         for (uint32_t tile = blockIdx.x; tile < total_tiles && !fail; tile += gridDim.x) {
@@ -458,13 +570,13 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const QmmArgs args
             plan.next<NMAT>((ntok + 15u) & ~15u);
 #pragma unroll
             for (uint32_t b = 0; b < 2; ++b) {
-                if (plan.takes(b) && !q_mbar_wait(bar_acc_full(b), plan.uses(b) & 1)) fail = kErrQmmTimeout | 5;
+                if (plan.takes(b) && !q_mbar_wait(bar_acc_full(b), plan.uses(b) & 1)) fail = kErrQmmTimeout | 9;
             }
             if (fail) break;
             tc_fence_after();
             const uint32_t acc = tmem_base + ((q * kWarp) << 16) + plan.col0;
             uint16_t* out_row = args.out + (size_t)(grp.row_start + tok0) * args.out_stride + out_col;
-            for (uint32_t c0 = chunk_par * 16; c0 < ntok; c0 += 32) {
+            for (uint32_t c0 = 0; c0 < ntok; c0 += 16) {
                 uint32_t v0[16], v1[16];
                 tc_ld16(acc + c0, v0);
                 if (NMAT == 2) tc_ld16(acc + plan.mat_stride + c0, v1);
@@ -522,30 +634,54 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// fp16 matrix [rows, k] with a row stride: box = 64 columns x 64 rows, 128-byte swizzle, zero fill outside.
+// fp16 matrix [rows, k] with a row stride: box = 64 columns x 16 rows, 128-byte swizzle, zero fill outside.
 static tf_status make_x_map(tf_context* ctx, CUtensorMap* map, const void* x, uint64_t rows, uint32_t k, uint32_t stride_elems,
                             const char* name) {
     EncodeTiledFn fn = encode_tiled_fn();
     TF_REQUIRE(ctx, fn != nullptr, TF_ERR_UNSUPPORTED, "%s: cuTensorMapEncodeTiled is not available in this driver", name);
     const cuuint64_t dims[2] = {k, rows};
     const cuuint64_t strides[1] = {(cuuint64_t)stride_elems * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kQmmK, (cuuint32_t)kQmmBoxRows};
+    const cuuint32_t box[2] = {64, (cuuint32_t)kQmmBoxRows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    TF_REQUIRE(ctx, r == CUDA_SUCCESS, TF_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed (%d)", name, (int)r);
+    TF_REQUIRE(ctx, r == CUDA_SUCCESS, TF_ERR_CUDA, "%s: cuTensorMapEncodeTiled(activations) failed (%d)", name, (int)r);
     return TF_OK;
 }
 
+// Packed int4 weights as bytes [experts, rows, k / 2]: box = 64 bytes x 128 rows x 1 expert, 64-byte swizzle
+// (the 16-byte chunks of a row are permuted by (row / 2) % 4, which makes the row-per-lane LDS.128 conflict
+// free); rows past the matrix and bytes past the row read as zero.
+static tf_status make_w_map(tf_context* ctx, CUtensorMap* map, const void* w, uint32_t rows, uint32_t k, uint64_t experts,
+                            uint64_t expert_stride, const char* name) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    TF_REQUIRE(ctx, fn != nullptr, TF_ERR_UNSUPPORTED, "%s: cuTensorMapEncodeTiled is not available in this driver", name);
+    const cuuint64_t dims[3] = {k / 2, rows, experts};
+    const cuuint64_t strides[2] = {(cuuint64_t)(k / 2), expert_stride};
+    const cuuint32_t box[3] = {(cuuint32_t)(kQmmK / 2), (cuuint32_t)kQmmRows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(w), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TF_REQUIRE(ctx, r == CUDA_SUCCESS, TF_ERR_CUDA, "%s: cuTensorMapEncodeTiled(weights) failed (%d)", name, (int)r);
+    return TF_OK;
+}
+
+// W[m]: base of matrix m's packed plane for expert 0 (dense: the matrix itself).
 template <int NMAT, bool NATURAL_K>
 static tf_status launch_qmm(tf_context* ctx, void* stream, QmmArgs& a, const void* x, uint64_t x_rows, uint32_t x_stride,
-                            bool dense, const char* name) {
-    TF_REQUIRE(ctx, a.k % kQmmK == 0 && a.k >= (uint32_t)kQmmK, TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);
+                            const uint8_t* const* W, uint64_t experts, uint64_t expert_stride, bool dense, const char* name) {
+    TF_REQUIRE(ctx, a.k % kGroup == 0 && a.k >= (uint32_t)kGroup, TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);
+    TF_REQUIRE(ctx, a.rows % 8 == 0 && a.rows > 0, TF_ERR_INVALID_ARGUMENT, "%s: the weight rows must be a positive multiple of 8", name);
     TF_REQUIRE(ctx, aligned(x, 16) && (x_stride * 2) % 16 == 0, TF_ERR_ALIGNMENT, "%s: activation rows must be 16-byte aligned", name);
     TF_REQUIRE(ctx, ctx->qmm_groups != nullptr, TF_ERR_OUT_OF_MEMORY, "%s: context scratch missing", name);
-    CUtensorMap map;
-    if (tf_status s = make_x_map(ctx, &map, x, x_rows, a.k, x_stride, name)) return s;
+    const uint32_t smem = QmmSmem<NMAT>::total(a.k);
+    TF_REQUIRE(ctx, smem <= 227u * 1024u, TF_ERR_UNSUPPORTED, "%s: K=%u needs %u bytes of shared memory for the scale planes", name, a.k, smem);
+    CUtensorMap xmap, wmap[2];
+    if (tf_status s = make_x_map(ctx, &xmap, x, x_rows, a.k, x_stride, name)) return s;
+    for (int m = 0; m < 2; ++m)
+        if (tf_status s = make_w_map(ctx, &wmap[m], W[m < NMAT ? m : 0], a.rows, a.k, experts, dense ? (uint64_t)a.rows * (a.k / 2) : expert_stride, name)) return s;
     a.groups = static_cast<QmmGroup*>(ctx->qmm_groups);
     a.totals = ctx->qmm_totals;
     a.error = ctx->device_error;
@@ -553,12 +689,12 @@ static tf_status launch_qmm(tf_context* ctx, void* stream, QmmArgs& a, const voi
     qmm_prepare_kernel<<<1, 32, 0, st>>>(a, NMAT, dense ? 1 : 0);
     if (tf_status s = check_launch(ctx, "qmm_prepare")) return s;
     auto kern = qmm_tcgen05_kernel<NMAT, NATURAL_K>;
-    static bool configured = false;
-    if (!configured) {
-        TF_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QmmSmem<NMAT>::kTotal));
-        configured = true;
+    static uint32_t configured = 0;
+    if (smem > configured) {
+        TF_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
     }
-    kern<<<ctx->sm_count, kQmmThreads, QmmSmem<NMAT>::kTotal, st>>>(map, a);
+    kern<<<ctx->sm_count, kQmmThreads, smem, st>>>(xmap, wmap[0], wmap[1], a);
     return check_launch(ctx, name);
 }
 
@@ -567,31 +703,37 @@ static tf_status launch_qmm(tf_context* ctx, void* stream, QmmArgs& a, const voi
 extern "C" {
 
 tf_status tf_grouped_moe_tensorcore(tf_context* ctx, void* stream, const void* x_sorted, uint32_t x_rows,
-                                    const void* pool_layer_base, uint64_t expert_stride, const tf_expert_offsets* offsets,
-                                    const tf_device_routes* routes, void* acts_scratch, void* out_rows,
-                                    uint32_t d, uint32_t f) {
+                                    const void* pool_layer_base, uint64_t expert_stride, uint32_t num_experts,
+                                    const tf_expert_offsets* offsets, const tf_device_routes* routes,
+                                    void* acts_scratch, void* out_rows, uint32_t d, uint32_t f) {
     const char* name = "tf_grouped_moe_tensorcore";
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, x_sorted && pool_layer_base && offsets && routes && acts_scratch && out_rows, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
     TF_REQUIRE(ctx, d % 64 == 0 && f % 64 == 0 && d > 0 && f > 0, TF_ERR_INVALID_ARGUMENT, "%s: D and F must be positive multiples of 64", name);
+    TF_REQUIRE(ctx, num_experts > 0 && num_experts <= TF_MAX_ROUTER_EXPERTS, TF_ERR_INVALID_ARGUMENT, "%s: numExperts must be in 1...256", name);
     const uint32_t all[9] = {offsets->gate_w_off, offsets->gate_s_off, offsets->gate_b_off, offsets->up_w_off, offsets->up_s_off,
                              offsets->up_b_off, offsets->down_w_off, offsets->down_s_off, offsets->down_b_off};
     for (uint32_t v : all) TF_REQUIRE(ctx, v % 16 == 0, TF_ERR_ALIGNMENT, "%s: blob sub-tensor offset %u is not a multiple of 16 bytes", name, v);
     TF_REQUIRE(ctx, tf::aligned(pool_layer_base, 16) && expert_stride % 16 == 0, TF_ERR_ALIGNMENT, "%s: pool must be 16-byte aligned", name);
     if (x_rows == 0) return TF_OK;
+    const uint8_t* pool = static_cast<const uint8_t*>(pool_layer_base);
     tf::QmmArgs a{};
-    a.pool_base = static_cast<const uint8_t*>(pool_layer_base); a.expert_stride = expert_stride;
-    a.w_off[0] = offsets->gate_w_off; a.s_off[0] = offsets->gate_s_off; a.b_off[0] = offsets->gate_b_off;
-    a.w_off[1] = offsets->up_w_off;   a.s_off[1] = offsets->up_s_off;   a.b_off[1] = offsets->up_b_off;
+    a.pool_base = pool; a.expert_stride = expert_stride;
+    a.s_off[0] = offsets->gate_s_off; a.b_off[0] = offsets->gate_b_off;
+    a.s_off[1] = offsets->up_s_off;   a.b_off[1] = offsets->up_b_off;
     a.route_groups = routes->groups; a.route_counters = routes->counters;
     a.rows = f; a.k = d; a.out = static_cast<uint16_t*>(acts_scratch); a.out_stride = f; a.round_gate_up = 0;
-    if (tf_status s = tf::launch_qmm<2, false>(ctx, stream, a, x_sorted, x_rows, d, false, "tf_grouped_moe_tensorcore(gate/up)")) return s;
+    const uint8_t* w_gu[2] = {pool + offsets->gate_w_off, pool + offsets->up_w_off};
+    if (tf_status s = tf::launch_qmm<2, false>(ctx, stream, a, x_sorted, x_rows, d, w_gu, num_experts, expert_stride, false,
+                                                "tf_grouped_moe_tensorcore(gate/up)")) return s;
     tf::QmmArgs b{};
-    b.pool_base = a.pool_base; b.expert_stride = expert_stride;
-    b.w_off[0] = offsets->down_w_off; b.s_off[0] = offsets->down_s_off; b.b_off[0] = offsets->down_b_off;
+    b.pool_base = pool; b.expert_stride = expert_stride;
+    b.s_off[0] = offsets->down_s_off; b.b_off[0] = offsets->down_b_off;
     b.route_groups = routes->groups; b.route_counters = routes->counters;
     b.rows = d; b.k = f; b.out = static_cast<uint16_t*>(out_rows); b.out_stride = d;
-    return tf::launch_qmm<1, false>(ctx, stream, b, acts_scratch, x_rows, f, false, "tf_grouped_moe_tensorcore(down)");
+    const uint8_t* w_dn[2] = {pool + offsets->down_w_off, pool + offsets->down_w_off};
+    return tf::launch_qmm<1, false>(ctx, stream, b, acts_scratch, x_rows, f, w_dn, num_experts, expert_stride, false,
+                                    "tf_grouped_moe_tensorcore(down)");
 }
 
 tf_status tf_int4_qmm(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off, const void* scales,
@@ -603,14 +745,14 @@ tf_status tf_int4_qmm(tf_context* ctx, void* stream, const void* weights, uint64
     TF_REQUIRE(ctx, k % 64 == 0 && k > 0, TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);   // MPPPrefillInt4QMM.swift:43-55
     if (m == 0 || n == 0) return TF_OK;
     tf::QmmArgs a{};
-    a.dense_W[0] = tf::byte_ptr(weights, weights_off);
+    const uint8_t* w[2] = {tf::byte_ptr(weights, weights_off), tf::byte_ptr(weights, weights_off)};
     a.dense_S[0] = reinterpret_cast<const uint16_t*>(tf::byte_ptr(scales, scales_off));
     a.dense_B[0] = reinterpret_cast<const uint16_t*>(tf::byte_ptr(biases, biases_off));
-    TF_REQUIRE(ctx, tf::aligned(a.dense_W[0], 16) && tf::aligned(a.dense_S[0], 2) && tf::aligned(a.dense_B[0], 2) && (k / 2) % 16 == 0,
-               TF_ERR_ALIGNMENT, "%s: packed rows must be 16-byte aligned", name);
+    TF_REQUIRE(ctx, tf::aligned(w[0], 16) && tf::aligned(a.dense_S[0], 16) && tf::aligned(a.dense_B[0], 16),
+               TF_ERR_ALIGNMENT, "%s: weight, scale and bias planes must be 16-byte aligned", name);
     a.dense_tokens = m; a.rows = n; a.k = k;
     a.out = reinterpret_cast<uint16_t*>(tf::byte_ptr(y, y_off)); a.out_stride = n;
-    return tf::launch_qmm<1, true>(ctx, stream, a, tf::byte_ptr(x, x_off), m, k, true, name);
+    return tf::launch_qmm<1, true>(ctx, stream, a, tf::byte_ptr(x, x_off), m, k, w, 1, 0, true, name);
 }
 
 tf_status tf_shared_expert_int4_tensorcore(tf_context* ctx, void* stream, const void* x, uint32_t x_stride_elements,
@@ -630,17 +772,20 @@ tf_status tf_shared_expert_int4_tensorcore(tf_context* ctx, void* stream, const 
         W[i] = tf::byte_ptr(ps[i]->weights, ps[i]->weights_off);
         S[i] = reinterpret_cast<const uint16_t*>(tf::byte_ptr(ps[i]->scales, ps[i]->scales_off));
         B[i] = reinterpret_cast<const uint16_t*>(tf::byte_ptr(ps[i]->biases, ps[i]->biases_off));
-        TF_REQUIRE(ctx, tf::aligned(W[i], 16) && tf::aligned(S[i], 2) && tf::aligned(B[i], 2), TF_ERR_ALIGNMENT, "%s: planes must be 16-byte aligned", name);
+        TF_REQUIRE(ctx, tf::aligned(W[i], 16) && tf::aligned(S[i], 16) && tf::aligned(B[i], 16), TF_ERR_ALIGNMENT, "%s: planes must be 16-byte aligned", name);
     }
     tf::QmmArgs a{};
-    a.dense_W[0] = W[0]; a.dense_S[0] = S[0]; a.dense_B[0] = B[0];
-    a.dense_W[1] = W[1]; a.dense_S[1] = S[1]; a.dense_B[1] = B[1];
+    a.dense_S[0] = S[0]; a.dense_B[0] = B[0];
+    a.dense_S[1] = S[1]; a.dense_B[1] = B[1];
     a.dense_tokens = rows; a.rows = fs; a.k = d; a.out = static_cast<uint16_t*>(scratch_act); a.out_stride = fs; a.round_gate_up = 1;
-    if (tf_status s = tf::launch_qmm<2, true>(ctx, stream, a, x, rows, x_stride_elements, true, "tf_shared_expert_int4_tensorcore(gate/up)")) return s;
+    const uint8_t* w_gu[2] = {W[0], W[1]};
+    if (tf_status s = tf::launch_qmm<2, true>(ctx, stream, a, x, rows, x_stride_elements, w_gu, 1, 0, true,
+                                               "tf_shared_expert_int4_tensorcore(gate/up)")) return s;
     tf::QmmArgs b{};
-    b.dense_W[0] = W[2]; b.dense_S[0] = S[2]; b.dense_B[0] = B[2];
+    b.dense_S[0] = S[2]; b.dense_B[0] = B[2];
     b.dense_tokens = rows; b.rows = d; b.k = fs; b.out = static_cast<uint16_t*>(y); b.out_stride = y_stride_elements;
-    return tf::launch_qmm<1, true>(ctx, stream, b, scratch_act, rows, fs, true, "tf_shared_expert_int4_tensorcore(down)");
+    const uint8_t* w_dn[2] = {W[2], W[2]};
+    return tf::launch_qmm<1, true>(ctx, stream, b, scratch_act, rows, fs, w_dn, 1, 0, true, "tf_shared_expert_int4_tensorcore(down)");
 }
 
 }  // extern "C"

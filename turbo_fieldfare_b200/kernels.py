@@ -381,12 +381,13 @@ class PrefillGroupedRoutedMoE:
             C.byref(routes.c_struct), query_count, top_k, num_experts, d, _ptr(x_sorted), _ptr(row_expert_ids),
             _ptr(inverse_perm)))
 
-    def encode_tensorcore(self, x_sorted, x_rows: int, pool_layer_base, expert_stride: int, offsets: ExpertOffsets,
-                          routes: DeviceRoutes, acts_scratch, out_rows, d: int, f: int, *, stream=None):
+    def encode_tensorcore(self, x_sorted, x_rows: int, pool_layer_base, expert_stride: int, num_experts: int,
+                          offsets: ExpertOffsets, routes: DeviceRoutes, acts_scratch, out_rows, d: int, f: int, *,
+                          stream=None):
         """Same operator on the tcgen05 tensor cores over expert-sorted rows (``tf_grouped_moe_tensorcore``)."""
         ctx = self.context
         ctx.check(ctx.lib.tf_grouped_moe_tensorcore(
-            ctx.handle, _stream(stream), _ptr(x_sorted), x_rows, _ptr(pool_layer_base), expert_stride,
+            ctx.handle, _stream(stream), _ptr(x_sorted), x_rows, _ptr(pool_layer_base), expert_stride, num_experts,
             C.byref(offsets), C.byref(routes.c_struct), _ptr(acts_scratch), _ptr(out_rows), d, f))
 
 
