@@ -128,6 +128,11 @@ int tf_abi_version(void);
 /* Number of kernels this context has enqueued since creation (for callers that
  * need to show that work ran on the GPU). */
 uint64_t tf_launch_count(tf_context* ctx);
+/* Block forwards (tf_moe_block_forward, tf_stack_forward) of at least `tokens` tokens run their expert
+ * GEMMs on the tcgen05 tensor cores, smaller ones on the CUDA-core streaming kernels. Default 256. Set it
+ * before creating the workspaces that should be able to take the tensor-core path. The reference picks its
+ * prefill kernels by chunk size in the same way (RealForwardRunner.swift:902-1186). */
+tf_status tf_context_set_tensorcore_min_tokens(tf_context* ctx, uint32_t tokens);
 /* Synchronises the device and reports whether any kernel abandoned one of its bounded waits
  * (mbarrier / flag polls never spin for ever: on expiry the kernel records a code and returns).
  * Replaces the command-buffer error check (Infrastructure/Metal/MetalContext.swift:22-26).

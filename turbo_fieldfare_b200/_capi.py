@@ -85,6 +85,7 @@ SIGNATURES = {
     "tf_moe_reduce_token_major": (C.c_int, [vp, vp, vp, C.c_int, vp, vp, u32, vp, u32, u32, u32, u32]),
     "tf_shared_expert_int4_block": (C.c_int, [vp, vp, vp, u64, u32, C.POINTER(Projection), C.POINTER(Projection),
                                               C.POINTER(Projection), vp, u64, u32, vp, u32]),
+    "tf_context_set_tensorcore_min_tokens": (C.c_int, [vp, u32]),
     "tf_int4_qmm": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, vp, u64, vp, u64, u32, u32, u32]),
     "tf_pack_sorted_rows": (C.c_int, [vp, vp, vp, u32, C.POINTER(DeviceRoutes), u32, u32, u32, u32, vp, vp, vp]),
     "tf_grouped_moe_tensorcore": (C.c_int, [vp, vp, vp, u32, vp, u64, u32, C.POINTER(ExpertOffsets),

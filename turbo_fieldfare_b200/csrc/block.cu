@@ -50,10 +50,6 @@ struct tf_stack {
 namespace tf {
 
 constexpr uint32_t kF32PartialTokens = 64;   // decode-sized batches keep fp32 partials (decode kernel semantics)
-// From this many tokens a block forward runs the expert GEMMs on the tensor cores (128-token tiles per expert:
-// 256 tokens x top-8 over 128 experts is 16 pairs per expert on average, where a 128-wide tile already beats
-// eight-token CUDA-core chunks because the weight tile is dequantised once instead of twice).
-constexpr uint32_t kTensorCoreTokens = 256;
 
 __device__ __forceinline__ uint64_t mix64(uint64_t z) {
     z += 0x9E3779B97F4A7C15ull;
@@ -266,7 +262,8 @@ tf_status tf_workspace_create(tf_context* ctx, uint32_t max_tokens, uint32_t d, 
                    o_cstart = take(E * 4), o_counters = take(16), o_acts = take(T * K * f * 2),
                    o_partials = take(T * K * d * (T <= tf::kF32PartialTokens ? 4 : 2)), o_sact = take(T * fs * 2),
                    o_sy = take(T * d * 2), o_xn = take(T * d * 2), o_yb = take(T * d * 2);
-    const bool tensor_path = T >= tf::kTensorCoreTokens && d % 64 == 0 && f % 64 == 0 && fs % 64 == 0;
+    // workspaces that can hold a tensor-core sized block also carry the expert-sorted activation rows
+    const bool tensor_path = T >= ctx->tensorcore_min_tokens && d % 64 == 0 && f % 64 == 0 && fs % 64 == 0;
     const uint64_t o_xs = tensor_path ? take(T * K * d * 2) : 0, o_inv = tensor_path ? take(T * K * 4) : 0,
                    o_pid = tensor_path ? take(T * K * 4) : 0;
     uint8_t* base = nullptr;
@@ -341,7 +338,7 @@ tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer
     if (s) return s;
     s = tf_group_routes_device(ctx, stream, ws->indices, ws->weights, tokens, K, E, &ws->routes);
     if (s) return s;
-    if (tokens >= tf::kTensorCoreTokens && ws->x_sorted != nullptr) {
+    if (tokens >= ctx->tensorcore_min_tokens && ws->x_sorted != nullptr) {
         // Prefill-sized block: gather the rows into expert order, run gate/up/GeGLU/down and the shared expert as
         // tcgen05 GEMMs, then fold the sorted rows back per token in rank order.
         s = tf_pack_sorted_rows(ctx, stream, x, x_stride_elements, &ws->routes, tokens, K, E, d, ws->x_sorted, ws->pack_ids,

@@ -106,6 +106,12 @@ const char* tf_last_error(tf_context* ctx) {
 
 uint64_t tf_launch_count(tf_context* ctx) { return ctx ? ctx->launches : 0; }
 
+tf_status tf_context_set_tensorcore_min_tokens(tf_context* ctx, uint32_t tokens) {
+    TF_REQUIRE(ctx, ctx != nullptr && tokens > 0, TF_ERR_INVALID_ARGUMENT, "tf_context_set_tensorcore_min_tokens: ctx is NULL or tokens is 0");
+    ctx->tensorcore_min_tokens = tokens;
+    return TF_OK;
+}
+
 tf_status tf_device_status(tf_context* ctx, uint32_t* code_out) {
     TF_REQUIRE(ctx, ctx != nullptr && code_out != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_device_status: NULL argument");
     TF_CUDA(ctx, cudaDeviceSynchronize());

@@ -43,6 +43,8 @@ struct tf_context {
     // Group table and tile totals of the tensor-core grouped GEMM (filled on the device per launch).
     void* qmm_groups = nullptr;
     uint32_t* qmm_totals = nullptr;
+    // Block forwards of at least this many tokens run their expert GEMMs on the tcgen05 tensor cores.
+    uint32_t tensorcore_min_tokens = 256;
 };
 
 namespace tf {

@@ -67,6 +67,10 @@ class TurboContext:
         self.check(self.lib.tf_device_status(self.handle, C.byref(code)))
         return int(code.value)
 
+    def set_tensorcore_min_tokens(self, tokens: int) -> None:
+        """Blocks of at least ``tokens`` tokens run their expert GEMMs on the tensor cores (default 256)."""
+        self.check(self.lib.tf_context_set_tensorcore_min_tokens(self.handle, tokens))
+
     @property
     def launch_count(self) -> int:
         return int(self.lib.tf_launch_count(self.handle))

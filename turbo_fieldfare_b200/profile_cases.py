@@ -20,6 +20,8 @@ from .stack import AffineTensor, MoEStack
 
 def case_block(args) -> None:
     ctx = TurboContext(0)
+    if args.tensor_min > 0:
+        ctx.set_tensorcore_min_tokens(args.tensor_min)
     stack = MoEStack(ctx, layers=args.layers, seed=3)
     ws = stack.workspace(args.tokens)
     h = torch.randn(args.tokens, 2816, device="cuda").half()
@@ -27,6 +29,8 @@ def case_block(args) -> None:
         import numpy as np
         p = 1.0 / (np.random.default_rng(0).permutation(128) + 1) ** args.zipf
         stack.set_logit_bias(np.log(p / p.sum()).astype(np.float32))
+    for _ in range(args.warm):
+        stack.forward(h, args.tokens, ws)
     times = []
     for _ in range(args.iters):
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -90,6 +94,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--cols", type=int, default=2816)
     ap.add_argument("--warm", type=int, default=0, help="untimed launches before the timed ones")
+    ap.add_argument("--tensor-min", type=int, default=0, help="block case: smallest token count that takes the tensor-core path")
     ap.add_argument("--zipf", type=float, default=0.0, help="router logit bias log(p), p ~ 1/rank^zipf (0 = none)")
     args = ap.parse_args()
     {"block": case_block, "gemv": case_gemv, "qmm": case_qmm}[args.case](args)
