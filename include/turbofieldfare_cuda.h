@@ -294,6 +294,34 @@ tf_status tf_shared_expert_int4_block(tf_context* ctx, void* stream,
                                       void* y, uint64_t y_off, uint32_t y_stride_elements,
                                       void* scratch_act, uint32_t rows);
 
+/* The shared expert block for callers that cannot allocate device memory. It has no counterpart in the
+ * reference. Who needs it: a serving process that hands all of the GPU's memory to its own pool at start-up and
+ * never calls cudaMalloc again (a later cudaMalloc would fail, or stall the device while the driver maps
+ * memory); a plugin loaded into such a process; code that runs while another thread captures a CUDA graph,
+ * where an allocation is an error. Everything else in this header needs a tf_context, a workspace or a
+ * caller-provided scratch buffer, and each of those is a device allocation by somebody.
+ * This call takes no context and no scratch: x, the three projections and y are the caller's buffers, and the
+ * fp16 activations between the gate/up kernel and the down kernel go to an array that is part of the library
+ * image (1 MiB per GPU that loads the library, held until the process exits). It calls no cudaMalloc, cudaFree
+ * or other allocating routine.
+ *   - Limit: rows * gate->rows * 2 bytes <= 1 MiB (248 rows at the Gemma-4 shared width 2112); a larger block
+ *     returns TF_ERR_SCRATCH_TOO_SMALL and the message names tf_shared_expert_int4_block as the way out.
+ *   - The first call on a device looks up the array's device address and the SM count and sets the kernels'
+ *     shared-memory attribute; make that first call with the device current and before any stream capture.
+ *   - All calls on a device share the one array, which still holds the previous call's activations. Nothing in
+ *     it has to start at zero; the status word is cleared by every call. Two calls that overlap on the GPU
+ *     (different streams, or graphs replayed concurrently) race on the array and corrupt each other.
+ *   - device_status: optional DEVICE word owned by the caller; it is cleared, and a kernel that gives up a
+ *     bounded wait writes its code there. NULL uses a word inside the library that cannot be read back.
+ *   - Errors: the status is returned and tf_last_error(NULL) holds the text. Arithmetic, alignment rules and
+ *     arguments otherwise as tf_shared_expert_int4_block. */
+tf_status tf_shared_expert_int4_block_noalloc(void* stream,
+                                              const void* x, uint64_t x_off, uint32_t x_stride_elements,
+                                              const tf_projection* gate, const tf_projection* up,
+                                              const tf_projection* down,
+                                              void* y, uint64_t y_off, uint32_t y_stride_elements, uint32_t rows,
+                                              uint32_t* device_status);
+
 /* ---- tensor-core (tcgen05 / TMEM) kernels for prefill-sized batches ---- */
 /* Y[M,N] = X[M,K] . dequant(W[N,K])^T, fp16 in/out, fp32 accumulation; the weight tile is staged as
  * half(q*s+b) and multiplied on the matrix unit. Replaces MPPPrefillInt4QMM.encode

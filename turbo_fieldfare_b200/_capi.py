@@ -92,6 +92,8 @@ SIGNATURES = {
                                             C.POINTER(DeviceRoutes), vp, vp, u32, u32]),
     "tf_shared_expert_int4_tensorcore": (C.c_int, [vp, vp, vp, u32, C.POINTER(Projection), C.POINTER(Projection),
                                                    C.POINTER(Projection), vp, u32, vp, u32]),
+    "tf_shared_expert_int4_block_noalloc": (C.c_int, [vp, vp, u64, u32, C.POINTER(Projection), C.POINTER(Projection),
+                                                      C.POINTER(Projection), vp, u64, u32, u32, vp]),
     "tf_expert_pool_create": (C.c_int, [vp, u32, u32, u64, C.POINTER(ExpertOffsets), C.POINTER(vp)]),
     "tf_expert_pool_destroy": (None, [vp]),
     "tf_expert_pool_ptr": (vp, [vp, u32, u32]),

@@ -733,6 +733,51 @@ static tf_status check_blob_alignment(tf_context* ctx, const void* pool, uint64_
     return TF_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Scratch that lives in the library image, for tf_shared_expert_int4_block_noalloc
+// ---------------------------------------------------------------------------
+// Every GPU that loads this library carries these arrays from load until the process exits.
+constexpr size_t kNoAllocScratchBytes = 1u << 20;          // 1 MiB of fp16 activations: rows * gate.rows * 2 bytes
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+static __device__ __align__(256) uint32_t g_noalloc_error_word[1];
+
+// In host code the two names above are stand-ins, not device addresses; the addresses a kernel can use come
+// from cudaGetSymbolAddress, asked once per device with that device current.
+struct NoAllocDevice {
+    bool ready = false;
+    void* scratch = nullptr;
+    uint32_t* error_word = nullptr;
+    int sm_count = 0;
+};
+constexpr int kNoAllocMaxDevices = 64;
+static NoAllocDevice g_noalloc_devices[kNoAllocMaxDevices];
+static std::mutex g_noalloc_mutex;
+
+static tf_status noalloc_device(NoAllocDevice** out, const char* name) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(nullptr, TF_ERR_NO_DEVICE, "%s: cudaGetDevice: %s", name, cudaGetErrorString(e));
+    if (dev < 0 || dev >= kNoAllocMaxDevices) return fail(nullptr, TF_ERR_UNSUPPORTED, "%s: device ordinal %d is out of range", name, dev);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    NoAllocDevice& d = g_noalloc_devices[dev];
+    if (!d.ready) {
+        int major = 0;
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e == cudaSuccess) e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess) return fail(nullptr, TF_ERR_CUDA, "%s: cudaDeviceGetAttribute: %s", name, cudaGetErrorString(e));
+        if (major != 10) return fail(nullptr, TF_ERR_UNSUPPORTED, "%s: device %d is not sm_100; this library is built for sm_100a only", name, dev);
+        e = cudaGetSymbolAddress(&d.scratch, g_noalloc_scratch);
+        if (e != cudaSuccess) return fail(nullptr, TF_ERR_CUDA, "%s: cudaGetSymbolAddress(scratch): %s", name, cudaGetErrorString(e));
+        void* w = nullptr;
+        e = cudaGetSymbolAddress(&w, g_noalloc_error_word);
+        if (e != cudaSuccess) return fail(nullptr, TF_ERR_CUDA, "%s: cudaGetSymbolAddress(error word): %s", name, cudaGetErrorString(e));
+        d.error_word = static_cast<uint32_t*>(w);
+        d.ready = true;
+    }
+    *out = &d;
+    return TF_OK;
+}
+
 }  // namespace tf
 
 extern "C" {
@@ -855,6 +900,35 @@ tf_status tf_shared_expert_int4_block(tf_context* ctx, void* stream, const void*
     b.x = static_cast<const uint16_t*>(scratch_act); b.x_stride = fs;
     b.out = tf::byte_ptr(y, y_off); b.out_stride = y_stride_elements; b.rows = d; b.k = fs; b.dense_tokens = rows;
     return tf::launch_grouped<1, true, tf::kOutDenseF16>(ctx, stream, b, "tf_shared_expert_int4_block(down)");
+}
+
+// The shared expert for callers that must not allocate. Same kernels as tf_shared_expert_int4_block; the
+// activation scratch between the gate/up kernel and the down kernel is the array built into the library.
+tf_status tf_shared_expert_int4_block_noalloc(void* stream, const void* x, uint64_t x_off, uint32_t x_stride_elements,
+                                              const tf_projection* gate, const tf_projection* up, const tf_projection* down,
+                                              void* y, uint64_t y_off, uint32_t y_stride_elements, uint32_t rows,
+                                              uint32_t* device_status) {
+    const char* name = "tf_shared_expert_int4_block_noalloc";
+    if (!gate || !up || !down) return tf::fail(nullptr, TF_ERR_INVALID_ARGUMENT, "%s: NULL projection", name);
+    const uint64_t need = (uint64_t)rows * gate->rows * 2;
+    if (need > tf::kNoAllocScratchBytes)
+        return tf::fail(nullptr, TF_ERR_SCRATCH_TOO_SMALL,
+                        "%s: %u rows x %u activations need %llu bytes of scratch; the built-in scratch holds %zu bytes "
+                        "(use tf_shared_expert_int4_block with your own scratch for larger blocks)",
+                        name, rows, gate->rows, (unsigned long long)need, tf::kNoAllocScratchBytes);
+    tf::NoAllocDevice* dev = nullptr;
+    if (tf_status s = tf::noalloc_device(&dev, name)) return s;      // first call on a device: the one-time set-up
+    // A context on the stack: nothing in it is allocated on the device, the launch code only reads these fields.
+    tf_context local;
+    cudaGetDevice(&local.device);
+    local.sm_count = dev->sm_count;
+    local.device_error = device_status ? device_status : dev->error_word;
+    // The scratch keeps what the previous call left. The activations need no clearing (the first kernel writes
+    // every element the second reads); the status word must start at zero.
+    cudaError_t e = cudaMemsetAsync(local.device_error, 0, sizeof(uint32_t), static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return tf::fail(nullptr, TF_ERR_CUDA, "%s: clearing the status word: %s", name, cudaGetErrorString(e));
+    return tf_shared_expert_int4_block(&local, stream, x, x_off, x_stride_elements, gate, up, down, y, y_off, y_stride_elements,
+                                       dev->scratch, rows);
 }
 
 }  // extern "C"
