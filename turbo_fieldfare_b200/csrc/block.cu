@@ -315,6 +315,43 @@ const tf_device_routes* tf_workspace_routes(const tf_workspace* ws) { return ws 
 // fused block and stack
 // ---------------------------------------------------------------------------
 
+}  // extern "C"
+
+namespace tf {
+
+// Router, device grouping and the routed experts of one block, on the caller's stream.
+static tf_status block_routed(tf_context* ctx, void* stream, const tf_moe_layer* layer, const void* x, uint32_t x_stride_elements,
+                              uint32_t tokens, tf_workspace* ws, bool tensor_path) {
+    const uint32_t d = layer->d, f = layer->f, K = layer->top_k, E = layer->num_experts;
+    tf_status s = tf_router_gemma4_block(ctx, stream, layer->router.weights, layer->router.weights_off,
+                                         layer->router.scales, layer->router.scales_off,
+                                         layer->router.biases, layer->router.biases_off,
+                                         x, 0, TF_FP16, layer->effective_scale, 0, layer->per_expert_scale, 0,
+                                         layer->logit_bias, ws->indices, 0, ws->weights, 0, nullptr,
+                                         tokens, E, d, K, x_stride_elements);
+    if (s) return s;
+    s = tf_group_routes_device(ctx, stream, ws->indices, ws->weights, tokens, K, E, &ws->routes);
+    if (s) return s;
+    if (tensor_path) {
+        // Prefill-sized block: gather the rows into expert order and run gate/up/GeGLU/down as tcgen05 GEMMs; the
+        // combine folds the sorted rows back per token in rank order.
+        s = tf_pack_sorted_rows(ctx, stream, x, x_stride_elements, &ws->routes, tokens, K, E, d, ws->x_sorted, ws->pack_ids,
+                                ws->inverse_perm);
+        if (s) return s;
+        return tf_grouped_moe_tensorcore(ctx, stream, ws->x_sorted, tokens * K, layer->pool_layer_base, layer->expert_stride, E,
+                                         &layer->offsets, &ws->routes, ws->acts, ws->partials, d, f);
+    }
+    // The partial dtype follows the workspace's capacity so that one workspace
+    // always runs the same arithmetic whatever the call's token count.
+    const int f32 = ws->max_tokens <= kF32PartialTokens ? 1 : 0;
+    return tf_grouped_moe_batched(ctx, stream, x, 0, x_stride_elements, layer->pool_layer_base, layer->expert_stride,
+                                  &layer->offsets, &ws->routes, ws->acts, ws->partials, f32, tokens, d, f, K);
+}
+
+}  // namespace tf
+
+extern "C" {
+
 tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer* layer,
                                const void* x, uint32_t x_stride_elements,
                                void* y, uint32_t y_stride_elements, uint32_t tokens, tf_workspace* ws) {
@@ -328,40 +365,30 @@ tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer
     TF_REQUIRE(ctx, layer->router.rows == layer->num_experts && layer->router.cols == layer->d, TF_ERR_DIMENSION_MISMATCH,
                "%s: router is (%u,%u), expected (%u,%u)", name, layer->router.rows, layer->router.cols, layer->num_experts, layer->d);
     if (tokens == 0) return TF_OK;
-    const uint32_t d = layer->d, f = layer->f, K = layer->top_k, E = layer->num_experts;
-    tf_status s = tf_router_gemma4_block(ctx, stream, layer->router.weights, layer->router.weights_off,
-                                         layer->router.scales, layer->router.scales_off,
-                                         layer->router.biases, layer->router.biases_off,
-                                         x, 0, TF_FP16, layer->effective_scale, 0, layer->per_expert_scale, 0,
-                                         layer->logit_bias, ws->indices, 0, ws->weights, 0, nullptr,
-                                         tokens, E, d, K, x_stride_elements);
-    if (s) return s;
-    s = tf_group_routes_device(ctx, stream, ws->indices, ws->weights, tokens, K, E, &ws->routes);
-    if (s) return s;
-    if (tokens >= ctx->tensorcore_min_tokens && ws->x_sorted != nullptr) {
-        // Prefill-sized block: gather the rows into expert order, run gate/up/GeGLU/down and the shared expert as
-        // tcgen05 GEMMs, then fold the sorted rows back per token in rank order.
-        s = tf_pack_sorted_rows(ctx, stream, x, x_stride_elements, &ws->routes, tokens, K, E, d, ws->x_sorted, ws->pack_ids,
-                                ws->inverse_perm);
-        if (s) return s;
-        s = tf_grouped_moe_tensorcore(ctx, stream, ws->x_sorted, tokens * K, layer->pool_layer_base, layer->expert_stride, E,
-                                      &layer->offsets, &ws->routes, ws->acts, ws->partials, d, f);
-        if (s) return s;
-        s = tf_shared_expert_int4_tensorcore(ctx, stream, x, x_stride_elements, &layer->shared_gate, &layer->shared_up,
+    const uint32_t d = layer->d, K = layer->top_k;
+    // The shared expert needs only x, so it runs on the context's side stream beside the router and the routed
+    // experts and joins before the combine (inside a stream capture this becomes a fork and a join of the graph).
+    cudaStream_t main_st = static_cast<cudaStream_t>(stream);
+    TF_CUDA(ctx, cudaEventRecord(ctx->fork_event, main_st));
+    TF_CUDA(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->fork_event, 0));
+    const bool tensor_path = tokens >= ctx->tensorcore_min_tokens && ws->x_sorted != nullptr;
+    tf_status s;
+    if (tensor_path)
+        s = tf_shared_expert_int4_tensorcore(ctx, ctx->side_stream, x, x_stride_elements, &layer->shared_gate, &layer->shared_up,
                                              &layer->shared_down, ws->shared_y, d, ws->shared_act, tokens);
-        if (s) return s;
+    else
+        s = tf_shared_expert_int4_block(ctx, ctx->side_stream, x, 0, x_stride_elements, &layer->shared_gate, &layer->shared_up,
+                                        &layer->shared_down, ws->shared_y, 0, d, ws->shared_act, tokens);
+    // the join is recorded even after a failure so that a capture in progress stays well formed
+    cudaEventRecord(ctx->join_event, ctx->side_stream);
+    if (s) { cudaStreamWaitEvent(main_st, ctx->join_event, 0); return s; }
+    s = tf::block_routed(ctx, stream, layer, x, x_stride_elements, tokens, ws, tensor_path);
+    TF_CUDA(ctx, cudaStreamWaitEvent(main_st, ctx->join_event, 0));
+    if (s) return s;
+    if (tensor_path)
         return tf_ep_combine(ctx, stream, ws->partials, ws->weights, ws->inverse_perm, ws->shared_y, d, y, y_stride_elements,
                              tokens, K, d);
-    }
-    // The partial dtype follows the workspace's capacity so that one workspace
-    // always runs the same arithmetic whatever the call's token count.
     const int f32 = ws->max_tokens <= tf::kF32PartialTokens ? 1 : 0;
-    s = tf_grouped_moe_batched(ctx, stream, x, 0, x_stride_elements, layer->pool_layer_base, layer->expert_stride,
-                               &layer->offsets, &ws->routes, ws->acts, ws->partials, f32, tokens, d, f, K);
-    if (s) return s;
-    s = tf_shared_expert_int4_block(ctx, stream, x, 0, x_stride_elements, &layer->shared_gate, &layer->shared_up,
-                                    &layer->shared_down, ws->shared_y, 0, d, ws->shared_act, tokens);
-    if (s) return s;
     return tf_moe_reduce_token_major(ctx, stream, ws->partials, f32, ws->weights, ws->shared_y, d, y,
                                      y_stride_elements, tokens, K, d);
 }

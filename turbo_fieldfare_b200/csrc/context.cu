@@ -77,8 +77,11 @@ tf_status tf_context_create(int device, tf_context** out) {
     if (e == cudaSuccess) e = cudaMemset(ctx->router_tickets, 0, sizeof(unsigned int) * tf::kRouterSplitRows);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->device_error, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->device_error, 0, sizeof(uint32_t));
-    if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_groups, 64 * (TF_MAX_ROUTER_EXPERTS + 1));
-    if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_totals, 2 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_groups, 2 * 64 * (TF_MAX_ROUTER_EXPERTS + 1));   // routed and dense tables
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_totals, 4 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->fork_event, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->join_event, cudaEventDisableTiming);
     if (e != cudaSuccess) {
         tf_status s = tf::fail(nullptr, TF_ERR_OUT_OF_MEMORY, "context scratch: %s", cudaGetErrorString(e));
         tf_context_destroy(ctx);
@@ -96,6 +99,9 @@ void tf_context_destroy(tf_context* ctx) {
     if (ctx->device_error) cudaFree(ctx->device_error);
     if (ctx->qmm_groups) cudaFree(ctx->qmm_groups);
     if (ctx->qmm_totals) cudaFree(ctx->qmm_totals);
+    if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
+    if (ctx->fork_event) cudaEventDestroy(ctx->fork_event);
+    if (ctx->join_event) cudaEventDestroy(ctx->join_event);
     delete ctx;
 }
 

@@ -682,8 +682,8 @@ static tf_status launch_qmm(tf_context* ctx, void* stream, QmmArgs& a, const voi
     if (tf_status s = make_x_map(ctx, &xmap, x, x_rows, a.k, x_stride, name)) return s;
     for (int m = 0; m < 2; ++m)
         if (tf_status s = make_w_map(ctx, &wmap[m], W[m < NMAT ? m : 0], a.rows, a.k, experts, dense ? (uint64_t)a.rows * (a.k / 2) : expert_stride, name)) return s;
-    a.groups = static_cast<QmmGroup*>(ctx->qmm_groups);
-    a.totals = ctx->qmm_totals;
+    a.groups = static_cast<QmmGroup*>(ctx->qmm_groups) + (dense ? TF_MAX_ROUTER_EXPERTS + 1 : 0);
+    a.totals = ctx->qmm_totals + (dense ? 2 : 0);
     a.error = ctx->device_error;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     qmm_prepare_kernel<<<1, 32, 0, st>>>(a, NMAT, dense ? 1 : 0);

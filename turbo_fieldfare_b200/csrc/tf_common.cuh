@@ -40,9 +40,13 @@ struct tf_context {
     unsigned int* router_tickets = nullptr;  // [kRouterSplitRows], self-resetting
     // One device word that kernels with bounded waits set when a wait gives up (0 = healthy).
     uint32_t* device_error = nullptr;
-    // Group table and tile totals of the tensor-core grouped GEMM (filled on the device per launch).
+    // Group tables and tile totals of the tensor-core grouped GEMM (filled on the device per launch): one set for
+    // routed launches and one for dense launches, which may run on two streams at once.
     void* qmm_groups = nullptr;
     uint32_t* qmm_totals = nullptr;
+    // Side stream and fork/join events: the shared expert of a block runs beside its router and routed experts.
+    cudaStream_t side_stream = nullptr;
+    cudaEvent_t fork_event = nullptr, join_event = nullptr;
     // Block forwards of at least this many tokens run their expert GEMMs on the tcgen05 tensor cores.
     uint32_t tensorcore_min_tokens = 256;
 };
