@@ -183,10 +183,11 @@ struct GroupedArgs {
 
 // D = A * B + C with C either the constant zero (first MMA of a group) or D itself.
 // A = codes of weight rows g (a0, a2) and g + 8 (a1, a3); B = activations of token g.
-__device__ __forceinline__ void mma16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, const uint2& b) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+__device__ __forceinline__ void mma16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, const uint2& b,
+                                               const float (&z)[4]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                  : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y), "f"(0.0f));
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y), "f"(z[0]), "f"(z[1]), "f"(z[2]), "f"(z[3]));
 }
 __device__ __forceinline__ void mma16816_acc(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, const uint2& b) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -316,15 +317,17 @@ __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v 
 __device__ __forceinline__ float bf16_lo_x2p24(uint32_t v) { return __uint_as_float((v << 16) + 0x0C000000u); }
 __device__ __forceinline__ float bf16_hi_x2p24(uint32_t v) { return __uint_as_float((v & 0xFFFF0000u) + 0x0C000000u); }
 
-template <int NMAT, bool DENSE, int OUT_MODE>
-__global__ void __launch_bounds__((kMaxComputeWarps + kExtraWarps) * kWarp)
+// KC > 0 fixes the column count at compile time (the production shapes), so that the shared-memory layout, the
+// warp count and every loop bound fold into constants; KC = 0 reads them from the arguments.
+template <int NMAT, bool DENSE, int OUT_MODE, int KC>
+__global__ void __launch_bounds__((KC ? (KC / kGroup + kGPW - 1) / kGPW : kMaxComputeWarps) * kWarp + kExtraWarps * kWarp)
 grouped_ksplit_kernel(const GroupedArgs args) {
     extern __shared__ __align__(16) uint8_t smem[];
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t cw = blockDim.x / kWarp - kExtraWarps;  // compute warps; then kReducers reducer warps; the last warp loads
-    const uint32_t ng = args.k / kGroup;
-    const uint32_t row_bytes = args.k / 2;
+    const uint32_t ng = KC ? (uint32_t)(KC / kGroup) : args.k / kGroup;
+    const uint32_t cw = KC ? (ng + kGPW - 1) / kGPW : blockDim.x / kWarp - kExtraWarps;  // compute warps; then the reducers; the last warp loads
+    const uint32_t row_bytes = KC ? (uint32_t)(KC / 2) : args.k / 2;
     const KSplitSmem<NMAT> lay{cw, ng, row_bytes};
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t red_base = smem_base + lay.off_red();
@@ -377,6 +380,11 @@ grouped_ksplit_kernel(const GroupedArgs args) {
         cur.tile = item_begin % tiles;
         resolve_chunk<NMAT, DENSE>(args, cur);
 
+        // Four registers that stay zero: the accumulator input of every group's first MMA (a literal zero makes the
+        // compiler clear four fresh registers per MMA).
+        float zc[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) asm volatile("mov.f32 %0, 0f00000000;" : "=f"(zc[j]));
         uint2 xb[kGPW][4];          // B fragments of token g: [group][MMA j] = {b0, b1}
         float2 xsum[kGPW];          // fp32 sums of the 64 activations of the group for tokens 2t and 2t + 1
         uint32_t loaded_chunk = 0xFFFFFFFFu;
@@ -444,7 +452,7 @@ grouped_ksplit_kernel(const GroupedArgs args) {
 #pragma unroll
                 for (int i = 0; i < kGPW; ++i)
                     mma16816_first(c[m][i], wa[m][i].x & 0x000F000Fu, wb[m][i].x & 0x000F000Fu,
-                                   (wa[m][i].x >> 8) & 0x000F000Fu, (wb[m][i].x >> 8) & 0x000F000Fu, xb[i][0]);
+                                   (wa[m][i].x >> 8) & 0x000F000Fu, (wb[m][i].x >> 8) & 0x000F000Fu, xb[i][0], zc);
             }
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
@@ -690,17 +698,14 @@ __global__ void reduce_token_major_kernel(const void* __restrict__ partials, con
     out[(size_t)t * out_stride + d] = __half_as_ushort(__float2half_rn(acc));
 }
 
-template <int NMAT, bool DENSE, int OUT_MODE>
-static tf_status launch_grouped(tf_context* ctx, void* stream, GroupedArgs& args, const char* name) {
+template <int NMAT, bool DENSE, int OUT_MODE, int KC>
+static tf_status launch_grouped_k(tf_context* ctx, void* stream, GroupedArgs& args, const char* name) {
     const uint32_t ng = args.k / kGroup;
-    TF_REQUIRE(ctx, ng >= 1 && args.k % kGroup == 0, TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);
     const uint32_t cw = (ng + kGPW - 1) / kGPW;
-    TF_REQUIRE(ctx, cw <= (uint32_t)kMaxComputeWarps, TF_ERR_UNSUPPORTED, "%s: K=%u outside the supported range (64..3072)", name, args.k);
-    TF_REQUIRE(ctx, args.rows % kTileRows == 0, TF_ERR_UNSUPPORTED, "%s: row count %u must be a multiple of 16", name, args.rows);
     const KSplitSmem<NMAT> lay{cw, ng, args.k / 2};
     const size_t smem = lay.total();
     TF_REQUIRE(ctx, smem <= 200 * 1024, TF_ERR_UNSUPPORTED, "%s: K=%u needs %zu bytes of shared memory (limit 200 KB)", name, args.k, smem);
-    auto kern = grouped_ksplit_kernel<NMAT, DENSE, OUT_MODE>;
+    auto kern = grouped_ksplit_kernel<NMAT, DENSE, OUT_MODE, KC>;
     // Attribute and occupancy are queried once per (instantiation, warp count) and cached, so
     // steady-state calls are a bare launch (and safe inside stream capture).
     static int cached_per_sm[kMaxComputeWarps + 1] = {0};
@@ -721,6 +726,19 @@ static tf_status launch_grouped(tf_context* ctx, void* stream, GroupedArgs& args
     }
     kern<<<grid, (cw + kExtraWarps) * kWarp, smem, static_cast<cudaStream_t>(stream)>>>(args);
     return check_launch(ctx, name);
+}
+
+// KSPEC: the column count this instantiation is specialised for (the Gemma-4 shape of its role); other
+// column counts take the generic kernel.
+template <int NMAT, bool DENSE, int OUT_MODE, int KSPEC>
+static tf_status launch_grouped(tf_context* ctx, void* stream, GroupedArgs& args, const char* name) {
+    const uint32_t ng = args.k / kGroup;
+    TF_REQUIRE(ctx, ng >= 1 && args.k % kGroup == 0, TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);
+    const uint32_t cw = (ng + kGPW - 1) / kGPW;
+    TF_REQUIRE(ctx, cw <= (uint32_t)kMaxComputeWarps, TF_ERR_UNSUPPORTED, "%s: K=%u outside the supported range (64..3072)", name, args.k);
+    TF_REQUIRE(ctx, args.rows % kTileRows == 0, TF_ERR_UNSUPPORTED, "%s: row count %u must be a multiple of 16", name, args.rows);
+    if (args.k == (uint32_t)KSPEC) return launch_grouped_k<NMAT, DENSE, OUT_MODE, KSPEC>(ctx, stream, args, name);
+    return launch_grouped_k<NMAT, DENSE, OUT_MODE, 0>(ctx, stream, args, name);
 }
 
 static tf_status check_blob_alignment(tf_context* ctx, const void* pool, uint64_t stride, const tf_expert_offsets* o, const char* name) {
@@ -827,7 +845,7 @@ tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream, const void* hidd
     a.chunk_start = routes->chunk_start; a.counters = routes->counters;
     a.x = reinterpret_cast<const uint16_t*>(hp); a.x_stride = hidden_stride_elements;
     a.out = acts_scratch; a.out_stride = f; a.rows = f; a.k = d; a.top_k = top_k;
-    tf_status s = tf::launch_grouped<2, false, tf::kOutActs>(ctx, stream, a, "tf_grouped_moe_batched(gate/up)");
+    tf_status s = tf::launch_grouped<2, false, tf::kOutActs, 2816>(ctx, stream, a, "tf_grouped_moe_batched(gate/up)");
     if (s) return s;
 
     tf::GroupedArgs b{};
@@ -837,8 +855,8 @@ tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream, const void* hidd
     b.chunk_start = routes->chunk_start; b.counters = routes->counters;
     b.x = static_cast<const uint16_t*>(acts_scratch); b.x_stride = f;
     b.out = route_partials; b.out_stride = d; b.rows = d; b.k = f; b.top_k = top_k;
-    if (partials_f32) return tf::launch_grouped<1, false, tf::kOutPartialF32>(ctx, stream, b, "tf_grouped_moe_batched(down)");
-    return tf::launch_grouped<1, false, tf::kOutPartialF16>(ctx, stream, b, "tf_grouped_moe_batched(down)");
+    if (partials_f32) return tf::launch_grouped<1, false, tf::kOutPartialF32, 704>(ctx, stream, b, "tf_grouped_moe_batched(down)");
+    return tf::launch_grouped<1, false, tf::kOutPartialF16, 704>(ctx, stream, b, "tf_grouped_moe_batched(down)");
 }
 
 tf_status tf_moe_reduce_token_major(tf_context* ctx, void* stream, const void* route_partials, int partials_f32,
@@ -893,13 +911,13 @@ tf_status tf_shared_expert_int4_block(tf_context* ctx, void* stream, const void*
     a.dense[0] = mp[0]; a.dense[1] = mp[1];
     a.x = reinterpret_cast<const uint16_t*>(xp); a.x_stride = x_stride_elements;
     a.out = scratch_act; a.out_stride = fs; a.rows = fs; a.k = d; a.dense_tokens = rows;
-    tf_status s = tf::launch_grouped<2, true, tf::kOutActs>(ctx, stream, a, "tf_shared_expert_int4_block(gate/up)");
+    tf_status s = tf::launch_grouped<2, true, tf::kOutActs, 2816>(ctx, stream, a, "tf_shared_expert_int4_block(gate/up)");
     if (s) return s;
     tf::GroupedArgs b{};
     b.dense[0] = mp[2];
     b.x = static_cast<const uint16_t*>(scratch_act); b.x_stride = fs;
     b.out = tf::byte_ptr(y, y_off); b.out_stride = y_stride_elements; b.rows = d; b.k = fs; b.dense_tokens = rows;
-    return tf::launch_grouped<1, true, tf::kOutDenseF16>(ctx, stream, b, "tf_shared_expert_int4_block(down)");
+    return tf::launch_grouped<1, true, tf::kOutDenseF16, 2112>(ctx, stream, b, "tf_shared_expert_int4_block(down)");
 }
 
 // The shared expert for callers that must not allocate. Same kernels as tf_shared_expert_int4_block; the
