@@ -18,7 +18,7 @@
 // bytes, and writing it to shared memory and reading it back for the MMA would cost more shared-memory
 // bandwidth than the whole HBM stream.
 // Roles of the 24 warps: warp 0 issues every asynchronous copy (packed codes per step, activation boxes of 16
-// rows per step, the tile's scale and bias planes as 1-D bulk copies); warp 1 issues the MMAs and commits
+// or 128 rows per step, the tile's scale and bias planes as 1-D bulk copies); warp 1 issues the MMAs and commits
 // stages back through mbarriers; warps 4-19 dequantise (four threads per weight row); warps 20-23 read the
 // accumulators with tcgen05.ld and apply GeGLU (gate and up accumulate side by side) or a plain fp16 store,
 // masked to the group's real tokens. Accumulators of tiles with at most 64 tokens (one matrix: any tile)
@@ -293,7 +293,8 @@ struct AccPlan {
 
 template <int NMAT, bool NATURAL_K>
 __global__ void __launch_bounds__(kQmmThreads, 1)
-qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map0,
+qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap x_map_big,
+                   const __grid_constant__ CUtensorMap w_map0,
                    const __grid_constant__ CUtensorMap w_map1, const QmmArgs args) {
     extern __shared__ uint8_t smem_raw[];
     using L = QmmSmem<NMAT>;
@@ -430,11 +431,18 @@ qmm_tcgen05_kernel(const __grid_constant__ CUtensorMap x_map, const __grid_const
                 }
                 if (ub > 0 && !q_mbar_wait(bar_empty_b(sb), (ub - 1) & 1)) { fail = kErrQmmTimeout | 7; break; }
                 if (leader) {
-                    q_mbar_expect_tx(bar_full_b(sb), 2 * boxes * kQmmBoxRows * 128);
-                    for (uint32_t h = 0; h < 2; ++h)              // columns past K (odd group count) read as zero
-                        for (uint32_t b = 0; b < boxes; ++b)
-                            tma_load_2d(base + L::kOffB + sb * 2 * b_half_bytes + h * b_half_bytes + b * kQmmBoxRows * 128, &x_map,
-                                        (int)(ks * kQmmK + h * 64), (int)(row0 + b * kQmmBoxRows), bar_full_b(sb));
+                    if (boxes > 4) {                              // more than 64 tokens: one 128-row box per half
+                        q_mbar_expect_tx(bar_full_b(sb), 2 * kQmmTokMax * 128);
+                        for (uint32_t h = 0; h < 2; ++h)
+                            tma_load_2d(base + L::kOffB + sb * 2 * b_half_bytes + h * b_half_bytes, &x_map_big,
+                                        (int)(ks * kQmmK + h * 64), (int)row0, bar_full_b(sb));
+                    } else {
+                        q_mbar_expect_tx(bar_full_b(sb), 2 * boxes * kQmmBoxRows * 128);
+                        for (uint32_t h = 0; h < 2; ++h)          // columns past K (odd group count) read as zero
+                            for (uint32_t b = 0; b < boxes; ++b)
+                                tma_load_2d(base + L::kOffB + sb * 2 * b_half_bytes + h * b_half_bytes + b * kQmmBoxRows * 128, &x_map,
+                                            (int)(ks * kQmmK + h * 64), (int)(row0 + b * kQmmBoxRows), bar_full_b(sb));
+                    }
                 }
                 __syncwarp();
                 if (++sb == b_stages) { sb = 0; ++ub; }
@@ -634,14 +642,14 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// fp16 matrix [rows, k] with a row stride: box = 64 columns x 16 rows, 128-byte swizzle, zero fill outside.
+// fp16 matrix [rows, k] with a row stride: box = 64 columns x box_rows rows, 128-byte swizzle, zero fill outside.
 static tf_status make_x_map(tf_context* ctx, CUtensorMap* map, const void* x, uint64_t rows, uint32_t k, uint32_t stride_elems,
-                            const char* name) {
+                            uint32_t box_rows, const char* name) {
     EncodeTiledFn fn = encode_tiled_fn();
     TF_REQUIRE(ctx, fn != nullptr, TF_ERR_UNSUPPORTED, "%s: cuTensorMapEncodeTiled is not available in this driver", name);
     const cuuint64_t dims[2] = {k, rows};
     const cuuint64_t strides[1] = {(cuuint64_t)stride_elems * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)kQmmBoxRows};
+    const cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -678,8 +686,9 @@ static tf_status launch_qmm(tf_context* ctx, void* stream, QmmArgs& a, const voi
     TF_REQUIRE(ctx, ctx->qmm_groups != nullptr, TF_ERR_OUT_OF_MEMORY, "%s: context scratch missing", name);
     const uint32_t smem = QmmSmem<NMAT>::total(a.k);
     TF_REQUIRE(ctx, smem <= 227u * 1024u, TF_ERR_UNSUPPORTED, "%s: K=%u needs %u bytes of shared memory for the scale planes", name, a.k, smem);
-    CUtensorMap xmap, wmap[2];
-    if (tf_status s = make_x_map(ctx, &xmap, x, x_rows, a.k, x_stride, name)) return s;
+    CUtensorMap xmap, xmap_big, wmap[2];
+    if (tf_status s = make_x_map(ctx, &xmap, x, x_rows, a.k, x_stride, kQmmBoxRows, name)) return s;
+    if (tf_status s = make_x_map(ctx, &xmap_big, x, x_rows, a.k, x_stride, kQmmTokMax, name)) return s;
     for (int m = 0; m < 2; ++m)
         if (tf_status s = make_w_map(ctx, &wmap[m], W[m < NMAT ? m : 0], a.rows, a.k, experts, dense ? (uint64_t)a.rows * (a.k / 2) : expert_stride, name)) return s;
     a.groups = static_cast<QmmGroup*>(ctx->qmm_groups) + (dense ? TF_MAX_ROUTER_EXPERTS + 1 : 0);
@@ -694,7 +703,7 @@ static tf_status launch_qmm(tf_context* ctx, void* stream, QmmArgs& a, const voi
         TF_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
-    kern<<<ctx->sm_count, kQmmThreads, smem, st>>>(xmap, wmap[0], wmap[1], a);
+    kern<<<ctx->sm_count, kQmmThreads, smem, st>>>(xmap, xmap_big, wmap[0], wmap[1], a);
     return check_launch(ctx, name);
 }
 
