@@ -126,6 +126,12 @@ def cpu_sample(sample_tokens: int, threads: int | None = None):
     return 1.0 / per_token_stack, cores, desc, dt
 
 
+def workload_name(layers, prefill_tokens, steps_dec, batch):
+    """The job both arms are quoted on (BASELINE config 4 at the default arguments)."""
+    return (f"config4: {layers}-layer MoE stack (128 experts int4 g64, top-8, shared expert, RMSNorm between layers, "
+            f"attention omitted): {prefill_tokens}-token prefill + {steps_dec} decode steps at batch 1 + {steps_dec} at batch {batch}")
+
+
 def run_reference(args):
     """The reference has no CPU production path and its Swift/Metal code cannot run here; this arm
     times the C restatement of its kernels (oracle/) with all host threads."""
@@ -144,8 +150,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": mean_dt * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "config4: 30-layer MoE stack (128 experts, top-8, shared expert, D=2816)",
-                   "sample": desc},
+        "config": {"workload": workload_name(LAYERS, PREFILL_TOKENS, DECODE_STEPS, DECODE_BATCH), "sample": desc},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -313,9 +318,7 @@ def run_gpu(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": f"config4: {args.layers}-layer MoE stack (128 experts int4 g64, top-8, shared expert, "
-                               f"RMSNorm between layers, attention omitted): {prefill_tokens}-token prefill + "
-                               f"{steps_dec} decode steps at batch 1 + {steps_dec} at batch {batch}",
+        "config": {"workload": workload_name(args.layers, prefill_tokens, steps_dec, batch),
                    "tokens_per_step": tokens, "routing": "zipf(1.1) logit bias" if args.zipf else "computed logits",
                    "l2": "every step streams 13.2 GB of distinct layer weights (>> 126 MB L2)",
                    "cuda_graphs": use_graphs, "device_status": device_code,
