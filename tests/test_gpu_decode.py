@@ -432,3 +432,24 @@ def test_rmsnorm_and_layer_tail(tf_ctx, oracle):
     torch.cuda.synchronize()
     ref = o.f16_to_f32(o.layer_tail(h2, h1, hid, w2, w, 1e-6, 0.75))
     assert o.rel_error(o.f16_to_f32(from_dev(hd, np.uint16).reshape(T, D)), ref) < 3e-3
+
+
+@pytest.mark.parametrize("m,n,sb", [(4096, 256, 0), (4224, 2816, 0), (5000, 2816, 1)])
+def test_int4_gemv_streaming_kernel_for_large_matrices(tf_ctx, oracle, m, n, sb):
+    """Matrices of at least 4096 rows with 16-byte aligned planes take the tensor-core streaming kernel; same bound as
+    the reference's GEMV tests (rel < 5e-3, Tests/TurboFieldfare/Core/Kernels/Quant/DequantInt4GEMVTests.swift:41-128),
+    ragged last block of rows included, both scale dtypes."""
+    import torch
+    from turbo_fieldfare_b200.kernels import DequantInt4GEMV
+    o = oracle
+    rng = np.random.default_rng(m + n + sb)
+    mat = config0_matrix(o, m, n, rng, sb_dtype=sb)
+    x16 = o.f32_to_f16(rng.standard_normal(n).astype(np.float32))
+    y = dev_zeros_u16(m, fill=0x7E00)
+    DequantInt4GEMV(tf_ctx).encode(to_dev(mat.packed), to_dev(mat.scales), to_dev(mat.biases), to_dev(x16), y, m, n,
+                                   sb_dtype=sb)
+    torch.cuda.synchronize()
+    got = o.f16_to_f32(from_dev(y, np.uint16))
+    ref = o.gemv_ref(mat, o.f16_to_f32(x16))
+    assert np.isfinite(got).all()
+    assert o.rel_error(got, ref) < 5e-3

@@ -9,6 +9,11 @@
 
 namespace tf {
 
+// gemv_mma.cu: the tensor-core streaming kernel for large, aligned matrices
+bool gemv_mma_eligible(const void* W, const void* S, const void* B, const void* x, uint32_t m, uint32_t n);
+tf_status launch_gemv_mma(tf_context* ctx, void* stream, const uint8_t* W, const uint16_t* S, const uint16_t* B,
+                          const uint16_t* x, uint16_t* y, uint32_t m, uint32_t n, bool sb_fp16, const char* name);
+
 constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = kGemvThreads / kWarp;
 
@@ -59,6 +64,10 @@ static tf_status launch_gemv(tf_context* ctx, void* stream, const void* weights,
         TF_REQUIRE(ctx, aligned(W, 2), TF_ERR_ALIGNMENT, "%s: weightsOffset must be even", name);
     TF_REQUIRE(ctx, aligned(S, 2) && aligned(Bp, 2) && aligned(xp, 2) && aligned(yp, 2), TF_ERR_ALIGNMENT,
                "%s: scale/bias/x/y planes must be 2-byte aligned", name);
+    if (BITS == 4 && gemv_mma_eligible(W, S, Bp, xp, m, n))
+        return launch_gemv_mma(ctx, stream, W, reinterpret_cast<const uint16_t*>(S), reinterpret_cast<const uint16_t*>(Bp),
+                               reinterpret_cast<const uint16_t*>(xp), reinterpret_cast<uint16_t*>(yp), m, n,
+                               sb_dtype == TF_FP16, name);
     const size_t smem = stage_x_bytes((int)n);
     TF_REQUIRE(ctx, smem <= 96 * 1024, TF_ERR_UNSUPPORTED, "%s: N=%u too large for the staged-x kernel", name, n);
 

@@ -50,10 +50,20 @@ def case_gemv(args) -> None:
     x = torch.randn(2816, device="cuda").half()
     y = torch.zeros(args.rows, dtype=torch.float16, device="cuda")
     k = DequantInt4GEMV(ctx)
+    launch = lambda: k.encode(mat.buffer, mat.buffer, mat.buffer, x, y, args.rows, 2816, scales_offset=mat.s_off, biases_offset=mat.b_off)
+    for _ in range(args.warm):
+        launch()
+    times = []
     for _ in range(args.iters):
-        k.encode(mat.buffer, mat.buffer, mat.buffer, x, y, args.rows, 2816, scales_offset=mat.s_off, biases_offset=mat.b_off)
-    torch.cuda.synchronize()
-    print(f"gemv case done: rows={args.rows} bytes={mat.w_bytes + 2 * mat.sb_bytes}")
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(10):
+            launch()
+        t1.record()
+        torch.cuda.synchronize()
+        times.append(t0.elapsed_time(t1) / 10)
+    nbytes = mat.w_bytes + 2 * mat.sb_bytes
+    print(f"gemv case done: rows={args.rows} bytes={nbytes} ms={[round(t, 4) for t in times]} GBps={nbytes / min(times) / 1e6:.0f}")
 
 
 def case_qmm(args) -> None:
