@@ -224,7 +224,8 @@ def run_gpu(args):
             launches[tokens] = ctx.launch_count - before
         return g
 
-    # the expert-parallel path interleaves NCCL collectives with the kernels and runs eagerly
+    # The expert-parallel path interleaves NCCL collectives with the kernels and runs eagerly: capturing the
+    # all-to-all exchanges in a CUDA graph did not complete on this software stack (the run was ended by its timeout).
     use_graphs = not args.no_graphs and not ep
     g1 = capture(h1, 1, ws_b1) if use_graphs else None
     gn = capture(hn, batch, ws_bn) if use_graphs else None
@@ -312,6 +313,7 @@ def run_gpu(args):
     # (gate/up launch + down launch of one layer timed as a pair, distinct layers back to back so
     # that nothing is re-read from L2).
     roofline = None if ep else measure_roofline(torch, ctx, stack, ws_bn, hn, batch, PrefillRouter, PrefillGroupedRoutedMoE)
+    gemv = None if ep else measure_gemv(torch, ctx, roofline["peak"], roofline["peak_source"])
     device_code = ctx.device_status()          # 0 unless a kernel abandoned a bounded wait
 
     line = {
@@ -331,6 +333,7 @@ def run_gpu(args):
                 "ms_per_step": ms_e2e},
         "gpu_launches": n_launches,
         "roofline": roofline,
+        "gemv_roofline": gemv,
     }
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
@@ -339,6 +342,36 @@ def run_gpu(args):
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def measure_gemv(torch, ctx, peak, peak_src):
+    """BASELINE's first metric, "int4 expert GEMV HBM GB/s (% of peak)": the stand-alone GEMV (config-0 row shape, N = 2816)
+    on a matrix far larger than L2 (262144 rows, 415 MB: the reference's LM-head-sized instance), timed with CUDA events
+    over back-to-back launches. Algorithmic bytes = packed codes + scale and bias planes."""
+    from turbo_fieldfare_b200.kernels import DequantInt4GEMV
+    from turbo_fieldfare_b200.stack import AffineTensor
+    rows = 262144
+    mat = AffineTensor(rows, D, 4)
+    mat.fill_synthetic(ctx, 77)
+    x = torch.randn(D, device="cuda").half()
+    y = torch.zeros(rows, dtype=torch.float16, device="cuda")
+    op = DequantInt4GEMV(ctx)
+    launch = lambda: op.encode(mat.buffer, mat.buffer, mat.buffer, x, y, rows, D, scales_offset=mat.s_off, biases_offset=mat.b_off)
+    for _ in range(5):
+        launch()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 20
+    s.record()
+    for _ in range(reps):
+        launch()
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / reps
+    nbytes = mat.w_bytes + 2 * mat.sb_bytes
+    achieved = nbytes / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "kernel": "gemv_mma_kernel (tf_int4_gemv, 262144 x 2816)", "achieved": achieved, "peak": peak, "unit": "GB/s",
+            "frac": achieved / peak, "peak_source": peak_src, "bytes_per_launch": nbytes, "us_per_launch": ms * 1e3}
 
 
 def measure_roofline(torch, ctx, stack, ws, h, batch, PrefillRouter, PrefillGroupedRoutedMoE):

@@ -460,6 +460,15 @@ tf_status tf_ep_experts(tf_context* ctx, void* stream, const void* pool_layer_ba
                         const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
                         uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
                         const void* zero_weights, void* acts_scratch, void* out_rows, uint32_t d, uint32_t f);
+/* tf_ep_experts for prefill-sized exchanges (every received slot holds a row): the same result through the tcgen05
+ * grouped GEMMs. Extra scratch: x_sorted and out_sorted [recv_slots, D] fp16, row_ids and inverse_perm [recv_slots],
+ * one_weights [recv_slots] fp16 holding 1.0. */
+tf_status tf_ep_experts_tensorcore(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
+                                   const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
+                                   uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
+                                   const void* zero_weights, const void* one_weights, void* x_sorted, uint32_t* row_ids,
+                                   uint32_t* inverse_perm, void* acts_scratch, void* out_sorted, void* out_rows,
+                                   uint32_t d, uint32_t f);
 tf_status tf_ep_finish(tf_context* ctx, void* stream, const tf_moe_layer* layer, const void* x, uint32_t tokens,
                        tf_workspace* ws, const void* returned_rows, const uint32_t* inverse_perm, void* y);
 /* out[t] = half(sum_r w[t,r] * returned_rows[inverse_perm[t*top_k + r]] + residual[t]), rank order. */

@@ -47,7 +47,7 @@ def test_pack_matches_numpy_plan(tf_ctx, oracle, T, capacity):
     assert np.array_equal(rows[valid], x16[tok[valid]])
 
 
-@pytest.mark.parametrize("T,fixed", [(1, True), (6, True), (70, False)])
+@pytest.mark.parametrize("T,fixed", [(1, True), (6, True), (70, False), (300, False)])   # 300 x 8 rows: tensor-core expert phase
 def test_single_rank_ep_stack_matches_fused_stack(tf_ctx, oracle, T, fixed):
     import torch
     from turbo_fieldfare_b200.ep import ExpertParallelStack
@@ -65,7 +65,8 @@ def test_single_rank_ep_stack_matches_fused_stack(tf_ctx, oracle, T, fixed):
     assert tf_ctx.device_status() == 0
     a = o.f16_to_f32(from_dev(h_ref, np.uint16))
     b = o.f16_to_f32(from_dev(h_ep, np.uint16))
-    assert o.rel_l2(b, a) < 3e-3          # fp16 result rows over the wire instead of fp32 partials
+    # fp16 result rows over the wire instead of fp32 partials; at 300 tokens both stacks run tcgen05 GEMMs in different tilings
+    assert o.rel_l2(b, a) < 3e-3
     ref_stack.close()
     ep_stack.close()
 

@@ -114,6 +114,8 @@ SIGNATURES = {
     "tf_residual_rmsnorm": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, u32, f32]),
     "tf_ep_dispatch": (C.c_int, [vp, vp, C.POINTER(MoELayer), vp, u32, vp, u32, u32, vp, vp, vp]),
     "tf_ep_experts": (C.c_int, [vp, vp, vp, u64, C.POINTER(ExpertOffsets), vp, vp, u32, u32, C.POINTER(DeviceRoutes), vp, vp, vp, u32, u32]),
+    "tf_ep_experts_tensorcore": (C.c_int, [vp, vp, vp, u64, C.POINTER(ExpertOffsets), vp, vp, u32, u32, C.POINTER(DeviceRoutes),
+                                           vp, vp, vp, vp, vp, vp, vp, vp, u32, u32]),
     "tf_ep_finish": (C.c_int, [vp, vp, C.POINTER(MoELayer), vp, u32, vp, vp, vp, vp]),
     "tf_ep_pack": (C.c_int, [vp, vp, vp, u64, u32, C.POINTER(DeviceRoutes), u32, u32, u32, u32, u32, u32, vp, vp, vp]),
     "tf_ep_combine": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, vp, u32, u32, u32, u32]),

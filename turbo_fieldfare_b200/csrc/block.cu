@@ -450,6 +450,30 @@ tf_status tf_ep_experts(tf_context* ctx, void* stream, const void* pool_layer_ba
                                   acts_scratch, out_rows, 0, recv_slots, d, f, 1);
 }
 
+tf_status tf_ep_experts_tensorcore(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
+                                   const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
+                                   uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
+                                   const void* zero_weights, const void* one_weights, void* x_sorted, uint32_t* row_ids,
+                                   uint32_t* inverse_perm, void* acts_scratch, void* out_sorted, void* out_rows,
+                                   uint32_t d, uint32_t f) {
+    const char* name = "tf_ep_experts_tensorcore";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, pool_layer_base && offsets && recv_rows && recv_expert_ids && recv_routes && zero_weights && one_weights &&
+                        x_sorted && row_ids && inverse_perm && acts_scratch && out_sorted && out_rows,
+               TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    if (recv_slots == 0) return TF_OK;
+    // group the received rows by local expert, gather them into expert order, run the tcgen05 GEMMs, and put the
+    // results back into slot order (a combine with one rank of weight 1.0 is an exact copy through the permutation)
+    tf_status s = tf_group_routes_device(ctx, stream, recv_expert_ids, zero_weights, recv_slots, 1, local_experts, recv_routes);
+    if (s) return s;
+    s = tf_pack_sorted_rows(ctx, stream, recv_rows, d, recv_routes, recv_slots, 1, local_experts, d, x_sorted, row_ids, inverse_perm);
+    if (s) return s;
+    s = tf_grouped_moe_tensorcore(ctx, stream, x_sorted, recv_slots, pool_layer_base, expert_stride, local_experts, offsets,
+                                  recv_routes, acts_scratch, out_sorted, d, f);
+    if (s) return s;
+    return tf_ep_combine(ctx, stream, out_sorted, one_weights, inverse_perm, nullptr, d, out_rows, d, recv_slots, 1, d);
+}
+
 tf_status tf_ep_finish(tf_context* ctx, void* stream, const tf_moe_layer* layer, const void* x, uint32_t tokens,
                        tf_workspace* ws, const void* returned_rows, const uint32_t* inverse_perm, void* y) {
     const char* name = "tf_ep_finish";

@@ -75,6 +75,8 @@ class ExpertParallelStack:
         if num_experts % self.world:
             raise ValueError(f"{num_experts} experts do not divide over {self.world} ranks")
         self.local_experts = num_experts // self.world
+        # exact-split exchanges of at least this many rows run their experts on the tensor cores (256 tokens x top-8)
+        self.tensorcore_min_rows = 2048
         self.dims = dict(layers=layers, d=d, f=f, fs=fs, num_experts=num_experts, top_k=top_k)
         self.eps = eps
         self.pool = ExpertPool(context, layers, self.local_experts, d, f, align)
@@ -148,10 +150,19 @@ class ExpertParallelStack:
                 recv_slots, recv_splits = n_pairs, send_splits
                 recv_ids, recv_rows = buf.send_ids, buf.send_rows
                 buf.ensure_recv(recv_slots)
-        ctx.check(lib.tf_ep_experts(ctx.handle, st, self.pool.ptr(l, 0), self.pool.stride, C.byref(self.pool.offsets),
-                                    _ptr(recv_rows), _ptr(recv_ids), recv_slots, self.local_experts,
-                                    C.byref(buf.recv_routes.c_struct), _ptr(buf.zero_weights), _ptr(buf.acts),
-                                    _ptr(buf.out_rows), d, f))
+        if not buf.fixed and recv_slots >= self.tensorcore_min_rows and d % 64 == 0 and f % 64 == 0:
+            # prefill-sized exchange: every received slot holds a row, the experts run as tcgen05 grouped GEMMs
+            buf.ensure_sorted(recv_slots)
+            ctx.check(lib.tf_ep_experts_tensorcore(
+                ctx.handle, st, self.pool.ptr(l, 0), self.pool.stride, C.byref(self.pool.offsets), _ptr(recv_rows),
+                _ptr(recv_ids), recv_slots, self.local_experts, C.byref(buf.recv_routes.c_struct), _ptr(buf.zero_weights),
+                _ptr(buf.one_weights), _ptr(buf.x_sorted), _ptr(buf.row_ids), _ptr(buf.inverse_sorted), _ptr(buf.acts),
+                _ptr(buf.out_sorted), _ptr(buf.out_rows), d, f))
+        else:
+            ctx.check(lib.tf_ep_experts(ctx.handle, st, self.pool.ptr(l, 0), self.pool.stride, C.byref(self.pool.offsets),
+                                        _ptr(recv_rows), _ptr(recv_ids), recv_slots, self.local_experts,
+                                        C.byref(buf.recv_routes.c_struct), _ptr(buf.zero_weights), _ptr(buf.acts),
+                                        _ptr(buf.out_rows), d, f))
         if self.world > 1:
             if buf.fixed:
                 dist.all_to_all_single(buf.back_rows[:recv_slots * d], buf.out_rows[:recv_slots * d], group=self.group)
@@ -204,6 +215,20 @@ class EPBuffers:
         self.zero_weights = torch.zeros(cap, **i16)
         self.recv_routes = DeviceRoutes(cap, 1, self.stack.local_experts)
         self._recv_cap = cap
+
+    def ensure_sorted(self, slots: int) -> None:
+        """Scratch of the tensor-core expert phase: expert-sorted rows in and out, the permutation, unit weights."""
+        if slots <= getattr(self, "_sorted_cap", 0):
+            return
+        cap = max(slots, self._recv_cap)
+        i16 = dict(dtype=torch.float16, device="cuda")
+        i32 = dict(dtype=torch.int32, device="cuda")
+        self.x_sorted = torch.zeros(cap * self.d, **i16)
+        self.out_sorted = torch.zeros(cap * self.d, **i16)
+        self.row_ids = torch.zeros(cap, **i32)
+        self.inverse_sorted = torch.zeros(cap, **i32)
+        self.one_weights = torch.ones(cap, **i16)
+        self._sorted_cap = cap
 
     def ws_counts(self, num_experts: int) -> np.ndarray:
         """Per-expert pair counts of the last dispatch, read back from the device (synchronises)."""
