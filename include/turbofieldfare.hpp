@@ -1,0 +1,180 @@
+// turbofieldfare.hpp — C++ host-side mirror of the reference's Swift operator classes over the C ABI.
+//
+// The reference's host code is Swift (Sources/TurboFieldfare/Kernels/...); where no Swift toolchain exists, this
+// header is the host side above turbofieldfare_cuda.h: the same class and method names, the same argument meaning
+// ((buffer, byte offset) pairs, a stream where Swift takes a command buffer), and the same error behaviour (a Swift
+// `precondition` or `throw` becomes a thrown tf::Error carrying the status and tf_last_error's text). Every method
+// is one call into the C ABI; nothing here computes or allocates on the device.
+#pragma once
+
+#include <stdexcept>
+#include <string>
+
+#include "turbofieldfare_cuda.h"
+
+namespace turbofieldfare {
+
+// SharedExpertError / PrefillMoEGroupingError / PrefillGroupedRoutedMoEError / MetalError in one type:
+// `status` tells which (TF_ERR_DIMENSION_MISMATCH, TF_ERR_GROUPING_*, TF_ERR_OUT_OF_MEMORY, TF_ERR_NO_DEVICE, ...).
+class Error : public std::runtime_error {
+public:
+    Error(tf_status s, const std::string& what) : std::runtime_error(what), status(s) {}
+    tf_status status;
+};
+
+// MetalContext (Infrastructure/Metal/MetalContext.swift:51-214): device + error text; kernels are compiled ahead of time.
+class Context {
+public:
+    explicit Context(int device = 0) {
+        const tf_status s = tf_context_create(device, &ctx_);
+        if (s != TF_OK) throw Error(s, tf_last_error(nullptr));
+    }
+    ~Context() { tf_context_destroy(ctx_); }
+    Context(const Context&) = delete;
+    Context& operator=(const Context&) = delete;
+    tf_context* handle() const { return ctx_; }
+    void check(tf_status s) const { if (s != TF_OK) throw Error(s, tf_last_error(ctx_)); }
+    // commandBuffer.waitUntilCompleted() + .error for kernels with bounded waits
+    void waitUntilCompleted() const { uint32_t code = 0; check(tf_device_status(ctx_, &code)); }
+private:
+    tf_context* ctx_ = nullptr;
+};
+
+// A buffer + byte offset, the pair every Swift wrapper takes (TensorView, ModelTypes.swift:164-192).
+struct BufferRef {
+    const void* buffer = nullptr;
+    uint64_t offset = 0;
+};
+struct MutableBufferRef {
+    void* buffer = nullptr;
+    uint64_t offset = 0;
+};
+
+// DequantInt4GEMV (Kernels/Quant/DequantInt4GEMV.swift:44-87)
+class DequantInt4GEMV {
+public:
+    explicit DequantInt4GEMV(const Context& c) : c_(c) {}
+    void encode(void* stream, BufferRef weights, BufferRef scales, BufferRef biases, BufferRef x, MutableBufferRef y,
+                uint32_t m, uint32_t n, tf_dtype scaleBiasType = TF_BF16) const {
+        c_.check(tf_int4_gemv(c_.handle(), stream, weights.buffer, weights.offset, scales.buffer, scales.offset, biases.buffer,
+                              biases.offset, x.buffer, x.offset, y.buffer, y.offset, m, n, scaleBiasType));
+    }
+private:
+    const Context& c_;
+};
+
+// DequantInt8GEMV (Kernels/Quant/DequantInt8GEMV.swift:50-81)
+class DequantInt8GEMV {
+public:
+    explicit DequantInt8GEMV(const Context& c) : c_(c) {}
+    void encode(void* stream, BufferRef weights, BufferRef scales, BufferRef biases, BufferRef x, MutableBufferRef y,
+                uint32_t m, uint32_t n, tf_dtype scaleBiasType = TF_BF16) const {
+        c_.check(tf_int8_gemv(c_.handle(), stream, weights.buffer, weights.offset, scales.buffer, scales.offset, biases.buffer,
+                              biases.offset, x.buffer, x.offset, y.buffer, y.offset, m, n, scaleBiasType));
+    }
+private:
+    const Context& c_;
+};
+
+// MoE (Kernels/MoE/MoE.swift:92-295): router and the reference-shaped decode phases over a table of blob pointers.
+class MoE {
+public:
+    explicit MoE(const Context& c) : c_(c) {}
+    void encodeRouterGemma4(void* stream, BufferRef weights, BufferRef scales, BufferRef biases, const void* hidden,
+                            BufferRef effectiveScale, BufferRef perExpertScale, uint32_t* outIndices, void* outWeights,
+                            uint32_t numExperts, uint32_t d, uint32_t topK = TF_MAX_TOP_K) const {
+        c_.check(tf_router_gemma4(c_.handle(), stream, weights.buffer, weights.offset, scales.buffer, scales.offset, biases.buffer,
+                                  biases.offset, hidden, effectiveScale.buffer, effectiveScale.offset, perExpertScale.buffer,
+                                  perExpertScale.offset, outIndices, outWeights, nullptr, numExperts, d, topK));
+    }
+    void encodeRoutedPersistentPhase1U16Load(void* stream, const void* const* blobTable, const tf_expert_offsets& offsets,
+                                             const void* x, void* acts, uint32_t d, uint32_t f, uint32_t topK) const {
+        c_.check(tf_moe_phase1(c_.handle(), stream, blobTable, &offsets, x, acts, d, f, topK));
+    }
+    void encodeRoutedPersistentPhase2Reduce(void* stream, const void* const* blobTable, const tf_expert_offsets& offsets,
+                                            const void* acts, const void* routingWeights, const void* residual, void* y,
+                                            uint32_t d, uint32_t f, uint32_t topK) const {
+        c_.check(tf_moe_phase2_reduce(c_.handle(), stream, blobTable, &offsets, acts, routingWeights, residual, y, d, f, topK));
+    }
+private:
+    const Context& c_;
+};
+
+// PrefillRouter (Kernels/Prefill/MoE/PrefillRouter.swift:37-89)
+class PrefillRouter {
+public:
+    explicit PrefillRouter(const Context& c) : c_(c) {}
+    void encodeGemma4Block(void* stream, BufferRef weights, BufferRef scales, BufferRef biases, BufferRef hidden,
+                           BufferRef effectiveScale, BufferRef perExpertScale, uint32_t* outIndices, void* outWeights,
+                           uint32_t queryCount, uint32_t numExperts, uint32_t d, uint32_t topK, uint32_t hiddenStrideElements,
+                           tf_dtype hiddenType = TF_FP16) const {
+        c_.check(tf_router_gemma4_block(c_.handle(), stream, weights.buffer, weights.offset, scales.buffer, scales.offset,
+                                        biases.buffer, biases.offset, hidden.buffer, hidden.offset, hiddenType, effectiveScale.buffer,
+                                        effectiveScale.offset, perExpertScale.buffer, perExpertScale.offset, nullptr, outIndices, 0,
+                                        outWeights, 0, nullptr, queryCount, numExperts, d, topK, hiddenStrideElements));
+    }
+private:
+    const Context& c_;
+};
+
+// PrefillGroupedRoutedMoE (Kernels/Prefill/MoE/PrefillGroupedRoutedMoE.swift:386-461) over the HBM-resident pool, with the
+// grouping done on the device (PrefillMoEGrouping.groupTokenExpertPairs without the CPU read-back).
+class PrefillGroupedRoutedMoE {
+public:
+    explicit PrefillGroupedRoutedMoE(const Context& c) : c_(c) {}
+    void encodeGroupRoutes(void* stream, const uint32_t* indices, const void* weights, uint32_t queryCount, uint32_t topK,
+                           uint32_t numExperts, const tf_device_routes& routes) const {
+        c_.check(tf_group_routes_device(c_.handle(), stream, indices, weights, queryCount, topK, numExperts, &routes));
+    }
+    void encodeStreamedBatched(void* stream, BufferRef hidden, uint32_t hiddenStrideElements, const void* poolLayerBase,
+                               uint64_t expertStride, const tf_expert_offsets& offsets, const tf_device_routes& routes,
+                               void* actsScratch, void* routePartials, bool partialsF32, uint32_t queryCount, uint32_t d,
+                               uint32_t f, uint32_t topK) const {
+        c_.check(tf_grouped_moe_batched(c_.handle(), stream, hidden.buffer, hidden.offset, hiddenStrideElements, poolLayerBase,
+                                        expertStride, &offsets, &routes, actsScratch, routePartials, partialsF32 ? 1 : 0, queryCount,
+                                        d, f, topK));
+    }
+private:
+    const Context& c_;
+};
+
+// PrefillMoE (Kernels/Prefill/MoE/PrefillMoE.swift:11-39)
+class PrefillMoE {
+public:
+    explicit PrefillMoE(const Context& c) : c_(c) {}
+    void encodeReduceTokenMajor(void* stream, const void* routePartials, bool partialsF32, const void* routeWeights, void* h2,
+                                uint32_t queryCount, uint32_t topK, uint32_t d) const {
+        c_.check(tf_moe_reduce_token_major(c_.handle(), stream, routePartials, partialsF32 ? 1 : 0, routeWeights, nullptr, d, h2, d,
+                                           queryCount, topK, d));
+    }
+private:
+    const Context& c_;
+};
+
+// PrefillSharedExpert (Kernels/Prefill/MoE/PrefillSharedExpert.swift:11-59)
+class PrefillSharedExpert {
+public:
+    explicit PrefillSharedExpert(const Context& c) : c_(c) {}
+    void encodeBlock(void* stream, BufferRef x, uint32_t xStrideElements, const tf_projection& gate, const tf_projection& up,
+                     const tf_projection& down, MutableBufferRef y, uint32_t yStrideElements, void* scratchAct, uint32_t rows) const {
+        c_.check(tf_shared_expert_int4_block(c_.handle(), stream, x.buffer, x.offset, xStrideElements, &gate, &up, &down, y.buffer,
+                                             y.offset, yStrideElements, scratchAct, rows));
+    }
+private:
+    const Context& c_;
+};
+
+// MPPPrefillInt4QMM (Kernels/TensorCore/MPPPrefillInt4QMM.swift:34-78): there is no `.unavailable` path here.
+class MPPPrefillInt4QMM {
+public:
+    explicit MPPPrefillInt4QMM(const Context& c) : c_(c) {}
+    void encode(void* stream, BufferRef weights, BufferRef scales, BufferRef biases, BufferRef x, MutableBufferRef y,
+                uint32_t m, uint32_t n, uint32_t k) const {
+        c_.check(tf_int4_qmm(c_.handle(), stream, weights.buffer, weights.offset, scales.buffer, scales.offset, biases.buffer,
+                             biases.offset, x.buffer, x.offset, y.buffer, y.offset, m, n, k));
+    }
+private:
+    const Context& c_;
+};
+
+}  // namespace turbofieldfare
