@@ -90,6 +90,8 @@ __global__ void __launch_bounds__(kRrnThreads)
 residual_rmsnorm_kernel(uint16_t* __restrict__ h, const uint16_t* __restrict__ y, const uint16_t* __restrict__ w,
                         uint16_t* __restrict__ x, uint32_t d, float eps) {
     __shared__ float red[kRrnThreads / kWarp];
+    pdl_launch_dependents();
+    pdl_wait();
     uint16_t* hr = h + (size_t)blockIdx.x * d;
     const uint32_t vecs = d / 8;
     float v[kRrnMaxSlices][8];
@@ -403,9 +405,9 @@ tf_status tf_residual_rmsnorm(tf_context* ctx, void* stream, void* hidden, const
     TF_REQUIRE(ctx, tf::aligned(hidden, 16) && tf::aligned(y, 16) && tf::aligned(weight_bf16, 16) && tf::aligned(x_out, 16),
                TF_ERR_ALIGNMENT, "%s: buffers must be 16-byte aligned", name);
     if (rows == 0) return TF_OK;
-    tf::residual_rmsnorm_kernel<<<rows, tf::kRrnThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<uint16_t*>(hidden), static_cast<const uint16_t*>(y), static_cast<const uint16_t*>(weight_bf16),
-        static_cast<uint16_t*>(x_out), d, eps);
+    tf::launch_pdl(tf::residual_rmsnorm_kernel, dim3(rows), dim3(tf::kRrnThreads), 0, static_cast<cudaStream_t>(stream),
+                   static_cast<uint16_t*>(hidden), static_cast<const uint16_t*>(y), static_cast<const uint16_t*>(weight_bf16),
+                   static_cast<uint16_t*>(x_out), d, eps);
     return tf::check_launch(ctx, name);
 }
 
@@ -522,13 +524,14 @@ tf_status tf_stack_forward(tf_stack* st, void* stream, void* hidden, uint32_t to
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     uint16_t* h = static_cast<uint16_t*>(hidden);
     for (size_t l = 0; l < st->layers.size(); ++l) {
-        tf::residual_rmsnorm_kernel<<<tokens, tf::kRrnThreads, smem, cs>>>(h, l == 0 ? nullptr : ws->y_block,
-                                                              static_cast<const uint16_t*>(st->norm_weights[l]),
-                                                              ws->x_norm, d, st->eps);
+        tf::launch_pdl(tf::residual_rmsnorm_kernel, dim3(tokens), dim3(tf::kRrnThreads), smem, cs, h,
+                       l == 0 ? static_cast<const uint16_t*>(nullptr) : static_cast<const uint16_t*>(ws->y_block),
+                       static_cast<const uint16_t*>(st->norm_weights[l]), ws->x_norm, d, st->eps);
         if (tf_status s = tf::check_launch(ctx, "residual_rmsnorm")) return s;
         if (tf_status s = tf_moe_block_forward(ctx, stream, &st->layers[l], ws->x_norm, d, ws->y_block, d, tokens, ws)) return s;
     }
-    tf::residual_rmsnorm_kernel<<<tokens, tf::kRrnThreads, smem, cs>>>(h, ws->y_block, nullptr, nullptr, d, st->eps);
+    tf::launch_pdl(tf::residual_rmsnorm_kernel, dim3(tokens), dim3(tf::kRrnThreads), smem, cs, h, static_cast<const uint16_t*>(ws->y_block),
+                   static_cast<const uint16_t*>(nullptr), static_cast<uint16_t*>(nullptr), d, st->eps);
     return tf::check_launch(ctx, "residual_add");
 }
 

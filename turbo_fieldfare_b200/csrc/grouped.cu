@@ -55,7 +55,9 @@ group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __rest
     __shared__ uint32_t s_offset, s_gi, s_chunk0;
     const uint32_t e = blockIdx.x;
     const uint32_t n = T * K;
+    pdl_launch_dependents();
     for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) hist[i] = 0;
+    pdl_wait();
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
         uint32_t ex = indices[i];
@@ -339,6 +341,8 @@ grouped_ksplit_kernel(const GroupedArgs args) {
     auto bar_red_free = [&](uint32_t r) { return bar_base + (2 * kWStages + kRedStages + r) * 8; };
 
     const uint32_t tiles = args.rows / kTileRows;
+    pdl_launch_dependents();
+    pdl_wait();              // routing metadata and activations come from the kernels before this one
     const uint32_t total_chunks = DENSE ? (args.dense_tokens + kChunkTokens - 1) / kChunkTokens : args.counters[1];
     const uint32_t total_items = total_chunks * tiles;
     // contiguous item range per CTA: consecutive items share the chunk, whose activations stay in registers
@@ -681,6 +685,8 @@ __global__ void reduce_token_major_kernel(const void* __restrict__ partials, con
                                           uint32_t T, uint32_t K, uint32_t D) {
     const uint32_t d = blockIdx.x * blockDim.x + threadIdx.x;
     const uint32_t t = blockIdx.y;
+    pdl_launch_dependents();
+    pdl_wait();
     if (d >= D || t >= T) return;
     float acc;
     if constexpr (PARTIAL_F32) {
@@ -724,7 +730,7 @@ static tf_status launch_grouped_k(tf_context* ctx, void* stream, GroupedArgs& ar
         if (items == 0) return TF_OK;
         if (items < grid) grid = (uint32_t)items;
     }
-    kern<<<grid, (cw + kExtraWarps) * kWarp, smem, static_cast<cudaStream_t>(stream)>>>(args);
+    launch_pdl(kern, dim3(grid), dim3((cw + kExtraWarps) * kWarp), smem, static_cast<cudaStream_t>(stream), args);
     return check_launch(ctx, name);
 }
 
@@ -813,10 +819,10 @@ tf_status tf_group_routes_device(tf_context* ctx, void* stream, const uint32_t* 
     TF_REQUIRE(ctx, num_experts > 0 && num_experts <= TF_MAX_ROUTER_EXPERTS, TF_ERR_GROUPING_INVALID_NUM_EXPERTS,
                "numExperts must be in 1...256, got %u", num_experts);
     TF_REQUIRE(ctx, (uint64_t)query_count * top_k < (1ull << 31), TF_ERR_INVALID_ARGUMENT, "%s: too many pairs", name);
-    tf::group_routes_kernel<<<num_experts, tf::kGroupThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        indices, static_cast<const uint16_t*>(weights_f16), query_count, top_k, num_experts, routes->sorted_pairs,
-        routes->per_expert_offsets, routes->per_expert_counts, routes->groups, routes->chunk_group, routes->chunk_start,
-        routes->counters);
+    tf::launch_pdl(tf::group_routes_kernel, dim3(num_experts), dim3(tf::kGroupThreads), 0, static_cast<cudaStream_t>(stream),
+                   indices, static_cast<const uint16_t*>(weights_f16), query_count, top_k, num_experts, routes->sorted_pairs,
+                   routes->per_expert_offsets, routes->per_expert_counts, routes->groups, routes->chunk_group, routes->chunk_start,
+                   routes->counters);
     return tf::check_launch(ctx, name);
 }
 
@@ -871,11 +877,11 @@ tf_status tf_moe_reduce_token_major(tf_context* ctx, void* stream, const void* r
     dim3 grid((d + 255) / 256, query_count);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (partials_f32)
-        tf::reduce_token_major_kernel<true><<<grid, 256, 0, st>>>(route_partials, static_cast<const uint16_t*>(route_weights),
+        tf::launch_pdl(tf::reduce_token_major_kernel<true>, grid, dim3(256), 0, st, route_partials, static_cast<const uint16_t*>(route_weights),
                                                                   static_cast<const uint16_t*>(residual), residual_stride_elements,
                                                                   static_cast<uint16_t*>(h2), h2_stride_elements, query_count, top_k, d);
     else
-        tf::reduce_token_major_kernel<false><<<grid, 256, 0, st>>>(route_partials, static_cast<const uint16_t*>(route_weights),
+        tf::launch_pdl(tf::reduce_token_major_kernel<false>, grid, dim3(256), 0, st, route_partials, static_cast<const uint16_t*>(route_weights),
                                                                    static_cast<const uint16_t*>(residual), residual_stride_elements,
                                                                    static_cast<uint16_t*>(h2), h2_stride_elements, query_count, top_k, d);
     return tf::check_launch(ctx, name);

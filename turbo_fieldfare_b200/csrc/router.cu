@@ -140,6 +140,7 @@ router_split_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
     const uint16_t* hrow = hidden + (size_t)row * hidden_stride;
     const bool a16 = (reinterpret_cast<uintptr_t>(wsrc) & 15) == 0 && (d & 15) == 0;
     const bool x16 = (reinterpret_cast<uintptr_t>(hrow) & 15) == 0 && (reinterpret_cast<uintptr_t>(eff) & 15) == 0 && (d & 7) == 0;
+    pdl_launch_dependents();
     if (a16 && x16 && ne * d <= kSplitThreads * 16 * 6 && d <= kSplitThreads * 8 * 3) {
         // latency path: every load of the block is issued before the first one is consumed
         uint4 wv[6], hv[3], ev[3];
@@ -148,6 +149,7 @@ router_split_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
             const uint32_t i = threadIdx.x + j * kSplitThreads;
             wv[j] = i < ne * d / 16 ? ldg_nc_u4(wsrc + (size_t)i * 16) : make_uint4(0u, 0u, 0u, 0u);
         }
+        pdl_wait();          // the weights above do not depend on the previous kernel; the hidden row does
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
             const uint32_t i = threadIdx.x + j * kSplitThreads;
@@ -194,6 +196,7 @@ router_split_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
             srows[i] = S[(size_t)e0 * groups + i];
             brows[i] = B[(size_t)e0 * groups + i];
         }
+        pdl_wait();
         stage_router_x<X_BF16>(hrow, eff, xf, d);     // ends with a barrier
     }
 
@@ -238,6 +241,8 @@ router_block_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
     float* xf = reinterpret_cast<float*>(smem);
     __shared__ float scores[TF_MAX_ROUTER_EXPERTS];
     const uint32_t row = blockIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
     stage_router_x<X_BF16>(hidden + (size_t)row * hidden_stride, eff, xf, d);
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t groups = d / kGroup;
@@ -280,13 +285,13 @@ static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, 
         const size_t smem_split = (size_t)d * 4 + (size_t)kSplitExpertsPerBlock * d + (size_t)kSplitExpertsPerBlock * (d / kGroup) * 4;
         TF_REQUIRE(ctx, smem_split <= 200 * 1024, TF_ERR_UNSUPPORTED, "%s: D=%u too large", name, d);
         if (smem_split > 40 * 1024) TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_split));
-        k<<<grid, kSplitThreads, smem_split, st>>>(W, Sp, Bp, hp, stride, ep, pp, logit_bias, out_idx, wp, out_logits,
-                                             ctx->router_logits, ctx->router_tickets, num_experts, d, top_k, a2);
+        launch_pdl(k, grid, dim3(kSplitThreads), smem_split, st, W, Sp, Bp, hp, stride, ep, pp, logit_bias, out_idx, wp, out_logits,
+                   ctx->router_logits, ctx->router_tickets, num_experts, d, top_k, a2);
     } else {
         auto k = bf ? router_block_kernel<true> : router_block_kernel<false>;
         if (smem > 40 * 1024) TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        k<<<rows, kBlockRouterThreads, smem, st>>>(W, Sp, Bp, hp, stride, ep, pp, logit_bias, out_idx, wp, out_logits,
-                                                   num_experts, d, top_k, a2);
+        launch_pdl(k, dim3(rows), dim3(kBlockRouterThreads), smem, st, W, Sp, Bp, hp, stride, ep, pp, logit_bias, out_idx, wp, out_logits,
+                   num_experts, d, top_k, a2);
     }
     return check_launch(ctx, name);
 }

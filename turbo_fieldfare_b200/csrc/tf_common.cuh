@@ -68,6 +68,18 @@ tf_status check_launch(tf_context* ctx, const char* what);
             return ::tf::fail((ctx), TF_ERR_CUDA, "%s: %s", #expr, cudaGetErrorString(_e)); \
     } while (0)
 
+// Launch with the programmatic-stream-serialisation attribute (see pdl_wait in the device helpers).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 inline const uint8_t* byte_ptr(const void* p, uint64_t off) { return static_cast<const uint8_t*>(p) + off; }
 inline uint8_t* byte_ptr(void* p, uint64_t off) { return static_cast<uint8_t*>(p) + off; }
@@ -104,6 +116,13 @@ __device__ __forceinline__ float gelu_tanh(float x) {
     const float th = 1.0f - __fdividef(2.0f, e + 1.0f);
     return 0.5f * x * (1.0f + th);
 }
+
+// Programmatic dependent launch: a kernel launched with launch_pdl may start (block scheduling, shared-memory set-up)
+// while its predecessor on the stream is still draining; pdl_wait() returns once the predecessor has completed and its
+// writes are visible, so it comes before the first access to anything another kernel produces (and before any
+// write). Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ uint4 ldg_nc_u4(const void* p) {
     uint4 v;
