@@ -442,24 +442,31 @@ tf_status tf_residual_rmsnorm(tf_context* ctx, void* stream, void* hidden, const
  * rank) order, with the expert id local to its owner, and record inverse_perm[token*top_k + rank] = slot.
  * capacity == 0: exact layout, slot = sorted pair index (split sizes come from per_expert_counts).
  * capacity > 0: fixed layout [ranks][capacity] with unused slots marked id = UINT32_MAX (no host
- * synchronisation; an overflowing destination sets the context's device error word). */
+ * synchronisation; an overflowing destination sets the context's device error word).
+ * send_row_stride_elements: 0 or D for plain rows; D + 8 or more (a multiple of 8) makes every send row carry its
+ * expert id in the four bytes after the D activations, so that one exchange moves rows and ids together. */
 tf_status tf_ep_pack(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off, uint32_t hidden_stride_elements,
                      const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
                      uint32_t experts_per_rank, uint32_t capacity, uint32_t d,
-                     void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm);
+                     void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm, uint32_t send_row_stride_elements);
+/* ids[slot] = the expert id that a row of row_stride_elements > D elements carries after its D activations. */
+tf_status tf_ep_extract_ids(tf_context* ctx, void* stream, const void* rows, uint32_t row_stride_elements, uint32_t d,
+                            uint32_t slots, uint32_t* ids);
 /* The three phases of one expert-parallel layer; the caller runs the all-to-all exchanges between them
  * (rows and expert ids out, result rows back).
  *   tf_ep_dispatch: router + top-k + device grouping over the GLOBAL experts + tf_ep_pack;
  *   tf_ep_experts:  on the owner: group the received rows by local expert and run gate/up/GeGLU/down;
- *                   out_rows[slot] is the fp16 expert output of the row received in that slot;
+ *                   out_rows[slot] is the fp16 expert output of the row received in that slot; with
+ *                   recv_row_stride_elements > D the ids are read from the row tails into recv_expert_ids first;
  *   tf_ep_finish:   shared expert on the local tokens + tf_ep_combine of the returned rows. */
 tf_status tf_ep_dispatch(tf_context* ctx, void* stream, const tf_moe_layer* layer, const void* x, uint32_t tokens,
                          tf_workspace* ws, uint32_t experts_per_rank, uint32_t capacity,
-                         void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm);
+                         void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm, uint32_t send_row_stride_elements);
 tf_status tf_ep_experts(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
                         const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
                         uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
-                        const void* zero_weights, void* acts_scratch, void* out_rows, uint32_t d, uint32_t f);
+                        const void* zero_weights, void* acts_scratch, void* out_rows, uint32_t d, uint32_t f,
+                        uint32_t recv_row_stride_elements);
 /* tf_ep_experts for prefill-sized exchanges (every received slot holds a row): the same result through the tcgen05
  * grouped GEMMs. Extra scratch: x_sorted and out_sorted [recv_slots, D] fp16, row_ids and inverse_perm [recv_slots],
  * one_weights [recv_slots] fp16 holding 1.0. */

@@ -31,20 +31,30 @@ def test_pack_matches_numpy_plan(tf_ctx, oracle, T, capacity):
     routes = DeviceRoutes(T, K, E)
     PrefillGroupedRoutedMoE(tf_ctx).encode_group_routes(to_dev(idx), to_dev(w16), T, K, E, routes)
     slots = world * capacity if capacity else T * K
-    send_rows = torch.full((slots * D,), -1, dtype=torch.int16, device="cuda")
+    # fixed-capacity rows carry the expert id in an 8-element tail (one exchange for rows and ids); exact rows are plain
+    stride = D + 8 if capacity else D
+    send_rows = torch.full((slots * stride,), -1, dtype=torch.int16, device="cuda")
     send_ids = torch.full((slots,), 7, dtype=torch.int32, device="cuda")
     inverse = torch.zeros(T * K, dtype=torch.int32, device="cuda")
     tf_ctx.check(tf_ctx.lib.tf_ep_pack(tf_ctx.handle, torch.cuda.current_stream().cuda_stream, to_dev(x16).data_ptr(), 0, D,
                                        C.byref(routes.c_struct), T, K, E, epr, capacity, D, send_rows.data_ptr(),
-                                       send_ids.data_ptr(), inverse.data_ptr()))
+                                       send_ids.data_ptr(), inverse.data_ptr(), stride))
     torch.cuda.synchronize()
     assert tf_ctx.device_status() == 0
     tok, eloc, inv, _ = plan_dispatch(idx, epr, world, capacity)
     assert np.array_equal(from_dev(send_ids, np.uint32), eloc)
     assert np.array_equal(from_dev(inverse, np.uint32), inv)
-    rows = from_dev(send_rows, np.uint16).reshape(slots, D)
+    rows = from_dev(send_rows, np.uint16).reshape(slots, stride)
     valid = tok >= 0
-    assert np.array_equal(rows[valid], x16[tok[valid]])
+    assert np.array_equal(rows[valid][:, :D], x16[tok[valid]])
+    if capacity:
+        tail_ids = np.ascontiguousarray(rows[:, D:D + 2]).view(np.uint32).reshape(slots)
+        assert np.array_equal(tail_ids, eloc)
+        ids2 = torch.zeros(slots, dtype=torch.int32, device="cuda")
+        tf_ctx.check(tf_ctx.lib.tf_ep_extract_ids(tf_ctx.handle, torch.cuda.current_stream().cuda_stream, send_rows.data_ptr(),
+                                                  stride, D, slots, ids2.data_ptr()))
+        torch.cuda.synchronize()
+        assert np.array_equal(from_dev(ids2, np.uint32), eloc)
 
 
 @pytest.mark.parametrize("T,fixed", [(1, True), (6, True), (70, False), (300, False)])   # 300 x 8 rows: tensor-core expert phase

@@ -112,12 +112,14 @@ SIGNATURES = {
     "tf_stack_destroy": (None, [vp]),
     "tf_stack_forward": (C.c_int, [vp, vp, vp, u32, vp]),
     "tf_residual_rmsnorm": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, u32, f32]),
-    "tf_ep_dispatch": (C.c_int, [vp, vp, C.POINTER(MoELayer), vp, u32, vp, u32, u32, vp, vp, vp]),
-    "tf_ep_experts": (C.c_int, [vp, vp, vp, u64, C.POINTER(ExpertOffsets), vp, vp, u32, u32, C.POINTER(DeviceRoutes), vp, vp, vp, u32, u32]),
+    "tf_ep_dispatch": (C.c_int, [vp, vp, C.POINTER(MoELayer), vp, u32, vp, u32, u32, vp, vp, vp, u32]),
+    "tf_ep_experts": (C.c_int, [vp, vp, vp, u64, C.POINTER(ExpertOffsets), vp, vp, u32, u32, C.POINTER(DeviceRoutes), vp, vp, vp, u32, u32,
+                                u32]),
     "tf_ep_experts_tensorcore": (C.c_int, [vp, vp, vp, u64, C.POINTER(ExpertOffsets), vp, vp, u32, u32, C.POINTER(DeviceRoutes),
                                            vp, vp, vp, vp, vp, vp, vp, vp, u32, u32]),
     "tf_ep_finish": (C.c_int, [vp, vp, C.POINTER(MoELayer), vp, u32, vp, vp, vp, vp]),
-    "tf_ep_pack": (C.c_int, [vp, vp, vp, u64, u32, C.POINTER(DeviceRoutes), u32, u32, u32, u32, u32, u32, vp, vp, vp]),
+    "tf_ep_pack": (C.c_int, [vp, vp, vp, u64, u32, C.POINTER(DeviceRoutes), u32, u32, u32, u32, u32, u32, vp, vp, vp, u32]),
+    "tf_ep_extract_ids": (C.c_int, [vp, vp, vp, u32, u32, u32, vp]),
     "tf_ep_combine": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, vp, u32, u32, u32, u32]),
     "tf_rmsnorm": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, u32, u32, u32, f32, C.c_int]),
     "tf_layer_tail": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, f32, f32]),

@@ -417,7 +417,7 @@ tf_status tf_residual_rmsnorm(tf_context* ctx, void* stream, void* hidden, const
 
 tf_status tf_ep_dispatch(tf_context* ctx, void* stream, const tf_moe_layer* layer, const void* x, uint32_t tokens,
                          tf_workspace* ws, uint32_t experts_per_rank, uint32_t capacity,
-                         void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm) {
+                         void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm, uint32_t send_row_stride_elements) {
     const char* name = "tf_ep_dispatch";
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, layer && x && ws, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
@@ -433,22 +433,30 @@ tf_status tf_ep_dispatch(tf_context* ctx, void* stream, const tf_moe_layer* laye
     s = tf_group_routes_device(ctx, stream, ws->indices, ws->weights, tokens, K, E, &ws->routes);
     if (s) return s;
     return tf_ep_pack(ctx, stream, x, 0, d, &ws->routes, tokens, K, E, experts_per_rank, capacity, d, send_rows,
-                      send_expert_ids, inverse_perm);
+                      send_expert_ids, inverse_perm, send_row_stride_elements);
 }
 
 tf_status tf_ep_experts(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
                         const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
                         uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
-                        const void* zero_weights, void* acts_scratch, void* out_rows, uint32_t d, uint32_t f) {
+                        const void* zero_weights, void* acts_scratch, void* out_rows, uint32_t d, uint32_t f,
+                        uint32_t recv_row_stride_elements) {
     const char* name = "tf_ep_experts";
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, pool_layer_base && offsets && recv_rows && recv_expert_ids && recv_routes && zero_weights && acts_scratch && out_rows,
                TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
     if (recv_slots == 0) return TF_OK;
+    const uint32_t stride = recv_row_stride_elements ? recv_row_stride_elements : d;
+    tf_status s;
+    if (stride > d) {
+        // the rows carry their expert id in the tail: recv_expert_ids is filled here instead of by a second exchange
+        s = tf_ep_extract_ids(ctx, stream, recv_rows, stride, d, recv_slots, const_cast<uint32_t*>(recv_expert_ids));
+        if (s) return s;
+    }
     // every received row is one (token = slot, rank 0) pair of a local expert; empty slots carry UINT32_MAX
-    tf_status s = tf_group_routes_device(ctx, stream, recv_expert_ids, zero_weights, recv_slots, 1, local_experts, recv_routes);
+    s = tf_group_routes_device(ctx, stream, recv_expert_ids, zero_weights, recv_slots, 1, local_experts, recv_routes);
     if (s) return s;
-    return tf_grouped_moe_batched(ctx, stream, recv_rows, 0, d, pool_layer_base, expert_stride, offsets, recv_routes,
+    return tf_grouped_moe_batched(ctx, stream, recv_rows, 0, stride, pool_layer_base, expert_stride, offsets, recv_routes,
                                   acts_scratch, out_rows, 0, recv_slots, d, f, 1);
 }
 

@@ -21,7 +21,7 @@ template <bool PERMUTE_K8>
 __global__ void __launch_bounds__(kPackThreads)
 ep_pack_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride, const tf_pair* __restrict__ sorted_pairs,
                const uint32_t* __restrict__ per_expert_counts, uint32_t n_pairs, uint32_t top_k, uint32_t num_experts,
-               uint32_t experts_per_rank, uint32_t n_dst, uint32_t capacity, uint32_t d,
+               uint32_t experts_per_rank, uint32_t n_dst, uint32_t capacity, uint32_t d, uint32_t send_stride,
                uint16_t* __restrict__ send_rows, uint32_t* __restrict__ send_ids, uint32_t* __restrict__ inverse_perm,
                uint32_t* __restrict__ overflow) {
     __shared__ uint32_t dst_base[257], dst_count[256];
@@ -48,7 +48,10 @@ ep_pack_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride, cons
     if (n_dst > 1) {
         const uint32_t dst = slot / capacity, pos = slot % capacity;
         if (pos >= dst_count[dst]) {
-            if (lane == 0) send_ids[slot] = 0xFFFFFFFFu;
+            if (lane == 0) {
+                send_ids[slot] = 0xFFFFFFFFu;
+                if (send_stride > d) *reinterpret_cast<uint32_t*>(send_rows + (size_t)slot * send_stride + d) = 0xFFFFFFFFu;
+            }
             return;
         }
         p = dst_base[dst] + pos;
@@ -58,10 +61,12 @@ ep_pack_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride, cons
     const tf_pair pr = sorted_pairs[p];
     if (lane == 0) {
         send_ids[slot] = pr.expert % experts_per_rank;
+        // rows wider than d carry the local expert id in their tail, so one exchange moves rows and ids
+        if (send_stride > d) *reinterpret_cast<uint32_t*>(send_rows + (size_t)slot * send_stride + d) = pr.expert % experts_per_rank;
         inverse_perm[pr.token * top_k + pr.rank] = slot;
     }
     const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)pr.token * hidden_stride);
-    uint4* dst_row = reinterpret_cast<uint4*>(send_rows + (size_t)slot * d);
+    uint4* dst_row = reinterpret_cast<uint4*>(send_rows + (size_t)slot * send_stride);
     for (uint32_t i = lane; i < d / 8; i += kWarp) {
         uint4 v = __ldg(src + i);
         if (PERMUTE_K8) {
@@ -74,6 +79,15 @@ ep_pack_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride, cons
         }
         dst_row[i] = v;
     }
+}
+
+// ids[slot] = the id a row of `stride` > d elements carries in its tail (see ep_pack_kernel).
+__global__ void ep_extract_ids_kernel(const uint16_t* __restrict__ rows, uint32_t stride, uint32_t d, uint32_t slots,
+                                      uint32_t* __restrict__ ids) {
+    const uint32_t slot = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    if (slot < slots) ids[slot] = *reinterpret_cast<const uint32_t*>(rows + (size_t)slot * stride + d);
 }
 
 // y[t,d] = half(sum_r fma(w[t,r], partial[inverse[t*K+r]][d], acc) + residual[t,d]), rank order.
@@ -99,8 +113,11 @@ extern "C" {
 
 static tf_status pack_rows(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off, uint32_t hidden_stride_elements,
                            const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
-                           uint32_t experts_per_rank, uint32_t capacity, uint32_t d,
+                           uint32_t experts_per_rank, uint32_t capacity, uint32_t d, uint32_t send_stride,
                            void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm, bool permute_k8, const char* name) {
+    if (send_stride == 0) send_stride = d;
+    TF_REQUIRE(ctx, send_stride == d || (send_stride >= d + 8 && send_stride % 8 == 0), TF_ERR_INVALID_ARGUMENT,
+               "%s: the send row stride must be D, or at least D + 8 and a multiple of 8 elements (the id sits in the tail)", name);
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, hidden && routes && send_rows && send_expert_ids && inverse_perm, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
     TF_REQUIRE(ctx, experts_per_rank > 0 && num_experts % experts_per_rank == 0 && num_experts <= TF_MAX_ROUTER_EXPERTS,
@@ -117,7 +134,7 @@ static tf_status pack_rows(tf_context* ctx, void* stream, const void* hidden, ui
     auto kern = permute_k8 ? tf::ep_pack_kernel<true> : tf::ep_pack_kernel<false>;
     kern<<<(slots + per_block - 1) / per_block, tf::kPackThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const uint16_t*>(hp), hidden_stride_elements, routes->sorted_pairs, routes->per_expert_counts, n_pairs,
-        top_k, num_experts, experts_per_rank, n_dst, capacity, d, static_cast<uint16_t*>(send_rows), send_expert_ids,
+        top_k, num_experts, experts_per_rank, n_dst, capacity, d, send_stride, static_cast<uint16_t*>(send_rows), send_expert_ids,
         inverse_perm, ctx->device_error);
     return tf::check_launch(ctx, name);
 }
@@ -125,15 +142,28 @@ static tf_status pack_rows(tf_context* ctx, void* stream, const void* hidden, ui
 tf_status tf_ep_pack(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off, uint32_t hidden_stride_elements,
                      const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
                      uint32_t experts_per_rank, uint32_t capacity, uint32_t d,
-                     void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm) {
+                     void* send_rows, uint32_t* send_expert_ids, uint32_t* inverse_perm, uint32_t send_row_stride_elements) {
     return pack_rows(ctx, stream, hidden, hidden_off, hidden_stride_elements, routes, query_count, top_k, num_experts,
-                     experts_per_rank, capacity, d, send_rows, send_expert_ids, inverse_perm, false, "tf_ep_pack");
+                     experts_per_rank, capacity, d, send_row_stride_elements, send_rows, send_expert_ids, inverse_perm, false, "tf_ep_pack");
+}
+
+tf_status tf_ep_extract_ids(tf_context* ctx, void* stream, const void* rows, uint32_t row_stride_elements, uint32_t d,
+                            uint32_t slots, uint32_t* ids) {
+    const char* name = "tf_ep_extract_ids";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, rows && ids, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, row_stride_elements >= d + 2 && d % 2 == 0 && row_stride_elements % 2 == 0 && tf::aligned(rows, 4), TF_ERR_INVALID_ARGUMENT,
+               "%s: rows must be wider than D and 4-byte aligned", name);
+    if (slots == 0) return TF_OK;
+    tf::launch_pdl(tf::ep_extract_ids_kernel, dim3((slots + 255) / 256), dim3(256), 0, static_cast<cudaStream_t>(stream),
+                   static_cast<const uint16_t*>(rows), row_stride_elements, d, slots, ids);
+    return tf::check_launch(ctx, name);
 }
 
 tf_status tf_pack_sorted_rows(tf_context* ctx, void* stream, const void* hidden, uint32_t hidden_stride_elements,
                               const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
                               uint32_t d, void* x_sorted, uint32_t* row_expert_ids, uint32_t* inverse_perm) {
-    return pack_rows(ctx, stream, hidden, 0, hidden_stride_elements, routes, query_count, top_k, num_experts, num_experts, 0, d,
+    return pack_rows(ctx, stream, hidden, 0, hidden_stride_elements, routes, query_count, top_k, num_experts, num_experts, 0, d, d,
                      x_sorted, row_expert_ids, inverse_perm, true, "tf_pack_sorted_rows");
 }
 

@@ -120,17 +120,18 @@ class ExpertParallelStack:
         layer = self._c_layers[l]
         n_pairs = tokens * K
         cap = buf.capacity if buf.fixed else 0
+        # fixed-capacity rows are D + 8 elements wide: the tail carries the expert id, one exchange moves both
+        row_stride = buf.row_stride
         ctx.check(lib.tf_ep_dispatch(ctx.handle, st, C.byref(layer), _ptr(x), tokens, buf.ws.handle, self.local_experts,
-                                     cap, _ptr(buf.send_rows), _ptr(buf.send_ids), _ptr(buf.inverse)))
+                                     cap, _ptr(buf.send_rows), _ptr(buf.send_ids), _ptr(buf.inverse), row_stride))
         if buf.fixed:
             slots = self.world * cap
             recv_slots = slots
             if self.world > 1:
-                dist.all_to_all_single(buf.recv_ids[:slots], buf.send_ids[:slots], group=self.group)
-                dist.all_to_all_single(buf.recv_rows[:slots * d], buf.send_rows[:slots * d], group=self.group)
+                dist.all_to_all_single(buf.recv_rows[:slots * row_stride], buf.send_rows[:slots * row_stride], group=self.group)
                 recv_ids, recv_rows = buf.recv_ids, buf.recv_rows
             else:
-                recv_ids, recv_rows = buf.send_ids, buf.send_rows
+                recv_ids, recv_rows = buf.recv_ids, buf.send_rows
         else:
             # exact split sizes: one read-back of the per-expert counts per layer
             counts = buf.ws_counts(self.dims["num_experts"]).reshape(self.world, self.local_experts).sum(axis=1)
@@ -162,7 +163,7 @@ class ExpertParallelStack:
             ctx.check(lib.tf_ep_experts(ctx.handle, st, self.pool.ptr(l, 0), self.pool.stride, C.byref(self.pool.offsets),
                                         _ptr(recv_rows), _ptr(recv_ids), recv_slots, self.local_experts,
                                         C.byref(buf.recv_routes.c_struct), _ptr(buf.zero_weights), _ptr(buf.acts),
-                                        _ptr(buf.out_rows), d, f))
+                                        _ptr(buf.out_rows), d, f, row_stride))
         if self.world > 1:
             if buf.fixed:
                 dist.all_to_all_single(buf.back_rows[:recv_slots * d], buf.out_rows[:recv_slots * d], group=self.group)
@@ -192,7 +193,8 @@ class EPBuffers:
         send_slots = stack.world * self.capacity if fixed_capacity else n_pairs
         i16 = dict(dtype=torch.float16, device="cuda")        # NCCL has no 16-bit integer type; the rows are fp16
         i32 = dict(dtype=torch.int32, device="cuda")
-        self.send_rows = torch.zeros(send_slots * d, **i16)
+        self.row_stride = d + 8 if fixed_capacity else d        # fixed-capacity rows carry their expert id in the tail
+        self.send_rows = torch.zeros(send_slots * self.row_stride, **i16)
         self.send_ids = torch.zeros(send_slots, **i32)
         self.inverse = torch.zeros(n_pairs, **i32)
         self.back_rows = torch.zeros(send_slots * d, **i16)
@@ -208,7 +210,7 @@ class EPBuffers:
         cap = max(slots, int(self._recv_cap * 1.5))
         i16 = dict(dtype=torch.float16, device="cuda")
         i32 = dict(dtype=torch.int32, device="cuda")
-        self.recv_rows = torch.zeros(cap * self.d, **i16)
+        self.recv_rows = torch.zeros(cap * self.row_stride, **i16)
         self.recv_ids = torch.zeros(cap, **i32)
         self.out_rows = torch.zeros(cap * self.d, **i16)
         self.acts = torch.zeros(cap * self.f, **i16)
