@@ -186,7 +186,7 @@ def test_router_exact_ties_lower_index_first(tf_ctx, oracle):
     assert np.allclose(o.f16_to_f32(w16), 0.125, atol=1e-3)
 
 
-@pytest.mark.parametrize("rows", [5, 64, 200])
+@pytest.mark.parametrize("rows", [5, 64, 200, 259, 1024])     # from 256 rows: the eight-rows-per-block kernel (ragged last block at 259)
 def test_block_router_strided_rows(tf_ctx, oracle, rows):
     # Tests/TurboFieldfare/Core/Kernels/Prefill/PrefillRouterTests.swift:33-101: stride D+13, sentinel padding
     o = oracle

@@ -52,7 +52,7 @@ group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __rest
                     uint32_t* __restrict__ counters) {
     __shared__ uint32_t hist[TF_MAX_ROUTER_EXPERTS];
     __shared__ uint32_t warp_tot[kGroupThreads / kWarp];
-    __shared__ uint32_t s_offset, s_gi, s_chunk0;
+    __shared__ uint32_t s_offset;
     const uint32_t e = blockIdx.x;
     const uint32_t n = T * K;
     pdl_launch_dependents();
@@ -73,7 +73,7 @@ group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __rest
             gi += hist[i] ? 1u : 0u;
             ch += (hist[i] + kChunkTokens - 1) / kChunkTokens;
         }
-        s_offset = off; s_gi = gi; s_chunk0 = ch;
+        s_offset = off;
         const uint32_t cnt = hist[e];
         per_expert_counts[e] = cnt;
         per_expert_offsets[e] = cnt ? off : 0xFFFFFFFFu;
@@ -144,7 +144,6 @@ constexpr int kTileRows = 16;           // weight rows per MMA tile (the m of m1
 constexpr int kMaxComputeWarps = 12;    // K <= 12 * 256 = 3072 columns
 constexpr uint32_t kSpinLimit = 1u << 21;
 constexpr uint32_t kErrTimeoutCodes = 0x7F000001u;   // device error words
-constexpr uint32_t kErrTimeoutScales = 0x7F000002u;
 constexpr uint32_t kErrTimeoutPartials = 0x7F000003u;
 constexpr uint32_t kErrTimeoutRedFree = 0x7F000004u;
 constexpr uint32_t kErrTimeoutStageFree = 0x7F000005u;

@@ -260,6 +260,77 @@ router_block_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
                          out_w + (size_t)row * top_k, lane);
 }
 
+// Prefill-sized batches: one block per eight rows. Same canonical arithmetic per (row, expert) as router_row_logit,
+// but an expert's codes, scale and bias are fetched once per group for eight token rows instead of once per row:
+// the eight rows' scaled activations sit in shared memory as fp32 and every lane carries eight accumulators.
+constexpr int kTileRouterRows = 8;
+template <bool X_BF16>
+__global__ void __launch_bounds__(kBlockRouterThreads)
+router_tile_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, const uint16_t* __restrict__ B,
+                   const uint16_t* __restrict__ hidden, uint32_t hidden_stride,
+                   const uint16_t* __restrict__ eff, const uint16_t* __restrict__ per_expert_scale,
+                   const float* __restrict__ logit_bias,
+                   uint32_t* __restrict__ out_idx, uint16_t* __restrict__ out_w, float* __restrict__ out_logits,
+                   uint32_t rows, uint32_t num_experts, uint32_t d, uint32_t top_k) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    float* xf = reinterpret_cast<float*>(smem);                                   // [8][d]
+    float* scores = xf + (size_t)kTileRouterRows * d;                             // [8][num_experts]
+    const uint32_t row0 = blockIdx.x * kTileRouterRows;
+    const uint32_t nrows = rows - row0 < (uint32_t)kTileRouterRows ? rows - row0 : (uint32_t)kTileRouterRows;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (uint32_t c = threadIdx.x; c < d; c += blockDim.x) {
+        const float es = bf16_bits_to_float(eff[c]);
+#pragma unroll
+        for (int r = 0; r < kTileRouterRows; ++r) {
+            float v = 0.0f;
+            if ((uint32_t)r < nrows) {
+                const uint16_t hb = hidden[(size_t)(row0 + r) * hidden_stride + c];
+                v = __fmul_rn(X_BF16 ? bf16_bits_to_float(hb) : f16_bits_to_float(hb), es);
+            }
+            xf[(size_t)r * d + c] = v;
+        }
+    }
+    __syncthreads();
+    const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const uint32_t groups = d / kGroup;
+    for (uint32_t e = warp; e < num_experts; e += kBlockRouterThreads / kWarp) {
+        const uint8_t* Wrow = W + (size_t)e * d;
+        const uint16_t* s_row = S + (size_t)e * groups;
+        const uint16_t* b_row = B + (size_t)e * groups;
+        float acc[kTileRouterRows];
+#pragma unroll
+        for (int r = 0; r < kTileRouterRows; ++r) acc[r] = 0.0f;
+        for (uint32_t g = 0; g < groups; ++g) {
+            const uint32_t i0 = g * kGroup + lane * 2;
+            const uint32_t w = *reinterpret_cast<const uint16_t*>(Wrow + i0);      // d % 64 == 0 and 2-byte aligned rows
+            const float q0 = (float)(w & 0xFFu), q1 = (float)(w >> 8);
+            const float sc = bf16_bits_to_float(s_row[g]);
+            const float bi = bf16_bits_to_float(b_row[g]);
+#pragma unroll
+            for (int r = 0; r < kTileRouterRows; ++r) {
+                const float2 xv = *reinterpret_cast<const float2*>(xf + (size_t)r * d + i0);
+                const float p = __fmaf_rn(q1, xv.y, __fmul_rn(q0, xv.x));
+                acc[r] = __fmaf_rn(sc, p, acc[r]);
+                acc[r] = __fmaf_rn(bi, __fadd_rn(xv.x, xv.y), acc[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < kTileRouterRows; ++r) {
+            float logit = warp_sum(acc[r]);
+            if (logit_bias) logit = __fadd_rn(logit, logit_bias[e]);
+            if (lane == 0 && (uint32_t)r < nrows) {
+                scores[r * num_experts + e] = logit;
+                if (out_logits) out_logits[(size_t)(row0 + r) * num_experts + e] = logit;
+            }
+        }
+    }
+    __syncthreads();
+    if ((uint32_t)warp < nrows)          // eight warps, eight rows
+        warp_select_topk(scores + warp * num_experts, num_experts, top_k, per_expert_scale, out_idx + (size_t)(row0 + warp) * top_k,
+                         out_w + (size_t)(row0 + warp) * top_k, lane);
+}
+
 static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, const uint8_t* S, const uint8_t* B,
                                const uint8_t* hidden, tf_dtype hidden_dtype, const uint8_t* eff, const uint8_t* pes,
                                const float* logit_bias, uint32_t* out_idx, uint8_t* out_w, float* out_logits,
@@ -287,6 +358,16 @@ static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, 
         if (smem_split > 40 * 1024) TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_split));
         launch_pdl(k, grid, dim3(kSplitThreads), smem_split, st, W, Sp, Bp, hp, stride, ep, pp, logit_bias, out_idx, wp, out_logits,
                    ctx->router_logits, ctx->router_tickets, num_experts, d, top_k, a2);
+    } else if (rows >= 256 && a2 && (size_t)kTileRouterRows * (d + num_experts) * 4 <= 100 * 1024) {
+        auto k = bf ? router_tile_kernel<true> : router_tile_kernel<false>;
+        const size_t smem_tile = (size_t)kTileRouterRows * (d + num_experts) * 4;
+        static size_t configured[2] = {0, 0};
+        if (smem_tile > configured[bf ? 1 : 0]) {
+            TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tile));
+            configured[bf ? 1 : 0] = smem_tile;
+        }
+        launch_pdl(k, dim3((rows + kTileRouterRows - 1) / kTileRouterRows), dim3(kBlockRouterThreads), smem_tile, st, W, Sp, Bp, hp, stride,
+                   ep, pp, logit_bias, out_idx, wp, out_logits, rows, num_experts, d, top_k);
     } else {
         auto k = bf ? router_block_kernel<true> : router_block_kernel<false>;
         if (smem > 40 * 1024) TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
