@@ -177,4 +177,42 @@ private:
     const Context& c_;
 };
 
+// ManifestReader + PackedExpertsLayoutReader + ResidentIndexReader in one handle
+// (Infrastructure/ModelIO/ManifestReader.swift:64-152, PackedExpertsLayout.swift:57-119, ResidentIndex.swift:44-140):
+// opening validates the three documents the way the Swift codecs do; ModelError / GTurboFormatError become Error
+// with TF_ERR_FORMAT_* / TF_ERR_IO / TF_ERR_NOT_FOUND. No GPU is needed.
+class GTurboDirectory {
+public:
+    explicit GTurboDirectory(const std::string& directory) {
+        const tf_status s = tf_gturbo_open(directory.c_str(), &g_);
+        if (s != TF_OK) throw Error(s, tf_last_error(nullptr));
+    }
+    // decode(data:) of the three codecs, from memory
+    GTurboDirectory(const std::string& manifestJSON, const std::string& layoutJSON, const std::string& residentIndex) {
+        const tf_status s = tf_gturbo_parse(manifestJSON.data(), manifestJSON.size(), layoutJSON.data(), layoutJSON.size(),
+                                            residentIndex.data(), residentIndex.size(), &g_);
+        if (s != TF_OK) throw Error(s, tf_last_error(nullptr));
+    }
+    ~GTurboDirectory() { tf_gturbo_close(g_); }
+    GTurboDirectory(const GTurboDirectory&) = delete;
+    GTurboDirectory& operator=(const GTurboDirectory&) = delete;
+    const tf_gturbo* handle() const { return g_; }
+    tf_gturbo_info info() const { tf_gturbo_info i; check(tf_gturbo_get_info(g_, &i)); return i; }
+    // Model.routedExpertOffsets(layer:) (Runtime/Inference/ModelExpertIO.swift:21-40)
+    tf_expert_offsets routedExpertOffsets(uint32_t layer) const {
+        tf_expert_offsets o; check(tf_gturbo_expert_offsets(g_, layer, &o)); return o;
+    }
+    // PackedExpertsLayout.expert(layer:expert:).offset
+    uint64_t expertOffset(uint32_t layer, uint32_t expert) const {
+        uint64_t off = 0; check(tf_gturbo_expert_location(g_, layer, expert, nullptr, &off, nullptr, nullptr)); return off;
+    }
+    // Model.resident(name:) (Runtime/Inference/Model.swift:195-233)
+    tf_gturbo_tensor resident(const std::string& name) const {
+        tf_gturbo_tensor t; check(tf_gturbo_resident(g_, name.c_str(), &t)); return t;
+    }
+private:
+    static void check(tf_status s) { if (s != TF_OK) throw Error(s, tf_last_error(nullptr)); }
+    tf_gturbo* g_ = nullptr;
+};
+
 }  // namespace turbofieldfare

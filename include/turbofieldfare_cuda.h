@@ -64,7 +64,14 @@ enum {
     TF_ERR_GROUPING_RANK_OUT_OF_RANGE = 107,
     TF_ERR_GROUPING_EXPERT_OUT_OF_RANGE = 108,
     TF_ERR_GROUPING_DUPLICATE_TOKEN_RANK = 109,
-    TF_ERR_GROUPING_SORT_KEY_COUNT_MISMATCH = 110
+    TF_ERR_GROUPING_SORT_KEY_COUNT_MISMATCH = 110,
+    /* GTurboFormatError cases (Sources/TurboFieldfareFormat/GTurboFormatV1.swift:25-38) and the
+       ModelError cases the .gturbo readers throw */
+    TF_ERR_FORMAT_INVALID = 201,
+    TF_ERR_FORMAT_OVERFLOW = 202,
+    TF_ERR_FORMAT_TRUNCATED = 203,
+    TF_ERR_IO = 204,               /* ModelError.posixFailed / missingFile */
+    TF_ERR_NOT_FOUND = 205         /* ModelError.tensorNotFound */
 };
 
 typedef enum { TF_BF16 = 0, TF_FP16 = 1 } tf_dtype;
@@ -377,6 +384,7 @@ void tf_expert_pool_destroy(tf_pool* pool);
 /* Device address of a blob; NULL when out of range. */
 const void* tf_expert_pool_ptr(const tf_pool* pool, uint32_t layer, uint32_t expert);
 uint64_t tf_expert_pool_bytes(const tf_pool* pool);
+void tf_expert_pool_dims(const tf_pool* pool, uint32_t* layers_out, uint32_t* experts_out, uint64_t* stride_out);
 /* Copy one blob (as stored in packed_experts/layer_XX.bin) from HOST memory. */
 tf_status tf_expert_pool_upload(tf_pool* pool, void* stream, uint32_t layer, uint32_t expert,
                                 const void* host_blob, uint64_t bytes);
@@ -388,6 +396,54 @@ tf_status tf_fill_affine_synthetic(tf_context* ctx, void* stream, void* weights,
  * sharded); blobs are seeded by the global expert id, so shards hold the bytes of the whole pool. */
 tf_status tf_expert_pool_fill_synthetic(tf_pool* pool, void* stream, uint64_t seed, uint32_t d, uint32_t f,
                                         uint32_t global_experts, uint32_t expert_offset);
+
+/* ---- .gturbo model directory -> HBM ----
+ * Reader of the installed model format: manifest.json, packed_experts/layout.json, packed_experts/<layer files>
+ * and model_weights.bin (24-byte header, 72-byte entries, names, padding to 16 KiB, then the resident tensors).
+ * Replaces ManifestReader.decode (Infrastructure/ModelIO/ManifestReader.swift:89-152),
+ * PackedExpertsLayoutReader.decode (Infrastructure/ModelIO/PackedExpertsLayout.swift:82-119),
+ * ResidentIndexReader.load (Infrastructure/ModelIO/ResidentIndex.swift:49-140) with the validation rules of
+ * Sources/TurboFieldfareFormat (GTurboManifestV1.swift:172-268, GTurboPackedExpertsLayoutV1.swift:86-211,
+ * GTurboResidentIndexV1.swift:40-158). Architecture fields are reported, not compared with a compiled-in
+ * configuration; SHA-256 verification of the payload files is left to the installer. Errors: the status is
+ * returned and tf_last_error(NULL) holds the text. None of the parsing calls needs a GPU. */
+typedef struct tf_gturbo tf_gturbo;
+typedef struct tf_gturbo_info {
+    uint32_t version_major, version_minor;
+    uint32_t num_layers, experts_per_layer, top_k;
+    uint32_t hidden_size, moe_intermediate_size, ffn_intermediate;
+    uint32_t shared_expert_bits;      /* manifest.quant.sharedExpert.weightBits; 0 when the manifest has no quant table */
+    uint32_t reserved;
+    uint64_t expert_stride;
+    uint64_t index_size, resident_size, entry_count;   /* header of model_weights.bin */
+} tf_gturbo_info;
+/* One resident tensor; offsets are relative to the resident payload (file offset minus index_size), as in
+ * Model.resident(name:) (Runtime/Inference/Model.swift:195-233). dtype: 0 u32, 1 bf16, 2 fp16, 3 fp32. */
+typedef struct tf_gturbo_tensor {
+    uint64_t offset, size;
+    uint64_t scale_offset, scale_size;
+    uint64_t bias_offset, bias_size;
+    uint32_t shape[4];
+    uint8_t dtype;
+    uint8_t reserved[7];
+} tf_gturbo_tensor;
+tf_status tf_gturbo_open(const char* directory, tf_gturbo** out);
+/* The same from memory: the two JSON documents and (at least) the index region of model_weights.bin. */
+tf_status tf_gturbo_parse(const void* manifest_json, uint64_t manifest_bytes, const void* layout_json, uint64_t layout_bytes,
+                          const void* resident_index, uint64_t resident_index_bytes, tf_gturbo** out);
+void tf_gturbo_close(tf_gturbo* g);
+tf_status tf_gturbo_get_info(const tf_gturbo* g, tf_gturbo_info* out);
+/* Model.routedExpertOffsets (Runtime/Inference/ModelExpertIO.swift:21-40). */
+tf_status tf_gturbo_expert_offsets(const tf_gturbo* g, uint32_t layer, tf_expert_offsets* out);
+/* PackedExpertsLayout.expert(layer:expert:) by LOGICAL expert id; outputs may be NULL. */
+tf_status tf_gturbo_expert_location(const tf_gturbo* g, uint32_t layer, uint32_t expert, const char** file_out,
+                                    uint64_t* offset_out, uint64_t* size_out, uint32_t* physical_rank_out);
+tf_status tf_gturbo_resident(const tf_gturbo* g, const char* name, tf_gturbo_tensor* out);
+tf_status tf_gturbo_resident_name(const tf_gturbo* g, uint64_t position, const char** name_out);
+/* Reads every layer file and copies each blob to its logical slot of the pool; a pool that holds a shard
+ * takes experts [expert_offset, expert_offset + pool experts). Replaces the pread streamer
+ * (Infrastructure/Streaming/PreadExpertStreamer.swift:57-414). Allocates two pinned staging buffers. */
+tf_status tf_expert_pool_load_gturbo(tf_pool* pool, void* stream, const tf_gturbo* g, uint32_t expert_offset);
 
 /* ---- fused MoE block and layer stack (new entry points; the reference spreads
  * this over RealForwardRunner with two CPU round trips per layer) ---- */
@@ -402,6 +458,16 @@ typedef struct tf_moe_layer {
     tf_projection shared_gate, shared_up, shared_down;   /* 4-bit affine */
     uint32_t num_experts, d, f, fs, top_k;
 } tf_moe_layer;
+
+/* Uploads the resident payload of model_weights.bin and builds one tf_moe_layer per layer from the checkpoint's
+ * tensor names (router.proj.weight, router.scale with 1/sqrt(D) folded in as in RealForwardRunner.swift:352-376,
+ * router.per_expert_scale, mlp.{gate,up,down}_proj.weight; Runtime/Inference/Model.swift:89-188). `pool` must
+ * hold every expert of the model. Allocates device memory; the layers stay valid until the model is destroyed. */
+typedef struct tf_gturbo_model tf_gturbo_model;
+tf_status tf_gturbo_model_load(tf_context* ctx, void* stream, const tf_gturbo* g, const tf_pool* pool, tf_gturbo_model** out);
+void tf_gturbo_model_destroy(tf_gturbo_model* model);
+const tf_moe_layer* tf_gturbo_model_layers(const tf_gturbo_model* model, uint32_t* count_out);
+const void* tf_gturbo_model_resident_base(const tf_gturbo_model* model);
 
 /* Device scratch for up to max_tokens tokens (router output, routes, activations,
  * partials). Replaces the runner-owned scratch buffers

@@ -51,6 +51,20 @@ class MoELayer(C.Structure):
                 ("num_experts", u32), ("d", u32), ("f", u32), ("fs", u32), ("top_k", u32)]
 
 
+class GTurboInfo(C.Structure):
+    """tf_gturbo_info: dimensions of an opened model directory."""
+    _fields_ = [("version_major", u32), ("version_minor", u32), ("num_layers", u32), ("experts_per_layer", u32),
+                ("top_k", u32), ("hidden_size", u32), ("moe_intermediate_size", u32), ("ffn_intermediate", u32),
+                ("shared_expert_bits", u32), ("reserved", u32), ("expert_stride", u64), ("index_size", u64),
+                ("resident_size", u64), ("entry_count", u64)]
+
+
+class GTurboTensor(C.Structure):
+    """tf_gturbo_tensor: one resident tensor, offsets relative to the resident payload."""
+    _fields_ = [("offset", u64), ("size", u64), ("scale_offset", u64), ("scale_size", u64), ("bias_offset", u64),
+                ("bias_size", u64), ("shape", u32 * 4), ("dtype", C.c_uint8), ("reserved", C.c_uint8 * 7)]
+
+
 class DeviceRoutes(C.Structure):
     """tf_device_routes: device buffers of the grouped routing metadata."""
     _fields_ = [(n, vp) for n in ("sorted_pairs", "per_expert_offsets", "per_expert_counts", "groups",
@@ -99,6 +113,21 @@ SIGNATURES = {
     "tf_expert_pool_ptr": (vp, [vp, u32, u32]),
     "tf_expert_pool_bytes": (u64, [vp]),
     "tf_expert_pool_upload": (C.c_int, [vp, vp, u32, u32, vp, u64]),
+    "tf_expert_pool_dims": (None, [vp, C.POINTER(u32), C.POINTER(u32), C.POINTER(u64)]),
+    "tf_gturbo_open": (C.c_int, [C.c_char_p, C.POINTER(vp)]),
+    "tf_gturbo_parse": (C.c_int, [vp, u64, vp, u64, vp, u64, C.POINTER(vp)]),
+    "tf_gturbo_close": (None, [vp]),
+    "tf_gturbo_get_info": (C.c_int, [vp, C.POINTER(GTurboInfo)]),
+    "tf_gturbo_expert_offsets": (C.c_int, [vp, u32, C.POINTER(ExpertOffsets)]),
+    "tf_gturbo_expert_location": (C.c_int, [vp, u32, u32, C.POINTER(C.c_char_p), C.POINTER(u64), C.POINTER(u64),
+                                            C.POINTER(u32)]),
+    "tf_gturbo_resident": (C.c_int, [vp, C.c_char_p, C.POINTER(GTurboTensor)]),
+    "tf_gturbo_resident_name": (C.c_int, [vp, u64, C.POINTER(C.c_char_p)]),
+    "tf_expert_pool_load_gturbo": (C.c_int, [vp, vp, vp, u32]),
+    "tf_gturbo_model_load": (C.c_int, [vp, vp, vp, vp, C.POINTER(vp)]),
+    "tf_gturbo_model_destroy": (None, [vp]),
+    "tf_gturbo_model_layers": (C.POINTER(MoELayer), [vp, C.POINTER(u32)]),
+    "tf_gturbo_model_resident_base": (vp, [vp]),
     "tf_fill_affine_synthetic": (C.c_int, [vp, vp, vp, vp, vp, u32, u32, u32, u64]),
     "tf_expert_pool_fill_synthetic": (C.c_int, [vp, vp, u64, u32, u32, u32, u32]),
     "tf_workspace_create": (C.c_int, [vp, u32, u32, u32, u32, u32, u32, C.POINTER(vp)]),

@@ -191,6 +191,12 @@ uint64_t tf_expert_pool_bytes(const tf_pool* pool) {
     return pool ? (uint64_t)pool->layers * pool->experts * pool->stride : 0;
 }
 
+void tf_expert_pool_dims(const tf_pool* pool, uint32_t* layers_out, uint32_t* experts_out, uint64_t* stride_out) {
+    if (layers_out) *layers_out = pool ? pool->layers : 0u;
+    if (experts_out) *experts_out = pool ? pool->experts : 0u;
+    if (stride_out) *stride_out = pool ? pool->stride : 0u;
+}
+
 tf_status tf_expert_pool_upload(tf_pool* pool, void* stream, uint32_t layer, uint32_t expert,
                                 const void* host_blob, uint64_t bytes) {
     const char* name = "tf_expert_pool_upload";
