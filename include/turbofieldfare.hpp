@@ -177,6 +177,22 @@ private:
     const Context& c_;
 };
 
+// FusedPostAttentionSetup (Kernels/Fusions/FusedPostAttentionSetup.swift:26-60) and, with rows and strides,
+// PrefillPostAttentionSetup (Kernels/Prefill/Epilogues/PrefillPostAttentionSetup.swift).
+class FusedPostAttentionSetup {
+public:
+    explicit FusedPostAttentionSetup(const Context& c) : c_(c) {}
+    void encode(void* stream, void* hidden, const void* attn, void* denseX, void* routedX, void* routerX,
+                const void* postAttentionWeight, const void* preFFNWeight, const void* preFFN2Weight, uint32_t d, float eps,
+                uint32_t rows = 1, uint32_t strideElements = 0) const {
+        const uint32_t st = strideElements ? strideElements : d;
+        c_.check(tf_post_attn_setup(c_.handle(), stream, hidden, st, attn, st, denseX, st, routedX, st, routerX, st,
+                                    postAttentionWeight, preFFNWeight, preFFN2Weight, rows, d, eps));
+    }
+private:
+    const Context& c_;
+};
+
 // ManifestReader + PackedExpertsLayoutReader + ResidentIndexReader in one handle
 // (Infrastructure/ModelIO/ManifestReader.swift:64-152, PackedExpertsLayout.swift:57-119, ResidentIndex.swift:44-140):
 // opening validates the three documents the way the Swift codecs do; ModelError / GTurboFormatError become Error

@@ -557,6 +557,18 @@ tf_status tf_rmsnorm(tf_context* ctx, void* stream,
                      const void* x, uint64_t x_off, const void* weight_bf16, uint64_t weight_off,
                      void* y, uint64_t y_off, uint32_t rows, uint32_t d,
                      uint32_t stride_elements, float eps, tf_dtype act_dtype);
+/* The three-way norm in front of the feed-forward block, per row and in fp16:
+ *   hidden += rms(attn) * w_post_attn (written back); h = rms_no_scale(hidden);
+ *   dense_x = h * w_pre_ffn; routed_x = h * w_pre_ffn2; router_x = h,
+ * every stage rounded to fp16 where the reference rounds, so the result equals the chain of tf_rmsnorm calls bit
+ * for bit. Replaces FusedPostAttentionSetup.encode (rows = 1; Kernels/Fusions/FusedPostAttentionSetup.swift:26-60,
+ * Metal/Fusions/fused.metal:190-269) and PrefillPostAttentionSetup.encode with its five row strides
+ * (Kernels/Prefill/Epilogues/PrefillPostAttentionSetup.swift; Metal/Prefill/prefill.metal:178-254). */
+tf_status tf_post_attn_setup(tf_context* ctx, void* stream, void* hidden, uint32_t hidden_stride_elements,
+                             const void* attn, uint32_t attn_stride_elements, void* dense_x, uint32_t dense_stride_elements,
+                             void* routed_x, uint32_t routed_stride_elements, void* router_x, uint32_t router_stride_elements,
+                             const void* w_post_attn_bf16, const void* w_pre_ffn_bf16, const void* w_pre_ffn2_bf16,
+                             uint32_t rows, uint32_t d, float eps);
 /* hidden = (hidden + rms(h1 + rms(h2) * w2) * w) * layer_scalar with fp16
  * rounding at each stage. Replaces FusedLayerTail / PrefillLayerTail
  * (Metal/Fusions/fused.metal:271-375; Metal/Prefill/prefill.metal:255-334). */

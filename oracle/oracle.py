@@ -464,6 +464,17 @@ def layer_tail(h2_f16, h1_f16, hidden_f16, w_postffn2_bf16, w_postffn_bf16, eps=
     return hid
 
 
+def post_attn_setup(hidden_f16, attn_f16, w_post_attn_bf16, w_pre_ffn_bf16, w_pre_ffn2_bf16, eps: float = 1e-6):
+    """The primitive chain the reference's test compares its fused kernel with
+    (Tests/TurboFieldfare/Core/Kernels/Fusions/FusedPostAttentionSetupTests.swift:52-101): attn = rms(attn) * w_post;
+    hidden = half(hidden + attn); dense = rms(hidden) * w_pre; routed = rms(hidden) * w_pre2; router = rms(hidden).
+    Returns (hidden, dense, routed, router) as fp16 bits [T, D]."""
+    a = rmsnorm(attn_f16, w_post_attn_bf16, eps)
+    h = np.ascontiguousarray(hidden_f16, dtype=np.uint16).reshape(a.shape)
+    hidden = f32_to_f16((f16_to_f32(h) + f16_to_f32(a)).astype(np.float32))
+    return (hidden, rmsnorm(hidden, w_pre_ffn_bf16, eps), rmsnorm(hidden, w_pre_ffn2_bf16, eps), rmsnorm(hidden, None, eps))
+
+
 # ---------------------------------------------------------------------------
 # metrics (Tolerance/RelError.swift:7-16)
 # ---------------------------------------------------------------------------

@@ -434,6 +434,75 @@ def test_rmsnorm_and_layer_tail(tf_ctx, oracle):
     assert o.rel_error(o.f16_to_f32(from_dev(hd, np.uint16).reshape(T, D)), ref) < 3e-3
 
 
+def test_post_attention_setup_equals_the_primitive_chain_bitwise(tf_ctx, oracle):
+    """The reference's own test of this fusion (FusedPostAttentionSetupTests.swift:11-108): seed 0x9057A77E, D = 2816,
+    uniform inputs; the fused kernel equals rmsnorm -> add -> rmsnorm x 3 bit for bit. The CPU chain of the oracle
+    (another summation order) bounds it as well."""
+    import torch
+    from turbo_fieldfare_b200.kernels import FusedPostAttentionSetup, RMSNorm
+    o = oracle
+    D = 2816
+    rng = o.SplitMix64(0x9057A77E)
+    hidden = o.f32_to_f16(rng.uniform_array(-1.0, 1.0, D))
+    attn = o.f32_to_f16(rng.uniform_array(-1.0, 1.0, D))
+    w_post, w_pre, w_pre2 = (o.f32_to_bf16(rng.uniform_array(0.5, 1.5, D)) for _ in range(3))
+    dw_post, dw_pre, dw_pre2 = to_dev(w_post), to_dev(w_pre), to_dev(w_pre2)
+    rms = RMSNorm(tf_ctx)
+    # primitive chain on the device; the fp16 add on the host, as in the reference's test
+    attn_legacy = to_dev(attn.copy())
+    rms.encode(attn_legacy, dw_post, attn_legacy, 1, D)
+    torch.cuda.synchronize()
+    hidden_legacy = o.f32_to_f16((o.f16_to_f32(hidden) + o.f16_to_f32(from_dev(attn_legacy, np.uint16))).astype(np.float32))
+    hl = to_dev(hidden_legacy)
+    dense_l, routed_l, router_l = dev_zeros_u16(D), dev_zeros_u16(D), dev_zeros_u16(D)
+    rms.encode(hl, dw_pre, dense_l, 1, D)
+    rms.encode(hl, dw_pre2, routed_l, 1, D)
+    rms.encode(hl, None, router_l, 1, D)
+    hf, af = to_dev(hidden.copy()), to_dev(attn.copy())
+    dense_f, routed_f, router_f = dev_zeros_u16(D), dev_zeros_u16(D), dev_zeros_u16(D)
+    FusedPostAttentionSetup(tf_ctx).encode(hf, af, dense_f, routed_f, router_f, dw_post, dw_pre, dw_pre2, D, 1e-6)
+    torch.cuda.synchronize()
+    assert np.array_equal(from_dev(hf, np.uint16), hidden_legacy)
+    assert np.array_equal(from_dev(dense_f, np.uint16), from_dev(dense_l, np.uint16))
+    assert np.array_equal(from_dev(routed_f, np.uint16), from_dev(routed_l, np.uint16))
+    assert np.array_equal(from_dev(router_f, np.uint16), from_dev(router_l, np.uint16))
+    assert np.array_equal(from_dev(af, np.uint16), attn)                        # attn is an input only
+    ref = o.post_attn_setup(hidden, attn, w_post, w_pre, w_pre2)
+    for got, want in zip((hf, dense_f, routed_f, router_f), ref):
+        assert o.rel_error(o.f16_to_f32(from_dev(got, np.uint16)), o.f16_to_f32(want.reshape(-1))) < 2e-3
+
+
+def test_post_attention_setup_block_form_with_row_strides(tf_ctx, oracle):
+    """The prefill form: T rows, a separate stride per buffer (Metal/Prefill/prefill.metal:178-254); padding untouched."""
+    import torch
+    from turbo_fieldfare_b200.kernels import FusedPostAttentionSetup
+    o = oracle
+    rng = np.random.default_rng(41)
+    T, D = 7, 2816
+    strides = dict(hidden=D + 8, attn=D + 24, dense=D, routed=D + 16, router=D + 40)
+    def rows(stride, fill):
+        a = np.full((T, stride), fill, dtype=np.uint16)
+        a[:, :D] = o.f32_to_f16(rng.standard_normal((T, D)).astype(np.float32))
+        return a
+    hidden, attn = rows(strides["hidden"], 0x1234), rows(strides["attn"], 0x4321)
+    w = [o.f32_to_bf16((1 + 0.1 * rng.standard_normal(D)).astype(np.float32)) for _ in range(3)]
+    hd, ad = to_dev(hidden.copy()), to_dev(attn.copy())
+    outs = {k: to_dev(np.full((T, strides[k]), 0x7777, dtype=np.uint16)) for k in ("dense", "routed", "router")}
+    FusedPostAttentionSetup(tf_ctx).encode(hd, ad, outs["dense"], outs["routed"], outs["router"], to_dev(w[0]), to_dev(w[1]),
+                                           to_dev(w[2]), D, 1e-6, rows=T, hidden_stride=strides["hidden"],
+                                           attn_stride=strides["attn"], dense_stride=strides["dense"],
+                                           routed_stride=strides["routed"], router_stride=strides["router"])
+    torch.cuda.synchronize()
+    ref = o.post_attn_setup(np.ascontiguousarray(hidden[:, :D]), np.ascontiguousarray(attn[:, :D]), *w)
+    got_hidden = from_dev(hd, np.uint16).reshape(T, strides["hidden"])
+    assert o.rel_error(o.f16_to_f32(got_hidden[:, :D]), o.f16_to_f32(ref[0])) < 2e-3
+    assert np.all(got_hidden[:, D:] == 0x1234)
+    for k, want in zip(("dense", "routed", "router"), ref[1:]):
+        got = from_dev(outs[k], np.uint16).reshape(T, strides[k])
+        assert o.rel_error(o.f16_to_f32(got[:, :D]), o.f16_to_f32(want)) < 2e-3, k
+        assert np.all(got[:, D:] == 0x7777), k
+
+
 @pytest.mark.parametrize("m,n,sb", [(4096, 256, 0), (4224, 2816, 0), (5000, 2816, 1)])
 def test_int4_gemv_streaming_kernel_for_large_matrices(tf_ctx, oracle, m, n, sb):
     """Matrices of at least 4096 rows with 16-byte aligned planes take the tensor-core streaming kernel; same bound as

@@ -1,6 +1,7 @@
 // RMSNorm and the Gemma-4 layer tail, one block per row.
 // Replaces rmsnorm_bf16w / rmsnorm_no_scale (Metal/Primitives/rmsnorm.metal:32-93,153-175),
-// their block forms (Metal/Prefill/prefill.metal:54-111) and fused_layer_tail /
+// their block forms (Metal/Prefill/prefill.metal:54-111), fused_post_attn_setup /
+// prefill_post_attn_setup_block (Metal/Fusions/fused.metal:190-269; prefill.metal:178-254) and fused_layer_tail /
 // prefill_layer_tail_block (Metal/Fusions/fused.metal:271-375; prefill.metal:255-334).
 #include "tf_common.cuh"
 
@@ -87,9 +88,82 @@ layer_tail_kernel(const uint16_t* __restrict__ h2, const uint16_t* __restrict__ 
     }
 }
 
+// The three-way norm in front of the feed-forward block, fp16 with the reference's rounding points:
+//   a      = half(attn * inv(attn) * w_post_attn);  hidden = half(hidden + a)            (written back)
+//   h      = hidden * inv(hidden)
+//   dense  = half(h * w_pre_ffn);  routed = half(h * w_pre_ffn2);  router = half(h)
+// Sums of squares use the thread striding and reduction tree of rmsnorm_kernel, so the outputs equal the chain
+// rmsnorm -> add -> rmsnorm x 3 bit for bit.
+__global__ void __launch_bounds__(kNormThreads)
+post_attn_setup_kernel(uint16_t* __restrict__ hidden, uint32_t hidden_stride, const uint16_t* __restrict__ attn,
+                       uint32_t attn_stride, uint16_t* __restrict__ dense_x, uint32_t dense_stride,
+                       uint16_t* __restrict__ routed_x, uint32_t routed_stride, uint16_t* __restrict__ router_x,
+                       uint32_t router_stride, const uint16_t* __restrict__ w_post_attn,
+                       const uint16_t* __restrict__ w_pre_ffn, const uint16_t* __restrict__ w_pre_ffn2,
+                       uint32_t d, float eps) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    __half* hid = reinterpret_cast<__half*>(smem);
+    __shared__ float red[kNormThreads / kWarp];
+    uint16_t* hr = hidden + (size_t)blockIdx.x * hidden_stride;
+    const uint16_t* ar = attn + (size_t)blockIdx.x * attn_stride;
+    float acc = 0.0f;
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+        const float v = f16_bits_to_float(ar[i]);
+        acc = fmaf(v, v, acc);
+    }
+    const float attn_inv = rsqrtf(block_sum(acc, red) / (float)d + eps);
+    acc = 0.0f;
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+        const __half a = __float2half_rn(f16_bits_to_float(ar[i]) * attn_inv * bf16_bits_to_float(w_post_attn[i]));
+        const __half h = __float2half_rn(f16_bits_to_float(hr[i]) + __half2float(a));
+        hid[i] = h;
+        hr[i] = __half_as_ushort(h);
+        const float hf = __half2float(h);
+        acc = fmaf(hf, hf, acc);
+    }
+    const float hidden_inv = rsqrtf(block_sum(acc, red) / (float)d + eps);
+    uint16_t* dr = dense_x + (size_t)blockIdx.x * dense_stride;
+    uint16_t* rr = routed_x + (size_t)blockIdx.x * routed_stride;
+    uint16_t* qr = router_x + (size_t)blockIdx.x * router_stride;
+    for (uint32_t i = threadIdx.x; i < d; i += blockDim.x) {
+        const float h = __half2float(hid[i]) * hidden_inv;
+        dr[i] = __half_as_ushort(__float2half_rn(h * bf16_bits_to_float(w_pre_ffn[i])));
+        rr[i] = __half_as_ushort(__float2half_rn(h * bf16_bits_to_float(w_pre_ffn2[i])));
+        qr[i] = __half_as_ushort(__float2half_rn(h));
+    }
+}
+
 }  // namespace tf
 
 extern "C" {
+
+tf_status tf_post_attn_setup(tf_context* ctx, void* stream, void* hidden, uint32_t hidden_stride_elements,
+                             const void* attn, uint32_t attn_stride_elements, void* dense_x, uint32_t dense_stride_elements,
+                             void* routed_x, uint32_t routed_stride_elements, void* router_x, uint32_t router_stride_elements,
+                             const void* w_post_attn_bf16, const void* w_pre_ffn_bf16, const void* w_pre_ffn2_bf16,
+                             uint32_t rows, uint32_t d, float eps) {
+    const char* name = "tf_post_attn_setup";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, hidden && attn && dense_x && routed_x && router_x && w_post_attn_bf16 && w_pre_ffn_bf16 && w_pre_ffn2_bf16,
+               TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, d > 0 && hidden_stride_elements >= d && attn_stride_elements >= d && dense_stride_elements >= d &&
+                        routed_stride_elements >= d && router_stride_elements >= d,
+               TF_ERR_INVALID_ARGUMENT, "%s: a row stride is smaller than D", name);
+    // FusedPostAttentionSetup.swift:40 requires d <= 4096 (two fp16 rows in threadgroup memory); one row is kept here
+    TF_REQUIRE(ctx, (size_t)d * 2 <= 96 * 1024, TF_ERR_UNSUPPORTED, "%s: D too large", name);
+    TF_REQUIRE(ctx, tf::aligned(hidden, 2) && tf::aligned(attn, 2) && tf::aligned(dense_x, 2) && tf::aligned(routed_x, 2) &&
+                        tf::aligned(router_x, 2), TF_ERR_ALIGNMENT, "%s: rows must be 2-byte aligned", name);
+    if (rows == 0) return TF_OK;
+    const size_t smem = (size_t)d * 2;
+    if (smem > 48 * 1024)
+        TF_CUDA(ctx, cudaFuncSetAttribute(tf::post_attn_setup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    tf::post_attn_setup_kernel<<<rows, tf::kNormThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<uint16_t*>(hidden), hidden_stride_elements, static_cast<const uint16_t*>(attn), attn_stride_elements,
+        static_cast<uint16_t*>(dense_x), dense_stride_elements, static_cast<uint16_t*>(routed_x), routed_stride_elements,
+        static_cast<uint16_t*>(router_x), router_stride_elements, static_cast<const uint16_t*>(w_post_attn_bf16),
+        static_cast<const uint16_t*>(w_pre_ffn_bf16), static_cast<const uint16_t*>(w_pre_ffn2_bf16), d, eps);
+    return tf::check_launch(ctx, name);
+}
 
 tf_status tf_rmsnorm(tf_context* ctx, void* stream, const void* x, uint64_t x_off, const void* weight_bf16,
                      uint64_t weight_off, void* y, uint64_t y_off, uint32_t rows, uint32_t d,

@@ -306,6 +306,26 @@ class RMSNorm:
                                      eps, act_dtype))
 
 
+class FusedPostAttentionSetup:
+    """``FusedPostAttentionSetup`` / ``PrefillPostAttentionSetup`` (Kernels/Fusions/FusedPostAttentionSetup.swift:26-60;
+    Kernels/Prefill/Epilogues/PrefillPostAttentionSetup.swift): the three-way norm in front of the feed-forward block."""
+
+    def __init__(self, context: TurboContext):
+        self.context = context
+
+    def encode(self, hidden, attn, dense_x, routed_x, router_x, post_attention_weight, pre_ffn_weight, pre_ffn2_weight,
+               d: int, eps: float = 1e-6, *, rows: int = 1, hidden_stride: int | None = None, attn_stride: int | None = None,
+               dense_stride: int | None = None, routed_stride: int | None = None, router_stride: int | None = None,
+               stream=None):
+        ctx = self.context
+        st = lambda v: d if v is None else v
+        ctx.check(ctx.lib.tf_post_attn_setup(ctx.handle, _stream(stream), _ptr(hidden), st(hidden_stride), _ptr(attn),
+                                             st(attn_stride), _ptr(dense_x), st(dense_stride), _ptr(routed_x),
+                                             st(routed_stride), _ptr(router_x), st(router_stride),
+                                             _ptr(post_attention_weight), _ptr(pre_ffn_weight), _ptr(pre_ffn2_weight),
+                                             rows, d, eps))
+
+
 class FusedLayerTail:
     """``FusedLayerTail`` / ``PrefillLayerTail`` (Metal/Fusions/fused.metal:271-375)."""
 
