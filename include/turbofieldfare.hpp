@@ -177,6 +177,20 @@ private:
     const Context& c_;
 };
 
+// LMHeadChainInt4 (Kernels/Fusions/LMHeadChainInt4.swift:53-135): final RMSNorm, tied int4 LM head, greedy token.
+class LMHeadChainInt4 {
+public:
+    explicit LMHeadChainInt4(const Context& c) : c_(c) {}
+    void encodeGreedyDecode(void* stream, BufferRef hidden, BufferRef normWeight, BufferRef weights, BufferRef scales,
+                            BufferRef biases, uint32_t* outToken, uint32_t d, uint32_t vocab, float rmsEps = 1e-6f) const {
+        c_.check(tf_lm_head_greedy_int4(c_.handle(), stream, hidden.buffer, hidden.offset, normWeight.buffer, normWeight.offset,
+                                        weights.buffer, weights.offset, scales.buffer, scales.offset, biases.buffer,
+                                        biases.offset, outToken, d, vocab, rmsEps));
+    }
+private:
+    const Context& c_;
+};
+
 // FusedPostAttentionSetup (Kernels/Fusions/FusedPostAttentionSetup.swift:26-60) and, with rows and strides,
 // PrefillPostAttentionSetup (Kernels/Prefill/Epilogues/PrefillPostAttentionSetup.swift).
 class FusedPostAttentionSetup {

@@ -549,6 +549,20 @@ tf_status tf_ep_combine(tf_context* ctx, void* stream, const void* returned_rows
                         const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
                         void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d);
 
+/* ---- greedy LM head ---- */
+/* out_token = argmax_row deq4(W[vocab, d]) . half(rms(hidden) * norm_weight): RMSNorm to fp16, the int4 GEMV with
+ * UNROUNDED fp32 logits, the maximum over the finite ones, ties to the lowest row, 0 when none is finite.
+ * Replaces LMHeadChainInt4.encodeGreedyDecode (Kernels/Fusions/LMHeadChainInt4.swift:53-135) and
+ * lm_head_greedy_int4_rows_chunk_raw / lm_head_greedy_int4_rows_reduce (Metal/Sampling/logit.metal:688-787).
+ * hidden_off selects a row of a larger buffer, as hiddenOffset does. Scales and biases are bf16. The context owns the
+ * scratch (normed row, fp32 logits), as the Swift wrapper does; it grows, with an allocation, the first time a
+ * larger d or vocab is seen. Calls on one context must not overlap on different streams. */
+tf_status tf_lm_head_greedy_int4(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off,
+                                 const void* norm_weight_bf16, uint64_t norm_off,
+                                 const void* weights, uint64_t weights_off, const void* scales, uint64_t scales_off,
+                                 const void* biases, uint64_t biases_off, uint32_t* out_token,
+                                 uint32_t d, uint32_t vocab, float rms_eps);
+
 /* ---- norms ---- */
 /* y = half(x * rsqrt(mean(x^2) + eps) * w_bf16); weight NULL = no-scale form.
  * Replaces RMSNorm.encode and the block form PrefillRMSNorm

@@ -475,6 +475,19 @@ def post_attn_setup(hidden_f16, attn_f16, w_post_attn_bf16, w_pre_ffn_bf16, w_pr
     return (hidden, rmsnorm(hidden, w_pre_ffn_bf16, eps), rmsnorm(hidden, w_pre_ffn2_bf16, eps), rmsnorm(hidden, None, eps))
 
 
+def lm_head_greedy(hidden_f16, norm_weight_bf16, mat: AffineMatrix, eps: float = 1e-6):
+    """CPU reference of the greedy LM head (Tests/TurboFieldfare/Core/Kernels/Fusions/LMHeadChainInt4Tests.swift:10-41):
+    RMSNorm rounded to fp16, dequantise-then-dot per row in fp32, first strict maximum (a NaN or -inf never wins;
+    index 0 when nothing does). Returns (token, logits f32)."""
+    normed = f16_to_f32(rmsnorm(hidden_f16, norm_weight_bf16, eps)).reshape(-1)
+    logits = gemv_ref(mat, normed, acc="f32")
+    best_v, best_i = -np.inf, 0
+    finite = np.where(np.isnan(logits), -np.inf, logits)
+    if finite.size and np.max(finite) > -np.inf:
+        best_i = int(np.argmax(finite))          # first occurrence of the maximum = strict '>' scan
+    return best_i, logits
+
+
 # ---------------------------------------------------------------------------
 # metrics (Tolerance/RelError.swift:7-16)
 # ---------------------------------------------------------------------------

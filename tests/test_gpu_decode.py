@@ -434,6 +434,72 @@ def test_rmsnorm_and_layer_tail(tf_ctx, oracle):
     assert o.rel_error(o.f16_to_f32(from_dev(hd, np.uint16).reshape(T, D)), ref) < 3e-3
 
 
+def _lm_head_gpu(tf_ctx, o, hidden16, norm, mat, d, v, hidden_offset=0):
+    import torch
+    from turbo_fieldfare_b200.kernels import LMHeadChainInt4
+    out = torch.full((1,), 0xFFFF, dtype=torch.int32, device="cuda")
+    LMHeadChainInt4(tf_ctx).encode_greedy_decode(to_dev(hidden16), to_dev(norm), to_dev(mat.packed), to_dev(mat.scales),
+                                                 to_dev(mat.biases), out, d, v, hidden_offset=hidden_offset)
+    torch.cuda.synchronize()
+    return int(out.cpu().numpy().view(np.uint32)[0])
+
+
+def _constant_rows(o, values, d):
+    return o.quantize_rows(np.repeat(np.asarray(values, dtype=np.float32)[:, None], d, axis=1), 4)
+
+
+def test_lm_head_greedy_reference_cases(tf_ctx, oracle):
+    """The five cases of Tests/TurboFieldfare/Core/Kernels/Fusions/LMHeadChainInt4Tests.swift:113-224."""
+    o = oracle
+    d, v = 64, 1024
+    # raw greedy == CPU reference, seed 0x1A4E4EAD20260603
+    rng = o.SplitMix64(0x1A4E4EAD20260603)
+    hidden = o.f32_to_f16(rng.uniform_array(-1, 1, d))
+    norm = o.f32_to_bf16(rng.uniform_array(0.5, 1.5, d))
+    mat = o.quantize_rows(np.stack([rng.uniform_array(-1, 1, d) for _ in range(v)]), 4)
+    want, _ = o.lm_head_greedy(hidden, norm, mat)
+    assert _lm_head_gpu(tf_ctx, o, hidden, norm, mat, d, v) == want
+    ones = o.f32_to_bf16(np.ones(d, np.float32))
+    # every candidate invalid -> token 0
+    nan_hidden = np.full(d, 0x7E00, dtype=np.uint16)
+    assert _lm_head_gpu(tf_ctx, o, nan_hidden, ones, _constant_rows(o, [0.25] * v, d), d, v) == 0
+    # vocabulary sizes
+    for vv in (1024, 2048, 4096):
+        target = vv - 3
+        hid = o.f32_to_f16(np.array([0.25 + (i % 7) * 0.01 for i in range(d)], np.float32))
+        rows = _constant_rows(o, [1.0 if r == target else -0.5 for r in range(vv)], d)
+        want, _ = o.lm_head_greedy(hid, ones, rows)
+        assert want == target
+        assert _lm_head_gpu(tf_ctx, o, hid, ones, rows, d, vv) == want
+    # ties resolve to the lowest index
+    hid = o.f32_to_f16(np.array([0.2 + (i % 5) * 0.02 for i in range(d)], np.float32))
+    rows = _constant_rows(o, [1.0 if r in (17, 311) else -0.25 for r in range(v)], d)
+    assert _lm_head_gpu(tf_ctx, o, hid, ones, rows, d, v) == 17
+    # the hidden offset selects a row of a strided buffer
+    stride, selected, target = d + 16, 3, 777
+    buf = np.zeros((5, stride), dtype=np.float32)
+    for r in range(5):
+        buf[r, :d] = [0.25 + (i % 7) * 0.01 if r == selected else -0.4 - (i % 5) * 0.01 for i in range(d)]
+    rows = _constant_rows(o, [1.0 if r == target else -0.25 for r in range(v)], d)
+    assert _lm_head_gpu(tf_ctx, o, o.f32_to_f16(buf), ones, rows, d, v, hidden_offset=selected * stride * 2) == target
+
+
+def test_lm_head_greedy_streaming_shape(tf_ctx, oracle):
+    """A vocabulary large enough for the tensor-core streaming GEMV (>= 4096 rows, D = 2816), ragged last block; the
+    context's scratch grows between calls. The chosen row must hold the oracle's maximum up to fp32 summation order."""
+    o = oracle
+    d = 2816
+    rng = np.random.default_rng(77)
+    for v in (5000, 16384 + 40):
+        mat = config0_matrix(o, v, d, rng)
+        hidden = o.f32_to_f16(rng.standard_normal(d).astype(np.float32))
+        norm = o.f32_to_bf16((1 + 0.1 * rng.standard_normal(d)).astype(np.float32))
+        want, logits = o.lm_head_greedy(hidden, norm, mat)
+        got = _lm_head_gpu(tf_ctx, o, hidden, norm, mat, d, v)
+        assert got == want or abs(float(logits[got]) - float(logits[want])) <= 1e-5 * max(1.0, abs(float(logits[want]))), (got, want)
+    assert tf_ctx.device_status() == 0
+
+
 def test_post_attention_setup_equals_the_primitive_chain_bitwise(tf_ctx, oracle):
     """The reference's own test of this fusion (FusedPostAttentionSetupTests.swift:11-108): seed 0x9057A77E, D = 2816,
     uniform inputs; the fused kernel equals rmsnorm -> add -> rmsnorm x 3 bit for bit. The CPU chain of the oracle

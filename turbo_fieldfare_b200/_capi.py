@@ -151,6 +151,7 @@ SIGNATURES = {
     "tf_ep_extract_ids": (C.c_int, [vp, vp, vp, u32, u32, u32, vp]),
     "tf_ep_combine": (C.c_int, [vp, vp, vp, vp, vp, vp, u32, vp, u32, u32, u32, u32]),
     "tf_rmsnorm": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, u32, u32, u32, f32, C.c_int]),
+    "tf_lm_head_greedy_int4": (C.c_int, [vp, vp, vp, u64, vp, u64, *_PLANES, vp, u32, u32, f32]),
     "tf_post_attn_setup": (C.c_int, [vp, vp, vp, u32, vp, u32, vp, u32, vp, u32, vp, u32, vp, vp, vp, u32, u32, f32]),
     "tf_layer_tail": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, f32, f32]),
 }

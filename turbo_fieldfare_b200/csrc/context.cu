@@ -99,6 +99,9 @@ void tf_context_destroy(tf_context* ctx) {
     if (ctx->device_error) cudaFree(ctx->device_error);
     if (ctx->qmm_groups) cudaFree(ctx->qmm_groups);
     if (ctx->qmm_totals) cudaFree(ctx->qmm_totals);
+    if (ctx->lm_x) cudaFree(ctx->lm_x);
+    if (ctx->lm_logits) cudaFree(ctx->lm_logits);
+    if (ctx->lm_best) cudaFree(ctx->lm_best);
     if (ctx->side_stream) cudaStreamDestroy(ctx->side_stream);
     if (ctx->fork_event) cudaEventDestroy(ctx->fork_event);
     if (ctx->join_event) cudaEventDestroy(ctx->join_event);

@@ -12,15 +12,16 @@ namespace tf {
 // gemv_mma.cu: the tensor-core streaming kernel for large, aligned matrices
 bool gemv_mma_eligible(const void* W, const void* S, const void* B, const void* x, uint32_t m, uint32_t n);
 tf_status launch_gemv_mma(tf_context* ctx, void* stream, const uint8_t* W, const uint16_t* S, const uint16_t* B,
-                          const uint16_t* x, uint16_t* y, uint32_t m, uint32_t n, bool sb_fp16, const char* name);
+                          const uint16_t* x, void* y, bool out_f32, uint32_t m, uint32_t n, bool sb_fp16, const char* name);
 
 constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = kGemvThreads / kWarp;
 
-template <int BITS, bool SB_FP16, bool A16>
+// OUT_F32: the row sums are stored as fp32 (the greedy LM head compares unrounded logits).
+template <int BITS, bool SB_FP16, bool A16, bool OUT_F32>
 __global__ void __launch_bounds__(kGemvThreads)
 affine_gemv_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, const uint16_t* __restrict__ B,
-                   const uint16_t* __restrict__ x, uint16_t* __restrict__ y, uint32_t m, uint32_t n, bool a4) {
+                   const uint16_t* __restrict__ x, void* __restrict__ y, uint32_t m, uint32_t n, bool a4) {
     extern __shared__ __align__(16) uint8_t smem[];
     uint16_t* xs = reinterpret_cast<uint16_t*>(smem);
     float* xsum16 = xsum_ptr(xs, (int)n);
@@ -41,11 +42,14 @@ affine_gemv_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S
             acc = int8_row_partial<SB_FP16, false>(Wrow, s_row, b_row, xs, (int)n, lane, a4);
         }
         acc = warp_sum(acc);
-        if (lane == 0) y[row] = __half_as_ushort(__float2half_rn(acc));
+        if (lane == 0) {
+            if constexpr (OUT_F32) static_cast<float*>(y)[row] = acc;
+            else static_cast<uint16_t*>(y)[row] = __half_as_ushort(__float2half_rn(acc));
+        }
     }
 }
 
-template <int BITS>
+template <int BITS, bool OUT_F32 = false>
 static tf_status launch_gemv(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off,
                              const void* scales, uint64_t scales_off, const void* biases, uint64_t biases_off,
                              const void* x, uint64_t x_off, void* y, uint64_t y_off, uint32_t m, uint32_t n,
@@ -62,12 +66,11 @@ static tf_status launch_gemv(tf_context* ctx, void* stream, const void* weights,
     uint8_t* yp = byte_ptr(y, y_off);
     if (BITS == 4)
         TF_REQUIRE(ctx, aligned(W, 2), TF_ERR_ALIGNMENT, "%s: weightsOffset must be even", name);
-    TF_REQUIRE(ctx, aligned(S, 2) && aligned(Bp, 2) && aligned(xp, 2) && aligned(yp, 2), TF_ERR_ALIGNMENT,
+    TF_REQUIRE(ctx, aligned(S, 2) && aligned(Bp, 2) && aligned(xp, 2) && aligned(yp, OUT_F32 ? 4 : 2), TF_ERR_ALIGNMENT,
                "%s: scale/bias/x/y planes must be 2-byte aligned", name);
     if (BITS == 4 && gemv_mma_eligible(W, S, Bp, xp, m, n))
         return launch_gemv_mma(ctx, stream, W, reinterpret_cast<const uint16_t*>(S), reinterpret_cast<const uint16_t*>(Bp),
-                               reinterpret_cast<const uint16_t*>(xp), reinterpret_cast<uint16_t*>(yp), m, n,
-                               sb_dtype == TF_FP16, name);
+                               reinterpret_cast<const uint16_t*>(xp), yp, OUT_F32, m, n, sb_dtype == TF_FP16, name);
     const size_t smem = stage_x_bytes((int)n);
     TF_REQUIRE(ctx, smem <= 96 * 1024, TF_ERR_UNSUPPORTED, "%s: N=%u too large for the staged-x kernel", name, n);
 
@@ -81,12 +84,12 @@ static tf_status launch_gemv(tf_context* ctx, void* stream, const void* weights,
 
 #define TF_GEMV_LAUNCH(SB, A)                                                                          \
     do {                                                                                               \
-        auto k = affine_gemv_kernel<BITS, SB, A>;                                                      \
+        auto k = affine_gemv_kernel<BITS, SB, A, OUT_F32>;                                                    \
         if (smem > 48 * 1024) TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
         k<<<grid, kGemvThreads, smem, st>>>(W, reinterpret_cast<const uint16_t*>(S),                   \
                                             reinterpret_cast<const uint16_t*>(Bp),                      \
                                             reinterpret_cast<const uint16_t*>(xp),                      \
-                                            reinterpret_cast<uint16_t*>(yp), m, n, a4);                 \
+                                            static_cast<void*>(yp), m, n, a4);                          \
     } while (0)
 
     if (BITS == 4 && a16) {
@@ -98,9 +101,97 @@ static tf_status launch_gemv(tf_context* ctx, void* stream, const void* weights,
     return check_launch(ctx, name);
 }
 
+// ---------------------------------------------------------------------------
+// Greedy LM head: argmax over the finite fp32 logits, ties to the lowest row
+// ---------------------------------------------------------------------------
+// A finite float as an unsigned key that orders like the float (every finite value maps above zero).
+__device__ __forceinline__ uint32_t ordered_key(float v) {
+    if (v == 0.0f) v = 0.0f;                        // -0 and +0 compare equal in the reference's reduction
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+constexpr int kArgmaxThreads = 256;
+
+// best = max over rows of (ordered logit << 32 | ~row): the larger logit wins, then the lower row.
+__global__ void __launch_bounds__(kArgmaxThreads)
+lm_head_argmax_kernel(const float* __restrict__ logits, uint32_t vocab, unsigned long long* __restrict__ best) {
+    unsigned long long mine = 0ull;                 // 0 = no finite candidate
+    for (uint32_t r = blockIdx.x * blockDim.x + threadIdx.x; r < vocab; r += gridDim.x * blockDim.x) {
+        const float z = logits[r];
+        if (isfinite(z)) {
+            const unsigned long long k = ((unsigned long long)ordered_key(z) << 32) | (unsigned long long)(~r);
+            mine = k > mine ? k : mine;
+        }
+    }
+#pragma unroll
+    for (int o = kWarp / 2; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(kFullMask, mine, o);
+        mine = other > mine ? other : mine;
+    }
+    __shared__ unsigned long long per_warp[kArgmaxThreads / kWarp];
+    if (threadIdx.x % kWarp == 0) per_warp[threadIdx.x / kWarp] = mine;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kArgmaxThreads / kWarp; ++w) mine = per_warp[w] > mine ? per_warp[w] : mine;
+        if (mine) atomicMax(best, mine);
+    }
+}
+
+// Decodes the winner (0 when no logit was finite, lm_head_greedy_int4_rows_reduce's fallback) and clears the
+// scratch word for the next call.
+__global__ void lm_head_finish_kernel(unsigned long long* __restrict__ best, uint32_t* __restrict__ out_token) {
+    const unsigned long long k = *best;
+    *out_token = k ? ~(uint32_t)(k & 0xFFFFFFFFull) : 0u;
+    *best = 0ull;
+}
+
 }  // namespace tf
 
 extern "C" {
+
+tf_status tf_lm_head_greedy_int4(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off,
+                                 const void* norm_weight_bf16, uint64_t norm_off,
+                                 const void* weights, uint64_t weights_off, const void* scales, uint64_t scales_off,
+                                 const void* biases, uint64_t biases_off, uint32_t* out_token,
+                                 uint32_t d, uint32_t vocab, float rms_eps) {
+    const char* name = "tf_lm_head_greedy_int4";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, hidden && norm_weight_bf16 && weights && scales && biases && out_token, TF_ERR_INVALID_ARGUMENT,
+               "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, d > 0 && vocab > 0, TF_ERR_INVALID_ARGUMENT, "%s: d and vocab must be positive", name);
+    TF_REQUIRE(ctx, d % tf::kGroup == 0, TF_ERR_INVALID_ARGUMENT, "%s: d must be a multiple of %d", name, tf::kGroup);
+    TF_REQUIRE(ctx, weights_off % 2 == 0, TF_ERR_ALIGNMENT, "%s: weightsOffset must be even", name);
+    TF_REQUIRE(ctx, tf::aligned(out_token, 4), TF_ERR_ALIGNMENT, "%s: outToken must be 4-byte aligned", name);
+    // scratch owned by the context; growing it allocates (and so cannot happen inside a stream capture)
+    if (ctx->lm_best == nullptr) {
+        TF_CUDA(ctx, cudaMalloc(&ctx->lm_best, sizeof(unsigned long long)));
+        TF_CUDA(ctx, cudaMemset(ctx->lm_best, 0, sizeof(unsigned long long)));
+    }
+    if (d > ctx->lm_x_capacity) {
+        if (ctx->lm_x) { TF_CUDA(ctx, cudaFree(ctx->lm_x)); ctx->lm_x = nullptr; ctx->lm_x_capacity = 0; }
+        TF_CUDA(ctx, cudaMalloc(&ctx->lm_x, (size_t)d * 2));
+        ctx->lm_x_capacity = d;
+    }
+    if (vocab > ctx->lm_logits_capacity) {
+        if (ctx->lm_logits) { TF_CUDA(ctx, cudaFree(ctx->lm_logits)); ctx->lm_logits = nullptr; ctx->lm_logits_capacity = 0; }
+        TF_CUDA(ctx, cudaMalloc(&ctx->lm_logits, (size_t)vocab * 4));
+        ctx->lm_logits_capacity = vocab;
+    }
+    tf_status st = tf_rmsnorm(ctx, stream, hidden, hidden_off, norm_weight_bf16, norm_off, ctx->lm_x, 0, 1, d, d, rms_eps, TF_FP16);
+    if (st != TF_OK) return st;
+    st = tf::launch_gemv<4, true>(ctx, stream, weights, weights_off, scales, scales_off, biases, biases_off, ctx->lm_x, 0,
+                                  ctx->lm_logits, 0, vocab, d, TF_BF16, name);
+    if (st != TF_OK) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const uint32_t want = (vocab + tf::kArgmaxThreads - 1) / tf::kArgmaxThreads;
+    const uint32_t grid = want < (uint32_t)ctx->sm_count ? want : (uint32_t)ctx->sm_count;
+    tf::lm_head_argmax_kernel<<<grid, tf::kArgmaxThreads, 0, s>>>(ctx->lm_logits, vocab, ctx->lm_best);
+    st = tf::check_launch(ctx, name);
+    if (st != TF_OK) return st;
+    tf::lm_head_finish_kernel<<<1, 1, 0, s>>>(ctx->lm_best, out_token);
+    return tf::check_launch(ctx, name);
+}
 
 tf_status tf_int4_gemv(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off,
                        const void* scales, uint64_t scales_off, const void* biases, uint64_t biases_off,

@@ -43,10 +43,10 @@ __device__ __forceinline__ uint2 gm_ldg64(const uint8_t* p) {
 
 // Shared memory: B fragments of x [ng][4 lanes t][8 words], group sums [ng], scale and bias planes of the block's
 // 128 rows [128][ng] each.
-template <bool SB_FP16>
+template <bool SB_FP16, bool OUT_F32>
 __global__ void __launch_bounds__(kGmThreads)
 gemv_mma_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, const uint16_t* __restrict__ B,
-                const uint16_t* __restrict__ x, uint16_t* __restrict__ y, uint32_t m, uint32_t n) {
+                const uint16_t* __restrict__ x, void* __restrict__ y, uint32_t m, uint32_t n) {
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t ng = n / kGroup;
     uint32_t* xfrag = reinterpret_cast<uint32_t*>(smem);                       // ng * 32 words
@@ -163,8 +163,13 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, c
         }
     }
     if (t == 0) {
-        if (r0 < m) y[r0] = __half_as_ushort(__float2half_rn(acc0));
-        if (r1 < m) y[r1] = __half_as_ushort(__float2half_rn(acc1));
+        if constexpr (OUT_F32) {       // unrounded row sums (the greedy LM head compares them as fp32)
+            if (r0 < m) static_cast<float*>(y)[r0] = acc0;
+            if (r1 < m) static_cast<float*>(y)[r1] = acc1;
+        } else {
+            if (r0 < m) static_cast<uint16_t*>(y)[r0] = __half_as_ushort(__float2half_rn(acc0));
+            if (r1 < m) static_cast<uint16_t*>(y)[r1] = __half_as_ushort(__float2half_rn(acc1));
+        }
     }
 }
 
@@ -180,13 +185,16 @@ bool gemv_mma_eligible(const void* W, const void* S, const void* B, const void* 
 }
 
 tf_status launch_gemv_mma(tf_context* ctx, void* stream, const uint8_t* W, const uint16_t* S, const uint16_t* B,
-                          const uint16_t* x, uint16_t* y, uint32_t m, uint32_t n, bool sb_fp16, const char* name) {
+                          const uint16_t* x, void* y, bool out_f32, uint32_t m, uint32_t n, bool sb_fp16, const char* name) {
     const size_t smem = gemv_mma_smem_bytes(n);
-    auto k = sb_fp16 ? gemv_mma_kernel<true> : gemv_mma_kernel<false>;
-    static size_t configured[2] = {0, 0};
-    if (smem > configured[sb_fp16 ? 1 : 0]) {
+    const int which = (sb_fp16 ? 1 : 0) + (out_f32 ? 2 : 0);
+    void (*k)(const uint8_t*, const uint16_t*, const uint16_t*, const uint16_t*, void*, uint32_t, uint32_t) =
+        which == 0 ? gemv_mma_kernel<false, false> : which == 1 ? gemv_mma_kernel<true, false>
+        : which == 2 ? gemv_mma_kernel<false, true> : gemv_mma_kernel<true, true>;
+    static size_t configured[4] = {0, 0, 0, 0};
+    if (smem > configured[which]) {
         TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured[sb_fp16 ? 1 : 0] = smem;
+        configured[which] = smem;
     }
     k<<<(m + kGmRows - 1) / kGmRows, kGmThreads, smem, static_cast<cudaStream_t>(stream)>>>(W, S, B, x, y, m, n);
     return check_launch(ctx, name);

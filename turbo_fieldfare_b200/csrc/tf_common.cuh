@@ -49,6 +49,13 @@ struct tf_context {
     cudaEvent_t fork_event = nullptr, join_event = nullptr;
     // Block forwards of at least this many tokens run their expert GEMMs on the tcgen05 tensor cores.
     uint32_t tensorcore_min_tokens = 256;
+    // Scratch of the greedy LM head, like the normed-row and row-summary buffers the reference's wrapper owns
+    // (Kernels/Fusions/LMHeadChainInt4.swift:26-51); grown on demand by tf_lm_head_greedy_int4.
+    uint16_t* lm_x = nullptr;               // fp16 [lm_x_capacity]
+    uint32_t lm_x_capacity = 0;
+    float* lm_logits = nullptr;             // fp32 [lm_logits_capacity]
+    uint32_t lm_logits_capacity = 0;
+    unsigned long long* lm_best = nullptr;  // packed (ordered logit, ~row); zero between calls
 };
 
 namespace tf {

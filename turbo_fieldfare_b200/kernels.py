@@ -306,6 +306,23 @@ class RMSNorm:
                                      eps, act_dtype))
 
 
+class LMHeadChainInt4:
+    """``LMHeadChainInt4.encodeGreedyDecode`` (Kernels/Fusions/LMHeadChainInt4.swift:53-135): final RMSNorm, tied int4
+    LM head, greedy token. ``out_token`` is a device uint32."""
+
+    def __init__(self, context: TurboContext):
+        self.context = context
+
+    def encode_greedy_decode(self, hidden, norm_weight, weights, scales, biases, out_token, d: int, vocab: int,
+                             rms_eps: float = 1e-6, *, hidden_offset=0, norm_offset=0, weights_offset=0, scales_offset=0,
+                             biases_offset=0, stream=None):
+        ctx = self.context
+        ctx.check(ctx.lib.tf_lm_head_greedy_int4(ctx.handle, _stream(stream), _ptr(hidden), hidden_offset,
+                                                 _ptr(norm_weight), norm_offset, _ptr(weights), weights_offset,
+                                                 _ptr(scales), scales_offset, _ptr(biases), biases_offset,
+                                                 _ptr(out_token), d, vocab, rms_eps))
+
+
 class FusedPostAttentionSetup:
     """``FusedPostAttentionSetup`` / ``PrefillPostAttentionSetup`` (Kernels/Fusions/FusedPostAttentionSetup.swift:26-60;
     Kernels/Prefill/Epilogues/PrefillPostAttentionSetup.swift): the three-way norm in front of the feed-forward block."""

@@ -66,6 +66,34 @@ def case_gemv(args) -> None:
     print(f"gemv case done: rows={args.rows} bytes={nbytes} ms={[round(t, 4) for t in times]} GBps={nbytes / min(times) / 1e6:.0f}")
 
 
+def case_lmhead(args) -> None:
+    """Greedy LM head (final RMSNorm, tied int4 head of --rows x 2816, argmax): four launches per token."""
+    from .kernels import LMHeadChainInt4
+    ctx = TurboContext(0)
+    mat = AffineTensor(args.rows, 2816, 4)
+    mat.fill_synthetic(ctx, 5)
+    hidden = torch.randn(2816, device="cuda").half()
+    norm = torch.ones(2816, device="cuda").bfloat16()
+    out = torch.zeros(1, dtype=torch.int32, device="cuda")
+    op = LMHeadChainInt4(ctx)
+    launch = lambda: op.encode_greedy_decode(hidden, norm, mat.buffer, mat.buffer, mat.buffer, out, 2816, args.rows,
+                                             scales_offset=mat.s_off, biases_offset=mat.b_off)
+    for _ in range(max(args.warm, 1)):
+        launch()
+    times = []
+    for _ in range(args.iters):
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(10):
+            launch()
+        t1.record()
+        torch.cuda.synchronize()
+        times.append(t0.elapsed_time(t1) / 10)
+    nbytes = mat.w_bytes + 2 * mat.sb_bytes
+    print(f"lmhead case done: rows={args.rows} bytes={nbytes} token={int(out.item())} status={ctx.device_status()} "
+          f"ms={[round(t, 4) for t in times]} GBps={nbytes / min(times) / 1e6:.0f}")
+
+
 def case_qmm(args) -> None:
     """Dense int4 QMM on the tensor cores: --tokens rows of activations against a [--rows, 2816] weight matrix."""
     from .kernels import MPPPrefillInt4QMM
@@ -97,7 +125,7 @@ def case_qmm(args) -> None:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["block", "gemv", "qmm"])
+    ap.add_argument("case", choices=["block", "gemv", "qmm", "lmhead"])
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--layers", type=int, default=2)
     ap.add_argument("--rows", type=int, default=262144)
@@ -107,7 +135,7 @@ def main() -> None:
     ap.add_argument("--tensor-min", type=int, default=0, help="block case: smallest token count that takes the tensor-core path")
     ap.add_argument("--zipf", type=float, default=0.0, help="router logit bias log(p), p ~ 1/rank^zipf (0 = none)")
     args = ap.parse_args()
-    {"block": case_block, "gemv": case_gemv, "qmm": case_qmm}[args.case](args)
+    {"block": case_block, "gemv": case_gemv, "qmm": case_qmm, "lmhead": case_lmhead}[args.case](args)
 
 
 if __name__ == "__main__":
