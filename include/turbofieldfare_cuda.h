@@ -269,6 +269,17 @@ tf_status tf_group_routes_device(tf_context* ctx, void* stream,
                                  const uint32_t* indices, const void* weights_f16,
                                  uint32_t query_count, uint32_t top_k, uint32_t num_experts,
                                  const tf_device_routes* routes);
+/* tf_router_gemma4_block followed by tf_group_routes_device. Blocks of at most 64 rows do both in ONE launch: the
+ * thread block that finishes the last row also sorts the pairs (decode steps are bound by launch latency, and the
+ * grouping of a few hundred pairs is a fraction of a launch). Results are identical to the two calls. */
+tf_status tf_router_gemma4_block_grouped(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off,
+                                         const void* scales, uint64_t scales_off, const void* biases, uint64_t biases_off,
+                                         const void* hidden, uint64_t hidden_off, tf_dtype hidden_dtype,
+                                         const void* effective_scale, uint64_t effective_scale_off,
+                                         const void* per_expert_scale, uint64_t per_expert_scale_off,
+                                         const float* logit_bias, uint32_t* out_indices, void* out_weights,
+                                         uint32_t query_count, uint32_t num_experts, uint32_t d, uint32_t top_k,
+                                         uint32_t hidden_stride_elements, const tf_device_routes* routes);
 /* Per pair: act = half(gelu(gate.x) * (up.x)) into acts_scratch[pair, F] (sorted
  * pair order), then down -> route_partials[(token*top_k + rank)*D + d], fp16
  * (the reference) or fp32 when partials_f32 != 0. Experts are read from the

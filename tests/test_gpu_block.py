@@ -91,7 +91,7 @@ def test_block_forward_configs_1_and_2(tf_ctx, oracle, production_layer, T):
     launches0 = tf_ctx.launch_count
     MoEBlock(tf_ctx, layer).forward(to_dev(x16), y, T, ws)
     torch.cuda.synchronize()
-    assert tf_ctx.launch_count - launches0 == 7
+    assert tf_ctx.launch_count - launches0 == 6     # router+grouping, gate/up, down, 2 x shared expert, combine
     idx_gpu, w_gpu = ws.routing(T)
     check = range(T) if T == 1 else (0, 13, 63)
     idx_ref, y_ref, w_ref = _oracle_block(o, layer, pool, x16, check)

@@ -129,6 +129,59 @@ def _run_router(tf_ctx, o, mat, hidden16, eff16, gain16, rows=None, stride=None,
     return from_dev(idx, np.uint32).reshape(rows, K), from_dev(w, np.uint16).reshape(rows, K), logits.cpu().numpy()
 
 
+@pytest.mark.parametrize("rows,E,D,skew", [(1, 128, 2816, 0.0), (5, 128, 2816, 0.0), (64, 128, 2816, 0.0),
+                                           (64, 128, 2816, 6.0), (37, 16, 128, 0.0), (64, 256, 256, 2.0), (100, 128, 2816, 0.0)])
+def test_router_with_grouping_in_one_launch_equals_the_two_calls(tf_ctx, oracle, rows, E, D, skew):
+    """Blocks of at most 64 rows route and group in one launch (the block that finishes the last row sorts the
+    pairs); every routing table must equal what the router followed by the grouping launch writes, skewed loads
+    (one expert taking most pairs) and the larger-block fallback included. Called twice to show the tickets reset."""
+    import torch
+    from turbo_fieldfare_b200.kernels import DeviceRoutes, PrefillGroupedRoutedMoE, PrefillRouter
+    o = oracle
+    K = 8
+    rng = np.random.default_rng(rows * 1000 + E + D)
+    mat = config0_matrix(o, E, D, rng, bits=8)
+    hidden = o.f32_to_f16(rng.standard_normal((rows, D)).astype(np.float32))
+    eff = o.f32_to_bf16(np.full(D, 1.0 / np.sqrt(D), np.float32))
+    gain = o.f32_to_bf16(np.ones(E, np.float32))
+    bias = None
+    if skew:
+        b = np.zeros(E, np.float32); b[3] = skew; b[E - 1] = skew / 2
+        bias = to_dev(b)
+    W, S, B = to_dev(mat.packed), to_dev(mat.scales), to_dev(mat.biases)
+    hid, effd, gaind = to_dev(hidden), to_dev(eff), to_dev(gain)
+    launches = tf_ctx.launch_count
+
+    def tables(routes, idx, w):
+        torch.cuda.synchronize()
+        n = rows * K
+        counters = from_dev(routes.counters, np.uint32)
+        ng, nch = int(counters[0]), int(counters[1])
+        return dict(idx=from_dev(idx, np.uint32), w=from_dev(w, np.uint16),
+                    pairs=from_dev(routes.sorted_pairs, np.uint32)[:n * 4], offsets=from_dev(routes.per_expert_offsets, np.uint32),
+                    counts=from_dev(routes.per_expert_counts, np.uint32), groups=from_dev(routes.groups, np.uint32)[:ng * 3],
+                    chunk_group=from_dev(routes.chunk_group, np.uint32)[:nch], chunk_start=from_dev(routes.chunk_start, np.uint32)[:ng],
+                    counters=counters[:3])
+
+    ref_routes = DeviceRoutes(rows, K, E)
+    idx0 = torch.full((rows, K), -1, dtype=torch.int32, device="cuda"); w0 = dev_zeros_u16(rows * K)
+    PrefillRouter(tf_ctx).encode_gemma4_block(W, S, B, hid, effd, gaind, idx0, w0, rows, E, D, K, D, logit_bias=bias)
+    PrefillGroupedRoutedMoE(tf_ctx).encode_group_routes(idx0, w0, rows, K, E, ref_routes)
+    want = tables(ref_routes, idx0, w0)
+    assert want["counters"][2] == rows * K and want["counts"].sum() == rows * K
+    for attempt in range(2):
+        routes = DeviceRoutes(rows, K, E)
+        idx1 = torch.full((rows, K), -1, dtype=torch.int32, device="cuda"); w1 = dev_zeros_u16(rows * K)
+        before = tf_ctx.launch_count
+        PrefillRouter(tf_ctx).encode_gemma4_block_grouped(W, S, B, hid, effd, gaind, idx1, w1, rows, E, D, K, D, routes,
+                                                          logit_bias=bias)
+        assert tf_ctx.launch_count - before == (1 if rows <= 64 else 2)
+        got = tables(routes, idx1, w1)
+        for key in want:
+            assert np.array_equal(got[key], want[key]), (key, attempt)
+    assert tf_ctx.device_status() == 0 and tf_ctx.launch_count > launches
+
+
 def test_router_reference_fixture(tf_ctx, oracle):
     # Tests/TurboFieldfare/Core/Kernels/MoE/RouterTopKTests.swift:17-45
     from test_oracle_pins import _router_fixture

@@ -85,6 +85,8 @@ SIGNATURES = {
     "tf_router_gemma4": (C.c_int, [vp, vp, *_PLANES, vp, vp, u64, vp, u64, vp, vp, vp, u32, u32, u32]),
     "tf_router_gemma4_block": (C.c_int, [vp, vp, *_PLANES, vp, u64, C.c_int, vp, u64, vp, u64, vp,
                                          vp, u64, vp, u64, vp, u32, u32, u32, u32, u32]),
+    "tf_router_gemma4_block_grouped": (C.c_int, [vp, vp, *_PLANES, vp, u64, C.c_int, vp, u64, vp, u64, vp, vp, vp,
+                                                 u32, u32, u32, u32, u32, C.POINTER(DeviceRoutes)]),
     "tf_moe_phase1": (C.c_int, [vp, vp, vp, C.POINTER(ExpertOffsets), vp, vp, u32, u32, u32]),
     "tf_moe_phase1_subset": (C.c_int, [vp, vp, vp, C.POINTER(ExpertOffsets), vp, vp, u32, u32, u32, vp, u32]),
     "tf_moe_phase2_reduce": (C.c_int, [vp, vp, vp, C.POINTER(ExpertOffsets), vp, vp, vp, vp, u32, u32, u32]),

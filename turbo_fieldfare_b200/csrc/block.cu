@@ -331,14 +331,13 @@ namespace tf {
 static tf_status block_routed(tf_context* ctx, void* stream, const tf_moe_layer* layer, const void* x, uint32_t x_stride_elements,
                               uint32_t tokens, tf_workspace* ws, bool tensor_path) {
     const uint32_t d = layer->d, f = layer->f, K = layer->top_k, E = layer->num_experts;
-    tf_status s = tf_router_gemma4_block(ctx, stream, layer->router.weights, layer->router.weights_off,
-                                         layer->router.scales, layer->router.scales_off,
-                                         layer->router.biases, layer->router.biases_off,
-                                         x, 0, TF_FP16, layer->effective_scale, 0, layer->per_expert_scale, 0,
-                                         layer->logit_bias, ws->indices, 0, ws->weights, 0, nullptr,
-                                         tokens, E, d, K, x_stride_elements);
-    if (s) return s;
-    s = tf_group_routes_device(ctx, stream, ws->indices, ws->weights, tokens, K, E, &ws->routes);
+    // decode-sized blocks route and group in one launch
+    tf_status s = tf_router_gemma4_block_grouped(ctx, stream, layer->router.weights, layer->router.weights_off,
+                                                 layer->router.scales, layer->router.scales_off,
+                                                 layer->router.biases, layer->router.biases_off,
+                                                 x, 0, TF_FP16, layer->effective_scale, 0, layer->per_expert_scale, 0,
+                                                 layer->logit_bias, ws->indices, ws->weights, tokens, E, d, K,
+                                                 x_stride_elements, &ws->routes);
     if (s) return s;
     if (tensor_path) {
         // Prefill-sized block: gather the rows into expert order and run gate/up/GeGLU/down as tcgen05 GEMMs; the

@@ -73,8 +73,8 @@ tf_status tf_context_create(int device, tf_context** out) {
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
     e = cudaMalloc(&ctx->router_logits, sizeof(float) * tf::kRouterSplitRows * TF_MAX_ROUTER_EXPERTS);
-    if (e == cudaSuccess) e = cudaMalloc(&ctx->router_tickets, sizeof(unsigned int) * tf::kRouterSplitRows);
-    if (e == cudaSuccess) e = cudaMemset(ctx->router_tickets, 0, sizeof(unsigned int) * tf::kRouterSplitRows);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->router_tickets, sizeof(unsigned int) * (tf::kRouterSplitRows + 1));   // rows + one for the whole block
+    if (e == cudaSuccess) e = cudaMemset(ctx->router_tickets, 0, sizeof(unsigned int) * (tf::kRouterSplitRows + 1));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->device_error, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->device_error, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_groups, 2 * 64 * (TF_MAX_ROUTER_EXPERTS + 1));   // routed and dense tables

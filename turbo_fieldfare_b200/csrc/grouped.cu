@@ -40,7 +40,6 @@ namespace tf {
 
 constexpr int kGroupThreads = 256;
 constexpr int kGroupPerThread = 4;
-constexpr int kChunkTokens = 8;       // tokens per work chunk of the grouped kernels (the n of m16n8k16)
 
 // counters: [0] group count, [1] total chunks (sum over groups of ceil(count/8)), [2] pair count
 __global__ void __launch_bounds__(kGroupThreads)

@@ -111,6 +111,91 @@ __device__ __forceinline__ float router_row_logit_smem(const uint8_t* Wrow, cons
     return warp_sum(acc);
 }
 
+// Grouping of a small block's routes inside the router launch (the work of group_routes_kernel for at most
+// kRouterSplitRows rows): the block that finishes the last row sorts the (token, rank) pairs by expert, stably in
+// token-major order, and writes offsets, counts, groups and the 8-token chunk table. A pair's place is its expert's
+// offset plus the number of earlier pairs of that expert, counted on a per-expert bitmap over the pairs.
+struct RouterGroupOut {
+    tf_pair* sorted_pairs;          // nullptr: no grouping
+    uint32_t* per_expert_offsets;
+    uint32_t* per_expert_counts;
+    tf_group* groups;
+    uint32_t* chunk_group;
+    uint32_t* chunk_start;
+    uint32_t* counters;
+};
+
+__host__ __device__ inline size_t router_group_smem_bytes(uint32_t n_pairs, uint32_t num_experts) {
+    const uint32_t nw = (n_pairs + 31) / 32;
+    return (size_t)num_experts * nw * 4 + (size_t)num_experts * 2 * 4 + (size_t)n_pairs * 4;
+}
+
+__device__ void group_routes_in_block(const uint32_t* __restrict__ idx, const uint16_t* __restrict__ w, uint32_t T, uint32_t K,
+                                      uint32_t E, const RouterGroupOut& out, uint8_t* smem) {
+    const uint32_t n = T * K, nw = (n + 31) / 32;
+    uint32_t* mask = reinterpret_cast<uint32_t*>(smem);          // [E][nw]
+    uint32_t* hist = mask + (size_t)E * nw;                      // [E]
+    uint32_t* offs = hist + E;                                   // [E]
+    uint32_t* exs = offs + E;                                    // [n]
+    for (uint32_t i = threadIdx.x; i < E * nw + E; i += blockDim.x) mask[i] = 0;      // mask and hist are adjacent
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        uint32_t ex = __ldcg(idx + i);                           // written by other blocks of this launch
+        if (ex != 0xFFFFFFFFu) {
+            if (ex >= E) ex = E - 1;                             // min(id, E-1): Runtime/Inference/RealForwardRunner.swift:955
+            atomicAdd(&hist[ex], 1u);
+            atomicOr(&mask[(size_t)ex * nw + i / 32], 1u << (i % 32));
+        }
+        exs[i] = ex;
+    }
+    __syncthreads();
+    if (threadIdx.x < kWarp) {
+        const uint32_t lane = threadIdx.x;
+        uint32_t off = 0, gi = 0, ch = 0;                        // running totals over the experts before `base`
+        for (uint32_t base = 0; base < E; base += kWarp) {
+            const uint32_t e = base + lane;
+            const uint32_t cnt = e < E ? hist[e] : 0u;
+            const uint32_t nch = (cnt + (uint32_t)kChunkTokens - 1) / (uint32_t)kChunkTokens;
+            uint32_t i_off = cnt, i_g = cnt ? 1u : 0u, i_ch = nch;
+#pragma unroll
+            for (int o = 1; o < kWarp; o <<= 1) {
+                const uint32_t a = __shfl_up_sync(kFullMask, i_off, o), b = __shfl_up_sync(kFullMask, i_g, o),
+                               c = __shfl_up_sync(kFullMask, i_ch, o);
+                if ((int)lane >= o) { i_off += a; i_g += b; i_ch += c; }
+            }
+            const uint32_t my_off = off + i_off - cnt, my_g = gi + i_g - (cnt ? 1u : 0u), my_ch = ch + i_ch - nch;
+            if (e < E) {
+                offs[e] = my_off;
+                out.per_expert_counts[e] = cnt;
+                out.per_expert_offsets[e] = cnt ? my_off : 0xFFFFFFFFu;
+                if (cnt) {
+                    out.groups[my_g] = tf_group{e, my_off, cnt};
+                    out.chunk_start[my_g] = my_ch;
+                    for (uint32_t j = 0; j < nch; ++j) out.chunk_group[my_ch + j] = my_g;
+                }
+            }
+            off += __shfl_sync(kFullMask, i_off, kWarp - 1);
+            gi += __shfl_sync(kFullMask, i_g, kWarp - 1);
+            ch += __shfl_sync(kFullMask, i_ch, kWarp - 1);
+        }
+        if (lane == 0) {
+            out.counters[0] = gi;
+            out.counters[1] = ch;
+            out.counters[2] = n;
+        }
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const uint32_t ex = exs[i];
+        if (ex == 0xFFFFFFFFu) continue;
+        const uint32_t* m = mask + (size_t)ex * nw;
+        uint32_t pos = offs[ex];
+        for (uint32_t q = 0; q < i / 32; ++q) pos += __popc(m[q]);
+        pos += __popc(m[i / 32] & ((1u << (i % 32)) - 1u));
+        out.sorted_pairs[pos] = tf_pair{i / K, ex, i % K, (uint32_t)__ldcg(w + i)};
+    }
+}
+
 // Few rows (decode): grid (rows, experts/4); the block first copies its four expert rows into
 // shared memory with coalesced loads (the per-lane access pattern of the canonical order would
 // otherwise be a chain of 2-byte global loads); the last block to finish a row (self-resetting
@@ -122,7 +207,7 @@ router_split_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
                     const uint16_t* __restrict__ eff, const uint16_t* __restrict__ per_expert_scale,
                     const float* __restrict__ logit_bias,
                     uint32_t* __restrict__ out_idx, uint16_t* __restrict__ out_w, float* __restrict__ out_logits,
-                    float* scratch_logits, unsigned int* tickets,
+                    float* scratch_logits, unsigned int* tickets, const RouterGroupOut grp,
                     uint32_t num_experts, uint32_t d, uint32_t top_k, bool a2) {
     extern __shared__ __align__(16) uint8_t smem[];
     float* xf = reinterpret_cast<float*>(smem);                                   // [d]
@@ -226,6 +311,51 @@ router_split_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
     if (warp == 0)
         warp_select_topk(scores, num_experts, top_k, per_expert_scale, out_idx + (size_t)row * top_k,
                          out_w + (size_t)row * top_k, lane);
+    if (grp.sorted_pairs == nullptr) return;
+    if (gridDim.x == 1) {
+        // One token: its experts are distinct, so a pair's place is the number of selected experts with a smaller id;
+        // every group holds one pair and one chunk.
+        __syncthreads();                       // warp 0 has written the row's indices and weights
+        for (uint32_t e = threadIdx.x; e < num_experts; e += blockDim.x) {
+            grp.per_expert_counts[e] = 0u;
+            grp.per_expert_offsets[e] = 0xFFFFFFFFu;
+        }
+        __syncthreads();
+        if (threadIdx.x < top_k) {
+            uint32_t mine = out_idx[threadIdx.x];
+            if (mine >= num_experts) mine = num_experts - 1;
+            uint32_t pos = 0;
+            for (uint32_t r = 0; r < top_k; ++r) {
+                uint32_t other = out_idx[r];
+                if (other >= num_experts) other = num_experts - 1;
+                pos += other < mine ? 1u : 0u;
+            }
+            grp.sorted_pairs[pos] = tf_pair{0u, mine, threadIdx.x, (uint32_t)out_w[threadIdx.x]};
+            grp.per_expert_counts[mine] = 1u;
+            grp.per_expert_offsets[mine] = pos;
+            grp.groups[pos] = tf_group{mine, pos, 1u};
+            grp.chunk_start[pos] = pos;
+            grp.chunk_group[pos] = pos;
+        }
+        if (threadIdx.x == 0) {
+            grp.counters[0] = top_k;
+            grp.counters[1] = top_k;
+            grp.counters[2] = top_k;
+        }
+        return;
+    }
+    // the block that completes the last row groups all rows (second ticket, after the row tickets)
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int tk = atomicAdd(&tickets[kRouterSplitRows], 1u);
+        is_last = (tk == gridDim.x - 1);
+        if (is_last) tickets[kRouterSplitRows] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    group_routes_in_block(out_idx, out_w, gridDim.x, top_k, num_experts, grp, smem);
 }
 
 // Many rows (batched decode, prefill): one block per row.
@@ -335,7 +465,7 @@ static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, 
                                const uint8_t* hidden, tf_dtype hidden_dtype, const uint8_t* eff, const uint8_t* pes,
                                const float* logit_bias, uint32_t* out_idx, uint8_t* out_w, float* out_logits,
                                uint32_t rows, uint32_t num_experts, uint32_t d, uint32_t top_k, uint32_t stride,
-                               const char* name) {
+                               const char* name, const tf_device_routes* routes = nullptr) {
     TF_REQUIRE(ctx, aligned(S, 2) && aligned(B, 2) && aligned(hidden, 2) && aligned(eff, 2) && aligned(pes, 2) &&
                         aligned(out_w, 2) && aligned(out_idx, 4),
                TF_ERR_ALIGNMENT, "%s: 16-bit planes must be 2-byte aligned, indices 4-byte aligned", name);
@@ -353,11 +483,21 @@ static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, 
     if (rows <= (uint32_t)kRouterSplitRows) {
         dim3 grid(rows, (num_experts + kSplitExpertsPerBlock - 1) / kSplitExpertsPerBlock);
         auto k = bf ? router_split_kernel<true> : router_split_kernel<false>;
-        const size_t smem_split = (size_t)d * 4 + (size_t)kSplitExpertsPerBlock * d + (size_t)kSplitExpertsPerBlock * (d / kGroup) * 4;
+        size_t smem_split = (size_t)d * 4 + (size_t)kSplitExpertsPerBlock * d + (size_t)kSplitExpertsPerBlock * (d / kGroup) * 4;
+        RouterGroupOut grp{};
+        if (routes) {
+            grp = RouterGroupOut{static_cast<tf_pair*>(routes->sorted_pairs), static_cast<uint32_t*>(routes->per_expert_offsets),
+                                 static_cast<uint32_t*>(routes->per_expert_counts), static_cast<tf_group*>(routes->groups),
+                                 static_cast<uint32_t*>(routes->chunk_group), static_cast<uint32_t*>(routes->chunk_start),
+                                 static_cast<uint32_t*>(routes->counters)};
+            const size_t need = router_group_smem_bytes(rows * top_k, num_experts);
+            if (need > smem_split) smem_split = need;
+        }
         TF_REQUIRE(ctx, smem_split <= 200 * 1024, TF_ERR_UNSUPPORTED, "%s: D=%u too large", name, d);
         if (smem_split > 40 * 1024) TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_split));
         launch_pdl(k, grid, dim3(kSplitThreads), smem_split, st, W, Sp, Bp, hp, stride, ep, pp, logit_bias, out_idx, wp, out_logits,
-                   ctx->router_logits, ctx->router_tickets, num_experts, d, top_k, a2);
+                   ctx->router_logits, ctx->router_tickets, grp, num_experts, d, top_k, a2);
+        return check_launch(ctx, name);
     } else if (rows >= 256 && a2 && (size_t)kTileRouterRows * (d + num_experts) * 4 <= 100 * 1024) {
         auto k = bf ? router_tile_kernel<true> : router_tile_kernel<false>;
         const size_t smem_tile = (size_t)kTileRouterRows * (d + num_experts) * 4;
@@ -433,6 +573,46 @@ tf_status tf_router_gemma4_block(tf_context* ctx, void* stream, const void* weig
                              reinterpret_cast<uint32_t*>(tf::byte_ptr(static_cast<void*>(out_indices), out_indices_off)),
                              tf::byte_ptr(out_weights, out_weights_off), out_logits, query_count, num_experts, d, top_k,
                              hidden_stride_elements, name);
+}
+
+tf_status tf_router_gemma4_block_grouped(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off,
+                                         const void* scales, uint64_t scales_off, const void* biases, uint64_t biases_off,
+                                         const void* hidden, uint64_t hidden_off, tf_dtype hidden_dtype,
+                                         const void* effective_scale, uint64_t effective_scale_off,
+                                         const void* per_expert_scale, uint64_t per_expert_scale_off,
+                                         const float* logit_bias, uint32_t* out_indices, void* out_weights,
+                                         uint32_t query_count, uint32_t num_experts, uint32_t d, uint32_t top_k,
+                                         uint32_t hidden_stride_elements, const tf_device_routes* routes) {
+    const char* name = "tf_router_gemma4_block_grouped";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, routes && routes->sorted_pairs && routes->per_expert_offsets && routes->per_expert_counts && routes->groups &&
+                        routes->chunk_group && routes->chunk_start && routes->counters,
+               TF_ERR_INVALID_ARGUMENT, "%s: NULL routes buffer", name);
+    if (query_count > (uint32_t)tf::kRouterSplitRows) {
+        // larger blocks: the router kernels for many rows, then the grouping launch
+        tf_status s = tf_router_gemma4_block(ctx, stream, weights, weights_off, scales, scales_off, biases, biases_off, hidden,
+                                             hidden_off, hidden_dtype, effective_scale, effective_scale_off, per_expert_scale,
+                                             per_expert_scale_off, logit_bias, out_indices, 0, out_weights, 0, nullptr,
+                                             query_count, num_experts, d, top_k, hidden_stride_elements);
+        if (s) return s;
+        return tf_group_routes_device(ctx, stream, out_indices, out_weights, query_count, top_k, num_experts, routes);
+    }
+    TF_REQUIRE(ctx, weights && scales && biases && hidden && effective_scale && per_expert_scale && out_indices && out_weights,
+               TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, query_count > 0, TF_ERR_INVALID_ARGUMENT, "%s: queryCount must be positive", name);
+    TF_REQUIRE(ctx, num_experts > 0 && num_experts <= TF_MAX_ROUTER_EXPERTS, TF_ERR_INVALID_ARGUMENT,
+               "%s: numExperts > 256 is not supported", name);
+    TF_REQUIRE(ctx, top_k > 0 && top_k <= TF_MAX_TOP_K && num_experts >= top_k, TF_ERR_INVALID_ARGUMENT,
+               "%s: topK must be in 1...%d and at most numExperts, got %u", name, TF_MAX_TOP_K, top_k);
+    TF_REQUIRE(ctx, d > 0 && d % tf::kGroup == 0 && hidden_stride_elements >= d, TF_ERR_INVALID_ARGUMENT,
+               "%s: D must be a multiple of 64 and the stride at least D", name);
+    TF_REQUIRE(ctx, hidden_dtype == TF_FP16 || hidden_dtype == TF_BF16, TF_ERR_INVALID_ARGUMENT, "%s: bad hidden dtype", name);
+    return tf::launch_router(ctx, stream, tf::byte_ptr(weights, weights_off), tf::byte_ptr(scales, scales_off),
+                             tf::byte_ptr(biases, biases_off), tf::byte_ptr(hidden, hidden_off), hidden_dtype,
+                             tf::byte_ptr(effective_scale, effective_scale_off),
+                             tf::byte_ptr(per_expert_scale, per_expert_scale_off), logit_bias, out_indices,
+                             static_cast<uint8_t*>(out_weights), nullptr, query_count, num_experts, d, top_k,
+                             hidden_stride_elements, name, routes);
 }
 
 }  // extern "C"

@@ -19,6 +19,7 @@ constexpr int kGroup = TF_GROUP_SIZE;
 constexpr int kWarp = 32;
 constexpr unsigned kFullMask = 0xFFFFFFFFu;
 constexpr int kRouterSplitRows = 64;   // rows served by the multi-block decode router
+constexpr int kChunkTokens = 8;        // tokens per work chunk of the grouped kernels (the n of m16n8k16)
 
 // ---------------------------------------------------------------------------
 // host side: context and error plumbing

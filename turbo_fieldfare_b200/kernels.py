@@ -206,6 +206,20 @@ class PrefillRouter:
             _ptr(logit_bias), _ptr(out_indices), out_indices_offset, _ptr(out_weights), out_weights_offset,
             _ptr(out_logits), query_count, num_experts, d, top_k, hidden_stride_elements))
 
+    def encode_gemma4_block_grouped(self, weights, scales, biases, hidden, effective_scale, per_expert_scale, out_indices,
+                                    out_weights, query_count: int, num_experts: int, d: int, top_k: int,
+                                    hidden_stride_elements: int, routes: "DeviceRoutes", *, weights_offset=0,
+                                    scales_offset=0, biases_offset=0, hidden_offset=0, hidden_dtype=TF_FP16,
+                                    effective_scale_offset=0, per_expert_scale_offset=0, logit_bias=None, stream=None) -> None:
+        """Router and device grouping; one launch for blocks of at most 64 rows."""
+        ctx = self.context
+        ctx.check(ctx.lib.tf_router_gemma4_block_grouped(
+            ctx.handle, _stream(stream), _ptr(weights), weights_offset, _ptr(scales), scales_offset,
+            _ptr(biases), biases_offset, _ptr(hidden), hidden_offset, hidden_dtype,
+            _ptr(effective_scale), effective_scale_offset, _ptr(per_expert_scale), per_expert_scale_offset,
+            _ptr(logit_bias), _ptr(out_indices), _ptr(out_weights), query_count, num_experts, d, top_k,
+            hidden_stride_elements, C.byref(routes.c_struct)))
+
     @staticmethod
     def make_token_expert_pairs(indices: np.ndarray, weights_f16_bits: np.ndarray, query_count: int, top_k: int):
         """Host arrays in, structured array of 16-byte pairs out (PrefillRouter.swift:91-111)."""
