@@ -192,7 +192,9 @@ def run_gpu(args):
         stack.set_logit_bias(np.log(p / p.sum()).astype(np.float32))
     if ep:
         ws_prefill = stack.buffers(prefill_tokens, fixed_capacity=False)
-        ws_b1, ws_bn = stack.buffers(1, fixed_capacity=True), stack.buffers(batch, fixed_capacity=True)
+        peer = args.ep_exchange == "peer"
+        ws_b1 = stack.buffers(1, fixed_capacity=True, peer=peer)
+        ws_bn = stack.buffers(batch, fixed_capacity=True, peer=peer)
     else:
         ws_prefill, ws_b1, ws_bn = stack.workspace(prefill_tokens), stack.workspace(1), stack.workspace(batch)
 
@@ -224,9 +226,11 @@ def run_gpu(args):
             launches[tokens] = ctx.launch_count - before
         return g
 
-    # The expert-parallel path interleaves NCCL collectives with the kernels and runs eagerly: capturing the
-    # all-to-all exchanges in a CUDA graph did not complete on this software stack (the run was ended by its timeout).
-    use_graphs = not args.no_graphs and not ep
+    # Expert-parallel decode steps exchange their rows over peer memory with plain kernels (flag barriers with bounded
+    # waits), so the whole step is one graph as on a single GPU. With --ep-exchange nccl the steps interleave NCCL
+    # collectives with the kernels and run eagerly: capturing those all-to-all calls in a CUDA graph did not complete
+    # on this software stack (the run was ended by its timeout).
+    use_graphs = not args.no_graphs and (not ep or args.ep_exchange == "peer")
     g1 = capture(h1, 1, ws_b1) if use_graphs else None
     gn = capture(hn, batch, ws_bn) if use_graphs else None
     counters = {"launches": 0}
@@ -324,7 +328,9 @@ def run_gpu(args):
                    "tokens_per_step": tokens, "routing": "zipf(1.1) logit bias" if args.zipf else "computed logits",
                    "l2": "every step streams 13.2 GB of distinct layer weights (>> 126 MB L2)",
                    "cuda_graphs": use_graphs, "device_status": device_code,
-                   "parallelism": f"ep{world}: experts sharded {E // world} per GPU, NCCL all-to-all dispatch + combine" if ep else "single GPU",
+                   "parallelism": (f"ep{world}: experts sharded {E // world} per GPU; prefill: NCCL all-to-all dispatch + combine; decode: "
+                                   + ("rows pushed over peer memory (NVLink) with flag barriers, one CUDA graph per step"
+                                      if args.ep_exchange == "peer" else "NCCL all-to-all, eager")) if ep else "single GPU",
                    "phase_ms": {"prefill": ms_prefill, "decode_b1_per_step": ms_dec1, f"decode_b{batch}_per_step": ms_decn},
                    "phase_tokens_per_s": {"prefill": prefill_tokens / ms_prefill * 1e3, "decode_b1": 1e3 / ms_dec1,
                                           f"decode_b{batch}": batch / ms_decn * 1e3}},
@@ -440,6 +446,8 @@ def main():
     ap.add_argument("--decode-batch", type=int, default=DECODE_BATCH)
     ap.add_argument("--zipf", action="store_true", help="add the Zipf(1.1) router logit bias of config 3")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
+                    help="decode exchange at N > 1: kernels over peer memory (default) or NCCL all-to-all")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-tokens", type=int, default=256)
     args = ap.parse_args()

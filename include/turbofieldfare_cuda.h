@@ -560,6 +560,36 @@ tf_status tf_ep_combine(tf_context* ctx, void* stream, const void* returned_rows
                         const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
                         void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d);
 
+/* ---- expert-parallel exchange over peer memory (decode steps; no reference counterpart: the reference runs on
+ * one device) ----
+ * A rank allocates one exchange buffer (tf_peer_buffer_create), hands its 64-byte handle to the other ranks' processes
+ * (any host channel), and maps theirs (tf_peer_buffer_import: CUDA IPC, peer access over NVLink). tf_ep_peer_push
+ * copies the used slots of a [world][capacity] block array into the owners' buffers (block `rank` of each), and
+ * tf_ep_peer_barrier is a flag barrier between the ranks with bounded waits: a wait that gives up sets the context's
+ * device error word (tf_device_status) and later barriers stop waiting. Plain kernels only, so a decode step with
+ * its exchanges can be captured in a CUDA graph. One process per GPU; every rank must issue the same sequence of
+ * barriers. */
+#define TF_PEER_HANDLE_BYTES 64
+typedef struct tf_peer_buffer tf_peer_buffer;
+tf_status tf_peer_buffer_create(tf_context* ctx, uint64_t bytes, tf_peer_buffer** out);      /* zero-filled */
+void tf_peer_buffer_destroy(tf_peer_buffer* buffer);
+void* tf_peer_buffer_ptr(const tf_peer_buffer* buffer);
+tf_status tf_peer_buffer_export(const tf_peer_buffer* buffer, void* handle_out_64_bytes);
+tf_status tf_peer_buffer_import(tf_context* ctx, const void* handle_64_bytes, void** ptr_out);
+tf_status tf_peer_buffer_release(tf_context* ctx, void* imported_ptr);
+/* peer_bases_device: device array of `world` base addresses (own buffer at index `rank`). Slot (s, j) of src_rows
+ * goes to peer s at dst_offset_bytes + ((rank * capacity + j) * dst_stride_elements) * 2 when its expert id is not
+ * 0xFFFFFFFF; the id comes from slot_ids[s * capacity + j], or, when slot_ids is NULL, from the 32 bits at element
+ * tail_at_element of the row (then an unused slot still gets its 16-byte tail written, so the owner sees it empty). */
+tf_status tf_ep_peer_push(tf_context* ctx, void* stream, const void* src_rows, uint32_t src_stride_elements,
+                          const void* const* peer_bases_device, uint64_t dst_offset_bytes, uint32_t dst_stride_elements,
+                          uint32_t copy_elements, const uint32_t* slot_ids, uint32_t tail_at_element,
+                          uint32_t world, uint32_t rank, uint32_t capacity);
+/* flags: `world` 32-bit words at flags_offset_bytes of every buffer; epoch_counter_device: one zero-initialised word
+ * of this rank, advanced by the kernel. */
+tf_status tf_ep_peer_barrier(tf_context* ctx, void* stream, const void* const* peer_bases_device, uint64_t flags_offset_bytes,
+                             uint32_t* epoch_counter_device, uint32_t world, uint32_t rank);
+
 /* ---- greedy LM head ---- */
 /* out_token = argmax_row deq4(W[vocab, d]) . half(rms(hidden) * norm_weight): RMSNorm to fp16, the int4 GEMV with
  * UNROUNDED fp32 logits, the maximum over the finite ones, ties to the lowest row, 0 when none is finite.

@@ -34,6 +34,28 @@ def main(out_dir: str) -> None:
         torch.cuda.synchronize()
         a, b = h_ref.float(), h_ep.float()
         worst = max(worst, float((a - b).norm() / a.norm()))
+    # decode-sized steps with the exchange over peer memory: eager, then the whole step as a replayed CUDA graph
+    for T in (1, 6):
+        g = torch.Generator().manual_seed(29 + rank + T)
+        h = torch.randn(T, 256, generator=g).half().cuda()
+        h_ref = h.clone()
+        ref_stack.forward(h_ref, T, ref_stack.workspace(T))
+        buf = ep_stack.buffers(T, True, peer=True)
+        h_ep = h.clone()
+        ep_stack.forward(h_ep, T, buf)
+        torch.cuda.synchronize()
+        a = h_ref.float()
+        worst = max(worst, float((a - h_ep.float()).norm() / a.norm()))
+        static_h = h.clone()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            ep_stack.forward(static_h, T, buf)
+        for _ in range(2):
+            static_h.copy_(h)
+            graph.replay()
+            torch.cuda.synchronize()
+            worst = max(worst, float((a - static_h.float()).norm() / a.norm()))
+        buf.close()
     assert ctx.device_status() == 0
     np.save(os.path.join(out_dir, f"err_{rank}.npy"), np.array(worst))
     dist.barrier()

@@ -81,6 +81,50 @@ def test_single_rank_ep_stack_matches_fused_stack(tf_ctx, oracle, T, fixed):
     ep_stack.close()
 
 
+@pytest.mark.parametrize("T", [1, 6, 64])
+def test_single_rank_peer_exchange_matches_fused_stack_and_replays_in_a_graph(tf_ctx, oracle, T):
+    """The peer-memory exchange with one rank (the rank pushes into its own buffer and passes its own flag barrier):
+    same result as the fused stack, eagerly and as a replayed CUDA graph of the whole step."""
+    import torch
+    from turbo_fieldfare_b200.ep import ExpertParallelStack
+    from turbo_fieldfare_b200.stack import MoEStack
+    o = oracle
+    dims = dict(layers=2, d=256, f=128, fs=192, num_experts=16, top_k=8, seed=5, align=256)
+    ref_stack = MoEStack(tf_ctx, **dims)
+    ep_stack = ExpertParallelStack(tf_ctx, **dims)
+    rng = np.random.default_rng(40 + T)
+    h16 = o.f32_to_f16(rng.standard_normal((T, 256)).astype(np.float32))
+    h_ref = to_dev(h16.copy())
+    ref_stack.forward(h_ref, T, ref_stack.workspace(T))
+    want = o.f16_to_f32(from_dev(h_ref, np.uint16))
+    buf = ep_stack.buffers(T, True, peer=True)
+    h_ep = to_dev(h16.copy())
+    ep_stack.forward(h_ep, T, buf)
+    torch.cuda.synchronize()
+    assert tf_ctx.device_status() == 0
+    assert o.rel_l2(o.f16_to_f32(from_dev(h_ep, np.uint16)), want) < 3e-3
+    # the same step as a graph, replayed twice on fresh inputs
+    static_h = to_dev(h16.copy())
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ep_stack.forward(static_h, T, buf)          # warm-up on the capture stream
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        ep_stack.forward(static_h, T, buf)
+    for _ in range(2):
+        static_h.copy_(to_dev(h16.copy()))
+        graph.replay()
+        torch.cuda.synchronize()
+        assert o.rel_l2(o.f16_to_f32(from_dev(static_h, np.uint16)), want) < 3e-3
+    assert tf_ctx.device_status() == 0
+    buf.close()
+    ref_stack.close()
+    ep_stack.close()
+
+
 def test_two_rank_nccl_matches_single_gpu(tmp_path):
     import torch
     if torch.cuda.device_count() < 2:

@@ -1,0 +1,190 @@
+// Expert-parallel exchange over peer memory (NVLink), for decode steps.
+//
+// The fixed-capacity exchange of a decode step is small (at most tokens x top_k rows per destination) and bound by
+// the latency of a library collective per direction per layer. Here every rank owns one exchange buffer that its
+// peers map (CUDA IPC); a rank stores the rows for expert owner r straight into r's receive area, and a flag
+// barrier (one release store per peer, one bounded acquire wait per peer) orders the phases. Everything is plain
+// kernels with plain peer loads and stores, so a whole decode step, exchange included, replays as one CUDA graph.
+//
+// Every wait is bounded: after kPeerSpinLimit polls the kernel records kErrPeerTimeout in the context's device error
+// word and returns; once that word is set, later barriers do not wait at all, so a missing rank costs one timeout.
+// Ranks must run one process per GPU (kernels that wait on one another never share a GPU).
+#include "tf_common.cuh"
+
+#include <cstring>
+
+namespace tf {
+
+constexpr uint32_t kPeerSpinLimit = 1u << 23;           // x ~0.2 us per poll: about 2 s
+constexpr uint32_t kErrPeerTimeout = 0x7F000011u;
+constexpr int kPeerPushThreads = 256;
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// One warp per slot (source rank block s, slot j). A slot is in use when its expert id is not 0xFFFFFFFF: the id is
+// read from `ids` when given, else from the row's tail (element `tail_at`, as 32 bits). Used slots are copied
+// (`copy_elems` fp16 elements, a multiple of 8) into peer s's buffer at block `me`; with tails, an unused slot gets
+// only its tail written so that the receiver sees it as empty.
+__global__ void __launch_bounds__(kPeerPushThreads)
+ep_peer_push_kernel(const uint16_t* __restrict__ src, uint32_t src_stride, uint8_t* const* __restrict__ peers,
+                    uint64_t dst_offset_bytes, uint32_t dst_stride, uint32_t copy_elems, const uint32_t* __restrict__ ids,
+                    uint32_t tail_at, uint32_t world, uint32_t me, uint32_t cap) {
+    const uint32_t warps_per_block = kPeerPushThreads / kWarp;
+    const uint32_t lane = threadIdx.x % kWarp;
+    const uint32_t total = world * cap;
+    for (uint32_t slot = blockIdx.x * warps_per_block + threadIdx.x / kWarp; slot < total; slot += gridDim.x * warps_per_block) {
+        const uint32_t s = slot / cap, j = slot % cap;
+        const uint16_t* row = src + (size_t)slot * src_stride;
+        uint32_t id;
+        if (ids) id = ids[slot];
+        else id = *reinterpret_cast<const uint32_t*>(row + tail_at);
+        uint16_t* dst = reinterpret_cast<uint16_t*>(peers[s] + dst_offset_bytes) + ((size_t)me * cap + j) * dst_stride;
+        if (id != 0xFFFFFFFFu) {
+            const uint4* in = reinterpret_cast<const uint4*>(row);
+            uint4* out = reinterpret_cast<uint4*>(dst);
+            for (uint32_t v = lane; v < copy_elems / 8; v += kWarp) out[v] = in[v];
+        } else if (!ids && lane == 0) {
+            *reinterpret_cast<uint4*>(dst + tail_at) = *reinterpret_cast<const uint4*>(row + tail_at);
+        }
+    }
+    __threadfence_system();
+}
+
+// Flag barrier: thread r tells peer r "rank `me` reached epoch e" and waits until peer r has said the same here.
+// The epoch lives on the device and advances by one per barrier, so a replayed graph needs no host value.
+__global__ void ep_peer_barrier_kernel(uint8_t* const* __restrict__ peers, uint64_t flags_offset_bytes,
+                                       uint32_t* __restrict__ epoch_counter, uint32_t* __restrict__ error,
+                                       uint32_t world, uint32_t me) {
+    __shared__ uint32_t epoch;
+    if (threadIdx.x == 0) {
+        epoch = *epoch_counter + 1u;
+        *epoch_counter = epoch;
+    }
+    __syncthreads();
+    __threadfence_system();
+    const uint32_t r = threadIdx.x;
+    if (r >= world) return;
+    st_release_sys(reinterpret_cast<uint32_t*>(peers[r] + flags_offset_bytes) + me, epoch);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(peers[me] + flags_offset_bytes) + r;
+    if (*reinterpret_cast<volatile uint32_t*>(error) != 0u) return;      // a wait already gave up: do not wait again
+    for (uint32_t spin = 0; spin < kPeerSpinLimit; ++spin) {
+        if ((int32_t)(ld_acquire_sys(mine) - epoch) >= 0) return;
+        __nanosleep(100);
+    }
+    atomicCAS(error, 0u, kErrPeerTimeout);
+}
+
+}  // namespace tf
+
+struct tf_peer_buffer {
+    tf_context* ctx = nullptr;
+    void* base = nullptr;
+    uint64_t bytes = 0;
+    cudaIpcMemHandle_t handle;
+};
+
+extern "C" {
+
+tf_status tf_peer_buffer_create(tf_context* ctx, uint64_t bytes, tf_peer_buffer** out) {
+    const char* name = "tf_peer_buffer_create";
+    TF_REQUIRE(ctx, ctx != nullptr && out != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    *out = nullptr;
+    TF_REQUIRE(ctx, bytes > 0, TF_ERR_INVALID_ARGUMENT, "%s: size must be positive", name);
+    void* base = nullptr;
+    cudaError_t e = cudaMalloc(&base, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return tf::fail(ctx, TF_ERR_OUT_OF_MEMORY, "%s: %llu bytes: %s", name, (unsigned long long)bytes, cudaGetErrorString(e));
+    }
+    e = cudaMemset(base, 0, bytes);
+    tf_peer_buffer* b = new tf_peer_buffer();
+    b->ctx = ctx; b->base = base; b->bytes = bytes;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&b->handle, base);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(base);
+        delete b;
+        return tf::fail(ctx, TF_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e));
+    }
+    *out = b;
+    return TF_OK;
+}
+
+void tf_peer_buffer_destroy(tf_peer_buffer* buffer) {
+    if (!buffer) return;
+    if (buffer->base) cudaFree(buffer->base);
+    delete buffer;
+}
+
+void* tf_peer_buffer_ptr(const tf_peer_buffer* buffer) { return buffer ? buffer->base : nullptr; }
+
+tf_status tf_peer_buffer_export(const tf_peer_buffer* buffer, void* handle_out_64_bytes) {
+    if (!buffer || !handle_out_64_bytes) return tf::fail(nullptr, TF_ERR_INVALID_ARGUMENT, "tf_peer_buffer_export: NULL argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == TF_PEER_HANDLE_BYTES, "handle size");
+    memcpy(handle_out_64_bytes, &buffer->handle, sizeof(cudaIpcMemHandle_t));
+    return TF_OK;
+}
+
+tf_status tf_peer_buffer_import(tf_context* ctx, const void* handle_64_bytes, void** ptr_out) {
+    const char* name = "tf_peer_buffer_import";
+    TF_REQUIRE(ctx, ctx != nullptr && handle_64_bytes && ptr_out, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle_64_bytes, sizeof h);
+    *ptr_out = nullptr;
+    TF_CUDA(ctx, cudaIpcOpenMemHandle(ptr_out, h, cudaIpcMemLazyEnablePeerAccess));
+    return TF_OK;
+}
+
+tf_status tf_peer_buffer_release(tf_context* ctx, void* imported_ptr) {
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_peer_buffer_release: ctx is NULL");
+    if (imported_ptr) TF_CUDA(ctx, cudaIpcCloseMemHandle(imported_ptr));
+    return TF_OK;
+}
+
+tf_status tf_ep_peer_push(tf_context* ctx, void* stream, const void* src_rows, uint32_t src_stride_elements,
+                          const void* const* peer_bases_device, uint64_t dst_offset_bytes, uint32_t dst_stride_elements,
+                          uint32_t copy_elements, const uint32_t* slot_ids, uint32_t tail_at_element,
+                          uint32_t world, uint32_t rank, uint32_t capacity) {
+    const char* name = "tf_ep_peer_push";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, src_rows && peer_bases_device, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, world > 0 && rank < world && capacity > 0, TF_ERR_INVALID_ARGUMENT, "%s: bad rank, world or capacity", name);
+    TF_REQUIRE(ctx, copy_elements % 8 == 0 && copy_elements <= src_stride_elements && copy_elements <= dst_stride_elements,
+               TF_ERR_INVALID_ARGUMENT, "%s: rows are copied in 16-byte pieces within both strides", name);
+    TF_REQUIRE(ctx, src_stride_elements % 8 == 0 && dst_stride_elements % 8 == 0 && dst_offset_bytes % 16 == 0 &&
+                        tf::aligned(src_rows, 16),
+               TF_ERR_ALIGNMENT, "%s: rows must be 16-byte aligned", name);
+    TF_REQUIRE(ctx, slot_ids != nullptr || (tail_at_element % 8 == 0 && tail_at_element + 8 <= src_stride_elements &&
+                                             tail_at_element + 8 <= dst_stride_elements),
+               TF_ERR_INVALID_ARGUMENT, "%s: the id tail must lie inside the row", name);
+    const uint32_t slots = world * capacity;
+    const uint32_t per_block = tf::kPeerPushThreads / tf::kWarp;
+    uint32_t grid = (slots + per_block - 1) / per_block;
+    const uint32_t limit = (uint32_t)ctx->sm_count * 4u;
+    if (grid > limit) grid = limit;
+    tf::ep_peer_push_kernel<<<grid, tf::kPeerPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(src_rows), src_stride_elements, (uint8_t* const*)peer_bases_device,
+        dst_offset_bytes, dst_stride_elements, copy_elements, slot_ids, tail_at_element, world, rank, capacity);
+    return tf::check_launch(ctx, name);
+}
+
+tf_status tf_ep_peer_barrier(tf_context* ctx, void* stream, const void* const* peer_bases_device, uint64_t flags_offset_bytes,
+                             uint32_t* epoch_counter_device, uint32_t world, uint32_t rank) {
+    const char* name = "tf_ep_peer_barrier";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, peer_bases_device && epoch_counter_device, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, world > 0 && world <= 32 && rank < world, TF_ERR_INVALID_ARGUMENT, "%s: world must be 1...32", name);
+    TF_REQUIRE(ctx, flags_offset_bytes % 4 == 0, TF_ERR_ALIGNMENT, "%s: flags must be 4-byte aligned", name);
+    tf::ep_peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        (uint8_t* const*)peer_bases_device, flags_offset_bytes, epoch_counter_device, ctx->device_error, world, rank);
+    return tf::check_launch(ctx, name);
+}
+
+}  // extern "C"

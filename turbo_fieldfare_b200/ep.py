@@ -97,8 +97,10 @@ class ExpertParallelStack:
             l.set_logit_bias(bias)
         self._c_layers = [l.c_struct() for l in self.layers]
 
-    def buffers(self, max_tokens: int, fixed_capacity: bool) -> "EPBuffers":
-        return EPBuffers(self, max_tokens, fixed_capacity)
+    def buffers(self, max_tokens: int, fixed_capacity: bool, peer: bool = False) -> "EPBuffers":
+        """``peer``: fixed-capacity buffers whose exchange runs over peer memory (plain kernels, capturable in a CUDA
+        graph) instead of NCCL all-to-all calls. Collective: every rank must ask for the same buffers in the same order."""
+        return EPBuffers(self, max_tokens, fixed_capacity, peer)
 
     def forward(self, hidden: torch.Tensor, tokens: int, buf: "EPBuffers", stream=None) -> None:
         """hidden: fp16 [tokens, d] on the device, updated in place: x = rmsnorm(h) * w_l; h = h + block_l(x)."""
@@ -124,7 +126,15 @@ class ExpertParallelStack:
         row_stride = buf.row_stride
         ctx.check(lib.tf_ep_dispatch(ctx.handle, st, C.byref(layer), _ptr(x), tokens, buf.ws.handle, self.local_experts,
                                      cap, _ptr(buf.send_rows), _ptr(buf.send_ids), _ptr(buf.inverse), row_stride))
-        if buf.fixed:
+        if buf.fixed and buf.peer:
+            # rows (with their id tails) straight into the owners' receive areas, then a flag barrier
+            slots = recv_slots = self.world * cap
+            ctx.check(lib.tf_ep_peer_push(ctx.handle, st, _ptr(buf.send_rows), row_stride, _ptr(buf.peer_bases), 0, row_stride,
+                                          row_stride, None, d, self.world, self.rank, cap))
+            ctx.check(lib.tf_ep_peer_barrier(ctx.handle, st, _ptr(buf.peer_bases), buf.flags_offset, _ptr(buf.epoch),
+                                             self.world, self.rank))
+            recv_ids, recv_rows = buf.recv_ids, buf.recv_rows
+        elif buf.fixed:
             slots = self.world * cap
             recv_slots = slots
             if self.world > 1:
@@ -164,7 +174,14 @@ class ExpertParallelStack:
                                         _ptr(recv_rows), _ptr(recv_ids), recv_slots, self.local_experts,
                                         C.byref(buf.recv_routes.c_struct), _ptr(buf.zero_weights), _ptr(buf.acts),
                                         _ptr(buf.out_rows), d, f, row_stride))
-        if self.world > 1:
+        if buf.fixed and buf.peer:
+            # results back into the home ranks' areas (only the slots that held a row), then the second barrier
+            ctx.check(lib.tf_ep_peer_push(ctx.handle, st, _ptr(buf.out_rows), d, _ptr(buf.peer_bases), buf.back_offset, d, d,
+                                          _ptr(buf.recv_ids), 0, self.world, self.rank, cap))
+            ctx.check(lib.tf_ep_peer_barrier(ctx.handle, st, _ptr(buf.peer_bases), buf.flags_offset, _ptr(buf.epoch),
+                                             self.world, self.rank))
+            back = buf.back_rows
+        elif self.world > 1:
             if buf.fixed:
                 dist.all_to_all_single(buf.back_rows[:recv_slots * d], buf.out_rows[:recv_slots * d], group=self.group)
             else:
@@ -183,8 +200,10 @@ class ExpertParallelStack:
 class EPBuffers:
     """Device buffers of one expert-parallel forward for up to ``max_tokens`` local tokens."""
 
-    def __init__(self, stack: ExpertParallelStack, max_tokens: int, fixed_capacity: bool):
+    def __init__(self, stack: ExpertParallelStack, max_tokens: int, fixed_capacity: bool, peer: bool = False):
         dm = stack.dims
+        self.peer = bool(peer and fixed_capacity)
+        self._peer_handle, self._imported = None, []
         d, f, K, E = dm["d"], dm["f"], dm["top_k"], dm["num_experts"]
         self.stack, self.fixed, self.max_tokens = stack, fixed_capacity, max_tokens
         self.ws = Workspace(stack.context, max_tokens, d, f, dm["fs"], K, E)
@@ -203,6 +222,60 @@ class EPBuffers:
         self.d, self.f = d, f
         self._recv_cap = 0
         self.ensure_recv(send_slots if fixed_capacity else max(n_pairs, 1))
+        if self.peer:
+            self._map_peer_buffers(send_slots)
+
+    def _map_peer_buffers(self, slots: int) -> None:
+        """One exchange buffer per rank: [receive area | return area | flags], mapped by every other rank (CUDA IPC).
+        The receive and return areas replace ``recv_rows`` and ``back_rows``."""
+        import ctypes as C
+        from .stack import device_view_u8
+        stack = self.stack
+        ctx, lib = stack.context, stack.context.lib
+        recv_bytes = slots * self.row_stride * 2
+        back_bytes = slots * self.d * 2
+        self.back_offset = (recv_bytes + 255) // 256 * 256
+        self.flags_offset = (self.back_offset + back_bytes + 255) // 256 * 256
+        total = self.flags_offset + 256
+        handle = C.c_void_p()
+        ctx.check(lib.tf_peer_buffer_create(ctx.handle, total, C.byref(handle)))
+        self._peer_handle = handle
+        own = lib.tf_peer_buffer_ptr(handle)
+        exported = C.create_string_buffer(64)
+        ctx.check(lib.tf_peer_buffer_export(handle, exported))
+        bases = [own]
+        if stack.world > 1:
+            gathered = [None] * stack.world
+            dist.all_gather_object(gathered, bytes(exported.raw), group=stack.group)
+            bases = []
+            for r, raw in enumerate(gathered):
+                if r == stack.rank:
+                    bases.append(own)
+                    continue
+                p = C.c_void_p()
+                ctx.check(lib.tf_peer_buffer_import(ctx.handle, C.create_string_buffer(raw, 64), C.byref(p)))
+                self._imported.append(p.value)
+                bases.append(p.value)
+            dist.barrier(group=stack.group)          # every rank has mapped every buffer before anyone writes
+        self.peer_bases = torch.tensor(bases, dtype=torch.int64, device="cuda")
+        self.epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.recv_rows = device_view_u8(own, recv_bytes).view(torch.float16)
+        self.back_rows = device_view_u8(own + self.back_offset, back_bytes).view(torch.float16)
+        torch.cuda.synchronize()
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and frees this rank's (collective when peers are mapped)."""
+        if self._peer_handle is None:
+            return
+        ctx, lib = self.stack.context, self.stack.context.lib
+        torch.cuda.synchronize()
+        if self.stack.world > 1:
+            dist.barrier(group=self.stack.group)     # nobody is still writing into a buffer that is about to go
+        for p in self._imported:
+            lib.tf_peer_buffer_release(ctx.handle, p)
+        self._imported = []
+        lib.tf_peer_buffer_destroy(self._peer_handle)
+        self._peer_handle = None
 
     def ensure_recv(self, slots: int) -> None:
         if slots <= self._recv_cap:
