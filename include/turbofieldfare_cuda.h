@@ -580,11 +580,14 @@ tf_status tf_peer_buffer_release(tf_context* ctx, void* imported_ptr);
 /* peer_bases_device: device array of `world` base addresses (own buffer at index `rank`). Slot (s, j) of src_rows
  * goes to peer s at dst_offset_bytes + ((rank * capacity + j) * dst_stride_elements) * 2 when its expert id is not
  * 0xFFFFFFFF; the id comes from slot_ids[s * capacity + j], or, when slot_ids is NULL, from the 32 bits at element
- * tail_at_element of the row (then an unused slot still gets its 16-byte tail written, so the owner sees it empty). */
+ * tail_at_element of the row (then an unused slot still gets its 16-byte tail written, so the owner sees it empty).
+ * epoch_and_ticket_device: NULL, or two zero-initialised words of this rank; then the thread block that finishes last
+ * runs the flag barrier of tf_ep_peer_barrier in the same launch (word 0 is the epoch counter that call takes). */
 tf_status tf_ep_peer_push(tf_context* ctx, void* stream, const void* src_rows, uint32_t src_stride_elements,
                           const void* const* peer_bases_device, uint64_t dst_offset_bytes, uint32_t dst_stride_elements,
                           uint32_t copy_elements, const uint32_t* slot_ids, uint32_t tail_at_element,
-                          uint32_t world, uint32_t rank, uint32_t capacity);
+                          uint32_t world, uint32_t rank, uint32_t capacity,
+                          uint64_t flags_offset_bytes, uint32_t* epoch_and_ticket_device);
 /* flags: `world` 32-bit words at flags_offset_bytes of every buffer; epoch_counter_device: one zero-initialised word
  * of this rank, advanced by the kernel. */
 tf_status tf_ep_peer_barrier(tf_context* ctx, void* stream, const void* const* peer_bases_device, uint64_t flags_offset_bytes,

@@ -125,6 +125,41 @@ def test_single_rank_peer_exchange_matches_fused_stack_and_replays_in_a_graph(tf
     ep_stack.close()
 
 
+def test_peer_barrier_wait_runs_out_and_reports(oracle):
+    """A barrier whose second participant never arrives (its flag is a word that nothing sets): the bounded wait gives
+    up after about two seconds, the kernel returns, the context reports the device code and stays usable, and a later
+    barrier passes. No fault, no hang: the wait simply runs out."""
+    import ctypes as C
+    import time
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    from turbo_fieldfare_b200.kernels import TFError, TurboContext
+    ctx = TurboContext(0)
+    lib = ctx.lib
+    handle = C.c_void_p()
+    ctx.check(lib.tf_peer_buffer_create(ctx.handle, 4096, C.byref(handle)))
+    own = lib.tf_peer_buffer_ptr(handle)
+    # "world" of two whose second member is this same buffer, 1 KiB further on: rank 0 signals it and then waits for
+    # flag word 1 of its own buffer, which nobody writes
+    bases = torch.tensor([own, own + 1024], dtype=torch.int64, device="cuda")
+    epoch = torch.zeros(2, dtype=torch.int32, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    t0 = time.time()
+    ctx.check(lib.tf_ep_peer_barrier(ctx.handle, st, bases.data_ptr(), 0, epoch.data_ptr(), 2, 0))
+    with pytest.raises(TFError) as err:
+        ctx.device_status()
+    waited = time.time() - t0
+    assert "0x7f000011" in str(err.value).lower()
+    assert waited < 30.0
+    # the context is still usable: a one-member barrier passes and the status is clean again
+    ctx.check(lib.tf_ep_peer_barrier(ctx.handle, st, bases.data_ptr(), 0, epoch.data_ptr(), 1, 0))
+    assert ctx.device_status() == 0
+    assert int(epoch.cpu()[0]) == 2
+    lib.tf_peer_buffer_destroy(handle)
+    ctx.close()
+
+
 def test_two_rank_nccl_matches_single_gpu(tmp_path):
     import torch
     if torch.cuda.device_count() < 2:

@@ -429,13 +429,12 @@ tf_status tf_ep_dispatch(tf_context* ctx, void* stream, const tf_moe_layer* laye
     TF_REQUIRE(ctx, tokens <= ws->max_tokens, TF_ERR_SCRATCH_TOO_SMALL, "%s: %u tokens exceed the workspace (%u)", name, tokens, ws->max_tokens);
     if (tokens == 0) return TF_OK;
     const uint32_t d = layer->d, K = layer->top_k, E = layer->num_experts;
-    tf_status s = tf_router_gemma4_block(ctx, stream, layer->router.weights, layer->router.weights_off,
-                                         layer->router.scales, layer->router.scales_off,
-                                         layer->router.biases, layer->router.biases_off,
-                                         x, 0, TF_FP16, layer->effective_scale, 0, layer->per_expert_scale, 0,
-                                         layer->logit_bias, ws->indices, 0, ws->weights, 0, nullptr, tokens, E, d, K, d);
-    if (s) return s;
-    s = tf_group_routes_device(ctx, stream, ws->indices, ws->weights, tokens, K, E, &ws->routes);
+    // router and grouping over the GLOBAL experts (one launch for decode-sized blocks)
+    tf_status s = tf_router_gemma4_block_grouped(ctx, stream, layer->router.weights, layer->router.weights_off,
+                                                 layer->router.scales, layer->router.scales_off,
+                                                 layer->router.biases, layer->router.biases_off,
+                                                 x, 0, TF_FP16, layer->effective_scale, 0, layer->per_expert_scale, 0,
+                                                 layer->logit_bias, ws->indices, ws->weights, tokens, E, d, K, d, &ws->routes);
     if (s) return s;
     return tf_ep_pack(ctx, stream, x, 0, d, &ws->routes, tokens, K, E, experts_per_rank, capacity, d, send_rows,
                       send_expert_ids, inverse_perm, send_row_stride_elements);

@@ -28,6 +28,31 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
     return v;
 }
 
+// Flag barrier: thread r tells peer r "rank `me` reached epoch e" and waits until peer r has said the same here.
+// The epoch lives on the device and advances by one per barrier, so a replayed graph needs no host value.
+// Called by every thread of one block (at least `world` threads).
+__device__ __forceinline__ void peer_barrier_in_block(uint8_t* const* __restrict__ peers, uint64_t flags_offset_bytes,
+                                                      uint32_t* __restrict__ epoch_counter, uint32_t* __restrict__ error,
+                                                      uint32_t world, uint32_t me) {
+    __shared__ uint32_t epoch;
+    if (threadIdx.x == 0) {
+        epoch = *epoch_counter + 1u;
+        *epoch_counter = epoch;
+    }
+    __syncthreads();
+    __threadfence_system();
+    const uint32_t r = threadIdx.x;
+    if (r >= world) return;
+    st_release_sys(reinterpret_cast<uint32_t*>(peers[r] + flags_offset_bytes) + me, epoch);
+    const uint32_t* mine = reinterpret_cast<const uint32_t*>(peers[me] + flags_offset_bytes) + r;
+    if (*reinterpret_cast<volatile uint32_t*>(error) != 0u) return;      // a wait already gave up: do not wait again
+    for (uint32_t spin = 0; spin < kPeerSpinLimit; ++spin) {
+        if ((int32_t)(ld_acquire_sys(mine) - epoch) >= 0) return;
+        __nanosleep(100);
+    }
+    atomicCAS(error, 0u, kErrPeerTimeout);
+}
+
 // One warp per slot (source rank block s, slot j). A slot is in use when its expert id is not 0xFFFFFFFF: the id is
 // read from `ids` when given, else from the row's tail (element `tail_at`, as 32 bits). Used slots are copied
 // (`copy_elems` fp16 elements, a multiple of 8) into peer s's buffer at block `me`; with tails, an unused slot gets
@@ -35,7 +60,8 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __global__ void __launch_bounds__(kPeerPushThreads)
 ep_peer_push_kernel(const uint16_t* __restrict__ src, uint32_t src_stride, uint8_t* const* __restrict__ peers,
                     uint64_t dst_offset_bytes, uint32_t dst_stride, uint32_t copy_elems, const uint32_t* __restrict__ ids,
-                    uint32_t tail_at, uint32_t world, uint32_t me, uint32_t cap) {
+                    uint32_t tail_at, uint32_t world, uint32_t me, uint32_t cap,
+                    uint64_t flags_offset_bytes, uint32_t* __restrict__ epoch_and_ticket, uint32_t* __restrict__ error) {
     const uint32_t warps_per_block = kPeerPushThreads / kWarp;
     const uint32_t lane = threadIdx.x % kWarp;
     const uint32_t total = world * cap;
@@ -55,30 +81,25 @@ ep_peer_push_kernel(const uint16_t* __restrict__ src, uint32_t src_stride, uint8
         }
     }
     __threadfence_system();
+    if (epoch_and_ticket == nullptr) return;
+    // the block that finishes last runs the flag barrier (word 0: epoch, word 1: self-resetting ticket)
+    __shared__ bool last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t tk = atomicAdd(&epoch_and_ticket[1], 1u);
+        last = tk == gridDim.x - 1;
+        if (last) epoch_and_ticket[1] = 0u;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    peer_barrier_in_block(peers, flags_offset_bytes, epoch_and_ticket, error, world, me);
 }
 
-// Flag barrier: thread r tells peer r "rank `me` reached epoch e" and waits until peer r has said the same here.
-// The epoch lives on the device and advances by one per barrier, so a replayed graph needs no host value.
 __global__ void ep_peer_barrier_kernel(uint8_t* const* __restrict__ peers, uint64_t flags_offset_bytes,
                                        uint32_t* __restrict__ epoch_counter, uint32_t* __restrict__ error,
                                        uint32_t world, uint32_t me) {
-    __shared__ uint32_t epoch;
-    if (threadIdx.x == 0) {
-        epoch = *epoch_counter + 1u;
-        *epoch_counter = epoch;
-    }
-    __syncthreads();
-    __threadfence_system();
-    const uint32_t r = threadIdx.x;
-    if (r >= world) return;
-    st_release_sys(reinterpret_cast<uint32_t*>(peers[r] + flags_offset_bytes) + me, epoch);
-    const uint32_t* mine = reinterpret_cast<const uint32_t*>(peers[me] + flags_offset_bytes) + r;
-    if (*reinterpret_cast<volatile uint32_t*>(error) != 0u) return;      // a wait already gave up: do not wait again
-    for (uint32_t spin = 0; spin < kPeerSpinLimit; ++spin) {
-        if ((int32_t)(ld_acquire_sys(mine) - epoch) >= 0) return;
-        __nanosleep(100);
-    }
-    atomicCAS(error, 0u, kErrPeerTimeout);
+    peer_barrier_in_block(peers, flags_offset_bytes, epoch_counter, error, world, me);
 }
 
 }  // namespace tf
@@ -151,11 +172,14 @@ tf_status tf_peer_buffer_release(tf_context* ctx, void* imported_ptr) {
 tf_status tf_ep_peer_push(tf_context* ctx, void* stream, const void* src_rows, uint32_t src_stride_elements,
                           const void* const* peer_bases_device, uint64_t dst_offset_bytes, uint32_t dst_stride_elements,
                           uint32_t copy_elements, const uint32_t* slot_ids, uint32_t tail_at_element,
-                          uint32_t world, uint32_t rank, uint32_t capacity) {
+                          uint32_t world, uint32_t rank, uint32_t capacity,
+                          uint64_t flags_offset_bytes, uint32_t* epoch_and_ticket_device) {
     const char* name = "tf_ep_peer_push";
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, src_rows && peer_bases_device, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
-    TF_REQUIRE(ctx, world > 0 && rank < world && capacity > 0, TF_ERR_INVALID_ARGUMENT, "%s: bad rank, world or capacity", name);
+    TF_REQUIRE(ctx, world > 0 && world <= 32 && rank < world && capacity > 0, TF_ERR_INVALID_ARGUMENT,
+               "%s: bad rank, world (1...32) or capacity", name);
+    TF_REQUIRE(ctx, flags_offset_bytes % 4 == 0, TF_ERR_ALIGNMENT, "%s: flags must be 4-byte aligned", name);
     TF_REQUIRE(ctx, copy_elements % 8 == 0 && copy_elements <= src_stride_elements && copy_elements <= dst_stride_elements,
                TF_ERR_INVALID_ARGUMENT, "%s: rows are copied in 16-byte pieces within both strides", name);
     TF_REQUIRE(ctx, src_stride_elements % 8 == 0 && dst_stride_elements % 8 == 0 && dst_offset_bytes % 16 == 0 &&
@@ -171,7 +195,8 @@ tf_status tf_ep_peer_push(tf_context* ctx, void* stream, const void* src_rows, u
     if (grid > limit) grid = limit;
     tf::ep_peer_push_kernel<<<grid, tf::kPeerPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(src_rows), src_stride_elements, (uint8_t* const*)peer_bases_device,
-        dst_offset_bytes, dst_stride_elements, copy_elements, slot_ids, tail_at_element, world, rank, capacity);
+        dst_offset_bytes, dst_stride_elements, copy_elements, slot_ids, tail_at_element, world, rank, capacity,
+        flags_offset_bytes, epoch_and_ticket_device, ctx->device_error);
     return tf::check_launch(ctx, name);
 }
 

@@ -127,12 +127,10 @@ class ExpertParallelStack:
         ctx.check(lib.tf_ep_dispatch(ctx.handle, st, C.byref(layer), _ptr(x), tokens, buf.ws.handle, self.local_experts,
                                      cap, _ptr(buf.send_rows), _ptr(buf.send_ids), _ptr(buf.inverse), row_stride))
         if buf.fixed and buf.peer:
-            # rows (with their id tails) straight into the owners' receive areas, then a flag barrier
+            # rows (with their id tails) straight into the owners' receive areas; the launch ends with the flag barrier
             slots = recv_slots = self.world * cap
             ctx.check(lib.tf_ep_peer_push(ctx.handle, st, _ptr(buf.send_rows), row_stride, _ptr(buf.peer_bases), 0, row_stride,
-                                          row_stride, None, d, self.world, self.rank, cap))
-            ctx.check(lib.tf_ep_peer_barrier(ctx.handle, st, _ptr(buf.peer_bases), buf.flags_offset, _ptr(buf.epoch),
-                                             self.world, self.rank))
+                                          row_stride, None, d, self.world, self.rank, cap, buf.flags_offset, _ptr(buf.epoch)))
             recv_ids, recv_rows = buf.recv_ids, buf.recv_rows
         elif buf.fixed:
             slots = self.world * cap
@@ -175,11 +173,9 @@ class ExpertParallelStack:
                                         C.byref(buf.recv_routes.c_struct), _ptr(buf.zero_weights), _ptr(buf.acts),
                                         _ptr(buf.out_rows), d, f, row_stride))
         if buf.fixed and buf.peer:
-            # results back into the home ranks' areas (only the slots that held a row), then the second barrier
+            # results back into the home ranks' areas (only the slots that held a row), and the second barrier
             ctx.check(lib.tf_ep_peer_push(ctx.handle, st, _ptr(buf.out_rows), d, _ptr(buf.peer_bases), buf.back_offset, d, d,
-                                          _ptr(buf.recv_ids), 0, self.world, self.rank, cap))
-            ctx.check(lib.tf_ep_peer_barrier(ctx.handle, st, _ptr(buf.peer_bases), buf.flags_offset, _ptr(buf.epoch),
-                                             self.world, self.rank))
+                                          _ptr(buf.recv_ids), 0, self.world, self.rank, cap, buf.flags_offset, _ptr(buf.epoch)))
             back = buf.back_rows
         elif self.world > 1:
             if buf.fixed:
@@ -258,7 +254,7 @@ class EPBuffers:
                 bases.append(p.value)
             dist.barrier(group=stack.group)          # every rank has mapped every buffer before anyone writes
         self.peer_bases = torch.tensor(bases, dtype=torch.int64, device="cuda")
-        self.epoch = torch.zeros(1, dtype=torch.int32, device="cuda")
+        self.epoch = torch.zeros(2, dtype=torch.int32, device="cuda")       # epoch counter, ticket of the push kernel
         self.recv_rows = device_view_u8(own, recv_bytes).view(torch.float16)
         self.back_rows = device_view_u8(own + self.back_offset, back_bytes).view(torch.float16)
         torch.cuda.synchronize()
