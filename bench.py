@@ -230,7 +230,8 @@ def run_gpu(args):
     # waits), so the whole step is one graph as on a single GPU. With --ep-exchange nccl the steps interleave NCCL
     # collectives with the kernels and run eagerly: capturing those all-to-all calls in a CUDA graph did not complete
     # on this software stack (the run was ended by its timeout).
-    use_graphs = not args.no_graphs and (not ep or args.ep_exchange == "peer")
+    peer_exchange = ep and ws_b1.peer and ws_bn.peer       # False when the peer buffers could not be mapped
+    use_graphs = not args.no_graphs and (not ep or peer_exchange)
     g1 = capture(h1, 1, ws_b1) if use_graphs else None
     gn = capture(hn, batch, ws_bn) if use_graphs else None
     counters = {"launches": 0}
@@ -330,7 +331,7 @@ def run_gpu(args):
                    "cuda_graphs": use_graphs, "device_status": device_code,
                    "parallelism": (f"ep{world}: experts sharded {E // world} per GPU; prefill: NCCL all-to-all dispatch + combine; decode: "
                                    + ("rows pushed over peer memory (NVLink) with flag barriers, one CUDA graph per step"
-                                      if args.ep_exchange == "peer" else "NCCL all-to-all, eager")) if ep else "single GPU",
+                                      if peer_exchange else "NCCL all-to-all, eager")) if ep else "single GPU",
                    "phase_ms": {"prefill": ms_prefill, "decode_b1_per_step": ms_dec1, f"decode_b{batch}_per_step": ms_decn},
                    "phase_tokens_per_s": {"prefill": prefill_tokens / ms_prefill * 1e3, "decode_b1": 1e3 / ms_dec1,
                                           f"decode_b{batch}": batch / ms_decn * 1e3}},

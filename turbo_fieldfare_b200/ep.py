@@ -219,7 +219,24 @@ class EPBuffers:
         self._recv_cap = 0
         self.ensure_recv(send_slots if fixed_capacity else max(n_pairs, 1))
         if self.peer:
-            self._map_peer_buffers(send_slots)
+            # Mapping is collective. If it fails on any rank (no peer access between two GPUs, IPC refused), every
+            # rank drops back to the NCCL exchange together, so the ranks never disagree about the path.
+            ok, why = 1, ""
+            try:
+                self._map_peer_buffers(send_slots)
+            except Exception as exc:          # noqa: BLE001 - any failure means "no peer path on this machine"
+                ok, why = 0, str(exc)
+            if stack.world > 1:
+                flag = torch.tensor([ok], dtype=torch.int32, device="cuda")
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=stack.group)
+                ok_all = int(flag.item())
+            else:
+                ok_all = ok
+            if not ok_all:
+                self._drop_peer_buffers()
+                self.peer = False
+                self.peer_failure = why or "another rank could not map the peer buffers"
+                self.ensure_recv_reset(send_slots)
 
     def _map_peer_buffers(self, slots: int) -> None:
         """One exchange buffer per rank: [receive area | return area | flags], mapped by every other rank (CUDA IPC).
@@ -234,15 +251,19 @@ class EPBuffers:
         self.flags_offset = (self.back_offset + back_bytes + 255) // 256 * 256
         total = self.flags_offset + 256
         handle = C.c_void_p()
-        ctx.check(lib.tf_peer_buffer_create(ctx.handle, total, C.byref(handle)))
-        self._peer_handle = handle
-        own = lib.tf_peer_buffer_ptr(handle)
         exported = C.create_string_buffer(64)
-        ctx.check(lib.tf_peer_buffer_export(handle, exported))
+        status = lib.tf_peer_buffer_create(ctx.handle, total, C.byref(handle))
+        if status == 0:
+            self._peer_handle = handle
+            status = lib.tf_peer_buffer_export(handle, exported)
+        own = lib.tf_peer_buffer_ptr(handle) if status == 0 else 0
         bases = [own]
         if stack.world > 1:
+            # every rank takes part in the gather even if its own allocation failed (None), so nobody waits alone
             gathered = [None] * stack.world
-            dist.all_gather_object(gathered, bytes(exported.raw), group=stack.group)
+            dist.all_gather_object(gathered, bytes(exported.raw) if status == 0 else None, group=stack.group)
+            if any(raw is None for raw in gathered):
+                raise RuntimeError("a rank could not allocate or export its exchange buffer")
             bases = []
             for r, raw in enumerate(gathered):
                 if r == stack.rank:
@@ -252,26 +273,37 @@ class EPBuffers:
                 ctx.check(lib.tf_peer_buffer_import(ctx.handle, C.create_string_buffer(raw, 64), C.byref(p)))
                 self._imported.append(p.value)
                 bases.append(p.value)
-            dist.barrier(group=stack.group)          # every rank has mapped every buffer before anyone writes
+        elif status != 0:
+            ctx.check(status)
         self.peer_bases = torch.tensor(bases, dtype=torch.int64, device="cuda")
         self.epoch = torch.zeros(2, dtype=torch.int32, device="cuda")       # epoch counter, ticket of the push kernel
         self.recv_rows = device_view_u8(own, recv_bytes).view(torch.float16)
         self.back_rows = device_view_u8(own + self.back_offset, back_bytes).view(torch.float16)
         torch.cuda.synchronize()
 
+    def _drop_peer_buffers(self) -> None:
+        ctx, lib = self.stack.context, self.stack.context.lib
+        for p in self._imported:
+            lib.tf_peer_buffer_release(ctx.handle, p)
+        self._imported = []
+        if self._peer_handle is not None:
+            lib.tf_peer_buffer_destroy(self._peer_handle)
+            self._peer_handle = None
+
+    def ensure_recv_reset(self, slots: int) -> None:
+        """Receive and return buffers of the NCCL exchange (after a peer mapping that did not come up)."""
+        self._recv_cap = 0
+        self.ensure_recv(slots)
+        self.back_rows = torch.zeros(slots * self.d, dtype=torch.float16, device="cuda")
+
     def close(self) -> None:
         """Unmaps the peers' buffers and frees this rank's (collective when peers are mapped)."""
         if self._peer_handle is None:
             return
-        ctx, lib = self.stack.context, self.stack.context.lib
         torch.cuda.synchronize()
         if self.stack.world > 1:
             dist.barrier(group=self.stack.group)     # nobody is still writing into a buffer that is about to go
-        for p in self._imported:
-            lib.tf_peer_buffer_release(ctx.handle, p)
-        self._imported = []
-        lib.tf_peer_buffer_destroy(self._peer_handle)
-        self._peer_handle = None
+        self._drop_peer_buffers()
 
     def ensure_recv(self, slots: int) -> None:
         if slots <= self._recv_cap:
