@@ -19,6 +19,7 @@ import statistics
 import subprocess
 import sys
 import time
+import traceback
 from pathlib import Path
 
 import numpy as np
@@ -94,8 +95,8 @@ def cpu_sample(sample_tokens: int, threads: int | None = None):
     Returns (tokens_per_s, cores, description, seconds)."""
     from oracle import oracle as o
     o.build()
-    if threads:
-        o.lib().tfo_set_num_threads(threads)
+    # all host cores, set explicitly: torchrun exports OMP_NUM_THREADS=1 to its workers
+    o.lib().tfo_set_num_threads(threads or host_cores())
     cores = o.num_threads()
     rng = np.random.default_rng(0)
     pool_experts = 16
@@ -126,6 +127,13 @@ def cpu_sample(sample_tokens: int, threads: int | None = None):
     return 1.0 / per_token_stack, cores, desc, dt
 
 
+def host_cores() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def workload_name(layers, prefill_tokens, steps_dec, batch):
     """The job both arms are quoted on (BASELINE config 4 at the default arguments)."""
     return (f"config4: {layers}-layer MoE stack (128 experts int4 g64, top-8, shared expert, RMSNorm between layers, "
@@ -138,7 +146,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 128
+    sample = args.cpu_sample_tokens          # the same sample as the GPU arm's cpu_baseline leg
     times, value, cores, desc = [], None, None, None
     for i in range(args.warmup + args.steps):
         v, cores, desc, dt = cpu_sample(sample)
@@ -232,6 +240,10 @@ def run_gpu(args):
     # on this software stack (the run was ended by its timeout).
     peer_exchange = ep and ws_b1.peer and ws_bn.peer       # False when the peer buffers could not be mapped
     use_graphs = not args.no_graphs and (not ep or peer_exchange)
+    if world > 1:
+        # the peer barriers inside the kernels wait a bounded time: line the ranks up on the host before the first one
+        torch.cuda.synchronize()
+        dist.barrier()
     g1 = capture(h1, 1, ws_b1) if use_graphs else None
     gn = capture(hn, batch, ws_bn) if use_graphs else None
     counters = {"launches": 0}
@@ -290,8 +302,17 @@ def run_gpu(args):
             ms = float(t.item())
         return ms / steps, clocks, counters["launches"]
 
+    def healthy(what):
+        # a bounded wait that ran out leaves the exchange unsynchronised: such a measurement is void
+        code = ctx.device_status()
+        if code:
+            raise RuntimeError(f"device status 0x{code:08x} after {what}: a kernel gave up a bounded wait")
+
     ms_step, clocks, n_launches = timed(False, args.steps, args.warmup)
-    ms_e2e, _, _ = timed(True, max(1, min(args.steps, 2)), 1)
+    healthy("the timed jobs")
+    e2e_steps = max(1, min(args.steps, 2))
+    ms_e2e, _, _ = timed(True, e2e_steps, 1)
+    healthy("the end-to-end jobs")
     tokens = tokens_per_job(prefill_tokens, steps_dec, batch) * world
     value = tokens / (ms_step * 1e-3)
     e2e_value = tokens / (ms_e2e * 1e-3)
@@ -337,7 +358,7 @@ def run_gpu(args):
                                           f"decode_b{batch}": batch / ms_decn * 1e3}},
         "clocks": clocks,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
-                "ms_per_step": ms_e2e},
+                "ms_per_step": ms_e2e, "steps": e2e_steps, "warmup": 1},
         "gpu_launches": n_launches,
         "roofline": roofline,
         "gemv_roofline": gemv,
@@ -454,10 +475,17 @@ def main():
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "b200":
         print(f"note: warmup {args.warmup} < 3 breaks the timing rules; use it for smoke runs only", file=sys.stderr)
-    if args.impl == "reference":
-        run_reference(args)
-    else:
-        run_gpu(args)
+    try:
+        if args.impl == "reference":
+            run_reference(args)
+        else:
+            run_gpu(args)
+    except BaseException as exc:
+        # a launcher that supervises several ranks reports only exit codes: say which rank failed and why
+        if not (isinstance(exc, SystemExit) and exc.code in (0, None)):
+            sys.stderr.write(f"rank {os.environ.get('RANK', '0')}: {type(exc).__name__}: {exc}\n{traceback.format_exc()}")
+            sys.stderr.flush()
+        raise
 
 
 if __name__ == "__main__":

@@ -140,6 +140,16 @@ uint64_t tf_launch_count(tf_context* ctx);
  * before creating the workspaces that should be able to take the tensor-core path. The reference picks its
  * prefill kernels by chunk size in the same way (RealForwardRunner.swift:902-1186). */
 tf_status tf_context_set_tensorcore_min_tokens(tf_context* ctx, uint32_t tokens);
+/* Profiling aid with no counterpart in the reference: when a device buffer of `capacity` 64-bit words is set, the
+ * single-launch one-token step of tf_stack_forward stamps the GPU's global nanosecond timer at every phase boundary
+ * (eight stamps per layer: start, norm, router + shared gate/up, barrier, routed gate/up, barrier, down + combine,
+ * barrier). NULL switches it off (the default). */
+tf_status tf_context_set_step_trace(tf_context* ctx, void* device_u64, uint32_t capacity);
+/* Chooses how tf_stack_forward runs a ONE-token step: as one persistent launch that walks all layers with grid
+ * barriers between the phases of a layer (enabled != 0), or layer by layer with the kernels of the block forward
+ * (0). New entry point: the reference has no equivalent of either (its decode step is one command buffer per
+ * phase, RealForwardRunner.swift:1449-1693). */
+tf_status tf_context_set_single_launch_step(tf_context* ctx, int enabled);
 /* Synchronises the device and reports whether any kernel abandoned one of its bounded waits
  * (mbarrier / flag polls never spin for ever: on expiry the kernel records a code and returns).
  * Replaces the command-buffer error check (Infrastructure/Metal/MetalContext.swift:22-26).
@@ -344,13 +354,30 @@ tf_status tf_shared_expert_int4_block_noalloc(void* stream,
 /* Y[M,N] = X[M,K] . dequant(W[N,K])^T, fp16 in/out, fp32 accumulation; the weight tile is staged as
  * half(q*s+b) and multiplied on the matrix unit. Replaces MPPPrefillInt4QMM.encode
  * (Kernels/TensorCore/MPPPrefillInt4QMM.swift:34-78; Metal/TensorCore/tensorops.metal:13-105).
- * K % 64 == 0 as there; M is free and N % 8 == 0 (the reference wants M % 32 == 0 and N % 64 == 0). */
+ * K % 64 == 0 as there; M and N are free. With N % 8 == 0 and 16-byte aligned planes the tcgen05 kernel runs;
+ * any other N, any byte offset of the packed plane and any even offset of the 16-bit planes (all accepted by the
+ * reference) run a CUDA-core kernel with the arithmetic of the reference's scalar QMM
+ * (Metal/Prefill/prefill.metal:672-709). */
 tf_status tf_int4_qmm(tf_context* ctx, void* stream,
                       const void* weights, uint64_t weights_off,
                       const void* scales, uint64_t scales_off,
                       const void* biases, uint64_t biases_off,
                       const void* x, uint64_t x_off, void* y, uint64_t y_off,
                       uint32_t m, uint32_t n, uint32_t k);
+/* The same call reporting which kernel ran, as MPPPrefillInt4QMM.encode returns its Path
+ * (MPPPrefillInt4QMM.swift:5-8). Inputs outside the reference's guard (K % 64 != 0, odd offsets of a 16-bit plane,
+ * an empty shape) launch nothing, set TF_QMM_PATH_UNAVAILABLE and return TF_OK: the caller falls back, as there. */
+typedef enum tf_qmm_path {
+    TF_QMM_PATH_UNAVAILABLE = 0,
+    TF_QMM_PATH_TENSORCORE = 1,    /* tcgen05 / TMEM (the reference's .affineThreadgroupF16) */
+    TF_QMM_PATH_CUDA_CORES = 2     /* unaligned planes or N % 8 != 0 */
+} tf_qmm_path;
+tf_status tf_int4_qmm_with_path(tf_context* ctx, void* stream,
+                                const void* weights, uint64_t weights_off,
+                                const void* scales, uint64_t scales_off,
+                                const void* biases, uint64_t biases_off,
+                                const void* x, uint64_t x_off, void* y, uint64_t y_off,
+                                uint32_t m, uint32_t n, uint32_t k, tf_qmm_path* path_out);
 /* Gathers the hidden row of every (token, expert) pair into x_sorted[T*top_k, D] in the order of
  * routes->sorted_pairs, with every eight columns stored in the order (0,4,1,5,2,6,3,7) that
  * tf_grouped_moe_tensorcore reads, and records inverse_perm[token*top_k + rank] = sorted row.

@@ -78,6 +78,8 @@ SIGNATURES = {
     "tf_context_create": (C.c_int, [C.c_int, C.POINTER(vp)]),
     "tf_context_destroy": (None, [vp]),
     "tf_last_error": (C.c_char_p, [vp]),
+    "tf_context_set_step_trace": (C.c_int, [vp, vp, u32]),
+    "tf_context_set_single_launch_step": (C.c_int, [vp, C.c_int]),
     "tf_launch_count": (u64, [vp]),
     "tf_device_status": (C.c_int, [vp, C.POINTER(u32)]),
     "tf_int4_gemv": (C.c_int, [vp, vp, *_PLANES, vp, u64, vp, u64, u32, u32, C.c_int]),
@@ -103,6 +105,7 @@ SIGNATURES = {
                                               C.POINTER(Projection), vp, u64, u32, vp, u32]),
     "tf_context_set_tensorcore_min_tokens": (C.c_int, [vp, u32]),
     "tf_int4_qmm": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, vp, u64, vp, u64, u32, u32, u32]),
+    "tf_int4_qmm_with_path": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, vp, u64, vp, u64, u32, u32, u32, C.POINTER(C.c_int)]),
     "tf_pack_sorted_rows": (C.c_int, [vp, vp, vp, u32, C.POINTER(DeviceRoutes), u32, u32, u32, u32, vp, vp, vp]),
     "tf_grouped_moe_tensorcore": (C.c_int, [vp, vp, vp, u32, vp, u64, u32, C.POINTER(ExpertOffsets),
                                             C.POINTER(DeviceRoutes), vp, vp, u32, u32]),

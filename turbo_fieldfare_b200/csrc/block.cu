@@ -9,43 +9,7 @@
 //   - the MoE section of the forward runner (Runtime/Inference/RealForwardRunner.swift:902-1186
 //     prefill, :1449-1693 decode), whose two CPU<->GPU round trips per layer exist only to
 //     plan SSD reads: here router ids, grouping and expert addressing stay on the device.
-#include <vector>
-
-#include "tf_common.cuh"
-
-struct tf_pool {
-    tf_context* ctx;
-    uint8_t* base;
-    uint32_t layers, experts;
-    uint64_t stride;
-    tf_expert_offsets offsets;
-};
-
-struct tf_workspace {
-    tf_context* ctx;
-    uint32_t max_tokens, d, f, fs, top_k, num_experts;
-    uint8_t* base;          // one allocation
-    uint32_t* indices;      // [T, K]
-    uint16_t* weights;      // [T, K] fp16
-    tf_device_routes routes;
-    uint16_t* acts;         // [T*K, F] fp16
-    void* partials;         // [T, K, D] fp32 (T <= f32_tokens) or fp16
-    uint16_t* shared_act;   // [T, Fs]
-    uint16_t* shared_y;     // [T, D]
-    uint16_t* x_norm;       // [T, D] (stack)
-    uint16_t* y_block;      // [T, D] (stack)
-    uint16_t* x_sorted;     // [T*K, D] expert-sorted activation rows (tensor-core path; NULL for small workspaces)
-    uint32_t* inverse_perm; // [T*K] sorted row of every (token, rank)
-    uint32_t* pack_ids;     // [T*K]
-    uint64_t bytes;
-};
-
-struct tf_stack {
-    tf_context* ctx;
-    std::vector<tf_moe_layer> layers;
-    std::vector<const void*> norm_weights;   // bf16 [D] per layer
-    float eps;
-};
+#include "block.cuh"
 
 namespace tf {
 
@@ -512,11 +476,16 @@ tf_status tf_stack_create(tf_context* ctx, const tf_moe_layer* layers, const voi
     st->eps = eps;
     st->layers.assign(layers, layers + layer_count);
     st->norm_weights.assign(norm_weights_bf16, norm_weights_bf16 + layer_count);
+    if (tf_status s = tf::decode_step_prepare(ctx, st)) { delete st; return s; }
     *out = st;
     return TF_OK;
 }
 
-void tf_stack_destroy(tf_stack* st) { delete st; }
+void tf_stack_destroy(tf_stack* st) {
+    if (!st) return;
+    if (st->device_layers) cudaFree(st->device_layers);
+    delete st;
+}
 
 // hidden [tokens, d] fp16, contiguous, updated in place:
 //   for each layer: x = rmsnorm(h) * w_l;  h = h + block_l(x)
@@ -533,6 +502,8 @@ tf_status tf_stack_forward(tf_stack* st, void* stream, void* hidden, uint32_t to
     TF_REQUIRE(ctx, d % 8 == 0 && d <= 8u * tf::kRrnThreads * tf::kRrnMaxSlices, TF_ERR_UNSUPPORTED,
                "%s: D must be a multiple of 8 and at most %d", name, 8 * tf::kRrnThreads * tf::kRrnMaxSlices);
     TF_REQUIRE(ctx, tf::aligned(hidden, 16), TF_ERR_ALIGNMENT, "%s: hidden must be 16-byte aligned", name);
+    // one token: the whole step is one persistent launch (decode_step.cu)
+    if (tokens == 1 && ctx->single_launch_step && tf::decode_step_eligible(st, ws)) return tf::launch_decode_step(ctx, stream, st, hidden, ws);
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     uint16_t* h = static_cast<uint16_t*>(hidden);
     for (size_t l = 0; l < st->layers.size(); ++l) {

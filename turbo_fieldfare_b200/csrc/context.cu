@@ -77,6 +77,8 @@ tf_status tf_context_create(int device, tf_context** out) {
     if (e == cudaSuccess) e = cudaMemset(ctx->router_tickets, 0, sizeof(unsigned int) * (tf::kRouterSplitRows + 1));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->device_error, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->device_error, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->grid_barrier, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(ctx->grid_barrier, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_groups, 2 * 64 * (TF_MAX_ROUTER_EXPERTS + 1));   // routed and dense tables
     if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_totals, 4 * sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->side_stream, cudaStreamNonBlocking);
@@ -97,6 +99,7 @@ void tf_context_destroy(tf_context* ctx) {
     if (ctx->router_logits) cudaFree(ctx->router_logits);
     if (ctx->router_tickets) cudaFree(ctx->router_tickets);
     if (ctx->device_error) cudaFree(ctx->device_error);
+    if (ctx->grid_barrier) cudaFree(ctx->grid_barrier);
     if (ctx->qmm_groups) cudaFree(ctx->qmm_groups);
     if (ctx->qmm_totals) cudaFree(ctx->qmm_totals);
     if (ctx->lm_x) cudaFree(ctx->lm_x);
@@ -118,6 +121,20 @@ uint64_t tf_launch_count(tf_context* ctx) { return ctx ? ctx->launches : 0; }
 tf_status tf_context_set_tensorcore_min_tokens(tf_context* ctx, uint32_t tokens) {
     TF_REQUIRE(ctx, ctx != nullptr && tokens > 0, TF_ERR_INVALID_ARGUMENT, "tf_context_set_tensorcore_min_tokens: ctx is NULL or tokens is 0");
     ctx->tensorcore_min_tokens = tokens;
+    return TF_OK;
+}
+
+tf_status tf_context_set_single_launch_step(tf_context* ctx, int enabled) {
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_context_set_single_launch_step: ctx is NULL");
+    ctx->single_launch_step = enabled != 0;
+    return TF_OK;
+}
+
+tf_status tf_context_set_step_trace(tf_context* ctx, void* device_u64, uint32_t capacity) {
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_context_set_step_trace: ctx is NULL");
+    TF_REQUIRE(ctx, device_u64 == nullptr || tf::aligned(device_u64, 8), TF_ERR_ALIGNMENT, "tf_context_set_step_trace: the buffer must be 8-byte aligned");
+    ctx->step_trace = static_cast<unsigned long long*>(device_u64);
+    ctx->step_trace_capacity = device_u64 ? capacity : 0;
     return TF_OK;
 }
 

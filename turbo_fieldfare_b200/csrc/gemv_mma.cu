@@ -11,7 +11,7 @@
 // memory in fragment order. Scale and bias are applied per group to the fp32 accumulator, acc += s * (q . x)
 // + b * sum(x), the reference's algebra (dequant_int4.metal:132-170). Four groups are in flight as
 // independent MMA chains, and the next four groups' codes are loaded before the current ones are consumed.
-#include "tf_common.cuh"
+#include "mma_gemv.cuh"
 
 namespace tf {
 
@@ -19,27 +19,6 @@ constexpr int kGmWarps = 8;                 // 16 rows each: 128 rows per block
 constexpr int kGmThreads = kGmWarps * kWarp;
 constexpr int kGmRows = kGmWarps * 16;
 constexpr int kGmBlockGroups = 4;           // groups per inner step (independent MMA chains)
-
-__device__ __forceinline__ uint32_t gm_prmt(uint32_t a, uint32_t b, uint32_t sel) {
-    uint32_t r;
-    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
-    return r;
-}
-__device__ __forceinline__ uint32_t gm_sixteenth(uint32_t v) {
-    const __half2 r = __hmul2(*reinterpret_cast<const __half2*>(&v), __half2half2(__float2half_rn(0.0625f)));
-    return *reinterpret_cast<const uint32_t*>(&r);
-}
-__device__ __forceinline__ void gm_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1,
-                                       const float (&z)[4]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
-                 : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(z[0]), "f"(z[1]), "f"(z[2]), "f"(z[3]));
-}
-__device__ __forceinline__ uint2 gm_ldg64(const uint8_t* p) {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
-}
 
 // Shared memory: B fragments of x [ng][4 lanes t][8 words], group sums [ng], scale and bias planes of the block's
 // 128 rows [128][ng] each.

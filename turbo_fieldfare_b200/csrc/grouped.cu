@@ -30,7 +30,7 @@
 // (deterministic), apply the epilogue and store. No warp ever meets another at a
 // block-wide barrier in the steady state. Every mbarrier wait is bounded: on expiry
 // the kernel records an error code and returns.
-#include "tf_common.cuh"
+#include "async_copy.cuh"
 
 namespace tf {
 
@@ -141,7 +141,6 @@ constexpr int kReducers = 2;            // reducer warps; reducer q owns the ite
 constexpr int kRedStages = kReducers;   // partial-sum buffers
 constexpr int kTileRows = 16;           // weight rows per MMA tile (the m of m16n8k16)
 constexpr int kMaxComputeWarps = 12;    // K <= 12 * 256 = 3072 columns
-constexpr uint32_t kSpinLimit = 1u << 21;
 constexpr uint32_t kErrTimeoutCodes = 0x7F000001u;   // device error words
 constexpr uint32_t kErrTimeoutPartials = 0x7F000003u;
 constexpr uint32_t kErrTimeoutRedFree = 0x7F000004u;
@@ -223,30 +222,6 @@ __device__ __forceinline__ void sts_f32x2(uint32_t addr, float a, float b) {
     asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
 }
 
-// ---- mbarrier and bulk-copy primitives (all waits are bounded) ----
-__device__ __forceinline__ void mbar_init(uint32_t addr, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(addr), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t addr) {
-    asm volatile("{ .reg .b64 st; mbarrier.arrive.shared::cta.b64 st, [%0]; }" ::"r"(addr) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t addr, uint32_t bytes) {
-    asm volatile("{ .reg .b64 st; mbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1; }" ::"r"(addr), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t addr, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
-        uint32_t ok;
-        asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t smem_dst, const void* gmem_src, uint32_t bytes, uint32_t mbar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(mbar) : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 enum OutMode { kOutActs = 0, kOutPartialF16 = 1, kOutPartialF32 = 2, kOutDenseF16 = 3 };
 

@@ -707,6 +707,9 @@ static tf_status launch_qmm(tf_context* ctx, void* stream, QmmArgs& a, const voi
     return check_launch(ctx, name);
 }
 
+tf_status launch_qmm_generic(tf_context* ctx, void* stream, const uint8_t* W, const uint16_t* S, const uint16_t* B,
+                             const uint16_t* X, uint16_t* Y, uint32_t m, uint32_t n, uint32_t k, const char* name);   // qmm_generic.cu
+
 }  // namespace tf
 
 extern "C" {
@@ -745,23 +748,51 @@ tf_status tf_grouped_moe_tensorcore(tf_context* ctx, void* stream, const void* x
                                     "tf_grouped_moe_tensorcore(down)");
 }
 
+tf_status tf_int4_qmm_with_path(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off, const void* scales,
+                                uint64_t scales_off, const void* biases, uint64_t biases_off, const void* x, uint64_t x_off,
+                                void* y, uint64_t y_off, uint32_t m, uint32_t n, uint32_t k, tf_qmm_path* path_out) {
+    const char* name = "tf_int4_qmm";
+    if (path_out) *path_out = TF_QMM_PATH_UNAVAILABLE;
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, weights && scales && biases && x && y, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    const uint8_t* wp = tf::byte_ptr(weights, weights_off);
+    const uint8_t* sp = tf::byte_ptr(scales, scales_off);
+    const uint8_t* bp = tf::byte_ptr(biases, biases_off);
+    const uint8_t* xp = tf::byte_ptr(x, x_off);
+    uint8_t* yp = tf::byte_ptr(y, y_off);
+    // the reference's guard (MPPPrefillInt4QMM.swift:43-55): positive sizes, K % 64 == 0, even 16-bit plane offsets
+    const bool supported = m > 0 && n > 0 && k > 0 && k % 64 == 0 && tf::aligned(sp, 2) && tf::aligned(bp, 2) &&
+                           tf::aligned(xp, 2) && tf::aligned(yp, 2);
+    if (!supported) {
+        if (path_out) return TF_OK;         // the reference reports .unavailable and the caller falls back
+        TF_REQUIRE(ctx, m == 0 || n == 0 || (k % 64 == 0 && k > 0), TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);
+        if (m == 0 || n == 0) return TF_OK;
+        return tf::fail(ctx, TF_ERR_ALIGNMENT, "%s: scale, bias, x and y offsets must be even", name);
+    }
+    const bool tensor = n % 8 == 0 && tf::aligned(wp, 16) && tf::aligned(sp, 16) && tf::aligned(bp, 16) && tf::aligned(xp, 16);
+    if (!tensor) {
+        // odd row counts or planes off the 16-byte grid: the CUDA-core kernel takes any byte offset
+        tf_status s = tf::launch_qmm_generic(ctx, stream, wp, reinterpret_cast<const uint16_t*>(sp), reinterpret_cast<const uint16_t*>(bp),
+                                             reinterpret_cast<const uint16_t*>(xp), reinterpret_cast<uint16_t*>(yp), m, n, k, name);
+        if (!s && path_out) *path_out = TF_QMM_PATH_CUDA_CORES;
+        return s;
+    }
+    tf::QmmArgs a{};
+    const uint8_t* w[2] = {wp, wp};
+    a.dense_S[0] = reinterpret_cast<const uint16_t*>(sp);
+    a.dense_B[0] = reinterpret_cast<const uint16_t*>(bp);
+    a.dense_tokens = m; a.rows = n; a.k = k;
+    a.out = reinterpret_cast<uint16_t*>(yp); a.out_stride = n;
+    tf_status s = tf::launch_qmm<1, true>(ctx, stream, a, xp, m, k, w, 1, 0, true, name);
+    if (!s && path_out) *path_out = TF_QMM_PATH_TENSORCORE;
+    return s;
+}
+
 tf_status tf_int4_qmm(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off, const void* scales,
                       uint64_t scales_off, const void* biases, uint64_t biases_off, const void* x, uint64_t x_off,
                       void* y, uint64_t y_off, uint32_t m, uint32_t n, uint32_t k) {
-    const char* name = "tf_int4_qmm";
-    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
-    TF_REQUIRE(ctx, weights && scales && biases && x && y, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
-    TF_REQUIRE(ctx, k % 64 == 0 && k > 0, TF_ERR_INVALID_ARGUMENT, "%s: K must be a positive multiple of 64", name);   // MPPPrefillInt4QMM.swift:43-55
-    if (m == 0 || n == 0) return TF_OK;
-    tf::QmmArgs a{};
-    const uint8_t* w[2] = {tf::byte_ptr(weights, weights_off), tf::byte_ptr(weights, weights_off)};
-    a.dense_S[0] = reinterpret_cast<const uint16_t*>(tf::byte_ptr(scales, scales_off));
-    a.dense_B[0] = reinterpret_cast<const uint16_t*>(tf::byte_ptr(biases, biases_off));
-    TF_REQUIRE(ctx, tf::aligned(w[0], 16) && tf::aligned(a.dense_S[0], 16) && tf::aligned(a.dense_B[0], 16),
-               TF_ERR_ALIGNMENT, "%s: weight, scale and bias planes must be 16-byte aligned", name);
-    a.dense_tokens = m; a.rows = n; a.k = k;
-    a.out = reinterpret_cast<uint16_t*>(tf::byte_ptr(y, y_off)); a.out_stride = n;
-    return tf::launch_qmm<1, true>(ctx, stream, a, tf::byte_ptr(x, x_off), m, k, w, 1, 0, true, name);
+    return tf_int4_qmm_with_path(ctx, stream, weights, weights_off, scales, scales_off, biases, biases_off, x, x_off, y, y_off,
+                                 m, n, k, nullptr);
 }
 
 tf_status tf_shared_expert_int4_tensorcore(tf_context* ctx, void* stream, const void* x, uint32_t x_stride_elements,

@@ -41,6 +41,13 @@ struct tf_context {
     unsigned int* router_tickets = nullptr;  // [kRouterSplitRows], self-resetting
     // One device word that kernels with bounded waits set when a wait gives up (0 = healthy).
     uint32_t* device_error = nullptr;
+    // Arrival counter of the grid barriers of the single-launch decode step (zeroed on the stream before each launch).
+    uint32_t* grid_barrier = nullptr;
+    // tf_stack_forward runs a one-token step as one persistent launch when set (tf_context_set_single_launch_step).
+    bool single_launch_step = false;
+    // Optional caller-owned device buffer that the single-launch decode step fills with global-timer stamps.
+    unsigned long long* step_trace = nullptr;
+    uint32_t step_trace_capacity = 0;
     // Group tables and tile totals of the tensor-core grouped GEMM (filled on the device per launch): one set for
     // routed launches and one for dense launches, which may run on two streams at once.
     void* qmm_groups = nullptr;

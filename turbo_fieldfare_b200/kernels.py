@@ -71,6 +71,10 @@ class TurboContext:
         """Blocks of at least ``tokens`` tokens run their expert GEMMs on the tensor cores (default 256)."""
         self.check(self.lib.tf_context_set_tensorcore_min_tokens(self.handle, tokens))
 
+    def set_single_launch_step(self, enabled: bool) -> None:
+        """One-token stack steps as one persistent launch (True) or layer by layer (False)."""
+        self.check(self.lib.tf_context_set_single_launch_step(self.handle, 1 if enabled else 0))
+
     @property
     def launch_count(self) -> int:
         return int(self.lib.tf_launch_count(self.handle))
@@ -455,10 +459,16 @@ class MPPPrefillInt4QMM:
 
     def encode(self, weights, scales, biases, x, y, m: int, n: int, k: int, *, weights_offset=0, scales_offset=0,
                biases_offset=0, x_offset=0, y_offset=0, stream=None):
+        """Returns the path that ran: ``"affine-threadgroup-f16"`` (tensor cores), ``"cuda-cores"`` (planes off the
+        16-byte grid or N % 8 != 0) or ``"unavailable"`` (outside the reference's guard; nothing launched)."""
         ctx = self.context
-        ctx.check(ctx.lib.tf_int4_qmm(ctx.handle, _stream(stream), _ptr(weights), weights_offset, _ptr(scales),
-                                      scales_offset, _ptr(biases), biases_offset, _ptr(x), x_offset, _ptr(y), y_offset,
-                                      m, n, k))
+        path = C.c_int(0)
+        ctx.check(ctx.lib.tf_int4_qmm_with_path(ctx.handle, _stream(stream), _ptr(weights), weights_offset, _ptr(scales),
+                                                scales_offset, _ptr(biases), biases_offset, _ptr(x), x_offset, _ptr(y),
+                                                y_offset, m, n, k, C.byref(path)))
+        return self.PATHS[path.value]
+
+    PATHS = ("unavailable", "affine-threadgroup-f16", "cuda-cores")
 
 
 class PrefillMoE:
