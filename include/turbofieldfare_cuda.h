@@ -166,6 +166,19 @@ tf_status tf_int4_gemv(tf_context* ctx, void* stream,
                        const void* biases, uint64_t biases_off,
                        const void* x, uint64_t x_off, void* y, uint64_t y_off,
                        uint32_t m, uint32_t n, tf_dtype sb_dtype);
+/* `count` such GEMVs in ONE launch over matrices of one shape whose three planes repeat every matrix_stride_bytes
+ * (e.g. the gate tensor of consecutive expert blobs: stride = the blob stride): y[b] = deq4(W[b]) . x[b]. x and y
+ * advance by their strides in elements per matrix; x_stride_elements 0 multiplies every matrix with the same vector.
+ * New entry point: the reference encodes one DequantInt4GEMV per matrix (DequantInt4GEMV.swift:44-87); this is
+ * how a sweep of expert-sized GEMVs reaches HBM speed. Same preconditions as tf_int4_gemv. */
+tf_status tf_int4_gemv_batched(tf_context* ctx, void* stream,
+                               const void* weights, uint64_t weights_off,
+                               const void* scales, uint64_t scales_off,
+                               const void* biases, uint64_t biases_off,
+                               uint64_t matrix_stride_bytes,
+                               const void* x, uint64_t x_off, uint32_t x_stride_elements,
+                               void* y, uint64_t y_off, uint32_t y_stride_elements,
+                               uint32_t m, uint32_t n, uint32_t count, tf_dtype sb_dtype);
 /* Replaces DequantInt8GEMV.encode (Kernels/Quant/DequantInt8GEMV.swift:50-81). */
 tf_status tf_int8_gemv(tf_context* ctx, void* stream,
                        const void* weights, uint64_t weights_off,

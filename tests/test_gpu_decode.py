@@ -130,7 +130,8 @@ def _run_router(tf_ctx, o, mat, hidden16, eff16, gain16, rows=None, stride=None,
 
 
 @pytest.mark.parametrize("rows,E,D,skew", [(1, 128, 2816, 0.0), (5, 128, 2816, 0.0), (64, 128, 2816, 0.0),
-                                           (64, 128, 2816, 6.0), (37, 16, 128, 0.0), (64, 256, 256, 2.0), (100, 128, 2816, 0.0)])
+                                           (64, 128, 2816, 6.0), (37, 16, 128, 0.0), (64, 256, 256, 2.0), (100, 128, 2816, 0.0),
+                                           (1, 128, 2816, -np.inf), (3, 16, 128, -np.inf)])
 def test_router_with_grouping_in_one_launch_equals_the_two_calls(tf_ctx, oracle, rows, E, D, skew):
     """Blocks of at most 64 rows route and group in one launch (the block that finishes the last row sorts the
     pairs); every routing table must equal what the router followed by the grouping launch writes, skewed loads
@@ -145,7 +146,12 @@ def test_router_with_grouping_in_one_launch_equals_the_two_calls(tf_ctx, oracle,
     eff = o.f32_to_bf16(np.full(D, 1.0 / np.sqrt(D), np.float32))
     gain = o.f32_to_bf16(np.ones(E, np.float32))
     bias = None
-    if skew:
+    if skew == -np.inf:
+        # only three experts stay selectable: the selection repeats expert 0 for the missing picks, and the grouping
+        # has to merge the repeats into one group
+        b = np.full(E, -np.inf, np.float32); b[[2, 5, E - 1]] = 0.0
+        bias = to_dev(b)
+    elif skew:
         b = np.zeros(E, np.float32); b[3] = skew; b[E - 1] = skew / 2
         bias = to_dev(b)
     W, S, B = to_dev(mat.packed), to_dev(mat.scales), to_dev(mat.biases)
@@ -169,6 +175,8 @@ def test_router_with_grouping_in_one_launch_equals_the_two_calls(tf_ctx, oracle,
     PrefillGroupedRoutedMoE(tf_ctx).encode_group_routes(idx0, w0, rows, K, E, ref_routes)
     want = tables(ref_routes, idx0, w0)
     assert want["counters"][2] == rows * K and want["counts"].sum() == rows * K
+    if skew == -np.inf:
+        assert want["counters"][0] == 4 and want["counts"][0] == rows * (K - 3)      # experts 0 (repeated), 2, 5, E - 1
     for attempt in range(2):
         routes = DeviceRoutes(rows, K, E)
         idx1 = torch.full((rows, K), -1, dtype=torch.int32, device="cuda"); w1 = dev_zeros_u16(rows * K)
@@ -641,3 +649,44 @@ def test_int4_gemv_streaming_kernel_for_large_matrices(tf_ctx, oracle, m, n, sb)
     ref = o.gemv_ref(mat, o.f16_to_f32(x16))
     assert np.isfinite(got).all()
     assert o.rel_error(got, ref) < 5e-3
+
+
+@pytest.mark.parametrize("m,n,count,shared_x", [(704, 2816, 7, True), (704, 2816, 3, False), (72, 256, 5, True), (96, 192, 4, False)])
+def test_int4_gemv_batched_over_expert_blobs(tf_ctx, oracle, m, n, count, shared_x):
+    """One launch over the same tensor of consecutive expert blobs (config-0 matrices 704 x 2816 at the blob stride)
+    equals one tf_int4_gemv per matrix bit for bit where both run the same kernel family, and the oracle within the
+    GEMV tolerance; n = 192 takes the per-matrix fallback."""
+    import torch
+    from turbo_fieldfare_b200.kernels import DequantInt4GEMV
+    o = oracle
+    rng = np.random.default_rng(m + n + count)
+    mats = [config0_matrix(o, m, n, rng) for _ in range(count)]
+    w_bytes, sb_bytes = m * n // 2, m * (n // 64) * 2
+    s_off = (w_bytes + 255) // 256 * 256
+    b_off = s_off + (sb_bytes + 255) // 256 * 256
+    stride = (b_off + sb_bytes + 16383) // 16384 * 16384
+    blob = np.zeros(count * stride, dtype=np.uint8)
+    for b, mat in enumerate(mats):
+        blob[b * stride:b * stride + w_bytes] = mat.packed.reshape(-1)
+        blob[b * stride + s_off:b * stride + s_off + sb_bytes] = mat.scales.view(np.uint8).reshape(-1)
+        blob[b * stride + b_off:b * stride + b_off + sb_bytes] = mat.biases.view(np.uint8).reshape(-1)
+    xs = o.f32_to_f16(rng.standard_normal((1 if shared_x else count, n)).astype(np.float32))
+    dev = to_dev(blob)
+    x = to_dev(xs)
+    y = dev_zeros_u16(count * m, fill=0x7E00)
+    op = DequantInt4GEMV(tf_ctx)
+    before = tf_ctx.launch_count
+    op.encode_batched(dev, dev, dev, stride, x, y, m, n, count, scales_offset=s_off, biases_offset=b_off,
+                      x_stride_elements=0 if shared_x else n)
+    torch.cuda.synchronize()
+    assert tf_ctx.launch_count - before == (1 if n % 256 == 0 else count)
+    got = from_dev(y, np.uint16).reshape(count, m)
+    for b, mat in enumerate(mats):
+        xb = xs[0 if shared_x else b]
+        ref = o.gemv_ref(mat, o.f16_to_f32(xb))
+        assert o.rel_error(o.f16_to_f32(got[b]), ref) < FP16_REDUCTION, b
+        y1 = dev_zeros_u16(m)
+        op.encode(dev, dev, dev, to_dev(xb), y1, m, n, weights_offset=b * stride, scales_offset=b * stride + s_off,
+                  biases_offset=b * stride + b_off)
+        torch.cuda.synchronize()
+        assert o.rel_error(o.f16_to_f32(got[b]), o.f16_to_f32(from_dev(y1, np.uint16))) < 2e-3, b

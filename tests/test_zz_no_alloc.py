@@ -68,3 +68,43 @@ def test_noalloc_entry_rejects_blocks_beyond_its_scratch(tf_ctx):
     assert st != 0
     msg = lib.tf_last_error(None).decode()
     assert "scratch" in msg and "tf_shared_expert_int4_block" in msg       # 249 * 2112 * 2 bytes > 1 MiB
+
+
+def test_second_gpu_gets_its_own_kernel_attributes(oracle):
+    """Kernel attributes (the raised shared-memory limit) belong to a device: after GPU 0 has run the kernels, both
+    entry points must still work on GPU 1 in the same process. Needs two GPUs."""
+    import torch
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from turbo_fieldfare_b200 import _capi
+    from turbo_fieldfare_b200.kernels import PrefillSharedExpert, TurboContext, _ptr
+    o = oracle
+    lib = _capi.load()
+    rng = np.random.default_rng(77)
+    D, Fs, T = 2816, 2112, 12                 # production width: the kernels need more than 48 KB of shared memory
+    gate, up, down = config0_matrix(o, Fs, D, rng), config0_matrix(o, Fs, D, rng), config0_matrix(o, D, Fs, rng)
+    x16 = o.f32_to_f16(rng.standard_normal((T, D)).astype(np.float32))
+    outs = []
+    for device in (0, 1):
+        torch.cuda.set_device(device)
+        ctx = TurboContext(device)
+        try:
+            pg, pu, pd = _projection(gate), _projection(up), _projection(down)
+            x = to_dev(x16)
+            y_ref = dev_zeros_u16(T * D, fill=0x7E00)
+            scratch = dev_zeros_u16(T * Fs)
+            PrefillSharedExpert(ctx).encode_block(x, pg, pu, pd, y_ref, scratch, T)
+            y = dev_zeros_u16(T * D, fill=0x7E00)
+            g, u, dn = pg.c_struct(), pu.c_struct(), pd.c_struct()
+            st = lib.tf_shared_expert_int4_block_noalloc(None, _ptr(x), 0, D, C.byref(g), C.byref(u), C.byref(dn),
+                                                         _ptr(y), 0, D, T, None)
+            assert st == 0, lib.tf_last_error(None).decode()
+            torch.cuda.synchronize()
+            assert ctx.device_status() == 0
+            a, b = from_dev(y, np.uint16), from_dev(y_ref, np.uint16)
+            assert np.array_equal(a, b)
+            outs.append(a)
+        finally:
+            ctx.close()
+            torch.cuda.set_device(0)
+    assert np.array_equal(outs[0], outs[1])

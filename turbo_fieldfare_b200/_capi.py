@@ -83,6 +83,7 @@ SIGNATURES = {
     "tf_launch_count": (u64, [vp]),
     "tf_device_status": (C.c_int, [vp, C.POINTER(u32)]),
     "tf_int4_gemv": (C.c_int, [vp, vp, *_PLANES, vp, u64, vp, u64, u32, u32, C.c_int]),
+    "tf_int4_gemv_batched": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, u64, vp, u64, u32, vp, u64, u32, u32, u32, u32, C.c_int]),
     "tf_int8_gemv": (C.c_int, [vp, vp, *_PLANES, vp, u64, vp, u64, u32, u32, C.c_int]),
     "tf_router_gemma4": (C.c_int, [vp, vp, *_PLANES, vp, vp, u64, vp, u64, vp, vp, vp, u32, u32, u32]),
     "tf_router_gemma4_block": (C.c_int, [vp, vp, *_PLANES, vp, u64, C.c_int, vp, u64, vp, u64, vp,

@@ -77,6 +77,8 @@ tf_status tf_context_create(int device, tf_context** out) {
     if (e == cudaSuccess) e = cudaMemset(ctx->router_tickets, 0, sizeof(unsigned int) * (tf::kRouterSplitRows + 1));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->device_error, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->device_error, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->peer_error, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMemset(ctx->peer_error, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->grid_barrier, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->grid_barrier, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_groups, 2 * 64 * (TF_MAX_ROUTER_EXPERTS + 1));   // routed and dense tables
@@ -99,6 +101,7 @@ void tf_context_destroy(tf_context* ctx) {
     if (ctx->router_logits) cudaFree(ctx->router_logits);
     if (ctx->router_tickets) cudaFree(ctx->router_tickets);
     if (ctx->device_error) cudaFree(ctx->device_error);
+    if (ctx->peer_error) cudaFree(ctx->peer_error);
     if (ctx->grid_barrier) cudaFree(ctx->grid_barrier);
     if (ctx->qmm_groups) cudaFree(ctx->qmm_groups);
     if (ctx->qmm_totals) cudaFree(ctx->qmm_totals);
@@ -141,11 +144,15 @@ tf_status tf_context_set_step_trace(tf_context* ctx, void* device_u64, uint32_t 
 tf_status tf_device_status(tf_context* ctx, uint32_t* code_out) {
     TF_REQUIRE(ctx, ctx != nullptr && code_out != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_device_status: NULL argument");
     TF_CUDA(ctx, cudaDeviceSynchronize());
-    TF_CUDA(ctx, cudaMemcpy(code_out, ctx->device_error, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    uint32_t kernel_code = 0, peer_code = 0;
+    TF_CUDA(ctx, cudaMemcpy(&kernel_code, ctx->device_error, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    TF_CUDA(ctx, cudaMemcpy(&peer_code, ctx->peer_error, sizeof(uint32_t), cudaMemcpyDeviceToHost));
+    *code_out = kernel_code ? kernel_code : peer_code;
     if (*code_out != 0) {
         const uint32_t code = *code_out;
         TF_CUDA(ctx, cudaMemset(ctx->device_error, 0, sizeof(uint32_t)));
-        return tf::fail(ctx, TF_ERR_CUDA, "a kernel gave up a bounded wait (device code 0x%08x)", code);
+        TF_CUDA(ctx, cudaMemset(ctx->peer_error, 0, sizeof(uint32_t)));
+        return tf::fail(ctx, TF_ERR_CUDA, "a kernel gave up a bounded wait (device code 0x%08x); results since the last check are invalid", code);
     }
     return TF_OK;
 }

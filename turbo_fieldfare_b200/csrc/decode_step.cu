@@ -8,37 +8,44 @@
 //       in shared memory as MMA B-fragments
 //   P1  router logits (canonical fp32 order of router.cuh, one expert row per CTA) and the shared expert's
 //       gate/up rows, split evenly over the CTAs                                              -> barrier 1
-//   P2  every CTA selects the top-k from the 128 logits (same warp routine as the router kernels), then the
-//       routed experts' gate/up rows, K * F row pairs split evenly over the CTAs               -> barrier 2
+//   P2  every CTA selects the top-k from the logits (same warp routine as the router kernels), then the routed
+//       experts' gate/up rows, K * F row pairs split evenly over the CTAs                      -> barrier 2
 //   P3  down projections of the K routed experts and of the shared expert for the CTA's slice of output rows,
 //       the weighted combine in rank order (Metal/MoE/moe.metal:473-480) and the residual add  -> barrier 3
 //
-// Weight rows are consumed straight from global memory by warps that own 16 rows x up to 4 column groups (the
-// mma.sync GEMV building block of mma_gemv.cuh); a CTA's rows of a phase are cut into such items, partial sums meet
-// in shared memory and are added in a fixed order, so the result does not depend on timing. Everything that does
-// not depend on the router (next phase's rows, the next layer's router row and shared rows) is prefetched into L2
-// while the current phase streams, so only the routed gate/up rows are waited for at DRAM latency.
+// Weights never wait for a warp: a loader warp streams the CTA's rows of P1, P2, P3, then the next layer's P1, ...
+// through a ring of shared-memory stages (16 rows each, one cp.async.bulk per row, completion on an mbarrier) as
+// far ahead as the ring and the router allow (the rows of P2 and P3 are known once the layer's top-k is), so HBM
+// keeps streaming across the grid barriers. Sixteen compute warps consume the stages in items of 16 rows x up to 4
+// column groups with the mma.sync GEMV building block of mma_gemv.cuh; partial sums meet in shared memory and are
+// added in a fixed order, so results do not depend on timing. Scale and bias rows of a phase are staged by the
+// compute warps while the first stage is in flight.
 //
 // Rounding points are those of the per-kernel path: routed act = half(gelu(g) * u) with g, u in fp32
 // (moe.metal:368); shared act = half(gelu(half(g)) * half(u)), shared y = half(down . act)
 // (Kernels/MoE/SharedExpertInt4.swift:62-93); y = half(shared_y + sum_r w_r * partial_r); h = half(h + y).
 //
-// Grid barriers are bounded: a CTA that waits longer than kDsSpinLimit polls records kErrGridBarrier in the
-// context's device error word, after which no barrier waits any more and the kernel runs to its end (with
-// meaningless results); tf_device_status reports it.
+// Every wait is bounded (grid barriers, stage barriers, the router hand-over to the loader): a wait that runs out
+// records a code in the context's device error word, after which nothing in the CTA waits any more and the kernel
+// runs to its end with meaningless results; tf_device_status reports it.
 #include <algorithm>
 
+#include "async_copy.cuh"
 #include "block.cuh"
 #include "mma_gemv.cuh"
 #include "router.cuh"
 
 namespace tf {
 
-constexpr int kDsThreads = 512;
-constexpr int kDsWarps = kDsThreads / kWarp;
-constexpr uint32_t kDsMaxItems = 192;            // items of one phase in one CTA
-constexpr uint32_t kDsSpinLimit = 1u << 22;      // x ~0.5 us per poll
+constexpr int kDsComputeWarps = 16;
+constexpr int kDsComputeThreads = kDsComputeWarps * kWarp;
+constexpr int kDsThreads = kDsComputeThreads + kWarp;      // + the loader warp
+constexpr uint32_t kDsStages = 6;                // ring depth
+constexpr uint32_t kDsMaxItems = 128;            // items of one phase in one CTA
+constexpr uint32_t kDsSpinLimit = 1u << 22;      // grid barrier polls, ~0.5 us each
 constexpr uint32_t kErrGridBarrier = 0x7F000021u;
+constexpr uint32_t kErrStageWait = 0x7F000022u;
+constexpr uint32_t kErrLoaderWait = 0x7F000023u;
 constexpr int kDsNormThreads = 128;              // threads that compute the sum of squares (as residual_rmsnorm_kernel)
 constexpr int kDsNormSlices = 4;
 
@@ -68,156 +75,296 @@ struct DecodeArgs {
     uint32_t trace_capacity;
 };
 
-// ---------------------------------------------------------------------------
-// grid barrier
-// ---------------------------------------------------------------------------
-struct GridSync {
-    uint32_t* counter; uint32_t* error; uint32_t target; bool dead;
+// One item: 16 rows of a stage x up to 4 column groups of one matrix. Constant across layers.
+struct DsItem {
+    uint16_t stage_local;    // stage of the phase that holds the item's rows
+    uint16_t stage_items;    // items that read that stage (the last one to finish hands the slot back)
+    uint16_t tile;           // 16-row tile of the CTA's slice
+    uint16_t row_off;        // byte offset of the item's first group inside a stage row
+    uint16_t group;          // first group in the B-fragment / group-sum arrays
+    uint16_t scale_col;      // first column in the staged scale / bias rows
+    uint16_t ngr;            // groups in the item (1...4)
+    uint16_t pad;
 };
 
-__device__ __forceinline__ void grid_sync(GridSync& gs) {
-    __syncthreads();
+__host__ __device__ inline uint32_t ds_split(uint32_t total, uint32_t part, uint32_t parts) {
+    return (uint32_t)(((uint64_t)total * part) / parts);
+}
+__host__ __device__ inline uint32_t ds_kparts(uint32_t ng) { return (ng + 3u) / 4u; }
+__host__ __device__ inline uint32_t ds_ceil_div(uint32_t a, uint32_t b) { return (a + b - 1) / b; }
+
+// Shared-memory layout (bytes from the start of dynamic shared memory).
+struct DsSmem {
+    uint32_t ring, row_stride, stage_bytes, scales, scale_plane_elems, x16, xf, a16, frag_a, sum_a, frag_b, sum_b, wrow, partial,
+        tabs, scores, sel_idx, sel_w, red, bars, cnt, total;
+    __host__ __device__ DsSmem(uint32_t d, uint32_t f, uint32_t fs, uint32_t E, uint32_t K, uint32_t grid) {
+        auto up = [](uint32_t v, uint32_t a) { return (v + a - 1) / a * a; };
+        const uint32_t ngd = d / 64, ngf = f / 64, ngs = fs / 64, ngb = K * ngf + ngs;
+        const uint32_t quad = (K < 4u ? K : 4u) * (f / 2);
+        uint32_t maxrow = d / 2 > quad ? d / 2 : quad;
+        maxrow = maxrow > fs / 2 ? maxrow : fs / 2;
+        row_stride = up(maxrow, 128) + 32;           // = 32 mod 128: the 8-byte reads of rows g = 0..7 hit distinct banks
+        stage_bytes = 16 * row_stride;
+        const uint32_t r1 = ds_ceil_div(fs, grid), r2 = ds_ceil_div(K * f, grid), r3 = ds_ceil_div(d, grid);
+        uint32_t se = r1 * 2 * ngd;
+        se = se > r2 * 2 * ngd ? se : r2 * 2 * ngd;
+        se = se > r3 * ngb ? se : r3 * ngb;
+        scale_plane_elems = up(se, 8);
+        uint32_t o = 0;
+        ring = o; o += kDsStages * stage_bytes;
+        scales = o; o += scale_plane_elems * 2 * 2;                 // scale plane, then bias plane
+        x16 = o; a16 = o; o += up(d * 2, 16);                       // a16 (P3) overlays x16 + xf (P0..P2)
+        xf = o; o += up(d * 4, 16);
+        if (o - a16 < up((K * f + fs) * 2, 16)) o = a16 + up((K * f + fs) * 2, 16);
+        frag_a = o; o += ngd * 128;
+        sum_a = o; o += up(ngd * 4, 16);
+        frag_b = o; o += ngb * 128;
+        sum_b = o; o += up(ngb * 4, 16);
+        wrow = o; o += up(d, 16) + up(ngd * 2, 16) * 2;
+        partial = o; o += kDsMaxItems * 64;
+        tabs = o; o += 3 * kDsMaxItems * (uint32_t)sizeof(DsItem);
+        scores = o; o += up(E * 4, 16);
+        sel_idx = o; o += 32;
+        sel_w = o; o += 16;
+        red = o; o += 16;
+        bars = o; o += (2 * kDsStages + 1) * 8 + 8;
+        cnt = o; o += up(kDsStages * 4 + 4, 16);                    // per-slot item counters, then the dead flag
+        total = o;
+    }
+};
+
+// Per-CTA constants of the launch, kept in shared memory so that the phase functions (compiled as separate
+// functions: each gets its own register allocation) read what they need instead of carrying it in registers.
+struct DsCtx {
+    uint32_t d, f, fs, E, K, ngd, ngf, ngs, kp_d, kp_f, kp_s, subs;
+    uint32_t p1_lo, p1_hi, p2_lo, p2_hi, p3_lo, p3_hi, p1_tiles, p2_tiles, p3_tiles, p3_per_tile;
+    uint32_t n_st1, n_st2, n_st3;                       // stages per phase
+    uint32_t cta, grid, row_stride, stage_bytes, scale_plane_elems;
+    uint32_t ring_addr, bars_addr;                      // shared-window addresses
+    uint8_t* ring; uint16_t* scales; uint16_t* x16; float* xf; uint16_t* a16; uint32_t* frag_a; float* sum_a;
+    uint32_t* frag_b; float* sum_b; uint8_t* wrow; float* partial; DsItem* tabs; float* scores; uint32_t* sel_idx;
+    uint16_t* sel_w; float* red; uint32_t* cnt; volatile uint32_t* dead;
+    uint16_t* hidden; float* logits; uint16_t* acts; uint16_t* shared_act; uint32_t* out_idx; uint16_t* out_w;
+    uint32_t* error;
+    float eps;
+};
+
+__device__ __forceinline__ uint32_t ds_bar_full(const DsCtx* c, uint32_t slot) { return c->bars_addr + slot * 8; }
+__device__ __forceinline__ uint32_t ds_bar_empty(const DsCtx* c, uint32_t slot) { return c->bars_addr + (kDsStages + slot) * 8; }
+__device__ __forceinline__ uint32_t ds_bar_routing(const DsCtx* c) { return c->bars_addr + 2 * kDsStages * 8; }
+
+// barrier of the compute warps only (the loader warp runs ahead on its own)
+__device__ __forceinline__ void cta_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kDsComputeThreads) : "memory"); }
+
+__device__ __forceinline__ void ds_fail(const DsCtx* c, uint32_t code) {
+    atomicCAS(c->error, 0u, code);
+    *c->dead = 1u;
+}
+
+// ---------------------------------------------------------------------------
+// grid barrier (compute warps)
+// ---------------------------------------------------------------------------
+struct GridSync {
+    uint32_t* counter; uint32_t target;
+};
+
+__device__ __forceinline__ void grid_sync(const DsCtx* c, GridSync& gs) {
+    cta_sync();
     if (threadIdx.x == 0) {
         gs.target += gridDim.x;
         __threadfence();
         asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(gs.counter) : "memory");
-        if (!gs.dead) {
+        if (!*c->dead) {
             uint32_t spins = 0;
             for (;;) {
                 uint32_t v;
                 asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(gs.counter) : "memory");
                 if ((int32_t)(v - gs.target) >= 0) break;
-                if (++spins > kDsSpinLimit) { atomicCAS(gs.error, 0u, kErrGridBarrier); gs.dead = true; break; }
-                if ((spins & 1023u) == 0u && *reinterpret_cast<volatile uint32_t*>(gs.error) != 0u) { gs.dead = true; break; }
+                if (++spins > kDsSpinLimit) { ds_fail(c, kErrGridBarrier); break; }
+                if ((spins & 1023u) == 0u && *reinterpret_cast<volatile uint32_t*>(c->error) != 0u) { *c->dead = 1u; break; }
             }
         }
     }
-    __syncthreads();
+    cta_sync();
 }
 
 __device__ __forceinline__ void prefetch_l2(const void* p, uint32_t bytes) {
     const uint8_t* b = static_cast<const uint8_t*>(p);
     const uintptr_t first = reinterpret_cast<uintptr_t>(b) & ~(uintptr_t)127;
     const uintptr_t last = reinterpret_cast<uintptr_t>(b) + bytes;
-    for (uintptr_t a = first + (uintptr_t)threadIdx.x * 128; a < last; a += (uintptr_t)kDsThreads * 128)
+    for (uintptr_t a = first + (uintptr_t)threadIdx.x * 128; a < last; a += (uintptr_t)kDsComputeThreads * 128)
         asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
 }
 
 // ---------------------------------------------------------------------------
-// items: 16 rows (two independent 8-row halves) x up to 4 column groups of one matrix
+// loader warp
 // ---------------------------------------------------------------------------
-struct ItemSrc {                                // where an item's operands come from (needed only to issue its loads)
-    const uint8_t* w0; const uint8_t* w1;       // this lane's rows g and g + 8, at the item's first group, + 8 t
-    const uint16_t* s0; const uint16_t* s1; const uint16_t* b0; const uint16_t* b1;   // at the item's first group
-};
-struct ItemUse {                                // what the arithmetic needs besides the loaded registers
-    uint32_t frag_word;                         // word offset of the B fragments of the item's first group for this lane's t
-    uint32_t group;                             // index of the first group in the group-sum array
-    uint32_t ngr;                               // groups in the item (1...4)
-};
-
-template <bool VEC>
-struct ItemRegs {
-    uint2 wa[4], wb[4];
-    uint2 vs0, vs1, vb0, vb1;                   // VEC: scale / bias of four groups per row
-    uint16_t ss0[4], ss1[4], sb0[4], sb1[4];    // !VEC
-};
-
-template <bool VEC>
-__device__ __forceinline__ void item_load(const ItemSrc& it, uint32_t ngr, ItemRegs<VEC>& r) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        if ((uint32_t)i < ngr) { r.wa[i] = gm_ldg64(it.w0 + i * 32); r.wb[i] = gm_ldg64(it.w1 + i * 32); }
-        else { r.wa[i] = make_uint2(0u, 0u); r.wb[i] = make_uint2(0u, 0u); }
+// Waits for the slot of stage q to be free and arms its barrier with the bytes about to land. Returns the slot's
+// shared-window address, or 0 when the CTA has given up waiting.
+__device__ __forceinline__ uint32_t ds_open_stage(const DsCtx* c, uint32_t q, uint32_t tx_bytes, int lane) {
+    const uint32_t slot = q % kDsStages, use = q / kDsStages;
+    if (*c->dead) return 0u;
+    if (use > 0 && !mbar_wait(ds_bar_empty(c, slot), (use - 1) & 1)) {
+        if (lane == 0) ds_fail(c, kErrLoaderWait);
+        __syncwarp();
+        return 0u;
     }
-    if constexpr (VEC) {
-        r.vs0 = __ldg(reinterpret_cast<const uint2*>(it.s0)); r.vs1 = __ldg(reinterpret_cast<const uint2*>(it.s1));
-        r.vb0 = __ldg(reinterpret_cast<const uint2*>(it.b0)); r.vb1 = __ldg(reinterpret_cast<const uint2*>(it.b1));
-    } else {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const bool ok = (uint32_t)i < ngr;
-            r.ss0[i] = ok ? __ldg(it.s0 + i) : (uint16_t)0; r.ss1[i] = ok ? __ldg(it.s1 + i) : (uint16_t)0;
-            r.sb0[i] = ok ? __ldg(it.b0 + i) : (uint16_t)0; r.sb1[i] = ok ? __ldg(it.b1 + i) : (uint16_t)0;
-        }
+    if (lane == 0) {
+        fence_proxy_async();                     // the slot was last read through the generic proxy
+        mbar_arrive_expect_tx(ds_bar_full(c, slot), tx_bytes);
     }
+    __syncwarp();
+    return c->ring_addr + slot * c->stage_bytes;
 }
 
-// Returns the item's partial sums of rows g (x) and g + 8 (y); valid in the lanes with t == 0.
-template <bool VEC>
-__device__ __forceinline__ float2 item_compute(const ItemUse& it, const ItemRegs<VEC>& r, const uint32_t* frag_base,
-                                               const float* xsum_base, int g) {
-    float zc[4];
-#pragma unroll
-    for (int j = 0; j < 4; ++j) asm volatile("mov.f32 %0, 0f00000000;" : "=f"(zc[j]));
-    float c[4][4];
-    const uint32_t* frag = frag_base + it.frag_word;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            uint2 bf = make_uint2(0u, 0u);
-            if (g == 0 && (uint32_t)i < it.ngr) bf = *reinterpret_cast<const uint2*>(frag + i * 32 + j * 2);
-            const uint32_t wx = (j < 2) ? r.wa[i].x : r.wa[i].y, wy = (j < 2) ? r.wb[i].x : r.wb[i].y;
-            const uint32_t mask = (j & 1) ? 0x00F000F0u : 0x000F000Fu;
-            const uint32_t a0 = wx & mask, a1 = wy & mask, a2 = (wx >> 8) & mask, a3 = (wy >> 8) & mask;
-            if (j == 0) gm_mma(c[i], a0, a1, a2, a3, bf.x, bf.y, zc);
-            else gm_mma(c[i], a0, a1, a2, a3, bf.x, bf.y, c[i]);
+__device__ __noinline__ void ds_loader(const DsCtx* c, const DecodeLayer* layers, uint32_t n_layers) {
+    const int lane = threadIdx.x % kWarp;
+    const uint32_t d = c->d, f = c->f, fs = c->fs, K = c->K, RS = c->row_stride;
+    uint32_t q = 0;
+    for (uint32_t l = 0; l < n_layers; ++l) {
+        const DecodeLayer* L = layers + l;
+        // P1: shared gate/up rows (no dependency: runs ahead of the previous layer's barrier 3)
+        for (uint32_t s = 0; s < c->n_st1; ++s, ++q) {
+            const uint32_t tile = s / 2, mat = s % 2;
+            const uint32_t r0 = c->p1_lo + tile * 16;
+            const uint32_t n = c->p1_hi - r0 < 16u ? c->p1_hi - r0 : 16u;
+            const uint32_t dst = ds_open_stage(c, q, n * (d / 2), lane);
+            if (!dst) continue;
+            const uint8_t* W = mat ? L->su_w : L->sg_w;
+            if ((uint32_t)lane < n) bulk_copy_g2s(dst + lane * RS, W + (size_t)(r0 + lane) * (d / 2), d / 2, ds_bar_full(c, q % kDsStages));
         }
-    }
-    float acc0 = 0.0f, acc1 = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        if ((uint32_t)i < it.ngr) {
-            uint16_t s0b, s1b, b0b, b1b;
-            if constexpr (VEC) {
-                const uint32_t sv0 = i < 2 ? r.vs0.x : r.vs0.y, sv1 = i < 2 ? r.vs1.x : r.vs1.y;
-                const uint32_t bv0 = i < 2 ? r.vb0.x : r.vb0.y, bv1 = i < 2 ? r.vb1.x : r.vb1.y;
-                s0b = (uint16_t)((i & 1) ? sv0 >> 16 : sv0 & 0xFFFFu); s1b = (uint16_t)((i & 1) ? sv1 >> 16 : sv1 & 0xFFFFu);
-                b0b = (uint16_t)((i & 1) ? bv0 >> 16 : bv0 & 0xFFFFu); b1b = (uint16_t)((i & 1) ? bv1 >> 16 : bv1 & 0xFFFFu);
-            } else {
-                s0b = r.ss0[i]; s1b = r.ss1[i]; b0b = r.sb0[i]; b1b = r.sb1[i];
+        // the rows of P2 and P3 depend on the layer's top-k
+        if (!*c->dead && !mbar_wait(ds_bar_routing(c), l & 1)) {
+            if (lane == 0) ds_fail(c, kErrLoaderWait);
+            __syncwarp();
+        }
+        const uint8_t* pool = L->pool;
+        const uint64_t stride = L->stride;
+        for (uint32_t s = 0; s < c->n_st2; ++s, ++q) {
+            const uint32_t tile = s / 2, mat = s % 2;
+            const uint32_t i0 = c->p2_lo + tile * 16;
+            const uint32_t n = c->p2_hi - i0 < 16u ? c->p2_hi - i0 : 16u;
+            const uint32_t dst = ds_open_stage(c, q, n * (d / 2), lane);
+            if (!dst) continue;
+            if ((uint32_t)lane < n) {
+                const uint32_t idx = i0 + lane, k = idx / f, r = idx % f;
+                const uint8_t* src = pool + (uint64_t)c->sel_idx[k] * stride + (mat ? L->off.up_w_off : L->off.gate_w_off) + (size_t)r * (d / 2);
+                bulk_copy_g2s(dst + lane * RS, src, d / 2, ds_bar_full(c, q % kDsStages));
             }
-            // the codes entered the MMA as q * 2^-24: fold 2^24 into the scale
-            const float s0 = bf16_bits_to_float(s0b) * 16777216.0f, s1 = bf16_bits_to_float(s1b) * 16777216.0f;
-            const float xs = xsum_base[it.group + i];
-            acc0 = fmaf(s0, c[i][0], fmaf(bf16_bits_to_float(b0b), xs, acc0));
-            acc1 = fmaf(s1, c[i][2], fmaf(bf16_bits_to_float(b1b), xs, acc1));
+        }
+        for (uint32_t s = 0; s < c->n_st3; ++s, ++q) {
+            const uint32_t tile = s / (c->subs + 1), sub = s % (c->subs + 1);
+            const uint32_t r0 = c->p3_lo + tile * 16;
+            const uint32_t n = c->p3_hi - r0 < 16u ? c->p3_hi - r0 : 16u;
+            if (sub < c->subs) {
+                const uint32_t k0 = sub * 4, nk = K - k0 < 4u ? K - k0 : 4u;
+                const uint32_t dst = ds_open_stage(c, q, n * nk * (f / 2), lane);
+                if (!dst) continue;
+                for (uint32_t j = lane; j < n * nk; j += kWarp) {
+                    const uint32_t row = j / nk, kk = j % nk;
+                    const uint8_t* src = pool + (uint64_t)c->sel_idx[k0 + kk] * stride + L->off.down_w_off + (size_t)(r0 + row) * (f / 2);
+                    bulk_copy_g2s(dst + row * RS + kk * (f / 2), src, f / 2, ds_bar_full(c, q % kDsStages));
+                }
+            } else {
+                const uint32_t dst = ds_open_stage(c, q, n * (fs / 2), lane);
+                if (!dst) continue;
+                if ((uint32_t)lane < n) bulk_copy_g2s(dst + lane * RS, L->sd_w + (size_t)(r0 + lane) * (fs / 2), fs / 2, ds_bar_full(c, q % kDsStages));
+            }
         }
     }
-    return make_float2(acc0, acc1);
+    // Copies still in flight must land before the CTA's shared memory goes away: wait (bounded) for the last use of
+    // every slot. On the normal path the consumers have already seen these phases complete.
+    for (uint32_t back = 0; back < kDsStages && back < q; ++back) {
+        const uint32_t qq = q - 1 - back;
+        mbar_wait(ds_bar_full(c, qq % kDsStages), (qq / kDsStages) & 1);
+    }
 }
 
-// Runs items first, first + step, ... < n_items on this warp; `make` fills the source and use records of an item for
-// this lane. The next item's loads are issued before the current item is computed.
-template <bool VEC, typename Make>
-__device__ __forceinline__ void run_items(uint32_t first, uint32_t step, uint32_t n_items, float* partial,
-                                          const uint32_t* frag_base, const float* xsum_base, int lane, Make make) {
+// ---------------------------------------------------------------------------
+// compute warps
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint2 lds64(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+
+// Runs the phase's items first, first + step, ... on this warp. Stage q0 + item.stage_local holds the item's rows;
+// scale / bias rows sit in c->scales as [row][sstride]; partial sums of rows g and g + 8 go to partial[item][16].
+__device__ __forceinline__ void run_items(const DsCtx* c, const DsItem* tab, uint32_t n_items, uint32_t first, uint32_t step,
+                                          uint32_t q0, uint32_t rows, uint32_t sstride, const uint32_t* frag_base,
+                                          const float* xsum_base, int lane) {
     const int g = lane >> 2, t = lane & 3;
-    if (first >= n_items) return;
-    ItemUse cur_u, nxt_u;
-    ItemRegs<VEC> cur_r, nxt_r;
-    {
-        ItemSrc src;
-        make(first, g, t, src, cur_u);
-        item_load<VEC>(src, cur_u.ngr, cur_r);
-    }
+    const uint32_t RS = c->row_stride;
+    const uint16_t* sS = c->scales;
+    const uint16_t* sB = c->scales + c->scale_plane_elems;
+    float* partial = c->partial;
     for (uint32_t it = first; it < n_items; it += step) {
-        const bool more = it + step < n_items;
-        if (more) {
-            ItemSrc src;
-            make(it + step, g, t, src, nxt_u);
-            item_load<VEC>(src, nxt_u.ngr, nxt_r);
+        const uint4 raw = *reinterpret_cast<const uint4*>(tab + it);
+        const uint32_t stage_local = raw.x & 0xFFFFu, stage_items = raw.x >> 16, tile = raw.y & 0xFFFFu, row_off = raw.y >> 16,
+                       group = raw.z & 0xFFFFu, scale_col = raw.z >> 16, ngr = raw.w & 0xFFFFu;
+        const uint32_t q = q0 + stage_local, slot = q % kDsStages;
+        if (!*c->dead && !mbar_wait(ds_bar_full(c, slot), (q / kDsStages) & 1)) {
+            if (lane == 0) ds_fail(c, kErrStageWait);
         }
-        const float2 v = item_compute<VEC>(cur_u, cur_r, frag_base, xsum_base, g);
-        if (t == 0) { partial[it * 16 + g] = v.x; partial[it * 16 + g + 8] = v.y; }
-        if (more) { cur_u = nxt_u; cur_r = nxt_r; }
+        __syncwarp();
+        const uint32_t base = c->ring_addr + slot * c->stage_bytes + row_off + t * 8;
+        uint2 wa[4], wb[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if ((uint32_t)i < ngr) { wa[i] = lds64(base + g * RS + i * 32); wb[i] = lds64(base + (g + 8) * RS + i * 32); }
+            else { wa[i] = make_uint2(0u, 0u); wb[i] = make_uint2(0u, 0u); }
+        }
+        uint32_t r0 = tile * 16 + g, r1 = r0 + 8;
+        r0 = r0 < rows ? r0 : rows - 1; r1 = r1 < rows ? r1 : rows - 1;
+        const uint16_t* s0p = sS + r0 * sstride + scale_col;
+        const uint16_t* s1p = sS + r1 * sstride + scale_col;
+        const uint16_t* b0p = sB + r0 * sstride + scale_col;
+        const uint16_t* b1p = sB + r1 * sstride + scale_col;
+        float zc[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) asm volatile("mov.f32 %0, 0f00000000;" : "=f"(zc[j]));
+        float cacc[4][4];
+        const uint32_t* frag = frag_base + (group * 4 + t) * 8;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                uint2 bf = make_uint2(0u, 0u);
+                if (g == 0 && (uint32_t)i < ngr) bf = *reinterpret_cast<const uint2*>(frag + i * 32 + j * 2);
+                const uint32_t wx = (j < 2) ? wa[i].x : wa[i].y, wy = (j < 2) ? wb[i].x : wb[i].y;
+                const uint32_t mask = (j & 1) ? 0x00F000F0u : 0x000F000Fu;
+                const uint32_t a0 = wx & mask, a1 = wy & mask, a2 = (wx >> 8) & mask, a3 = (wy >> 8) & mask;
+                if (j == 0) gm_mma(cacc[i], a0, a1, a2, a3, bf.x, bf.y, zc);
+                else gm_mma(cacc[i], a0, a1, a2, a3, bf.x, bf.y, cacc[i]);
+            }
+        }
+        float acc0 = 0.0f, acc1 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            if ((uint32_t)i < ngr) {
+                // the codes entered the MMA as q * 2^-24: fold 2^24 into the scale
+                const float s0 = bf16_bits_to_float(s0p[i]) * 16777216.0f, s1 = bf16_bits_to_float(s1p[i]) * 16777216.0f;
+                const float xs = xsum_base[group + i];
+                acc0 = fmaf(s0, cacc[i][0], fmaf(bf16_bits_to_float(b0p[i]), xs, acc0));
+                acc1 = fmaf(s1, cacc[i][2], fmaf(bf16_bits_to_float(b1p[i]), xs, acc1));
+            }
+        }
+        if (t == 0) { partial[it * 16 + g] = acc0; partial[it * 16 + g + 8] = acc1; }
+        __syncwarp();
+        if (lane == 0) {
+            // the last item that read the stage hands the slot back to the loader
+            if (atomicAdd(&c->cnt[slot], 1u) + 1u == stage_items) {
+                c->cnt[slot] = 0u;
+                mbar_arrive(ds_bar_empty(c, slot));
+            }
+        }
     }
 }
 
 // B fragments and group sums of an fp16 vector that sits in shared memory (16-byte aligned, n = 64 ng).
 __device__ __forceinline__ void stage_frags(const uint16_t* xs, uint32_t ng, uint32_t* frag, float* xsum) {
-    for (uint32_t idx = threadIdx.x; idx < ((ng * 4 + 31u) & ~31u); idx += kDsThreads) {     // whole warps: shuffles below
+    for (uint32_t idx = threadIdx.x; idx < ((ng * 4 + 31u) & ~31u); idx += kDsComputeThreads) {     // whole warps: shuffles below
         const bool ok = idx < ng * 4;
         uint4 lo = make_uint4(0u, 0u, 0u, 0u), hi = lo;
         if (ok) {
@@ -239,48 +386,23 @@ __device__ __forceinline__ void stage_frags(const uint16_t* xs, uint32_t ng, uin
     }
 }
 
-__host__ __device__ inline uint32_t ds_split(uint32_t total, uint32_t part, uint32_t parts) {
-    return (uint32_t)(((uint64_t)total * part) / parts);
-}
-__host__ __device__ inline uint32_t ds_kparts(uint32_t ng) { return (ng + 3u) / 4u; }
-
-struct DsSmem {
-    uint32_t x16, xf, frag_a, sum_a, a16, frag_b, sum_b, wrow, partial, scores, sel_idx, sel_w, red, total;
-    __host__ __device__ DsSmem(uint32_t d, uint32_t f, uint32_t fs, uint32_t E, uint32_t K) {
-        auto up = [](uint32_t v) { return (v + 15u) & ~15u; };
-        const uint32_t ngd = d / 64, ngb = K * (f / 64) + fs / 64;
-        uint32_t o = 0;
-        x16 = o; o += up(d * 2);
-        xf = o; o += up(d * 4);
-        frag_a = o; o += ngd * 128;
-        sum_a = o; o += up(ngd * 4);
-        a16 = o; o += up((K * f + fs) * 2);
-        frag_b = o; o += ngb * 128;
-        sum_b = o; o += up(ngb * 4);
-        wrow = o; o += up(d) + up(ngd * 2) * 2;
-        partial = o; o += kDsMaxItems * 64;
-        scores = o; o += up(E * 4);
-        sel_idx = o; o += 32;
-        sel_w = o; o += 16;
-        red = o; o += 16;
-        total = o;
+// Copies n 16-bit scale or bias values, element i from src(i), into dst[i]; loads are issued eight at a time.
+template <typename Src>
+__device__ __forceinline__ void stage_u16(uint32_t n, uint16_t* dst, Src src) {
+    for (uint32_t base = threadIdx.x; base < n; base += kDsComputeThreads * 8) {
+        uint16_t v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t i = base + j * kDsComputeThreads;
+            v[j] = i < n ? __ldg(src(i)) : (uint16_t)0;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint32_t i = base + j * kDsComputeThreads;
+            if (i < n) dst[i] = v[j];
+        }
     }
-};
-
-// ---------------------------------------------------------------------------
-// the kernel
-// ---------------------------------------------------------------------------
-// Per-CTA constants of the launch, kept in shared memory so that the phase functions (compiled as separate
-// functions: each gets its own register allocation) read what they need instead of carrying it in registers.
-struct DsCtx {
-    uint32_t d, f, fs, E, K, ngd, ngf, ngs, kp_d, kp_f, kp_s;
-    uint32_t p1_lo, p1_hi, p2_lo, p2_hi, p3_lo, p3_hi, p1_tiles, p2_tiles, p3_tiles, p3_per_tile;
-    uint32_t cta, grid;
-    uint16_t* x16; float* xf; uint32_t* frag_a; float* sum_a; uint16_t* a16; uint32_t* frag_b; float* sum_b;
-    uint8_t* wrow; uint16_t* srow; uint16_t* brow; float* partial; float* scores; uint32_t* sel_idx; uint16_t* sel_w; float* red;
-    uint16_t* hidden; float* logits; uint16_t* acts; uint16_t* shared_act; uint32_t* out_idx; uint16_t* out_w;
-    float eps;
-};
+}
 
 // P0: x = half(rmsnorm(h) * w) into shared memory (bits of residual_rmsnorm_kernel: same thread striding and
 // reduction tree), its B fragments, and the router's fp32 operand x * effective_scale.
@@ -288,14 +410,22 @@ __device__ __noinline__ void ds_phase0(const DsCtx* c, const DecodeLayer* L) {
     const uint32_t d = c->d, vecs = d / 8;
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     float v[kDsNormSlices][8];
+    uint4 wv[kDsNormSlices];
     float acc = 0.0f;
+    const uint16_t* nw = L->norm_w;
     if (threadIdx.x < kDsNormThreads) {
+        uint4 hv[kDsNormSlices];
+#pragma unroll
+        for (int s = 0; s < kDsNormSlices; ++s) {
+            const uint32_t i = threadIdx.x + s * kDsNormThreads;
+            hv[s] = make_uint4(0u, 0u, 0u, 0u); wv[s] = hv[s];
+            if (i < vecs) { hv[s] = __ldcg(reinterpret_cast<const uint4*>(c->hidden) + i); wv[s] = __ldg(reinterpret_cast<const uint4*>(nw) + i); }
+        }
 #pragma unroll
         for (int s = 0; s < kDsNormSlices; ++s) {
             const uint32_t i = threadIdx.x + s * kDsNormThreads;
             if (i < vecs) {
-                const uint4 hv = __ldcg(reinterpret_cast<const uint4*>(c->hidden) + i);
-                const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w};
+                const uint32_t hw[4] = {hv[s].x, hv[s].y, hv[s].z, hv[s].w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&hw[j]));
@@ -307,18 +437,16 @@ __device__ __noinline__ void ds_phase0(const DsCtx* c, const DecodeLayer* L) {
         acc = warp_sum(acc);
         if (lane == 0) c->red[warp] = acc;
     }
-    __syncthreads();
+    cta_sync();
     if (threadIdx.x < kDsNormThreads) {
         float tot = lane < kDsNormThreads / kWarp ? c->red[lane] : 0.0f;
         tot = warp_sum(tot);
         const float inv = rsqrtf(tot / (float)d + c->eps);
-        const uint16_t* nw = L->norm_w;
 #pragma unroll
         for (int s = 0; s < kDsNormSlices; ++s) {
             const uint32_t i = threadIdx.x + s * kDsNormThreads;
             if (i < vecs) {
-                const uint4 wv = __ldg(reinterpret_cast<const uint4*>(nw) + i);
-                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                const uint32_t ww[4] = {wv[s].x, wv[s].y, wv[s].z, wv[s].w};
                 uint32_t ow[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -330,62 +458,59 @@ __device__ __noinline__ void ds_phase0(const DsCtx* c, const DecodeLayer* L) {
             }
         }
     }
-    __syncthreads();
+    cta_sync();
     stage_frags(c->x16, c->ngd, c->frag_a, c->sum_a);
     const uint16_t* eff = L->eff;
-    for (uint32_t i = threadIdx.x; i < d; i += kDsThreads)
+    for (uint32_t i = threadIdx.x; i < d; i += kDsComputeThreads)
         c->xf[i] = __fmul_rn(f16_bits_to_float(c->x16[i]), bf16_bits_to_float(eff[i]));
-    __syncthreads();
+    cta_sync();
 }
 
-// P1: this CTA's router rows (canonical logit) and its slice of the shared expert's gate/up rows.
-__device__ __noinline__ void ds_phase1(const DsCtx* c, const DecodeLayer* L) {
+// P1: this CTA's router rows (canonical logit, last compute warp) beside its slice of the shared expert's gate/up rows.
+__device__ __noinline__ void ds_phase1(const DsCtx* c, const DecodeLayer* L, uint32_t q0) {
     const uint32_t d = c->d, ngd = c->ngd, kp_d = c->kp_d;
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
-    for (uint32_t e = c->cta; e < c->E; e += c->grid) {
-        const uint8_t* wsrc = L->router_w + (size_t)e * d;
-        if ((reinterpret_cast<uintptr_t>(wsrc) & 15) == 0) {
-            for (uint32_t i = threadIdx.x; i < d / 16; i += kDsThreads) reinterpret_cast<uint4*>(c->wrow)[i] = ldg_nc_u4(wsrc + (size_t)i * 16);
-        } else {
-            for (uint32_t i = threadIdx.x; i < d; i += kDsThreads) c->wrow[i] = wsrc[i];
-        }
-        for (uint32_t i = threadIdx.x; i < ngd; i += kDsThreads) {
-            c->srow[i] = L->router_s[(size_t)e * ngd + i];
-            c->brow[i] = L->router_b[(size_t)e * ngd + i];
-        }
-        __syncthreads();
-        if (warp == 0) {
-            float logit = router_row_logit_smem(c->wrow, c->srow, c->brow, c->xf, ngd, lane);
+    const uint32_t lo = c->p1_lo, rows = c->p1_hi - c->p1_lo;
+    const uint32_t n_items = c->p1_tiles * 2 * kp_d;
+    {
+        // scale and bias rows of the slice: [row][gate groups | up groups]
+        const uint16_t* Sg = L->sg_s; const uint16_t* Su = L->su_s; const uint16_t* Bg = L->sg_b; const uint16_t* Bu = L->su_b;
+        const uint32_t stride = 2 * ngd, n = rows * stride;
+        stage_u16(n, c->scales, [&](uint32_t i) {
+            const uint32_t row = i / stride, col = i % stride;
+            return (col < ngd ? Sg : Su) + (size_t)(lo + row) * ngd + (col < ngd ? col : col - ngd);
+        });
+        stage_u16(n, c->scales + c->scale_plane_elems, [&](uint32_t i) {
+            const uint32_t row = i / stride, col = i % stride;
+            return (col < ngd ? Bg : Bu) + (size_t)(lo + row) * ngd + (col < ngd ? col : col - ngd);
+        });
+    }
+    cta_sync();
+    if (warp == kDsComputeWarps - 1) {
+        uint16_t* srow = reinterpret_cast<uint16_t*>(c->wrow + ((d + 15u) & ~15u));
+        uint16_t* brow = srow + ((ngd * 2 + 15u) & ~15u) / 2;
+        for (uint32_t e = c->cta; e < c->E; e += c->grid) {
+            const uint8_t* wsrc = L->router_w + (size_t)e * d;
+            if ((reinterpret_cast<uintptr_t>(wsrc) & 15) == 0) {
+                for (uint32_t i = lane; i < d / 16; i += kWarp) reinterpret_cast<uint4*>(c->wrow)[i] = ldg_nc_u4(wsrc + (size_t)i * 16);
+            } else {
+                for (uint32_t i = lane; i < d; i += kWarp) c->wrow[i] = wsrc[i];
+            }
+            for (uint32_t i = lane; i < ngd; i += kWarp) {
+                srow[i] = L->router_s[(size_t)e * ngd + i];
+                brow[i] = L->router_b[(size_t)e * ngd + i];
+            }
+            __syncwarp();
+            float logit = router_row_logit_smem(c->wrow, srow, brow, c->xf, ngd, lane);
             if (L->logit_bias) logit = __fadd_rn(logit, L->logit_bias[e]);
             if (lane == 0) c->logits[e] = logit;
+            __syncwarp();
         }
-        __syncthreads();
     }
-    const uint32_t lo = c->p1_lo, hi = c->p1_hi;
-    const uint32_t n_items = c->p1_tiles * 2 * kp_d;
-    const uint8_t* Wg = L->sg_w; const uint8_t* Wu = L->su_w;
-    const uint16_t* Sg = L->sg_s; const uint16_t* Su = L->su_s; const uint16_t* Bg = L->sg_b; const uint16_t* Bu = L->su_b;
-    const bool vec = (ngd % 4 == 0) && ((reinterpret_cast<uintptr_t>(Sg) | reinterpret_cast<uintptr_t>(Bg) |
-                                           reinterpret_cast<uintptr_t>(Su) | reinterpret_cast<uintptr_t>(Bu)) & 7) == 0;
-    auto make = [&](uint32_t it, int g, int t, ItemSrc& o, ItemUse& u) {
-        const uint32_t tile = it / (2 * kp_d), rem = it % (2 * kp_d), mat = rem / kp_d, kp = rem % kp_d;
-        const uint32_t G0 = kp * 4;
-        uint32_t r0 = lo + tile * 16 + g, r1 = r0 + 8;
-        r0 = r0 < hi ? r0 : hi - 1; r1 = r1 < hi ? r1 : hi - 1;
-        const uint8_t* W = mat ? Wu : Wg;
-        const uint16_t* S = mat ? Su : Sg;
-        const uint16_t* B = mat ? Bu : Bg;
-        o.w0 = W + (size_t)r0 * (d / 2) + G0 * 32 + t * 8; o.w1 = W + (size_t)r1 * (d / 2) + G0 * 32 + t * 8;
-        o.s0 = S + (size_t)r0 * ngd + G0; o.s1 = S + (size_t)r1 * ngd + G0;
-        o.b0 = B + (size_t)r0 * ngd + G0; o.b1 = B + (size_t)r1 * ngd + G0;
-        u.frag_word = (G0 * 4 + t) * 8; u.group = G0;
-        u.ngr = ngd - G0 < 4u ? ngd - G0 : 4u;
-    };
-    if (vec) run_items<true>(warp, kDsWarps, n_items, c->partial, c->frag_a, c->sum_a, lane, make);
-    else run_items<false>(warp, kDsWarps, n_items, c->partial, c->frag_a, c->sum_a, lane, make);
-    __syncthreads();
+    run_items(c, c->tabs, n_items, warp, kDsComputeWarps, q0, rows, 2 * ngd, c->frag_a, c->sum_a, lane);
+    cta_sync();
     const float* partial = c->partial;
-    for (uint32_t j = threadIdx.x; j < hi - lo; j += kDsThreads) {
+    for (uint32_t j = threadIdx.x; j < rows; j += kDsComputeThreads) {
         const uint32_t tile = j / 16, r = j % 16;
         float gt = 0.0f, up = 0.0f;
         for (uint32_t kp = 0; kp < kp_d; ++kp) {
@@ -400,76 +525,76 @@ __device__ __noinline__ void ds_phase1(const DsCtx* c, const DecodeLayer* L) {
 }
 
 // P2: top-k of the logits (every CTA, identically), then this CTA's slice of the routed experts' gate/up rows.
-__device__ __noinline__ void ds_phase2(const DsCtx* c, const DecodeLayer* L, const DecodeLayer* N) {
-    const uint32_t d = c->d, f = c->f, fs = c->fs, E = c->E, K = c->K, ngd = c->ngd, ngf = c->ngf, ngs = c->ngs, kp_d = c->kp_d;
+__device__ __noinline__ void ds_phase2(const DsCtx* c, const DecodeLayer* L, const DecodeLayer* N, uint32_t q0) {
+    const uint32_t d = c->d, f = c->f, E = c->E, K = c->K, ngd = c->ngd, ngf = c->ngf, ngs = c->ngs, kp_d = c->kp_d;
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
-    for (uint32_t i = threadIdx.x; i < E; i += kDsThreads) c->scores[i] = __ldcg(c->logits + i);
-    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < E; i += kDsComputeThreads) c->scores[i] = __ldcg(c->logits + i);
+    cta_sync();
     if (warp == 0) warp_select_topk(c->scores, E, K, L->pes, c->sel_idx, c->sel_w, lane);
-    __syncthreads();
+    cta_sync();
     if (threadIdx.x < K) {
         uint32_t e = c->sel_idx[threadIdx.x];
         if (c->cta == 0) { c->out_idx[threadIdx.x] = e; c->out_w[threadIdx.x] = c->sel_w[threadIdx.x]; }
         if (e >= E) e = E - 1;                        // min(id, E-1): Runtime/Inference/RealForwardRunner.swift:1486
         c->sel_idx[threadIdx.x] = e;
     }
-    __syncthreads();
-    const uint32_t lo = c->p2_lo, hi = c->p2_hi;
+    cta_sync();
+    if (threadIdx.x == 0) mbar_arrive(ds_bar_routing(c));          // the loader may now address the routed experts
+    const uint32_t lo = c->p2_lo, rows = c->p2_hi - c->p2_lo;
     const uint32_t n_items = c->p2_tiles * 2 * kp_d;
     const uint8_t* pool = L->pool;
     const uint64_t stride = L->stride;
     const tf_expert_offsets off = L->off;
     const uint32_t* sel = c->sel_idx;
-    const bool vec = (ngd % 4 == 0) && ((reinterpret_cast<uintptr_t>(pool) | stride | off.gate_s_off | off.gate_b_off |
-                                           off.up_s_off | off.up_b_off) & 7) == 0;
-    auto make = [&](uint32_t it, int g, int t, ItemSrc& o, ItemUse& u) {
-        const uint32_t tile = it / (2 * kp_d), rem = it % (2 * kp_d), mat = rem / kp_d, kp = rem % kp_d;
-        const uint32_t G0 = kp * 4;
-        uint32_t i0 = lo + tile * 16 + g, i1 = i0 + 8;
-        i0 = i0 < hi ? i0 : hi - 1; i1 = i1 < hi ? i1 : hi - 1;
-        const uint8_t* blob0 = pool + (uint64_t)sel[i0 / f] * stride;
-        const uint8_t* blob1 = pool + (uint64_t)sel[i1 / f] * stride;
-        const uint32_t r0 = i0 % f, r1 = i1 % f;
-        const uint32_t wo = mat ? off.up_w_off : off.gate_w_off, so = mat ? off.up_s_off : off.gate_s_off,
-                       bo = mat ? off.up_b_off : off.gate_b_off;
-        o.w0 = blob0 + wo + (size_t)r0 * (d / 2) + G0 * 32 + t * 8; o.w1 = blob1 + wo + (size_t)r1 * (d / 2) + G0 * 32 + t * 8;
-        o.s0 = reinterpret_cast<const uint16_t*>(blob0 + so) + (size_t)r0 * ngd + G0;
-        o.s1 = reinterpret_cast<const uint16_t*>(blob1 + so) + (size_t)r1 * ngd + G0;
-        o.b0 = reinterpret_cast<const uint16_t*>(blob0 + bo) + (size_t)r0 * ngd + G0;
-        o.b1 = reinterpret_cast<const uint16_t*>(blob1 + bo) + (size_t)r1 * ngd + G0;
-        u.frag_word = (G0 * 4 + t) * 8; u.group = G0;
-        u.ngr = ngd - G0 < 4u ? ngd - G0 : 4u;
-    };
-    if (vec) run_items<true>(warp, kDsWarps, n_items, c->partial, c->frag_a, c->sum_a, lane, make);
-    else run_items<false>(warp, kDsWarps, n_items, c->partial, c->frag_a, c->sum_a, lane, make);
-    // while the routed rows stream: bring this CTA's rows of P3 and of the next layer's P1 into L2
+    {
+        const uint32_t sst = 2 * ngd, n = rows * sst;
+        stage_u16(n, c->scales, [&](uint32_t i) {
+            const uint32_t row = i / sst, col = i % sst, idx = lo + row;
+            const uint8_t* blob = pool + (uint64_t)sel[idx / f] * stride;
+            return reinterpret_cast<const uint16_t*>(blob + (col < ngd ? off.gate_s_off : off.up_s_off)) + (size_t)(idx % f) * ngd +
+                   (col < ngd ? col : col - ngd);
+        });
+        stage_u16(n, c->scales + c->scale_plane_elems, [&](uint32_t i) {
+            const uint32_t row = i / sst, col = i % sst, idx = lo + row;
+            const uint8_t* blob = pool + (uint64_t)sel[idx / f] * stride;
+            return reinterpret_cast<const uint16_t*>(blob + (col < ngd ? off.gate_b_off : off.up_b_off)) + (size_t)(idx % f) * ngd +
+                   (col < ngd ? col : col - ngd);
+        });
+    }
+    // scale and bias rows of P3 and of the next layer's P1, the next router row and norm weights: into L2 ahead of use
     const uint32_t lo3 = c->p3_lo, n3 = c->p3_hi - c->p3_lo;
     if (n3) {
         for (uint32_t k = 0; k < K; ++k) {
             const uint8_t* blob = pool + (uint64_t)sel[k] * stride;
-            prefetch_l2(blob + off.down_w_off + (size_t)lo3 * (f / 2), n3 * (f / 2));
             prefetch_l2(blob + off.down_s_off + (size_t)lo3 * ngf * 2, n3 * ngf * 2);
             prefetch_l2(blob + off.down_b_off + (size_t)lo3 * ngf * 2, n3 * ngf * 2);
         }
-        prefetch_l2(L->sd_w + (size_t)lo3 * (fs / 2), n3 * (fs / 2));
         prefetch_l2(L->sd_s + (size_t)lo3 * ngs, n3 * ngs * 2);
         prefetch_l2(L->sd_b + (size_t)lo3 * ngs, n3 * ngs * 2);
     }
     if (N) {
-        for (uint32_t e = c->cta; e < E; e += c->grid) prefetch_l2(N->router_w + (size_t)e * d, d);
+        for (uint32_t e = c->cta; e < E; e += c->grid) {
+            prefetch_l2(N->router_w + (size_t)e * d, d);
+            prefetch_l2(N->router_s + (size_t)e * ngd, ngd * 2);
+            prefetch_l2(N->router_b + (size_t)e * ngd, ngd * 2);
+        }
         const uint32_t lo1 = c->p1_lo, n1 = c->p1_hi - c->p1_lo;
         if (n1) {
-            prefetch_l2(N->sg_w + (size_t)lo1 * (d / 2), n1 * (d / 2));
-            prefetch_l2(N->su_w + (size_t)lo1 * (d / 2), n1 * (d / 2));
             prefetch_l2(N->sg_s + (size_t)lo1 * ngd, n1 * ngd * 2);
             prefetch_l2(N->sg_b + (size_t)lo1 * ngd, n1 * ngd * 2);
             prefetch_l2(N->su_s + (size_t)lo1 * ngd, n1 * ngd * 2);
             prefetch_l2(N->su_b + (size_t)lo1 * ngd, n1 * ngd * 2);
         }
+        if (c->cta < 8) {           // a few CTAs are enough to bring the small replicated vectors in
+            prefetch_l2(N->norm_w, d * 2);
+            prefetch_l2(N->eff, d * 2);
+        }
     }
-    __syncthreads();
+    cta_sync();
+    run_items(c, c->tabs + kDsMaxItems, n_items, warp, kDsComputeWarps, q0, rows, 2 * ngd, c->frag_a, c->sum_a, lane);
+    cta_sync();
     const float* partial = c->partial;
-    for (uint32_t j = threadIdx.x; j < hi - lo; j += kDsThreads) {
+    for (uint32_t j = threadIdx.x; j < rows; j += kDsComputeThreads) {
         const uint32_t tile = j / 16, r = j % 16;
         float gt = 0.0f, up = 0.0f;
         for (uint32_t kp = 0; kp < kp_d; ++kp) {
@@ -482,53 +607,45 @@ __device__ __noinline__ void ds_phase2(const DsCtx* c, const DecodeLayer* L, con
 
 // P3: down projections of the K routed experts and of the shared expert for this CTA's output rows, combine in rank
 // order, residual add.
-__device__ __noinline__ void ds_phase3(const DsCtx* c, const DecodeLayer* L) {
+__device__ __noinline__ void ds_phase3(const DsCtx* c, const DecodeLayer* L, uint32_t q0) {
     const uint32_t f = c->f, fs = c->fs, K = c->K, ngf = c->ngf, ngs = c->ngs, kp_f = c->kp_f, kp_s = c->kp_s;
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const uint32_t lo = c->p3_lo, rows = c->p3_hi - c->p3_lo, per_tile = c->p3_per_tile;
     const uint32_t n_act = K * f + fs;
-    for (uint32_t i = threadIdx.x; i < n_act / 8; i += kDsThreads) {
+    for (uint32_t i = threadIdx.x; i < n_act / 8; i += kDsComputeThreads) {
         const uint32_t e8 = i * 8;
         const uint16_t* src = e8 < K * f ? c->acts + e8 : c->shared_act + (e8 - K * f);
         reinterpret_cast<uint4*>(c->a16)[i] = __ldcg(reinterpret_cast<const uint4*>(src));
     }
-    __syncthreads();
+    {
+        // scale and bias rows: [row][K routed experts x ngf | shared ngs]
+        const uint8_t* pool = L->pool;
+        const uint64_t stride = L->stride;
+        const uint32_t dso = L->off.down_s_off, dbo = L->off.down_b_off;
+        const uint16_t* sds = L->sd_s; const uint16_t* sdb = L->sd_b;
+        const uint32_t* sel = c->sel_idx;
+        const uint32_t sst = K * ngf + ngs, n = rows * sst;
+        stage_u16(n, c->scales, [&](uint32_t i) {
+            const uint32_t row = i / sst, col = i % sst;
+            if (col >= K * ngf) return sds + (size_t)(lo + row) * ngs + (col - K * ngf);
+            const uint8_t* blob = pool + (uint64_t)sel[col / ngf] * stride;
+            return reinterpret_cast<const uint16_t*>(blob + dso) + (size_t)(lo + row) * ngf + col % ngf;
+        });
+        stage_u16(n, c->scales + c->scale_plane_elems, [&](uint32_t i) {
+            const uint32_t row = i / sst, col = i % sst;
+            if (col >= K * ngf) return sdb + (size_t)(lo + row) * ngs + (col - K * ngf);
+            const uint8_t* blob = pool + (uint64_t)sel[col / ngf] * stride;
+            return reinterpret_cast<const uint16_t*>(blob + dbo) + (size_t)(lo + row) * ngf + col % ngf;
+        });
+    }
+    cta_sync();
     stage_frags(c->a16, K * ngf + ngs, c->frag_b, c->sum_b);      // K routed vectors of ngf groups, then the shared one
-    __syncthreads();
-    const uint32_t lo = c->p3_lo, hi = c->p3_hi, per_tile = c->p3_per_tile;
+    cta_sync();
     const uint32_t n_items = c->p3_tiles * per_tile;
-    const uint8_t* pool = L->pool;
-    const uint64_t stride = L->stride;
-    const uint32_t dw = L->off.down_w_off, dso = L->off.down_s_off, dbo = L->off.down_b_off;
-    const uint8_t* sdw = L->sd_w; const uint16_t* sds = L->sd_s; const uint16_t* sdb = L->sd_b;
-    const uint32_t* sel = c->sel_idx;
-    auto make = [&](uint32_t it, int g, int t, ItemSrc& o, ItemUse& u) {
-        const uint32_t tile = it / per_tile, rem = it % per_tile;
-        uint32_t r0 = lo + tile * 16 + g, r1 = r0 + 8;
-        r0 = r0 < hi ? r0 : hi - 1; r1 = r1 < hi ? r1 : hi - 1;
-        if (rem < K * kp_f) {
-            const uint32_t k = rem / kp_f, G0 = (rem % kp_f) * 4;
-            const uint8_t* blob = pool + (uint64_t)sel[k] * stride;
-            const uint16_t* S = reinterpret_cast<const uint16_t*>(blob + dso);
-            const uint16_t* B = reinterpret_cast<const uint16_t*>(blob + dbo);
-            o.w0 = blob + dw + (size_t)r0 * (f / 2) + G0 * 32 + t * 8;
-            o.w1 = blob + dw + (size_t)r1 * (f / 2) + G0 * 32 + t * 8;
-            o.s0 = S + (size_t)r0 * ngf + G0; o.s1 = S + (size_t)r1 * ngf + G0;
-            o.b0 = B + (size_t)r0 * ngf + G0; o.b1 = B + (size_t)r1 * ngf + G0;
-            u.frag_word = ((k * ngf + G0) * 4 + t) * 8; u.group = k * ngf + G0;
-            u.ngr = ngf - G0 < 4u ? ngf - G0 : 4u;
-        } else {
-            const uint32_t G0 = (rem - K * kp_f) * 4;
-            o.w0 = sdw + (size_t)r0 * (fs / 2) + G0 * 32 + t * 8; o.w1 = sdw + (size_t)r1 * (fs / 2) + G0 * 32 + t * 8;
-            o.s0 = sds + (size_t)r0 * ngs + G0; o.s1 = sds + (size_t)r1 * ngs + G0;
-            o.b0 = sdb + (size_t)r0 * ngs + G0; o.b1 = sdb + (size_t)r1 * ngs + G0;
-            u.frag_word = ((K * ngf + G0) * 4 + t) * 8; u.group = K * ngf + G0;
-            u.ngr = ngs - G0 < 4u ? ngs - G0 : 4u;
-        }
-    };
-    run_items<false>(warp, kDsWarps, n_items, c->partial, c->frag_b, c->sum_b, lane, make);
-    __syncthreads();
+    run_items(c, c->tabs + 2 * kDsMaxItems, n_items, warp, kDsComputeWarps, q0, rows, K * ngf + ngs, c->frag_b, c->sum_b, lane);
+    cta_sync();
     const float* partial = c->partial;
-    for (uint32_t j = threadIdx.x; j < hi - lo; j += kDsThreads) {
+    for (uint32_t j = threadIdx.x; j < rows; j += kDsComputeThreads) {
         const uint32_t tile = j / 16, r = j % 16;
         const float* pt = partial + (size_t)tile * per_tile * 16 + r;
         float sh = 0.0f;
@@ -545,43 +662,99 @@ __device__ __noinline__ void ds_phase3(const DsCtx* c, const DecodeLayer* L) {
     }
 }
 
+// Item tables of the three phases (constant across layers), built once per launch.
+__device__ void ds_build_tables(const DsCtx* c) {
+    const uint32_t kp_d = c->kp_d, kp_f = c->kp_f, kp_s = c->kp_s, K = c->K, ngd = c->ngd, ngf = c->ngf, ngs = c->ngs, f = c->f;
+    for (uint32_t ph = 0; ph < 2; ++ph) {
+        const uint32_t n = (ph ? c->p2_tiles : c->p1_tiles) * 2 * kp_d;
+        for (uint32_t it = threadIdx.x; it < n; it += kDsComputeThreads) {
+            const uint32_t st = it / kp_d, kp = it % kp_d, G0 = kp * 4;
+            DsItem e;
+            e.stage_local = (uint16_t)st; e.stage_items = (uint16_t)kp_d; e.tile = (uint16_t)(st / 2);
+            e.row_off = (uint16_t)(G0 * 32); e.group = (uint16_t)G0; e.scale_col = (uint16_t)((st % 2) * ngd + G0);
+            e.ngr = (uint16_t)(ngd - G0 < 4u ? ngd - G0 : 4u); e.pad = 0;
+            c->tabs[ph * kDsMaxItems + it] = e;
+        }
+    }
+    const uint32_t per_tile = c->p3_per_tile, n3 = c->p3_tiles * per_tile;
+    for (uint32_t it = threadIdx.x; it < n3; it += kDsComputeThreads) {
+        const uint32_t tile = it / per_tile, rem = it % per_tile;
+        DsItem e;
+        e.tile = (uint16_t)tile; e.pad = 0;
+        if (rem < K * kp_f) {
+            const uint32_t k = rem / kp_f, G0 = (rem % kp_f) * 4, sub = k / 4;
+            const uint32_t nk = K - sub * 4 < 4u ? K - sub * 4 : 4u;
+            e.stage_local = (uint16_t)(tile * (c->subs + 1) + sub); e.stage_items = (uint16_t)(nk * kp_f);
+            e.row_off = (uint16_t)((k % 4) * (f / 2) + G0 * 32); e.group = (uint16_t)(k * ngf + G0); e.scale_col = e.group;
+            e.ngr = (uint16_t)(ngf - G0 < 4u ? ngf - G0 : 4u);
+        } else {
+            const uint32_t G0 = (rem - K * kp_f) * 4;
+            e.stage_local = (uint16_t)(tile * (c->subs + 1) + c->subs); e.stage_items = (uint16_t)kp_s;
+            e.row_off = (uint16_t)(G0 * 32); e.group = (uint16_t)(K * ngf + G0); e.scale_col = e.group;
+            e.ngr = (uint16_t)(ngs - G0 < 4u ? ngs - G0 : 4u);
+        }
+        c->tabs[2 * kDsMaxItems + it] = e;
+    }
+}
+
 __global__ void __launch_bounds__(kDsThreads, 1)
 decode_step_kernel(const DecodeArgs args) {
-    extern __shared__ __align__(16) uint8_t smem[];
+    extern __shared__ __align__(128) uint8_t smem[];
     __shared__ DsCtx ctx;
     if (threadIdx.x == 0) {
         const uint32_t d = args.d, f = args.f, fs = args.fs, E = args.E, K = args.K;
-        const DsSmem lay(d, f, fs, E, K);
+        const DsSmem lay(d, f, fs, E, K, gridDim.x);
         DsCtx& c = ctx;
         c.d = d; c.f = f; c.fs = fs; c.E = E; c.K = K;
         c.ngd = d / kGroup; c.ngf = f / kGroup; c.ngs = fs / kGroup;
         c.kp_d = ds_kparts(c.ngd); c.kp_f = ds_kparts(c.ngf); c.kp_s = ds_kparts(c.ngs);
+        c.subs = (K + 3) / 4;
         c.cta = blockIdx.x; c.grid = gridDim.x;
         c.p1_lo = ds_split(fs, c.cta, c.grid); c.p1_hi = ds_split(fs, c.cta + 1, c.grid);
         c.p2_lo = ds_split(K * f, c.cta, c.grid); c.p2_hi = ds_split(K * f, c.cta + 1, c.grid);
         c.p3_lo = ds_split(d, c.cta, c.grid); c.p3_hi = ds_split(d, c.cta + 1, c.grid);
         c.p1_tiles = (c.p1_hi - c.p1_lo + 15) / 16; c.p2_tiles = (c.p2_hi - c.p2_lo + 15) / 16; c.p3_tiles = (c.p3_hi - c.p3_lo + 15) / 16;
         c.p3_per_tile = K * c.kp_f + c.kp_s;
+        c.n_st1 = c.p1_tiles * 2; c.n_st2 = c.p2_tiles * 2; c.n_st3 = c.p3_tiles * (c.subs + 1);
+        c.row_stride = lay.row_stride; c.stage_bytes = lay.stage_bytes; c.scale_plane_elems = lay.scale_plane_elems;
+        c.ring = smem + lay.ring; c.ring_addr = smem_addr_u32(c.ring);
+        c.bars_addr = smem_addr_u32(smem + lay.bars);
+        c.scales = reinterpret_cast<uint16_t*>(smem + lay.scales);
         c.x16 = reinterpret_cast<uint16_t*>(smem + lay.x16);
         c.xf = reinterpret_cast<float*>(smem + lay.xf);
+        c.a16 = reinterpret_cast<uint16_t*>(smem + lay.a16);
         c.frag_a = reinterpret_cast<uint32_t*>(smem + lay.frag_a);
         c.sum_a = reinterpret_cast<float*>(smem + lay.sum_a);
-        c.a16 = reinterpret_cast<uint16_t*>(smem + lay.a16);
         c.frag_b = reinterpret_cast<uint32_t*>(smem + lay.frag_b);
         c.sum_b = reinterpret_cast<float*>(smem + lay.sum_b);
         c.wrow = smem + lay.wrow;
-        c.srow = reinterpret_cast<uint16_t*>(c.wrow + ((d + 15u) & ~15u));
-        c.brow = c.srow + ((c.ngd * 2 + 15u) & ~15u) / 2;
         c.partial = reinterpret_cast<float*>(smem + lay.partial);
+        c.tabs = reinterpret_cast<DsItem*>(smem + lay.tabs);
         c.scores = reinterpret_cast<float*>(smem + lay.scores);
         c.sel_idx = reinterpret_cast<uint32_t*>(smem + lay.sel_idx);
         c.sel_w = reinterpret_cast<uint16_t*>(smem + lay.sel_w);
         c.red = reinterpret_cast<float*>(smem + lay.red);
+        c.cnt = reinterpret_cast<uint32_t*>(smem + lay.cnt);
+        c.dead = c.cnt + kDsStages;
         c.hidden = args.hidden; c.logits = args.logits; c.acts = args.acts; c.shared_act = args.shared_act;
-        c.out_idx = args.out_idx; c.out_w = args.out_w; c.eps = args.eps;
+        c.out_idx = args.out_idx; c.out_w = args.out_w; c.error = args.error; c.eps = args.eps;
+        for (uint32_t s = 0; s < kDsStages; ++s) {
+            mbar_init(c.bars_addr + s * 8, 1);
+            mbar_init(c.bars_addr + (kDsStages + s) * 8, 1);
+            c.cnt[s] = 0u;
+        }
+        mbar_init(c.bars_addr + 2 * kDsStages * 8, 1);
+        *c.dead = 0u;
+        fence_proxy_async();
     }
     __syncthreads();
-    GridSync gs{args.barrier, args.error, 0u, false};
+    if (threadIdx.x >= kDsComputeThreads) {
+        ds_loader(&ctx, args.layers, args.n_layers);
+        return;
+    }
+    ds_build_tables(&ctx);
+    cta_sync();
+    GridSync gs{args.barrier, 0u};
     uint32_t stamp_at = 0;
     auto stamp = [&]() {
         if (args.trace && blockIdx.x == 0 && threadIdx.x == 0 && stamp_at < args.trace_capacity) {
@@ -590,22 +763,24 @@ decode_step_kernel(const DecodeArgs args) {
             args.trace[stamp_at++] = t;
         }
     };
+    const uint32_t per_layer = ctx.n_st1 + ctx.n_st2 + ctx.n_st3;
     for (uint32_t l = 0; l < args.n_layers; ++l) {
         const DecodeLayer* L = args.layers + l;
+        const uint32_t q0 = l * per_layer;
         stamp();
         ds_phase0(&ctx, L);
         stamp();
-        ds_phase1(&ctx, L);
+        ds_phase1(&ctx, L, q0);
         stamp();
-        grid_sync(gs);
+        grid_sync(&ctx, gs);
         stamp();
-        ds_phase2(&ctx, L, l + 1 < args.n_layers ? L + 1 : nullptr);
+        ds_phase2(&ctx, L, l + 1 < args.n_layers ? L + 1 : nullptr, q0 + ctx.n_st1);
         stamp();
-        grid_sync(gs);
+        grid_sync(&ctx, gs);
         stamp();
-        ds_phase3(&ctx, L);
+        ds_phase3(&ctx, L, q0 + ctx.n_st1 + ctx.n_st2);
         stamp();
-        grid_sync(gs);
+        grid_sync(&ctx, gs);
         stamp();
     }
 }
@@ -640,12 +815,14 @@ bool decode_step_eligible(const tf_stack* st, const tf_workspace* ws) {
     if (ws->d != d || ws->f != f || ws->fs != fs || ws->top_k != K || ws->num_experts != E) return false;
     const uint32_t grid = (uint32_t)st->ctx->sm_count;
     if (ds_max_items(d, f, fs, K, grid) > kDsMaxItems) return false;
-    if (DsSmem(d, f, fs, E, K).total > 200u * 1024u) return false;
+    const DsSmem lay(d, f, fs, E, K, grid);
+    if (lay.total > 227u * 1024u || lay.row_stride > 0xFFFFu) return false;
+    if ((uint64_t)K * (f / 64) + fs / 64 > 0xFFFFu) return false;
     return st->decode_step_ok;
 }
 
 tf_status decode_step_prepare(tf_context* ctx, tf_stack* st) {
-    // one device copy of the per-layer pointers; alignment rules of the item loads (8-byte code loads, 2-byte planes)
+    // one device copy of the per-layer pointers; alignment rules of the stage copies (16-byte rows) and 2-byte planes
     std::vector<DecodeLayer> host(st->layers.size());
     bool ok = true;
     for (size_t l = 0; l < st->layers.size(); ++l) {
@@ -667,8 +844,8 @@ tf_status decode_step_prepare(tf_context* ctx, tf_stack* st) {
         ok = ok && m.router.rows == m.num_experts && m.router.cols == m.d;
         ok = ok && m.shared_gate.rows == m.fs && m.shared_gate.cols == m.d && m.shared_up.rows == m.fs && m.shared_up.cols == m.d &&
              m.shared_down.rows == m.d && m.shared_down.cols == m.fs;
-        ok = ok && aligned(o.pool, 8) && o.stride % 8 == 0 && o.off.gate_w_off % 8 == 0 && o.off.up_w_off % 8 == 0 && o.off.down_w_off % 8 == 0;
-        ok = ok && aligned(o.sg_w, 8) && aligned(o.su_w, 8) && aligned(o.sd_w, 8) && aligned(o.norm_w, 16);
+        ok = ok && aligned(o.pool, 16) && o.stride % 16 == 0 && o.off.gate_w_off % 16 == 0 && o.off.up_w_off % 16 == 0 && o.off.down_w_off % 16 == 0;
+        ok = ok && aligned(o.sg_w, 16) && aligned(o.su_w, 16) && aligned(o.sd_w, 16) && aligned(o.norm_w, 16);
         const uint32_t sb[6] = {o.off.gate_s_off, o.off.gate_b_off, o.off.up_s_off, o.off.up_b_off, o.off.down_s_off, o.off.down_b_off};
         for (uint32_t v : sb) ok = ok && v % 2 == 0;
         ok = ok && aligned(o.sg_s, 2) && aligned(o.sg_b, 2) && aligned(o.su_s, 2) && aligned(o.su_b, 2) && aligned(o.sd_s, 2) &&
@@ -694,21 +871,10 @@ tf_status launch_decode_step(tf_context* ctx, void* stream, tf_stack* st, void* 
     args.out_idx = ws->indices; args.out_w = ws->weights;
     args.barrier = ctx->grid_barrier; args.error = ctx->device_error;
     args.trace = ctx->step_trace; args.trace_capacity = ctx->step_trace_capacity;
-    const uint32_t smem = DsSmem(args.d, args.f, args.fs, args.E, args.K).total;
+    const uint32_t smem = DsSmem(args.d, args.f, args.fs, args.E, args.K, (uint32_t)ctx->sm_count).total;
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
-    {
-        static std::mutex mu;
-        static uint32_t configured[64] = {0};
-        std::lock_guard<std::mutex> lock(mu);
-        const int dev = ctx->device < 64 ? ctx->device : 63;
-        if (smem > configured[dev] || ctx->device >= 64) {
-            TF_CUDA(ctx, cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            int per_sm = 0;
-            TF_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_step_kernel, kDsThreads, smem));
-            TF_REQUIRE(ctx, per_sm >= 1, TF_ERR_UNSUPPORTED, "%s: the kernel does not fit an SM with %u bytes of shared memory", name, smem);
-            configured[dev] = smem;
-        }
-    }
+    static DeviceSmemCache configured;
+    if (tf_status s = ensure_dynamic_smem(ctx, decode_step_kernel, configured, smem)) return s;
     TF_CUDA(ctx, cudaMemsetAsync(ctx->grid_barrier, 0, sizeof(uint32_t), cs));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ctx->sm_count); cfg.blockDim = dim3(kDsThreads); cfg.dynamicSmemBytes = smem; cfg.stream = cs;

@@ -13,6 +13,9 @@ namespace tf {
 bool gemv_mma_eligible(const void* W, const void* S, const void* B, const void* x, uint32_t m, uint32_t n);
 tf_status launch_gemv_mma(tf_context* ctx, void* stream, const uint8_t* W, const uint16_t* S, const uint16_t* B,
                           const uint16_t* x, void* y, bool out_f32, uint32_t m, uint32_t n, bool sb_fp16, const char* name);
+tf_status launch_gemv_mma_batched(tf_context* ctx, void* stream, const uint8_t* W, const uint16_t* S, const uint16_t* B,
+                                  uint64_t plane_stride, const uint16_t* x, uint32_t x_stride, uint16_t* y, uint32_t y_stride,
+                                  uint32_t m, uint32_t n, uint32_t count, bool sb_fp16, const char* name);
 
 constexpr int kGemvThreads = 256;
 constexpr int kGemvWarps = kGemvThreads / kWarp;
@@ -199,6 +202,39 @@ tf_status tf_int4_gemv(tf_context* ctx, void* stream, const void* weights, uint6
                        uint32_t m, uint32_t n, tf_dtype sb_dtype) {
     return tf::launch_gemv<4>(ctx, stream, weights, weights_off, scales, scales_off, biases, biases_off,
                               x, x_off, y, y_off, m, n, sb_dtype, "tf_int4_gemv");
+}
+
+tf_status tf_int4_gemv_batched(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off,
+                               const void* scales, uint64_t scales_off, const void* biases, uint64_t biases_off,
+                               uint64_t matrix_stride_bytes, const void* x, uint64_t x_off, uint32_t x_stride_elements,
+                               void* y, uint64_t y_off, uint32_t y_stride_elements,
+                               uint32_t m, uint32_t n, uint32_t count, tf_dtype sb_dtype) {
+    const char* name = "tf_int4_gemv_batched";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, weights && scales && biases && x && y, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, m > 0 && n > 0, TF_ERR_INVALID_ARGUMENT, "%s: m and n must be positive", name);
+    TF_REQUIRE(ctx, sb_dtype == TF_BF16 || sb_dtype == TF_FP16, TF_ERR_INVALID_ARGUMENT, "%s: bad sb_dtype", name);
+    TF_REQUIRE(ctx, y_stride_elements >= m, TF_ERR_INVALID_ARGUMENT, "%s: the y stride must be at least m", name);
+    if (count == 0) return TF_OK;
+    const uint8_t* W = tf::byte_ptr(weights, weights_off);
+    const uint8_t* S = tf::byte_ptr(scales, scales_off);
+    const uint8_t* Bp = tf::byte_ptr(biases, biases_off);
+    const uint8_t* xp = tf::byte_ptr(x, x_off);
+    uint8_t* yp = tf::byte_ptr(y, y_off);
+    const bool streaming = n % 256 == 0 && tf::aligned(W, 16) && tf::aligned(S, 16) && tf::aligned(Bp, 16) && tf::aligned(xp, 16) &&
+                           matrix_stride_bytes % 16 == 0 && (x_stride_elements * 2) % 16 == 0 && tf::aligned(yp, 2) && n <= 16384;
+    if (streaming)
+        return tf::launch_gemv_mma_batched(ctx, stream, W, reinterpret_cast<const uint16_t*>(S), reinterpret_cast<const uint16_t*>(Bp),
+                                           matrix_stride_bytes, reinterpret_cast<const uint16_t*>(xp), x_stride_elements,
+                                           reinterpret_cast<uint16_t*>(yp), y_stride_elements, m, n, count, sb_dtype == TF_FP16, name);
+    // shapes or alignments the streaming kernel does not take: one ordinary GEMV per matrix
+    for (uint32_t b = 0; b < count; ++b) {
+        tf_status s = tf::launch_gemv<4>(ctx, stream, W + (size_t)b * matrix_stride_bytes, 0, S + (size_t)b * matrix_stride_bytes, 0,
+                                         Bp + (size_t)b * matrix_stride_bytes, 0, xp + (size_t)b * x_stride_elements * 2, 0,
+                                         yp + (size_t)b * y_stride_elements * 2, 0, m, n, sb_dtype, name);
+        if (s) return s;
+    }
+    return TF_OK;
 }
 
 tf_status tf_int8_gemv(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off,

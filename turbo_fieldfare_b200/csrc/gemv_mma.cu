@@ -15,18 +15,34 @@
 
 namespace tf {
 
-constexpr int kGmWarps = 8;                 // 16 rows each: 128 rows per block
-constexpr int kGmThreads = kGmWarps * kWarp;
-constexpr int kGmRows = kGmWarps * 16;
+constexpr int kGmWarps = 8;                 // 16 rows each: 128 rows per block (one large matrix)
+constexpr int kGmBatchWarps = 4;            // 64 rows per block for batches of expert-sized matrices (704 = 11 x 64)
 constexpr int kGmBlockGroups = 4;           // groups per inner step (independent MMA chains)
 
 // Shared memory: B fragments of x [ng][4 lanes t][8 words], group sums [ng], scale and bias planes of the block's
 // 128 rows [128][ng] each.
-template <bool SB_FP16, bool OUT_F32>
-__global__ void __launch_bounds__(kGmThreads)
+// A batch (blockIdx.y) walks matrices that share one layout: matrix b has its three planes `plane_stride` bytes
+// after those of matrix b - 1 (e.g. the same tensor of consecutive expert blobs), its activations x_stride and its
+// results y_stride elements further on (x_stride 0: one vector for all).
+struct GemvBatch {
+    uint64_t plane_stride;
+    uint32_t x_stride, y_stride;
+};
+
+template <bool SB_FP16, bool OUT_F32, int WARPS>
+__global__ void __launch_bounds__(WARPS * kWarp)
 gemv_mma_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, const uint16_t* __restrict__ B,
-                const uint16_t* __restrict__ x, void* __restrict__ y, uint32_t m, uint32_t n) {
+                const uint16_t* __restrict__ x, void* __restrict__ y, uint32_t m, uint32_t n, const GemvBatch bt) {
     extern __shared__ __align__(16) uint8_t smem[];
+    constexpr int kGmRows = WARPS * 16, kGmThreads = WARPS * kWarp;
+    {
+        const size_t b = blockIdx.y;
+        W += b * bt.plane_stride;
+        S = reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(S) + b * bt.plane_stride);
+        B = reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(B) + b * bt.plane_stride);
+        x += b * bt.x_stride;
+        y = static_cast<uint8_t*>(y) + b * bt.y_stride * (OUT_F32 ? 4 : 2);
+    }
     const uint32_t ng = n / kGroup;
     uint32_t* xfrag = reinterpret_cast<uint32_t*>(smem);                       // ng * 32 words
     float* xsum = reinterpret_cast<float*>(smem + (size_t)ng * 128);           // ng floats
@@ -152,10 +168,11 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, c
     }
 }
 
-size_t gemv_mma_smem_bytes(uint32_t n) {
+static size_t gemv_mma_smem_bytes_for(uint32_t n, int warps) {
     const size_t ng = n / kGroup;
-    return ng * 132 + (size_t)2 * kGmRows * ng * 2;
+    return ng * 132 + (size_t)2 * warps * 16 * ng * 2;
 }
+size_t gemv_mma_smem_bytes(uint32_t n) { return gemv_mma_smem_bytes_for(n, kGmWarps); }
 
 // Eligible: large, 16-byte aligned planes, a multiple of 256 columns (scale rows are read four groups at a time).
 bool gemv_mma_eligible(const void* W, const void* S, const void* B, const void* x, uint32_t m, uint32_t n) {
@@ -167,16 +184,34 @@ tf_status launch_gemv_mma(tf_context* ctx, void* stream, const uint8_t* W, const
                           const uint16_t* x, void* y, bool out_f32, uint32_t m, uint32_t n, bool sb_fp16, const char* name) {
     const size_t smem = gemv_mma_smem_bytes(n);
     const int which = (sb_fp16 ? 1 : 0) + (out_f32 ? 2 : 0);
-    void (*k)(const uint8_t*, const uint16_t*, const uint16_t*, const uint16_t*, void*, uint32_t, uint32_t) =
-        which == 0 ? gemv_mma_kernel<false, false> : which == 1 ? gemv_mma_kernel<true, false>
-        : which == 2 ? gemv_mma_kernel<false, true> : gemv_mma_kernel<true, true>;
-    static size_t configured[4] = {0, 0, 0, 0};
-    if (smem > configured[which]) {
-        TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured[which] = smem;
-    }
-    k<<<(m + kGmRows - 1) / kGmRows, kGmThreads, smem, static_cast<cudaStream_t>(stream)>>>(W, S, B, x, y, m, n);
+    auto k = which == 0 ? gemv_mma_kernel<false, false, kGmWarps> : which == 1 ? gemv_mma_kernel<true, false, kGmWarps>
+             : which == 2 ? gemv_mma_kernel<false, true, kGmWarps> : gemv_mma_kernel<true, true, kGmWarps>;
+    static DeviceSmemCache configured[4];
+    if (tf_status st = ensure_dynamic_smem(ctx, k, configured[which], smem)) return st;
+    k<<<(m + kGmWarps * 16 - 1) / (kGmWarps * 16), kGmWarps * kWarp, smem, static_cast<cudaStream_t>(stream)>>>(W, S, B, x, y, m, n, GemvBatch{0, 0, 0});
     return check_launch(ctx, name);
+}
+
+// `count` GEMVs over matrices of one shape whose planes repeat every plane_stride bytes, in one launch.
+tf_status launch_gemv_mma_batched(tf_context* ctx, void* stream, const uint8_t* W, const uint16_t* S, const uint16_t* B,
+                                  uint64_t plane_stride, const uint16_t* x, uint32_t x_stride, uint16_t* y, uint32_t y_stride,
+                                  uint32_t m, uint32_t n, uint32_t count, bool sb_fp16, const char* name) {
+    const size_t smem = gemv_mma_smem_bytes_for(n, kGmBatchWarps);
+    auto k = sb_fp16 ? gemv_mma_kernel<true, false, kGmBatchWarps> : gemv_mma_kernel<false, false, kGmBatchWarps>;
+    static DeviceSmemCache configured[2];
+    if (tf_status st = ensure_dynamic_smem(ctx, k, configured[sb_fp16 ? 1 : 0], smem)) return st;
+    const uint32_t rows_per_block = kGmBatchWarps * 16;
+    for (uint32_t first = 0; first < count; first += 65535u) {        // gridDim.y limit
+        const uint32_t nb = count - first < 65535u ? count - first : 65535u;
+        dim3 grid((m + rows_per_block - 1) / rows_per_block, nb);
+        k<<<grid, kGmBatchWarps * kWarp, smem, static_cast<cudaStream_t>(stream)>>>(
+            W + (size_t)first * plane_stride,
+            reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(S) + (size_t)first * plane_stride),
+            reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(B) + (size_t)first * plane_stride),
+            x + (size_t)first * x_stride, y + (size_t)first * y_stride, m, n, GemvBatch{plane_stride, x_stride, y_stride});
+        if (tf_status st = check_launch(ctx, name)) return st;
+    }
+    return TF_OK;
 }
 
 }  // namespace tf

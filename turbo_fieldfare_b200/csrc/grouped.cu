@@ -685,16 +685,22 @@ static tf_status launch_grouped_k(tf_context* ctx, void* stream, GroupedArgs& ar
     const size_t smem = lay.total();
     TF_REQUIRE(ctx, smem <= 200 * 1024, TF_ERR_UNSUPPORTED, "%s: K=%u needs %zu bytes of shared memory (limit 200 KB)", name, args.k, smem);
     auto kern = grouped_ksplit_kernel<NMAT, DENSE, OUT_MODE, KC>;
-    // Attribute and occupancy are queried once per (instantiation, warp count) and cached, so
+    // Attribute and occupancy are queried once per (instantiation, device, warp count) and cached, so
     // steady-state calls are a bare launch (and safe inside stream capture).
-    static int cached_per_sm[kMaxComputeWarps + 1] = {0};
-    int per_sm = cached_per_sm[cw];
-    if (per_sm == 0) {
-        TF_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        TF_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, (int)((cw + kExtraWarps) * kWarp), smem));
-        if (per_sm < 1) per_sm = 1;
-        if (per_sm > 8) per_sm = 8;
-        cached_per_sm[cw] = per_sm;
+    static std::mutex cache_mu;
+    static int cached_per_sm[kMaxDevices][kMaxComputeWarps + 1] = {};
+    const int dev = ctx->device >= 0 && ctx->device < kMaxDevices ? ctx->device : -1;
+    int per_sm = 0;
+    {
+        std::lock_guard<std::mutex> lock(cache_mu);
+        if (dev >= 0) per_sm = cached_per_sm[dev][cw];
+        if (per_sm == 0) {
+            TF_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            TF_CUDA(ctx, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, (int)((cw + kExtraWarps) * kWarp), smem));
+            if (per_sm < 1) per_sm = 1;
+            if (per_sm > 8) per_sm = 8;
+            if (dev >= 0) cached_per_sm[dev][cw] = per_sm;
+        }
     }
     args.error = ctx->device_error;
     uint32_t grid = (uint32_t)ctx->sm_count * (uint32_t)per_sm;
@@ -915,7 +921,9 @@ tf_status tf_shared_expert_int4_block_noalloc(void* stream, const void* x, uint6
                         name, rows, gate->rows, (unsigned long long)need, tf::kNoAllocScratchBytes);
     tf::NoAllocDevice* dev = nullptr;
     if (tf_status s = tf::noalloc_device(&dev, name)) return s;      // first call on a device: the one-time set-up
-    // A context on the stack: nothing in it is allocated on the device, the launch code only reads these fields.
+    // A context on the stack: nothing in it is allocated on the device. tf_shared_expert_int4_block and the launch
+    // code under it use only device, sm_count, device_error, launches and last_error; the side stream, the router
+    // and tensor-core scratch stay NULL and must not be touched on this path.
     tf_context local;
     cudaGetDevice(&local.device);
     local.sm_count = dev->sm_count;

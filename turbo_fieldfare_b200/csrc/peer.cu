@@ -6,8 +6,10 @@
 // barrier (one release store per peer, one bounded acquire wait per peer) orders the phases. Everything is plain
 // kernels with plain peer loads and stores, so a whole decode step, exchange included, replays as one CUDA graph.
 //
-// Every wait is bounded: after kPeerSpinLimit polls the kernel records kErrPeerTimeout in the context's device error
-// word and returns; once that word is set, later barriers do not wait at all, so a missing rank costs one timeout.
+// Every wait is bounded: after kPeerSpinLimit polls the kernel records kErrPeerTimeout in the context's peer status
+// word (its own word: codes of other kernels do not touch it) and returns; once that word is set, later barriers do
+// not wait at all, so a missing rank costs one timeout. From that point on the ranks are no longer synchronised and
+// every result is invalid until tf_device_status has reported and cleared the code.
 // Ranks must run one process per GPU (kernels that wait on one another never share a GPU).
 #include "tf_common.cuh"
 
@@ -196,7 +198,7 @@ tf_status tf_ep_peer_push(tf_context* ctx, void* stream, const void* src_rows, u
     tf::ep_peer_push_kernel<<<grid, tf::kPeerPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(src_rows), src_stride_elements, (uint8_t* const*)peer_bases_device,
         dst_offset_bytes, dst_stride_elements, copy_elements, slot_ids, tail_at_element, world, rank, capacity,
-        flags_offset_bytes, epoch_and_ticket_device, ctx->device_error);
+        flags_offset_bytes, epoch_and_ticket_device, ctx->peer_error);
     return tf::check_launch(ctx, name);
 }
 
@@ -208,7 +210,7 @@ tf_status tf_ep_peer_barrier(tf_context* ctx, void* stream, const void* const* p
     TF_REQUIRE(ctx, world > 0 && world <= 32 && rank < world, TF_ERR_INVALID_ARGUMENT, "%s: world must be 1...32", name);
     TF_REQUIRE(ctx, flags_offset_bytes % 4 == 0, TF_ERR_ALIGNMENT, "%s: flags must be 4-byte aligned", name);
     tf::ep_peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        (uint8_t* const*)peer_bases_device, flags_offset_bytes, epoch_counter_device, ctx->device_error, world, rank);
+        (uint8_t* const*)peer_bases_device, flags_offset_bytes, epoch_counter_device, ctx->peer_error, world, rank);
     return tf::check_launch(ctx, name);
 }
 

@@ -698,11 +698,8 @@ static tf_status launch_qmm(tf_context* ctx, void* stream, QmmArgs& a, const voi
     qmm_prepare_kernel<<<1, 32, 0, st>>>(a, NMAT, dense ? 1 : 0);
     if (tf_status s = check_launch(ctx, "qmm_prepare")) return s;
     auto kern = qmm_tcgen05_kernel<NMAT, NATURAL_K>;
-    static uint32_t configured = 0;
-    if (smem > configured) {
-        TF_CUDA(ctx, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
+    static DeviceSmemCache configured;
+    if (tf_status s = ensure_dynamic_smem(ctx, kern, configured, smem)) return s;
     kern<<<ctx->sm_count, kQmmThreads, smem, st>>>(xmap, xmap_big, wmap[0], wmap[1], a);
     return check_launch(ctx, name);
 }

@@ -251,9 +251,24 @@ router_split_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
                          out_w + (size_t)row * top_k, lane);
     if (grp.sorted_pairs == nullptr) return;
     if (gridDim.x == 1) {
-        // One token: its experts are distinct, so a pair's place is the number of selected experts with a smaller id;
-        // every group holds one pair and one chunk.
+        // One token: a pair's place is the number of selected experts with a smaller id; every group holds one pair
+        // and one chunk. That needs distinct experts: a row with fewer than top_k selectable logits (NaN, -inf)
+        // repeats expert 0, and then the general grouping below merges the repeats into one group.
         __syncthreads();                       // warp 0 has written the row's indices and weights
+        int repeated = 0;
+        if (threadIdx.x < top_k) {
+            uint32_t mine = out_idx[threadIdx.x];
+            if (mine >= num_experts) mine = num_experts - 1;
+            for (uint32_t r = 0; r < top_k; ++r) {
+                uint32_t other = out_idx[r];
+                if (other >= num_experts) other = num_experts - 1;
+                repeated |= (r != threadIdx.x && other == mine) ? 1 : 0;
+            }
+        }
+        if (__syncthreads_or(repeated)) {
+            group_routes_in_block(out_idx, out_w, 1, top_k, num_experts, grp, smem);
+            return;
+        }
         for (uint32_t e = threadIdx.x; e < num_experts; e += blockDim.x) {
             grp.per_expert_counts[e] = 0u;
             grp.per_expert_offsets[e] = 0xFFFFFFFFu;
@@ -439,11 +454,8 @@ static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, 
     } else if (rows >= 256 && a2 && (size_t)kTileRouterRows * (d + num_experts) * 4 <= 100 * 1024) {
         auto k = bf ? router_tile_kernel<true> : router_tile_kernel<false>;
         const size_t smem_tile = (size_t)kTileRouterRows * (d + num_experts) * 4;
-        static size_t configured[2] = {0, 0};
-        if (smem_tile > configured[bf ? 1 : 0]) {
-            TF_CUDA(ctx, cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_tile));
-            configured[bf ? 1 : 0] = smem_tile;
-        }
+        static DeviceSmemCache configured[2];
+        if (tf_status s = ensure_dynamic_smem(ctx, k, configured[bf ? 1 : 0], smem_tile)) return s;
         launch_pdl(k, dim3((rows + kTileRouterRows - 1) / kTileRouterRows), dim3(kBlockRouterThreads), smem_tile, st, W, Sp, Bp, hp, stride,
                    ep, pp, logit_bias, out_idx, wp, out_logits, rows, num_experts, d, top_k);
     } else {

@@ -41,6 +41,9 @@ struct tf_context {
     unsigned int* router_tickets = nullptr;  // [kRouterSplitRows], self-resetting
     // One device word that kernels with bounded waits set when a wait gives up (0 = healthy).
     uint32_t* device_error = nullptr;
+    // The same for the flag barriers of the peer exchange (peer.cu), kept apart so that a code from another kernel
+    // cannot switch the cross-GPU waits off.
+    uint32_t* peer_error = nullptr;
     // Arrival counter of the grid barriers of the single-launch decode step (zeroed on the stream before each launch).
     uint32_t* grid_barrier = nullptr;
     // tf_stack_forward runs a one-token step as one persistent launch when set (tf_context_set_single_launch_step).
@@ -93,6 +96,24 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr; cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// Function attributes and occupancy are properties of (kernel, device): caches of them are keyed by the device ordinal
+// and guarded, so a second GPU in the same process (or a second thread) configures its own copy of a kernel.
+constexpr int kMaxDevices = 64;
+struct DeviceSmemCache {
+    std::mutex mu;
+    uint32_t bytes[kMaxDevices] = {};
+};
+// Raises the kernel's dynamic shared-memory limit on ctx's device to at least `bytes` (once per device and size).
+template <typename Kernel>
+inline tf_status ensure_dynamic_smem(tf_context* ctx, Kernel kernel, DeviceSmemCache& cache, size_t bytes) {
+    const int dev = ctx->device >= 0 && ctx->device < kMaxDevices ? ctx->device : -1;
+    std::lock_guard<std::mutex> lock(cache.mu);
+    if (dev >= 0 && bytes <= cache.bytes[dev]) return TF_OK;
+    TF_CUDA(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (dev >= 0) cache.bytes[dev] = (uint32_t)bytes;
+    return TF_OK;
 }
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }

@@ -282,10 +282,14 @@ class EPBuffers:
         torch.cuda.synchronize()
 
     def _drop_peer_buffers(self) -> None:
+        """Collective tear-down in the order CUDA IPC asks for: every rank closes its imports, all ranks meet, and only
+        then does each rank free the buffer it exported (freeing exported memory that a peer still maps is undefined)."""
         ctx, lib = self.stack.context, self.stack.context.lib
         for p in self._imported:
             lib.tf_peer_buffer_release(ctx.handle, p)
         self._imported = []
+        if self.stack.world > 1:
+            dist.barrier(group=self.stack.group)
         if self._peer_handle is not None:
             lib.tf_peer_buffer_destroy(self._peer_handle)
             self._peer_handle = None
@@ -298,8 +302,9 @@ class EPBuffers:
 
     def close(self) -> None:
         """Unmaps the peers' buffers and frees this rank's (collective when peers are mapped)."""
-        if self._peer_handle is None:
+        if not self.peer:
             return
+        self.peer = False
         torch.cuda.synchronize()
         if self.stack.world > 1:
             dist.barrier(group=self.stack.group)     # nobody is still writing into a buffer that is about to go

@@ -123,6 +123,17 @@ class DequantInt4GEMV:
                      _ptr(biases), biases_offset, _ptr(x), x_offset, _ptr(y), y_offset, m, n, sb_dtype))
 
 
+    def encode_batched(self, weights, scales, biases, matrix_stride_bytes: int, x, y, m: int, n: int, count: int, *,
+                       weights_offset=0, scales_offset=0, biases_offset=0, x_offset=0, x_stride_elements=0, y_offset=0,
+                       y_stride_elements=None, sb_dtype=TF_BF16, stream=None) -> None:
+        """``count`` GEMVs over matrices of one layout (planes ``matrix_stride_bytes`` apart) in one launch."""
+        ctx = self.context
+        ctx.check(ctx.lib.tf_int4_gemv_batched(ctx.handle, _stream(stream), _ptr(weights), weights_offset, _ptr(scales),
+                                               scales_offset, _ptr(biases), biases_offset, matrix_stride_bytes, _ptr(x), x_offset,
+                                               x_stride_elements, _ptr(y), y_offset, m if y_stride_elements is None else y_stride_elements,
+                                               m, n, count, sb_dtype))
+
+
 class DequantInt8GEMV(DequantInt4GEMV):
     """``DequantInt8GEMV`` (Kernels/Quant/DequantInt8GEMV.swift:16-82)."""
     _fn = "tf_int8_gemv"
