@@ -315,6 +315,38 @@ tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream,
                                  const tf_expert_offsets* offsets, const tf_device_routes* routes,
                                  void* acts_scratch, void* route_partials, int partials_f32,
                                  uint32_t query_count, uint32_t d, uint32_t f, uint32_t top_k);
+/* The reference's streamed form of the batched routed experts: one tile of at most 16 live experts bound to blob
+ * base addresses, and the 128-byte parameter block whose layout its tests pin
+ * (PrefillGroupedRoutedMoEStreamedParams, Kernels/Prefill/MoE/PrefillGroupedRoutedMoE.swift:104-183;
+ * Tests/.../Prefill/PrefillGroupedRoutedMoETests+Layout.swift:7-28). */
+#define TF_STREAMED_MAX_EXPERTS 16
+typedef struct tf_streamed_params {
+    uint32_t pair_start;                 /* first sorted pair of the tile */
+    uint32_t pair_count;
+    uint32_t d;
+    uint32_t routed_intermediate;        /* F */
+    uint32_t top_k;
+    uint32_t hidden_stride_elements;
+    uint32_t live_expert_count;
+    uint32_t local_expert[TF_STREAMED_MAX_EXPERTS];   /* expert id of local slot i; UINT32_MAX when unused */
+    uint32_t gate_w_off, gate_s_off, gate_b_off, up_w_off, up_s_off, up_b_off, down_w_off, down_s_off, down_b_off;
+} tf_streamed_params;
+/* Replaces PrefillGroupedRoutedMoE.encodeStreamedBatched (PrefillGroupedRoutedMoE.swift:386-461) for the sorted pairs
+ * [pair_start, pair_start + pair_count): per pair gate, up, act = half(gelu(g) * u), down, written to
+ * route_partials[(token * top_k + rank) * d] as fp16. `blobs` is a HOST array of blob_count device addresses, blob i
+ * holding expert params->local_expert[i] (the views of PrefillStreamedTileBinding, :185-214); every expert of the pair
+ * range must be bound (a pair of an unbound expert is skipped and tf_device_status reports 0x7F000031).
+ * gate_up_act_scratch holds pair_count * F fp16; the reference's second scratch is not needed. The call does all pairs
+ * at once; pair_microbatch_rows only sets *microbatches_out (the reference's return value) and must be positive.
+ * As there, pair_count == 0, live_expert_count != blob_count or pair_microbatch_rows == 0 do nothing and return TF_OK
+ * with *microbatches_out = 0. At most 65536 pairs per call. */
+tf_status tf_grouped_moe_streamed(tf_context* ctx, void* stream,
+                                  const void* hidden, uint64_t hidden_off,
+                                  const void* sorted_pairs, uint64_t sorted_pairs_off,
+                                  void* route_partials, uint64_t route_partials_off,
+                                  void* gate_up_act_scratch, uint64_t gate_up_act_scratch_off,
+                                  const void* const* blobs, uint32_t blob_count, const tf_streamed_params* params,
+                                  uint32_t pair_microbatch_rows, uint32_t* microbatches_out);
 /* h2[t,d] = half(sum_r w[t,r] * partial[t,r,d] (+ residual[t,d])), rank order.
  * Replaces PrefillMoE.encodeReduceTokenMajor (Kernels/Prefill/MoE/PrefillMoE.swift:11-39);
  * residual may be NULL (the reference has none); with fp32 partials the order is

@@ -101,3 +101,14 @@ def test_host_grouping_matches_oracle_on_random_routes(lib, oracle, T, K, E, til
     assert np.array_equal(got.per_expert_offsets, ref.per_expert_offsets)
     assert np.array_equal(got.per_expert_counts, ref.per_expert_counts)
     assert got.groups.tobytes() == ref.groups.tobytes() and got.tiles.tobytes() == ref.tiles.tobytes()
+
+
+def test_streamed_params_layout_is_the_reference_one():
+    """PrefillGroupedRoutedMoETests+Layout.swift:7-28: 128 bytes, the pinned member offsets."""
+    from turbo_fieldfare_b200._capi import StreamedParams as P
+    assert C.sizeof(P) == 128
+    want = {"pair_start": 0, "pair_count": 4, "d": 8, "routed_intermediate": 12, "top_k": 16, "hidden_stride_elements": 20,
+            "live_expert_count": 24, "local_expert": 28, "gate_w_off": 92, "down_b_off": 124}
+    for name, offset in want.items():
+        assert getattr(P, name).offset == offset, name
+    assert P.local_expert.offset + 15 * 4 == 88           # localExpert15

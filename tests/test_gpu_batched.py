@@ -97,6 +97,91 @@ def test_grouped_moe_closed_form_fixture(tf_ctx, oracle):
     assert np.max(np.abs(o.f16_to_f32(got) - o.f16_to_f32(ref))) <= 0.0015
 
 
+def _run_streamed(tf_ctx, o, blobs_h, bound_experts, off, hidden16, pairs_sorted, pair_start, pair_count, D, F, K, microbatch=4):
+    """tf_grouped_moe_streamed on separately allocated blobs (one device buffer per bound expert, in the given slot order)."""
+    import ctypes as C
+    import torch
+    from turbo_fieldfare_b200._capi import StreamedParams
+    from turbo_fieldfare_b200.kernels import _ptr
+    T = hidden16.shape[0]
+    devs = [to_dev(b) for b in blobs_h]
+    table = (C.c_void_p * len(devs))(*[d.data_ptr() for d in devs])
+    p = StreamedParams()
+    p.pair_start, p.pair_count, p.d, p.routed_intermediate, p.top_k, p.hidden_stride_elements = pair_start, pair_count, D, F, K, D
+    p.live_expert_count = len(devs)
+    for i in range(16):
+        p.local_expert[i] = bound_experts[i] if i < len(bound_experts) else 0xFFFFFFFF
+    (p.gate_w_off, p.gate_s_off, p.gate_b_off, p.up_w_off, p.up_s_off, p.up_b_off, p.down_w_off, p.down_s_off, p.down_b_off) = (
+        off.gate_w, off.gate_s, off.gate_b, off.up_w, off.up_s, off.up_b, off.down_w, off.down_s, off.down_b)
+    pairs_dev = to_dev(np.ascontiguousarray(pairs_sorted).view(np.uint32))
+    partials = dev_zeros_u16(T * K * D, fill=0x7E00)
+    acts = dev_zeros_u16(max(pair_count, 1) * F)
+    n_mb = C.c_uint32(99)
+    tf_ctx.check(tf_ctx.lib.tf_grouped_moe_streamed(tf_ctx.handle, 0, _ptr(to_dev(hidden16)), 0, _ptr(pairs_dev), 0, _ptr(partials), 0,
+                                                    _ptr(acts), 0, table, len(devs), C.byref(p), microbatch, C.byref(n_mb)))
+    torch.cuda.synchronize()
+    return from_dev(partials, np.uint16).reshape(T, K, D), int(n_mb.value)
+
+
+def test_grouped_moe_streamed_closed_form_fixture(tf_ctx, oracle):
+    """The reference's streamed execution test (PrefillGroupedRoutedMoETests+Execution.swift:8-103): the closed-form
+    fixture through the tile-binding form (blob addresses + the 128-byte parameter block), max-abs <= 0.0015, two
+    microbatches at four rows; bound experts in an order that is not the sorted one; then only part of the pairs."""
+    o = oracle
+    E, D, F, T, K = 16, 64, 64, 3, 2
+    pool, off, stride = _closed_form_pool(o, E, D, F)
+    hidden = (((np.arange(T * D) % 17) - 8) * 0.01).astype(np.float32).reshape(T, D)
+    h16 = o.f32_to_f16(hidden)
+    idx = np.array([[3, 9], [9, 1], [15, 3]], dtype=np.uint32)
+    w16 = o.f32_to_f16(np.full((T, K), 0.5, dtype=np.float32))
+    pairs = o.make_token_expert_pairs(idx, w16, T, K)
+    routes = o.group_pairs(pairs, T, K, E)
+    sorted_pairs = routes.sorted_pairs
+    ref = o.f16_to_f32(o.grouped_moe_pairs(pool, stride, off, h16, 0, pairs, D, F, K, T))
+    bound = [9, 1, 15, 3]                                  # slot order differs from the sorted expert order
+    blobs = [pool[e * stride:(e + 1) * stride].copy() for e in bound]
+    got, n_mb = _run_streamed(tf_ctx, o, blobs, bound, off, h16, sorted_pairs, 0, T * K, D, F, K, microbatch=4)
+    assert tf_ctx.device_status() == 0
+    assert n_mb == 2
+    assert np.max(np.abs(o.f16_to_f32(got) - ref)) <= 0.0015
+    # the second half of the sorted pairs only: the other partial rows stay untouched
+    got2, n_mb2 = _run_streamed(tf_ctx, o, blobs, bound, off, h16, sorted_pairs, 3, 3, D, F, K, microbatch=32)
+    assert n_mb2 == 1 and tf_ctx.device_status() == 0
+    touched = np.zeros((T, K), dtype=bool)
+    for pr in sorted_pairs[3:6]:
+        touched[int(pr["token"]), int(pr["rank"])] = True
+    assert np.max(np.abs(o.f16_to_f32(got2)[touched] - ref[touched])) <= 0.0015
+    assert (got2[~touched] == 0x7E00).all()
+    # nothing to do (PrefillGroupedRoutedMoE.swift:402-404): no launch, zero microbatches
+    before = tf_ctx.launch_count
+    _, n0 = _run_streamed(tf_ctx, o, blobs, bound, off, h16, sorted_pairs, 0, 0, D, F, K)
+    assert n0 == 0 and tf_ctx.launch_count == before
+
+
+def test_grouped_moe_streamed_reports_unbound_expert(tf_ctx, oracle):
+    """A pair whose expert is not bound in the tile is skipped and reported (the reference validates this on the
+    host: PrefillStreamedTileBinding.validateCoversPairs, PrefillGroupedRoutedMoE.swift:287-301)."""
+    from turbo_fieldfare_b200.kernels import TFError
+    o = oracle
+    E, D, F, T, K = 16, 64, 64, 3, 2
+    pool, off, stride = _closed_form_pool(o, E, D, F)
+    h16 = o.f32_to_f16((((np.arange(T * D) % 17) - 8) * 0.01).astype(np.float32).reshape(T, D))
+    idx = np.array([[3, 9], [9, 1], [15, 3]], dtype=np.uint32)
+    w16 = o.f32_to_f16(np.full((T, K), 0.5, dtype=np.float32))
+    pairs = o.make_token_expert_pairs(idx, w16, T, K)
+    sorted_pairs = o.group_pairs(pairs, T, K, E).sorted_pairs
+    bound = [1, 3, 9]                                       # expert 15 is missing
+    blobs = [pool[e * stride:(e + 1) * stride].copy() for e in bound]
+    got, _ = _run_streamed(tf_ctx, o, blobs, bound, off, h16, sorted_pairs, 0, T * K, D, F, K)
+    with pytest.raises(TFError):
+        tf_ctx.device_status()
+    assert tf_ctx.device_status() == 0                      # reported once, then cleared
+    ref = o.f16_to_f32(o.grouped_moe_pairs(pool, stride, off, h16, 0, pairs, D, F, K, T))
+    ok = idx != 15
+    assert np.max(np.abs(o.f16_to_f32(got)[ok] - ref[ok])) <= 0.0015
+    assert (got[~ok] == 0x7E00).all()
+
+
 @pytest.mark.parametrize("T,D,F,E,K", [(1, 128, 64, 16, 8), (5, 128, 64, 16, 8), (40, 256, 128, 8, 4), (64, 2816, 704, 16, 8)])
 def test_grouped_moe_random_vs_oracle(tf_ctx, oracle, T, D, F, E, K):
     """Config-2 style: T tokens scattered over E experts (up to 64 x 8 pairs on 16 experts: chunks of 8 and ragged tails)."""

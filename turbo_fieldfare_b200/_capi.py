@@ -65,6 +65,15 @@ class GTurboTensor(C.Structure):
                 ("bias_size", u64), ("shape", u32 * 4), ("dtype", C.c_uint8), ("reserved", C.c_uint8 * 7)]
 
 
+class StreamedParams(C.Structure):
+    """tf_streamed_params: the 128-byte PrefillGroupedRoutedMoEStreamedParams
+    (Kernels/Prefill/MoE/PrefillGroupedRoutedMoE.swift:104-183)."""
+    _fields_ = ([(n, u32) for n in ("pair_start", "pair_count", "d", "routed_intermediate", "top_k", "hidden_stride_elements",
+                                    "live_expert_count")] + [("local_expert", u32 * 16)] +
+                [(n, u32) for n in ("gate_w_off", "gate_s_off", "gate_b_off", "up_w_off", "up_s_off", "up_b_off",
+                                    "down_w_off", "down_s_off", "down_b_off")])
+
+
 class DeviceRoutes(C.Structure):
     """tf_device_routes: device buffers of the grouped routing metadata."""
     _fields_ = [(n, vp) for n in ("sorted_pairs", "per_expert_offsets", "per_expert_counts", "groups",
@@ -101,6 +110,7 @@ SIGNATURES = {
     "tf_group_routes_device": (C.c_int, [vp, vp, vp, vp, u32, u32, u32, C.POINTER(DeviceRoutes)]),
     "tf_grouped_moe_batched": (C.c_int, [vp, vp, vp, u64, u32, vp, u64, C.POINTER(ExpertOffsets), C.POINTER(DeviceRoutes),
                                          vp, vp, C.c_int, u32, u32, u32, u32]),
+    "tf_grouped_moe_streamed": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, vp, u64, C.POINTER(vp), u32, vp, u32, C.POINTER(u32)]),
     "tf_moe_reduce_token_major": (C.c_int, [vp, vp, vp, C.c_int, vp, vp, u32, vp, u32, u32, u32, u32]),
     "tf_shared_expert_int4_block": (C.c_int, [vp, vp, vp, u64, u32, C.POINTER(Projection), C.POINTER(Projection),
                                               C.POINTER(Projection), vp, u64, u32, vp, u32]),

@@ -6,6 +6,8 @@
 
 namespace tf {
 
+size_t streamed_scratch_bytes();      // grouped.cu
+
 std::string& global_error() {
     static std::string s;
     return s;
@@ -79,6 +81,7 @@ tf_status tf_context_create(int device, tf_context** out) {
     if (e == cudaSuccess) e = cudaMemset(ctx->device_error, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->peer_error, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->peer_error, 0, sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->streamed_scratch, tf::streamed_scratch_bytes());
     if (e == cudaSuccess) e = cudaMalloc(&ctx->grid_barrier, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->grid_barrier, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_groups, 2 * 64 * (TF_MAX_ROUTER_EXPERTS + 1));   // routed and dense tables
@@ -102,6 +105,7 @@ void tf_context_destroy(tf_context* ctx) {
     if (ctx->router_tickets) cudaFree(ctx->router_tickets);
     if (ctx->device_error) cudaFree(ctx->device_error);
     if (ctx->peer_error) cudaFree(ctx->peer_error);
+    if (ctx->streamed_scratch) cudaFree(ctx->streamed_scratch);
     if (ctx->grid_barrier) cudaFree(ctx->grid_barrier);
     if (ctx->qmm_groups) cudaFree(ctx->qmm_groups);
     if (ctx->qmm_totals) cudaFree(ctx->qmm_totals);

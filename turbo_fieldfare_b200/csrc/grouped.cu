@@ -844,6 +844,143 @@ tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream, const void* hidd
     return tf::launch_grouped<1, false, tf::kOutPartialF16, 704>(ctx, stream, b, "tf_grouped_moe_batched(down)");
 }
 
+}  // extern "C"
+
+namespace tf {
+
+constexpr uint32_t kStreamedMaxPairs = 65536;       // pairs of one tf_grouped_moe_streamed call
+constexpr uint32_t kErrUnboundExpert = 0x7F000031u; // a pair's expert is not among the tile's bound experts
+
+// Scratch layout of the streamed form inside tf_context::streamed_scratch.
+struct StreamedScratch {
+    tf_group groups[TF_STREAMED_MAX_EXPERTS];
+    uint32_t chunk_start[TF_STREAMED_MAX_EXPERTS];
+    uint32_t counters[4];
+    uint32_t chunk_group[kStreamedMaxPairs / kChunkTokens + TF_STREAMED_MAX_EXPERTS];
+};
+size_t streamed_scratch_bytes() { return sizeof(StreamedScratch); }
+
+struct StreamedBinding {
+    uint32_t expert[TF_STREAMED_MAX_EXPERTS];       // params.local_expert
+    uint32_t blob16[TF_STREAMED_MAX_EXPERTS];       // (blob - lowest blob) / 16
+    uint32_t live;
+};
+
+// The pairs of one tile are sorted by expert, so a bound expert's pairs are one run. One block: count the run of
+// every bound expert, then emit the groups in order of appearance with the blob's encoded address in the expert
+// field (the grouped kernel computes blob = base + expert * 16), and the 8-token chunk table.
+__global__ void streamed_routes_kernel(const tf_pair* __restrict__ pairs, uint32_t count, const StreamedBinding bind,
+                                       StreamedScratch* out, uint32_t* error) {
+    __shared__ uint32_t hist[TF_STREAMED_MAX_EXPERTS], first[TF_STREAMED_MAX_EXPERTS];
+    if (threadIdx.x < TF_STREAMED_MAX_EXPERTS) { hist[threadIdx.x] = 0u; first[threadIdx.x] = 0xFFFFFFFFu; }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < count; i += blockDim.x) {
+        const uint32_t e = pairs[i].expert;
+        uint32_t slot = 0xFFFFFFFFu;
+        for (uint32_t sl = 0; sl < bind.live; ++sl)
+            if (bind.expert[sl] == e) { slot = sl; break; }
+        if (slot == 0xFFFFFFFFu) { atomicCAS(error, 0u, kErrUnboundExpert); continue; }
+        atomicAdd(&hist[slot], 1u);
+        atomicMin(&first[slot], i);
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    uint32_t ng = 0, nch = 0;
+    uint32_t last_first = 0;
+    for (uint32_t round = 0; round < bind.live; ++round) {
+        // next bound expert in order of appearance
+        uint32_t best = 0xFFFFFFFFu, best_first = 0xFFFFFFFFu;
+        for (uint32_t sl = 0; sl < bind.live; ++sl)
+            if (hist[sl] && first[sl] < best_first && (round == 0 || first[sl] > last_first)) { best = sl; best_first = first[sl]; }
+        if (best == 0xFFFFFFFFu) break;
+        last_first = best_first;
+        const uint32_t cnt = hist[best], ch = (cnt + kChunkTokens - 1) / kChunkTokens;
+        out->groups[ng] = tf_group{bind.blob16[best], best_first, cnt};
+        out->chunk_start[ng] = nch;
+        for (uint32_t j = 0; j < ch; ++j) out->chunk_group[nch + j] = ng;
+        ++ng; nch += ch;
+    }
+    out->counters[0] = ng; out->counters[1] = nch; out->counters[2] = count; out->counters[3] = 0u;
+}
+
+}  // namespace tf
+
+extern "C" {
+
+tf_status tf_grouped_moe_streamed(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off,
+                                  const void* sorted_pairs, uint64_t sorted_pairs_off,
+                                  void* route_partials, uint64_t route_partials_off,
+                                  void* gate_up_act_scratch, uint64_t gate_up_act_scratch_off,
+                                  const void* const* blobs, uint32_t blob_count, const tf_streamed_params* params,
+                                  uint32_t pair_microbatch_rows, uint32_t* microbatches_out) {
+    const char* name = "tf_grouped_moe_streamed";
+    if (microbatches_out) *microbatches_out = 0;
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, params != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: params is NULL", name);
+    // PrefillGroupedRoutedMoE.swift:402-404: nothing to do, no error
+    if (params->pair_count == 0 || params->live_expert_count != blob_count || pair_microbatch_rows == 0) return TF_OK;
+    TF_REQUIRE(ctx, hidden && sorted_pairs && route_partials && gate_up_act_scratch && blobs, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    TF_REQUIRE(ctx, blob_count >= 1 && blob_count <= TF_STREAMED_MAX_EXPERTS, TF_ERR_INVALID_ARGUMENT,
+               "tile binding has %u experts; expected 1...%d", blob_count, TF_STREAMED_MAX_EXPERTS);       // :188-195
+    TF_REQUIRE(ctx, params->pair_count <= tf::kStreamedMaxPairs, TF_ERR_SCRATCH_TOO_SMALL, "%s: %u pairs exceed the %u a call can take",
+               name, params->pair_count, tf::kStreamedMaxPairs);
+    const uint32_t d = params->d, f = params->routed_intermediate;
+    TF_REQUIRE(ctx, d % tf::kGroup == 0 && f % tf::kGroup == 0 && d > 0 && f > 0, TF_ERR_INVALID_ARGUMENT,
+               "%s: D and F must be positive multiples of 64", name);
+    TF_REQUIRE(ctx, params->top_k > 0 && params->hidden_stride_elements >= d, TF_ERR_INVALID_ARGUMENT, "%s: bad topK or hidden stride", name);
+    const tf_expert_offsets offsets{params->gate_w_off, params->gate_s_off, params->gate_b_off, params->up_w_off, params->up_s_off,
+                                    params->up_b_off, params->down_w_off, params->down_s_off, params->down_b_off};
+    // blob addresses relative to the lowest one, in units of 16 bytes (the grouped kernel's expert stride)
+    const uint8_t* lowest = static_cast<const uint8_t*>(blobs[0]);
+    for (uint32_t i = 0; i < blob_count; ++i) {
+        TF_REQUIRE(ctx, blobs[i] != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: blob %u is NULL", name, i);
+        for (uint32_t j = 0; j < i; ++j)
+            TF_REQUIRE(ctx, params->local_expert[i] != params->local_expert[j], TF_ERR_INVALID_ARGUMENT,
+                       "duplicate expert id %u in tile binding", params->local_expert[i]);                 // :204-207
+        if (static_cast<const uint8_t*>(blobs[i]) < lowest) lowest = static_cast<const uint8_t*>(blobs[i]);
+    }
+    if (tf_status s = tf::check_blob_alignment(ctx, lowest, 16, &offsets, name)) return s;
+    tf::StreamedBinding bind{};
+    bind.live = blob_count;
+    for (uint32_t i = 0; i < blob_count; ++i) {
+        const uint64_t delta = (uint64_t)(static_cast<const uint8_t*>(blobs[i]) - lowest);
+        TF_REQUIRE(ctx, delta % 16 == 0, TF_ERR_ALIGNMENT, "%s: blobs must be 16-byte aligned", name);
+        TF_REQUIRE(ctx, delta / 16 <= 0xFFFFFFFFull, TF_ERR_UNSUPPORTED, "%s: the bound blobs span more than 64 GiB", name);
+        bind.expert[i] = params->local_expert[i];
+        bind.blob16[i] = (uint32_t)(delta / 16);
+    }
+    const uint8_t* hp = tf::byte_ptr(hidden, hidden_off);
+    uint8_t* acts = tf::byte_ptr(gate_up_act_scratch, gate_up_act_scratch_off);
+    const tf_pair* pairs = reinterpret_cast<const tf_pair*>(tf::byte_ptr(sorted_pairs, sorted_pairs_off)) + params->pair_start;
+    TF_REQUIRE(ctx, tf::aligned(hp, 16) && (params->hidden_stride_elements * 2) % 16 == 0 && tf::aligned(acts, 16) && tf::aligned(pairs, 4),
+               TF_ERR_ALIGNMENT, "%s: hidden rows and the activation scratch must be 16-byte aligned", name);
+    TF_REQUIRE(ctx, ctx->streamed_scratch != nullptr, TF_ERR_OUT_OF_MEMORY, "%s: context scratch missing", name);
+    auto* scratch = static_cast<tf::StreamedScratch*>(ctx->streamed_scratch);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    tf::streamed_routes_kernel<<<1, 256, 0, st>>>(pairs, params->pair_count, bind, scratch, ctx->device_error);
+    if (tf_status s = tf::check_launch(ctx, name)) return s;
+
+    tf::GroupedArgs a{};
+    a.pool_base = lowest; a.expert_stride = 16;
+    a.w_off[0] = offsets.gate_w_off; a.s_off[0] = offsets.gate_s_off; a.b_off[0] = offsets.gate_b_off;
+    a.w_off[1] = offsets.up_w_off;   a.s_off[1] = offsets.up_s_off;   a.b_off[1] = offsets.up_b_off;
+    a.sorted_pairs = pairs; a.groups = scratch->groups; a.chunk_group = scratch->chunk_group;
+    a.chunk_start = scratch->chunk_start; a.counters = scratch->counters;
+    a.x = reinterpret_cast<const uint16_t*>(hp); a.x_stride = params->hidden_stride_elements;
+    a.out = acts; a.out_stride = f; a.rows = f; a.k = d; a.top_k = params->top_k;
+    if (tf_status s = tf::launch_grouped<2, false, tf::kOutActs, 2816>(ctx, stream, a, "tf_grouped_moe_streamed(gate/up)")) return s;
+    tf::GroupedArgs b{};
+    b.pool_base = lowest; b.expert_stride = 16;
+    b.w_off[0] = offsets.down_w_off; b.s_off[0] = offsets.down_s_off; b.b_off[0] = offsets.down_b_off;
+    b.sorted_pairs = pairs; b.groups = scratch->groups; b.chunk_group = scratch->chunk_group;
+    b.chunk_start = scratch->chunk_start; b.counters = scratch->counters;
+    b.x = reinterpret_cast<const uint16_t*>(acts); b.x_stride = f;
+    b.out = tf::byte_ptr(route_partials, route_partials_off); b.out_stride = d; b.rows = d; b.k = f; b.top_k = params->top_k;
+    if (tf_status s = tf::launch_grouped<1, false, tf::kOutPartialF16, 704>(ctx, stream, b, "tf_grouped_moe_streamed(down)")) return s;
+    if (microbatches_out) *microbatches_out = (params->pair_count + pair_microbatch_rows - 1) / pair_microbatch_rows;
+    return TF_OK;
+}
+
 tf_status tf_moe_reduce_token_major(tf_context* ctx, void* stream, const void* route_partials, int partials_f32,
                                     const void* route_weights, const void* residual, uint32_t residual_stride_elements,
                                     void* h2, uint32_t h2_stride_elements,

@@ -44,6 +44,8 @@ struct tf_context {
     // The same for the flag barriers of the peer exchange (peer.cu), kept apart so that a code from another kernel
     // cannot switch the cross-GPU waits off.
     uint32_t* peer_error = nullptr;
+    // Group and chunk tables of tf_grouped_moe_streamed (built on the device per call).
+    void* streamed_scratch = nullptr;
     // Arrival counter of the grid barriers of the single-launch decode step (zeroed on the stream before each launch).
     uint32_t* grid_barrier = nullptr;
     // tf_stack_forward runs a one-token step as one persistent launch when set (tf_context_set_single_launch_step).
