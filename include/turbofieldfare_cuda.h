@@ -708,6 +708,48 @@ tf_status tf_layer_tail(tf_context* ctx, void* stream,
                         uint32_t rows, uint32_t d, uint32_t stride_elements,
                         float eps, float layer_scalar);
 
+/* ---- expert parallelism behind the C ABI (new: the reference is single-GPU,
+ * Infrastructure/Metal/MetalContext.swift:51-71). One process per GPU; experts sharded num_experts / world per rank
+ * (tf_moe_layer.pool_layer_base is the rank's shard, num_experts the global count); tokens stay with their rank. The
+ * calls below replace, per layer, the MoE section of the reference's forward runner
+ * (Runtime/Inference/RealForwardRunner.swift:902-1186 prefill, :1449-1693 decode) with the collectives inside. NCCL is
+ * bound at run time (libnccl.so.2). ---- */
+#define TF_EP_UNIQUE_ID_BYTES 128
+typedef struct tf_ep tf_ep;
+typedef struct tf_ep_buffers tf_ep_buffers;
+typedef enum tf_ep_mode {
+    TF_EP_EXACT = 0,        /* exact row counts over NCCL send/recv; one host synchronisation per layer (prefill) */
+    TF_EP_FIXED_NCCL = 1,   /* fixed capacity per destination, no host synchronisation, NCCL send/recv */
+    TF_EP_FIXED_PEER = 2    /* fixed capacity, rows pushed over peer memory by a kernel with flag barriers: plain
+                             * kernels only, capturable in a CUDA graph; becomes TF_EP_FIXED_NCCL on every rank together
+                             * when a peer mapping fails */
+} tf_ep_mode;
+/* Rank 0 makes the 128-byte id (ncclGetUniqueId) and hands it to the other ranks over any host channel. */
+tf_status tf_ep_unique_id(void* out_128_bytes);
+/* Collective over the ranks: ncclCommInitRank on ctx's device. world 1 needs no id and no NCCL. */
+tf_status tf_ep_create(tf_context* ctx, const void* unique_id_128_bytes, int rank, int world, tf_ep** out);
+/* The same over a communicator the host already has (an ncclComm_t); it is not destroyed by tf_ep_destroy. */
+tf_status tf_ep_create_from_comm(tf_context* ctx, void* nccl_comm, int rank, int world, tf_ep** out);
+void tf_ep_destroy(tf_ep* ep);
+int tf_ep_rank(const tf_ep* ep);
+int tf_ep_world(const tf_ep* ep);
+/* Exchange buffers and scratch for up to max_tokens LOCAL tokens. Collective: every rank asks for the same buffers in
+ * the same order (the peer mode maps the ranks' buffers into one another). Allocates device memory. */
+tf_status tf_ep_buffers_create(tf_ep* ep, uint32_t max_tokens, uint32_t d, uint32_t f, uint32_t fs, uint32_t top_k,
+                               uint32_t num_experts, tf_ep_mode mode, tf_ep_buffers** out);
+void tf_ep_buffers_destroy(tf_ep_buffers* buffers);                 /* collective in the peer mode */
+tf_ep_mode tf_ep_buffers_mode(const tf_ep_buffers* buffers);       /* the mode in use (after a fallback) */
+tf_workspace* tf_ep_buffers_workspace(const tf_ep_buffers* buffers);   /* router output of the last forward */
+/* y[tokens, d] = shared(x) + sum_r w_r * routed_r(x) with the routed experts on their owner ranks. Collective: every
+ * rank calls it for the same layer (its own tokens; tokens may differ per rank, 0 included only in the fixed modes). In
+ * TF_EP_EXACT the call synchronises the stream once (to read the row counts) and may grow its receive buffers, so it
+ * cannot be captured in a CUDA graph; the fixed modes only enqueue. */
+tf_status tf_moe_block_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* layer, const void* x, void* y, uint32_t tokens,
+                                  tf_ep_buffers* buffers);
+/* hidden [tokens, d] fp16, updated in place: for each layer x = rmsnorm(h) * w_l; h = h + block_l(x). */
+tf_status tf_stack_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* layers, const void* const* norm_weights_bf16,
+                              uint32_t layer_count, float eps, void* hidden, uint32_t tokens, tf_ep_buffers* buffers);
+
 #ifdef __cplusplus
 }
 #endif

@@ -88,6 +88,18 @@ SIGNATURES = {
     "tf_context_destroy": (None, [vp]),
     "tf_last_error": (C.c_char_p, [vp]),
     "tf_context_set_step_trace": (C.c_int, [vp, vp, u32]),
+    "tf_ep_unique_id": (C.c_int, [vp]),
+    "tf_ep_create": (C.c_int, [vp, vp, C.c_int, C.c_int, C.POINTER(vp)]),
+    "tf_ep_create_from_comm": (C.c_int, [vp, vp, C.c_int, C.c_int, C.POINTER(vp)]),
+    "tf_ep_destroy": (None, [vp]),
+    "tf_ep_rank": (C.c_int, [vp]),
+    "tf_ep_world": (C.c_int, [vp]),
+    "tf_ep_buffers_create": (C.c_int, [vp, u32, u32, u32, u32, u32, u32, C.c_int, C.POINTER(vp)]),
+    "tf_ep_buffers_destroy": (None, [vp]),
+    "tf_ep_buffers_mode": (C.c_int, [vp]),
+    "tf_ep_buffers_workspace": (vp, [vp]),
+    "tf_moe_block_forward_ep": (C.c_int, [vp, vp, C.POINTER(MoELayer), vp, vp, u32, vp]),
+    "tf_stack_forward_ep": (C.c_int, [vp, vp, C.POINTER(MoELayer), C.POINTER(vp), u32, f32, vp, u32, vp]),
     "tf_context_set_single_launch_step": (C.c_int, [vp, C.c_int]),
     "tf_launch_count": (u64, [vp]),
     "tf_device_status": (C.c_int, [vp, C.POINTER(u32)]),
