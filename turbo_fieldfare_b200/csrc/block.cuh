@@ -40,6 +40,7 @@ struct tf_stack {
     // device copy of the per-layer pointers for the single-launch one-token step (decode_step.cu)
     void* device_layers = nullptr;
     bool decode_step_ok = false;
+    bool decode_step_bulk_scales = false;
 };
 
 namespace tf {
