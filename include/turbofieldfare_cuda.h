@@ -367,6 +367,16 @@ tf_status tf_shared_expert_int4_block(tf_context* ctx, void* stream,
                                       void* y, uint64_t y_off, uint32_t y_stride_elements,
                                       void* scratch_act, uint32_t rows);
 
+/* The 8-bit shared expert for a block of rows: fused gate/up projection with act = half(gelu(half(gate)) * half(up)),
+ * then the 8-bit down projection. Replaces SharedExpertInt8.encode (Kernels/MoE/SharedExpertInt8.swift:55-210;
+ * shared_int8_gate_up_act_simd, Metal/Quant/dequant_int8.metal:98-154) and its row loop in
+ * PrefillSharedExpert.encodeBlock. scratch_act holds rows * gate.rows fp16. Dimension errors as there
+ * (TF_ERR_DIMENSION_MISMATCH). Packed planes may sit at any byte offset, 16-bit planes at even offsets. */
+tf_status tf_shared_expert_int8_block(tf_context* ctx, void* stream,
+                                      const void* x, uint64_t x_off, uint32_t x_stride_elements,
+                                      const tf_projection* gate, const tf_projection* up, const tf_projection* down,
+                                      void* y, uint64_t y_off, uint32_t y_stride_elements,
+                                      void* scratch_act, uint32_t rows);
 /* The shared expert block for callers that cannot allocate device memory. It has no counterpart in the
  * reference. Who needs it: a serving process that hands all of the GPU's memory to its own pool at start-up and
  * never calls cudaMalloc again (a later cudaMalloc would fail, or stall the device while the driver maps
@@ -540,6 +550,7 @@ typedef struct tf_moe_layer {
     tf_expert_offsets offsets;
     tf_projection shared_gate, shared_up, shared_down;   /* 4-bit affine */
     uint32_t num_experts, d, f, fs, top_k;
+    uint32_t shared_bits;            /* 8: the shared expert is 8-bit affine (SharedExpertInt8); 0 or 4: 4-bit */
 } tf_moe_layer;
 
 /* Uploads the resident payload of model_weights.bin and builds one tf_moe_layer per layer from the checkpoint's

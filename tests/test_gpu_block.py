@@ -301,3 +301,47 @@ def test_one_token_stack_equals_layered_path(tf_ctx, oracle):
         assert o.rel_l2(got, ref) < 2e-3
     finally:
         stack.close()
+
+
+@pytest.mark.parametrize("T", [1, 40])
+def test_block_forward_with_8bit_shared_expert(tf_ctx, oracle, T):
+    """A layer whose shared expert is 8-bit affine (tf_moe_layer.shared_bits = 8; SharedExpertInt8.swift:55-210): the
+    block runs the fused 8-bit gate/up + down beside the routed experts."""
+    import torch
+    from turbo_fieldfare_b200.stack import ExpertPool, MoEBlock, MoEBlockLayer, Workspace
+    o = oracle
+    d, f, fs, E, K = 256, 128, 192, 16, 8
+    pool = ExpertPool(tf_ctx, 1, E, d, f, align=256)
+    pool.fill_synthetic(21)
+    layer = MoEBlockLayer(tf_ctx, pool, 0, d, f, fs, E, K, shared_bits=8)
+    layer.fill_synthetic(22)
+    try:
+        rng = np.random.default_rng(T)
+        x16 = o.f32_to_f16(rng.standard_normal((T, d)).astype(np.float32))
+        ws = Workspace(tf_ctx, T, d, f, fs, K, E)
+        y = torch.zeros(T * d, dtype=torch.int16, device="cuda")
+        MoEBlock(tf_ctx, layer).forward(to_dev(x16), y, T, ws)
+        torch.cuda.synchronize()
+        assert tf_ctx.device_status() == 0
+        router = _affine_from(o, layer.router)
+        sg, su, sd = (_affine_from(o, t) for t in (layer.shared_gate, layer.shared_up, layer.shared_down))
+        assert sg.bits == 8
+        eff = from_dev(layer.effective_scale, np.uint16)
+        gain = from_dev(layer.per_expert_scale, np.uint16)
+        idx_ref, w16, _ = o.router_select(o.router_logits(router, x16, eff), gain, K)
+        idx_gpu, _ = ws.routing(T)
+        assert np.array_equal(idx_gpu, idx_ref)
+        off = _oracle_offsets(o, pool.offsets)
+        got = o.f16_to_f32(from_dev(y, np.uint16).reshape(T, d))
+        for t in sorted({0, T // 2, T - 1}):
+            x = o.f16_to_f32(x16[t])
+            g, u = o.gemv_ref(sg, x), o.gemv_ref(su, x)
+            g, u = o.f16_to_f32(o.f32_to_f16(g)), o.f16_to_f32(o.f32_to_f16(u))
+            inner = np.clip(0.7978845608028654 * (g.astype(np.float64) + 0.044715 * g.astype(np.float64) ** 3), -20, 20)
+            act = o.f32_to_f16((0.5 * g * (1.0 + np.tanh(inner))).astype(np.float32) * u)
+            shared16 = o.f32_to_f16(o.gemv_ref(sd, o.f16_to_f32(act)))
+            blobs = [pool.download(0, int(e)) for e in idx_ref[t]]
+            _, ref, _ = o.moe_routed_decode(blobs, off, x16[t], w16[t], shared16, d, f, order=0)
+            assert o.rel_l2(got[t], ref) < TOL, f"token {t}"
+    finally:
+        pool.close()

@@ -447,6 +447,81 @@ def test_shared_expert_production_shape(tf_ctx, oracle):
     assert o.rel_l2(o.f16_to_f32(y), truth) < FP16_CHAINED
 
 
+def _shared_int8_reference(o, gate, up, down, x16):
+    """SharedExpertInt8Tests.swift:62-75: gate and up by the GEMV reference, act = half(gelu(g) * u), then down.
+    (The kernel also rounds gate and up to fp16 before the activation, dequant_int8.metal:148-152; both forms sit well
+    inside the bound.)"""
+    x = o.f16_to_f32(x16)
+    g, u = o.gemv_ref(gate, x), o.gemv_ref(up, x)
+    inner = 0.7978845608028654 * (g.astype(np.float64) + 0.044715 * g.astype(np.float64) ** 3)
+    act = o.f32_to_f16((0.5 * g.astype(np.float64) * (1.0 + np.tanh(inner))).astype(np.float32) * u)
+    return o.gemv_ref(down, o.f16_to_f32(act))
+
+
+def _shared_int8_run(tf_ctx, o, gate, up, down, x16_rows, w_off=0):
+    import ctypes as C
+    import torch
+    from turbo_fieldfare_b200.kernels import SharedExpertProjection, _ptr
+    T, D = x16_rows.shape
+    Fs = gate.m
+
+    def proj(m):
+        w = np.zeros(w_off + m.packed.size, dtype=np.uint8)
+        w[w_off:] = m.packed.reshape(-1)
+        return SharedExpertProjection(to_dev(w), to_dev(m.scales), to_dev(m.biases), m.m, m.n, weights_offset=w_off)
+
+    pg, pu, pd = proj(gate), proj(up), proj(down)
+    y = dev_zeros_u16(T * D, fill=0x7E00)
+    scratch = dev_zeros_u16(T * Fs)
+    g, u, dn = pg.c_struct(), pu.c_struct(), pd.c_struct()
+    tf_ctx.check(tf_ctx.lib.tf_shared_expert_int8_block(tf_ctx.handle, 0, _ptr(to_dev(x16_rows)), 0, D, C.byref(g), C.byref(u), C.byref(dn),
+                                                        _ptr(y), 0, D, _ptr(scratch), T))
+    torch.cuda.synchronize()
+    return from_dev(y, np.uint16).reshape(T, D)
+
+
+def test_shared_expert_int8_reference_fixture(tf_ctx, oracle):
+    # Tests/TurboFieldfare/Core/Kernels/MoE/SharedExpertInt8Tests.swift:49-118 (D=128, F=64, seed 0x601; rel < 4e-3)
+    o = oracle
+    D, Fs = 128, 64
+    rng = o.SeedTree(0x601).key("shared-expert-int8")
+    x16 = o.f32_to_f16(rng.uniform_array(-0.4, 0.4, D))
+    gate = o.quantize_rows(np.stack([rng.uniform_array(-0.4, 0.4, D) for _ in range(Fs)]), 8)
+    up = o.quantize_rows(np.stack([rng.uniform_array(-0.4, 0.4, D) for _ in range(Fs)]), 8)
+    down = o.quantize_rows(np.stack([rng.uniform_array(-0.4, 0.4, Fs) for _ in range(D)]), 8)
+    y = _shared_int8_run(tf_ctx, o, gate, up, down, x16[None, :])
+    assert o.rel_error(o.f16_to_f32(y[0]), _shared_int8_reference(o, gate, up, down, x16)) < 4e-3
+
+
+@pytest.mark.parametrize("T,w_off", [(1, 0), (5, 0), (70, 3)])
+def test_shared_expert_int8_block_production_shape(tf_ctx, oracle, T, w_off):
+    """The 8-bit shared expert at production width for a block of rows (PrefillSharedExpert loops the rows,
+    Kernels/Prefill/MoE/PrefillSharedExpert.swift:11-59), packed planes at an odd byte offset included."""
+    o = oracle
+    rng = np.random.default_rng(500 + T)
+    D, Fs = 2816, 2112
+    gate, up, down = (config0_matrix(o, Fs, D, rng, bits=8), config0_matrix(o, Fs, D, rng, bits=8), config0_matrix(o, D, Fs, rng, bits=8))
+    x16 = o.f32_to_f16(rng.standard_normal((T, D)).astype(np.float32))
+    y = _shared_int8_run(tf_ctx, o, gate, up, down, x16, w_off)
+    assert np.isfinite(o.f16_to_f32(y)).all()
+    for t in sorted({0, T // 2, T - 1}):
+        assert o.rel_l2(o.f16_to_f32(y[t]), _shared_int8_reference(o, gate, up, down, x16[t])) < FP16_CHAINED
+
+
+def test_shared_expert_int8_errors(tf_ctx):
+    import ctypes as C
+    import torch
+    from turbo_fieldfare_b200.kernels import SharedExpertProjection, _ptr
+    b = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    p = lambda r, c: SharedExpertProjection(b, b, b, r, c).c_struct()
+    g, u, d_bad, d_ok = p(64, 128), p(64, 128), p(128, 128), p(128, 64)
+    call = lambda dn: tf_ctx.lib.tf_shared_expert_int8_block(tf_ctx.handle, 0, _ptr(b), 0, 128, C.byref(g), C.byref(u), C.byref(dn),
+                                                             _ptr(b), 0, 128, _ptr(b), 1)
+    assert call(d_bad) == 7                      # SharedExpertInt8Error.dimensionMismatch (SharedExpertInt8.swift:84-88)
+    assert call(d_ok) == 0
+    torch.cuda.synchronize()
+
+
 def test_shared_expert_errors(tf_ctx, oracle):
     import torch
     from turbo_fieldfare_b200.kernels import SharedExpertInt4, SharedExpertProjection, TFError

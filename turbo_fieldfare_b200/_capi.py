@@ -48,7 +48,7 @@ class MoELayer(C.Structure):
     _fields_ = [("router", Projection), ("effective_scale", vp), ("per_expert_scale", vp), ("logit_bias", vp),
                 ("pool_layer_base", vp), ("expert_stride", u64), ("offsets", ExpertOffsets),
                 ("shared_gate", Projection), ("shared_up", Projection), ("shared_down", Projection),
-                ("num_experts", u32), ("d", u32), ("f", u32), ("fs", u32), ("top_k", u32)]
+                ("num_experts", u32), ("d", u32), ("f", u32), ("fs", u32), ("top_k", u32), ("shared_bits", u32)]
 
 
 class GTurboInfo(C.Structure):
@@ -124,6 +124,8 @@ SIGNATURES = {
                                          vp, vp, C.c_int, u32, u32, u32, u32]),
     "tf_grouped_moe_streamed": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, vp, u64, C.POINTER(vp), u32, vp, u32, C.POINTER(u32)]),
     "tf_moe_reduce_token_major": (C.c_int, [vp, vp, vp, C.c_int, vp, vp, u32, vp, u32, u32, u32, u32]),
+    "tf_shared_expert_int8_block": (C.c_int, [vp, vp, vp, u64, u32, C.POINTER(Projection), C.POINTER(Projection),
+                                              C.POINTER(Projection), vp, u64, u32, vp, u32]),
     "tf_shared_expert_int4_block": (C.c_int, [vp, vp, vp, u64, u32, C.POINTER(Projection), C.POINTER(Projection),
                                               C.POINTER(Projection), vp, u64, u32, vp, u32]),
     "tf_context_set_tensorcore_min_tokens": (C.c_int, [vp, u32]),

@@ -344,7 +344,10 @@ tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer
     TF_CUDA(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->fork_event, 0));
     const bool tensor_path = tokens >= ctx->tensorcore_min_tokens && ws->x_sorted != nullptr;
     tf_status s;
-    if (tensor_path)
+    if (layer->shared_bits == 8)
+        s = tf_shared_expert_int8_block(ctx, ctx->side_stream, x, 0, x_stride_elements, &layer->shared_gate, &layer->shared_up,
+                                        &layer->shared_down, ws->shared_y, 0, d, ws->shared_act, tokens);
+    else if (tensor_path)
         s = tf_shared_expert_int4_tensorcore(ctx, ctx->side_stream, x, x_stride_elements, &layer->shared_gate, &layer->shared_up,
                                              &layer->shared_down, ws->shared_y, d, ws->shared_act, tokens);
     else
@@ -459,8 +462,11 @@ tf_status tf_ep_finish(tf_context* ctx, void* stream, const tf_moe_layer* layer,
     TF_REQUIRE(ctx, layer && x && ws && returned_rows && inverse_perm && y, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
     if (tokens == 0) return TF_OK;
     const uint32_t d = layer->d;
-    tf_status s = tf_shared_expert_int4_block(ctx, stream, x, 0, d, &layer->shared_gate, &layer->shared_up, &layer->shared_down,
-                                              ws->shared_y, 0, d, ws->shared_act, tokens);
+    tf_status s = layer->shared_bits == 8
+                      ? tf_shared_expert_int8_block(ctx, stream, x, 0, d, &layer->shared_gate, &layer->shared_up, &layer->shared_down,
+                                                    ws->shared_y, 0, d, ws->shared_act, tokens)
+                      : tf_shared_expert_int4_block(ctx, stream, x, 0, d, &layer->shared_gate, &layer->shared_up, &layer->shared_down,
+                                                    ws->shared_y, 0, d, ws->shared_act, tokens);
     if (s) return s;
     return tf_ep_combine(ctx, stream, returned_rows, ws->weights, inverse_perm, ws->shared_y, d, y, d, tokens, layer->top_k, d);
 }

@@ -1087,7 +1087,7 @@ tf_status decode_step_prepare(tf_context* ctx, tf_stack* st) {
         o.su_w = w(m.shared_up); o.su_s = s(m.shared_up); o.su_b = b(m.shared_up);
         o.sd_w = w(m.shared_down); o.sd_s = s(m.shared_down); o.sd_b = b(m.shared_down);
         o.norm_w = static_cast<const uint16_t*>(st->norm_weights[l]);
-        ok = ok && m.router.rows == m.num_experts && m.router.cols == m.d;
+        ok = ok && m.router.rows == m.num_experts && m.router.cols == m.d && m.shared_bits != 8;
         ok = ok && m.shared_gate.rows == m.fs && m.shared_gate.cols == m.d && m.shared_up.rows == m.fs && m.shared_up.cols == m.d &&
              m.shared_down.rows == m.d && m.shared_down.cols == m.fs;
         ok = ok && aligned(o.pool, 16) && o.stride % 16 == 0 && o.off.gate_w_off % 16 == 0 && o.off.up_w_off % 16 == 0 && o.off.down_w_off % 16 == 0;

@@ -418,7 +418,10 @@ tf_status tf_moe_block_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* l
     TF_CUDA(ctx, cudaStreamWaitEvent(ctx->side_stream, ctx->fork_event, 0));
     tf_status s;
     const bool shared_tensor = tokens >= ctx->tensorcore_min_tokens && d % 64 == 0 && b->fs % 64 == 0;
-    if (shared_tensor)
+    if (layer->shared_bits == 8)
+        s = tf_shared_expert_int8_block(ctx, ctx->side_stream, x, 0, d, &layer->shared_gate, &layer->shared_up, &layer->shared_down,
+                                        ws->shared_y, 0, d, ws->shared_act, tokens);
+    else if (shared_tensor)
         s = tf_shared_expert_int4_tensorcore(ctx, ctx->side_stream, x, d, &layer->shared_gate, &layer->shared_up, &layer->shared_down,
                                              ws->shared_y, d, ws->shared_act, tokens);
     else

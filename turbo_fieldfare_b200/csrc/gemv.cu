@@ -52,6 +52,50 @@ affine_gemv_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S
     }
 }
 
+// Fused gate/up projection of the 8-bit shared expert: one warp per intermediate row computes both dot products over
+// the activations staged once per block and stores act = half(gelu(half(gate)) * half(up))
+// (shared_int8_gate_up_act_simd, Metal/Quant/dequant_int8.metal:98-154). grid.y walks token rows.
+__global__ void __launch_bounds__(kGemvThreads)
+shared_int8_gate_up_act_kernel(const uint8_t* __restrict__ Wg, const uint16_t* __restrict__ Sg, const uint16_t* __restrict__ Bg,
+                               const uint8_t* __restrict__ Wu, const uint16_t* __restrict__ Su, const uint16_t* __restrict__ Bu,
+                               const uint16_t* __restrict__ x, uint32_t x_stride, uint16_t* __restrict__ act, uint32_t act_stride,
+                               uint32_t m, uint32_t n, bool a4) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint16_t* xs = reinterpret_cast<uint16_t*>(smem);
+    float* xsum16 = xsum_ptr(xs, (int)n);
+    stage_x<false>(x + (size_t)blockIdx.y * x_stride, xs, xsum16, (int)n);
+    const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const uint32_t groups = n / kGroup;
+    for (uint32_t row = blockIdx.x * kGemvWarps + warp; row < m; row += gridDim.x * kGemvWarps) {
+        float g = int8_row_partial<false, false>(Wg + (size_t)row * n, Sg + (size_t)row * groups, Bg + (size_t)row * groups, xs, (int)n, lane, a4);
+        float u = int8_row_partial<false, false>(Wu + (size_t)row * n, Su + (size_t)row * groups, Bu + (size_t)row * groups, xs, (int)n, lane, a4);
+        g = warp_sum(g);
+        u = warp_sum(u);
+        if (lane == 0) {
+            const float gh = __half2float(__float2half_rn(g)), uh = __half2float(__float2half_rn(u));
+            act[(size_t)blockIdx.y * act_stride + row] = __half_as_ushort(__float2half_rn(gelu_tanh(gh) * uh));
+        }
+    }
+}
+
+// y[row t] = deq8(W) . x[row t] for a block of token rows (grid.y), the down projection of the 8-bit shared expert.
+__global__ void __launch_bounds__(kGemvThreads)
+int8_gemv_rows_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, const uint16_t* __restrict__ B,
+                      const uint16_t* __restrict__ x, uint32_t x_stride, uint16_t* __restrict__ y, uint32_t y_stride,
+                      uint32_t m, uint32_t n, bool a4) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint16_t* xs = reinterpret_cast<uint16_t*>(smem);
+    float* xsum16 = xsum_ptr(xs, (int)n);
+    stage_x<false>(x + (size_t)blockIdx.y * x_stride, xs, xsum16, (int)n);
+    const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const uint32_t groups = n / kGroup;
+    for (uint32_t row = blockIdx.x * kGemvWarps + warp; row < m; row += gridDim.x * kGemvWarps) {
+        float acc = int8_row_partial<false, false>(W + (size_t)row * n, S + (size_t)row * groups, B + (size_t)row * groups, xs, (int)n, lane, a4);
+        acc = warp_sum(acc);
+        if (lane == 0) y[(size_t)blockIdx.y * y_stride + row] = __half_as_ushort(__float2half_rn(acc));
+    }
+}
+
 template <int BITS, bool OUT_F32 = false>
 static tf_status launch_gemv(tf_context* ctx, void* stream, const void* weights, uint64_t weights_off,
                              const void* scales, uint64_t scales_off, const void* biases, uint64_t biases_off,
@@ -243,6 +287,51 @@ tf_status tf_int8_gemv(tf_context* ctx, void* stream, const void* weights, uint6
                        uint32_t m, uint32_t n, tf_dtype sb_dtype) {
     return tf::launch_gemv<8>(ctx, stream, weights, weights_off, scales, scales_off, biases, biases_off,
                               x, x_off, y, y_off, m, n, sb_dtype, "tf_int8_gemv");
+}
+
+tf_status tf_shared_expert_int8_block(tf_context* ctx, void* stream, const void* x, uint64_t x_off, uint32_t x_stride_elements,
+                                      const tf_projection* gate, const tf_projection* up, const tf_projection* down,
+                                      void* y, uint64_t y_off, uint32_t y_stride_elements, void* scratch_act, uint32_t rows) {
+    const char* name = "tf_shared_expert_int8_block";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, x && gate && up && down && y && scratch_act, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    // SharedExpertInt8.swift:80-88
+    TF_REQUIRE(ctx, gate->rows == up->rows && gate->cols == up->cols, TF_ERR_DIMENSION_MISMATCH,
+               "gate/up shapes differ: gate=(%u,%u) up=(%u,%u)", gate->rows, gate->cols, up->rows, up->cols);
+    TF_REQUIRE(ctx, down->rows == gate->cols && down->cols == gate->rows, TF_ERR_DIMENSION_MISMATCH,
+               "down expected (%u,%u), got (%u,%u)", gate->cols, gate->rows, down->rows, down->cols);
+    const uint32_t fs = gate->rows, d = gate->cols;
+    TF_REQUIRE(ctx, d % tf::kGroup == 0 && fs % tf::kGroup == 0 && d > 0 && fs > 0, TF_ERR_INVALID_ARGUMENT, "%s: dimensions must be multiples of 64", name);
+    TF_REQUIRE(ctx, x_stride_elements >= d && y_stride_elements >= d, TF_ERR_INVALID_ARGUMENT, "%s: stride is too small", name);
+    if (rows == 0) return TF_OK;
+    TF_REQUIRE(ctx, rows <= 65535u, TF_ERR_UNSUPPORTED, "%s: at most 65535 rows per call", name);
+    const tf_projection* ps[3] = {gate, up, down};
+    const uint8_t* W[3]; const uint16_t* S[3]; const uint16_t* B[3];
+    bool a4 = true;
+    for (int i = 0; i < 3; ++i) {
+        W[i] = tf::byte_ptr(ps[i]->weights, ps[i]->weights_off);
+        S[i] = reinterpret_cast<const uint16_t*>(tf::byte_ptr(ps[i]->scales, ps[i]->scales_off));
+        B[i] = reinterpret_cast<const uint16_t*>(tf::byte_ptr(ps[i]->biases, ps[i]->biases_off));
+        TF_REQUIRE(ctx, tf::aligned(S[i], 2) && tf::aligned(B[i], 2), TF_ERR_ALIGNMENT, "%s: scale and bias planes must be 2-byte aligned", name);
+        a4 = a4 && tf::aligned(W[i], 4);
+    }
+    const uint16_t* xp = reinterpret_cast<const uint16_t*>(tf::byte_ptr(x, x_off));
+    uint16_t* yp = reinterpret_cast<uint16_t*>(tf::byte_ptr(y, y_off));
+    TF_REQUIRE(ctx, tf::aligned(xp, 2) && tf::aligned(yp, 2) && tf::aligned(scratch_act, 2), TF_ERR_ALIGNMENT, "%s: x, y and the scratch must be 2-byte aligned", name);
+    const size_t smem1 = tf::stage_x_bytes((int)d), smem2 = tf::stage_x_bytes((int)fs);
+    TF_REQUIRE(ctx, smem1 <= 96 * 1024 && smem2 <= 96 * 1024, TF_ERR_UNSUPPORTED, "%s: dimensions too large for the staged-x kernels", name);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    static tf::DeviceSmemCache c1, c2;
+    if (smem1 > 48 * 1024) if (tf_status s = tf::ensure_dynamic_smem(ctx, tf::shared_int8_gate_up_act_kernel, c1, smem1)) return s;
+    if (smem2 > 48 * 1024) if (tf_status s = tf::ensure_dynamic_smem(ctx, tf::int8_gemv_rows_kernel, c2, smem2)) return s;
+    const uint32_t per_row_blocks = rows >= 64 ? 8u : (uint32_t)ctx->sm_count * 2u;       // a block keeps its token's activations staged
+    auto blocks = [&](uint32_t m) { const uint32_t need = (m + tf::kGemvWarps - 1) / tf::kGemvWarps; return need < per_row_blocks ? need : per_row_blocks; };
+    uint16_t* act = static_cast<uint16_t*>(scratch_act);
+    tf::shared_int8_gate_up_act_kernel<<<dim3(blocks(fs), rows), tf::kGemvThreads, smem1, st>>>(W[0], S[0], B[0], W[1], S[1], B[1], xp,
+                                                                                              x_stride_elements, act, fs, fs, d, a4);
+    if (tf_status s = tf::check_launch(ctx, "tf_shared_expert_int8_block(gate/up)")) return s;
+    tf::int8_gemv_rows_kernel<<<dim3(blocks(d), rows), tf::kGemvThreads, smem2, st>>>(W[2], S[2], B[2], act, fs, yp, y_stride_elements, d, fs, a4);
+    return tf::check_launch(ctx, "tf_shared_expert_int8_block(down)");
 }
 
 }  // extern "C"

@@ -998,8 +998,9 @@ tf_status tf_gturbo_model_load(tf_context* ctx, void* stream, const tf_gturbo* g
         if (!ctx || !g || !pool || !out) raise(TF_ERR_INVALID_ARGUMENT, "NULL argument");
         if (g->directory.empty()) raise(TF_ERR_INVALID_ARGUMENT, "the handle was parsed from memory and has no directory");
         const Manifest& m = g->manifest;
-        if (m.has_quant && m.q_shared.weight_bits != 4)
-            raise(TF_ERR_UNSUPPORTED, "shared expert at %d bits: the block kernels take the 4-bit shared expert", m.q_shared.weight_bits);
+        const int shared_bits = m.has_quant ? m.q_shared.weight_bits : 4;
+        if (shared_bits != 4 && shared_bits != 8)
+            raise(TF_ERR_UNSUPPORTED, "shared expert at %d bits: the block kernels take a 4-bit or an 8-bit shared expert", shared_bits);
         uint32_t pool_layers = 0, pool_experts = 0;
         uint64_t pool_stride = 0;
         tf_expert_pool_dims(pool, &pool_layers, &pool_experts, &pool_stride);
@@ -1059,10 +1060,11 @@ tf_status tf_gturbo_model_load(tf_context* ctx, void* stream, const tf_gturbo* g
             layer.pool_layer_base = tf_expert_pool_ptr(pool, (uint32_t)L, 0);
             layer.expert_stride = m.expert_stride;
             layer.offsets = expert_offsets_of(*g, (uint32_t)L);
-            layer.shared_gate = projection_of(*g, model->resident, prefix + ".mlp.gate_proj.weight", Fs, D, 4);
-            layer.shared_up = projection_of(*g, model->resident, prefix + ".mlp.up_proj.weight", Fs, D, 4);
-            layer.shared_down = projection_of(*g, model->resident, prefix + ".mlp.down_proj.weight", D, Fs, 4);
+            layer.shared_gate = projection_of(*g, model->resident, prefix + ".mlp.gate_proj.weight", Fs, D, shared_bits);
+            layer.shared_up = projection_of(*g, model->resident, prefix + ".mlp.up_proj.weight", Fs, D, shared_bits);
+            layer.shared_down = projection_of(*g, model->resident, prefix + ".mlp.down_proj.weight", D, Fs, shared_bits);
             layer.num_experts = E; layer.d = D; layer.f = F; layer.fs = Fs; layer.top_k = (uint32_t)m.top_k;
+            layer.shared_bits = (uint32_t)shared_bits;
             model->layers.push_back(layer);
         }
         guard.keep = true;

@@ -146,13 +146,13 @@ class MoEBlockLayer:
     """Weights of one MoE block: router, gains, shared expert and a slice of the expert pool."""
 
     def __init__(self, context: TurboContext, pool: ExpertPool, layer_index: int, d: int, f: int, fs: int,
-                 num_experts: int, top_k: int):
+                 num_experts: int, top_k: int, shared_bits: int = 4):
         self.context, self.pool, self.layer_index = context, pool, layer_index
-        self.d, self.f, self.fs, self.num_experts, self.top_k = d, f, fs, num_experts, top_k
+        self.d, self.f, self.fs, self.num_experts, self.top_k, self.shared_bits = d, f, fs, num_experts, top_k, shared_bits
         self.router = AffineTensor(num_experts, d, 8)
-        self.shared_gate = AffineTensor(fs, d, 4)
-        self.shared_up = AffineTensor(fs, d, 4)
-        self.shared_down = AffineTensor(d, fs, 4)
+        self.shared_gate = AffineTensor(fs, d, shared_bits)
+        self.shared_up = AffineTensor(fs, d, shared_bits)
+        self.shared_down = AffineTensor(d, fs, shared_bits)
         eff = np.full(d, 1.0 / math.sqrt(d), dtype=np.float32)
         self.effective_scale = torch.from_numpy(_bf16_bits(eff).view(np.int16)).cuda()
         self.per_expert_scale = torch.from_numpy(_bf16_bits(np.ones(num_experts, np.float32)).view(np.int16)).cuda()
@@ -172,7 +172,7 @@ class MoEBlockLayer:
         return MoELayer(self.router.projection(), _ptr(self.effective_scale), _ptr(self.per_expert_scale),
                         _ptr(self.logit_bias), self.pool.ptr(self.layer_index, 0), self.pool.stride, self.pool.offsets,
                         self.shared_gate.projection(), self.shared_up.projection(), self.shared_down.projection(),
-                        self.num_experts, self.d, self.f, self.fs, self.top_k)
+                        self.num_experts, self.d, self.f, self.fs, self.top_k, self.shared_bits)
 
 
 class Workspace:
