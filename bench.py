@@ -730,7 +730,7 @@ def main():
     ap.add_argument("--zipf-exponent", type=float, default=0.0, help="--case block: router logit bias log(p), p ~ 1/rank^s (0 = none)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of layer-0 outputs after the timed regions")
-    ap.add_argument("--single-launch-step", type=int, default=1,
+    ap.add_argument("--single-launch-step", type=int, default=0,
                     help="one-token steps as one persistent launch (1) or layer by layer (0); single GPU only")
     ap.add_argument("--cpu-sample-tokens", type=int, default=256)
     args = ap.parse_args()

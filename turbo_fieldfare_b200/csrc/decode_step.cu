@@ -727,42 +727,6 @@ __device__ __noinline__ void ds_phase1(const DsCtx* c, const DecodeLayer* L, uin
     }
 }
 
-// The router's top-k + softmax of warp_select_topk (router.cuh) with the exponentials of the selected scores taken by
-// eight lanes at once; the sum and every other operation keep that routine's order, so the bits are the same.
-__device__ __forceinline__ void ds_select_topk(float* scores, uint32_t num_experts, uint32_t top_k, const uint16_t* __restrict__ pes,
-                                               uint32_t* out_idx, uint16_t* out_w, int lane) {
-    float my_score = 0.0f;
-    uint32_t my_idx = 0;
-    float max_s = 0.0f;
-    for (uint32_t r = 0; r < top_k; ++r) {
-        float best = -INFINITY;
-        uint32_t best_e = 0xFFFFFFFFu;
-        for (uint32_t e = lane; e < num_experts; e += kWarp) {
-            const float s = scores[e];
-            if (s > best || (s == best && e < best_e)) { best = s; best_e = e; }
-        }
-#pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) {
-            const float os = __shfl_xor_sync(kFullMask, best, off);
-            const uint32_t oe = __shfl_xor_sync(kFullMask, best_e, off);
-            if (os > best || (os == best && oe < best_e)) { best = os; best_e = oe; }
-        }
-        if (best_e == 0xFFFFFFFFu) best_e = 0;   // fewer finite candidates than top_k
-        if (r == 0) max_s = best;
-        if ((uint32_t)lane == r) { my_score = best; my_idx = best_e; }
-        if (lane == 0 && best_e < num_experts) scores[best_e] = -INFINITY;
-        __syncwarp();
-    }
-    const float ex = (uint32_t)lane < top_k ? expf(my_score - max_s) : 0.0f;
-    float sum_exp = 0.0f;
-    for (uint32_t r = 0; r < top_k; ++r) sum_exp += __shfl_sync(kFullMask, ex, (int)r);      // rank order, as the serial loop
-    if ((uint32_t)lane < top_k) {
-        const float w = ex / sum_exp * bf16_bits_to_float(pes[my_idx]);
-        out_idx[lane] = my_idx;
-        out_w[lane] = __half_as_ushort(__float2half_rn(w));
-    }
-}
-
 // P2: top-k of the logits (every CTA, identically), then this CTA's slice of the routed experts' gate/up rows.
 __device__ __noinline__ void ds_phase2(const DsCtx* c, const DecodeLayer* L, const DecodeLayer* N, uint32_t q0, uint32_t layer) {
     const uint32_t d = c->d, f = c->f, E = c->E, K = c->K, ngd = c->ngd, ngf = c->ngf, ngs = c->ngs, kp_d = c->kp_d;
@@ -772,7 +736,7 @@ __device__ __noinline__ void ds_phase2(const DsCtx* c, const DecodeLayer* L, con
     cta_sync();
     mk.mark(0);
     if (warp == 0) {
-        ds_select_topk(c->scores, E, K, L->pes, c->sel_idx, c->sel_w, lane);
+        warp_select_topk(c->scores, E, K, L->pes, c->sel_idx, c->sel_w, lane);
         __syncwarp();
         if ((uint32_t)lane < K) {
             uint32_t e = c->sel_idx[lane];
@@ -797,22 +761,17 @@ __device__ __noinline__ void ds_phase2(const DsCtx* c, const DecodeLayer* L, con
             return ScaleSrc{blob + off.gate_s_off, blob + off.gate_b_off, blob + off.up_s_off, blob + off.up_b_off};
         });
     }
-    // Scale and bias rows of P3 (they depend only on the routing): staged now, while the routed rows stream in.
-    // Layout: plane p at p * sc3_plane, source s (K routed experts, then the shared one) at s * rows3_cap * ngf_pad, then
-    // [row][groups padded to a multiple of four].
-    {
+    // Scale and bias rows of P3 depend only on the routing: one warp asks for them in L2 now, P3 copies them from there.
+    if (warp == kDsComputeWarps - 2) {
         const uint32_t lo3 = c->p3_lo, n3 = c->p3_hi - c->p3_lo;
-        const uint32_t jobs = n3 ? (K + 1) * 2 : 0;
-        for (uint32_t j = warp; j < jobs; j += kDsComputeWarps) {
-            const uint32_t src = j / 2, pl = j % 2;
-            if (src < K) {
+        if (n3) {
+            for (uint32_t src = 0; src < K; ++src) {
                 const uint8_t* blob = pool + (uint64_t)sel[src] * stride;
-                const uint16_t* plane = reinterpret_cast<const uint16_t*>(blob + (pl ? off.down_b_off : off.down_s_off));
-                warp_copy_rows_u16(plane + (size_t)lo3 * ngf, c->sc3 + pl * c->sc3_plane + src * c->rows3_cap * c->ngf_pad, n3, ngf, c->ngf_pad, lane);
-            } else {
-                const uint16_t* plane = pl ? L->sd_b : L->sd_s;
-                warp_copy_rows_u16(plane + (size_t)lo3 * ngs, c->sc3 + pl * c->sc3_plane + K * c->rows3_cap * c->ngf_pad, n3, ngs, c->ngs_pad, lane);
+                prefetch_l2_warp(blob + off.down_s_off + (size_t)lo3 * ngf * 2, n3 * ngf * 2, lane);
+                prefetch_l2_warp(blob + off.down_b_off + (size_t)lo3 * ngf * 2, n3 * ngf * 2, lane);
             }
+            prefetch_l2_warp(L->sd_s + (size_t)lo3 * ngs, n3 * ngs * 2, lane);
+            prefetch_l2_warp(L->sd_b + (size_t)lo3 * ngs, n3 * ngs * 2, lane);
         }
     }
     // the last warp brings the next layer's small operands into L2 ahead of use
@@ -850,6 +809,49 @@ __device__ __noinline__ void ds_phase2(const DsCtx* c, const DecodeLayer* L, con
     mk.mark(6);
 }
 
+// Scale and bias rows of P3 from global memory (L2 after the prefetch of P2) into shared memory, all threads at once and
+// every thread's loads issued before its first store. Layout: plane p at p * sc3_plane, source s (K routed experts, then
+// the shared one) at s * rows3_cap * ngf_pad, then [row][groups padded to a multiple of four]. A job is up to
+// kDsScaleChunk consecutive groups of one row of one source and plane.
+constexpr uint32_t kDsScaleChunk = 12;
+__device__ __forceinline__ void ds_stage_down_scales(const DsCtx* c, const DecodeLayer* L) {
+    const uint32_t K = c->K, ngf = c->ngf, ngs = c->ngs;
+    const uint32_t lo3 = c->p3_lo, n3 = c->p3_hi - c->p3_lo;
+    const uint32_t cf = (ngf + kDsScaleChunk - 1) / kDsScaleChunk, cs = (ngs + kDsScaleChunk - 1) / kDsScaleChunk;
+    const uint32_t per_row = K * cf + cs;                    // chunks of one (row, plane)
+    const uint32_t jobs = n3 * 2 * per_row;
+    const uint32_t rcp_row = 0xFFFFFFFFu / per_row + 1u;          // per_row >= 2
+    const uint32_t rcp_cf = cf > 1 ? 0xFFFFFFFFu / cf + 1u : 0u;
+    const uint8_t* pool = L->pool;
+    const uint64_t stride = L->stride;
+    for (uint32_t j = threadIdx.x; j < jobs; j += kDsComputeThreads) {
+        const uint32_t rp = __umulhi(j, rcp_row), slot = j - rp * per_row;       // rp = row * 2 + plane
+        const uint32_t r = rp >> 1, pl = rp & 1;
+        const uint16_t* src;
+        uint16_t* dst;
+        uint32_t n;
+        if (slot < K * cf) {
+            const uint32_t k = cf > 1 ? __umulhi(slot, rcp_cf) : slot, ch = slot - k * cf;
+            const uint8_t* blob = pool + (uint64_t)c->sel_idx[k] * stride;
+            const uint32_t g0 = ch * kDsScaleChunk;
+            src = reinterpret_cast<const uint16_t*>(blob + (pl ? L->off.down_b_off : L->off.down_s_off)) + (size_t)(lo3 + r) * ngf + g0;
+            dst = c->sc3 + pl * c->sc3_plane + k * c->rows3_cap * c->ngf_pad + r * c->ngf_pad + g0;
+            n = ngf - g0 < kDsScaleChunk ? ngf - g0 : kDsScaleChunk;
+        } else {
+            const uint32_t g0 = (slot - K * cf) * kDsScaleChunk;
+            src = (pl ? L->sd_b : L->sd_s) + (size_t)(lo3 + r) * ngs + g0;
+            dst = c->sc3 + pl * c->sc3_plane + K * c->rows3_cap * c->ngf_pad + r * c->ngs_pad + g0;
+            n = ngs - g0 < kDsScaleChunk ? ngs - g0 : kDsScaleChunk;
+        }
+        uint16_t v[kDsScaleChunk];
+#pragma unroll
+        for (uint32_t i = 0; i < kDsScaleChunk; ++i) v[i] = i < n ? __ldg(src + i) : (uint16_t)0;
+#pragma unroll
+        for (uint32_t i = 0; i < kDsScaleChunk; ++i)
+            if (i < n) dst[i] = v[i];
+    }
+}
+
 // P3: down projections of the K routed experts and of the shared expert for this CTA's output rows, combine in rank
 // order, residual add.
 __device__ __noinline__ void ds_phase3(const DsCtx* c, const DecodeLayer* L, uint32_t q0) {
@@ -863,9 +865,14 @@ __device__ __noinline__ void ds_phase3(const DsCtx* c, const DecodeLayer* L, uin
         const uint16_t* src = e8 < K * f ? c->acts + e8 : c->shared_act + (e8 - K * f);
         reinterpret_cast<uint4*>(c->a16)[i] = __ldcg(reinterpret_cast<const uint4*>(src));
     }
+    ds_stage_down_scales(c, L);
     cta_sync();
     mk.mark(8);
     stage_frags(c->a16, K * ngf + ngs, c->frag_b, c->sum_b);      // K routed vectors of ngf groups, then the shared one
+    // the residual row of this CTA's finalize lanes (half-warp per output row, below): read ahead of the item loop
+    const uint32_t fin_row = threadIdx.x / 16, fin_lane = threadIdx.x % 16;
+    float h_in = 0.0f;
+    if (fin_lane == 0 && fin_row < rows) h_in = f16_bits_to_float(__ldcg(c->hidden + lo + fin_row));
     cta_sync();
     mk.mark(9);
     const uint32_t n_items = c->p3_tiles * per_tile;
@@ -873,21 +880,30 @@ __device__ __noinline__ void ds_phase3(const DsCtx* c, const DecodeLayer* L, uin
     mk.mark(10);
     cta_sync();
     mk.mark(11);
+    // Finalize: a half-warp per output row. Lane s < K sums the K-parts of routed expert s, lane K those of the shared
+    // expert (each in ascending part order, as a single thread would); lane 0 then folds them in rank order.
     const float* partial = c->partial;
-    for (uint32_t j = threadIdx.x; j < rows; j += kDsComputeThreads) {
-        const uint32_t tile = j / 16, r = j % 16;
-        const float* pt = partial + (size_t)tile * per_tile * 16 + r;
-        float sh = 0.0f;
-        for (uint32_t kp = 0; kp < kp_s; ++kp) sh += pt[(K * kp_f + kp) * 16];
-        float acc = __half2float(__float2half_rn(sh));                 // shared y is stored as fp16
-        for (uint32_t k = 0; k < K; ++k) {
-            float pk = 0.0f;
-            for (uint32_t kp = 0; kp < kp_f; ++kp) pk += pt[(k * kp_f + kp) * 16];
-            acc = __fadd_rn(acc, __fmul_rn(f16_bits_to_float(c->sel_w[k]), pk));      // rank order 0..K-1
+    for (uint32_t j0 = 0; j0 < rows; j0 += kDsComputeThreads / 16) {
+        const uint32_t j = j0 + fin_row;
+        const bool live = j < rows;
+        float pk = 0.0f;
+        if (live && fin_lane <= K) {
+            const uint32_t tile = j / 16, r = j % 16;
+            const float* pt = partial + (size_t)tile * per_tile * 16 + r;
+            if (fin_lane < K) { for (uint32_t kp = 0; kp < kp_f; ++kp) pk += pt[(fin_lane * kp_f + kp) * 16]; }
+            else              { for (uint32_t kp = 0; kp < kp_s; ++kp) pk += pt[(K * kp_f + kp) * 16]; }
         }
-        const float y = __half2float(__float2half_rn(acc));
-        const float h = f16_bits_to_float(__ldcg(c->hidden + lo + j));
-        c->hidden[lo + j] = __half_as_ushort(__float2half_rn(h + y));
+        const int base = (lane / 16) * 16;
+        float acc = __half2float(__float2half_rn(__shfl_sync(kFullMask, pk, base + (int)K)));        // shared y is stored as fp16
+        for (uint32_t k = 0; k < K; ++k) {
+            const float p = __shfl_sync(kFullMask, pk, base + (int)k);
+            acc = __fadd_rn(acc, __fmul_rn(f16_bits_to_float(c->sel_w[k]), p));                          // rank order 0..K-1
+        }
+        if (live && fin_lane == 0) {
+            const float y = __half2float(__float2half_rn(acc));
+            const float h = j0 == 0 ? h_in : f16_bits_to_float(__ldcg(c->hidden + lo + j));
+            c->hidden[lo + j] = __half_as_ushort(__float2half_rn(h + y));
+        }
     }
     mk.mark(12);
 }

@@ -137,6 +137,10 @@ group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __rest
 
 constexpr int kGPW = 4;                 // 64-column groups per compute warp
 constexpr int kWStages = 3;             // ring depth (items) of the tile ring (codes + scales)
+// Narrow single-matrix tiles (the routed down projection: 16 rows x 352 bytes) are a few KB each, so three of them in
+// flight per CTA leave the memory system idle; their ring is deeper.
+template <int NMAT, int KC>
+__host__ __device__ constexpr uint32_t ring_stages() { return (NMAT == 1 && KC > 0 && KC <= 1024) ? 8u : (uint32_t)kWStages; }
 constexpr int kReducers = 2;            // reducer warps; reducer q owns the items and the partial buffer of parity q
 constexpr int kRedStages = kReducers;   // partial-sum buffers
 constexpr int kTileRows = 16;           // weight rows per MMA tile (the m of m16n8k16)
@@ -237,16 +241,16 @@ __host__ __device__ inline uint32_t ring_row_stride(uint32_t row_bytes) {
 // Shared-memory layout of a CTA with `cw` compute warps.
 template <int NMAT>
 struct KSplitSmem {
-    uint32_t cw, ng, row_bytes;
+    uint32_t cw, ng, row_bytes, stages;
     __host__ __device__ uint32_t row_stride() const { return ring_row_stride(row_bytes); }
     __host__ __device__ uint32_t mat_bytes() const { return kTileRows * row_stride(); }
     __host__ __device__ uint32_t sb_plane_bytes() const { return kTileRows * ng * 2; }                            // multiple of 16
     __host__ __device__ uint32_t stage_bytes() const { return NMAT * mat_bytes() + NMAT * 2 * sb_plane_bytes(); } // codes, then scales
     __host__ __device__ uint32_t off_sb_in_stage() const { return NMAT * mat_bytes(); }
-    __host__ __device__ uint32_t ring_bytes() const { return kWStages * stage_bytes(); }
+    __host__ __device__ uint32_t ring_bytes() const { return stages * stage_bytes(); }
     __host__ __device__ uint32_t red_stage_bytes() const { return cw * NMAT * 128 * 4; }
     __host__ __device__ uint32_t red_bytes() const { return kRedStages * red_stage_bytes(); }
-    __host__ __device__ uint32_t bar_count() const { return 2 * kWStages + 2 * kRedStages; }
+    __host__ __device__ uint32_t bar_count() const { return 2 * stages + 2 * kRedStages; }
     __host__ __device__ uint32_t off_red() const { return ring_bytes(); }
     __host__ __device__ uint32_t off_bar() const { return off_red() + red_bytes(); }
     __host__ __device__ size_t total() const { return (size_t)off_bar() + (size_t)bar_count() * 8; }
@@ -287,11 +291,6 @@ __device__ __forceinline__ void resolve_chunk(const GroupedArgs& args, ItemCurso
 
 __device__ __forceinline__ float bf16_lo(uint32_t v) { return __uint_as_float(v << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t v) { return __uint_as_float(v & 0xFFFF0000u); }
-// bf16 scale times 2^24 (the codes enter the MMA as q * 2^-24): add 24 to the exponent field.
-// A zero scale becomes 2^-103, whose product with the accumulator is far below fp32 resolution.
-__device__ __forceinline__ float bf16_lo_x2p24(uint32_t v) { return __uint_as_float((v << 16) + 0x0C000000u); }
-__device__ __forceinline__ float bf16_hi_x2p24(uint32_t v) { return __uint_as_float((v & 0xFFFF0000u) + 0x0C000000u); }
-
 // KC > 0 fixes the column count at compile time (the production shapes), so that the shared-memory layout, the
 // warp count and every loop bound fold into constants; KC = 0 reads them from the arguments.
 template <int NMAT, bool DENSE, int OUT_MODE, int KC>
@@ -303,15 +302,16 @@ grouped_ksplit_kernel(const GroupedArgs args) {
     const uint32_t ng = KC ? (uint32_t)(KC / kGroup) : args.k / kGroup;
     const uint32_t cw = KC ? (ng + kGPW - 1) / kGPW : blockDim.x / kWarp - kExtraWarps;  // compute warps; then the reducers; the last warp loads
     const uint32_t row_bytes = KC ? (uint32_t)(KC / 2) : args.k / 2;
-    const KSplitSmem<NMAT> lay{cw, ng, row_bytes};
+    constexpr uint32_t kSt = ring_stages<NMAT, KC>();
+    const KSplitSmem<NMAT> lay{cw, ng, row_bytes, kSt};
     const uint32_t smem_base = (uint32_t)__cvta_generic_to_shared(smem);
     const uint32_t red_base = smem_base + lay.off_red();
     const uint32_t bar_base = smem_base + lay.off_bar();
     // mbarriers: full[stage] | empty[stage] | part_full[r] | red_free[r]
     auto bar_full = [&](uint32_t st) { return bar_base + st * 8; };
-    auto bar_empty = [&](uint32_t st) { return bar_base + (kWStages + st) * 8; };
-    auto bar_part_full = [&](uint32_t r) { return bar_base + (2 * kWStages + r) * 8; };
-    auto bar_red_free = [&](uint32_t r) { return bar_base + (2 * kWStages + kRedStages + r) * 8; };
+    auto bar_empty = [&](uint32_t st) { return bar_base + (kSt + st) * 8; };
+    auto bar_part_full = [&](uint32_t r) { return bar_base + (2 * kSt + r) * 8; };
+    auto bar_red_free = [&](uint32_t r) { return bar_base + (2 * kSt + kRedStages + r) * 8; };
 
     const uint32_t tiles = args.rows / kTileRows;
     pdl_launch_dependents();
@@ -325,7 +325,7 @@ grouped_ksplit_kernel(const GroupedArgs args) {
     const uint32_t n_items = item_end - item_begin;
 
     if (threadIdx.x == 0) {
-        for (uint32_t st = 0; st < (uint32_t)kWStages; ++st) { mbar_init(bar_full(st), 1); mbar_init(bar_empty(st), cw); }
+        for (uint32_t st = 0; st < kSt; ++st) { mbar_init(bar_full(st), 1); mbar_init(bar_empty(st), cw); }
         for (uint32_t r = 0; r < (uint32_t)kRedStages; ++r) { mbar_init(bar_part_full(r), cw); mbar_init(bar_red_free(r), 1); }
         fence_proxy_async();
     }
@@ -367,8 +367,8 @@ grouped_ksplit_kernel(const GroupedArgs args) {
         uint32_t loaded_chunk = 0xFFFFFFFFu;
         uint32_t fail = 0;
 
-        for (uint32_t li = 0; li < n_items; ++li) {
-            const uint32_t st = li % kWStages, use = li / kWStages;
+        uint32_t st = 0, use = 0;            // ring slot of item li and how often the ring has wrapped
+        for (uint32_t li = 0; li < n_items; ++li, st = st + 1 == kSt ? 0u : st + 1, use += st == 0 ? 1u : 0u) {
             if (cur.chunk != loaded_chunk) {
                 // activations of this warp's columns for the chunk's token g, in MMA operand order: the 16 values
                 // x0..x15 at columns 64 G + 16 t feed four MMAs,
@@ -396,6 +396,9 @@ grouped_ksplit_kernel(const GroupedArgs args) {
                     }
                     sum += __shfl_xor_sync(kFullMask, sum, 1);
                     sum += __shfl_xor_sync(kFullMask, sum, 2);        // every lane of quad g holds token g's group sum
+                    // The codes enter the MMA as q * 2^-24, so the whole row sum is carried at 2^-24 of its value (the group
+                    // sums are scaled to match here, once per chunk) and multiplied back once per item: powers of two, exact.
+                    sum *= 5.9604644775390625e-08f;
                     xsum[i] = make_float2(__shfl_sync(kFullMask, sum, 8 * t), __shfl_sync(kFullMask, sum, 8 * t + 4));
 #pragma unroll
                     for (int h2 = 0; h2 < 2; ++h2) {
@@ -418,9 +421,11 @@ grouped_ksplit_kernel(const GroupedArgs args) {
             for (int m = 0; m < NMAT; ++m) {
 #pragma unroll
                 for (int i = 0; i < kGPW; ++i) {
-                    const bool v = (uint32_t)i < ngw;
-                    wa[m][i] = v ? lds64(ring_item + m * lay.mat_bytes() + i * 32) : make_uint2(0u, 0u);
-                    wb[m][i] = v ? lds64(ring_item + m * lay.mat_bytes() + row8_off + i * 32) : make_uint2(0u, 0u);
+                    // Groups past this warp's range (the last warp of a K that is not a multiple of 256) read the bytes that
+                    // follow the row inside the stage (padding, the next row, the scale planes): masked nibbles are finite
+                    // and meet zero activations, so they add exact zeros and need no predicate.
+                    wa[m][i] = lds64(ring_item + m * lay.mat_bytes() + i * 32);
+                    wb[m][i] = lds64(ring_item + m * lay.mat_bytes() + row8_off + i * 32);
                 }
             }
             float c[NMAT][kGPW][4];
@@ -480,8 +485,8 @@ grouped_ksplit_kernel(const GroupedArgs args) {
                     // zeroed above (or belong to the next warp's group and multiply a zero accumulator and a zero sum)
                     const uint32_t sv0 = i < 2 ? vs0.x : vs0.y, sv1 = i < 2 ? vs1.x : vs1.y;
                     const uint32_t bv0 = i < 2 ? vb0.x : vb0.y, bv1 = i < 2 ? vb1.x : vb1.y;
-                    const float s0 = (i & 1) ? bf16_hi_x2p24(sv0) : bf16_lo_x2p24(sv0);
-                    const float s1 = (i & 1) ? bf16_hi_x2p24(sv1) : bf16_lo_x2p24(sv1);
+                    const float s0 = (i & 1) ? bf16_hi(sv0) : bf16_lo(sv0);
+                    const float s1 = (i & 1) ? bf16_hi(sv1) : bf16_lo(sv1);
                     const float b0 = (i & 1) ? bf16_hi(bv0) : bf16_lo(bv0), b1 = (i & 1) ? bf16_hi(bv1) : bf16_lo(bv1);
                     // c0, c1: weight row g, tokens 2t, 2t+1; c2, c3: weight row g + 8 (scale words 0 / 1)
                     acc[0] = fmaf(s0, c[m][i][0], fmaf(b0, xsum[i].x, acc[0]));
@@ -490,7 +495,7 @@ grouped_ksplit_kernel(const GroupedArgs args) {
                     acc[3] = fmaf(s1, c[m][i][3], fmaf(b1, xsum[i].y, acc[3]));
                 }
 #pragma unroll
-                for (int j = 0; j < 4; ++j) y[m][j] = acc[j];
+                for (int j = 0; j < 4; ++j) y[m][j] = acc[j] * 16777216.0f;
             }
             // this warp is done with the stage (codes and scales are in registers or consumed)
             __syncwarp();
@@ -519,8 +524,8 @@ grouped_ksplit_kernel(const GroupedArgs args) {
         const bool contiguous = lay.row_stride() == row_bytes;       // the 8 rows of a tile land as one copy
         const uint32_t tx_bytes = NMAT * kTileRows * row_bytes + NMAT * 2 * plane_bytes;
         uint32_t fail = 0, issued = 0;
-        for (uint32_t li = 0; li < n_items; ++li) {
-            const uint32_t st = li % kWStages, use = li / kWStages;
+        uint32_t st = 0, use = 0;
+        for (uint32_t li = 0; li < n_items; ++li, st = st + 1 == kSt ? 0u : st + 1, use += st == 0 ? 1u : 0u) {
             if (use > 0 && !mbar_wait(bar_empty(st), (use - 1) & 1)) { fail = kErrTimeoutStageFree; break; }
             const uint32_t mbar = bar_full(st);
             const uint32_t stage = smem_base + st * lay.stage_bytes();
@@ -556,7 +561,7 @@ grouped_ksplit_kernel(const GroupedArgs args) {
         if (fail) {
             if (lane == 0) atomicCAS(args.error, 0u, fail);
             // let the copies already issued land before the CTA's shared memory goes away (bounded)
-            for (uint32_t st = 0; st < (uint32_t)kWStages && st < issued; ++st)
+            for (uint32_t st = 0; st < kSt && st < issued; ++st)
                 for (uint32_t par = 0; par < 2; ++par) mbar_wait(bar_full(st), par);
         }
     } else {
@@ -681,7 +686,7 @@ template <int NMAT, bool DENSE, int OUT_MODE, int KC>
 static tf_status launch_grouped_k(tf_context* ctx, void* stream, GroupedArgs& args, const char* name) {
     const uint32_t ng = args.k / kGroup;
     const uint32_t cw = (ng + kGPW - 1) / kGPW;
-    const KSplitSmem<NMAT> lay{cw, ng, args.k / 2};
+    const KSplitSmem<NMAT> lay{cw, ng, args.k / 2, ring_stages<NMAT, KC>()};
     const size_t smem = lay.total();
     TF_REQUIRE(ctx, smem <= 200 * 1024, TF_ERR_UNSUPPORTED, "%s: K=%u needs %zu bytes of shared memory (limit 200 KB)", name, args.k, smem);
     auto kern = grouped_ksplit_kernel<NMAT, DENSE, OUT_MODE, KC>;

@@ -65,7 +65,8 @@ struct RouterGroupOut {
 
 __host__ __device__ inline size_t router_group_smem_bytes(uint32_t n_pairs, uint32_t num_experts) {
     const uint32_t nw = (n_pairs + 31) / 32;
-    return (size_t)num_experts * nw * 4 + (size_t)num_experts * 2 * 4 + (size_t)n_pairs * 4;
+    // mask, hist + offs, expert ids, warp totals (3 x 32), weights
+    return (size_t)num_experts * nw * 4 + (size_t)num_experts * 2 * 4 + (size_t)n_pairs * 4 + 96 * 4 + (size_t)((n_pairs + 1) / 2) * 4;
 }
 
 __device__ void group_routes_in_block(const uint32_t* __restrict__ idx, const uint16_t* __restrict__ w, uint32_t T, uint32_t K,
@@ -75,54 +76,66 @@ __device__ void group_routes_in_block(const uint32_t* __restrict__ idx, const ui
     uint32_t* hist = mask + (size_t)E * nw;                      // [E]
     uint32_t* offs = hist + E;                                   // [E]
     uint32_t* exs = offs + E;                                    // [n]
+    uint32_t* wtot = exs + n;                                    // [3][32]: per-warp totals of the scan
+    uint16_t* wts = reinterpret_cast<uint16_t*>(wtot + 96);      // [n]
+    const uint32_t lane = threadIdx.x % kWarp, warp = threadIdx.x / kWarp, nwarps = blockDim.x / kWarp;
+    // ids and weights (written by other blocks of this launch) travel while the bitmaps are cleared
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        uint32_t ex = __ldcg(idx + i);
+        if (ex != 0xFFFFFFFFu && ex >= E) ex = E - 1;            // min(id, E-1): Runtime/Inference/RealForwardRunner.swift:955
+        exs[i] = ex;
+        wts[i] = __ldcg(w + i);
+    }
     for (uint32_t i = threadIdx.x; i < E * nw + E; i += blockDim.x) mask[i] = 0;      // mask and hist are adjacent
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        uint32_t ex = __ldcg(idx + i);                           // written by other blocks of this launch
+        const uint32_t ex = exs[i];
         if (ex != 0xFFFFFFFFu) {
-            if (ex >= E) ex = E - 1;                             // min(id, E-1): Runtime/Inference/RealForwardRunner.swift:955
             atomicAdd(&hist[ex], 1u);
             atomicOr(&mask[(size_t)ex * nw + i / 32], 1u << (i % 32));
         }
-        exs[i] = ex;
     }
     __syncthreads();
-    if (threadIdx.x < kWarp) {
-        const uint32_t lane = threadIdx.x;
-        uint32_t off = 0, gi = 0, ch = 0;                        // running totals over the experts before `base`
-        for (uint32_t base = 0; base < E; base += kWarp) {
-            const uint32_t e = base + lane;
-            const uint32_t cnt = e < E ? hist[e] : 0u;
-            const uint32_t nch = (cnt + (uint32_t)kChunkTokens - 1) / (uint32_t)kChunkTokens;
-            uint32_t i_off = cnt, i_g = cnt ? 1u : 0u, i_ch = nch;
+    // exclusive scans over the experts (pairs, non-empty groups, chunks): every warp scans 32 experts, the warps'
+    // totals meet in shared memory, and rounds of nwarps * 32 experts carry the running totals.
+    uint32_t off = 0, gi = 0, ch = 0;
+    for (uint32_t base = 0; base < E; base += nwarps * kWarp) {
+        const uint32_t e = base + warp * kWarp + lane;
+        const uint32_t cnt = e < E ? hist[e] : 0u;
+        const uint32_t nch = (cnt + (uint32_t)kChunkTokens - 1) / (uint32_t)kChunkTokens;
+        uint32_t i_off = cnt, i_g = cnt ? 1u : 0u, i_ch = nch;
 #pragma unroll
-            for (int o = 1; o < kWarp; o <<= 1) {
-                const uint32_t a = __shfl_up_sync(kFullMask, i_off, o), b = __shfl_up_sync(kFullMask, i_g, o),
-                               c = __shfl_up_sync(kFullMask, i_ch, o);
-                if ((int)lane >= o) { i_off += a; i_g += b; i_ch += c; }
-            }
-            const uint32_t my_off = off + i_off - cnt, my_g = gi + i_g - (cnt ? 1u : 0u), my_ch = ch + i_ch - nch;
-            if (e < E) {
-                offs[e] = my_off;
-                out.per_expert_counts[e] = cnt;
-                out.per_expert_offsets[e] = cnt ? my_off : 0xFFFFFFFFu;
-                if (cnt) {
-                    out.groups[my_g] = tf_group{e, my_off, cnt};
-                    out.chunk_start[my_g] = my_ch;
-                    for (uint32_t j = 0; j < nch; ++j) out.chunk_group[my_ch + j] = my_g;
-                }
-            }
-            off += __shfl_sync(kFullMask, i_off, kWarp - 1);
-            gi += __shfl_sync(kFullMask, i_g, kWarp - 1);
-            ch += __shfl_sync(kFullMask, i_ch, kWarp - 1);
+        for (int o = 1; o < kWarp; o <<= 1) {
+            const uint32_t a = __shfl_up_sync(kFullMask, i_off, o), b2 = __shfl_up_sync(kFullMask, i_g, o),
+                           c = __shfl_up_sync(kFullMask, i_ch, o);
+            if ((int)lane >= o) { i_off += a; i_g += b2; i_ch += c; }
         }
-        if (lane == 0) {
-            out.counters[0] = gi;
-            out.counters[1] = ch;
-            out.counters[2] = n;
+        if (lane == kWarp - 1) { wtot[warp] = i_off; wtot[32 + warp] = i_g; wtot[64 + warp] = i_ch; }
+        __syncthreads();
+        uint32_t p_off = off, p_g = gi, p_ch = ch;
+        for (uint32_t v = 0; v < nwarps; ++v) {
+            const uint32_t a = wtot[v], b2 = wtot[32 + v], c = wtot[64 + v];
+            if (v < warp) { p_off += a; p_g += b2; p_ch += c; }
+            off += a; gi += b2; ch += c;
         }
+        const uint32_t my_off = p_off + i_off - cnt, my_g = p_g + i_g - (cnt ? 1u : 0u), my_ch = p_ch + i_ch - nch;
+        if (e < E) {
+            offs[e] = my_off;
+            out.per_expert_counts[e] = cnt;
+            out.per_expert_offsets[e] = cnt ? my_off : 0xFFFFFFFFu;
+            if (cnt) {
+                out.groups[my_g] = tf_group{e, my_off, cnt};
+                out.chunk_start[my_g] = my_ch;
+                for (uint32_t j = 0; j < nch; ++j) out.chunk_group[my_ch + j] = my_g;
+            }
+        }
+        __syncthreads();                                          // wtot is reused by the next round; offs is read below
     }
-    __syncthreads();
+    if (threadIdx.x == 0) {
+        out.counters[0] = gi;
+        out.counters[1] = ch;
+        out.counters[2] = n;
+    }
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
         const uint32_t ex = exs[i];
         if (ex == 0xFFFFFFFFu) continue;
@@ -130,7 +143,7 @@ __device__ void group_routes_in_block(const uint32_t* __restrict__ idx, const ui
         uint32_t pos = offs[ex];
         for (uint32_t q = 0; q < i / 32; ++q) pos += __popc(m[q]);
         pos += __popc(m[i / 32] & ((1u << (i % 32)) - 1u));
-        out.sorted_pairs[pos] = tf_pair{i / K, ex, i % K, (uint32_t)__ldcg(w + i)};
+        out.sorted_pairs[pos] = tf_pair{i / K, ex, i % K, (uint32_t)wts[i]};
     }
 }
 
@@ -311,6 +324,143 @@ router_split_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
     group_routes_in_block(out_idx, out_w, gridDim.x, top_k, num_experts, grp, smem);
 }
 
+// A handful of rows (batched decode, 2...kRouterSplitRows): grid (rows / R, experts / 8). A block stages R activation
+// rows (as fp32 x * effective_scale) and its eight expert rows in shared memory; warp w then computes the logits of
+// expert e0 + w for all R rows at once, so the codes, scales and biases of a group are decoded once per R rows. The
+// arithmetic and its order per (row, expert) are those of router_row_logit_smem. The last block of a row group
+// (ticket) selects the top-k of its R rows, one warp per row; the block that completes the last row group builds the
+// grouping tables.
+constexpr int kRowsThreads = 256;
+constexpr int kRowsExpertsPerBlock = kRowsThreads / kWarp;
+template <bool X_BF16, int R>
+__global__ void __launch_bounds__(kRowsThreads)
+router_rows_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, const uint16_t* __restrict__ B,
+                   const uint16_t* __restrict__ hidden, uint32_t hidden_stride,
+                   const uint16_t* __restrict__ eff, const uint16_t* __restrict__ per_expert_scale,
+                   const float* __restrict__ logit_bias,
+                   uint32_t* __restrict__ out_idx, uint16_t* __restrict__ out_w, float* __restrict__ out_logits,
+                   float* scratch_logits, unsigned int* tickets, const RouterGroupOut grp,
+                   uint32_t rows, uint32_t num_experts, uint32_t d, uint32_t top_k) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t groups = d / kGroup;
+    float* xf = reinterpret_cast<float*>(smem);                                        // [R][d]
+    uint8_t* wrows = smem + (size_t)R * d * 4;                                         // [8][d]
+    uint16_t* srows = reinterpret_cast<uint16_t*>(wrows + (size_t)kRowsExpertsPerBlock * d);   // [8][groups]
+    uint16_t* brows = srows + kRowsExpertsPerBlock * groups;
+    __shared__ float scores[R][TF_MAX_ROUTER_EXPERTS];
+    __shared__ bool is_last;
+    const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
+    const uint32_t row0 = blockIdx.x * R;
+    const uint32_t e0 = blockIdx.y * kRowsExpertsPerBlock;
+    const uint32_t ne = num_experts - e0 < (uint32_t)kRowsExpertsPerBlock ? num_experts - e0 : (uint32_t)kRowsExpertsPerBlock;
+    pdl_launch_dependents();
+    // expert rows (contiguous in every plane; d is a multiple of 64 and the planes are 16-byte aligned by contract)
+    {
+        const uint8_t* wsrc = W + (size_t)e0 * d;
+        for (uint32_t i = threadIdx.x; i < ne * d / 16; i += kRowsThreads)
+            reinterpret_cast<uint4*>(wrows)[i] = ldg_nc_u4(wsrc + (size_t)i * 16);
+        for (uint32_t i = threadIdx.x; i < ne * groups; i += kRowsThreads) {
+            srows[i] = S[(size_t)e0 * groups + i];
+            brows[i] = B[(size_t)e0 * groups + i];
+        }
+    }
+    pdl_wait();          // the weights above do not depend on the previous kernel; the hidden rows do
+    for (uint32_t i = threadIdx.x; i < d / 8; i += kRowsThreads) {
+        const uint4 ev = __ldg(reinterpret_cast<const uint4*>(eff) + i);
+        const uint32_t ew[4] = {ev.x, ev.y, ev.z, ev.w};
+        uint4 hv[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+            hv[r] = row0 + r < rows ? __ldg(reinterpret_cast<const uint4*>(hidden + (size_t)(row0 + r) * hidden_stride) + i)
+                                    : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const uint32_t hw[4] = {hv[r].x, hv[r].y, hv[r].z, hv[r].w};
+            float o[8];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint16_t h0 = (uint16_t)(hw[q] & 0xFFFFu), h1 = (uint16_t)(hw[q] >> 16);
+                const float f0 = X_BF16 ? bf16_bits_to_float(h0) : f16_bits_to_float(h0);
+                const float f1 = X_BF16 ? bf16_bits_to_float(h1) : f16_bits_to_float(h1);
+                o[2 * q] = __fmul_rn(f0, bf16_bits_to_float((uint16_t)(ew[q] & 0xFFFFu)));
+                o[2 * q + 1] = __fmul_rn(f1, bf16_bits_to_float((uint16_t)(ew[q] >> 16)));
+            }
+            float4* dst = reinterpret_cast<float4*>(xf + (size_t)r * d + i * 8);
+            dst[0] = make_float4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+        }
+    }
+    __syncthreads();
+
+    if ((uint32_t)warp < ne) {
+        const uint8_t* wr = wrows + (size_t)warp * d;
+        const uint16_t* sr = srows + warp * groups;
+        const uint16_t* br = brows + warp * groups;
+        float acc[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r] = 0.0f;
+#pragma unroll 2
+        for (uint32_t g = 0; g < groups; ++g) {
+            const uint32_t i0 = g * kGroup + lane * 2;
+            const uint32_t w = *reinterpret_cast<const uint16_t*>(wr + i0);
+            // byte -> float through the 2^23 mantissa trick (exact for 0...255)
+            const float q0 = __uint_as_float(0x4B000000u | (w & 0xFFu)) - 8388608.0f;
+            const float q1 = __uint_as_float(0x4B000000u | (w >> 8)) - 8388608.0f;
+            const float sc = bf16_bits_to_float(sr[g]);
+            const float bi = bf16_bits_to_float(br[g]);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float2 xv = *reinterpret_cast<const float2*>(xf + (size_t)r * d + i0);
+                const float p = __fmaf_rn(q1, xv.y, __fmul_rn(q0, xv.x));
+                acc[r] = __fmaf_rn(sc, p, acc[r]);
+                acc[r] = __fmaf_rn(bi, __fadd_rn(xv.x, xv.y), acc[r]);
+            }
+        }
+        const uint32_t e = e0 + warp;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float logit = warp_sum(acc[r]);
+            if (logit_bias) logit = __fadd_rn(logit, logit_bias[e]);
+            if (lane == 0 && row0 + r < rows) scratch_logits[(size_t)(row0 + r) * TF_MAX_ROUTER_EXPERTS + e] = logit;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int tk = atomicAdd(&tickets[blockIdx.x], 1u);
+        is_last = (tk == gridDim.y - 1);
+        if (is_last) tickets[blockIdx.x] = 0;            // ready for the next launch on this stream
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (uint32_t i = threadIdx.x; i < R * num_experts; i += kRowsThreads) {
+        const uint32_t r = i / num_experts, e = i % num_experts;
+        if (row0 + r < rows) {
+            const float v = __ldcg(&scratch_logits[(size_t)(row0 + r) * TF_MAX_ROUTER_EXPERTS + e]);
+            scores[r][e] = v;
+            if (out_logits) out_logits[(size_t)(row0 + r) * num_experts + e] = v;
+        }
+    }
+    __syncthreads();
+    if (warp < R && row0 + warp < rows)
+        warp_select_topk(scores[warp], num_experts, top_k, per_expert_scale, out_idx + (size_t)(row0 + warp) * top_k,
+                         out_w + (size_t)(row0 + warp) * top_k, lane);
+    if (grp.sorted_pairs == nullptr) return;
+    // the block that completes the last row group groups all rows (second ticket, after the row tickets)
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int tk = atomicAdd(&tickets[kRouterSplitRows], 1u);
+        is_last = (tk == gridDim.x - 1);
+        if (is_last) tickets[kRouterSplitRows] = 0;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    group_routes_in_block(out_idx, out_w, rows, top_k, num_experts, grp, smem);
+}
+
 // Many rows (batched decode, prefill): one block per row.
 template <bool X_BF16>
 __global__ void __launch_bounds__(kBlockRouterThreads)
@@ -344,8 +494,9 @@ router_block_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
 }
 
 // Prefill-sized batches: one block per eight rows. Same canonical arithmetic per (row, expert) as router_row_logit,
-// but an expert's codes, scale and bias are fetched once per group for eight token rows instead of once per row:
-// the eight rows' scaled activations sit in shared memory as fp32 and every lane carries eight accumulators.
+// but an expert's codes, scale and bias are fetched once per group for eight token rows instead of once per row, and
+// a group's activations are read once for two experts: the eight rows' scaled activations sit in shared memory as
+// fp32 and every lane carries sixteen accumulators.
 constexpr int kTileRouterRows = 8;
 template <bool X_BF16>
 __global__ void __launch_bounds__(kBlockRouterThreads)
@@ -377,34 +528,58 @@ router_tile_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S
     __syncthreads();
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t groups = d / kGroup;
-    for (uint32_t e = warp; e < num_experts; e += kBlockRouterThreads / kWarp) {
-        const uint8_t* Wrow = W + (size_t)e * d;
-        const uint16_t* s_row = S + (size_t)e * groups;
-        const uint16_t* b_row = B + (size_t)e * groups;
-        float acc[kTileRouterRows];
+    constexpr uint32_t kWarps = kBlockRouterThreads / kWarp;
+    // A warp takes two experts at a time (e and e + 8): the eight rows' activations of a group are read from shared
+    // memory once for both, and the next group's codes, scales and biases are already on their way while the current
+    // group is multiplied. Per (row, expert) the operations and their order are those of router_row_logit.
+    for (uint32_t e0 = warp; e0 < num_experts; e0 += 2 * kWarps) {
+        const uint32_t e1 = e0 + kWarps;
+        const bool two = e1 < num_experts;
+        const uint32_t ea = e0, eb = two ? e1 : e0;
+        const uint8_t* Wa = W + (size_t)ea * d + lane * 2;
+        const uint8_t* Wb = W + (size_t)eb * d + lane * 2;
+        const uint16_t* sa = S + (size_t)ea * groups; const uint16_t* ba = B + (size_t)ea * groups;
+        const uint16_t* sb = S + (size_t)eb * groups; const uint16_t* bb = B + (size_t)eb * groups;
+        float acc_a[kTileRouterRows], acc_b[kTileRouterRows];
 #pragma unroll
-        for (int r = 0; r < kTileRouterRows; ++r) acc[r] = 0.0f;
+        for (int r = 0; r < kTileRouterRows; ++r) { acc_a[r] = 0.0f; acc_b[r] = 0.0f; }
+        uint32_t wa = *reinterpret_cast<const uint16_t*>(Wa), wb = *reinterpret_cast<const uint16_t*>(Wb);   // d % 64 == 0, 2-byte aligned rows
+        uint16_t nsa = sa[0], nba = ba[0], nsb = sb[0], nbb = bb[0];
         for (uint32_t g = 0; g < groups; ++g) {
+            const uint32_t cwa = wa, cwb = wb;
+            const float sca = bf16_bits_to_float(nsa), bia = bf16_bits_to_float(nba);
+            const float scb = bf16_bits_to_float(nsb), bib = bf16_bits_to_float(nbb);
+            if (g + 1 < groups) {
+                wa = *reinterpret_cast<const uint16_t*>(Wa + (g + 1) * kGroup);
+                wb = *reinterpret_cast<const uint16_t*>(Wb + (g + 1) * kGroup);
+                nsa = sa[g + 1]; nba = ba[g + 1]; nsb = sb[g + 1]; nbb = bb[g + 1];
+            }
+            const float qa0 = (float)(cwa & 0xFFu), qa1 = (float)(cwa >> 8);
+            const float qb0 = (float)(cwb & 0xFFu), qb1 = (float)(cwb >> 8);
             const uint32_t i0 = g * kGroup + lane * 2;
-            const uint32_t w = *reinterpret_cast<const uint16_t*>(Wrow + i0);      // d % 64 == 0 and 2-byte aligned rows
-            const float q0 = (float)(w & 0xFFu), q1 = (float)(w >> 8);
-            const float sc = bf16_bits_to_float(s_row[g]);
-            const float bi = bf16_bits_to_float(b_row[g]);
 #pragma unroll
             for (int r = 0; r < kTileRouterRows; ++r) {
                 const float2 xv = *reinterpret_cast<const float2*>(xf + (size_t)r * d + i0);
-                const float p = __fmaf_rn(q1, xv.y, __fmul_rn(q0, xv.x));
-                acc[r] = __fmaf_rn(sc, p, acc[r]);
-                acc[r] = __fmaf_rn(bi, __fadd_rn(xv.x, xv.y), acc[r]);
+                const float xs = __fadd_rn(xv.x, xv.y);
+                const float pa = __fmaf_rn(qa1, xv.y, __fmul_rn(qa0, xv.x));
+                acc_a[r] = __fmaf_rn(sca, pa, acc_a[r]);
+                acc_a[r] = __fmaf_rn(bia, xs, acc_a[r]);
+                const float pb = __fmaf_rn(qb1, xv.y, __fmul_rn(qb0, xv.x));
+                acc_b[r] = __fmaf_rn(scb, pb, acc_b[r]);
+                acc_b[r] = __fmaf_rn(bib, xs, acc_b[r]);
             }
         }
 #pragma unroll
         for (int r = 0; r < kTileRouterRows; ++r) {
-            float logit = warp_sum(acc[r]);
-            if (logit_bias) logit = __fadd_rn(logit, logit_bias[e]);
+            float la = warp_sum(acc_a[r]), lb = warp_sum(acc_b[r]);
+            if (logit_bias) { la = __fadd_rn(la, logit_bias[ea]); lb = __fadd_rn(lb, logit_bias[eb]); }
             if (lane == 0 && (uint32_t)r < nrows) {
-                scores[r * num_experts + e] = logit;
-                if (out_logits) out_logits[(size_t)(row0 + r) * num_experts + e] = logit;
+                scores[r * num_experts + ea] = la;
+                if (out_logits) out_logits[(size_t)(row0 + r) * num_experts + ea] = la;
+                if (two) {
+                    scores[r * num_experts + eb] = lb;
+                    if (out_logits) out_logits[(size_t)(row0 + r) * num_experts + eb] = lb;
+                }
             }
         }
     }
@@ -433,6 +608,28 @@ static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, 
     auto ep = reinterpret_cast<const uint16_t*>(eff);
     auto pp = reinterpret_cast<const uint16_t*>(pes);
     auto wp = reinterpret_cast<uint16_t*>(out_w);
+    const bool vec16 = aligned(W, 16) && aligned(hp, 16) && aligned(ep, 16) && d % 16 == 0 && stride % 8 == 0;
+    if (rows >= 2 && rows <= (uint32_t)kRouterSplitRows && vec16) {
+        constexpr int R = 4;
+        auto k = bf ? router_rows_kernel<true, R> : router_rows_kernel<false, R>;
+        size_t smem_rows = (size_t)R * d * 4 + (size_t)kRowsExpertsPerBlock * d + (size_t)kRowsExpertsPerBlock * (d / kGroup) * 4;
+        RouterGroupOut grp{};
+        if (routes) {
+            grp = RouterGroupOut{static_cast<tf_pair*>(routes->sorted_pairs), static_cast<uint32_t*>(routes->per_expert_offsets),
+                                 static_cast<uint32_t*>(routes->per_expert_counts), static_cast<tf_group*>(routes->groups),
+                                 static_cast<uint32_t*>(routes->chunk_group), static_cast<uint32_t*>(routes->chunk_start),
+                                 static_cast<uint32_t*>(routes->counters)};
+            const size_t need = router_group_smem_bytes(rows * top_k, num_experts);
+            if (need > smem_rows) smem_rows = need;
+        }
+        TF_REQUIRE(ctx, smem_rows <= 200 * 1024, TF_ERR_UNSUPPORTED, "%s: D=%u too large", name, d);
+        static DeviceSmemCache configured_rows[2];
+        if (tf_status s2 = ensure_dynamic_smem(ctx, k, configured_rows[bf ? 1 : 0], smem_rows)) return s2;
+        dim3 grid((rows + R - 1) / R, (num_experts + kRowsExpertsPerBlock - 1) / kRowsExpertsPerBlock);
+        launch_pdl(k, grid, dim3(kRowsThreads), smem_rows, st, W, Sp, Bp, hp, stride, ep, pp, logit_bias, out_idx, wp, out_logits,
+                   ctx->router_logits, ctx->router_tickets, grp, rows, num_experts, d, top_k);
+        return check_launch(ctx, name);
+    }
     if (rows <= (uint32_t)kRouterSplitRows) {
         dim3 grid(rows, (num_experts + kSplitExpertsPerBlock - 1) / kSplitExpertsPerBlock);
         auto k = bf ? router_split_kernel<true> : router_split_kernel<false>;

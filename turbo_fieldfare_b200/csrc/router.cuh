@@ -6,45 +6,60 @@
 
 namespace tf {
 
-// Warp-parallel top-k over logits in shared memory: k rounds of arg-max with
-// ties to the lower index, i.e. the first k entries of the order
-// (score desc, index asc) — the result of the reference's insertion scan
-// (moe.metal:152-166). Then softmax over the selected scores times the
-// per-expert gain, rounded to fp16 (moe.metal:168-184). Called by warp 0.
-__device__ __forceinline__ void warp_select_topk(float* scores /*shared, clobbered*/, uint32_t num_experts, uint32_t top_k,
+// Top-k of a row of scores (highest first, ties to the lower expert index) and the softmax over the selected scores
+// times the per-expert gain, rounded to fp16: the first k entries of the order (score desc, index asc), which is the
+// result of the reference's insertion scan (Metal/MoE/moe.metal:152-184). Every lane keeps its experts' scores in registers as
+// order-preserving integer keys; a round is one warp-wide integer maximum followed by a warp-wide minimum over the
+// indices that hold it; a selected expert drops to -inf, so it can only come back when nothing greater is left (fewer
+// comparable candidates than top_k). NaN scores never win. The exponentials are taken by top_k lanes at once and summed
+// in rank order. `scores` is only read.
+__device__ __forceinline__ uint32_t topk_score_key(float v) {
+    if (v != v) return 0u;
+    const uint32_t b = __float_as_uint(v + 0.0f);             // -0 and +0 compare equal: one key for both
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);       // -inf maps to 0x007FFFFF, above the NaN key
+}
+__device__ __forceinline__ float topk_key_score(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k & 0x7FFFFFFFu) : ~k);
+}
+__device__ __forceinline__ void warp_select_topk(const float* scores /*shared*/, uint32_t num_experts, uint32_t top_k,
                                                  const uint16_t* __restrict__ per_expert_scale,
                                                  uint32_t* __restrict__ out_idx, uint16_t* __restrict__ out_w, int lane) {
-    float sel_score[TF_MAX_TOP_K];
-    uint32_t sel_idx[TF_MAX_TOP_K];
-    for (uint32_t r = 0; r < top_k; ++r) {
-        float best = -INFINITY;
-        uint32_t best_e = 0xFFFFFFFFu;
-        for (uint32_t e = lane; e < num_experts; e += kWarp) {
-            const float s = scores[e];
-            if (s > best || (s == best && e < best_e)) { best = s; best_e = e; }
-        }
+    constexpr int kPerLane = TF_MAX_ROUTER_EXPERTS / kWarp;
+    uint32_t key[kPerLane];
 #pragma unroll
-        for (int off = 16; off >= 1; off >>= 1) {
-            const float os = __shfl_xor_sync(kFullMask, best, off);
-            const uint32_t oe = __shfl_xor_sync(kFullMask, best_e, off);
-            if (os > best || (os == best && oe < best_e)) { best = os; best_e = oe; }
-        }
-        if (best_e == 0xFFFFFFFFu) best_e = 0;   // fewer finite candidates than top_k
-        sel_score[r] = best;
-        sel_idx[r] = best_e;
-        if (lane == 0 && best_e < num_experts) scores[best_e] = -INFINITY;   // NaN-free inputs: -inf never wins again before real scores
-        __syncwarp();
+    for (int j = 0; j < kPerLane; ++j) {
+        const uint32_t e = lane + j * kWarp;
+        key[j] = e < num_experts ? topk_score_key(scores[e]) : 0u;
     }
-    if (lane == 0) {
-        const float max_s = sel_score[0];
-        float exps[TF_MAX_TOP_K];
-        float sum_exp = 0.0f;
-        for (uint32_t r = 0; r < top_k; ++r) { exps[r] = expf(sel_score[r] - max_s); sum_exp += exps[r]; }
-        for (uint32_t r = 0; r < top_k; ++r) {
-            const float w = exps[r] / sum_exp * bf16_bits_to_float(per_expert_scale[sel_idx[r]]);
-            out_idx[r] = sel_idx[r];
-            out_w[r] = __half_as_ushort(__float2half_rn(w));
+    const uint32_t neg_inf_key = 0x007FFFFFu;
+    float my_score = 0.0f, max_s = 0.0f;
+    uint32_t my_idx = 0;
+    for (uint32_t r = 0; r < top_k; ++r) {
+        uint32_t best = 0u, best_e = 0xFFFFFFFFu;
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j) {
+            const uint32_t e = lane + j * kWarp;
+            if (e < num_experts && key[j] > best) { best = key[j]; best_e = e; }      // ascending e: ties keep the lower index
         }
+        const uint32_t top = __reduce_max_sync(kFullMask, best);
+        uint32_t winner = __reduce_min_sync(kFullMask, (best == top && top != 0u) ? best_e : 0xFFFFFFFFu);
+        float top_score = topk_key_score(top);
+        if (winner == 0xFFFFFFFFu) { winner = 0u; top_score = -INFINITY; }            // no comparable candidate at all
+        if (r == 0) max_s = top_score;
+        if ((uint32_t)lane == r) { my_score = top_score; my_idx = winner; }
+        if (winner < num_experts && (winner % kWarp) == (uint32_t)lane) {
+#pragma unroll
+            for (int j = 0; j < kPerLane; ++j)
+                if ((uint32_t)j == winner / kWarp) key[j] = neg_inf_key;
+        }
+    }
+    const float ex = (uint32_t)lane < top_k ? expf(my_score - max_s) : 0.0f;
+    float sum_exp = 0.0f;
+    for (uint32_t r = 0; r < top_k; ++r) sum_exp += __shfl_sync(kFullMask, ex, (int)r);
+    if ((uint32_t)lane < top_k) {
+        const float w = ex / sum_exp * bf16_bits_to_float(per_expert_scale[my_idx]);
+        out_idx[lane] = my_idx;
+        out_w[lane] = __half_as_ushort(__float2half_rn(w));
     }
 }
 
