@@ -188,12 +188,12 @@ struct GroupedArgs {
 // A = codes of weight rows g (a0, a2) and g + 8 (a1, a3); B = activations of token g.
 __device__ __forceinline__ void mma16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, const uint2& b,
                                                const float (&z)[4]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
                  : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y), "f"(z[0]), "f"(z[1]), "f"(z[2]), "f"(z[3]));
 }
 __device__ __forceinline__ void mma16816_acc(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, const uint2& b) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b.x), "r"(b.y));
 }
@@ -461,38 +461,36 @@ grouped_ksplit_kernel(const GroupedArgs args) {
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
                 const uint32_t sm_s = sb_item + (m * 2) * lay.sb_plane_bytes(), sm_b = sm_s + lay.sb_plane_bytes();
-                uint2 vs0, vs1, vb0, vb1;
+                // scale and bias of weight rows g (index 0) and g + 8 (index 1) for this warp's groups, as fp32
+                float sf[2][kGPW], bf[2][kGPW];
                 if (sb_vec) {
-                    vs0 = lds64(sm_s + sb_row0); vs1 = lds64(sm_s + sb_row1);
-                    vb0 = lds64(sm_b + sb_row0); vb1 = lds64(sm_b + sb_row1);
+                    const uint2 vs0 = lds64(sm_s + sb_row0), vs1 = lds64(sm_s + sb_row1);
+                    const uint2 vb0 = lds64(sm_b + sb_row0), vb1 = lds64(sm_b + sb_row1);
+#pragma unroll
+                    for (int i = 0; i < kGPW; ++i) {
+                        const uint32_t sv0 = i < 2 ? vs0.x : vs0.y, sv1 = i < 2 ? vs1.x : vs1.y;
+                        const uint32_t bv0 = i < 2 ? vb0.x : vb0.y, bv1 = i < 2 ? vb1.x : vb1.y;
+                        sf[0][i] = (i & 1) ? bf16_hi(sv0) : bf16_lo(sv0); sf[1][i] = (i & 1) ? bf16_hi(sv1) : bf16_lo(sv1);
+                        bf[0][i] = (i & 1) ? bf16_hi(bv0) : bf16_lo(bv0); bf[1][i] = (i & 1) ? bf16_hi(bv1) : bf16_lo(bv1);
+                    }
                 } else {
-                    uint32_t v[4][4];
+                    // groups beyond this warp's range carry zero activations; their scale words are forced to zero so that
+                    // whatever follows the plane in the stage cannot turn 0 * x into a NaN
 #pragma unroll
                     for (int i = 0; i < kGPW; ++i) {
                         const bool ok = (uint32_t)i < ngw;
-                        v[0][i] = ok ? lds16(sm_s + sb_row0 + i * 2) : 0u; v[1][i] = ok ? lds16(sm_s + sb_row1 + i * 2) : 0u;
-                        v[2][i] = ok ? lds16(sm_b + sb_row0 + i * 2) : 0u; v[3][i] = ok ? lds16(sm_b + sb_row1 + i * 2) : 0u;
+                        sf[0][i] = ok ? bf16_lo(lds16(sm_s + sb_row0 + i * 2)) : 0.0f; sf[1][i] = ok ? bf16_lo(lds16(sm_s + sb_row1 + i * 2)) : 0.0f;
+                        bf[0][i] = ok ? bf16_lo(lds16(sm_b + sb_row0 + i * 2)) : 0.0f; bf[1][i] = ok ? bf16_lo(lds16(sm_b + sb_row1 + i * 2)) : 0.0f;
                     }
-                    vs0 = make_uint2(v[0][0] | (v[0][1] << 16), v[0][2] | (v[0][3] << 16));
-                    vs1 = make_uint2(v[1][0] | (v[1][1] << 16), v[1][2] | (v[1][3] << 16));
-                    vb0 = make_uint2(v[2][0] | (v[2][1] << 16), v[2][2] | (v[2][3] << 16));
-                    vb1 = make_uint2(v[3][0] | (v[3][1] << 16), v[3][2] | (v[3][3] << 16));
                 }
                 float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
                 for (int i = 0; i < kGPW; ++i) {
-                    // groups beyond this warp's range carry zero codes and zero activations; their scale words are
-                    // zeroed above (or belong to the next warp's group and multiply a zero accumulator and a zero sum)
-                    const uint32_t sv0 = i < 2 ? vs0.x : vs0.y, sv1 = i < 2 ? vs1.x : vs1.y;
-                    const uint32_t bv0 = i < 2 ? vb0.x : vb0.y, bv1 = i < 2 ? vb1.x : vb1.y;
-                    const float s0 = (i & 1) ? bf16_hi(sv0) : bf16_lo(sv0);
-                    const float s1 = (i & 1) ? bf16_hi(sv1) : bf16_lo(sv1);
-                    const float b0 = (i & 1) ? bf16_hi(bv0) : bf16_lo(bv0), b1 = (i & 1) ? bf16_hi(bv1) : bf16_lo(bv1);
-                    // c0, c1: weight row g, tokens 2t, 2t+1; c2, c3: weight row g + 8 (scale words 0 / 1)
-                    acc[0] = fmaf(s0, c[m][i][0], fmaf(b0, xsum[i].x, acc[0]));
-                    acc[1] = fmaf(s0, c[m][i][1], fmaf(b0, xsum[i].y, acc[1]));
-                    acc[2] = fmaf(s1, c[m][i][2], fmaf(b1, xsum[i].x, acc[2]));
-                    acc[3] = fmaf(s1, c[m][i][3], fmaf(b1, xsum[i].y, acc[3]));
+                    // c0, c1: weight row g, tokens 2t, 2t+1; c2, c3: weight row g + 8
+                    acc[0] = fmaf(sf[0][i], c[m][i][0], fmaf(bf[0][i], xsum[i].x, acc[0]));
+                    acc[1] = fmaf(sf[0][i], c[m][i][1], fmaf(bf[0][i], xsum[i].y, acc[1]));
+                    acc[2] = fmaf(sf[1][i], c[m][i][2], fmaf(bf[1][i], xsum[i].x, acc[2]));
+                    acc[3] = fmaf(sf[1][i], c[m][i][3], fmaf(bf[1][i], xsum[i].y, acc[3]));
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) y[m][j] = acc[j] * 16777216.0f;
