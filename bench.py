@@ -188,6 +188,8 @@ def run_gpu(args):
     prefill_tokens, steps_dec, batch = args.prefill_tokens, args.decode_steps, args.decode_batch
     ctx = TurboContext(local_rank)
     ctx.set_single_launch_step(bool(args.single_launch_step))
+    if args.shared_tensor_min > 0:
+        ctx.set_shared_tensorcore_min_tokens(args.shared_tensor_min)
     ep = world > 1
     if ep:
         # experts sharded 128/N per GPU, per-rank token counts fixed (weak scaling), all-to-all dispatch and combine
@@ -578,6 +580,8 @@ def case_block(args) -> None:
     ctx.set_single_launch_step(bool(args.single_launch_step))
     if args.tensor_min > 0:
         ctx.set_tensorcore_min_tokens(args.tensor_min)
+    if args.shared_tensor_min > 0:
+        ctx.set_shared_tensorcore_min_tokens(args.shared_tensor_min)
     stack = MoEStack(ctx, layers=args.layers, seed=3)
     ws = stack.workspace(args.tokens)
     h = torch.randn(args.tokens, 2816, device="cuda").half()
@@ -726,6 +730,8 @@ def main():
     ap.add_argument("--cols", type=int, default=2816, help="--case qmm: weight columns")
     ap.add_argument("--iters", type=int, default=3, help="--case: timed repetitions")
     ap.add_argument("--case-warm", type=int, default=0, help="--case: untimed launches before the timed ones")
+    ap.add_argument("--shared-tensor-min", type=int, default=0,
+                    help="smallest token count whose shared expert runs on the tensor cores (0: the library's default)")
     ap.add_argument("--tensor-min", type=int, default=0, help="--case block: smallest token count that takes the tensor-core path")
     ap.add_argument("--zipf-exponent", type=float, default=0.0, help="--case block: router logit bias log(p), p ~ 1/rank^s (0 = none)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -57,6 +57,31 @@ def test_pack_matches_numpy_plan(tf_ctx, oracle, T, capacity):
         assert np.array_equal(from_dev(ids2, np.uint32), eloc)
 
 
+def test_combine_and_reduce_take_more_rows_than_a_grid_dimension_holds(tf_ctx, oracle):
+    """An expert-parallel rank whose experts are popular can hold more than 65535 rows (eight ranks, 4096 tokens each,
+    a shard with twice the average traffic): the row count must not sit in a 16-bit grid dimension."""
+    import torch
+    o = oracle
+    rows, D = 70001, 64
+    rng = np.random.default_rng(70001)
+    src = o.f32_to_f16(rng.standard_normal((rows, D)).astype(np.float32))
+    perm = rng.permutation(rows).astype(np.uint32)
+    ones = np.full(rows, 0x3C00, dtype=np.uint16)                 # fp16 1.0: an exact copy through the permutation
+    st = torch.cuda.current_stream().cuda_stream
+    out = torch.zeros(rows * D, dtype=torch.int16, device="cuda")
+    d_src, d_ones, d_perm = to_dev(src), to_dev(ones), to_dev(perm)
+    tf_ctx.check(tf_ctx.lib.tf_ep_combine(tf_ctx.handle, st, d_src.data_ptr(), d_ones.data_ptr(), d_perm.data_ptr(),
+                                          None, D, out.data_ptr(), D, rows, 1, D))
+    torch.cuda.synchronize()
+    assert np.array_equal(from_dev(out, np.uint16).reshape(rows, D), src[perm])
+    # the token-major reduce with one rank of weight 1.0 and fp16 partials rounds each value through fp32 and back
+    out2 = torch.zeros(rows * D, dtype=torch.int16, device="cuda")
+    tf_ctx.check(tf_ctx.lib.tf_moe_reduce_token_major(tf_ctx.handle, st, d_src.data_ptr(), 0, d_ones.data_ptr(), None, D,
+                                                      out2.data_ptr(), D, rows, 1, D))
+    torch.cuda.synchronize()
+    assert np.array_equal(from_dev(out2, np.uint16).reshape(rows, D), src)
+
+
 @pytest.mark.parametrize("T,fixed", [(1, True), (6, True), (70, False), (300, False)])   # 300 x 8 rows: tensor-core expert phase
 def test_single_rank_ep_stack_matches_fused_stack(tf_ctx, oracle, T, fixed):
     import torch

@@ -347,7 +347,7 @@ tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer
     if (layer->shared_bits == 8)
         s = tf_shared_expert_int8_block(ctx, ctx->side_stream, x, 0, x_stride_elements, &layer->shared_gate, &layer->shared_up,
                                         &layer->shared_down, ws->shared_y, 0, d, ws->shared_act, tokens);
-    else if (tensor_path)
+    else if (tensor_path || (tokens >= ctx->shared_tensorcore_min_tokens && d % 64 == 0 && layer->fs % 64 == 0))
         s = tf_shared_expert_int4_tensorcore(ctx, ctx->side_stream, x, x_stride_elements, &layer->shared_gate, &layer->shared_up,
                                              &layer->shared_down, ws->shared_y, d, ws->shared_act, tokens);
     else

@@ -131,6 +131,12 @@ tf_status tf_context_set_tensorcore_min_tokens(tf_context* ctx, uint32_t tokens)
     return TF_OK;
 }
 
+tf_status tf_context_set_shared_tensorcore_min_tokens(tf_context* ctx, uint32_t tokens) {
+    TF_REQUIRE(ctx, ctx != nullptr && tokens > 0, TF_ERR_INVALID_ARGUMENT, "tf_context_set_shared_tensorcore_min_tokens: ctx is NULL or tokens is 0");
+    ctx->shared_tensorcore_min_tokens = tokens;
+    return TF_OK;
+}
+
 tf_status tf_context_set_single_launch_step(tf_context* ctx, int enabled) {
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_context_set_single_launch_step: ctx is NULL");
     ctx->single_launch_step = enabled != 0;

@@ -95,8 +95,9 @@ __global__ void ep_combine_kernel(const uint16_t* __restrict__ rows, const uint1
                                   const uint32_t* __restrict__ inverse_perm, const uint16_t* __restrict__ residual,
                                   uint32_t residual_stride, uint16_t* __restrict__ out, uint32_t out_stride,
                                   uint32_t T, uint32_t K, uint32_t D) {
-    const uint32_t d = blockIdx.x * blockDim.x + threadIdx.x;
-    const uint32_t t = blockIdx.y;
+    // rows in grid.x (up to 2^31 - 1 blocks), column blocks in grid.y: an expert-parallel rank can hold more than 65535 rows
+    const uint32_t d = blockIdx.y * blockDim.x + threadIdx.x;
+    const uint32_t t = blockIdx.x;
     if (d >= D || t >= T) return;
     float acc = 0.0f;
     for (uint32_t r = 0; r < K; ++r) {
@@ -175,7 +176,7 @@ tf_status tf_ep_combine(tf_context* ctx, void* stream, const void* returned_rows
     TF_REQUIRE(ctx, returned_rows && route_weights && inverse_perm && out, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
     TF_REQUIRE(ctx, top_k > 0 && d > 0 && out_stride_elements >= d, TF_ERR_INVALID_ARGUMENT, "%s: bad dimensions", name);
     if (query_count == 0) return TF_OK;
-    dim3 grid((d + 255) / 256, query_count);
+    dim3 grid(query_count, (d + 255) / 256);
     tf::ep_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(returned_rows), static_cast<const uint16_t*>(route_weights), inverse_perm,
         static_cast<const uint16_t*>(residual), residual_stride_elements, static_cast<uint16_t*>(out), out_stride_elements,

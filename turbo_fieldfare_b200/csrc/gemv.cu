@@ -324,6 +324,7 @@ tf_status tf_shared_expert_int8_block(tf_context* ctx, void* stream, const void*
     static tf::DeviceSmemCache c1, c2;
     if (smem1 > 48 * 1024) if (tf_status s = tf::ensure_dynamic_smem(ctx, tf::shared_int8_gate_up_act_kernel, c1, smem1)) return s;
     if (smem2 > 48 * 1024) if (tf_status s = tf::ensure_dynamic_smem(ctx, tf::int8_gemv_rows_kernel, c2, smem2)) return s;
+    TF_REQUIRE(ctx, rows <= 65535u, TF_ERR_UNSUPPORTED, "%s: at most 65535 rows per call", name);
     const uint32_t per_row_blocks = rows >= 64 ? 8u : (uint32_t)ctx->sm_count * 2u;       // a block keeps its token's activations staged
     auto blocks = [&](uint32_t m) { const uint32_t need = (m + tf::kGemvWarps - 1) / tf::kGemvWarps; return need < per_row_blocks ? need : per_row_blocks; };
     uint16_t* act = static_cast<uint16_t*>(scratch_act);

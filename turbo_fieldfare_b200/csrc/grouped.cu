@@ -659,8 +659,8 @@ __global__ void reduce_token_major_kernel(const void* __restrict__ partials, con
                                           const uint16_t* __restrict__ residual, uint32_t residual_stride,
                                           uint16_t* __restrict__ out, uint32_t out_stride,
                                           uint32_t T, uint32_t K, uint32_t D) {
-    const uint32_t d = blockIdx.x * blockDim.x + threadIdx.x;
-    const uint32_t t = blockIdx.y;
+    const uint32_t d = blockIdx.y * blockDim.x + threadIdx.x;      // rows in grid.x: no 65535 limit on the token count
+    const uint32_t t = blockIdx.x;
     pdl_launch_dependents();
     pdl_wait();
     if (d >= D || t >= T) return;
@@ -993,7 +993,7 @@ tf_status tf_moe_reduce_token_major(tf_context* ctx, void* stream, const void* r
     TF_REQUIRE(ctx, route_partials && route_weights && h2, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
     TF_REQUIRE(ctx, top_k > 0 && d > 0 && h2_stride_elements >= d, TF_ERR_INVALID_ARGUMENT, "%s: bad dimensions", name);
     if (query_count == 0) return TF_OK;
-    dim3 grid((d + 255) / 256, query_count);
+    dim3 grid(query_count, (d + 255) / 256);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (partials_f32)
         tf::launch_pdl(tf::reduce_token_major_kernel<true>, grid, dim3(256), 0, st, route_partials, static_cast<const uint16_t*>(route_weights),

@@ -71,6 +71,10 @@ class TurboContext:
         """Blocks of at least ``tokens`` tokens run their expert GEMMs on the tensor cores (default 256)."""
         self.check(self.lib.tf_context_set_tensorcore_min_tokens(self.handle, tokens))
 
+    def set_shared_tensorcore_min_tokens(self, tokens: int) -> None:
+        """The same threshold for a block's shared expert alone (default 32)."""
+        self.check(self.lib.tf_context_set_shared_tensorcore_min_tokens(self.handle, tokens))
+
     def set_single_launch_step(self, enabled: bool) -> None:
         """One-token stack steps as one persistent launch (True) or layer by layer (False)."""
         self.check(self.lib.tf_context_set_single_launch_step(self.handle, 1 if enabled else 0))
