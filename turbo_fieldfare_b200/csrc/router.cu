@@ -493,13 +493,14 @@ router_block_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
                          out_w + (size_t)row * top_k, lane);
 }
 
-// Prefill-sized batches: one block per eight rows. Same canonical arithmetic per (row, expert) as router_row_logit,
-// but an expert's codes, scale and bias are fetched once per group for eight token rows instead of once per row, and
-// a group's activations are read once for two experts: the eight rows' scaled activations sit in shared memory as
-// fp32 and every lane carries sixteen accumulators.
-constexpr int kTileRouterRows = 8;
-template <bool X_BF16>
-__global__ void __launch_bounds__(kBlockRouterThreads)
+// Prefill-sized batches: one block per R token rows (R = 6, 7 or 8, picked by the host so that the row tiles fill whole
+// rounds of the resident blocks). Same canonical arithmetic per (row, expert) as router_row_logit, but an expert's codes,
+// scale and bias are decoded once per group for R rows, and a group's activations are read from shared memory once for
+// four experts: the rows' scaled activations sit in shared memory as fp32 and every lane carries 4 R accumulators.
+constexpr int kTileRouterRows = 8;          // most rows per block (sizes the shared memory)
+constexpr int kTileExperts = 4;             // experts per warp iteration
+template <bool X_BF16, int R>
+__global__ void __launch_bounds__(kBlockRouterThreads, 2)
 router_tile_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S, const uint16_t* __restrict__ B,
                    const uint16_t* __restrict__ hidden, uint32_t hidden_stride,
                    const uint16_t* __restrict__ eff, const uint16_t* __restrict__ per_expert_scale,
@@ -507,16 +508,16 @@ router_tile_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S
                    uint32_t* __restrict__ out_idx, uint16_t* __restrict__ out_w, float* __restrict__ out_logits,
                    uint32_t rows, uint32_t num_experts, uint32_t d, uint32_t top_k) {
     extern __shared__ __align__(16) uint8_t smem[];
-    float* xf = reinterpret_cast<float*>(smem);                                   // [8][d]
-    float* scores = xf + (size_t)kTileRouterRows * d;                             // [8][num_experts]
-    const uint32_t row0 = blockIdx.x * kTileRouterRows;
-    const uint32_t nrows = rows - row0 < (uint32_t)kTileRouterRows ? rows - row0 : (uint32_t)kTileRouterRows;
+    float* xf = reinterpret_cast<float*>(smem);                                   // [R][d]
+    float* scores = xf + (size_t)R * d;                                           // [R][num_experts]
+    const uint32_t row0 = blockIdx.x * R;
+    const uint32_t nrows = rows - row0 < (uint32_t)R ? rows - row0 : (uint32_t)R;
     pdl_launch_dependents();
     pdl_wait();
     for (uint32_t c = threadIdx.x; c < d; c += blockDim.x) {
         const float es = bf16_bits_to_float(eff[c]);
 #pragma unroll
-        for (int r = 0; r < kTileRouterRows; ++r) {
+        for (int r = 0; r < R; ++r) {
             float v = 0.0f;
             if ((uint32_t)r < nrows) {
                 const uint16_t hb = hidden[(size_t)(row0 + r) * hidden_stride + c];
@@ -529,64 +530,92 @@ router_tile_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ S
     const int warp = threadIdx.x / kWarp, lane = threadIdx.x % kWarp;
     const uint32_t groups = d / kGroup;
     constexpr uint32_t kWarps = kBlockRouterThreads / kWarp;
-    // A warp takes two experts at a time (e and e + 8): the eight rows' activations of a group are read from shared
-    // memory once for both, and the next group's codes, scales and biases are already on their way while the current
-    // group is multiplied. Per (row, expert) the operations and their order are those of router_row_logit.
-    for (uint32_t e0 = warp; e0 < num_experts; e0 += 2 * kWarps) {
-        const uint32_t e1 = e0 + kWarps;
-        const bool two = e1 < num_experts;
-        const uint32_t ea = e0, eb = two ? e1 : e0;
-        const uint8_t* Wa = W + (size_t)ea * d + lane * 2;
-        const uint8_t* Wb = W + (size_t)eb * d + lane * 2;
-        const uint16_t* sa = S + (size_t)ea * groups; const uint16_t* ba = B + (size_t)ea * groups;
-        const uint16_t* sb = S + (size_t)eb * groups; const uint16_t* bb = B + (size_t)eb * groups;
-        float acc_a[kTileRouterRows], acc_b[kTileRouterRows];
+    // A warp takes four experts at a time (e, e + 8, e + 16, e + 24); experts past the end repeat the first one and
+    // are not stored. The next group's codes, scales and biases are on their way while the current group is multiplied.
+    for (uint32_t e0 = warp; e0 < num_experts; e0 += kTileExperts * kWarps) {
+        uint32_t ex[kTileExperts];
+        const uint8_t* Wp[kTileExperts];
+        const uint16_t* sp[kTileExperts];
+        const uint16_t* bp[kTileExperts];
 #pragma unroll
-        for (int r = 0; r < kTileRouterRows; ++r) { acc_a[r] = 0.0f; acc_b[r] = 0.0f; }
-        uint32_t wa = *reinterpret_cast<const uint16_t*>(Wa), wb = *reinterpret_cast<const uint16_t*>(Wb);   // d % 64 == 0, 2-byte aligned rows
-        uint16_t nsa = sa[0], nba = ba[0], nsb = sb[0], nbb = bb[0];
+        for (int j = 0; j < kTileExperts; ++j) {
+            const uint32_t e = e0 + j * kWarps;
+            ex[j] = e < num_experts ? e : e0;
+            Wp[j] = W + (size_t)ex[j] * d + lane * 2;
+            sp[j] = S + (size_t)ex[j] * groups;
+            bp[j] = B + (size_t)ex[j] * groups;
+        }
+        float acc[kTileExperts][R];
+        uint32_t wn[kTileExperts];
+        uint16_t sn[kTileExperts], bn[kTileExperts];
+#pragma unroll
+        for (int j = 0; j < kTileExperts; ++j) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[j][r] = 0.0f;
+            wn[j] = *reinterpret_cast<const uint16_t*>(Wp[j]);          // d % 64 == 0, 2-byte aligned rows
+            sn[j] = sp[j][0]; bn[j] = bp[j][0];
+        }
         for (uint32_t g = 0; g < groups; ++g) {
-            const uint32_t cwa = wa, cwb = wb;
-            const float sca = bf16_bits_to_float(nsa), bia = bf16_bits_to_float(nba);
-            const float scb = bf16_bits_to_float(nsb), bib = bf16_bits_to_float(nbb);
-            if (g + 1 < groups) {
-                wa = *reinterpret_cast<const uint16_t*>(Wa + (g + 1) * kGroup);
-                wb = *reinterpret_cast<const uint16_t*>(Wb + (g + 1) * kGroup);
-                nsa = sa[g + 1]; nba = ba[g + 1]; nsb = sb[g + 1]; nbb = bb[g + 1];
-            }
-            const float qa0 = (float)(cwa & 0xFFu), qa1 = (float)(cwa >> 8);
-            const float qb0 = (float)(cwb & 0xFFu), qb1 = (float)(cwb >> 8);
-            const uint32_t i0 = g * kGroup + lane * 2;
+            float q0[kTileExperts], q1[kTileExperts], sc[kTileExperts], bi[kTileExperts];
 #pragma unroll
-            for (int r = 0; r < kTileRouterRows; ++r) {
-                const float2 xv = *reinterpret_cast<const float2*>(xf + (size_t)r * d + i0);
+            for (int j = 0; j < kTileExperts; ++j) {
+                // byte -> float through the 2^23 mantissa trick (exact for 0...255)
+                q0[j] = __uint_as_float(0x4B000000u | (wn[j] & 0xFFu)) - 8388608.0f;
+                q1[j] = __uint_as_float(0x4B000000u | (wn[j] >> 8)) - 8388608.0f;
+                sc[j] = bf16_bits_to_float(sn[j]);
+                bi[j] = bf16_bits_to_float(bn[j]);
+            }
+            if (g + 1 < groups) {
+#pragma unroll
+                for (int j = 0; j < kTileExperts; ++j) {
+                    wn[j] = *reinterpret_cast<const uint16_t*>(Wp[j] + (g + 1) * kGroup);
+                    sn[j] = sp[j][g + 1]; bn[j] = bp[j][g + 1];
+                }
+            }
+            const float* xg = xf + g * kGroup + lane * 2;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const float2 xv = *reinterpret_cast<const float2*>(xg + (size_t)r * d);
                 const float xs = __fadd_rn(xv.x, xv.y);
-                const float pa = __fmaf_rn(qa1, xv.y, __fmul_rn(qa0, xv.x));
-                acc_a[r] = __fmaf_rn(sca, pa, acc_a[r]);
-                acc_a[r] = __fmaf_rn(bia, xs, acc_a[r]);
-                const float pb = __fmaf_rn(qb1, xv.y, __fmul_rn(qb0, xv.x));
-                acc_b[r] = __fmaf_rn(scb, pb, acc_b[r]);
-                acc_b[r] = __fmaf_rn(bib, xs, acc_b[r]);
+#pragma unroll
+                for (int j = 0; j < kTileExperts; ++j) {
+                    const float p = __fmaf_rn(q1[j], xv.y, __fmul_rn(q0[j], xv.x));
+                    acc[j][r] = __fmaf_rn(sc[j], p, acc[j][r]);
+                    acc[j][r] = __fmaf_rn(bi[j], xs, acc[j][r]);
+                }
             }
         }
 #pragma unroll
-        for (int r = 0; r < kTileRouterRows; ++r) {
-            float la = warp_sum(acc_a[r]), lb = warp_sum(acc_b[r]);
-            if (logit_bias) { la = __fadd_rn(la, logit_bias[ea]); lb = __fadd_rn(lb, logit_bias[eb]); }
-            if (lane == 0 && (uint32_t)r < nrows) {
-                scores[r * num_experts + ea] = la;
-                if (out_logits) out_logits[(size_t)(row0 + r) * num_experts + ea] = la;
-                if (two) {
-                    scores[r * num_experts + eb] = lb;
-                    if (out_logits) out_logits[(size_t)(row0 + r) * num_experts + eb] = lb;
+        for (int j = 0; j < kTileExperts; ++j) {
+            const bool live = e0 + j * kWarps < num_experts;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                float l = warp_sum(acc[j][r]);
+                if (logit_bias) l = __fadd_rn(l, logit_bias[ex[j]]);
+                if (lane == 0 && live && (uint32_t)r < nrows) {
+                    scores[r * num_experts + ex[j]] = l;
+                    if (out_logits) out_logits[(size_t)(row0 + r) * num_experts + ex[j]] = l;
                 }
             }
         }
     }
     __syncthreads();
-    if ((uint32_t)warp < nrows)          // eight warps, eight rows
+    if ((uint32_t)warp < nrows)          // eight warps, at most eight rows
         warp_select_topk(scores + warp * num_experts, num_experts, top_k, per_expert_scale, out_idx + (size_t)(row0 + warp) * top_k,
                          out_w + (size_t)(row0 + warp) * top_k, lane);
+}
+
+// Rows per block of router_tile_kernel: the R in 6...8 whose tiles leave the fewest idle block slots in the last round
+// (rounds x R is the time in units of one row's work).
+static int tile_router_rows(uint32_t rows, uint32_t slots) {
+    int best = kTileRouterRows;
+    uint64_t best_cost = ~0ull;
+    for (int r = kTileRouterRows; r >= 6; --r) {
+        const uint32_t tiles = (rows + r - 1) / r;
+        const uint64_t cost = (uint64_t)((tiles + slots - 1) / slots) * r;
+        if (cost < best_cost) { best_cost = cost; best = r; }
+    }
+    return best;
 }
 
 static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, const uint8_t* S, const uint8_t* B,
@@ -649,11 +678,16 @@ static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, 
                    ctx->router_logits, ctx->router_tickets, grp, num_experts, d, top_k, a2);
         return check_launch(ctx, name);
     } else if (rows >= 256 && a2 && (size_t)kTileRouterRows * (d + num_experts) * 4 <= 100 * 1024) {
-        auto k = bf ? router_tile_kernel<true> : router_tile_kernel<false>;
-        const size_t smem_tile = (size_t)kTileRouterRows * (d + num_experts) * 4;
-        static DeviceSmemCache configured[2];
-        if (tf_status s = ensure_dynamic_smem(ctx, k, configured[bf ? 1 : 0], smem_tile)) return s;
-        launch_pdl(k, dim3((rows + kTileRouterRows - 1) / kTileRouterRows), dim3(kBlockRouterThreads), smem_tile, st, W, Sp, Bp, hp, stride,
+        const int R = tile_router_rows(rows, (uint32_t)ctx->sm_count * 2u);
+        void (*k)(const uint8_t*, const uint16_t*, const uint16_t*, const uint16_t*, uint32_t, const uint16_t*, const uint16_t*, const float*,
+                  uint32_t*, uint16_t*, float*, uint32_t, uint32_t, uint32_t, uint32_t);
+        if (R == 6) k = bf ? router_tile_kernel<true, 6> : router_tile_kernel<false, 6>;
+        else if (R == 7) k = bf ? router_tile_kernel<true, 7> : router_tile_kernel<false, 7>;
+        else k = bf ? router_tile_kernel<true, 8> : router_tile_kernel<false, 8>;
+        const size_t smem_tile = (size_t)R * (d + num_experts) * 4;
+        static DeviceSmemCache configured[2][3];
+        if (tf_status s = ensure_dynamic_smem(ctx, k, configured[bf ? 1 : 0][R - 6], smem_tile)) return s;
+        launch_pdl(k, dim3((rows + R - 1) / R), dim3(kBlockRouterThreads), smem_tile, st, W, Sp, Bp, hp, stride,
                    ep, pp, logit_bias, out_idx, wp, out_logits, rows, num_experts, d, top_k);
     } else {
         auto k = bf ? router_block_kernel<true> : router_block_kernel<false>;

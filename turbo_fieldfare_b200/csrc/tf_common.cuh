@@ -63,7 +63,7 @@ struct tf_context {
     // Block forwards of at least this many tokens run their expert GEMMs on the tcgen05 tensor cores.
     uint32_t tensorcore_min_tokens = 256;
     // The same for the shared expert alone (a dense GEMM over all tokens of the block).
-    uint32_t shared_tensorcore_min_tokens = 32;
+    uint32_t shared_tensorcore_min_tokens = 256;
     // Scratch of the greedy LM head, like the normed-row and row-summary buffers the reference's wrapper owns
     // (Kernels/Fusions/LMHeadChainInt4.swift:26-51); grown on demand by tf_lm_head_greedy_int4.
     uint16_t* lm_x = nullptr;               // fp16 [lm_x_capacity]

@@ -72,7 +72,7 @@ class TurboContext:
         self.check(self.lib.tf_context_set_tensorcore_min_tokens(self.handle, tokens))
 
     def set_shared_tensorcore_min_tokens(self, tokens: int) -> None:
-        """The same threshold for a block's shared expert alone (default 32)."""
+        """The same threshold for a block's shared expert alone (default 256)."""
         self.check(self.lib.tf_context_set_shared_tensorcore_min_tokens(self.handle, tokens))
 
     def set_single_launch_step(self, enabled: bool) -> None:
