@@ -144,6 +144,7 @@ __host__ __device__ constexpr uint32_t ring_stages() { return (NMAT == 1 && KC >
 constexpr int kReducers = 2;            // reducer warps; reducer q owns the items and the partial buffer of parity q
 constexpr int kRedStages = kReducers;   // partial-sum buffers
 constexpr int kTileRows = 16;           // weight rows per MMA tile (the m of m16n8k16)
+constexpr int kRowsPerCopy = 2;         // rows per bulk copy when the rows need padding against bank conflicts (divides 8)
 constexpr int kMaxComputeWarps = 12;    // K <= 12 * 256 = 3072 columns
 constexpr uint32_t kErrTimeoutCodes = 0x7F000001u;   // device error words
 constexpr uint32_t kErrTimeoutPartials = 0x7F000003u;
@@ -242,8 +243,14 @@ __host__ __device__ inline uint32_t ring_row_stride(uint32_t row_bytes) {
 template <int NMAT>
 struct KSplitSmem {
     uint32_t cw, ng, row_bytes, stages;
-    __host__ __device__ uint32_t row_stride() const { return ring_row_stride(row_bytes); }
-    __host__ __device__ uint32_t mat_bytes() const { return kTileRows * row_stride(); }
+    // Rows whose natural stride would put a half warp's four rows on the same banks get 32 bytes of padding per
+    // kRowsPerCopy rows: the loader moves kRowsPerCopy rows per bulk copy (a copy has a fixed cost of some tens of cycles
+    // in the copy engine, and sixteen single-row copies per matrix kept the compute warps waiting for a third of an
+    // item's time), at the price of a two-way bank conflict between the rows of a pair.
+    __host__ __device__ uint32_t row_pad() const { return ring_row_stride(row_bytes) - row_bytes; }
+    __host__ __device__ uint32_t rows_per_copy() const { return row_pad() ? (uint32_t)kRowsPerCopy : (uint32_t)kTileRows; }
+    __host__ __device__ uint32_t row_off(uint32_t r) const { return r * row_bytes + (r / rows_per_copy()) * row_pad(); }
+    __host__ __device__ uint32_t mat_bytes() const { return kTileRows * row_bytes + (kTileRows / rows_per_copy()) * row_pad(); }
     __host__ __device__ uint32_t sb_plane_bytes() const { return kTileRows * ng * 2; }                            // multiple of 16
     __host__ __device__ uint32_t stage_bytes() const { return NMAT * mat_bytes() + NMAT * 2 * sb_plane_bytes(); } // codes, then scales
     __host__ __device__ uint32_t off_sb_in_stage() const { return NMAT * mat_bytes(); }
@@ -349,8 +356,8 @@ grouped_ksplit_kernel(const GroupedArgs args) {
         const uint32_t ngw = ng - g0 < (uint32_t)kGPW ? ng - g0 : (uint32_t)kGPW;     // g0 < ng by construction
         const bool sb_vec = (ng % 4) == 0;
         const uint32_t sb_row0 = (g * ng + g0) * 2, sb_row1 = ((g + 8) * ng + g0) * 2;     // scale rows of weight rows g, g + 8
-        const uint32_t lane_code_off = g * lay.row_stride() + g0 * 32 + t * 8;          // this lane's codes of row g within a matrix tile
-        const uint32_t row8_off = 8 * lay.row_stride();                                 // row g + 8
+        const uint32_t lane_code_off = lay.row_off(g) + g0 * 32 + t * 8;                // this lane's codes of row g within a matrix tile
+        const uint32_t row8_off = lay.row_off(g + 8) - lay.row_off(g);                   // row g + 8
 
         ItemCursor<NMAT> cur;
         cur.chunk = item_begin / tiles;
@@ -501,6 +508,7 @@ grouped_ksplit_kernel(const GroupedArgs args) {
             // hand the partial sums to the reducer
             const uint32_t r = li % kRedStages, ruse = li / kRedStages;
             if (!mbar_wait(bar_red_free(r), (ruse & 1) ^ 1)) { fail = kErrTimeoutRedFree; break; }
+
             const uint32_t red_w = red_base + r * lay.red_stage_bytes() + (warp * NMAT) * 512 + (g * 8 + 2 * t) * 4;
 #pragma unroll
             for (int m = 0; m < NMAT; ++m) {
@@ -519,7 +527,7 @@ grouped_ksplit_kernel(const GroupedArgs args) {
         iss.tile = item_begin % tiles;
         resolve_chunk<NMAT, DENSE>(args, iss);
         const uint32_t plane_bytes = lay.sb_plane_bytes();
-        const bool contiguous = lay.row_stride() == row_bytes;       // the 8 rows of a tile land as one copy
+        const uint32_t rpc = lay.rows_per_copy();                    // 16: the rows of a tile land as one copy
         const uint32_t tx_bytes = NMAT * kTileRows * row_bytes + NMAT * 2 * plane_bytes;
         uint32_t fail = 0, issued = 0;
         uint32_t st = 0, use = 0;
@@ -532,19 +540,11 @@ grouped_ksplit_kernel(const GroupedArgs args) {
                 mbar_arrive_expect_tx(mbar, tx_bytes);
             }
             __syncwarp();
-            if (contiguous) {
-                if (lane < NMAT) {
-                    const MatPlanes& mp = lane ? iss.pl[NMAT - 1] : iss.pl[0];
-                    bulk_copy_g2s(stage + lane * lay.mat_bytes(), mp.W + (size_t)iss.tile * kTileRows * row_bytes,
-                                  kTileRows * row_bytes, mbar);
-                }
-            } else {
-                for (uint32_t j = lane; j < (uint32_t)(NMAT * kTileRows); j += kWarp) {
-                    const uint32_t m = j / kTileRows, r = j % kTileRows;
-                    const MatPlanes& mp = m ? iss.pl[NMAT - 1] : iss.pl[0];
-                    bulk_copy_g2s(stage + m * lay.mat_bytes() + r * lay.row_stride(),
-                                  mp.W + (size_t)(iss.tile * kTileRows + r) * row_bytes, row_bytes, mbar);
-                }
+            for (uint32_t j = lane; j < (uint32_t)(NMAT * kTileRows) / rpc; j += kWarp) {
+                const uint32_t per_mat = kTileRows / rpc, m = j / per_mat, r = (j % per_mat) * rpc;
+                const MatPlanes& mp = m ? iss.pl[NMAT - 1] : iss.pl[0];
+                bulk_copy_g2s(stage + m * lay.mat_bytes() + lay.row_off(r),
+                              mp.W + (size_t)(iss.tile * kTileRows + r) * row_bytes, rpc * row_bytes, mbar);
             }
             if (lane < NMAT * 2) {
                 const uint32_t m = lane >> 1, which = lane & 1;
