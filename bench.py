@@ -602,6 +602,66 @@ def case_block(args) -> None:
           f"status={ctx.device_status()} ms_per_forward={[round(t, 3) for t in times]}")
 
 
+def case_ep_block(args) -> None:
+    """The expert-parallel layer loop with ONE rank (the rank exchanges with itself over its own peer buffer): the same
+    launches per layer as at N > 1, on one GPU, so that a profiler may list them."""
+    import torch
+    from turbo_fieldfare_b200.ep import ExpertParallelStack
+    from turbo_fieldfare_b200.kernels import TurboContext
+    ctx = TurboContext(0)
+    stack = ExpertParallelStack(ctx, layers=args.layers, seed=3)
+    fixed = args.tokens <= 64
+    buf = stack.buffers(args.tokens, fixed, peer=fixed)
+    h = torch.randn(args.tokens, 2816, device="cuda").half()
+    for _ in range(args.case_warm):
+        stack.forward(h, args.tokens, buf)
+    times = []
+    for _ in range(args.iters):
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        stack.forward(h, args.tokens, buf)
+        t1.record()
+        torch.cuda.synchronize()
+        times.append(t0.elapsed_time(t1))
+    print(f"ep-block case done: tokens={args.tokens} layers={args.layers} iters={args.iters} launches={ctx.launch_count} "
+          f"status={ctx.device_status()} ms_per_forward={[round(t, 3) for t in times]}")
+
+
+def case_step(args) -> None:
+    """The one-launch form of a one-token step with its global-timer trace: nanoseconds per phase and layer."""
+    import torch
+    from turbo_fieldfare_b200.kernels import TurboContext
+    from turbo_fieldfare_b200.stack import MoEStack
+    layers = args.layers
+    ctx = TurboContext(0)
+    stack = MoEStack(ctx, layers=layers, seed=3)
+    ctx.set_single_launch_step(True)
+    ws = stack.workspace(1)
+    h = torch.randn(1, 2816, device="cuda").half()
+    trace = torch.zeros(8 * layers + 28, dtype=torch.int64, device="cuda")
+    ctx.check(ctx.lib.tf_context_set_step_trace(ctx.handle, trace.data_ptr(), trace.numel()))
+    for _ in range(max(args.case_warm, 1) + 1):
+        stack.forward(h, 1, ws)
+    torch.cuda.synchronize()
+    raw = trace.cpu().numpy()
+    stamps = raw[:8 * layers].reshape(layers, 8)
+    names = ["norm", "router+shared gate/up", "barrier 1", "top-k+routed gate/up", "barrier 2", "down+combine", "barrier 3"]
+    mean = np.diff(stamps, axis=1)[1:].mean(axis=0) if layers > 1 else np.diff(stamps, axis=1)[0]
+    print("ns per layer:", ", ".join(f"{n}={v:.0f}" for n, v in zip(names, mean)), f"layer={mean.sum():.0f}")
+    ctx.check(ctx.lib.tf_context_set_step_trace(ctx.handle, None, 0))
+    for single in (True, False):
+        ctx.set_single_launch_step(single)
+        stack.forward(h, 1, ws)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(args.iters):
+            stack.forward(h, 1, ws)
+        t1.record()
+        torch.cuda.synchronize()
+        print(f"{'one launch' if single else 'layered (eager launches)'}: {t0.elapsed_time(t1) / args.iters * 1e3 / layers:.2f} us per layer")
+    print(f"step case done: layers={layers} status={ctx.device_status()}")
+
+
 def case_gemv(args) -> None:
     import torch
     from turbo_fieldfare_b200.kernels import DequantInt4GEMV, TurboContext
@@ -706,7 +766,7 @@ def case_gemv_sweep(args) -> None:
     print("gemv-sweep case done:", json.dumps(measure_gemv_sweep(torch, ctx, st, 6555.8, "MEASURED_PEAKS.json hbm_gbs at the time of writing")))
 
 
-CASES = {"block": case_block, "gemv": case_gemv, "gemv-sweep": case_gemv_sweep, "qmm": case_qmm, "lmhead": case_lmhead}
+CASES = {"block": case_block, "ep-block": case_ep_block, "step": case_step, "gemv": case_gemv, "gemv-sweep": case_gemv_sweep, "qmm": case_qmm, "lmhead": case_lmhead}
 
 
 def main():
@@ -723,7 +783,7 @@ def main():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
                     help="decode exchange at N > 1: kernels over peer memory (default) or NCCL all-to-all")
-    ap.add_argument("--case", default=None, choices=["block", "gemv", "gemv-sweep", "qmm", "lmhead"],
+    ap.add_argument("--case", default=None, choices=["block", "ep-block", "step", "gemv", "gemv-sweep", "qmm", "lmhead"],
                     help="run one small single-kernel case instead of the benchmark (for profiler captures)")
     ap.add_argument("--tokens", type=int, default=64, help="--case block / qmm: token rows")
     ap.add_argument("--rows", type=int, default=262144, help="--case gemv / qmm / lmhead: weight rows")
@@ -744,7 +804,7 @@ def main():
         print(f"note: warmup {args.warmup} < 3 breaks the timing rules; use it for smoke runs only", file=sys.stderr)
     try:
         if args.case:
-            if args.case == "block" and args.layers == LAYERS:
+            if args.case in ("block", "ep-block", "step") and args.layers == LAYERS:
                 args.layers = 2
             CASES[args.case](args)
         elif args.impl == "reference":
