@@ -675,6 +675,16 @@ tf_status tf_ep_peer_push(tf_context* ctx, void* stream, const void* src_rows, u
                           uint32_t copy_elements, const uint32_t* slot_ids, uint32_t tail_at_element,
                           uint32_t world, uint32_t rank, uint32_t capacity,
                           uint64_t flags_offset_bytes, uint32_t* epoch_and_ticket_device);
+/* tf_ep_pack + tf_ep_peer_push in one launch, for a block whose routes are already grouped (tf_router_gemma4_block_grouped):
+ * the row of pair p goes from hidden[token] straight into its owner's buffer at dst_offset_bytes +
+ * ((rank * capacity + position) * dst_stride_elements) * 2, with the local expert id in the 16-byte tail at element d;
+ * unused slots get an empty tail; inverse_perm[token * top_k + r] = owner * capacity + position. Ends with the flag
+ * barrier like tf_ep_peer_push. */
+tf_status tf_ep_pack_push(tf_context* ctx, void* stream, const void* hidden, uint32_t hidden_stride_elements,
+                          const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                          uint32_t experts_per_rank, uint32_t d, const void* const* peer_bases_device, uint64_t dst_offset_bytes,
+                          uint32_t dst_stride_elements, uint32_t* inverse_perm, uint32_t world, uint32_t rank, uint32_t capacity,
+                          uint64_t flags_offset_bytes, uint32_t* epoch_and_ticket_device);
 /* flags: `world` 32-bit words at flags_offset_bytes of every buffer; epoch_counter_device: one zero-initialised word
  * of this rank, advanced by the kernel. */
 tf_status tf_ep_peer_barrier(tf_context* ctx, void* stream, const void* const* peer_bases_device, uint64_t flags_offset_bytes,

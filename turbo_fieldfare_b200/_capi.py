@@ -190,6 +190,7 @@ SIGNATURES = {
     "tf_peer_buffer_release": (C.c_int, [vp, vp]),
     "tf_ep_peer_push": (C.c_int, [vp, vp, vp, u32, vp, u64, u32, u32, vp, u32, u32, u32, u32, u64, vp]),
     "tf_ep_peer_barrier": (C.c_int, [vp, vp, vp, u64, vp, u32, u32]),
+    "tf_ep_pack_push": (C.c_int, [vp, vp, vp, u32, vp, u32, u32, u32, u32, u32, vp, u64, u32, vp, u32, u32, u32, u64, vp]),
     "tf_lm_head_greedy_int4": (C.c_int, [vp, vp, vp, u64, vp, u64, *_PLANES, vp, u32, u32, f32]),
     "tf_post_attn_setup": (C.c_int, [vp, vp, vp, u32, vp, u32, vp, u32, vp, u32, vp, u32, vp, vp, vp, u32, u32, f32]),
     "tf_layer_tail": (C.c_int, [vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, f32, f32]),

@@ -419,13 +419,16 @@ tf_status tf_ep_experts(tf_context* ctx, void* stream, const void* pool_layer_ba
     if (recv_slots == 0) return TF_OK;
     const uint32_t stride = recv_row_stride_elements ? recv_row_stride_elements : d;
     tf_status s;
-    if (stride > d) {
-        // the rows carry their expert id in the tail: recv_expert_ids is filled here instead of by a second exchange
-        s = tf_ep_extract_ids(ctx, stream, recv_rows, stride, d, recv_slots, const_cast<uint32_t*>(recv_expert_ids));
-        if (s) return s;
-    }
     // every received row is one (token = slot, rank 0) pair of a local expert; empty slots carry UINT32_MAX
-    s = tf_group_routes_device(ctx, stream, recv_expert_ids, zero_weights, recv_slots, 1, local_experts, recv_routes);
+    if (stride > d) {
+        // the rows carry their expert id in the tail: the grouping reads it there (no second exchange, no extra launch)
+        // and fills recv_expert_ids on the way
+        TF_REQUIRE(ctx, d % 2 == 0 && stride % 2 == 0 && tf::aligned(recv_rows, 4), TF_ERR_ALIGNMENT, "%s: rows must be 4-byte aligned", name);
+        s = tf::group_routes_strided(ctx, stream, reinterpret_cast<const uint32_t*>(static_cast<const uint16_t*>(recv_rows) + d), stride / 2,
+                                     const_cast<uint32_t*>(recv_expert_ids), zero_weights, recv_slots, 1, local_experts, recv_routes, name);
+    } else {
+        s = tf_group_routes_device(ctx, stream, recv_expert_ids, zero_weights, recv_slots, 1, local_experts, recv_routes);
+    }
     if (s) return s;
     return tf_grouped_moe_batched(ctx, stream, recv_rows, 0, stride, pool_layer_base, expert_stride, offsets, recv_routes,
                                   acts_scratch, out_rows, 0, recv_slots, d, f, 1);

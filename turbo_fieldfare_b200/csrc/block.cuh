@@ -47,5 +47,9 @@ namespace tf {
 bool decode_step_eligible(const tf_stack* st, const tf_workspace* ws);
 tf_status decode_step_prepare(tf_context* ctx, tf_stack* st);
 tf_status launch_decode_step(tf_context* ctx, void* stream, tf_stack* st, void* hidden, tf_workspace* ws);
+// grouped.cu: tf_group_routes_device over ids read at a stride (and optionally written out densely)
+tf_status group_routes_strided(tf_context* ctx, void* stream, const uint32_t* indices, uint32_t idx_stride, uint32_t* ids_out,
+                               const void* weights_f16, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                               const tf_device_routes* routes, const char* name);
 }  // namespace tf
 

@@ -431,17 +431,24 @@ tf_status tf_moe_block_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* l
     auto bail = [&](tf_status code) { cudaStreamWaitEvent(st, ctx->join_event, 0); return code; };
     if (s) return bail(s);
 
-    s = tf_ep_dispatch(ctx, stream, layer, x, tokens, ws, le, cap, b->send_rows, b->send_ids, b->inverse, stride);
-    if (s) return bail(s);
     uint32_t recv_slots = 0;
     const uint16_t* recv_rows = nullptr; const uint32_t* recv_ids = b->recv_ids; const uint16_t* back = nullptr;
     if (peer) {
-        // rows (with their id tails) straight into the owners' receive areas; the launch ends with the flag barrier
+        // router + grouping over the global experts, then one launch that takes every pair's row from x straight into
+        // its owner's receive area (id in the row tail) and ends with the flag barrier
+        s = tf_router_gemma4_block_grouped(ctx, stream, layer->router.weights, layer->router.weights_off, layer->router.scales,
+                                           layer->router.scales_off, layer->router.biases, layer->router.biases_off, x, 0, TF_FP16,
+                                           layer->effective_scale, 0, layer->per_expert_scale, 0, layer->logit_bias, ws->indices,
+                                           ws->weights, tokens, b->num_experts, d, K, d, tf_workspace_routes(ws));
+        if (s) return bail(s);
         recv_slots = world * cap;
-        s = tf_ep_peer_push(ctx, stream, b->send_rows, stride, (const void* const*)b->peer_bases_dev, 0, stride, stride, nullptr, d,
-                            world, (uint32_t)ep->rank, cap, b->flags_offset, b->epoch);
+        s = tf_ep_pack_push(ctx, stream, x, d, tf_workspace_routes(ws), tokens, K, b->num_experts, le, d,
+                            (const void* const*)b->peer_bases_dev, 0, stride, b->inverse, world, (uint32_t)ep->rank, cap,
+                            b->flags_offset, b->epoch);
         if (s) return bail(s);
         recv_rows = b->recv_rows;
+    } else if ((s = tf_ep_dispatch(ctx, stream, layer, x, tokens, ws, le, cap, b->send_rows, b->send_ids, b->inverse, stride)) != TF_OK) {
+        return bail(s);
     } else if (fixed) {
         recv_slots = world * cap;
         if (world > 1) {

@@ -43,8 +43,8 @@ constexpr int kGroupPerThread = 4;
 
 // counters: [0] group count, [1] total chunks (sum over groups of ceil(count/8)), [2] pair count
 __global__ void __launch_bounds__(kGroupThreads)
-group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __restrict__ weights,
-                    uint32_t T, uint32_t K, uint32_t E,
+group_routes_kernel(const uint32_t* __restrict__ indices, uint32_t idx_stride, uint32_t* __restrict__ ids_out,
+                    const uint16_t* __restrict__ weights, uint32_t T, uint32_t K, uint32_t E,
                     tf_pair* __restrict__ sorted_pairs, uint32_t* __restrict__ per_expert_offsets,
                     uint32_t* __restrict__ per_expert_counts, tf_group* __restrict__ groups,
                     uint32_t* __restrict__ chunk_group, uint32_t* __restrict__ chunk_start,
@@ -59,7 +59,9 @@ group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __rest
     pdl_wait();
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        uint32_t ex = indices[i];
+        // idx_stride > 1: the ids sit in the tails of exchanged rows; the first block also writes them out densely
+        uint32_t ex = indices[(size_t)i * idx_stride];
+        if (ids_out && e == 0) ids_out[i] = ex;
         if (ex == 0xFFFFFFFFu) continue;    // empty slot of a fixed-capacity exchange buffer
         if (ex >= E) ex = E - 1;            // min(id, E-1): Runtime/Inference/RealForwardRunner.swift:955
         atomicAdd(&hist[ex], 1u);
@@ -100,7 +102,7 @@ group_routes_kernel(const uint32_t* __restrict__ indices, const uint16_t* __rest
         for (int j = 0; j < kGroupPerThread; ++j) {
             const uint32_t i = first + j;
             if (i < n) {
-                uint32_t ex = indices[i];
+                uint32_t ex = indices[(size_t)i * idx_stride];
                 if (ex != 0xFFFFFFFFu && ex >= E) ex = E - 1;
                 if (ex == e) { flags |= 1u << j; ++cnt; }
             }
@@ -788,10 +790,15 @@ static tf_status noalloc_device(NoAllocDevice** out, const char* name) {
 
 extern "C" {
 
-tf_status tf_group_routes_device(tf_context* ctx, void* stream, const uint32_t* indices, const void* weights_f16,
-                                 uint32_t query_count, uint32_t top_k, uint32_t num_experts,
-                                 const tf_device_routes* routes) {
-    const char* name = "tf_group_routes_device";
+}  // extern "C"
+
+namespace tf {
+
+// tf_group_routes_device with the ids read at a stride of `idx_stride` 32-bit words (the id tails of exchanged rows)
+// and, when ids_out is given, also written out densely.
+tf_status group_routes_strided(tf_context* ctx, void* stream, const uint32_t* indices, uint32_t idx_stride, uint32_t* ids_out,
+                               const void* weights_f16, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                               const tf_device_routes* routes, const char* name) {
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, indices && weights_f16 && routes, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
     TF_REQUIRE(ctx, routes->sorted_pairs && routes->per_expert_offsets && routes->per_expert_counts && routes->groups &&
@@ -801,11 +808,23 @@ tf_status tf_group_routes_device(tf_context* ctx, void* stream, const uint32_t* 
     TF_REQUIRE(ctx, num_experts > 0 && num_experts <= TF_MAX_ROUTER_EXPERTS, TF_ERR_GROUPING_INVALID_NUM_EXPERTS,
                "numExperts must be in 1...256, got %u", num_experts);
     TF_REQUIRE(ctx, (uint64_t)query_count * top_k < (1ull << 31), TF_ERR_INVALID_ARGUMENT, "%s: too many pairs", name);
+    TF_REQUIRE(ctx, idx_stride > 0, TF_ERR_INVALID_ARGUMENT, "%s: the id stride must be positive", name);
     tf::launch_pdl(tf::group_routes_kernel, dim3(num_experts), dim3(tf::kGroupThreads), 0, static_cast<cudaStream_t>(stream),
-                   indices, static_cast<const uint16_t*>(weights_f16), query_count, top_k, num_experts, routes->sorted_pairs,
-                   routes->per_expert_offsets, routes->per_expert_counts, routes->groups, routes->chunk_group, routes->chunk_start,
-                   routes->counters);
+                   indices, idx_stride, ids_out, static_cast<const uint16_t*>(weights_f16), query_count, top_k, num_experts,
+                   routes->sorted_pairs, routes->per_expert_offsets, routes->per_expert_counts, routes->groups, routes->chunk_group,
+                   routes->chunk_start, routes->counters);
     return tf::check_launch(ctx, name);
+}
+
+}  // namespace tf
+
+extern "C" {
+
+tf_status tf_group_routes_device(tf_context* ctx, void* stream, const uint32_t* indices, const void* weights_f16,
+                                 uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                                 const tf_device_routes* routes) {
+    return tf::group_routes_strided(ctx, stream, indices, 1, nullptr, weights_f16, query_count, top_k, num_experts, routes,
+                                    "tf_group_routes_device");
 }
 
 tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off,

@@ -98,6 +98,64 @@ ep_peer_push_kernel(const uint16_t* __restrict__ src, uint32_t src_stride, uint8
     peer_barrier_in_block(peers, flags_offset_bytes, epoch_and_ticket, error, world, me);
 }
 
+// Dispatch of a decode step in one launch: the rows of this rank's (token, rank) pairs go straight from the activation
+// rows into the owners' receive areas (no local send buffer), in the slot order of ep_pack_kernel: destination r holds
+// this rank's pairs for r's experts in (expert, token, rank) order from slot 0, unused slots get an empty id tail. The
+// row's 16-byte tail carries the local expert id. inverse_perm[token * top_k + rank] = dst * capacity + position, the
+// slot the result comes back in. The block that finishes last runs the flag barrier.
+__global__ void __launch_bounds__(kPeerPushThreads)
+ep_pack_push_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride, const tf_pair* __restrict__ sorted_pairs,
+                    const uint32_t* __restrict__ per_expert_counts, uint32_t top_k, uint32_t num_experts, uint32_t experts_per_rank,
+                    uint32_t d, uint32_t dst_stride, uint8_t* const* __restrict__ peers, uint64_t dst_offset_bytes,
+                    uint32_t* __restrict__ inverse_perm, uint32_t world, uint32_t me, uint32_t cap,
+                    uint64_t flags_offset_bytes, uint32_t* __restrict__ epoch_and_ticket, uint32_t* __restrict__ error,
+                    uint32_t* __restrict__ overflow) {
+    __shared__ uint32_t dst_base[33], dst_count[32];
+    if (threadIdx.x < world) {
+        // pairs are sorted by expert and experts are contiguous per rank: a destination's pairs are one run
+        uint32_t before = 0, mine = 0;
+        for (uint32_t e = 0; e < (threadIdx.x + 1) * experts_per_rank && e < num_experts; ++e) {
+            const uint32_t c = per_expert_counts[e];
+            if (e < threadIdx.x * experts_per_rank) before += c; else mine += c;
+        }
+        dst_base[threadIdx.x] = before;
+        dst_count[threadIdx.x] = mine;
+        if (mine > cap && blockIdx.x == 0) atomicMax(overflow, mine);
+    }
+    __syncthreads();
+    const uint32_t warps_per_block = kPeerPushThreads / kWarp;
+    const uint32_t lane = threadIdx.x % kWarp;
+    const uint32_t total = world * cap;
+    for (uint32_t slot = blockIdx.x * warps_per_block + threadIdx.x / kWarp; slot < total; slot += gridDim.x * warps_per_block) {
+        const uint32_t dst = slot / cap, pos = slot % cap;
+        uint16_t* out_row = reinterpret_cast<uint16_t*>(peers[dst] + dst_offset_bytes) + ((size_t)me * cap + pos) * dst_stride;
+        if (pos >= dst_count[dst]) {
+            if (lane == 0) *reinterpret_cast<uint4*>(out_row + d) = make_uint4(0xFFFFFFFFu, 0u, 0u, 0u);
+            continue;
+        }
+        const tf_pair pr = sorted_pairs[dst_base[dst] + pos];
+        const uint4* in = reinterpret_cast<const uint4*>(hidden + (size_t)pr.token * hidden_stride);
+        uint4* out = reinterpret_cast<uint4*>(out_row);
+        for (uint32_t v = lane; v < d / 8; v += kWarp) out[v] = __ldg(in + v);
+        if (lane == 0) {
+            out[d / 8] = make_uint4(pr.expert % experts_per_rank, 0u, 0u, 0u);
+            inverse_perm[pr.token * top_k + pr.rank] = slot;
+        }
+    }
+    __threadfence_system();
+    __shared__ bool last;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const uint32_t tk = atomicAdd(&epoch_and_ticket[1], 1u);
+        last = tk == gridDim.x - 1;
+        if (last) epoch_and_ticket[1] = 0u;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    peer_barrier_in_block(peers, flags_offset_bytes, epoch_and_ticket, error, world, me);
+}
+
 __global__ void ep_peer_barrier_kernel(uint8_t* const* __restrict__ peers, uint64_t flags_offset_bytes,
                                        uint32_t* __restrict__ epoch_counter, uint32_t* __restrict__ error,
                                        uint32_t world, uint32_t me) {
@@ -199,6 +257,37 @@ tf_status tf_ep_peer_push(tf_context* ctx, void* stream, const void* src_rows, u
         static_cast<const uint16_t*>(src_rows), src_stride_elements, (uint8_t* const*)peer_bases_device,
         dst_offset_bytes, dst_stride_elements, copy_elements, slot_ids, tail_at_element, world, rank, capacity,
         flags_offset_bytes, epoch_and_ticket_device, ctx->peer_error);
+    return tf::check_launch(ctx, name);
+}
+
+tf_status tf_ep_pack_push(tf_context* ctx, void* stream, const void* hidden, uint32_t hidden_stride_elements,
+                          const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                          uint32_t experts_per_rank, uint32_t d, const void* const* peer_bases_device, uint64_t dst_offset_bytes,
+                          uint32_t dst_stride_elements, uint32_t* inverse_perm, uint32_t world, uint32_t rank, uint32_t capacity,
+                          uint64_t flags_offset_bytes, uint32_t* epoch_and_ticket_device) {
+    const char* name = "tf_ep_pack_push";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, hidden && routes && routes->sorted_pairs && routes->per_expert_counts && peer_bases_device && inverse_perm &&
+                        epoch_and_ticket_device,
+               TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    TF_REQUIRE(ctx, world > 0 && world <= 32 && rank < world && capacity > 0, TF_ERR_INVALID_ARGUMENT,
+               "%s: bad rank, world (1...32) or capacity", name);
+    TF_REQUIRE(ctx, experts_per_rank > 0 && experts_per_rank * world == num_experts, TF_ERR_INVALID_ARGUMENT,
+               "%s: %u experts do not divide over %u ranks of %u", name, num_experts, world, experts_per_rank);
+    TF_REQUIRE(ctx, d % 8 == 0 && hidden_stride_elements >= d && dst_stride_elements >= d + 8 && dst_stride_elements % 8 == 0,
+               TF_ERR_INVALID_ARGUMENT, "%s: D must be a multiple of 8 and the destination rows at least D + 8 wide", name);
+    TF_REQUIRE(ctx, tf::aligned(hidden, 16) && (hidden_stride_elements * 2) % 16 == 0 && dst_offset_bytes % 16 == 0 && flags_offset_bytes % 4 == 0,
+               TF_ERR_ALIGNMENT, "%s: rows must be 16-byte aligned", name);
+    if (query_count == 0) return TF_OK;
+    const uint32_t slots = world * capacity;
+    const uint32_t per_block = tf::kPeerPushThreads / tf::kWarp;
+    uint32_t grid = (slots + per_block - 1) / per_block;
+    const uint32_t limit = (uint32_t)ctx->sm_count * 4u;
+    if (grid > limit) grid = limit;
+    tf::ep_pack_push_kernel<<<grid, tf::kPeerPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint16_t*>(hidden), hidden_stride_elements, routes->sorted_pairs, routes->per_expert_counts, top_k, num_experts,
+        experts_per_rank, d, dst_stride_elements, (uint8_t* const*)peer_bases_device, dst_offset_bytes, inverse_perm, world, rank,
+        capacity, flags_offset_bytes, epoch_and_ticket_device, ctx->peer_error, ctx->device_error);
     return tf::check_launch(ctx, name);
 }
 
