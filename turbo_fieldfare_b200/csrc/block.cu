@@ -10,6 +10,7 @@
 //     prefill, :1449-1693 decode), whose two CPU<->GPU round trips per layer exist only to
 //     plan SSD reads: here router ids, grouping and expert addressing stay on the device.
 #include "block.cuh"
+#include "peer.cuh"
 
 namespace tf {
 
@@ -407,11 +408,15 @@ tf_status tf_ep_dispatch(tf_context* ctx, void* stream, const tf_moe_layer* laye
                       send_expert_ids, inverse_perm, send_row_stride_elements);
 }
 
-tf_status tf_ep_experts(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
-                        const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
-                        uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
-                        const void* zero_weights, void* acts_scratch, void* out_rows, uint32_t d, uint32_t f,
-                        uint32_t recv_row_stride_elements) {
+}  // extern "C"
+
+namespace tf {
+
+tf_status ep_experts_waiting(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
+                             const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
+                             uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
+                             const void* zero_weights, void* acts_scratch, void* out_rows, uint32_t d, uint32_t f,
+                             uint32_t recv_row_stride_elements, const PeerWait* peer_wait) {
     const char* name = "tf_ep_experts";
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, pool_layer_base && offsets && recv_rows && recv_expert_ids && recv_routes && zero_weights && acts_scratch && out_rows,
@@ -425,13 +430,28 @@ tf_status tf_ep_experts(tf_context* ctx, void* stream, const void* pool_layer_ba
         // and fills recv_expert_ids on the way
         TF_REQUIRE(ctx, d % 2 == 0 && stride % 2 == 0 && tf::aligned(recv_rows, 4), TF_ERR_ALIGNMENT, "%s: rows must be 4-byte aligned", name);
         s = tf::group_routes_strided(ctx, stream, reinterpret_cast<const uint32_t*>(static_cast<const uint16_t*>(recv_rows) + d), stride / 2,
-                                     const_cast<uint32_t*>(recv_expert_ids), zero_weights, recv_slots, 1, local_experts, recv_routes, name);
+                                     const_cast<uint32_t*>(recv_expert_ids), zero_weights, recv_slots, 1, local_experts, recv_routes, name,
+                                     peer_wait);
     } else {
-        s = tf_group_routes_device(ctx, stream, recv_expert_ids, zero_weights, recv_slots, 1, local_experts, recv_routes);
+        s = tf::group_routes_strided(ctx, stream, recv_expert_ids, 1, nullptr, zero_weights, recv_slots, 1, local_experts, recv_routes,
+                                     name, peer_wait);
     }
     if (s) return s;
     return tf_grouped_moe_batched(ctx, stream, recv_rows, 0, stride, pool_layer_base, expert_stride, offsets, recv_routes,
                                   acts_scratch, out_rows, 0, recv_slots, d, f, 1);
+}
+
+}  // namespace tf
+
+extern "C" {
+
+tf_status tf_ep_experts(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
+                        const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
+                        uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
+                        const void* zero_weights, void* acts_scratch, void* out_rows, uint32_t d, uint32_t f,
+                        uint32_t recv_row_stride_elements) {
+    return tf::ep_experts_waiting(ctx, stream, pool_layer_base, expert_stride, offsets, recv_rows, recv_expert_ids, recv_slots,
+                                  local_experts, recv_routes, zero_weights, acts_scratch, out_rows, d, f, recv_row_stride_elements, nullptr);
 }
 
 tf_status tf_ep_experts_tensorcore(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,

@@ -44,12 +44,23 @@ struct tf_stack {
 };
 
 namespace tf {
+struct PeerWait;
 bool decode_step_eligible(const tf_stack* st, const tf_workspace* ws);
 tf_status decode_step_prepare(tf_context* ctx, tf_stack* st);
 tf_status launch_decode_step(tf_context* ctx, void* stream, tf_stack* st, void* hidden, tf_workspace* ws);
 // grouped.cu: tf_group_routes_device over ids read at a stride (and optionally written out densely)
 tf_status group_routes_strided(tf_context* ctx, void* stream, const uint32_t* indices, uint32_t idx_stride, uint32_t* ids_out,
                                const void* weights_f16, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
-                               const tf_device_routes* routes, const char* name);
+                               const tf_device_routes* routes, const char* name, const struct PeerWait* peer_wait);
+// block.cu / ep.cu: tf_ep_experts and tf_ep_combine whose first kernel waits (bounded) for the peers' flags
+tf_status ep_experts_waiting(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
+                             const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
+                             uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
+                             const void* zero_weights, void* acts_scratch, void* out_rows, uint32_t d, uint32_t f,
+                             uint32_t recv_row_stride_elements, const struct PeerWait* peer_wait);
+tf_status ep_combine_waiting(tf_context* ctx, void* stream, const void* returned_rows, const void* route_weights,
+                             const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
+                             void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d,
+                             const struct PeerWait* peer_wait);
 }  // namespace tf
 

@@ -8,7 +8,8 @@
 // (destination, expert, token, rank) order, which is the order the device grouping already produced,
 // and records where each (token, rank) went; the combine kernel gathers the returned rows through
 // that record, so no row is copied twice and the summation order is fixed (rank 0..K-1).
-#include "tf_common.cuh"
+#include "block.cuh"
+#include "peer.cuh"
 
 namespace tf {
 
@@ -94,7 +95,8 @@ __global__ void ep_extract_ids_kernel(const uint16_t* __restrict__ rows, uint32_
 __global__ void ep_combine_kernel(const uint16_t* __restrict__ rows, const uint16_t* __restrict__ weights,
                                   const uint32_t* __restrict__ inverse_perm, const uint16_t* __restrict__ residual,
                                   uint32_t residual_stride, uint16_t* __restrict__ out, uint32_t out_stride,
-                                  uint32_t T, uint32_t K, uint32_t D) {
+                                  uint32_t T, uint32_t K, uint32_t D, const PeerWait peer_wait) {
+    peer_wait_in_block(peer_wait);      // the rows may come from peers that are still writing them
     // rows in grid.x (up to 2^31 - 1 blocks), column blocks in grid.y: an expert-parallel rank can hold more than 65535 rows
     const uint32_t d = blockIdx.y * blockDim.x + threadIdx.x;
     const uint32_t t = blockIdx.x;
@@ -168,9 +170,14 @@ tf_status tf_pack_sorted_rows(tf_context* ctx, void* stream, const void* hidden,
                      x_sorted, row_expert_ids, inverse_perm, true, "tf_pack_sorted_rows");
 }
 
-tf_status tf_ep_combine(tf_context* ctx, void* stream, const void* returned_rows, const void* route_weights,
-                        const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
-                        void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d) {
+}  // extern "C"
+
+namespace tf {
+
+tf_status ep_combine_waiting(tf_context* ctx, void* stream, const void* returned_rows, const void* route_weights,
+                             const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
+                             void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d,
+                             const PeerWait* peer_wait) {
     const char* name = "tf_ep_combine";
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, returned_rows && route_weights && inverse_perm && out, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
@@ -180,8 +187,19 @@ tf_status tf_ep_combine(tf_context* ctx, void* stream, const void* returned_rows
     tf::ep_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(returned_rows), static_cast<const uint16_t*>(route_weights), inverse_perm,
         static_cast<const uint16_t*>(residual), residual_stride_elements, static_cast<uint16_t*>(out), out_stride_elements,
-        query_count, top_k, d);
+        query_count, top_k, d, peer_wait ? *peer_wait : PeerWait{nullptr, nullptr, nullptr, 0u});
     return tf::check_launch(ctx, name);
+}
+
+}  // namespace tf
+
+extern "C" {
+
+tf_status tf_ep_combine(tf_context* ctx, void* stream, const void* returned_rows, const void* route_weights,
+                        const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
+                        void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d) {
+    return tf::ep_combine_waiting(ctx, stream, returned_rows, route_weights, inverse_perm, residual, residual_stride_elements, out,
+                                  out_stride_elements, query_count, top_k, d, nullptr);
 }
 
 }  // extern "C"

@@ -30,6 +30,7 @@
 #include <vector>
 
 #include "block.cuh"
+#include "peer.cuh"
 
 namespace tf {
 
@@ -412,6 +413,11 @@ tf_status tf_moe_block_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* l
     const uint32_t n_pairs = tokens * K, cap = b->capacity, stride = b->row_stride;
     const bool fixed = b->mode != TF_EP_EXACT, peer = b->mode == TF_EP_FIXED_PEER;
     tf_workspace* ws = b->ws;
+    // peer mode: a push publishes this rank's flag and ends; the kernel that consumes the exchanged rows waits for the peers
+    tf::PeerWait peer_wait{nullptr, nullptr, nullptr, 0u};
+    if (peer)
+        peer_wait = tf::PeerWait{reinterpret_cast<const uint32_t*>(static_cast<const uint8_t*>(tf_peer_buffer_ptr(b->peer)) + b->flags_offset), b->epoch,
+                                 ctx->peer_error, world};
 
     // the shared expert needs only x: it runs on the side stream beside the dispatch, the exchanges and the experts
     TF_CUDA(ctx, cudaEventRecord(ctx->fork_event, st));
@@ -442,9 +448,9 @@ tf_status tf_moe_block_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* l
                                            ws->weights, tokens, b->num_experts, d, K, d, tf_workspace_routes(ws));
         if (s) return bail(s);
         recv_slots = world * cap;
-        s = tf_ep_pack_push(ctx, stream, x, d, tf_workspace_routes(ws), tokens, K, b->num_experts, le, d,
-                            (const void* const*)b->peer_bases_dev, 0, stride, b->inverse, world, (uint32_t)ep->rank, cap,
-                            b->flags_offset, b->epoch);
+        s = tf::pack_push(ctx, stream, x, d, tf_workspace_routes(ws), tokens, K, b->num_experts, le, d,
+                          (const void* const*)b->peer_bases_dev, 0, stride, b->inverse, world, (uint32_t)ep->rank, cap,
+                          b->flags_offset, b->epoch, false);      // the grouping of the received rows waits for the peers
         if (s) return bail(s);
         recv_rows = b->recv_rows;
     } else if ((s = tf_ep_dispatch(ctx, stream, layer, x, tokens, ws, le, cap, b->send_rows, b->send_ids, b->inverse, stride)) != TF_OK) {
@@ -516,15 +522,16 @@ tf_status tf_moe_block_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* l
                                          recv_slots, le, &b->routes, b->zero_weights, b->one_weights, b->x_sorted, b->row_ids,
                                          b->inverse_sorted, b->acts, b->out_sorted, b->out_rows, d, f);
         else
-            s = tf_ep_experts(ctx, stream, layer->pool_layer_base, layer->expert_stride, &layer->offsets, recv_rows, recv_ids, recv_slots,
-                              le, &b->routes, b->zero_weights, b->acts, b->out_rows, d, f, stride);
+            s = tf::ep_experts_waiting(ctx, stream, layer->pool_layer_base, layer->expert_stride, &layer->offsets, recv_rows, recv_ids,
+                                       recv_slots, le, &b->routes, b->zero_weights, b->acts, b->out_rows, d, f, stride,
+                                       peer ? &peer_wait : nullptr);
         if (s) return bail(s);
     }
 
     // results back to the home ranks
     if (peer) {
-        s = tf_ep_peer_push(ctx, stream, b->out_rows, d, (const void* const*)b->peer_bases_dev, b->back_offset, d, d, b->recv_ids, 0,
-                            world, (uint32_t)ep->rank, cap, b->flags_offset, b->epoch);
+        s = tf::peer_push(ctx, stream, b->out_rows, d, (const void* const*)b->peer_bases_dev, b->back_offset, d, d, b->recv_ids, 0,
+                          world, (uint32_t)ep->rank, cap, b->flags_offset, b->epoch, false);      // the combine waits for the peers
         if (s) return bail(s);
         back = b->back_rows;
     } else if (world > 1) {
@@ -550,7 +557,8 @@ tf_status tf_moe_block_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* l
     }
     TF_CUDA(ctx, cudaStreamWaitEvent(st, ctx->join_event, 0));
     (void)n_pairs;
-    return tf_ep_combine(ctx, stream, back, ws->weights, b->inverse, ws->shared_y, d, y, d, tokens, K, d);
+    return tf::ep_combine_waiting(ctx, stream, back, ws->weights, b->inverse, ws->shared_y, d, y, d, tokens, K, d,
+                                  peer ? &peer_wait : nullptr);
 }
 
 tf_status tf_stack_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* layers, const void* const* norm_weights_bf16,

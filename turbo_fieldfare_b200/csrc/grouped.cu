@@ -31,6 +31,7 @@
 // block-wide barrier in the steady state. Every mbarrier wait is bounded: on expiry
 // the kernel records an error code and returns.
 #include "async_copy.cuh"
+#include "peer.cuh"
 
 namespace tf {
 
@@ -48,7 +49,7 @@ group_routes_kernel(const uint32_t* __restrict__ indices, uint32_t idx_stride, u
                     tf_pair* __restrict__ sorted_pairs, uint32_t* __restrict__ per_expert_offsets,
                     uint32_t* __restrict__ per_expert_counts, tf_group* __restrict__ groups,
                     uint32_t* __restrict__ chunk_group, uint32_t* __restrict__ chunk_start,
-                    uint32_t* __restrict__ counters) {
+                    uint32_t* __restrict__ counters, const PeerWait peer_wait) {
     __shared__ uint32_t hist[TF_MAX_ROUTER_EXPERTS];
     __shared__ uint32_t warp_tot[kGroupThreads / kWarp];
     __shared__ uint32_t s_offset;
@@ -57,6 +58,7 @@ group_routes_kernel(const uint32_t* __restrict__ indices, uint32_t idx_stride, u
     pdl_launch_dependents();
     for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) hist[i] = 0;
     pdl_wait();
+    peer_wait_in_block(peer_wait);      // the ids may sit in rows that peers are still writing (ends with a block barrier)
     __syncthreads();
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
         // idx_stride > 1: the ids sit in the tails of exchanged rows; the first block also writes them out densely
@@ -798,7 +800,7 @@ namespace tf {
 // and, when ids_out is given, also written out densely.
 tf_status group_routes_strided(tf_context* ctx, void* stream, const uint32_t* indices, uint32_t idx_stride, uint32_t* ids_out,
                                const void* weights_f16, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
-                               const tf_device_routes* routes, const char* name) {
+                               const tf_device_routes* routes, const char* name, const PeerWait* peer_wait) {
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, indices && weights_f16 && routes, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
     TF_REQUIRE(ctx, routes->sorted_pairs && routes->per_expert_offsets && routes->per_expert_counts && routes->groups &&
@@ -812,7 +814,7 @@ tf_status group_routes_strided(tf_context* ctx, void* stream, const uint32_t* in
     tf::launch_pdl(tf::group_routes_kernel, dim3(num_experts), dim3(tf::kGroupThreads), 0, static_cast<cudaStream_t>(stream),
                    indices, idx_stride, ids_out, static_cast<const uint16_t*>(weights_f16), query_count, top_k, num_experts,
                    routes->sorted_pairs, routes->per_expert_offsets, routes->per_expert_counts, routes->groups, routes->chunk_group,
-                   routes->chunk_start, routes->counters);
+                   routes->chunk_start, routes->counters, peer_wait ? *peer_wait : PeerWait{nullptr, nullptr, nullptr, 0u});
     return tf::check_launch(ctx, name);
 }
 
@@ -824,7 +826,7 @@ tf_status tf_group_routes_device(tf_context* ctx, void* stream, const uint32_t* 
                                  uint32_t query_count, uint32_t top_k, uint32_t num_experts,
                                  const tf_device_routes* routes) {
     return tf::group_routes_strided(ctx, stream, indices, 1, nullptr, weights_f16, query_count, top_k, num_experts, routes,
-                                    "tf_group_routes_device");
+                                    "tf_group_routes_device", nullptr);
 }
 
 tf_status tf_grouped_moe_batched(tf_context* ctx, void* stream, const void* hidden, uint64_t hidden_off,

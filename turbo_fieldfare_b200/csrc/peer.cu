@@ -11,28 +11,19 @@
 // not wait at all, so a missing rank costs one timeout. From that point on the ranks are no longer synchronised and
 // every result is invalid until tf_device_status has reported and cleared the code.
 // Ranks must run one process per GPU (kernels that wait on one another never share a GPU).
-#include "tf_common.cuh"
+#include "peer.cuh"
 
 #include <cstring>
 
 namespace tf {
 
-constexpr uint32_t kPeerSpinLimit = 1u << 23;           // x ~0.2 us per poll: about 2 s
-constexpr uint32_t kErrPeerTimeout = 0x7F000011u;
 constexpr int kPeerPushThreads = 256;
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
 
 // Flag barrier: thread r tells peer r "rank `me` reached epoch e" and waits until peer r has said the same here.
 // The epoch lives on the device and advances by one per barrier, so a replayed graph needs no host value.
 // Called by every thread of one block (at least `world` threads).
+// WAIT = false publishes the epoch and returns: the wait is then the consumer kernel's (peer_wait_in_block).
+template <bool WAIT>
 __device__ __forceinline__ void peer_barrier_in_block(uint8_t* const* __restrict__ peers, uint64_t flags_offset_bytes,
                                                       uint32_t* __restrict__ epoch_counter, uint32_t* __restrict__ error,
                                                       uint32_t world, uint32_t me) {
@@ -46,19 +37,14 @@ __device__ __forceinline__ void peer_barrier_in_block(uint8_t* const* __restrict
     const uint32_t r = threadIdx.x;
     if (r >= world) return;
     st_release_sys(reinterpret_cast<uint32_t*>(peers[r] + flags_offset_bytes) + me, epoch);
-    const uint32_t* mine = reinterpret_cast<const uint32_t*>(peers[me] + flags_offset_bytes) + r;
-    if (*reinterpret_cast<volatile uint32_t*>(error) != 0u) return;      // a wait already gave up: do not wait again
-    for (uint32_t spin = 0; spin < kPeerSpinLimit; ++spin) {
-        if ((int32_t)(ld_acquire_sys(mine) - epoch) >= 0) return;
-        __nanosleep(100);
-    }
-    atomicCAS(error, 0u, kErrPeerTimeout);
+    if constexpr (WAIT) peer_wait_flag(reinterpret_cast<const uint32_t*>(peers[me] + flags_offset_bytes) + r, epoch, error);
 }
 
 // One warp per slot (source rank block s, slot j). A slot is in use when its expert id is not 0xFFFFFFFF: the id is
 // read from `ids` when given, else from the row's tail (element `tail_at`, as 32 bits). Used slots are copied
 // (`copy_elems` fp16 elements, a multiple of 8) into peer s's buffer at block `me`; with tails, an unused slot gets
 // only its tail written so that the receiver sees it as empty.
+template <bool WAIT>
 __global__ void __launch_bounds__(kPeerPushThreads)
 ep_peer_push_kernel(const uint16_t* __restrict__ src, uint32_t src_stride, uint8_t* const* __restrict__ peers,
                     uint64_t dst_offset_bytes, uint32_t dst_stride, uint32_t copy_elems, const uint32_t* __restrict__ ids,
@@ -95,7 +81,7 @@ ep_peer_push_kernel(const uint16_t* __restrict__ src, uint32_t src_stride, uint8
     __syncthreads();
     if (!last) return;
     __threadfence();
-    peer_barrier_in_block(peers, flags_offset_bytes, epoch_and_ticket, error, world, me);
+    peer_barrier_in_block<WAIT>(peers, flags_offset_bytes, epoch_and_ticket, error, world, me);
 }
 
 // Dispatch of a decode step in one launch: the rows of this rank's (token, rank) pairs go straight from the activation
@@ -103,6 +89,7 @@ ep_peer_push_kernel(const uint16_t* __restrict__ src, uint32_t src_stride, uint8
 // this rank's pairs for r's experts in (expert, token, rank) order from slot 0, unused slots get an empty id tail. The
 // row's 16-byte tail carries the local expert id. inverse_perm[token * top_k + rank] = dst * capacity + position, the
 // slot the result comes back in. The block that finishes last runs the flag barrier.
+template <bool WAIT>
 __global__ void __launch_bounds__(kPeerPushThreads)
 ep_pack_push_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride, const tf_pair* __restrict__ sorted_pairs,
                     const uint32_t* __restrict__ per_expert_counts, uint32_t top_k, uint32_t num_experts, uint32_t experts_per_rank,
@@ -153,13 +140,13 @@ ep_pack_push_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride,
     __syncthreads();
     if (!last) return;
     __threadfence();
-    peer_barrier_in_block(peers, flags_offset_bytes, epoch_and_ticket, error, world, me);
+    peer_barrier_in_block<WAIT>(peers, flags_offset_bytes, epoch_and_ticket, error, world, me);
 }
 
 __global__ void ep_peer_barrier_kernel(uint8_t* const* __restrict__ peers, uint64_t flags_offset_bytes,
                                        uint32_t* __restrict__ epoch_counter, uint32_t* __restrict__ error,
                                        uint32_t world, uint32_t me) {
-    peer_barrier_in_block(peers, flags_offset_bytes, epoch_counter, error, world, me);
+    peer_barrier_in_block<true>(peers, flags_offset_bytes, epoch_counter, error, world, me);
 }
 
 }  // namespace tf
@@ -229,11 +216,16 @@ tf_status tf_peer_buffer_release(tf_context* ctx, void* imported_ptr) {
     return TF_OK;
 }
 
-tf_status tf_ep_peer_push(tf_context* ctx, void* stream, const void* src_rows, uint32_t src_stride_elements,
-                          const void* const* peer_bases_device, uint64_t dst_offset_bytes, uint32_t dst_stride_elements,
-                          uint32_t copy_elements, const uint32_t* slot_ids, uint32_t tail_at_element,
-                          uint32_t world, uint32_t rank, uint32_t capacity,
-                          uint64_t flags_offset_bytes, uint32_t* epoch_and_ticket_device) {
+}  // extern "C"
+
+namespace tf {
+
+// tf_ep_peer_push; wait = false: the launch publishes this rank's flags and ends, the consumer kernel waits.
+tf_status peer_push(tf_context* ctx, void* stream, const void* src_rows, uint32_t src_stride_elements,
+                    const void* const* peer_bases_device, uint64_t dst_offset_bytes, uint32_t dst_stride_elements,
+                    uint32_t copy_elements, const uint32_t* slot_ids, uint32_t tail_at_element,
+                    uint32_t world, uint32_t rank, uint32_t capacity,
+                    uint64_t flags_offset_bytes, uint32_t* epoch_and_ticket_device, bool wait) {
     const char* name = "tf_ep_peer_push";
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, src_rows && peer_bases_device, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
@@ -253,18 +245,20 @@ tf_status tf_ep_peer_push(tf_context* ctx, void* stream, const void* src_rows, u
     uint32_t grid = (slots + per_block - 1) / per_block;
     const uint32_t limit = (uint32_t)ctx->sm_count * 4u;
     if (grid > limit) grid = limit;
-    tf::ep_peer_push_kernel<<<grid, tf::kPeerPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+    auto kern = wait ? tf::ep_peer_push_kernel<true> : tf::ep_peer_push_kernel<false>;
+    kern<<<grid, tf::kPeerPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(src_rows), src_stride_elements, (uint8_t* const*)peer_bases_device,
         dst_offset_bytes, dst_stride_elements, copy_elements, slot_ids, tail_at_element, world, rank, capacity,
         flags_offset_bytes, epoch_and_ticket_device, ctx->peer_error);
     return tf::check_launch(ctx, name);
 }
 
-tf_status tf_ep_pack_push(tf_context* ctx, void* stream, const void* hidden, uint32_t hidden_stride_elements,
-                          const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
-                          uint32_t experts_per_rank, uint32_t d, const void* const* peer_bases_device, uint64_t dst_offset_bytes,
-                          uint32_t dst_stride_elements, uint32_t* inverse_perm, uint32_t world, uint32_t rank, uint32_t capacity,
-                          uint64_t flags_offset_bytes, uint32_t* epoch_and_ticket_device) {
+// tf_ep_pack_push with the same choice.
+tf_status pack_push(tf_context* ctx, void* stream, const void* hidden, uint32_t hidden_stride_elements,
+                    const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                    uint32_t experts_per_rank, uint32_t d, const void* const* peer_bases_device, uint64_t dst_offset_bytes,
+                    uint32_t dst_stride_elements, uint32_t* inverse_perm, uint32_t world, uint32_t rank, uint32_t capacity,
+                    uint64_t flags_offset_bytes, uint32_t* epoch_and_ticket_device, bool wait) {
     const char* name = "tf_ep_pack_push";
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, hidden && routes && routes->sorted_pairs && routes->per_expert_counts && peer_bases_device && inverse_perm &&
@@ -284,11 +278,35 @@ tf_status tf_ep_pack_push(tf_context* ctx, void* stream, const void* hidden, uin
     uint32_t grid = (slots + per_block - 1) / per_block;
     const uint32_t limit = (uint32_t)ctx->sm_count * 4u;
     if (grid > limit) grid = limit;
-    tf::ep_pack_push_kernel<<<grid, tf::kPeerPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+    auto kern = wait ? tf::ep_pack_push_kernel<true> : tf::ep_pack_push_kernel<false>;
+    kern<<<grid, tf::kPeerPushThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint16_t*>(hidden), hidden_stride_elements, routes->sorted_pairs, routes->per_expert_counts, top_k, num_experts,
         experts_per_rank, d, dst_stride_elements, (uint8_t* const*)peer_bases_device, dst_offset_bytes, inverse_perm, world, rank,
         capacity, flags_offset_bytes, epoch_and_ticket_device, ctx->peer_error, ctx->device_error);
     return tf::check_launch(ctx, name);
+}
+
+}  // namespace tf
+
+extern "C" {
+
+tf_status tf_ep_peer_push(tf_context* ctx, void* stream, const void* src_rows, uint32_t src_stride_elements,
+                          const void* const* peer_bases_device, uint64_t dst_offset_bytes, uint32_t dst_stride_elements,
+                          uint32_t copy_elements, const uint32_t* slot_ids, uint32_t tail_at_element,
+                          uint32_t world, uint32_t rank, uint32_t capacity,
+                          uint64_t flags_offset_bytes, uint32_t* epoch_and_ticket_device) {
+    return tf::peer_push(ctx, stream, src_rows, src_stride_elements, peer_bases_device, dst_offset_bytes, dst_stride_elements,
+                         copy_elements, slot_ids, tail_at_element, world, rank, capacity, flags_offset_bytes, epoch_and_ticket_device, true);
+}
+
+tf_status tf_ep_pack_push(tf_context* ctx, void* stream, const void* hidden, uint32_t hidden_stride_elements,
+                          const tf_device_routes* routes, uint32_t query_count, uint32_t top_k, uint32_t num_experts,
+                          uint32_t experts_per_rank, uint32_t d, const void* const* peer_bases_device, uint64_t dst_offset_bytes,
+                          uint32_t dst_stride_elements, uint32_t* inverse_perm, uint32_t world, uint32_t rank, uint32_t capacity,
+                          uint64_t flags_offset_bytes, uint32_t* epoch_and_ticket_device) {
+    return tf::pack_push(ctx, stream, hidden, hidden_stride_elements, routes, query_count, top_k, num_experts, experts_per_rank, d,
+                         peer_bases_device, dst_offset_bytes, dst_stride_elements, inverse_perm, world, rank, capacity,
+                         flags_offset_bytes, epoch_and_ticket_device, true);
 }
 
 tf_status tf_ep_peer_barrier(tf_context* ctx, void* stream, const void* const* peer_bases_device, uint64_t flags_offset_bytes,
