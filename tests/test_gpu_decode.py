@@ -301,6 +301,34 @@ def test_production_router_128x2816_with_bias(tf_ctx, oracle):
         assert lg1.tobytes() == o.router_logits(mat, h16[0], eff)[0].tobytes()
 
 
+@pytest.mark.parametrize("T", [2, 7, 33, 64])
+def test_few_row_router_is_bit_exact(tf_ctx, oracle, T):
+    """2 to 64 aligned rows take the kernel that computes four rows per expert pass: logits bit for bit those of the
+    oracle's canonical order, indices equal, ragged last group of rows (7, 33) included; bf16 rows against the truth."""
+    o = oracle
+    rng = np.random.default_rng(7000 + T)
+    E, D = 128, 2816
+    mat = config0_matrix(o, E, D, rng, bits=8)
+    eff = o.f32_to_bf16((rng.uniform(0.5, 1.5, D) / np.sqrt(D)).astype(np.float32))
+    gain = o.f32_to_bf16(rng.uniform(0.6, 1.4, E).astype(np.float32))
+    bias = (0.3 * rng.standard_normal(E)).astype(np.float32)
+    x = rng.standard_normal((T, D)).astype(np.float32)
+    h16 = o.f32_to_f16(x)
+    idx, w16, logits = _run_router(tf_ctx, o, mat, h16, eff, gain, rows=T, logit_bias=bias)
+    ref_logits = (o.router_logits(mat, h16, eff) + bias).astype(np.float32)
+    assert logits.tobytes() == ref_logits.tobytes()
+    ridx, _, rw32 = o.router_select(ref_logits, gain, 8)
+    assert np.array_equal(idx, ridx)
+    assert np.max(np.abs(o.f16_to_f32(w16) - rw32)) < 5e-3
+    hb = o.f32_to_bf16(x)
+    idx_b, _, logits_b = _run_router(tf_ctx, o, mat, hb, eff, gain, rows=T, logit_bias=bias, bf16_hidden=True)
+    xf = o.bf16_to_f32(hb).astype(np.float64) * o.bf16_to_f32(eff).astype(np.float64)
+    truth = xf @ o.dequantize(mat).astype(np.float64).T + bias
+    assert np.max(np.abs(logits_b - truth)) < 1e-4
+    assert np.array_equal(idx_b, np.argsort(-logits_b, axis=1, kind="stable")[:, :8].astype(np.uint32))
+    assert tf_ctx.device_status() == 0
+
+
 def test_router_preconditions(tf_ctx):
     import torch
     from turbo_fieldfare_b200.kernels import MoE, TFError
