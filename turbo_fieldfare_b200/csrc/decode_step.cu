@@ -47,6 +47,7 @@ constexpr uint32_t kErrGridBarrier = 0x7F000021u;
 constexpr uint32_t kErrStageWait = 0x7F000022u;
 constexpr uint32_t kErrLoaderWait = 0x7F000023u;
 constexpr uint32_t kErrScaleWait = 0x7F000024u;
+constexpr uint32_t kDsPairPad = 32;               // bytes of padding after every pair of gate/up rows in a ring stage
 constexpr int kDsNormThreads = 128;              // threads that compute the sum of squares (as residual_rmsnorm_kernel)
 constexpr int kDsNormSlices = 4;
 
@@ -80,9 +81,9 @@ struct DecodeArgs {
 // One item: 16 rows of a stage x up to 4 column groups of one matrix. Constant across layers.
 struct DsItem {
     uint16_t stage_local;    // stage of the phase that holds the item's rows
-    uint16_t stage_items;    // items that read that stage (the last one to finish hands the slot back)
-    uint16_t tile;           // 16-row tile of the CTA's slice
-    uint16_t row_off;        // byte offset of the item's first group inside a stage row
+    uint16_t stage_items;    // low byte: items that read that stage (the last one to finish hands the slot back); high byte: row stride / 16
+    uint16_t tile;           // 16-row tile of the CTA's slice; bit 15: the stage pads every pair of rows (gate/up layout)
+    uint16_t row_off;        // byte offset of the item's first group inside the stage (expert block + column)
     uint16_t group;          // first group in the B-fragment / group-sum arrays
     uint16_t scale_base;     // element offset of the source's scale rows inside the phase's scale plane
     uint16_t scale_stride;   // groups per scale row of the source
@@ -110,11 +111,14 @@ struct DsSmem {
     __host__ __device__ DsSmem(uint32_t d, uint32_t f, uint32_t fs, uint32_t E, uint32_t K, uint32_t grid) {
         auto up = [](uint32_t v, uint32_t a) { return (v + a - 1) / a * a; };
         const uint32_t ngd = d / 64, ngf = f / 64, ngs = fs / 64, ngb = K * ngf + ngs;
-        const uint32_t quad = (K < 4u ? K : 4u) * (f / 2);
-        uint32_t maxrow = d / 2 > quad ? d / 2 : quad;
-        maxrow = maxrow > fs / 2 ? maxrow : fs / 2;
-        row_stride = up(maxrow, 128) + 32;           // = 32 mod 128: the 8-byte reads of rows g = 0..7 hit distinct banks
-        stage_bytes = 16 * row_stride;
+        // A ring stage holds one of three layouts (a bulk copy has a fixed cost in the copy engine, so a stage is
+        // filled with as few copies as the source layout allows):
+        //   gate/up rows (P1, P2): 16 rows of d/2 bytes, two rows per copy, 32 bytes of padding per pair of rows
+        //   routed down rows (P3): up to four experts x 16 rows of f/2 bytes, expert-major and dense, one copy per expert
+        //   shared down rows (P3): 16 rows of fs/2 bytes, dense, one copy
+        row_stride = d / 2;
+        const uint32_t st_gu = 16 * (d / 2) + 8 * kDsPairPad, st_rd = (K < 4u ? K : 4u) * 16 * (f / 2), st_sd = 16 * (fs / 2);
+        stage_bytes = up(st_gu > st_rd ? (st_gu > st_sd ? st_gu : st_sd) : (st_rd > st_sd ? st_rd : st_sd), 128);
         rows1 = ds_max_rows(fs, grid); rows2 = ds_max_rows(K * f, grid); rows3 = (d + grid - 1) / grid;
         // scale planes (elements): P1 / P2 hold [matrix][row][group], P3 holds [source][row][group]
         // (P3 rows are padded to a multiple of four groups so that four scales are one aligned 8-byte read)
@@ -292,7 +296,10 @@ __device__ __noinline__ void ds_loader(const DsCtx* c, const DecodeLayer* layers
             const uint32_t dst = ds_open_stage(c, q, n * (d / 2), lane);
             if (!dst) continue;
             const uint8_t* W = mat ? L->su_w : L->sg_w;
-            if ((uint32_t)lane < n) bulk_copy_g2s(dst + lane * RS, W + (size_t)(r0 + lane) * (d / 2), d / 2, ds_bar_full(c, q % kDsStages));
+            if ((uint32_t)lane * 2 < n) {       // rows 2 lane, 2 lane + 1 (consecutive in the matrix) as one copy
+                const uint32_t nr = n - lane * 2 < 2u ? 1u : 2u;
+                bulk_copy_g2s(dst + lane * (2 * RS + kDsPairPad), W + (size_t)(r0 + lane * 2) * RS, nr * RS, ds_bar_full(c, q % kDsStages));
+            }
         }
         // the rows of P2 and P3 depend on the layer's top-k
         if (!*c->dead && !mbar_wait(ds_bar_routing(c), l & 1)) {
@@ -312,10 +319,12 @@ __device__ __noinline__ void ds_loader(const DsCtx* c, const DecodeLayer* layers
             const uint32_t n = c->p2_hi - i0 < 16u ? c->p2_hi - i0 : 16u;
             const uint32_t dst = ds_open_stage(c, q, n * (d / 2), lane);
             if (!dst) continue;
-            if ((uint32_t)lane < n) {
-                const uint32_t idx = i0 + lane, k = idx / f, r = idx % f;
-                const uint8_t* src = pool + (uint64_t)c->sel_idx[k] * stride + (mat ? L->off.up_w_off : L->off.gate_w_off) + (size_t)r * (d / 2);
-                bulk_copy_g2s(dst + lane * RS, src, d / 2, ds_bar_full(c, q % kDsStages));
+            if ((uint32_t)lane * 2 < n) {
+                // slices start on even rows and f is even: a pair of rows never straddles two experts
+                const uint32_t idx = i0 + lane * 2, k = idx / f, r = idx % f;
+                const uint32_t nr = n - lane * 2 < 2u ? 1u : 2u;
+                const uint8_t* src = pool + (uint64_t)c->sel_idx[k] * stride + (mat ? L->off.up_w_off : L->off.gate_w_off) + (size_t)r * RS;
+                bulk_copy_g2s(dst + lane * (2 * RS + kDsPairPad), src, nr * RS, ds_bar_full(c, q % kDsStages));
             }
         }
         for (uint32_t s = 0; s < c->n_st3; ++s, ++q) {
@@ -326,15 +335,14 @@ __device__ __noinline__ void ds_loader(const DsCtx* c, const DecodeLayer* layers
                 const uint32_t k0 = sub * 4, nk = K - k0 < 4u ? K - k0 : 4u;
                 const uint32_t dst = ds_open_stage(c, q, n * nk * (f / 2), lane);
                 if (!dst) continue;
-                for (uint32_t j = lane; j < n * nk; j += kWarp) {
-                    const uint32_t row = j / nk, kk = j % nk;
-                    const uint8_t* src = pool + (uint64_t)c->sel_idx[k0 + kk] * stride + L->off.down_w_off + (size_t)(r0 + row) * (f / 2);
-                    bulk_copy_g2s(dst + row * RS + kk * (f / 2), src, f / 2, ds_bar_full(c, q % kDsStages));
+                if ((uint32_t)lane < nk) {     // the rows of one expert are consecutive in its blob: one copy per expert
+                    const uint8_t* src = pool + (uint64_t)c->sel_idx[k0 + lane] * stride + L->off.down_w_off + (size_t)r0 * (f / 2);
+                    bulk_copy_g2s(dst + lane * 16 * (f / 2), src, n * (f / 2), ds_bar_full(c, q % kDsStages));
                 }
             } else {
                 const uint32_t dst = ds_open_stage(c, q, n * (fs / 2), lane);
                 if (!dst) continue;
-                if ((uint32_t)lane < n) bulk_copy_g2s(dst + lane * RS, L->sd_w + (size_t)(r0 + lane) * (fs / 2), fs / 2, ds_bar_full(c, q % kDsStages));
+                if (lane == 0) bulk_copy_g2s(dst, L->sd_w + (size_t)r0 * (fs / 2), n * (fs / 2), ds_bar_full(c, q % kDsStages));
             }
         }
     }
@@ -367,14 +375,15 @@ __device__ __forceinline__ void run_items(const DsCtx* c, const DsItem* tab, uin
                                           uint32_t q0, uint32_t rows, const uint16_t* sS, uint32_t plane_elems,
                                           const uint32_t* frag_base, const float* xsum_base, int lane, uint32_t prof_slot = 0) {
     const int g = lane >> 2, t = lane & 3;
-    const uint32_t RS = c->row_stride;
     const uint16_t* sB = sS + plane_elems;
     float* partial = c->partial;
     const bool prof = c->prof != nullptr && c->cta == 0 && threadIdx.x == 0;
     long long t_wait = 0, t_load = 0, t_math = 0, t_tail = 0, t0 = prof ? clock64() : 0;
     for (uint32_t it = first; it < n_items; it += step) {
         const uint4 raw = *reinterpret_cast<const uint4*>(tab + it);
-        const uint32_t stage_local = raw.x & 0xFFFFu, stage_items = raw.x >> 16, tile = raw.y & 0xFFFFu, row_off = raw.y >> 16,
+        // word 0: stage | items of the stage (8 bits) | row stride / 16 (8 bits); word 1: tile (15 bits) | pair padding | row offset
+        const uint32_t stage_local = raw.x & 0xFFFFu, stage_items = (raw.x >> 16) & 0xFFu, rs = (raw.x >> 24) * 16u,
+                       tile = raw.y & 0x7FFFu, pad = (raw.y & 0x8000u) ? kDsPairPad : 0u, row_off = raw.y >> 16,
                        group = raw.z & 0xFFFFu, scale_base = raw.z >> 16, scale_stride = raw.w & 0xFFFFu,
                        G0 = raw.w >> 20, ngr = (raw.w >> 16) & 0xFu;
         const uint32_t q = q0 + stage_local, slot = q % kDsStages;
@@ -383,11 +392,12 @@ __device__ __forceinline__ void run_items(const DsCtx* c, const DsItem* tab, uin
         }
         __syncwarp();
         if (prof) { const long long n = clock64(); t_wait += n - t0; t0 = n; }
-        const uint32_t base = c->ring_addr + slot * c->stage_bytes + row_off + t * 8;
+        const uint32_t base = c->ring_addr + slot * c->stage_bytes + row_off + t * 8 + g * rs + (g >> 1) * pad;
+        const uint32_t row8 = 8 * rs + 4 * pad;
         uint2 wa[4], wb[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            if ((uint32_t)i < ngr) { wa[i] = lds64(base + g * RS + i * 32); wb[i] = lds64(base + (g + 8) * RS + i * 32); }
+            if ((uint32_t)i < ngr) { wa[i] = lds64(base + i * 32); wb[i] = lds64(base + row8 + i * 32); }
             else { wa[i] = make_uint2(0u, 0u); wb[i] = make_uint2(0u, 0u); }
         }
         uint32_t r0 = tile * 16 + g, r1 = r0 + 8;
@@ -917,7 +927,7 @@ __device__ void ds_build_tables(const DsCtx* c) {
         for (uint32_t it = threadIdx.x; it < n; it += kDsComputeThreads) {
             const uint32_t st = it / kp_d, kp = it % kp_d, G0 = kp * 4;
             DsItem e;
-            e.stage_local = (uint16_t)st; e.stage_items = (uint16_t)kp_d; e.tile = (uint16_t)(st / 2);
+            e.stage_local = (uint16_t)st; e.stage_items = (uint16_t)(kp_d | ((c->d / 32) << 8)); e.tile = (uint16_t)((st / 2) | 0x8000u);
             e.row_off = (uint16_t)(G0 * 32); e.group = (uint16_t)G0; e.scale_base = (uint16_t)((st % 2) * rows_cap * ngd);
             e.scale_stride = (uint16_t)ngd;
             e.g0_ngr = (uint16_t)((G0 << 4) | (ngd - G0 < 4u ? ngd - G0 : 4u));
@@ -932,13 +942,13 @@ __device__ void ds_build_tables(const DsCtx* c) {
         if (rem < K * kp_f) {
             const uint32_t k = rem / kp_f, G0 = (rem % kp_f) * 4, sub = k / 4;
             const uint32_t nk = K - sub * 4 < 4u ? K - sub * 4 : 4u;
-            e.stage_local = (uint16_t)(tile * (c->subs + 1) + sub); e.stage_items = (uint16_t)(nk * kp_f);
-            e.row_off = (uint16_t)((k % 4) * (f / 2) + G0 * 32); e.group = (uint16_t)(k * ngf + G0);
+            e.stage_local = (uint16_t)(tile * (c->subs + 1) + sub); e.stage_items = (uint16_t)((nk * kp_f) | ((f / 32) << 8));
+            e.row_off = (uint16_t)((k % 4) * 16 * (f / 2) + G0 * 32); e.group = (uint16_t)(k * ngf + G0);
             e.scale_base = (uint16_t)(k * c->rows3_cap * c->ngf_pad); e.scale_stride = (uint16_t)c->ngf_pad;
             e.g0_ngr = (uint16_t)((G0 << 4) | (ngf - G0 < 4u ? ngf - G0 : 4u));
         } else {
             const uint32_t G0 = (rem - K * kp_f) * 4;
-            e.stage_local = (uint16_t)(tile * (c->subs + 1) + c->subs); e.stage_items = (uint16_t)kp_s;
+            e.stage_local = (uint16_t)(tile * (c->subs + 1) + c->subs); e.stage_items = (uint16_t)(kp_s | ((c->fs / 32) << 8));
             e.row_off = (uint16_t)(G0 * 32); e.group = (uint16_t)(K * ngf + G0);
             e.scale_base = (uint16_t)(K * c->rows3_cap * c->ngf_pad); e.scale_stride = (uint16_t)c->ngs_pad;
             e.g0_ngr = (uint16_t)((G0 << 4) | (ngs - G0 < 4u ? ngs - G0 : 4u));
@@ -1075,7 +1085,10 @@ bool decode_step_eligible(const tf_stack* st, const tf_workspace* ws) {
     const uint32_t grid = (uint32_t)st->ctx->sm_count;
     if (ds_max_items(d, f, fs, K, grid) > kDsMaxItems) return false;
     const DsSmem lay(d, f, fs, E, K, grid);
-    if (lay.total > 227u * 1024u || lay.row_stride > 0xFFFFu) return false;
+    if (lay.total > 227u * 1024u) return false;
+    // 8-bit fields of the item table: row strides in 16-byte units, items per stage; 16-bit row offsets inside a stage
+    if (d / 32 > 0xFFu || f / 32 > 0xFFu || fs / 32 > 0xFFu || 4u * ((f / 64 + 3) / 4) > 0xFFu || (d / 64 + 3) / 4 > 0xFFu ||
+        (fs / 64 + 3) / 4 > 0xFFu || lay.stage_bytes > 0xFFFFu) return false;
     // 16-bit fields of the item table
     if ((uint64_t)K * (f / 64) + fs / 64 > 0xFFFu || d / 64 > 0xFFFu) return false;
     if ((uint64_t)2 * lay.rows2 * (d / 64) > 0xFFFFu || (uint64_t)2 * lay.rows1 * (d / 64) > 0xFFFFu ||
