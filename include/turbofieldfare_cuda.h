@@ -109,7 +109,8 @@ typedef struct tf_tile { uint32_t group_start, group_count, pair_start, pair_cou
  * consumed by tf_grouped_moe_batched. All pointers are DEVICE buffers the
  * caller owns: sorted_pairs [T*K]; per_expert_offsets, per_expert_counts,
  * groups, chunk_start [E]; chunk_group [T*K/8 + E]; counters [4] =
- * {group count, chunk count, pair count, reserved}. A chunk is up to 8
+ * {group count, chunk count, pair count, grouped pairs (less than the pair count when
+ * slots of an exchange buffer were empty)}. A chunk is up to 8
  * consecutive sorted pairs of one expert (one pass of the grouped kernels).
  * Replaces PrefillMoEGroupedRoutes (PrefillMoEGrouping.swift:33-50), which the
  * reference builds on the CPU after reading the router output back. */
@@ -144,6 +145,11 @@ tf_status tf_context_set_tensorcore_min_tokens(tf_context* ctx, uint32_t tokens)
  * Default 256, like the routed experts: measured at 8, 16, 32 and 64 tokens the streaming kernels were faster
  * (1.07 ms against 1.22 ms for six layers at 64 tokens). */
 tf_status tf_context_set_shared_tensorcore_min_tokens(tf_context* ctx, uint32_t tokens);
+/* Expert parallelism with fixed-capacity exchanges (decode steps): when ranks * tokens * top_k / (experts of a rank), the
+ * expected rows per local expert, reaches `rows`, the owner's expert phase runs on the tensor cores (the streaming
+ * kernels spend the same time per 8-row chunk whether or not the weights are already cached, so they do not get
+ * faster when an expert sees many rows). Default 24: eight ranks at 64 tokens. Read by tf_ep_buffers_create. */
+tf_status tf_context_set_ep_tensorcore_min_rows_per_expert(tf_context* ctx, uint32_t rows);
 /* Profiling aid with no counterpart in the reference: when a device buffer of `capacity` 64-bit words is set, the
  * single-launch one-token step of tf_stack_forward stamps the GPU's global nanosecond timer at every phase boundary
  * (eight stamps per layer: start, norm, router + shared gate/up, barrier, routed gate/up, barrier, down + combine,

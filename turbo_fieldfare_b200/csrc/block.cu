@@ -454,12 +454,18 @@ tf_status tf_ep_experts(tf_context* ctx, void* stream, const void* pool_layer_ba
                                   local_experts, recv_routes, zero_weights, acts_scratch, out_rows, d, f, recv_row_stride_elements, nullptr);
 }
 
-tf_status tf_ep_experts_tensorcore(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
-                                   const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
-                                   uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
-                                   const void* zero_weights, const void* one_weights, void* x_sorted, uint32_t* row_ids,
-                                   uint32_t* inverse_perm, void* acts_scratch, void* out_sorted, void* out_rows,
-                                   uint32_t d, uint32_t f) {
+}  // extern "C"
+
+namespace tf {
+
+// tf_ep_experts_tensorcore for rows of `recv_row_stride_elements` (> d: the ids sit in the row tails, empty slots carry
+// UINT32_MAX and are skipped) whose first kernel may have to wait for the peers that write them.
+tf_status ep_experts_tensorcore_waiting(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
+                                        const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
+                                        uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
+                                        const void* zero_weights, const void* one_weights, void* x_sorted, uint32_t* row_ids,
+                                        uint32_t* inverse_perm, void* acts_scratch, void* out_sorted, void* out_rows,
+                                        uint32_t d, uint32_t f, uint32_t recv_row_stride_elements, const PeerWait* peer_wait) {
     const char* name = "tf_ep_experts_tensorcore";
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, pool_layer_base && offsets && recv_rows && recv_expert_ids && recv_routes && zero_weights && one_weights &&
@@ -468,14 +474,41 @@ tf_status tf_ep_experts_tensorcore(tf_context* ctx, void* stream, const void* po
     if (recv_slots == 0) return TF_OK;
     // group the received rows by local expert, gather them into expert order, run the tcgen05 GEMMs, and put the
     // results back into slot order (a combine with one rank of weight 1.0 is an exact copy through the permutation)
-    tf_status s = tf_group_routes_device(ctx, stream, recv_expert_ids, zero_weights, recv_slots, 1, local_experts, recv_routes);
+    const uint32_t stride = recv_row_stride_elements ? recv_row_stride_elements : d;
+    tf_status s;
+    if (stride > d) {
+        TF_REQUIRE(ctx, d % 2 == 0 && stride % 2 == 0 && tf::aligned(recv_rows, 4), TF_ERR_ALIGNMENT, "%s: rows must be 4-byte aligned", name);
+        s = tf::group_routes_strided(ctx, stream, reinterpret_cast<const uint32_t*>(static_cast<const uint16_t*>(recv_rows) + d), stride / 2,
+                                     const_cast<uint32_t*>(recv_expert_ids), zero_weights, recv_slots, 1, local_experts, recv_routes, name,
+                                     peer_wait);
+    } else {
+        s = tf::group_routes_strided(ctx, stream, recv_expert_ids, 1, nullptr, zero_weights, recv_slots, 1, local_experts, recv_routes,
+                                     name, peer_wait);
+    }
     if (s) return s;
-    s = tf_pack_sorted_rows(ctx, stream, recv_rows, d, recv_routes, recv_slots, 1, local_experts, d, x_sorted, row_ids, inverse_perm);
+    // only the grouped pairs are gathered (the gather stops at the count the grouping left on the device); the slots that
+    // were empty keep whatever inverse_perm held before, which points inside out_sorted, and nobody reads their results
+    s = tf_pack_sorted_rows(ctx, stream, recv_rows, stride, recv_routes, recv_slots, 1, local_experts, d, x_sorted, row_ids, inverse_perm);
     if (s) return s;
     s = tf_grouped_moe_tensorcore(ctx, stream, x_sorted, recv_slots, pool_layer_base, expert_stride, local_experts, offsets,
                                   recv_routes, acts_scratch, out_sorted, d, f);
     if (s) return s;
     return tf_ep_combine(ctx, stream, out_sorted, one_weights, inverse_perm, nullptr, d, out_rows, d, recv_slots, 1, d);
+}
+
+}  // namespace tf
+
+extern "C" {
+
+tf_status tf_ep_experts_tensorcore(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
+                                   const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
+                                   uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
+                                   const void* zero_weights, const void* one_weights, void* x_sorted, uint32_t* row_ids,
+                                   uint32_t* inverse_perm, void* acts_scratch, void* out_sorted, void* out_rows,
+                                   uint32_t d, uint32_t f) {
+    return tf::ep_experts_tensorcore_waiting(ctx, stream, pool_layer_base, expert_stride, offsets, recv_rows, recv_expert_ids, recv_slots,
+                                             local_experts, recv_routes, zero_weights, one_weights, x_sorted, row_ids, inverse_perm,
+                                             acts_scratch, out_sorted, out_rows, d, f, 0, nullptr);
 }
 
 tf_status tf_ep_finish(tf_context* ctx, void* stream, const tf_moe_layer* layer, const void* x, uint32_t tokens,

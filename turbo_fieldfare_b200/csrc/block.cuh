@@ -58,6 +58,12 @@ tf_status ep_experts_waiting(tf_context* ctx, void* stream, const void* pool_lay
                              uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
                              const void* zero_weights, void* acts_scratch, void* out_rows, uint32_t d, uint32_t f,
                              uint32_t recv_row_stride_elements, const struct PeerWait* peer_wait);
+tf_status ep_experts_tensorcore_waiting(tf_context* ctx, void* stream, const void* pool_layer_base, uint64_t expert_stride,
+                                        const tf_expert_offsets* offsets, const void* recv_rows, const uint32_t* recv_expert_ids,
+                                        uint32_t recv_slots, uint32_t local_experts, const tf_device_routes* recv_routes,
+                                        const void* zero_weights, const void* one_weights, void* x_sorted, uint32_t* row_ids,
+                                        uint32_t* inverse_perm, void* acts_scratch, void* out_sorted, void* out_rows,
+                                        uint32_t d, uint32_t f, uint32_t recv_row_stride_elements, const struct PeerWait* peer_wait);
 tf_status ep_combine_waiting(tf_context* ctx, void* stream, const void* returned_rows, const void* route_weights,
                              const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
                              void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d,

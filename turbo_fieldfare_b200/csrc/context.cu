@@ -137,6 +137,12 @@ tf_status tf_context_set_shared_tensorcore_min_tokens(tf_context* ctx, uint32_t 
     return TF_OK;
 }
 
+tf_status tf_context_set_ep_tensorcore_min_rows_per_expert(tf_context* ctx, uint32_t rows) {
+    TF_REQUIRE(ctx, ctx != nullptr && rows > 0, TF_ERR_INVALID_ARGUMENT, "tf_context_set_ep_tensorcore_min_rows_per_expert: ctx is NULL or rows is 0");
+    ctx->ep_tensorcore_min_rows_per_expert = rows;
+    return TF_OK;
+}
+
 tf_status tf_context_set_single_launch_step(tf_context* ctx, int enabled) {
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_context_set_single_launch_step: ctx is NULL");
     ctx->single_launch_step = enabled != 0;

@@ -24,7 +24,7 @@ ep_pack_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride, cons
                const uint32_t* __restrict__ per_expert_counts, uint32_t n_pairs, uint32_t top_k, uint32_t num_experts,
                uint32_t experts_per_rank, uint32_t n_dst, uint32_t capacity, uint32_t d, uint32_t send_stride,
                uint16_t* __restrict__ send_rows, uint32_t* __restrict__ send_ids, uint32_t* __restrict__ inverse_perm,
-               uint32_t* __restrict__ overflow) {
+               uint32_t* __restrict__ overflow, const uint32_t* __restrict__ grouped_pairs) {
     __shared__ uint32_t dst_base[257], dst_count[256];
     if (n_dst > 1) {
         // pairs are sorted by expert, experts are contiguous per rank: dst_base = prefix of the counts
@@ -58,6 +58,7 @@ ep_pack_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride, cons
         p = dst_base[dst] + pos;
     } else {
         p = slot;
+        if (p >= *grouped_pairs) return;      // routes built from an exchange buffer with empty slots hold fewer pairs
     }
     const tf_pair pr = sorted_pairs[p];
     if (lane == 0) {
@@ -122,7 +123,7 @@ static tf_status pack_rows(tf_context* ctx, void* stream, const void* hidden, ui
     TF_REQUIRE(ctx, send_stride == d || (send_stride >= d + 8 && send_stride % 8 == 0), TF_ERR_INVALID_ARGUMENT,
                "%s: the send row stride must be D, or at least D + 8 and a multiple of 8 elements (the id sits in the tail)", name);
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
-    TF_REQUIRE(ctx, hidden && routes && send_rows && send_expert_ids && inverse_perm, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    TF_REQUIRE(ctx, hidden && routes && routes->counters && send_rows && send_expert_ids && inverse_perm, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
     TF_REQUIRE(ctx, experts_per_rank > 0 && num_experts % experts_per_rank == 0 && num_experts <= TF_MAX_ROUTER_EXPERTS,
                TF_ERR_INVALID_ARGUMENT, "%s: experts (%u) must divide evenly over ranks (%u per rank)", name, num_experts, experts_per_rank);
     TF_REQUIRE(ctx, d % 8 == 0 && hidden_stride_elements >= d, TF_ERR_INVALID_ARGUMENT, "%s: D must be a multiple of 8", name);
@@ -138,7 +139,7 @@ static tf_status pack_rows(tf_context* ctx, void* stream, const void* hidden, ui
     kern<<<(slots + per_block - 1) / per_block, tf::kPackThreads, 0, static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const uint16_t*>(hp), hidden_stride_elements, routes->sorted_pairs, routes->per_expert_counts, n_pairs,
         top_k, num_experts, experts_per_rank, n_dst, capacity, d, send_stride, static_cast<uint16_t*>(send_rows), send_expert_ids,
-        inverse_perm, ctx->device_error);
+        inverse_perm, ctx->device_error, routes->counters + 3);
     return tf::check_launch(ctx, name);
 }
 

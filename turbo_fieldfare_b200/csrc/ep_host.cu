@@ -113,6 +113,7 @@ struct tf_ep_buffers {
     uint64_t back_offset = 0, flags_offset = 0;
     bool owns_recv_rows = true, owns_back_rows = true;
     uint32_t tensorcore_min_rows = 2048;       // exact exchanges of at least this many rows run the experts on the tensor cores
+    bool fixed_tensor = false;                 // fixed-capacity exchanges: the expert phase runs on the tensor cores
 };
 
 namespace tf {
@@ -155,6 +156,7 @@ static tf_status ensure_recv(tf_ep_buffers* b, uint32_t slots, bool sorted_scrat
         TF_CUDA(ctx, cudaMalloc(&b->out_sorted, (size_t)cap * d * 2));
         TF_CUDA(ctx, cudaMalloc(&b->row_ids, (size_t)cap * 4));
         TF_CUDA(ctx, cudaMalloc(&b->inverse_sorted, (size_t)cap * 4));
+        TF_CUDA(ctx, cudaMemset(b->inverse_sorted, 0, (size_t)cap * 4));      // entries of empty slots must point inside out_sorted
     }
     // routing tables of the received rows: every row is one (token = slot, rank 0) pair of a local expert
     auto up = [](size_t v) { return (v + 255) / 256 * 256; };
@@ -388,7 +390,11 @@ tf_status tf_ep_buffers_create(tf_ep* ep, uint32_t max_tokens, uint32_t d, uint3
         if (!ok) b->mode = TF_EP_FIXED_NCCL;        // every rank takes this branch together
     }
     if (b->owns_back_rows) dev(&b->back_rows, (size_t)b->send_slots * d * 2);
-    if (!s) s = tf::ensure_recv(b, fixed ? b->send_slots : (b->n_pairs ? b->n_pairs : 1), false);
+    // fixed capacity: the choice of the expert kernels cannot wait for a row count (no host synchronisation), so it is
+    // made here from the expected rows per local expert
+    b->fixed_tensor = fixed && d % 64 == 0 && f % 64 == 0 &&
+                      (uint64_t)ep->world * max_tokens * top_k >= (uint64_t)b->local_experts * ctx->ep_tensorcore_min_rows_per_expert;
+    if (!s) s = tf::ensure_recv(b, fixed ? b->send_slots : (b->n_pairs ? b->n_pairs : 1), b->fixed_tensor);
     if (s) { tf_ep_buffers_destroy(b); return s; }
     *out = b;
     return TF_OK;
@@ -515,12 +521,13 @@ tf_status tf_moe_block_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* l
     }
 
     // the owner's expert phase
-    const bool tensor = !fixed && recv_slots >= b->tensorcore_min_rows && d % 64 == 0 && f % 64 == 0 && b->x_sorted;
+    const bool tensor = (fixed ? b->fixed_tensor : (recv_slots >= b->tensorcore_min_rows && d % 64 == 0 && f % 64 == 0)) && b->x_sorted;
     if (recv_slots) {
         if (tensor)
-            s = tf_ep_experts_tensorcore(ctx, stream, layer->pool_layer_base, layer->expert_stride, &layer->offsets, recv_rows, recv_ids,
-                                         recv_slots, le, &b->routes, b->zero_weights, b->one_weights, b->x_sorted, b->row_ids,
-                                         b->inverse_sorted, b->acts, b->out_sorted, b->out_rows, d, f);
+            s = tf::ep_experts_tensorcore_waiting(ctx, stream, layer->pool_layer_base, layer->expert_stride, &layer->offsets, recv_rows,
+                                                  recv_ids, recv_slots, le, &b->routes, b->zero_weights, b->one_weights, b->x_sorted,
+                                                  b->row_ids, b->inverse_sorted, b->acts, b->out_sorted, b->out_rows, d, f,
+                                                  fixed ? stride : 0, peer ? &peer_wait : nullptr);
         else
             s = tf::ep_experts_waiting(ctx, stream, layer->pool_layer_base, layer->expert_stride, &layer->offsets, recv_rows, recv_ids,
                                        recv_slots, le, &b->routes, b->zero_weights, b->acts, b->out_rows, d, f, stride,

@@ -90,6 +90,7 @@ group_routes_kernel(const uint32_t* __restrict__ indices, uint32_t idx_stride, u
             counters[0] = gi + (cnt ? 1u : 0u);
             counters[1] = ch + (cnt + kChunkTokens - 1) / kChunkTokens;
             counters[2] = n;
+            counters[3] = off + cnt;            // pairs that were grouped (empty slots of an exchange buffer are not)
         }
     }
     __syncthreads();
@@ -924,7 +925,7 @@ __global__ void streamed_routes_kernel(const tf_pair* __restrict__ pairs, uint32
         for (uint32_t j = 0; j < ch; ++j) out->chunk_group[nch + j] = ng;
         ++ng; nch += ch;
     }
-    out->counters[0] = ng; out->counters[1] = nch; out->counters[2] = count; out->counters[3] = 0u;
+    out->counters[0] = ng; out->counters[1] = nch; out->counters[2] = count; out->counters[3] = count;
 }
 
 }  // namespace tf

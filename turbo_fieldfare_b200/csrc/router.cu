@@ -135,6 +135,7 @@ __device__ void group_routes_in_block(const uint32_t* __restrict__ idx, const ui
         out.counters[0] = gi;
         out.counters[1] = ch;
         out.counters[2] = n;
+        out.counters[3] = off;
     }
     for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
         const uint32_t ex = exs[i];
@@ -307,6 +308,7 @@ router_split_kernel(const uint8_t* __restrict__ W, const uint16_t* __restrict__ 
             grp.counters[0] = top_k;
             grp.counters[1] = top_k;
             grp.counters[2] = top_k;
+            grp.counters[3] = top_k;
         }
         return;
     }

@@ -71,6 +71,11 @@ class TurboContext:
         """Blocks of at least ``tokens`` tokens run their expert GEMMs on the tensor cores (default 256)."""
         self.check(self.lib.tf_context_set_tensorcore_min_tokens(self.handle, tokens))
 
+    def set_ep_tensorcore_min_rows_per_expert(self, rows: int) -> None:
+        """Fixed-capacity expert-parallel buffers created afterwards run the expert phase on the tensor cores when the
+        expected rows per local expert reach ``rows`` (default 24)."""
+        self.check(self.lib.tf_context_set_ep_tensorcore_min_rows_per_expert(self.handle, rows))
+
     def set_shared_tensorcore_min_tokens(self, tokens: int) -> None:
         """The same threshold for a block's shared expert alone (default 256)."""
         self.check(self.lib.tf_context_set_shared_tensorcore_min_tokens(self.handle, tokens))
