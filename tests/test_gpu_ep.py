@@ -111,12 +111,12 @@ def test_single_rank_peer_exchange_matches_fused_stack_and_replays_in_a_graph(tf
     """The peer-memory exchange with one rank (the rank pushes into its own buffer and passes its own flag barrier):
     same result as the fused stack, eagerly and as a replayed CUDA graph of the whole step. tensor_rows = 1 forces the
     owner's expert phase onto the tensor cores (most slots of the fixed-capacity buffer are empty then), 100000 onto
-    the streaming kernels, 0 leaves the library's rule (tensor cores at 64 tokens here: 32 rows per expert)."""
+    the streaming kernels, 0 leaves the library's default (streaming kernels)."""
     import torch
     from turbo_fieldfare_b200.ep import ExpertParallelStack
     from turbo_fieldfare_b200.stack import MoEStack
     o = oracle
-    tf_ctx.set_ep_tensorcore_min_rows_per_expert(tensor_rows or 24)
+    tf_ctx.set_ep_tensorcore_min_rows_per_expert(tensor_rows or 0xFFFFFFFF)
     dims = dict(layers=2, d=256, f=128, fs=192, num_experts=16, top_k=8, seed=5, align=256)
     ref_stack = MoEStack(tf_ctx, **dims)
     ep_stack = ExpertParallelStack(tf_ctx, **dims)
@@ -148,7 +148,7 @@ def test_single_rank_peer_exchange_matches_fused_stack_and_replays_in_a_graph(tf
         torch.cuda.synchronize()
         assert o.rel_l2(o.f16_to_f32(from_dev(static_h, np.uint16)), want) < 3e-3
     assert tf_ctx.device_status() == 0
-    tf_ctx.set_ep_tensorcore_min_rows_per_expert(24)
+    tf_ctx.set_ep_tensorcore_min_rows_per_expert(0xFFFFFFFF)
     buf.close()
     ref_stack.close()
     ep_stack.close()

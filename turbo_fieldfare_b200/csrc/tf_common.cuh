@@ -65,8 +65,9 @@ struct tf_context {
     // The same for the shared expert alone (a dense GEMM over all tokens of the block).
     uint32_t shared_tensorcore_min_tokens = 256;
     // Fixed-capacity expert-parallel exchanges whose expected rows per local expert (ranks x tokens x top_k / experts of
-    // a rank) reach this number run the owner's expert phase on the tensor cores.
-    uint32_t ep_tensorcore_min_rows_per_expert = 24;
+    // a rank) reach this number run the owner's expert phase on the tensor cores. Off by default (measured slower at eight
+    // ranks x 64 tokens, 32 rows per expert: 6.62 ms against 5.98 ms per step).
+    uint32_t ep_tensorcore_min_rows_per_expert = 0xFFFFFFFFu;
     // Scratch of the greedy LM head, like the normed-row and row-summary buffers the reference's wrapper owns
     // (Kernels/Fusions/LMHeadChainInt4.swift:26-51); grown on demand by tf_lm_head_greedy_int4.
     uint16_t* lm_x = nullptr;               // fp16 [lm_x_capacity]

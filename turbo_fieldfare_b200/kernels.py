@@ -73,7 +73,7 @@ class TurboContext:
 
     def set_ep_tensorcore_min_rows_per_expert(self, rows: int) -> None:
         """Fixed-capacity expert-parallel buffers created afterwards run the expert phase on the tensor cores when the
-        expected rows per local expert reach ``rows`` (default 24)."""
+        expected rows per local expert reach ``rows`` (off by default)."""
         self.check(self.lib.tf_context_set_ep_tensorcore_min_rows_per_expert(self.handle, rows))
 
     def set_shared_tensorcore_min_tokens(self, tokens: int) -> None:
