@@ -20,7 +20,9 @@ def _route(rng, T, K, E, zipf=False):
 
 
 @pytest.mark.parametrize("T,K,E,zipf", [(1, 8, 128, False), (64, 8, 128, False), (300, 8, 128, True), (4096, 8, 128, True),
-                                         (3, 2, 16, False), (7, 3, 5, False)])
+                                         (3, 2, 16, False), (7, 3, 5, False),
+                                         # from 4096 pairs on: slices of pairs, three launches (ragged last slice, E not a multiple of 32)
+                                         (513, 8, 128, False), (700, 8, 250, True), (20000, 8, 128, True)])
 def test_device_grouping_matches_oracle(tf_ctx, oracle, T, K, E, zipf):
     import torch
     from turbo_fieldfare_b200.kernels import DeviceRoutes, PrefillGroupedRoutedMoE
@@ -40,7 +42,7 @@ def test_device_grouping_matches_oracle(tf_ctx, oracle, T, K, E, zipf):
     assert np.array_equal(got.per_expert_counts, ref.per_expert_counts)
     assert got.groups.tobytes() == ref.groups.tobytes()
     counters = routes.counters.cpu().numpy().view(np.uint32)
-    assert counters[0] == len(ref.groups) and counters[2] == T * K
+    assert counters[0] == len(ref.groups) and counters[2] == T * K and counters[3] == T * K
     assert counters[1] == sum((int(c) + 7) // 8 for c in ref.per_expert_counts)
 
 

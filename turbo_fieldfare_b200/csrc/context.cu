@@ -82,6 +82,7 @@ tf_status tf_context_create(int device, tf_context** out) {
     if (e == cudaSuccess) e = cudaMalloc(&ctx->peer_error, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->peer_error, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->streamed_scratch, tf::streamed_scratch_bytes());
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->group_scratch, sizeof(uint32_t) * 256 * TF_MAX_ROUTER_EXPERTS);
     if (e == cudaSuccess) e = cudaMalloc(&ctx->grid_barrier, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->grid_barrier, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_groups, 2 * 64 * (TF_MAX_ROUTER_EXPERTS + 1));   // routed and dense tables
@@ -106,6 +107,7 @@ void tf_context_destroy(tf_context* ctx) {
     if (ctx->device_error) cudaFree(ctx->device_error);
     if (ctx->peer_error) cudaFree(ctx->peer_error);
     if (ctx->streamed_scratch) cudaFree(ctx->streamed_scratch);
+    if (ctx->group_scratch) cudaFree(ctx->group_scratch);
     if (ctx->grid_barrier) cudaFree(ctx->grid_barrier);
     if (ctx->qmm_groups) cudaFree(ctx->qmm_groups);
     if (ctx->qmm_totals) cudaFree(ctx->qmm_totals);

@@ -93,22 +93,74 @@ __global__ void ep_extract_ids_kernel(const uint16_t* __restrict__ rows, uint32_
 }
 
 // y[t,d] = half(sum_r fma(w[t,r], partial[inverse[t*K+r]][d], acc) + residual[t,d]), rank order.
+// VEC: a thread owns eight consecutive columns (16-byte loads and stores; D a multiple of 8, rows 16-byte aligned).
+template <bool VEC>
 __global__ void ep_combine_kernel(const uint16_t* __restrict__ rows, const uint16_t* __restrict__ weights,
                                   const uint32_t* __restrict__ inverse_perm, const uint16_t* __restrict__ residual,
                                   uint32_t residual_stride, uint16_t* __restrict__ out, uint32_t out_stride,
                                   uint32_t T, uint32_t K, uint32_t D, const PeerWait peer_wait) {
     peer_wait_in_block(peer_wait);      // the rows may come from peers that are still writing them
     // rows in grid.x (up to 2^31 - 1 blocks), column blocks in grid.y: an expert-parallel rank can hold more than 65535 rows
-    const uint32_t d = blockIdx.y * blockDim.x + threadIdx.x;
     const uint32_t t = blockIdx.x;
-    if (d >= D || t >= T) return;
-    float acc = 0.0f;
-    for (uint32_t r = 0; r < K; ++r) {
-        const uint32_t slot = inverse_perm[(size_t)t * K + r];
-        acc = fmaf(f16_bits_to_float(weights[(size_t)t * K + r]), f16_bits_to_float(rows[(size_t)slot * D + d]), acc);
+    if (t >= T) return;
+    if constexpr (VEC) {
+        const uint32_t c = blockIdx.y * blockDim.x + threadIdx.x;          // group of eight columns
+        if (c >= D / 8) return;
+        float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+        for (uint32_t r0 = 0; r0 < K; r0 += 4) {
+            // up to four ranks' rows are requested before the first one is used
+            uint4 v[4];
+            float w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t r = r0 + j;
+                if (r < K) {
+                    const uint32_t slot = inverse_perm[(size_t)t * K + r];
+                    w[j] = f16_bits_to_float(weights[(size_t)t * K + r]);
+                    v[j] = *reinterpret_cast<const uint4*>(rows + (size_t)slot * D + c * 8);
+                } else {
+                    w[j] = 0.0f; v[j] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (r0 + j < K) {
+                    const uint32_t xw[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        acc[2 * q] = fmaf(w[j], f16_bits_to_float((uint16_t)(xw[q] & 0xFFFFu)), acc[2 * q]);
+                        acc[2 * q + 1] = fmaf(w[j], f16_bits_to_float((uint16_t)(xw[q] >> 16)), acc[2 * q + 1]);
+                    }
+                }
+            }
+        }
+        if (residual) {
+            const uint4 rv = *reinterpret_cast<const uint4*>(residual + (size_t)t * residual_stride + c * 8);
+            const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                acc[2 * q] += f16_bits_to_float((uint16_t)(rw[q] & 0xFFFFu));
+                acc[2 * q + 1] += f16_bits_to_float((uint16_t)(rw[q] >> 16));
+            }
+        }
+        uint32_t ow[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const __half2 h = __floats2half2_rn(acc[2 * q], acc[2 * q + 1]);
+            ow[q] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)t * out_stride + c * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    } else {
+        const uint32_t d = blockIdx.y * blockDim.x + threadIdx.x;
+        if (d >= D) return;
+        float acc = 0.0f;
+        for (uint32_t r = 0; r < K; ++r) {
+            const uint32_t slot = inverse_perm[(size_t)t * K + r];
+            acc = fmaf(f16_bits_to_float(weights[(size_t)t * K + r]), f16_bits_to_float(rows[(size_t)slot * D + d]), acc);
+        }
+        if (residual) acc += f16_bits_to_float(residual[(size_t)t * residual_stride + d]);
+        out[(size_t)t * out_stride + d] = __half_as_ushort(__float2half_rn(acc));
     }
-    if (residual) acc += f16_bits_to_float(residual[(size_t)t * residual_stride + d]);
-    out[(size_t)t * out_stride + d] = __half_as_ushort(__float2half_rn(acc));
 }
 
 }  // namespace tf
@@ -184,11 +236,24 @@ tf_status ep_combine_waiting(tf_context* ctx, void* stream, const void* returned
     TF_REQUIRE(ctx, returned_rows && route_weights && inverse_perm && out, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
     TF_REQUIRE(ctx, top_k > 0 && d > 0 && out_stride_elements >= d, TF_ERR_INVALID_ARGUMENT, "%s: bad dimensions", name);
     if (query_count == 0) return TF_OK;
-    dim3 grid(query_count, (d + 255) / 256);
-    tf::ep_combine_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const uint16_t*>(returned_rows), static_cast<const uint16_t*>(route_weights), inverse_perm,
-        static_cast<const uint16_t*>(residual), residual_stride_elements, static_cast<uint16_t*>(out), out_stride_elements,
-        query_count, top_k, d, peer_wait ? *peer_wait : PeerWait{nullptr, nullptr, nullptr, 0u});
+    const PeerWait pw = peer_wait ? *peer_wait : PeerWait{nullptr, nullptr, nullptr, 0u};
+    const bool vec = d % 8 == 0 && out_stride_elements % 8 == 0 && tf::aligned(returned_rows, 16) && tf::aligned(out, 16) &&
+                     (!residual || (residual_stride_elements % 8 == 0 && tf::aligned(residual, 16)));
+    if (vec) {
+        uint32_t threads = (d / 8 + 31) / 32 * 32;          // one block per row up to 4096 columns
+        if (threads > 512) threads = 512;
+        dim3 grid(query_count, (d / 8 + threads - 1) / threads);
+        tf::ep_combine_kernel<true><<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint16_t*>(returned_rows), static_cast<const uint16_t*>(route_weights), inverse_perm,
+            static_cast<const uint16_t*>(residual), residual_stride_elements, static_cast<uint16_t*>(out), out_stride_elements,
+            query_count, top_k, d, pw);
+    } else {
+        dim3 grid(query_count, (d + 255) / 256);
+        tf::ep_combine_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            static_cast<const uint16_t*>(returned_rows), static_cast<const uint16_t*>(route_weights), inverse_perm,
+            static_cast<const uint16_t*>(residual), residual_stride_elements, static_cast<uint16_t*>(out), out_stride_elements,
+            query_count, top_k, d, pw);
+    }
     return tf::check_launch(ctx, name);
 }
 

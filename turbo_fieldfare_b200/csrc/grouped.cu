@@ -136,6 +136,127 @@ group_routes_kernel(const uint32_t* __restrict__ indices, uint32_t idx_stride, u
     }
 }
 
+// Many pairs (prefill, large exchanges): the one-block-per-expert kernel above reads all n ids in every expert's block
+// (E x n reads). Here the pairs are split into contiguous slices, one per block: (1) per-slice expert histograms,
+// (2) one block turns them into per-expert offsets, groups, chunks and per-(slice, expert) start positions, (3) every
+// slice places its pairs: a warp takes 32 consecutive pairs, lanes with the same expert find their rank among
+// themselves with match.any, the warps' counts are prefixed per expert in shared memory. The result is the same stable
+// (expert, token, rank) order.
+constexpr int kGrpSliceThreads = 1024;
+constexpr int kGrpMaxSlices = 256;
+constexpr uint32_t kGrpLargePairs = 4096;       // from this many pairs on
+
+__host__ __device__ inline uint32_t grp_slice_len(uint32_t n, uint32_t slices) {
+    const uint32_t per = (n + slices - 1) / slices;
+    return (per + kGrpSliceThreads - 1) / kGrpSliceThreads * kGrpSliceThreads;      // whole rounds of the block
+}
+
+__global__ void __launch_bounds__(kGrpSliceThreads)
+group_count_kernel(const uint32_t* __restrict__ indices, uint32_t idx_stride, uint32_t* __restrict__ ids_out, uint32_t n, uint32_t E,
+                   uint32_t slice_len, uint32_t* __restrict__ slice_hist, const PeerWait peer_wait) {
+    __shared__ uint32_t hist[TF_MAX_ROUTER_EXPERTS];
+    pdl_launch_dependents();
+    for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) hist[i] = 0;
+    pdl_wait();
+    peer_wait_in_block(peer_wait);
+    __syncthreads();
+    const uint32_t lo = blockIdx.x * slice_len, hi = lo + slice_len < n ? lo + slice_len : n;
+    for (uint32_t i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        uint32_t ex = indices[(size_t)i * idx_stride];
+        if (ids_out) ids_out[i] = ex;
+        if (ex == 0xFFFFFFFFu) continue;
+        if (ex >= E) ex = E - 1;
+        atomicAdd(&hist[ex], 1u);
+    }
+    __syncthreads();
+    for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) slice_hist[(size_t)blockIdx.x * E + i] = hist[i];
+}
+
+__global__ void __launch_bounds__(TF_MAX_ROUTER_EXPERTS)
+group_scan_kernel(uint32_t* __restrict__ slice_hist /* in: counts; out: start positions */, uint32_t slices, uint32_t n, uint32_t E,
+                  uint32_t* __restrict__ per_expert_offsets, uint32_t* __restrict__ per_expert_counts, tf_group* __restrict__ groups,
+                  uint32_t* __restrict__ chunk_group, uint32_t* __restrict__ chunk_start, uint32_t* __restrict__ counters) {
+    __shared__ uint32_t wtot[3][TF_MAX_ROUTER_EXPERTS / kWarp];
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t e = threadIdx.x, lane = threadIdx.x % kWarp, warp = threadIdx.x / kWarp, nwarps = blockDim.x / kWarp;
+    // per expert: total count, and the slices' counts turned into running sums (relative to the expert's start)
+    uint32_t cnt = 0;
+    if (e < E) {
+        for (uint32_t b = 0; b < slices; ++b) {
+            const uint32_t c = slice_hist[(size_t)b * E + e];
+            slice_hist[(size_t)b * E + e] = cnt;
+            cnt += c;
+        }
+    }
+    const uint32_t nch = (cnt + (uint32_t)kChunkTokens - 1) / (uint32_t)kChunkTokens;
+    uint32_t i_off = cnt, i_g = cnt ? 1u : 0u, i_ch = nch;
+#pragma unroll
+    for (int o = 1; o < kWarp; o <<= 1) {
+        const uint32_t a = __shfl_up_sync(kFullMask, i_off, o), b2 = __shfl_up_sync(kFullMask, i_g, o), c = __shfl_up_sync(kFullMask, i_ch, o);
+        if ((int)lane >= o) { i_off += a; i_g += b2; i_ch += c; }
+    }
+    if (lane == kWarp - 1) { wtot[0][warp] = i_off; wtot[1][warp] = i_g; wtot[2][warp] = i_ch; }
+    __syncthreads();
+    uint32_t p_off = 0, p_g = 0, p_ch = 0, t_off = 0, t_g = 0, t_ch = 0;
+    for (uint32_t v = 0; v < nwarps; ++v) {
+        if (v < warp) { p_off += wtot[0][v]; p_g += wtot[1][v]; p_ch += wtot[2][v]; }
+        t_off += wtot[0][v]; t_g += wtot[1][v]; t_ch += wtot[2][v];
+    }
+    const uint32_t my_off = p_off + i_off - cnt, my_g = p_g + i_g - (cnt ? 1u : 0u), my_ch = p_ch + i_ch - nch;
+    if (e < E) {
+        per_expert_counts[e] = cnt;
+        per_expert_offsets[e] = cnt ? my_off : 0xFFFFFFFFu;
+        if (cnt) {
+            groups[my_g] = tf_group{e, my_off, cnt};
+            chunk_start[my_g] = my_ch;
+            for (uint32_t j = 0; j < nch; ++j) chunk_group[my_ch + j] = my_g;
+        }
+        for (uint32_t b = 0; b < slices; ++b) slice_hist[(size_t)b * E + e] += my_off;
+    }
+    if (threadIdx.x == 0) { counters[0] = t_g; counters[1] = t_ch; counters[2] = n; counters[3] = t_off; }
+}
+
+__global__ void __launch_bounds__(kGrpSliceThreads)
+group_place_kernel(const uint32_t* __restrict__ indices, uint32_t idx_stride, const uint16_t* __restrict__ weights, uint32_t n, uint32_t K,
+                   uint32_t E, uint32_t slice_len, const uint32_t* __restrict__ slice_start, tf_pair* __restrict__ sorted_pairs) {
+    __shared__ uint32_t wcnt[kGrpSliceThreads / kWarp][TF_MAX_ROUTER_EXPERTS];     // per warp and expert: count, then start
+    __shared__ uint32_t run[TF_MAX_ROUTER_EXPERTS];                                // next free position per expert
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t lane = threadIdx.x % kWarp, warp = threadIdx.x / kWarp;
+    constexpr uint32_t kWarps = kGrpSliceThreads / kWarp;
+    for (uint32_t i = threadIdx.x; i < E; i += blockDim.x) run[i] = slice_start[(size_t)blockIdx.x * E + i];
+    const uint32_t lo = blockIdx.x * slice_len, hi = lo + slice_len < n ? lo + slice_len : n;
+    for (uint32_t base = lo; base < hi; base += kGrpSliceThreads) {        // uniform trip count: slice_len is whole rounds
+        for (uint32_t i = threadIdx.x; i < kWarps * E; i += blockDim.x) (&wcnt[0][0])[(i / E) * TF_MAX_ROUTER_EXPERTS + i % E] = 0;
+        __syncthreads();
+        const uint32_t i = base + threadIdx.x;
+        uint32_t ex = 0xFFFFFFFFu;
+        if (i < hi) {
+            ex = indices[(size_t)i * idx_stride];
+            if (ex != 0xFFFFFFFFu && ex >= E) ex = E - 1;
+        }
+        const bool valid = ex != 0xFFFFFFFFu;
+        const uint32_t peers = __match_any_sync(kFullMask, ex);            // invalid lanes match one another and are ignored
+        const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+        if (valid && rank == 0) wcnt[warp][ex] = __popc(peers);
+        __syncthreads();
+        for (uint32_t e = threadIdx.x; e < E; e += blockDim.x) {
+            uint32_t acc = run[e];
+            for (uint32_t w2 = 0; w2 < kWarps; ++w2) {
+                const uint32_t c = wcnt[w2][e];
+                wcnt[w2][e] = acc;
+                acc += c;
+            }
+            run[e] = acc;
+        }
+        __syncthreads();
+        if (valid) sorted_pairs[wcnt[warp][ex] + rank] = tf_pair{i / K, ex, i % K, (uint32_t)weights[i]};
+        __syncthreads();
+    }
+}
+
 // ---------------------------------------------------------------------------
 // grouped small-batch expert kernels
 // ---------------------------------------------------------------------------
@@ -812,6 +933,28 @@ tf_status group_routes_strided(tf_context* ctx, void* stream, const uint32_t* in
                "numExperts must be in 1...256, got %u", num_experts);
     TF_REQUIRE(ctx, (uint64_t)query_count * top_k < (1ull << 31), TF_ERR_INVALID_ARGUMENT, "%s: too many pairs", name);
     TF_REQUIRE(ctx, idx_stride > 0, TF_ERR_INVALID_ARGUMENT, "%s: the id stride must be positive", name);
+    const uint32_t n = query_count * top_k;
+    if (n >= kGrpLargePairs && ctx->group_scratch) {
+        cudaStream_t st = static_cast<cudaStream_t>(stream);
+        uint32_t slices = (n + kGrpSliceThreads - 1) / kGrpSliceThreads;
+        const uint32_t want = (uint32_t)ctx->sm_count;
+        if (slices > want) slices = want;
+        if (slices > (uint32_t)kGrpMaxSlices) slices = kGrpMaxSlices;
+        const uint32_t slice_len = grp_slice_len(n, slices);
+        slices = (n + slice_len - 1) / slice_len;
+        const PeerWait pw = peer_wait ? *peer_wait : PeerWait{nullptr, nullptr, nullptr, 0u};
+        tf::launch_pdl(tf::group_count_kernel, dim3(slices), dim3(kGrpSliceThreads), 0, st, indices, idx_stride, ids_out, n, num_experts,
+                       slice_len, ctx->group_scratch, pw);
+        if (tf_status s = tf::check_launch(ctx, name)) return s;
+        tf::launch_pdl(tf::group_scan_kernel, dim3(1), dim3(TF_MAX_ROUTER_EXPERTS), 0, st, ctx->group_scratch, slices, n, num_experts,
+                       routes->per_expert_offsets, routes->per_expert_counts, routes->groups, routes->chunk_group, routes->chunk_start,
+                       routes->counters);
+        if (tf_status s = tf::check_launch(ctx, name)) return s;
+        tf::launch_pdl(tf::group_place_kernel, dim3(slices), dim3(kGrpSliceThreads), 0, st, indices, idx_stride,
+                       static_cast<const uint16_t*>(weights_f16), n, top_k, num_experts, slice_len,
+                       static_cast<const uint32_t*>(ctx->group_scratch), routes->sorted_pairs);
+        return tf::check_launch(ctx, name);
+    }
     tf::launch_pdl(tf::group_routes_kernel, dim3(num_experts), dim3(tf::kGroupThreads), 0, static_cast<cudaStream_t>(stream),
                    indices, idx_stride, ids_out, static_cast<const uint16_t*>(weights_f16), query_count, top_k, num_experts,
                    routes->sorted_pairs, routes->per_expert_offsets, routes->per_expert_counts, routes->groups, routes->chunk_group,
