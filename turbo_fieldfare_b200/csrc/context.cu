@@ -82,7 +82,7 @@ tf_status tf_context_create(int device, tf_context** out) {
     if (e == cudaSuccess) e = cudaMalloc(&ctx->peer_error, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->peer_error, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->streamed_scratch, tf::streamed_scratch_bytes());
-    if (e == cudaSuccess) e = cudaMalloc(&ctx->group_scratch, sizeof(uint32_t) * 256 * TF_MAX_ROUTER_EXPERTS);
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->group_scratch, sizeof(uint32_t) * 2 * 256 * TF_MAX_ROUTER_EXPERTS);     // counts, then start positions
     if (e == cudaSuccess) e = cudaMalloc(&ctx->grid_barrier, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMemset(ctx->grid_barrier, 0, sizeof(uint32_t));
     if (e == cudaSuccess) e = cudaMalloc(&ctx->qmm_groups, 2 * 64 * (TF_MAX_ROUTER_EXPERTS + 1));   // routed and dense tables

@@ -173,21 +173,18 @@ group_count_kernel(const uint32_t* __restrict__ indices, uint32_t idx_stride, ui
 }
 
 __global__ void __launch_bounds__(TF_MAX_ROUTER_EXPERTS)
-group_scan_kernel(uint32_t* __restrict__ slice_hist /* in: counts; out: start positions */, uint32_t slices, uint32_t n, uint32_t E,
+group_scan_kernel(const uint32_t* __restrict__ slice_hist, uint32_t* __restrict__ slice_start, uint32_t slices, uint32_t n, uint32_t E,
                   uint32_t* __restrict__ per_expert_offsets, uint32_t* __restrict__ per_expert_counts, tf_group* __restrict__ groups,
                   uint32_t* __restrict__ chunk_group, uint32_t* __restrict__ chunk_start, uint32_t* __restrict__ counters) {
     __shared__ uint32_t wtot[3][TF_MAX_ROUTER_EXPERTS / kWarp];
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t e = threadIdx.x, lane = threadIdx.x % kWarp, warp = threadIdx.x / kWarp, nwarps = blockDim.x / kWarp;
-    // per expert: total count, and the slices' counts turned into running sums (relative to the expert's start)
+    // per expert: total count over the slices (independent loads, no stores in between)
     uint32_t cnt = 0;
     if (e < E) {
-        for (uint32_t b = 0; b < slices; ++b) {
-            const uint32_t c = slice_hist[(size_t)b * E + e];
-            slice_hist[(size_t)b * E + e] = cnt;
-            cnt += c;
-        }
+#pragma unroll 8
+        for (uint32_t b = 0; b < slices; ++b) cnt += slice_hist[(size_t)b * E + e];
     }
     const uint32_t nch = (cnt + (uint32_t)kChunkTokens - 1) / (uint32_t)kChunkTokens;
     uint32_t i_off = cnt, i_g = cnt ? 1u : 0u, i_ch = nch;
@@ -212,7 +209,13 @@ group_scan_kernel(uint32_t* __restrict__ slice_hist /* in: counts; out: start po
             chunk_start[my_g] = my_ch;
             for (uint32_t j = 0; j < nch; ++j) chunk_group[my_ch + j] = my_g;
         }
-        for (uint32_t b = 0; b < slices; ++b) slice_hist[(size_t)b * E + e] += my_off;
+        // where each slice's pairs of this expert start
+        uint32_t running = my_off;
+#pragma unroll 8
+        for (uint32_t b = 0; b < slices; ++b) {
+            slice_start[(size_t)b * E + e] = running;
+            running += slice_hist[(size_t)b * E + e];
+        }
     }
     if (threadIdx.x == 0) { counters[0] = t_g; counters[1] = t_ch; counters[2] = n; counters[3] = t_off; }
 }
@@ -946,13 +949,15 @@ tf_status group_routes_strided(tf_context* ctx, void* stream, const uint32_t* in
         tf::launch_pdl(tf::group_count_kernel, dim3(slices), dim3(kGrpSliceThreads), 0, st, indices, idx_stride, ids_out, n, num_experts,
                        slice_len, ctx->group_scratch, pw);
         if (tf_status s = tf::check_launch(ctx, name)) return s;
-        tf::launch_pdl(tf::group_scan_kernel, dim3(1), dim3(TF_MAX_ROUTER_EXPERTS), 0, st, ctx->group_scratch, slices, n, num_experts,
+        uint32_t* slice_start = ctx->group_scratch + (size_t)kGrpMaxSlices * TF_MAX_ROUTER_EXPERTS;
+        tf::launch_pdl(tf::group_scan_kernel, dim3(1), dim3(TF_MAX_ROUTER_EXPERTS), 0, st, static_cast<const uint32_t*>(ctx->group_scratch),
+                       slice_start, slices, n, num_experts,
                        routes->per_expert_offsets, routes->per_expert_counts, routes->groups, routes->chunk_group, routes->chunk_start,
                        routes->counters);
         if (tf_status s = tf::check_launch(ctx, name)) return s;
         tf::launch_pdl(tf::group_place_kernel, dim3(slices), dim3(kGrpSliceThreads), 0, st, indices, idx_stride,
                        static_cast<const uint16_t*>(weights_f16), n, top_k, num_experts, slice_len,
-                       static_cast<const uint32_t*>(ctx->group_scratch), routes->sorted_pairs);
+                       static_cast<const uint32_t*>(slice_start), routes->sorted_pairs);
         return tf::check_launch(ctx, name);
     }
     tf::launch_pdl(tf::group_routes_kernel, dim3(num_experts), dim3(tf::kGroupThreads), 0, static_cast<cudaStream_t>(stream),

@@ -53,7 +53,7 @@ struct tf_context {
     // Optional caller-owned device buffer that the single-launch decode step fills with global-timer stamps.
     unsigned long long* step_trace = nullptr;
     uint32_t step_trace_capacity = 0;
-    // Per-slice expert histograms of the grouping of many pairs (grouped.cu): 256 slices x 256 experts.
+    // Per-slice expert histograms and start positions of the grouping of many pairs (grouped.cu): 2 x 256 slices x 256 experts.
     uint32_t* group_scratch = nullptr;
     // Group tables and tile totals of the tensor-core grouped GEMM (filled on the device per launch): one set for
     // routed launches and one for dense launches, which may run on two streams at once.
