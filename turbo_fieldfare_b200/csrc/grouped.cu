@@ -273,7 +273,11 @@ __host__ __device__ constexpr uint32_t ring_stages() { return (NMAT == 1 && KC >
 constexpr int kReducers = 2;            // reducer warps; reducer q owns the items and the partial buffer of parity q
 constexpr int kRedStages = kReducers;   // partial-sum buffers
 constexpr int kTileRows = 16;           // weight rows per MMA tile (the m of m16n8k16)
-constexpr int kRowsPerCopy = 2;         // rows per bulk copy when the rows need padding against bank conflicts (divides 8)
+constexpr int kRowsPerCopy = 4;         // rows per bulk copy when the rows need padding against bank conflicts
+// Row m of the MMA tile (m = g for the a0/a2 registers, g + 8 for a1/a3) is weight row tile_row(m) of the 16-row tile:
+// the four rows that one half warp reads in one shared-memory pass (m = 4j ... 4j + 3) then lie in the four different
+// 4-row blocks of the ring stage, whose paddings put them 32 bytes apart in the banks. No conflicts, four rows per copy.
+__host__ __device__ constexpr uint32_t tile_row(uint32_t m) { return 4u * (m & 3u) + (m >> 2); }
 constexpr int kMaxComputeWarps = 12;    // K <= 12 * 256 = 3072 columns
 constexpr uint32_t kErrTimeoutCodes = 0x7F000001u;   // device error words
 constexpr uint32_t kErrTimeoutPartials = 0x7F000003u;
@@ -375,8 +379,11 @@ struct KSplitSmem {
     // Rows whose natural stride would put a half warp's four rows on the same banks get 32 bytes of padding per
     // kRowsPerCopy rows: the loader moves kRowsPerCopy rows per bulk copy (a copy has a fixed cost of some tens of cycles
     // in the copy engine, and sixteen single-row copies per matrix kept the compute warps waiting for a third of an
-    // item's time), at the price of a two-way bank conflict between the rows of a pair.
+    // item's time); the row permutation tile_row keeps the fragment loads free of bank conflicts all the same.
     __host__ __device__ uint32_t row_pad() const { return ring_row_stride(row_bytes) - row_bytes; }
+    // weight row of the tile behind MMA row m: permuted when the rows are padded per block of kRowsPerCopy (see tile_row),
+    // the identity when the natural row stride already spreads a half warp's rows over the banks
+    __host__ __device__ uint32_t mma_row(uint32_t m) const { return row_pad() ? tile_row(m) : m; }
     __host__ __device__ uint32_t rows_per_copy() const { return row_pad() ? (uint32_t)kRowsPerCopy : (uint32_t)kTileRows; }
     __host__ __device__ uint32_t row_off(uint32_t r) const { return r * row_bytes + (r / rows_per_copy()) * row_pad(); }
     __host__ __device__ uint32_t mat_bytes() const { return kTileRows * row_bytes + (kTileRows / rows_per_copy()) * row_pad(); }
@@ -484,9 +491,10 @@ grouped_ksplit_kernel(const GroupedArgs args) {
         const uint32_t g0 = warp * kGPW;
         const uint32_t ngw = ng - g0 < (uint32_t)kGPW ? ng - g0 : (uint32_t)kGPW;     // g0 < ng by construction
         const bool sb_vec = (ng % 4) == 0;
-        const uint32_t sb_row0 = (g * ng + g0) * 2, sb_row1 = ((g + 8) * ng + g0) * 2;     // scale rows of weight rows g, g + 8
-        const uint32_t lane_code_off = lay.row_off(g) + g0 * 32 + t * 8;                // this lane's codes of row g within a matrix tile
-        const uint32_t row8_off = lay.row_off(g + 8) - lay.row_off(g);                   // row g + 8
+        const uint32_t r_lo = lay.mma_row(g), r_hi = lay.mma_row(g + 8);                       // weight rows behind MMA rows g and g + 8
+        const uint32_t sb_row0 = (r_lo * ng + g0) * 2, sb_row1 = (r_hi * ng + g0) * 2;   // their scale rows
+        const uint32_t lane_code_off = lay.row_off(r_lo) + g0 * 32 + t * 8;              // this lane's codes of MMA row g within a matrix tile
+        const uint32_t row8_off = lay.row_off(r_hi) - lay.row_off(r_lo);                 // MMA row g + 8
 
         ItemCursor<NMAT> cur;
         cur.chunk = item_begin / tiles;
@@ -701,7 +709,7 @@ grouped_ksplit_kernel(const GroupedArgs args) {
         resolve_chunk<NMAT, DENSE>(args, cur);
         if (q < n_items) advance_by(cur, q);
         uint32_t fail = 0;
-        const uint32_t row = lane >> 1, tok4 = (lane & 1) * 4;      // this lane sums one weight row for 4 consecutive tokens
+        const uint32_t row = lay.mma_row(lane >> 1), tok4 = (lane & 1) * 4;      // this lane sums one weight row (MMA row lane / 2) for 4 consecutive tokens
         const uint32_t red_q = red_base + q * lay.red_stage_bytes() + lane * 16;
         uint32_t pair_chunk = 0xFFFFFFFFu;
         uint32_t pair_base[4] = {0u, 0u, 0u, 0u};                   // (token * top_k + rank) of this lane's 4 tokens
