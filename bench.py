@@ -180,8 +180,6 @@ def run_gpu(args):
         raise SystemExit("bench.py needs a CUDA device: this library has no CPU fallback")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        # NCCL writes its version banner (NCCL_DEBUG=VERSION and above) to stdout, where the one JSON line goes
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     from turbo_fieldfare_b200.kernels import PrefillGroupedRoutedMoE, PrefillRouter, TurboContext
