@@ -298,8 +298,50 @@ def test_one_token_stack_equals_layered_path(tf_ctx, oracle):
             y_prev = y
         tf_ctx.check(lib.tf_residual_rmsnorm(tf_ctx.handle, 0, _ptr(hid2), _ptr(y_prev), None, None, 1, 256, C.c_float(1e-6)))
         torch.cuda.synchronize()
-        ref = o.f16_to_f32(from_dev(hid2, np.uint16))
+        ref_bits = from_dev(hid2, np.uint16)
+        ref = o.f16_to_f32(ref_bits)
         assert o.rel_l2(got, ref) < 2e-3
+        # the layered stack forward folds each layer's reduce into the next norm: same bits as the chain of entry points
+        hid3 = to_dev(h16.copy())
+        stack.forward(hid3, 1, stack.workspace(1))
+        torch.cuda.synchronize()
+        assert np.array_equal(from_dev(hid3, np.uint16), ref_bits)
+    finally:
+        stack.close()
+
+
+@pytest.mark.parametrize("T,d", [(7, 256), (40, 2816)])
+def test_decode_sized_stack_equals_the_chain_of_entry_points_bit_for_bit(tf_ctx, oracle, T, d):
+    """tf_stack_forward on a decode-sized batch forms the weighted sum of the route partials inside the next norm; the
+    hidden state must equal tf_residual_rmsnorm + tf_moe_block_forward layer by layer, bit for bit (d = 2816: three
+    slices of the norm's sum of squares, the last one partial)."""
+    import ctypes as C
+    import torch
+    from turbo_fieldfare_b200.kernels import _ptr
+    from turbo_fieldfare_b200.stack import MoEBlock, MoEStack
+    o = oracle
+    dims = dict(layers=3, d=d, f=128, fs=192, num_experts=16, top_k=8, seed=11, align=256)
+    stack = MoEStack(tf_ctx, **dims)
+    try:
+        rng = np.random.default_rng(T + d)
+        h16 = o.f32_to_f16(rng.standard_normal((T, d)).astype(np.float32))
+        a = to_dev(h16.copy())
+        stack.forward(a, T, stack.workspace(T))
+        lib = tf_ctx.lib
+        b = to_dev(h16.copy())
+        x = torch.zeros(T * d, dtype=torch.int16, device="cuda")
+        y = torch.zeros(T * d, dtype=torch.int16, device="cuda")
+        ws = stack.workspace(T)
+        y_prev = None
+        for l, layer in enumerate(stack.layers):
+            tf_ctx.check(lib.tf_residual_rmsnorm(tf_ctx.handle, 0, _ptr(b), _ptr(y_prev), _ptr(stack.norm_weights[l]), _ptr(x), T, d,
+                                                 C.c_float(1e-6)))
+            MoEBlock(tf_ctx, layer).forward(x, y, T, ws, stream=0)
+            y_prev = y
+        tf_ctx.check(lib.tf_residual_rmsnorm(tf_ctx.handle, 0, _ptr(b), _ptr(y_prev), None, None, T, d, C.c_float(1e-6)))
+        torch.cuda.synchronize()
+        assert tf_ctx.device_status() == 0
+        assert np.array_equal(from_dev(a, np.uint16), from_dev(b, np.uint16))
     finally:
         stack.close()
 

@@ -113,6 +113,100 @@ residual_rmsnorm_kernel(uint16_t* __restrict__ h, const uint16_t* __restrict__ y
     }
 }
 
+// The weighted sum of a decode-sized block's fp32 route partials, the residual add and the next norm in one launch:
+//   y = half(float(shared_y) + sum_r float(w_r) * partial_r)   (rank order; reduce_token_major_kernel<true>, moe.metal:473-480)
+//   h = half(h + y);  x = half(rmsnorm(h) * w)                 (residual_rmsnorm_kernel)
+// with the bits of those two kernels. One block per token, one thread per eight columns (every thread has 2 K + 2
+// 16-byte loads in flight), so the 90 KB of partials of a token do not wait on a 128-thread block. The sum of squares
+// keeps the order of residual_rmsnorm_kernel: there thread t adds the squares of its slices t, t + 128, t + 256 in turn;
+// here the thread of slice s takes over the running sum of the thread of slice s - 1 through shared memory.
+constexpr int kCrnMaxThreads = kRrnThreads * kRrnMaxSlices;      // 512: d <= 4096
+__global__ void __launch_bounds__(kCrnMaxThreads)
+combine_residual_rmsnorm_kernel(uint16_t* __restrict__ h, const float* __restrict__ partials, const uint16_t* __restrict__ route_weights,
+                                const uint16_t* __restrict__ shared_y, const uint16_t* __restrict__ w, uint16_t* __restrict__ x,
+                                uint32_t d, uint32_t top_k, float eps) {
+    __shared__ float chain[kRrnThreads];
+    __shared__ float red[kRrnThreads / kWarp];
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t vecs = d / 8, i = threadIdx.x, token = blockIdx.x;
+    const uint32_t vt = i % kRrnThreads, slice = i / kRrnThreads;
+    float v[8];
+    if (i < vecs) {
+        float4 p[TF_MAX_TOP_K][2];
+        float rw[TF_MAX_TOP_K];
+#pragma unroll
+        for (int r = 0; r < TF_MAX_TOP_K; ++r) {
+            if ((uint32_t)r < top_k) {
+                const float4* src = reinterpret_cast<const float4*>(partials + ((size_t)token * top_k + r) * d + i * 8);
+                p[r][0] = __ldg(src); p[r][1] = __ldg(src + 1);
+                rw[r] = f16_bits_to_float(__ldg(route_weights + (size_t)token * top_k + r));
+            } else {
+                p[r][0] = make_float4(0.0f, 0.0f, 0.0f, 0.0f); p[r][1] = p[r][0]; rw[r] = 0.0f;
+            }
+        }
+        const uint4 hv = *reinterpret_cast<const uint4*>(h + (size_t)token * d + i * 8);
+        uint4 sv = make_uint4(0u, 0u, 0u, 0u);
+        if (shared_y) sv = __ldg(reinterpret_cast<const uint4*>(shared_y + (size_t)token * d + i * 8));
+        const uint32_t hw[4] = {hv.x, hv.y, hv.z, hv.w}, sw[4] = {sv.x, sv.y, sv.z, sv.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 res = __half22float2(*reinterpret_cast<const __half2*>(&sw[j]));
+            float a0 = res.x, a1 = res.y;
+#pragma unroll
+            for (int r = 0; r < TF_MAX_TOP_K; ++r) {
+                if ((uint32_t)r < top_k) {
+                    const float* pr = reinterpret_cast<const float*>(&p[r][0]);
+                    a0 = __fadd_rn(a0, __fmul_rn(rw[r], pr[2 * j]));
+                    a1 = __fadd_rn(a1, __fmul_rn(rw[r], pr[2 * j + 1]));
+                }
+            }
+            const float2 yy = __half22float2(__floats2half2_rn(a0, a1));                       // y, stored as fp16 by the reduce
+            const float2 hh = __half22float2(*reinterpret_cast<const __half2*>(&hw[j]));
+            const __half2 nh = __floats2half2_rn(hh.x + yy.x, hh.y + yy.y);
+            ow[j] = *reinterpret_cast<const uint32_t*>(&nh);
+            const float2 nf = __half22float2(nh);
+            v[2 * j] = nf.x; v[2 * j + 1] = nf.y;
+        }
+        *reinterpret_cast<uint4*>(h + (size_t)token * d + i * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+    // sum of squares in the order of residual_rmsnorm_kernel
+    const uint32_t slices = (vecs + kRrnThreads - 1) / kRrnThreads;
+    if (i < kRrnThreads) chain[i] = 0.0f;
+    __syncthreads();
+    for (uint32_t s = 0; s < slices; ++s) {
+        if (slice == s && i < vecs) {
+            float acc = chain[vt];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) acc = fmaf(v[q], v[q], acc);
+            chain[vt] = acc;
+        }
+        __syncthreads();
+    }
+    if (i < kRrnThreads) {
+        const float acc = warp_sum(chain[i]);
+        if ((i & 31) == 0) red[i >> 5] = acc;
+    }
+    __syncthreads();
+    if (!x) return;
+    float tot = (threadIdx.x & 31) < (kRrnThreads / kWarp) ? red[threadIdx.x & 31] : 0.0f;
+    tot = warp_sum(tot);
+    const float inv = rsqrtf(tot / (float)d + eps);
+    if (i < vecs) {
+        const uint4 wv = __ldg(reinterpret_cast<const uint4*>(w + i * 8));
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+        uint32_t ow[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __half2 r = __floats2half2_rn(v[2 * j] * inv * bf16_bits_to_float((uint16_t)(ww[j] & 0xFFFFu)),
+                                                v[2 * j + 1] * inv * bf16_bits_to_float((uint16_t)(ww[j] >> 16)));
+            ow[j] = *reinterpret_cast<const uint32_t*>(&r);
+        }
+        *reinterpret_cast<uint4*>(x + (size_t)token * d + i * 8) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+}
+
 }  // namespace tf
 
 extern "C" {
@@ -324,12 +418,24 @@ static tf_status block_routed(tf_context* ctx, void* stream, const tf_moe_layer*
 
 extern "C" {
 
-tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer* layer,
+}  // extern "C"
+
+namespace tf {
+
+// Decode-sized blocks leave fp32 route partials that the next layer's norm can fold in (combine_residual_rmsnorm_kernel).
+static bool block_keeps_f32_partials(const tf_context* ctx, const tf_workspace* ws, uint32_t tokens) {
+    const bool tensor_path = tokens >= ctx->tensorcore_min_tokens && ws->x_sorted != nullptr;
+    return !tensor_path && ws->max_tokens <= kF32PartialTokens;
+}
+
+// tf_moe_block_forward; with y == nullptr the last step (weighted sum of the route partials plus the shared expert)
+// is left to the caller, which finds the partials, weights and shared output in the workspace.
+static tf_status block_forward(tf_context* ctx, void* stream, const tf_moe_layer* layer,
                                const void* x, uint32_t x_stride_elements,
                                void* y, uint32_t y_stride_elements, uint32_t tokens, tf_workspace* ws) {
     const char* name = "tf_moe_block_forward";
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
-    TF_REQUIRE(ctx, layer && x && y && ws, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    TF_REQUIRE(ctx, layer && x && ws, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
     TF_REQUIRE(ctx, tokens <= ws->max_tokens, TF_ERR_SCRATCH_TOO_SMALL, "%s: %u tokens exceed the workspace (%u)", name, tokens, ws->max_tokens);
     TF_REQUIRE(ctx, layer->d == ws->d && layer->f == ws->f && layer->fs == ws->fs && layer->top_k == ws->top_k &&
                         layer->num_experts == ws->num_experts,
@@ -360,12 +466,25 @@ tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer
     s = tf::block_routed(ctx, stream, layer, x, x_stride_elements, tokens, ws, tensor_path);
     TF_CUDA(ctx, cudaStreamWaitEvent(main_st, ctx->join_event, 0));
     if (s) return s;
+    if (y == nullptr) return TF_OK;
     if (tensor_path)
         return tf_ep_combine(ctx, stream, ws->partials, ws->weights, ws->inverse_perm, ws->shared_y, d, y, y_stride_elements,
                              tokens, K, d);
     const int f32 = ws->max_tokens <= tf::kF32PartialTokens ? 1 : 0;
     return tf_moe_reduce_token_major(ctx, stream, ws->partials, f32, ws->weights, ws->shared_y, d, y,
                                      y_stride_elements, tokens, K, d);
+}
+
+}  // namespace tf
+
+extern "C" {
+
+tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer* layer,
+                               const void* x, uint32_t x_stride_elements,
+                               void* y, uint32_t y_stride_elements, uint32_t tokens, tf_workspace* ws) {
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_moe_block_forward: ctx is NULL");
+    TF_REQUIRE(ctx, y != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_moe_block_forward: NULL argument");
+    return tf::block_forward(ctx, stream, layer, x, x_stride_elements, y, y_stride_elements, tokens, ws);
 }
 
 tf_status tf_residual_rmsnorm(tf_context* ctx, void* stream, void* hidden, const void* y, const void* weight_bf16,
@@ -568,15 +687,33 @@ tf_status tf_stack_forward(tf_stack* st, void* stream, void* hidden, uint32_t to
     if (tokens == 1 && ctx->single_launch_step && tf::decode_step_eligible(st, ws)) return tf::launch_decode_step(ctx, stream, st, hidden, ws);
     cudaStream_t cs = static_cast<cudaStream_t>(stream);
     uint16_t* h = static_cast<uint16_t*>(hidden);
+    // Decode-sized steps: the weighted sum of a layer's route partials, the residual add and the next norm are one
+    // launch (combine_residual_rmsnorm_kernel; the values of the separate reduce and norm launches, two launches less).
+    const bool fold = !st->layers.empty() && tf::block_keeps_f32_partials(ctx, ws, tokens) && st->layers[0].top_k <= TF_MAX_TOP_K &&
+                      tf::aligned(ws->partials, 16) && tf::aligned(ws->shared_y, 16);
+    uint32_t fold_threads = ((d / 8 + 31) / 32) * 32;          // one thread per eight columns,
+    if (fold_threads < (uint32_t)tf::kRrnThreads) fold_threads = tf::kRrnThreads;      // at least the norm's 128 (its reduction tree)
+    const uint16_t* no16 = nullptr;
+    uint16_t* no_x = nullptr;
     for (size_t l = 0; l < st->layers.size(); ++l) {
-        tf::launch_pdl(tf::residual_rmsnorm_kernel, dim3(tokens), dim3(tf::kRrnThreads), smem, cs, h,
-                       l == 0 ? static_cast<const uint16_t*>(nullptr) : static_cast<const uint16_t*>(ws->y_block),
-                       static_cast<const uint16_t*>(st->norm_weights[l]), ws->x_norm, d, st->eps);
+        const uint16_t* nw = static_cast<const uint16_t*>(st->norm_weights[l]);
+        if (l > 0 && fold)
+            tf::launch_pdl(tf::combine_residual_rmsnorm_kernel, dim3(tokens), dim3(fold_threads), smem, cs, h,
+                           static_cast<const float*>(ws->partials), static_cast<const uint16_t*>(ws->weights),
+                           static_cast<const uint16_t*>(ws->shared_y), nw, ws->x_norm, d, st->layers[l - 1].top_k, st->eps);
+        else
+            tf::launch_pdl(tf::residual_rmsnorm_kernel, dim3(tokens), dim3(tf::kRrnThreads), smem, cs, h,
+                           l == 0 ? no16 : static_cast<const uint16_t*>(ws->y_block), nw, ws->x_norm, d, st->eps);
         if (tf_status s = tf::check_launch(ctx, "residual_rmsnorm")) return s;
-        if (tf_status s = tf_moe_block_forward(ctx, stream, &st->layers[l], ws->x_norm, d, ws->y_block, d, tokens, ws)) return s;
+        if (tf_status s = tf::block_forward(ctx, stream, &st->layers[l], ws->x_norm, d, fold ? nullptr : ws->y_block, d, tokens, ws)) return s;
     }
-    tf::launch_pdl(tf::residual_rmsnorm_kernel, dim3(tokens), dim3(tf::kRrnThreads), smem, cs, h, static_cast<const uint16_t*>(ws->y_block),
-                   static_cast<const uint16_t*>(nullptr), static_cast<uint16_t*>(nullptr), d, st->eps);
+    if (fold)
+        tf::launch_pdl(tf::combine_residual_rmsnorm_kernel, dim3(tokens), dim3(fold_threads), smem, cs, h,
+                       static_cast<const float*>(ws->partials), static_cast<const uint16_t*>(ws->weights),
+                       static_cast<const uint16_t*>(ws->shared_y), no16, no_x, d, st->layers.back().top_k, st->eps);
+    else
+        tf::launch_pdl(tf::residual_rmsnorm_kernel, dim3(tokens), dim3(tf::kRrnThreads), smem, cs, h,
+                       static_cast<const uint16_t*>(ws->y_block), no16, no_x, d, st->eps);
     return tf::check_launch(ctx, "residual_add");
 }
 
