@@ -120,26 +120,38 @@ residual_rmsnorm_kernel(uint16_t* __restrict__ h, const uint16_t* __restrict__ y
 // 16-byte loads in flight), so the 90 KB of partials of a token do not wait on a 128-thread block. The sum of squares
 // keeps the order of residual_rmsnorm_kernel: there thread t adds the squares of its slices t, t + 128, t + 256 in turn;
 // here the thread of slice s takes over the running sum of the thread of slice s - 1 through shared memory.
+// ROWS: the block's results are fp16 rows reached through a permutation (the expert-parallel combine, and prefill-sized
+// blocks): y = half(sum_r fma(float(w_r), float(rows[perm[t, r]]), acc) + float(shared_y)) (ep_combine_kernel), and the rows
+// may still be on their way from peers (peer_wait).
 constexpr int kCrnMaxThreads = kRrnThreads * kRrnMaxSlices;      // 512: d <= 4096
+template <bool ROWS>
 __global__ void __launch_bounds__(kCrnMaxThreads)
-combine_residual_rmsnorm_kernel(uint16_t* __restrict__ h, const float* __restrict__ partials, const uint16_t* __restrict__ route_weights,
-                                const uint16_t* __restrict__ shared_y, const uint16_t* __restrict__ w, uint16_t* __restrict__ x,
-                                uint32_t d, uint32_t top_k, float eps) {
+combine_residual_rmsnorm_kernel(uint16_t* __restrict__ h, const void* __restrict__ results, const uint16_t* __restrict__ route_weights,
+                                const uint32_t* __restrict__ inverse_perm, const uint16_t* __restrict__ shared_y,
+                                const uint16_t* __restrict__ w, uint16_t* __restrict__ x, uint32_t d, uint32_t top_k, float eps,
+                                const PeerWait peer_wait) {
     __shared__ float chain[kRrnThreads];
     __shared__ float red[kRrnThreads / kWarp];
     pdl_launch_dependents();
     pdl_wait();
+    if constexpr (ROWS) peer_wait_in_block(peer_wait);
     const uint32_t vecs = d / 8, i = threadIdx.x, token = blockIdx.x;
     const uint32_t vt = i % kRrnThreads, slice = i / kRrnThreads;
     float v[8];
     if (i < vecs) {
-        float4 p[TF_MAX_TOP_K][2];
+        float4 p[TF_MAX_TOP_K][2];          // fp32 partials, or (ROWS) the eight fp16 values of a row in p[r][0]
         float rw[TF_MAX_TOP_K];
 #pragma unroll
         for (int r = 0; r < TF_MAX_TOP_K; ++r) {
             if ((uint32_t)r < top_k) {
-                const float4* src = reinterpret_cast<const float4*>(partials + ((size_t)token * top_k + r) * d + i * 8);
-                p[r][0] = __ldg(src); p[r][1] = __ldg(src + 1);
+                if constexpr (ROWS) {
+                    const uint32_t slot = __ldg(inverse_perm + (size_t)token * top_k + r);
+                    const uint4 rv = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(results) + (size_t)slot * d + i * 8);
+                    p[r][0] = make_float4(__uint_as_float(rv.x), __uint_as_float(rv.y), __uint_as_float(rv.z), __uint_as_float(rv.w));
+                } else {
+                    const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(results) + ((size_t)token * top_k + r) * d + i * 8);
+                    p[r][0] = __ldg(src); p[r][1] = __ldg(src + 1);
+                }
                 rw[r] = f16_bits_to_float(__ldg(route_weights + (size_t)token * top_k + r));
             } else {
                 p[r][0] = make_float4(0.0f, 0.0f, 0.0f, 0.0f); p[r][1] = p[r][0]; rw[r] = 0.0f;
@@ -153,13 +165,27 @@ combine_residual_rmsnorm_kernel(uint16_t* __restrict__ h, const float* __restric
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float2 res = __half22float2(*reinterpret_cast<const __half2*>(&sw[j]));
-            float a0 = res.x, a1 = res.y;
+            float a0, a1;
+            if constexpr (ROWS) {
+                a0 = 0.0f; a1 = 0.0f;
 #pragma unroll
-            for (int r = 0; r < TF_MAX_TOP_K; ++r) {
-                if ((uint32_t)r < top_k) {
-                    const float* pr = reinterpret_cast<const float*>(&p[r][0]);
-                    a0 = __fadd_rn(a0, __fmul_rn(rw[r], pr[2 * j]));
-                    a1 = __fadd_rn(a1, __fmul_rn(rw[r], pr[2 * j + 1]));
+                for (int r = 0; r < TF_MAX_TOP_K; ++r) {
+                    if ((uint32_t)r < top_k) {
+                        const uint32_t pair = __float_as_uint(reinterpret_cast<const float*>(&p[r][0])[j]);
+                        a0 = fmaf(rw[r], f16_bits_to_float((uint16_t)(pair & 0xFFFFu)), a0);
+                        a1 = fmaf(rw[r], f16_bits_to_float((uint16_t)(pair >> 16)), a1);
+                    }
+                }
+                if (shared_y) { a0 += res.x; a1 += res.y; }
+            } else {
+                a0 = res.x; a1 = res.y;
+#pragma unroll
+                for (int r = 0; r < TF_MAX_TOP_K; ++r) {
+                    if ((uint32_t)r < top_k) {
+                        const float* pr = reinterpret_cast<const float*>(&p[r][0]);
+                        a0 = __fadd_rn(a0, __fmul_rn(rw[r], pr[2 * j]));
+                        a1 = __fadd_rn(a1, __fmul_rn(rw[r], pr[2 * j + 1]));
+                    }
                 }
             }
             const float2 yy = __half22float2(__floats2half2_rn(a0, a1));                       // y, stored as fp16 by the reduce
@@ -477,6 +503,32 @@ static tf_status block_forward(tf_context* ctx, void* stream, const tf_moe_layer
 
 }  // namespace tf
 
+namespace tf {
+
+// h += y, x = rmsnorm(h) * w with y formed from fp16 result rows through a permutation (see combine_residual_rmsnorm_kernel);
+// norm_weight_bf16 and x may be NULL (the closing residual add of a stack).
+tf_status combine_rows_residual_rmsnorm(tf_context* ctx, void* stream, void* hidden, const void* rows, const void* route_weights,
+                                        const uint32_t* inverse_perm, const void* shared_y, const void* norm_weight_bf16, void* x,
+                                        uint32_t tokens, uint32_t top_k, uint32_t d, float eps, const PeerWait* peer_wait) {
+    const char* name = "combine_rows_residual_rmsnorm";
+    TF_REQUIRE(ctx, hidden && rows && route_weights && inverse_perm && (x == nullptr || norm_weight_bf16 != nullptr), TF_ERR_INVALID_ARGUMENT,
+               "%s: NULL argument", name);
+    TF_REQUIRE(ctx, d % 8 == 0 && d <= 8u * kCrnMaxThreads && top_k > 0 && top_k <= TF_MAX_TOP_K, TF_ERR_UNSUPPORTED,
+               "%s: D must be a multiple of 8 up to %d and top_k at most %d", name, 8 * kCrnMaxThreads, TF_MAX_TOP_K);
+    TF_REQUIRE(ctx, aligned(hidden, 16) && aligned(rows, 16) && aligned(shared_y, 16) && aligned(norm_weight_bf16, 16) && aligned(x, 16),
+               TF_ERR_ALIGNMENT, "%s: buffers must be 16-byte aligned", name);
+    if (tokens == 0) return TF_OK;
+    uint32_t threads = ((d / 8 + 31) / 32) * 32;
+    if (threads < (uint32_t)kRrnThreads) threads = kRrnThreads;
+    launch_pdl(combine_residual_rmsnorm_kernel<true>, dim3(tokens), dim3(threads), 0, static_cast<cudaStream_t>(stream),
+               static_cast<uint16_t*>(hidden), rows, static_cast<const uint16_t*>(route_weights), inverse_perm,
+               static_cast<const uint16_t*>(shared_y), static_cast<const uint16_t*>(norm_weight_bf16), static_cast<uint16_t*>(x), d, top_k, eps,
+               peer_wait ? *peer_wait : PeerWait{nullptr, nullptr, nullptr, 0u});
+    return check_launch(ctx, name);
+}
+
+}  // namespace tf
+
 extern "C" {
 
 tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer* layer,
@@ -694,13 +746,15 @@ tf_status tf_stack_forward(tf_stack* st, void* stream, void* hidden, uint32_t to
     uint32_t fold_threads = ((d / 8 + 31) / 32) * 32;          // one thread per eight columns,
     if (fold_threads < (uint32_t)tf::kRrnThreads) fold_threads = tf::kRrnThreads;      // at least the norm's 128 (its reduction tree)
     const uint16_t* no16 = nullptr;
+    const uint32_t* no32u = nullptr;
     uint16_t* no_x = nullptr;
+    const tf::PeerWait no_wait{nullptr, nullptr, nullptr, 0u};
     for (size_t l = 0; l < st->layers.size(); ++l) {
         const uint16_t* nw = static_cast<const uint16_t*>(st->norm_weights[l]);
         if (l > 0 && fold)
-            tf::launch_pdl(tf::combine_residual_rmsnorm_kernel, dim3(tokens), dim3(fold_threads), smem, cs, h,
-                           static_cast<const float*>(ws->partials), static_cast<const uint16_t*>(ws->weights),
-                           static_cast<const uint16_t*>(ws->shared_y), nw, ws->x_norm, d, st->layers[l - 1].top_k, st->eps);
+            tf::launch_pdl(tf::combine_residual_rmsnorm_kernel<false>, dim3(tokens), dim3(fold_threads), smem, cs, h,
+                           static_cast<const void*>(ws->partials), static_cast<const uint16_t*>(ws->weights), no32u,
+                           static_cast<const uint16_t*>(ws->shared_y), nw, ws->x_norm, d, st->layers[l - 1].top_k, st->eps, no_wait);
         else
             tf::launch_pdl(tf::residual_rmsnorm_kernel, dim3(tokens), dim3(tf::kRrnThreads), smem, cs, h,
                            l == 0 ? no16 : static_cast<const uint16_t*>(ws->y_block), nw, ws->x_norm, d, st->eps);
@@ -708,9 +762,9 @@ tf_status tf_stack_forward(tf_stack* st, void* stream, void* hidden, uint32_t to
         if (tf_status s = tf::block_forward(ctx, stream, &st->layers[l], ws->x_norm, d, fold ? nullptr : ws->y_block, d, tokens, ws)) return s;
     }
     if (fold)
-        tf::launch_pdl(tf::combine_residual_rmsnorm_kernel, dim3(tokens), dim3(fold_threads), smem, cs, h,
-                       static_cast<const float*>(ws->partials), static_cast<const uint16_t*>(ws->weights),
-                       static_cast<const uint16_t*>(ws->shared_y), no16, no_x, d, st->layers.back().top_k, st->eps);
+        tf::launch_pdl(tf::combine_residual_rmsnorm_kernel<false>, dim3(tokens), dim3(fold_threads), smem, cs, h,
+                       static_cast<const void*>(ws->partials), static_cast<const uint16_t*>(ws->weights), no32u,
+                       static_cast<const uint16_t*>(ws->shared_y), no16, no_x, d, st->layers.back().top_k, st->eps, no_wait);
     else
         tf::launch_pdl(tf::residual_rmsnorm_kernel, dim3(tokens), dim3(tf::kRrnThreads), smem, cs, h,
                        static_cast<const uint16_t*>(ws->y_block), no16, no_x, d, st->eps);

@@ -64,6 +64,9 @@ tf_status ep_experts_tensorcore_waiting(tf_context* ctx, void* stream, const voi
                                         const void* zero_weights, const void* one_weights, void* x_sorted, uint32_t* row_ids,
                                         uint32_t* inverse_perm, void* acts_scratch, void* out_sorted, void* out_rows,
                                         uint32_t d, uint32_t f, uint32_t recv_row_stride_elements, const struct PeerWait* peer_wait);
+tf_status combine_rows_residual_rmsnorm(tf_context* ctx, void* stream, void* hidden, const void* rows, const void* route_weights,
+                                        const uint32_t* inverse_perm, const void* shared_y, const void* norm_weight_bf16, void* x,
+                                        uint32_t tokens, uint32_t top_k, uint32_t d, float eps, const struct PeerWait* peer_wait);
 tf_status ep_combine_waiting(tf_context* ctx, void* stream, const void* returned_rows, const void* route_weights,
                              const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
                              void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d,

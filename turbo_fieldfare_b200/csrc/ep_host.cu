@@ -403,12 +403,24 @@ tf_status tf_ep_buffers_create(tf_ep* ep, uint32_t max_tokens, uint32_t d, uint3
 tf_ep_mode tf_ep_buffers_mode(const tf_ep_buffers* b) { return b ? b->mode : TF_EP_EXACT; }
 tf_workspace* tf_ep_buffers_workspace(const tf_ep_buffers* b) { return b ? b->ws : nullptr; }
 
-tf_status tf_moe_block_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* layer, const void* x, void* y, uint32_t tokens,
-                                  tf_ep_buffers* b) {
+}  // extern "C"
+
+namespace tf {
+
+// What the combine of a layer needs, for a caller that folds it into its next launch.
+struct EpPendingCombine {
+    const uint16_t* back = nullptr;      // returned result rows
+    PeerWait wait{nullptr, nullptr, nullptr, 0u};
+    bool has_wait = false;
+};
+
+// tf_moe_block_forward_ep; with y == nullptr the weighted combine is left to the caller (`pending` says from what).
+static tf_status block_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* layer, const void* x, void* y, uint32_t tokens,
+                                  tf_ep_buffers* b, EpPendingCombine* pending) {
     const char* name = "tf_moe_block_forward_ep";
     TF_REQUIRE(nullptr, ep != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ep is NULL", name);
     tf_context* ctx = ep->ctx;
-    TF_REQUIRE(ctx, layer && x && y && b && b->ep == ep, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument or buffers of another communicator", name);
+    TF_REQUIRE(ctx, layer && x && (y || pending) && b && b->ep == ep, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument or buffers of another communicator", name);
     TF_REQUIRE(ctx, tokens <= b->max_tokens, TF_ERR_SCRATCH_TOO_SMALL, "%s: %u tokens exceed the buffers (%u)", name, tokens, b->max_tokens);
     TF_REQUIRE(ctx, layer->d == b->d && layer->f == b->f && layer->fs == b->fs && layer->top_k == b->top_k && layer->num_experts == b->num_experts,
                TF_ERR_DIMENSION_MISMATCH, "%s: layer dimensions differ from the buffers", name);
@@ -564,8 +576,22 @@ tf_status tf_moe_block_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* l
     }
     TF_CUDA(ctx, cudaStreamWaitEvent(st, ctx->join_event, 0));
     (void)n_pairs;
+    if (y == nullptr) {
+        pending->back = back; pending->wait = peer_wait; pending->has_wait = peer;
+        return TF_OK;
+    }
     return tf::ep_combine_waiting(ctx, stream, back, ws->weights, b->inverse, ws->shared_y, d, y, d, tokens, K, d,
                                   peer ? &peer_wait : nullptr);
+}
+
+}  // namespace tf
+
+extern "C" {
+
+tf_status tf_moe_block_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* layer, const void* x, void* y, uint32_t tokens,
+                                  tf_ep_buffers* b) {
+    TF_REQUIRE(ep ? ep->ctx : nullptr, y != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_moe_block_forward_ep: NULL argument");
+    return tf::block_forward_ep(ep, stream, layer, x, y, tokens, b, nullptr);
 }
 
 tf_status tf_stack_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* layers, const void* const* norm_weights_bf16,
@@ -576,14 +602,35 @@ tf_status tf_stack_forward_ep(tf_ep* ep, void* stream, const tf_moe_layer* layer
     TF_REQUIRE(ctx, layers && norm_weights_bf16 && hidden && b, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
     TF_REQUIRE(ctx, tokens <= b->max_tokens, TF_ERR_SCRATCH_TOO_SMALL, "%s: %u tokens exceed the buffers (%u)", name, tokens, b->max_tokens);
     if (tokens == 0 || layer_count == 0) return TF_OK;
+    // The weighted combine of layer l - 1, its residual add and the norm of layer l are one launch when the layout
+    // allows (16-byte rows, top_k <= 8, D <= 4096); otherwise combine, then tf_residual_rmsnorm.
+    const uint32_t d = b->d;
+    const bool fold = d % 8 == 0 && d <= 4096 && b->top_k <= TF_MAX_TOP_K && tf::aligned(hidden, 16);
     const void* y_prev = nullptr;
+    tf::EpPendingCombine pending;
+    bool have_pending = false;
+    tf_workspace* ws = b->ws;
     for (uint32_t l = 0; l < layer_count; ++l) {
-        // x = rmsnorm(h + y_prev) * w_l (the residual add of layer l - 1 is fused into the norm of layer l)
-        if (tf_status s = tf_residual_rmsnorm(ctx, stream, hidden, y_prev, norm_weights_bf16[l], b->x_norm, tokens, b->d, eps)) return s;
-        if (tf_status s = tf_moe_block_forward_ep(ep, stream, &layers[l], b->x_norm, b->y_block, tokens, b)) return s;
-        y_prev = b->y_block;
+        tf_status s;
+        if (have_pending)
+            s = tf::combine_rows_residual_rmsnorm(ctx, stream, hidden, pending.back, tf_workspace_weights(ws), b->inverse, ws->shared_y,
+                                                  norm_weights_bf16[l], b->x_norm, tokens, b->top_k, d, eps,
+                                                  pending.has_wait ? &pending.wait : nullptr);
+        else
+            s = tf_residual_rmsnorm(ctx, stream, hidden, y_prev, norm_weights_bf16[l], b->x_norm, tokens, d, eps);
+        if (s) return s;
+        if (fold) {
+            if ((s = tf::block_forward_ep(ep, stream, &layers[l], b->x_norm, nullptr, tokens, b, &pending)) != TF_OK) return s;
+            have_pending = true;
+        } else {
+            if ((s = tf::block_forward_ep(ep, stream, &layers[l], b->x_norm, b->y_block, tokens, b, nullptr)) != TF_OK) return s;
+            y_prev = b->y_block;
+        }
     }
-    return tf_residual_rmsnorm(ctx, stream, hidden, y_prev, nullptr, nullptr, tokens, b->d, eps);
+    if (have_pending)
+        return tf::combine_rows_residual_rmsnorm(ctx, stream, hidden, pending.back, tf_workspace_weights(ws), b->inverse, ws->shared_y,
+                                                 nullptr, nullptr, tokens, b->top_k, d, eps, pending.has_wait ? &pending.wait : nullptr);
+    return tf_residual_rmsnorm(ctx, stream, hidden, y_prev, nullptr, nullptr, tokens, d, eps);
 }
 
 }  // extern "C"
