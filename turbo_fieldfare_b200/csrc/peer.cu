@@ -98,20 +98,27 @@ ep_pack_push_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride,
                     uint64_t flags_offset_bytes, uint32_t* __restrict__ epoch_and_ticket, uint32_t* __restrict__ error,
                     uint32_t* __restrict__ overflow) {
     __shared__ uint32_t dst_base[33], dst_count[32];
-    if (threadIdx.x < world) {
-        // pairs are sorted by expert and experts are contiguous per rank: a destination's pairs are one run
-        uint32_t before = 0, mine = 0;
-        for (uint32_t e = 0; e < (threadIdx.x + 1) * experts_per_rank && e < num_experts; ++e) {
-            const uint32_t c = per_expert_counts[e];
-            if (e < threadIdx.x * experts_per_rank) before += c; else mine += c;
-        }
-        dst_base[threadIdx.x] = before;
-        dst_count[threadIdx.x] = mine;
-        if (mine > cap && blockIdx.x == 0) atomicMax(overflow, mine);
-    }
-    __syncthreads();
     const uint32_t warps_per_block = kPeerPushThreads / kWarp;
     const uint32_t lane = threadIdx.x % kWarp;
+    // pairs are sorted by expert and experts are contiguous per rank: a destination's pairs are one run. A warp sums a
+    // destination's expert counts (independent loads), then one thread prefixes the at most 32 totals.
+    for (uint32_t r = threadIdx.x / kWarp; r < world; r += warps_per_block) {
+        uint32_t c = 0;
+        for (uint32_t e = r * experts_per_rank + lane; e < (r + 1) * experts_per_rank && e < num_experts; e += kWarp) c += per_expert_counts[e];
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) c += __shfl_xor_sync(kFullMask, c, off);
+        if (lane == 0) dst_count[r] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        uint32_t run = 0;
+        for (uint32_t r = 0; r < world; ++r) {
+            dst_base[r] = run;
+            run += dst_count[r];
+            if (dst_count[r] > cap && blockIdx.x == 0) atomicMax(overflow, dst_count[r]);
+        }
+    }
+    __syncthreads();
     const uint32_t total = world * cap;
     for (uint32_t slot = blockIdx.x * warps_per_block + threadIdx.x / kWarp; slot < total; slot += gridDim.x * warps_per_block) {
         const uint32_t dst = slot / cap, pos = slot % cap;
