@@ -40,6 +40,24 @@ __device__ __forceinline__ void peer_barrier_in_block(uint8_t* const* __restrict
     if constexpr (WAIT) peer_wait_flag(reinterpret_cast<const uint32_t*>(peers[me] + flags_offset_bytes) + r, epoch, error);
 }
 
+// A warp copies nvec 16-byte pieces with eight loads per lane in flight before the first store (a row is a few
+// hundred pieces: one load per trip would pay the memory latency a dozen times in a row).
+__device__ __forceinline__ void warp_copy_u4(const uint4* __restrict__ in, uint4* __restrict__ out, uint32_t nvec, uint32_t lane) {
+    for (uint32_t v0 = lane; v0 < nvec; v0 += kWarp * 8) {
+        uint4 t[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const uint32_t v = v0 + q * kWarp;
+            if (v < nvec) t[q] = in[v];
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            const uint32_t v = v0 + q * kWarp;
+            if (v < nvec) out[v] = t[q];
+        }
+    }
+}
+
 // One warp per slot (source rank block s, slot j). A slot is in use when its expert id is not 0xFFFFFFFF: the id is
 // read from `ids` when given, else from the row's tail (element `tail_at`, as 32 bits). Used slots are copied
 // (`copy_elems` fp16 elements, a multiple of 8) into peer s's buffer at block `me`; with tails, an unused slot gets
@@ -61,9 +79,7 @@ ep_peer_push_kernel(const uint16_t* __restrict__ src, uint32_t src_stride, uint8
         else id = *reinterpret_cast<const uint32_t*>(row + tail_at);
         uint16_t* dst = reinterpret_cast<uint16_t*>(peers[s] + dst_offset_bytes) + ((size_t)me * cap + j) * dst_stride;
         if (id != 0xFFFFFFFFu) {
-            const uint4* in = reinterpret_cast<const uint4*>(row);
-            uint4* out = reinterpret_cast<uint4*>(dst);
-            for (uint32_t v = lane; v < copy_elems / 8; v += kWarp) out[v] = in[v];
+            warp_copy_u4(reinterpret_cast<const uint4*>(row), reinterpret_cast<uint4*>(dst), copy_elems / 8, lane);
         } else if (!ids && lane == 0) {
             *reinterpret_cast<uint4*>(dst + tail_at) = *reinterpret_cast<const uint4*>(row + tail_at);
         }
@@ -128,9 +144,8 @@ ep_pack_push_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride,
             continue;
         }
         const tf_pair pr = sorted_pairs[dst_base[dst] + pos];
-        const uint4* in = reinterpret_cast<const uint4*>(hidden + (size_t)pr.token * hidden_stride);
         uint4* out = reinterpret_cast<uint4*>(out_row);
-        for (uint32_t v = lane; v < d / 8; v += kWarp) out[v] = __ldg(in + v);
+        warp_copy_u4(reinterpret_cast<const uint4*>(hidden + (size_t)pr.token * hidden_stride), out, d / 8, lane);
         if (lane == 0) {
             out[d / 8] = make_uint4(pr.expert % experts_per_rank, 0u, 0u, 0u);
             inverse_perm[pr.token * top_k + pr.rank] = slot;
