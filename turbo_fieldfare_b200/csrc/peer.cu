@@ -31,9 +31,11 @@ __device__ __forceinline__ void peer_barrier_in_block(uint8_t* const* __restrict
     if (threadIdx.x == 0) {
         epoch = *epoch_counter + 1u;
         *epoch_counter = epoch;
+        // One system-scope fence by the thread that saw every block's ticket: it orders all rows written before the
+        // tickets (each block fenced before its own) ahead of the flag stores below, which follow it through the block barrier.
+        __threadfence_system();
     }
     __syncthreads();
-    __threadfence_system();
     const uint32_t r = threadIdx.x;
     if (r >= world) return;
     st_release_sys(reinterpret_cast<uint32_t*>(peers[r] + flags_offset_bytes) + me, epoch);
@@ -84,19 +86,23 @@ ep_peer_push_kernel(const uint16_t* __restrict__ src, uint32_t src_stride, uint8
             *reinterpret_cast<uint4*>(dst + tail_at) = *reinterpret_cast<const uint4*>(row + tail_at);
         }
     }
-    __threadfence_system();
-    if (epoch_and_ticket == nullptr) return;
-    // the block that finishes last runs the flag barrier (word 0: epoch, word 1: self-resetting ticket)
+    // The block's rows are ordered before its ticket by ONE system-scope fence: the block barrier makes the fencing
+    // thread the successor of every thread's stores, and a fence is cumulative over what its thread has synchronised with.
     __shared__ bool last;
     __syncthreads();
     if (threadIdx.x == 0) {
-        const uint32_t tk = atomicAdd(&epoch_and_ticket[1], 1u);
-        last = tk == gridDim.x - 1;
-        if (last) epoch_and_ticket[1] = 0u;
+        __threadfence_system();
+        if (epoch_and_ticket != nullptr) {
+            // the block that finishes last runs the flag barrier (word 0: epoch, word 1: self-resetting ticket)
+            const uint32_t tk = atomicAdd(&epoch_and_ticket[1], 1u);
+            last = tk == gridDim.x - 1;
+            if (last) epoch_and_ticket[1] = 0u;
+        } else {
+            last = false;
+        }
     }
     __syncthreads();
     if (!last) return;
-    __threadfence();
     peer_barrier_in_block<WAIT>(peers, flags_offset_bytes, epoch_and_ticket, error, world, me);
 }
 
@@ -151,17 +157,16 @@ ep_pack_push_kernel(const uint16_t* __restrict__ hidden, uint32_t hidden_stride,
             inverse_perm[pr.token * top_k + pr.rank] = slot;
         }
     }
-    __threadfence_system();
     __shared__ bool last;
     __syncthreads();
     if (threadIdx.x == 0) {
+        __threadfence_system();          // this block's rows before its ticket (see ep_peer_push_kernel)
         const uint32_t tk = atomicAdd(&epoch_and_ticket[1], 1u);
         last = tk == gridDim.x - 1;
         if (last) epoch_and_ticket[1] = 0u;
     }
     __syncthreads();
     if (!last) return;
-    __threadfence();
     peer_barrier_in_block<WAIT>(peers, flags_offset_bytes, epoch_and_ticket, error, world, me);
 }
 
