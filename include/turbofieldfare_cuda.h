@@ -297,7 +297,9 @@ tf_status tf_group_pairs(const tf_pair* host_pairs, uint32_t pair_count,
  * empty slot and is skipped. No sort keys and no
  * tiles: tiles exist in the reference only to bound SSD slots. Replaces the
  * CPU stage PrefillRouter.makeTokenExpertPairs + PrefillMoEGrouping
- * (RealForwardRunner.swift:945-979). */
+ * (RealForwardRunner.swift:945-979). From 4096 pairs on the call is three
+ * launches that share a scratch area of the context, so such calls on one
+ * context must not overlap (use one stream, or a context per stream). */
 tf_status tf_group_routes_device(tf_context* ctx, void* stream,
                                  const uint32_t* indices, const void* weights_f16,
                                  uint32_t query_count, uint32_t top_k, uint32_t num_experts,
