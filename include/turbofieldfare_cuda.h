@@ -595,6 +595,16 @@ const tf_device_routes* tf_workspace_routes(const tf_workspace* ws);
 tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer* layer,
                                const void* x, uint32_t x_stride_elements,
                                void* y, uint32_t y_stride_elements, uint32_t tokens, tf_workspace* ws);
+/* The same block on bf16 activation rows (the prefill configuration that names bf16 tiles): x is converted to fp16 on
+ * entry -- exact for every bf16 value that is zero or inside fp16's normal range, 6.1e-5 ... 65504 in magnitude, which
+ * normalised activations are -- the block runs as above (its fp16 weight tiles carry three more significant bits than
+ * bf16 tiles would), and y is rounded to bf16 on exit. Uses the workspace's stack scratch for the fp16 copies. */
+tf_status tf_moe_block_forward_bf16(tf_context* ctx, void* stream, const tf_moe_layer* layer,
+                                    const void* x_bf16, uint32_t x_stride_elements,
+                                    void* y_bf16, uint32_t y_stride_elements, uint32_t tokens, tf_workspace* ws);
+/* dst = src converted between fp16 and bf16, row by row (16-byte aligned rows, D a multiple of 8). */
+tf_status tf_convert_rows(tf_context* ctx, void* stream, const void* src, tf_dtype src_dtype, uint32_t src_stride_elements,
+                          void* dst, tf_dtype dst_dtype, uint32_t dst_stride_elements, uint32_t rows, uint32_t d);
 
 /* A stack of MoE blocks with RMSNorm between layers and a residual stream:
  * x = rmsnorm(h) * w_l; h = h + block_l(x). hidden is fp16 [tokens, d], in place. */

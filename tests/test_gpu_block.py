@@ -195,6 +195,44 @@ def test_block_forward_prefill_sized_runs_on_tensor_cores(tf_ctx, oracle, produc
         layer.set_logit_bias(None)
 
 
+@pytest.mark.parametrize("T", [5, 4096])
+def test_block_forward_bf16_rows(tf_ctx, oracle, production_layer, T):
+    """BASELINE config 3 names bf16 activations: the block takes bf16 rows, converts them to fp16 exactly (every bf16
+    value of normalised activations is an fp16 value), and rounds its result to bf16. Same router decisions as the oracle
+    on every row; outputs within 1e-2 relative L2 plus the bf16 rounding of the result (2^-9)."""
+    import torch
+    from turbo_fieldfare_b200.stack import MoEBlock, Workspace
+    o = oracle
+    layer, pool = production_layer
+    rng = np.random.default_rng(300 + T)
+    p = 1.0 / (rng.permutation(128) + 1) ** 1.1
+    bias = np.log(p / p.sum()).astype(np.float32)
+    layer.set_logit_bias(bias)
+    try:
+        xb = o.f32_to_bf16(rng.standard_normal((T, 2816)).astype(np.float32))
+        x16 = o.f32_to_f16(o.bf16_to_f32(xb))
+        xf = o.bf16_to_f32(xb)
+        normal = np.abs(xf) >= 2.0 ** -14
+        assert np.array_equal(o.f16_to_f32(x16)[normal], xf[normal])             # exact inside fp16's normal range
+        assert np.max(np.abs(o.f16_to_f32(x16) - xf)) <= 2.0 ** -25              # below it: fp16's subnormal spacing
+        ws = Workspace(tf_ctx, T, 2816, 704, 2112, 8, 128)
+        y = torch.zeros(T * 2816, dtype=torch.int16, device="cuda")
+        MoEBlock(tf_ctx, layer).forward_bf16(to_dev(xb), y, T, ws)
+        torch.cuda.synchronize()
+        assert tf_ctx.device_status() == 0
+        idx_gpu, _ = ws.routing(T)
+        idx_all, _, _ = _oracle_block(o, layer, pool, x16, (), logit_bias=bias)
+        assert np.array_equal(idx_gpu, idx_all), "top-k indices differ from the oracle on some row"
+        check = _sample_rows(idx_all, T, 16, T)
+        _, y_ref, _ = _oracle_block(o, layer, pool, x16, check, logit_bias=bias)
+        got = o.bf16_to_f32(from_dev(y, np.uint16).reshape(T, 2816))
+        assert np.isfinite(got).all()
+        for i, t in enumerate(check):
+            assert o.rel_l2(got[t], y_ref[i]) < TOL + 2.0 ** -8, f"token {t}"
+    finally:
+        layer.set_logit_bias(None)
+
+
 def test_small_stack_matches_oracle(tf_ctx, oracle):
     """Config-4 structure at small dimensions: 3 layers, RMSNorm between layers, residual stream."""
     import torch

@@ -169,6 +169,8 @@ SIGNATURES = {
     "tf_workspace_weights": (vp, [vp]),
     "tf_workspace_routes": (C.POINTER(DeviceRoutes), [vp]),
     "tf_moe_block_forward": (C.c_int, [vp, vp, C.POINTER(MoELayer), vp, u32, vp, u32, u32, vp]),
+    "tf_moe_block_forward_bf16": (C.c_int, [vp, vp, C.POINTER(MoELayer), vp, u32, vp, u32, u32, vp]),
+    "tf_convert_rows": (C.c_int, [vp, vp, vp, C.c_int, u32, vp, C.c_int, u32, u32, u32]),
     "tf_stack_create": (C.c_int, [vp, C.POINTER(MoELayer), C.POINTER(vp), u32, f32, C.POINTER(vp)]),
     "tf_stack_destroy": (None, [vp]),
     "tf_stack_forward": (C.c_int, [vp, vp, vp, u32, vp]),

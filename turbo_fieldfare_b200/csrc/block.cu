@@ -113,6 +113,35 @@ residual_rmsnorm_kernel(uint16_t* __restrict__ h, const uint16_t* __restrict__ y
     }
 }
 
+// Rows of 16-bit floats from one format into the other (TO_BF16 = false: bf16 -> fp16, exact for every value whose
+// magnitude is zero or within fp16's normal range, since bf16 carries 8 significant bits and fp16 11; TO_BF16 = true:
+// fp16 -> bf16, round to nearest even). Eight elements per thread.
+template <bool TO_BF16>
+__global__ void convert_rows_kernel(const uint16_t* __restrict__ src, uint32_t src_stride, uint16_t* __restrict__ dst, uint32_t dst_stride,
+                                    uint32_t rows, uint32_t d) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t vecs = d / 8;
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (uint64_t)rows * vecs) return;
+    const uint32_t r = (uint32_t)(i / vecs), c = (uint32_t)(i % vecs);
+    const uint4 v = *reinterpret_cast<const uint4*>(src + (size_t)r * src_stride + c * 8);
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w};
+    uint32_t out[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if constexpr (TO_BF16) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&in[j]));
+            const __nv_bfloat162 b = __floats2bfloat162_rn(f.x, f.y);
+            out[j] = *reinterpret_cast<const uint32_t*>(&b);
+        } else {
+            const __half2 h = __floats2half2_rn(bf16_bits_to_float((uint16_t)(in[j] & 0xFFFFu)), bf16_bits_to_float((uint16_t)(in[j] >> 16)));
+            out[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+    }
+    *reinterpret_cast<uint4*>(dst + (size_t)r * dst_stride + c * 8) = make_uint4(out[0], out[1], out[2], out[3]);
+}
+
 // The weighted sum of a decode-sized block's fp32 route partials, the residual add and the next norm in one launch:
 //   y = half(float(shared_y) + sum_r float(w_r) * partial_r)   (rank order; reduce_token_major_kernel<true>, moe.metal:473-480)
 //   h = half(h + y);  x = half(rmsnorm(h) * w)                 (residual_rmsnorm_kernel)
@@ -537,6 +566,45 @@ tf_status tf_moe_block_forward(tf_context* ctx, void* stream, const tf_moe_layer
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_moe_block_forward: ctx is NULL");
     TF_REQUIRE(ctx, y != nullptr, TF_ERR_INVALID_ARGUMENT, "tf_moe_block_forward: NULL argument");
     return tf::block_forward(ctx, stream, layer, x, x_stride_elements, y, y_stride_elements, tokens, ws);
+}
+
+tf_status tf_convert_rows(tf_context* ctx, void* stream, const void* src, tf_dtype src_dtype, uint32_t src_stride_elements,
+                          void* dst, tf_dtype dst_dtype, uint32_t dst_stride_elements, uint32_t rows, uint32_t d) {
+    const char* name = "tf_convert_rows";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, src && dst, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
+    TF_REQUIRE(ctx, (src_dtype == TF_BF16 && dst_dtype == TF_FP16) || (src_dtype == TF_FP16 && dst_dtype == TF_BF16), TF_ERR_INVALID_ARGUMENT,
+               "%s: one side must be fp16 and the other bf16", name);
+    TF_REQUIRE(ctx, d % 8 == 0 && src_stride_elements >= d && dst_stride_elements >= d && src_stride_elements % 8 == 0 &&
+                        dst_stride_elements % 8 == 0 && tf::aligned(src, 16) && tf::aligned(dst, 16),
+               TF_ERR_ALIGNMENT, "%s: rows must be 16-byte aligned and D a multiple of 8", name);
+    if (rows == 0 || d == 0) return TF_OK;
+    const uint64_t n = (uint64_t)rows * (d / 8);
+    const dim3 grid((uint32_t)((n + 255) / 256));
+    if (dst_dtype == TF_BF16)
+        tf::launch_pdl(tf::convert_rows_kernel<true>, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(src),
+                       src_stride_elements, static_cast<uint16_t*>(dst), dst_stride_elements, rows, d);
+    else
+        tf::launch_pdl(tf::convert_rows_kernel<false>, grid, dim3(256), 0, static_cast<cudaStream_t>(stream), static_cast<const uint16_t*>(src),
+                       src_stride_elements, static_cast<uint16_t*>(dst), dst_stride_elements, rows, d);
+    return tf::check_launch(ctx, name);
+}
+
+tf_status tf_moe_block_forward_bf16(tf_context* ctx, void* stream, const tf_moe_layer* layer,
+                                    const void* x_bf16, uint32_t x_stride_elements,
+                                    void* y_bf16, uint32_t y_stride_elements, uint32_t tokens, tf_workspace* ws) {
+    const char* name = "tf_moe_block_forward_bf16";
+    TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
+    TF_REQUIRE(ctx, layer && x_bf16 && y_bf16 && ws, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    TF_REQUIRE(ctx, tokens <= ws->max_tokens, TF_ERR_SCRATCH_TOO_SMALL, "%s: %u tokens exceed the workspace (%u)", name, tokens, ws->max_tokens);
+    TF_REQUIRE(ctx, layer->d == ws->d, TF_ERR_DIMENSION_MISMATCH, "%s: layer dimensions differ from the workspace", name);
+    if (tokens == 0) return TF_OK;
+    const uint32_t d = ws->d;
+    // bf16 rows are exact in fp16 inside fp16's normal range, so the block computes on the same activation values; its fp16
+    // weight tiles carry three more significant bits than bf16 tiles would. The workspace's stack scratch holds both copies.
+    if (tf_status s = tf_convert_rows(ctx, stream, x_bf16, TF_BF16, x_stride_elements, ws->x_norm, TF_FP16, d, tokens, d)) return s;
+    if (tf_status s = tf::block_forward(ctx, stream, layer, ws->x_norm, d, ws->y_block, d, tokens, ws)) return s;
+    return tf_convert_rows(ctx, stream, ws->y_block, TF_FP16, d, y_bf16, TF_BF16, y_stride_elements, tokens, d);
 }
 
 tf_status tf_residual_rmsnorm(tf_context* ctx, void* stream, void* hidden, const void* y, const void* weight_bf16,

@@ -221,6 +221,12 @@ class MoEBlock:
         ctx.check(ctx.lib.tf_moe_block_forward(ctx.handle, _stream(stream), C.byref(self._c), _ptr(x), self.layer.d,
                                                _ptr(y), self.layer.d, tokens, ws.handle))
 
+    def forward_bf16(self, x: torch.Tensor, y: torch.Tensor, tokens: int, ws: Workspace, stream=None) -> None:
+        """The same block on bf16 rows in and out (exact conversion to fp16 on entry, rounding to bf16 on exit)."""
+        ctx = self.context
+        ctx.check(ctx.lib.tf_moe_block_forward_bf16(ctx.handle, _stream(stream), C.byref(self._c), _ptr(x), self.layer.d,
+                                                    _ptr(y), self.layer.d, tokens, ws.handle))
+
 
 class MoEStack:
     """Synthetic stack of MoE blocks with RMSNorm between layers (attention omitted)."""
