@@ -202,8 +202,14 @@ def run_gpu(args):
         p = 1.0 / (rng.permutation(E) + 1) ** 1.1
         stack.set_logit_bias(np.log(p / p.sum()).astype(np.float32))
     if ep:
-        ws_prefill = stack.buffers(prefill_tokens, fixed_capacity=False)
         peer = args.ep_exchange == "peer"
+        if args.ep_prefill == "peer" and peer:
+            # no host in the prefill layer loop either: fixed-capacity slots over peer memory, expert phase on the tensor
+            # cores (a local expert expects thousands of rows there, tens in the decode steps)
+            ctx.set_ep_tensorcore_min_rows_per_expert(256)
+            ws_prefill = stack.buffers(prefill_tokens, fixed_capacity=True, peer=True)
+        else:
+            ws_prefill = stack.buffers(prefill_tokens, fixed_capacity=False)
         ws_b1 = stack.buffers(1, fixed_capacity=True, peer=peer)
         ws_bn = stack.buffers(batch, fixed_capacity=True, peer=peer)
     else:
@@ -798,6 +804,9 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of layer-0 outputs after the timed regions")
     ap.add_argument("--single-launch-step", type=int, default=0,
                     help="one-token steps as one persistent launch (1) or layer by layer (0); single GPU only")
+    ap.add_argument("--ep-prefill", default="peer", choices=["exact", "peer"],
+                    help="expert-parallel prefill exchange: exact row counts over NCCL (one host read-back per layer) or "
+                         "fixed-capacity slots over peer memory (no host in the layer loop)")
     ap.add_argument("--cpu-sample-tokens", type=int, default=256)
     args = ap.parse_args()
     if args.warmup < 3 and args.impl == "b200":

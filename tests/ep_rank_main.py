@@ -56,6 +56,21 @@ def main(out_dir: str) -> None:
             torch.cuda.synchronize()
             worst = max(worst, float((a - static_h.float()).norm() / a.norm()))
         buf.close()
+    # a prefill-sized block without the host in the layer loop: fixed-capacity slots over peer memory, and the owner's
+    # expert phase on the tensor cores (most slots of the receive area are empty)
+    ctx.set_ep_tensorcore_min_rows_per_expert(1)
+    for T in (70, 300):
+        g = torch.Generator().manual_seed(41 + rank + T)
+        h = torch.randn(T, 256, generator=g).half().cuda()
+        h_ref, h_ep = h.clone(), h.clone()
+        ref_stack.forward(h_ref, T, ref_stack.workspace(T))
+        buf = ep_stack.buffers(T, True, peer=True)
+        ep_stack.forward(h_ep, T, buf)
+        torch.cuda.synchronize()
+        a = h_ref.float()
+        worst = max(worst, float((a - h_ep.float()).norm() / a.norm()))
+        buf.close()
+    ctx.set_ep_tensorcore_min_rows_per_expert(0xFFFFFFFF)
     assert ctx.device_status() == 0
     np.save(os.path.join(out_dir, f"err_{rank}.npy"), np.array(worst))
     dist.barrier()

@@ -732,7 +732,9 @@ tf_status ep_experts_tensorcore_waiting(tf_context* ctx, void* stream, const voi
     s = tf_grouped_moe_tensorcore(ctx, stream, x_sorted, recv_slots, pool_layer_base, expert_stride, local_experts, offsets,
                                   recv_routes, acts_scratch, out_sorted, d, f);
     if (s) return s;
-    return tf_ep_combine(ctx, stream, out_sorted, one_weights, inverse_perm, nullptr, d, out_rows, d, recv_slots, 1, d);
+    // back into slot order; with id tails (a fixed-capacity buffer) the empty slots are left alone
+    return tf::ep_combine_waiting(ctx, stream, out_sorted, one_weights, inverse_perm, nullptr, d, out_rows, d, recv_slots, 1, d, nullptr,
+                                  stride > d ? recv_expert_ids : nullptr);
 }
 
 }  // namespace tf

@@ -70,6 +70,6 @@ tf_status combine_rows_residual_rmsnorm(tf_context* ctx, void* stream, void* hid
 tf_status ep_combine_waiting(tf_context* ctx, void* stream, const void* returned_rows, const void* route_weights,
                              const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
                              void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d,
-                             const struct PeerWait* peer_wait);
+                             const struct PeerWait* peer_wait, const uint32_t* skip_ids = nullptr);
 }  // namespace tf
 

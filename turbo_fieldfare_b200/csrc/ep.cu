@@ -98,11 +98,12 @@ template <bool VEC>
 __global__ void ep_combine_kernel(const uint16_t* __restrict__ rows, const uint16_t* __restrict__ weights,
                                   const uint32_t* __restrict__ inverse_perm, const uint16_t* __restrict__ residual,
                                   uint32_t residual_stride, uint16_t* __restrict__ out, uint32_t out_stride,
-                                  uint32_t T, uint32_t K, uint32_t D, const PeerWait peer_wait) {
+                                  uint32_t T, uint32_t K, uint32_t D, const PeerWait peer_wait, const uint32_t* __restrict__ skip_ids) {
     peer_wait_in_block(peer_wait);      // the rows may come from peers that are still writing them
     // rows in grid.x (up to 2^31 - 1 blocks), column blocks in grid.y: an expert-parallel rank can hold more than 65535 rows
     const uint32_t t = blockIdx.x;
     if (t >= T) return;
+    if (skip_ids && skip_ids[t] == 0xFFFFFFFFu) return;      // an empty slot of a fixed-capacity exchange buffer
     if constexpr (VEC) {
         const uint32_t c = blockIdx.y * blockDim.x + threadIdx.x;          // group of eight columns
         if (c >= D / 8) return;
@@ -230,7 +231,7 @@ namespace tf {
 tf_status ep_combine_waiting(tf_context* ctx, void* stream, const void* returned_rows, const void* route_weights,
                              const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
                              void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d,
-                             const PeerWait* peer_wait) {
+                             const PeerWait* peer_wait, const uint32_t* skip_ids) {
     const char* name = "tf_ep_combine";
     TF_REQUIRE(ctx, ctx != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: ctx is NULL", name);
     TF_REQUIRE(ctx, returned_rows && route_weights && inverse_perm && out, TF_ERR_INVALID_ARGUMENT, "%s: NULL buffer", name);
@@ -246,13 +247,13 @@ tf_status ep_combine_waiting(tf_context* ctx, void* stream, const void* returned
         tf::ep_combine_kernel<true><<<grid, threads, 0, static_cast<cudaStream_t>(stream)>>>(
             static_cast<const uint16_t*>(returned_rows), static_cast<const uint16_t*>(route_weights), inverse_perm,
             static_cast<const uint16_t*>(residual), residual_stride_elements, static_cast<uint16_t*>(out), out_stride_elements,
-            query_count, top_k, d, pw);
+            query_count, top_k, d, pw, skip_ids);
     } else {
         dim3 grid(query_count, (d + 255) / 256);
         tf::ep_combine_kernel<false><<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
             static_cast<const uint16_t*>(returned_rows), static_cast<const uint16_t*>(route_weights), inverse_perm,
             static_cast<const uint16_t*>(residual), residual_stride_elements, static_cast<uint16_t*>(out), out_stride_elements,
-            query_count, top_k, d, pw);
+            query_count, top_k, d, pw, skip_ids);
     }
     return tf::check_launch(ctx, name);
 }
@@ -265,7 +266,7 @@ tf_status tf_ep_combine(tf_context* ctx, void* stream, const void* returned_rows
                         const uint32_t* inverse_perm, const void* residual, uint32_t residual_stride_elements,
                         void* out, uint32_t out_stride_elements, uint32_t query_count, uint32_t top_k, uint32_t d) {
     return tf::ep_combine_waiting(ctx, stream, returned_rows, route_weights, inverse_perm, residual, residual_stride_elements, out,
-                                  out_stride_elements, query_count, top_k, d, nullptr);
+                                  out_stride_elements, query_count, top_k, d, nullptr, nullptr);
 }
 
 }  // extern "C"
