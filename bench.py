@@ -201,7 +201,26 @@ def run_gpu(args):
         rng = np.random.default_rng(17)
         p = 1.0 / (rng.permutation(E) + 1) ** 1.1
         stack.set_logit_bias(np.log(p / p.sum()).astype(np.float32))
+    placement_record = None
     if ep:
+        if args.ep_placement == "balanced":
+            # Static placement by measured load: a calibration batch of other tokens than the timed ones goes through the
+            # stack one layer at a time, the per-expert pair counts of all ranks are summed, and every layer's experts
+            # are renumbered so that the 128/N-expert shards carry equal load (the weights and the outputs are the same).
+            from turbo_fieldfare_b200.ep import balanced_placement, shard_imbalance
+            calib_tokens = 1024
+            calib = torch.randn(calib_tokens, D, generator=torch.Generator().manual_seed(777 + rank)).half().cuda()
+            calib_buf = stack.buffers(calib_tokens, fixed_capacity=False)
+            load = stack.expert_load(calib, calib_tokens, calib_buf)
+            placement = balanced_placement(ctx.lib, load, world)
+            stack.set_placement(placement)
+            calib_buf.close()
+            placement_record = {"kind": "balanced", "calibration": f"{calib_tokens} seeded tokens per rank, not the timed inputs",
+                                "hot_over_mean_shard_calibration": {
+                                    "contiguous": float(shard_imbalance(load, None, world).mean()),
+                                    "balanced": float(shard_imbalance(load, placement, world).mean())}}
+        else:
+            placement_record = {"kind": "contiguous"}
         peer = args.ep_exchange == "peer"
         prefill_peer = (args.ep_prefill == "peer" or (args.ep_prefill == "auto" and world <= 4)) and peer
         if prefill_peer:
@@ -224,6 +243,15 @@ def run_gpu(args):
     host_out_dec1 = torch.empty_like(host_dec1).pin_memory()
     host_out_decn = torch.empty_like(host_decn).pin_memory()
     dev_prefill, dev_dec1, dev_decn = host_prefill.cuda(), host_dec1.cuda(), host_decn.cuda()
+    if ep and placement_record is not None:
+        # what the placement does on the TIMED prefill inputs (hot shard's rows over the mean shard's, mean over layers)
+        from turbo_fieldfare_b200.ep import shard_imbalance
+        timed_buf = stack.buffers(prefill_tokens, fixed_capacity=False)
+        timed_load = stack.expert_load(dev_prefill, prefill_tokens, timed_buf)
+        timed_buf.close()
+        placement_record["hot_over_mean_shard_timed_prefill"] = {
+            "contiguous": float(shard_imbalance(timed_load, None, world).mean()),
+            "as_placed": float(shard_imbalance(timed_load, stack.placement, world).mean())}
     work_prefill = torch.empty_like(dev_prefill)
     out_dec1, out_decn = torch.empty_like(dev_dec1), torch.empty_like(dev_decn)
     h1 = torch.zeros(1, D, dtype=torch.float16, device="cuda")
@@ -373,7 +401,7 @@ def run_gpu(args):
         "config": {"workload": workload_name(args.layers, prefill_tokens, steps_dec, batch),
                    "tokens_per_step": tokens, "routing": "zipf(1.1) logit bias" if args.zipf else "computed logits",
                    "l2": "every step streams 13.2 GB of distinct layer weights (>> 126 MB L2)",
-                   "cuda_graphs": use_graphs, "device_status": device_code,
+                   "cuda_graphs": use_graphs, "device_status": device_code, "expert_placement": placement_record,
                    "parallelism": (f"ep{world}: experts sharded {E // world} per GPU; prefill: "
                                    + ("fixed-capacity slots over peer memory, expert phase on the tensor cores, no host "
                                       "read-back in the layer loop" if prefill_peer and ws_prefill.peer
@@ -809,6 +837,9 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of layer-0 outputs after the timed regions")
     ap.add_argument("--single-launch-step", type=int, default=0,
                     help="one-token steps as one persistent launch (1) or layer by layer (0); single GPU only")
+    ap.add_argument("--ep-placement", default="balanced", choices=["contiguous", "balanced"],
+                    help="expert parallelism: experts in contiguous shards, or renumbered per layer so that the shards "
+                         "carry equal load on a seeded calibration batch (not the timed inputs)")
     ap.add_argument("--ep-prefill", default="auto", choices=["auto", "exact", "peer"],
                     help="expert-parallel prefill exchange: exact row counts over NCCL (one host read-back per layer) or "
                          "fixed-capacity slots over peer memory (no host in the layer loop); auto: peer up to four ranks "

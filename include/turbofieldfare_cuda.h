@@ -501,6 +501,10 @@ tf_status tf_fill_affine_synthetic(tf_context* ctx, void* stream, void* weights,
  * sharded); blobs are seeded by the global expert id, so shards hold the bytes of the whole pool. */
 tf_status tf_expert_pool_fill_synthetic(tf_pool* pool, void* stream, uint64_t seed, uint32_t d, uint32_t f,
                                         uint32_t global_experts, uint32_t expert_offset);
+/* The same for a shard that holds an arbitrary selection of the experts: slot e of layer l gets the bytes of expert
+ * original_ids[l * experts + e] (HOST array, layers * experts entries, each < global_experts) of the whole pool. */
+tf_status tf_expert_pool_fill_synthetic_placed(tf_pool* pool, void* stream, uint64_t seed, uint32_t d, uint32_t f,
+                                               uint32_t global_experts, const uint32_t* original_ids);
 
 /* ---- .gturbo model directory -> HBM ----
  * Reader of the installed model format: manifest.json, packed_experts/layout.json, packed_experts/<layer files>
@@ -776,6 +780,16 @@ tf_status tf_ep_create_from_comm(tf_context* ctx, void* nccl_comm, int rank, int
 void tf_ep_destroy(tf_ep* ep);
 int tf_ep_rank(const tf_ep* ep);
 int tf_ep_world(const tf_ep* ep);
+/* Expert placement by measured load (host only, no device work). The library shards experts contiguously: rank r owns
+ * ids [r * E / world, (r + 1) * E / world). A host that wants the ranks equally loaded renumbers the experts of a layer
+ * when it loads the weights: placement[l * E + new_id] = original id, the router's rows (weights, scales, biases,
+ * per-expert scale, logit bias) and the pool slots stored in the new order. Outputs do not change (the router only
+ * reports other ids for the same experts; exactly equal logits may break their tie the other way).
+ * counts[l * E + e]: routed (token, rank) pairs that expert e of layer l received on a calibration batch, summed over
+ * all ranks' tokens. Per layer, experts are taken by descending count (ties by id) and each goes to the least loaded
+ * rank that still has a free slot (ties to the lowest rank); a rank's slots are filled in that order. */
+tf_status tf_ep_balanced_placement(const uint64_t* counts, uint32_t layers, uint32_t num_experts, uint32_t world,
+                                   uint32_t* placement);
 /* Exchange buffers and scratch for up to max_tokens LOCAL tokens. Collective: every rank asks for the same buffers in
  * the same order (the peer mode maps the ranks' buffers into one another). Allocates device memory. */
 tf_status tf_ep_buffers_create(tf_ep* ep, uint32_t max_tokens, uint32_t d, uint32_t f, uint32_t fs, uint32_t top_k,

@@ -71,6 +71,29 @@ def main(out_dir: str) -> None:
         worst = max(worst, float((a - h_ep.float()).norm() / a.norm()))
         buf.close()
     ctx.set_ep_tensorcore_min_rows_per_expert(0xFFFFFFFF)
+    # experts placed by the load of a calibration batch: the shards level out, the load per original expert id and the
+    # outputs stay those of the contiguous placement
+    from turbo_fieldfare_b200.ep import balanced_placement, shard_imbalance
+    g = torch.Generator().manual_seed(53 + rank)
+    calib = torch.randn(96, 256, generator=g).half().cuda()
+    exact = ep_stack.buffers(96, False)
+    load = ep_stack.expert_load(calib, 96, exact)
+    assert int(load.sum()) == 2 * 2 * 96 * 8
+    placement = balanced_placement(ctx.lib, load, 2)
+    assert np.all(shard_imbalance(load, placement, 2) <= shard_imbalance(load, None, 2) + 1e-12)
+    ep_stack.set_placement(placement)
+    assert np.array_equal(ep_stack.expert_load(calib, 96, exact), load)
+    for T, fixed, peer in ((70, False, False), (6, True, True), (1, True, True)):
+        g = torch.Generator().manual_seed(67 + rank + T)
+        h = torch.randn(T, 256, generator=g).half().cuda()
+        h_ref, h_ep = h.clone(), h.clone()
+        ref_stack.forward(h_ref, T, ref_stack.workspace(T))
+        buf = ep_stack.buffers(T, fixed, peer=peer)
+        ep_stack.forward(h_ep, T, buf)
+        torch.cuda.synchronize()
+        a = h_ref.float()
+        worst = max(worst, float((a - h_ep.float()).norm() / a.norm()))
+        buf.close()
     assert ctx.device_status() == 0
     np.save(os.path.join(out_dir, f"err_{rank}.npy"), np.array(worst))
     dist.barrier()

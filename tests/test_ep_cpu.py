@@ -103,3 +103,59 @@ def test_plan_dispatch_orders_and_inverse():
     assert eloc2[3] == EMPTY_SLOT and inv2.reshape(3, 3).tolist() == [[8, 0, 5], [6, 13, 2], [1, 12, 4]]
     with pytest.raises(ValueError):
         plan_dispatch(np.zeros((5, 1), dtype=np.uint32), 2, 4, capacity=4)
+
+
+def _lpt_reference(counts, world):
+    """Numpy restatement of the rule tf_ep_balanced_placement documents."""
+    L, E = counts.shape
+    per = E // world
+    out = np.zeros((L, E), dtype=np.uint32)
+    for l in range(L):
+        order = sorted(range(E), key=lambda e: (-int(counts[l, e]), e))
+        used, load = [0] * world, [0] * world
+        for e in order:
+            free = [r for r in range(world) if used[r] < per]
+            best = min(free, key=lambda r: (load[r], r))
+            out[l, best * per + used[best]] = e
+            used[best] += 1
+            load[best] += int(counts[l, e])
+    return out
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_balanced_placement_is_a_permutation_and_levels_the_shards(world):
+    """Host-only entry of the library (no device work): per layer a permutation, equal to the documented greedy rule,
+    and never worse balanced than contiguous shards."""
+    from turbo_fieldfare_b200 import _capi
+    from turbo_fieldfare_b200.ep import balanced_placement, shard_imbalance
+    lib = _capi.load()
+    rng = np.random.default_rng(7 + world)
+    L, E = 5, 128
+    counts = np.floor(rng.pareto(1.2, size=(L, E)) * 100).astype(np.uint64)
+    counts[3] = 11                                   # all equal: identity
+    counts[4, :] = 0
+    counts[4, 5] = 1000                              # one expert takes everything
+    placement = balanced_placement(lib, counts, world)
+    assert placement.shape == (L, E) and placement.dtype == np.uint32
+    for l in range(L):
+        assert sorted(placement[l].tolist()) == list(range(E))
+    assert np.array_equal(placement, _lpt_reference(counts, world))
+    before = shard_imbalance(counts, None, world)
+    after = shard_imbalance(counts, placement, world)
+    assert np.all(after <= before + 1e-12)
+    if world > 1:
+        # heavy-tailed loads: the greedy rule lands within 4/3 of the larger of (mean, largest single expert)
+        per_rank_mean = counts[:3].sum(axis=1) / world
+        bound = np.maximum(per_rank_mean, counts[:3].max(axis=1)) * (4.0 / 3.0)
+        placed = np.take_along_axis(counts, placement.astype(np.int64), axis=1)[:3].reshape(3, world, -1).sum(axis=2).max(axis=1)
+        assert np.all(placed <= bound + 1)
+
+
+def test_balanced_placement_rejects_bad_arguments():
+    from turbo_fieldfare_b200 import _capi
+    from turbo_fieldfare_b200.ep import balanced_placement
+    lib = _capi.load()
+    with pytest.raises(ValueError):
+        balanced_placement(lib, np.ones((2, 10), np.uint64), 4)          # 10 experts do not divide over 4 ranks
+    with pytest.raises(ValueError):
+        balanced_placement(lib, np.ones(10, np.uint64), 2)               # not [layers, experts]

@@ -106,6 +106,46 @@ def test_single_rank_ep_stack_matches_fused_stack(tf_ctx, oracle, T, fixed):
     ep_stack.close()
 
 
+@pytest.mark.parametrize("T,fixed", [(1, True), (6, True), (70, False)])
+def test_renumbered_experts_leave_the_outputs_alone(tf_ctx, oracle, T, fixed):
+    """Experts placed by load: router rows and pool slots stored in another order. The measured load per ORIGINAL expert
+    id and the stack's output must be those of the original numbering (one rank: the placement is the experts sorted
+    by descending load, a non-trivial permutation)."""
+    import torch
+    from turbo_fieldfare_b200.ep import ExpertParallelStack, balanced_placement
+    from turbo_fieldfare_b200.stack import MoEStack
+    o = oracle
+    dims = dict(layers=2, d=256, f=128, fs=192, num_experts=16, top_k=8, seed=5, align=256)
+    ref_stack = MoEStack(tf_ctx, **dims)
+    ep_stack = ExpertParallelStack(tf_ctx, **dims)
+    rng = np.random.default_rng(900 + T)
+    calib = to_dev(o.f32_to_f16(rng.standard_normal((40, 256)).astype(np.float32)))
+    exact = ep_stack.buffers(40, False)
+    load = ep_stack.expert_load(calib, 40, exact)
+    assert load.shape == (2, 16) and np.all(load.sum(axis=1) == 40 * 8)
+    placement = balanced_placement(tf_ctx.lib, load, 1)
+    assert any(not np.array_equal(placement[l], np.arange(16)) for l in range(2))
+    ep_stack.set_placement(placement)
+    assert np.array_equal(ep_stack.expert_load(calib, 40, exact), load)
+    h16 = o.f32_to_f16(rng.standard_normal((T, 256)).astype(np.float32))
+    h_ref, h_ep = to_dev(h16.copy()), to_dev(h16.copy())
+    ref_stack.forward(h_ref, T, ref_stack.workspace(T))
+    ep_stack.forward(h_ep, T, ep_stack.buffers(T, fixed))
+    torch.cuda.synchronize()
+    assert tf_ctx.device_status() == 0
+    a = o.f16_to_f32(from_dev(h_ref, np.uint16))
+    b = o.f16_to_f32(from_dev(h_ep, np.uint16))
+    assert o.rel_l2(b, a) < 3e-3
+    # back to the original numbering: the contiguous stack again
+    ep_stack.set_placement(None)
+    h_back = to_dev(h16.copy())
+    ep_stack.forward(h_back, T, ep_stack.buffers(T, fixed))
+    torch.cuda.synchronize()
+    assert o.rel_l2(o.f16_to_f32(from_dev(h_back, np.uint16)), a) < 3e-3
+    ref_stack.close()
+    ep_stack.close()
+
+
 @pytest.mark.parametrize("T,tensor_rows", [(1, 0), (6, 0), (64, 0), (6, 1), (64, 1), (64, 100000)])
 def test_single_rank_peer_exchange_matches_fused_stack_and_replays_in_a_graph(tf_ctx, oracle, T, tensor_rows):
     """The peer-memory exchange with one rank (the rank pushes into its own buffer and passes its own flag barrier):

@@ -162,6 +162,8 @@ SIGNATURES = {
     "tf_gturbo_model_resident_base": (vp, [vp]),
     "tf_fill_affine_synthetic": (C.c_int, [vp, vp, vp, vp, vp, u32, u32, u32, u64]),
     "tf_expert_pool_fill_synthetic": (C.c_int, [vp, vp, u64, u32, u32, u32, u32]),
+    "tf_expert_pool_fill_synthetic_placed": (C.c_int, [vp, vp, u64, u32, u32, u32, vp]),
+    "tf_ep_balanced_placement": (C.c_int, [vp, u32, u32, u32, vp]),
     "tf_workspace_create": (C.c_int, [vp, u32, u32, u32, u32, u32, u32, C.POINTER(vp)]),
     "tf_workspace_destroy": (None, [vp]),
     "tf_workspace_bytes": (u64, [vp]),

@@ -343,6 +343,24 @@ tf_status tf_fill_affine_synthetic(tf_context* ctx, void* stream, void* weights,
     return tf::check_launch(ctx, name);
 }
 
+static tf_status fill_pool_synthetic(tf_pool* pool, void* stream, uint64_t seed, uint32_t d, uint32_t f,
+                                     uint32_t global_experts, uint32_t expert_offset, const uint32_t* original_ids) {
+    tf_context* ctx = pool->ctx;
+    const tf_expert_offsets& o = pool->offsets;
+    for (uint32_t l = 0; l < pool->layers; ++l)
+        for (uint32_t e = 0; e < pool->experts; ++e) {
+            uint8_t* b = const_cast<uint8_t*>(static_cast<const uint8_t*>(tf_expert_pool_ptr(pool, l, e)));
+            // seeded by the GLOBAL expert id, so a shard holds the same bytes as the unsharded pool
+            const uint32_t id = original_ids ? original_ids[(size_t)l * pool->experts + e] : expert_offset + e;
+            const uint64_t s0 = seed + ((uint64_t)l * global_experts + id) * 3;
+            tf_status s = tf_fill_affine_synthetic(ctx, stream, b + o.gate_w_off, b + o.gate_s_off, b + o.gate_b_off, f, d, 4, s0);
+            if (!s) s = tf_fill_affine_synthetic(ctx, stream, b + o.up_w_off, b + o.up_s_off, b + o.up_b_off, f, d, 4, s0 + 1);
+            if (!s) s = tf_fill_affine_synthetic(ctx, stream, b + o.down_w_off, b + o.down_s_off, b + o.down_b_off, d, f, 4, s0 + 2);
+            if (s) return s;
+        }
+    return TF_OK;
+}
+
 tf_status tf_expert_pool_fill_synthetic(tf_pool* pool, void* stream, uint64_t seed, uint32_t d, uint32_t f,
                                         uint32_t global_experts, uint32_t expert_offset) {
     const char* name = "tf_expert_pool_fill_synthetic";
@@ -351,18 +369,20 @@ tf_status tf_expert_pool_fill_synthetic(tf_pool* pool, void* stream, uint64_t se
     if (global_experts == 0) global_experts = pool->experts;
     TF_REQUIRE(ctx, expert_offset + pool->experts <= global_experts, TF_ERR_INVALID_ARGUMENT,
                "%s: shard [%u, %u) exceeds %u experts", name, expert_offset, expert_offset + pool->experts, global_experts);
-    const tf_expert_offsets& o = pool->offsets;
-    for (uint32_t l = 0; l < pool->layers; ++l)
-        for (uint32_t e = 0; e < pool->experts; ++e) {
-            uint8_t* b = const_cast<uint8_t*>(static_cast<const uint8_t*>(tf_expert_pool_ptr(pool, l, e)));
-            // seeded by the GLOBAL expert id, so a shard holds the same bytes as the unsharded pool
-            const uint64_t s0 = seed + ((uint64_t)l * global_experts + expert_offset + e) * 3;
-            tf_status s = tf_fill_affine_synthetic(ctx, stream, b + o.gate_w_off, b + o.gate_s_off, b + o.gate_b_off, f, d, 4, s0);
-            if (!s) s = tf_fill_affine_synthetic(ctx, stream, b + o.up_w_off, b + o.up_s_off, b + o.up_b_off, f, d, 4, s0 + 1);
-            if (!s) s = tf_fill_affine_synthetic(ctx, stream, b + o.down_w_off, b + o.down_s_off, b + o.down_b_off, d, f, 4, s0 + 2);
-            if (s) return s;
-        }
-    return TF_OK;
+    return fill_pool_synthetic(pool, stream, seed, d, f, global_experts, expert_offset, nullptr);
+}
+
+tf_status tf_expert_pool_fill_synthetic_placed(tf_pool* pool, void* stream, uint64_t seed, uint32_t d, uint32_t f,
+                                               uint32_t global_experts, const uint32_t* original_ids) {
+    const char* name = "tf_expert_pool_fill_synthetic_placed";
+    TF_REQUIRE(nullptr, pool != nullptr, TF_ERR_INVALID_ARGUMENT, "%s: pool is NULL", name);
+    tf_context* ctx = pool->ctx;
+    TF_REQUIRE(ctx, original_ids != nullptr && global_experts >= pool->experts, TF_ERR_INVALID_ARGUMENT,
+               "%s: NULL id table or fewer global experts than slots", name);
+    for (size_t i = 0; i < (size_t)pool->layers * pool->experts; ++i)
+        TF_REQUIRE(ctx, original_ids[i] < global_experts, TF_ERR_INVALID_ARGUMENT, "%s: id %u of entry %zu is not below %u",
+                   name, original_ids[i], i, global_experts);
+    return fill_pool_synthetic(pool, stream, seed, d, f, global_experts, 0, original_ids);
 }
 
 // ---------------------------------------------------------------------------

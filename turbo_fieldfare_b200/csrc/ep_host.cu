@@ -26,6 +26,7 @@
 #include <dlfcn.h>
 #include <nccl.h>
 
+#include <algorithm>
 #include <cstring>
 #include <vector>
 
@@ -272,6 +273,33 @@ tf_status tf_ep_unique_id(void* out_128_bytes) {
     ncclResult_t r = api.GetUniqueId(&id);
     if (r != ncclSuccess) return tf::fail(nullptr, TF_ERR_CUDA, "ncclGetUniqueId: %s", api.GetErrorString(r));
     memcpy(out_128_bytes, &id, sizeof id);
+    return TF_OK;
+}
+
+tf_status tf_ep_balanced_placement(const uint64_t* counts, uint32_t layers, uint32_t num_experts, uint32_t world,
+                                   uint32_t* placement) {
+    const char* name = "tf_ep_balanced_placement";
+    if (!counts || !placement) return tf::fail(nullptr, TF_ERR_INVALID_ARGUMENT, "%s: NULL argument", name);
+    if (layers == 0 || num_experts == 0 || world == 0 || num_experts % world != 0)
+        return tf::fail(nullptr, TF_ERR_INVALID_ARGUMENT, "%s: %u experts do not divide over %u ranks", name, num_experts, world);
+    const uint32_t per_rank = num_experts / world;
+    std::vector<uint32_t> order(num_experts), used(world);
+    std::vector<uint64_t> load(world);
+    for (uint32_t l = 0; l < layers; ++l) {
+        const uint64_t* c = counts + (size_t)l * num_experts;
+        for (uint32_t e = 0; e < num_experts; ++e) order[e] = e;
+        std::stable_sort(order.begin(), order.end(), [c](uint32_t a, uint32_t b) { return c[a] > c[b]; });
+        std::fill(used.begin(), used.end(), 0u);
+        std::fill(load.begin(), load.end(), (uint64_t)0);
+        for (uint32_t e : order) {
+            uint32_t best = world;
+            for (uint32_t r = 0; r < world; ++r)
+                if (used[r] < per_rank && (best == world || load[r] < load[best])) best = r;
+            placement[(size_t)l * num_experts + best * per_rank + used[best]] = e;
+            used[best] += 1;
+            load[best] += c[e];
+        }
+    }
     return TF_OK;
 }
 

@@ -56,6 +56,28 @@ def plan_dispatch(indices: np.ndarray, experts_per_rank: int, n_ranks: int, capa
 TF_EP_EXACT, TF_EP_FIXED_NCCL, TF_EP_FIXED_PEER = 0, 1, 2
 
 
+def balanced_placement(lib, counts: np.ndarray, n_ranks: int) -> np.ndarray:
+    """``tf_ep_balanced_placement``: per layer, the renumbering (new id -> original id) that spreads the measured
+    load ``counts`` [layers, experts] evenly over ``n_ranks`` contiguous shards."""
+    c = np.ascontiguousarray(counts, dtype=np.uint64)
+    if c.ndim != 2:
+        raise ValueError("counts must be [layers, experts]")
+    out = np.zeros(c.shape, dtype=np.uint32)
+    status = lib.tf_ep_balanced_placement(c.ctypes.data, c.shape[0], c.shape[1], n_ranks, out.ctypes.data)
+    if status != 0:
+        raise ValueError(f"tf_ep_balanced_placement: status {status} ({c.shape[1]} experts over {n_ranks} ranks)")
+    return out
+
+
+def shard_imbalance(counts: np.ndarray, placement: np.ndarray | None, n_ranks: int) -> np.ndarray:
+    """Per layer: rows of the most loaded shard / rows of the average shard under ``placement`` (None: contiguous)."""
+    c = np.asarray(counts, dtype=np.float64)
+    if placement is not None:
+        c = np.take_along_axis(c, np.asarray(placement, dtype=np.int64), axis=1)
+    per_rank = c.reshape(c.shape[0], n_ranks, -1).sum(axis=2)
+    return per_rank.max(axis=1) / np.maximum(per_rank.mean(axis=1), 1e-30)
+
+
 class ExpertParallelStack:
     """Synthetic stack of MoE blocks with the routed experts sharded over the ranks of ``group``.
 
@@ -74,6 +96,8 @@ class ExpertParallelStack:
         self.local_experts = num_experts // self.world
         self.dims = dict(layers=layers, d=d, f=f, fs=fs, num_experts=num_experts, top_k=top_k)
         self.eps = eps
+        self.seed = seed
+        self.placement = None                     # [layers, experts] new id -> original id (None: contiguous shards)
         self.pool = ExpertPool(context, layers, self.local_experts, d, f, align)
         self.pool.fill_synthetic(seed, global_experts=num_experts, expert_offset=self.rank * self.local_experts)
         rng = np.random.default_rng(seed)
@@ -108,6 +132,51 @@ class ExpertParallelStack:
         for l in self.layers:
             l.set_logit_bias(bias)
         self._build()
+
+    def set_placement(self, placement: np.ndarray | None) -> None:
+        """Place the experts by ``placement`` [layers, experts] (new id -> original id; rank r owns the new ids
+        [r * E / world, (r + 1) * E / world)): the routers' rows are renumbered and this rank's pool is refilled with the
+        experts it now owns. Every rank must pass the same table. Outputs do not change."""
+        E, L = self.dims["num_experts"], self.dims["layers"]
+        if placement is None:
+            self.pool.fill_synthetic(self.seed, global_experts=E, expert_offset=self.rank * self.local_experts)
+        else:
+            placement = np.ascontiguousarray(placement, dtype=np.uint32)
+            if placement.shape != (L, E):
+                raise ValueError(f"placement must be [{L}, {E}], got {placement.shape}")
+            mine = placement[:, self.rank * self.local_experts:(self.rank + 1) * self.local_experts]
+            self.pool.fill_synthetic(self.seed, global_experts=E, original_ids=mine)
+        for l, layer in enumerate(self.layers):
+            layer.set_placement(None if placement is None else placement[l])
+        self.placement = placement
+        torch.cuda.synchronize()
+        self._build()
+
+    def expert_load(self, hidden: torch.Tensor, tokens: int, buf: "EPBuffers", stream=None) -> np.ndarray:
+        """Routed pairs per (layer, ORIGINAL expert id) that ``hidden`` [tokens, d] produces, summed over the ranks'
+        batches: the layer loop of ``forward`` run one layer at a time with the router's output read back after each
+        (a calibration pass, not a fast path). Collective; ``buf`` must be exact-count buffers."""
+        from .kernels import RMSNorm
+        E, L, d = self.dims["num_experts"], self.dims["layers"], self.dims["d"]
+        norm = RMSNorm(self.context)
+        h = hidden[:tokens].clone()
+        x, y = torch.empty_like(h), torch.empty_like(h)
+        counts = np.zeros((L, E), dtype=np.int64)
+        for l in range(L):
+            norm.encode(h, self.norm_weights[l], x, tokens, d, eps=self.eps, stream=stream)
+            self.block_forward(l, x, y, tokens, buf, stream)
+            idx, _ = buf.routing(tokens)
+            new_ids = np.bincount(idx.ravel().astype(np.int64), minlength=E)
+            if self.placement is None:
+                counts[l] = new_ids
+            else:
+                counts[l, self.placement[l].astype(np.int64)] = new_ids
+            h += y
+        if self.world > 1:
+            t = torch.from_numpy(counts).cuda()
+            dist.all_reduce(t, group=self.group)
+            counts = t.cpu().numpy()
+        return counts
 
     def buffers(self, max_tokens: int, fixed_capacity: bool, peer: bool = False) -> "EPBuffers":
         """``fixed_capacity``: static shapes and no host synchronisation (decode-sized batches); otherwise exact row

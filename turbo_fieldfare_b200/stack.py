@@ -76,11 +76,21 @@ class ExpertPool:
                                                                   blob.ctypes.data, blob.size))
         torch.cuda.current_stream().synchronize()    # the host array may be freed by the caller
 
-    def fill_synthetic(self, seed: int, stream=None, global_experts: int = 0, expert_offset: int = 0) -> None:
+    def fill_synthetic(self, seed: int, stream=None, global_experts: int = 0, expert_offset: int = 0,
+                       original_ids: np.ndarray | None = None) -> None:
         """Seeded synthetic blobs; a shard passes the global expert count and its first expert id so that
-        it holds the same bytes as the corresponding slice of the unsharded pool."""
-        self.context.check(self.context.lib.tf_expert_pool_fill_synthetic(self.handle, _stream(stream), seed,
-                                                                          self.d, self.f, global_experts, expert_offset))
+        it holds the same bytes as the corresponding slice of the unsharded pool. ``original_ids`` [layers, experts]
+        instead names the expert of the unsharded pool that each slot holds (experts placed by load)."""
+        lib, ctx = self.context.lib, self.context
+        if original_ids is None:
+            ctx.check(lib.tf_expert_pool_fill_synthetic(self.handle, _stream(stream), seed, self.d, self.f, global_experts,
+                                                        expert_offset))
+            return
+        ids = np.ascontiguousarray(original_ids, dtype=np.uint32)
+        if ids.shape != (self.layers, self.experts):
+            raise ValueError(f"original_ids must be [{self.layers}, {self.experts}], got {ids.shape}")
+        ctx.check(lib.tf_expert_pool_fill_synthetic_placed(self.handle, _stream(stream), seed, self.d, self.f,
+                                                           global_experts or self.experts, ids.ctypes.data))
 
     def download(self, layer: int, expert: int) -> np.ndarray:
         """Copy one blob back to the host (tests use this to feed the oracle the exact bytes)."""
@@ -157,16 +167,47 @@ class MoEBlockLayer:
         self.effective_scale = torch.from_numpy(_bf16_bits(eff).view(np.int16)).cuda()
         self.per_expert_scale = torch.from_numpy(_bf16_bits(np.ones(num_experts, np.float32)).view(np.int16)).cuda()
         self.logit_bias = None
+        self.placement = None                     # new expert id -> original id (None: identity)
+        self._router_original = None
+        self._bias_original = None
 
     def fill_synthetic(self, seed: int) -> None:
         ctx = self.context
+        self._router_original, self.placement = None, None
         self.router.fill_synthetic(ctx, seed * 16 + 1)
         self.shared_gate.fill_synthetic(ctx, seed * 16 + 2)
         self.shared_up.fill_synthetic(ctx, seed * 16 + 3)
         self.shared_down.fill_synthetic(ctx, seed * 16 + 4)
 
     def set_logit_bias(self, bias: np.ndarray | None) -> None:
-        self.logit_bias = None if bias is None else torch.from_numpy(np.ascontiguousarray(bias, np.float32)).cuda()
+        """``bias`` is indexed by the ORIGINAL expert id; it is stored in the placement's order."""
+        self._bias_original = None if bias is None else np.ascontiguousarray(bias, np.float32)
+        if bias is None:
+            self.logit_bias = None
+        else:
+            order = self.placement if self.placement is not None else np.arange(self.num_experts)
+            self.logit_bias = torch.from_numpy(self._bias_original[order].copy()).cuda()
+
+    def set_placement(self, new_to_original: np.ndarray | None) -> None:
+        """Renumber the experts: the router's row ``n`` becomes the row of expert ``new_to_original[n]`` (codes, scales,
+        biases, per-expert scale, logit bias). The pool must store its slots in the same order. ``None`` restores the
+        original numbering."""
+        if self._router_original is None:
+            self._router_original = self.router.download()
+            self._pes_original = self.per_expert_scale.cpu().numpy().copy()
+        if new_to_original is None:
+            order = np.arange(self.num_experts)
+            self.placement = None
+        else:
+            order = np.ascontiguousarray(new_to_original, dtype=np.int64)
+            if sorted(order.tolist()) != list(range(self.num_experts)):
+                raise ValueError("placement must be a permutation of the expert ids")
+            self.placement = order
+        packed, scales, biases = self._router_original
+        self.router.upload(packed[order], scales[order], biases[order])
+        self.per_expert_scale.copy_(torch.from_numpy(self._pes_original[order].copy()))
+        if getattr(self, "_bias_original", None) is not None:
+            self.logit_bias = torch.from_numpy(self._bias_original[order].copy()).cuda()
 
     def c_struct(self) -> MoELayer:
         return MoELayer(self.router.projection(), _ptr(self.effective_scale), _ptr(self.per_expert_scale),
