@@ -373,6 +373,32 @@ def run_gpu(args):
     ms_dec1 = phase_ms(lambda: g1.replay() if g1 else stack.forward(h1, 1, ws_b1, stream=cs), 20)
     ms_decn = phase_ms(lambda: gn.replay() if gn else stack.forward(hn, batch, ws_bn, stream=cs), 20)
 
+    # Strong-scaling view beside the weak headline: the SAME totals (one prefill block, one decode batch) sharded over
+    # the ranks, each phase timed on the device and taken as the maximum over the ranks.
+    strong = None
+    if ep and not args.no_strong and prefill_tokens % world == 0 and batch % world == 0 and batch // world > 1:
+        sp, sb = prefill_tokens // world, batch // world
+        ws_sp = (stack.buffers(sp, fixed_capacity=True, peer=True) if prefill_peer
+                 else stack.buffers(sp, fixed_capacity=False))
+        ws_sb = stack.buffers(sb, fixed_capacity=True, peer=peer)
+        h_sp = dev_prefill[:sp].clone()
+        h_sb = torch.zeros(sb, D, dtype=torch.float16, device="cuda")
+        torch.cuda.synchronize()
+        dist.barrier()
+        g_sb = capture(h_sb, sb, ws_sb) if use_graphs and ws_sb.peer else None
+        barrier()
+        ms_sp = phase_ms(lambda: stack.forward(h_sp, sp, ws_sp, stream=cs))
+        barrier()
+        ms_sb = phase_ms(lambda: g_sb.replay() if g_sb else stack.forward(h_sb, sb, ws_sb, stream=cs), 20)
+        t = torch.tensor([ms_sp, ms_sb], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_sp, ms_sb = (float(v) for v in t.tolist())
+        strong = {"what": "the single-GPU totals sharded over the ranks (max over ranks, device time)",
+                  "prefill_tokens_total": prefill_tokens, "prefill_tokens_per_rank": sp, "prefill_ms": ms_sp,
+                  "decode_batch_total": batch, "decode_batch_per_rank": sb, "decode_step_ms": ms_sb,
+                  "prefill_tokens_per_s": prefill_tokens / ms_sp * 1e3, "decode_tokens_per_s": batch / ms_sb * 1e3}
+        healthy("the strong-scaling phases")
+
     # roofline of the dominant kernel: the grouped tensor-core expert kernel at decode batch 64
     # (gate/up launch + down launch of one layer timed as a pair, distinct layers back to back so
     # that nothing is re-read from L2).
@@ -402,6 +428,7 @@ def run_gpu(args):
                    "tokens_per_step": tokens, "routing": "zipf(1.1) logit bias" if args.zipf else "computed logits",
                    "l2": "every step streams 13.2 GB of distinct layer weights (>> 126 MB L2)",
                    "cuda_graphs": use_graphs, "device_status": device_code, "expert_placement": placement_record,
+                   "strong": strong,
                    "parallelism": (f"ep{world}: experts sharded {E // world} per GPU; prefill: "
                                    + ("fixed-capacity slots over peer memory, expert phase on the tensor cores, no host "
                                       "read-back in the layer loop" if prefill_peer and ws_prefill.peer
@@ -837,6 +864,7 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of layer-0 outputs after the timed regions")
     ap.add_argument("--single-launch-step", type=int, default=0,
                     help="one-token steps as one persistent launch (1) or layer by layer (0); single GPU only")
+    ap.add_argument("--no-strong", action="store_true", help="skip the strong-scaling sub-record at N > 1")
     ap.add_argument("--ep-placement", default="balanced", choices=["contiguous", "balanced"],
                     help="expert parallelism: experts in contiguous shards, or renumbered per layer so that the shards "
                          "carry equal load on a seeded calibration batch (not the timed inputs)")
