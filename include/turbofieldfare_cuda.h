@@ -145,6 +145,12 @@ tf_status tf_context_set_tensorcore_min_tokens(tf_context* ctx, uint32_t tokens)
  * Default 256, like the routed experts: measured at 8, 16, 32 and 64 tokens the streaming kernels were faster
  * (1.07 ms against 1.22 ms for six layers at 64 tokens). */
 tf_status tf_context_set_shared_tensorcore_min_tokens(tf_context* ctx, uint32_t tokens);
+/* Router calls over at least `rows` rows (default 256) take two launches: every logit on the tensor cores with a bound
+ * on its distance from the canonical fp32 value, then the canonical logit (the reference's order of operations,
+ * Metal/MoE/moe.metal:135-185) of the experts that can still reach the top k, typically top_k + 1 or 2 of them.
+ * Indices and weights are those of the one-launch kernels bit for bit. UINT32_MAX keeps the one-launch kernel. Calls
+ * that ask for the logits (out_logits) always take the one-launch kernel. */
+tf_status tf_context_set_router_tensorcore_min_rows(tf_context* ctx, uint32_t rows);
 /* Expert parallelism with fixed-capacity exchanges (decode steps): when ranks * tokens * top_k / (experts of a rank), the
  * expected rows per local expert, reaches `rows`, the owner's expert phase runs on the tensor cores instead of the
  * streaming kernels. Off by default (UINT32_MAX): at eight ranks x 64 tokens (32 rows per expert) the tensor-core phase

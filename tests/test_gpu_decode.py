@@ -329,6 +329,72 @@ def test_few_row_router_is_bit_exact(tf_ctx, oracle, T):
     assert tf_ctx.device_status() == 0
 
 
+@pytest.mark.parametrize("rows,E,D,case,bf16", [(300, 16, 256, "plain", False), (1000, 128, 2816, "bias", False),
+                                                (257, 250, 512, "few_finite", False), (700, 128, 2816, "some_ninf", True),
+                                                (4096, 128, 2816, "twins", False), (513, 128, 2816, "odd_rows", False)])
+def test_two_launch_router_equals_the_canonical_router(tf_ctx, oracle, rows, E, D, case, bf16):
+    """Batches of 256 rows and more compute all logits on the tensor cores and re-check the experts that can reach the
+    top 8 in the canonical order: indices and weights must be those of the one-launch kernel byte for byte (a call that
+    asks for the logits takes the one-launch kernel, whose logits are checked against the oracle at full size).
+    Cases: a logit bias; fewer than 8 experts with a finite bias; most experts at -inf; two experts with identical
+    rows (an exact tie in every token); rows of zeros, subnormal, huge, infinite and NaN activations."""
+    import torch
+    from turbo_fieldfare_b200.kernels import PrefillRouter
+    o = oracle
+    rng = np.random.default_rng(9100 + rows + E)
+    mat = config0_matrix(o, E, D, rng, bits=8)
+    if case == "twins":
+        for arr in (mat.packed, mat.scales, mat.biases):
+            arr[77] = arr[3]
+            arr[12] = arr[100]
+    eff = o.f32_to_bf16((rng.uniform(0.5, 1.5, D) / np.sqrt(D)).astype(np.float32))
+    gain = o.f32_to_bf16(rng.uniform(0.6, 1.4, E).astype(np.float32))
+    bias = None
+    if case == "bias":
+        bias = (0.3 * rng.standard_normal(E)).astype(np.float32)
+    elif case == "few_finite":
+        bias = np.full(E, -np.inf, np.float32); bias[[2, 5, 100, E - 1]] = [0.0, 0.1, -0.2, 0.05]
+    elif case == "some_ninf":
+        bias = np.full(E, -np.inf, np.float32); bias[rng.permutation(E)[:20]] = 0.0
+    x = rng.standard_normal((rows, D)).astype(np.float32)
+    if case == "odd_rows":
+        x[0] = 0.0
+        x[1] = 1e-7                                   # subnormal in fp16
+        x[2] *= 3000.0                                # the fp16 split of x * 2^10 overflows
+        x[3, 17] = np.inf
+        x[4, 5] = np.nan
+        x[5] = 60000.0 * np.sign(x[5])
+        x[6, :64] = 0.0
+        x[7] *= 1e-3
+    h = o.f32_to_bf16(x) if bf16 else o.f32_to_f16(x)
+    W, S, B = to_dev(mat.packed), to_dev(mat.scales), to_dev(mat.biases)
+    effd, gaind, hid = to_dev(eff), to_dev(gain), to_dev(h)
+    biasd = None if bias is None else to_dev(bias)
+    K = 8
+
+    def run(want_logits, min_rows):
+        tf_ctx.set_router_tensorcore_min_rows(min_rows)
+        idx = torch.full((rows, K), -1, dtype=torch.int32, device="cuda")
+        w = dev_zeros_u16(rows * K)
+        logits = torch.zeros((rows, E), dtype=torch.float32, device="cuda") if want_logits else None
+        PrefillRouter(tf_ctx).encode_gemma4_block(W, S, B, hid, effd, gaind, idx, w, rows, E, D, K, D,
+                                                  hidden_dtype=0 if bf16 else 1, logit_bias=biasd, out_logits=logits)
+        torch.cuda.synchronize()
+        return from_dev(idx, np.uint32).reshape(rows, K), from_dev(w, np.uint16).reshape(rows, K)
+
+    try:
+        idx_one, w_one = run(False, 0xFFFFFFFF)         # the one-launch kernel
+        idx_log, w_log = run(True, 256)                 # asks for the logits: the one-launch kernel as well
+        idx_two, w_two = run(False, 256)                # tensor-core logits + canonical re-check
+    finally:
+        tf_ctx.set_router_tensorcore_min_rows(256)
+    assert np.array_equal(idx_one, idx_log) and w_one.tobytes() == w_log.tobytes()
+    bad = np.nonzero(np.any(idx_two != idx_one, axis=1))[0]
+    assert bad.size == 0, f"rows {bad[:8]} differ: {idx_two[bad[:2]]} vs {idx_one[bad[:2]]}"
+    assert w_two.tobytes() == w_one.tobytes()
+    assert tf_ctx.device_status() == 0
+
+
 def test_router_preconditions(tf_ctx):
     import torch
     from turbo_fieldfare_b200.kernels import MoE, TFError

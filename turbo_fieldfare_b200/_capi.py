@@ -130,6 +130,7 @@ SIGNATURES = {
                                               C.POINTER(Projection), vp, u64, u32, vp, u32]),
     "tf_context_set_tensorcore_min_tokens": (C.c_int, [vp, u32]),
     "tf_context_set_shared_tensorcore_min_tokens": (C.c_int, [vp, u32]),
+    "tf_context_set_router_tensorcore_min_rows": (C.c_int, [vp, u32]),
     "tf_context_set_ep_tensorcore_min_rows_per_expert": (C.c_int, [vp, u32]),
     "tf_int4_qmm": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, vp, u64, vp, u64, u32, u32, u32]),
     "tf_int4_qmm_with_path": (C.c_int, [vp, vp, vp, u64, vp, u64, vp, u64, vp, u64, vp, u64, u32, u32, u32, C.POINTER(C.c_int)]),

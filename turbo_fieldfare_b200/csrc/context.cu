@@ -104,6 +104,7 @@ void tf_context_destroy(tf_context* ctx) {
     cudaSetDevice(ctx->device);
     if (ctx->router_logits) cudaFree(ctx->router_logits);
     if (ctx->router_tickets) cudaFree(ctx->router_tickets);
+    if (ctx->router_approx) cudaFree(ctx->router_approx);
     if (ctx->device_error) cudaFree(ctx->device_error);
     if (ctx->peer_error) cudaFree(ctx->peer_error);
     if (ctx->streamed_scratch) cudaFree(ctx->streamed_scratch);
@@ -136,6 +137,12 @@ tf_status tf_context_set_tensorcore_min_tokens(tf_context* ctx, uint32_t tokens)
 tf_status tf_context_set_shared_tensorcore_min_tokens(tf_context* ctx, uint32_t tokens) {
     TF_REQUIRE(ctx, ctx != nullptr && tokens > 0, TF_ERR_INVALID_ARGUMENT, "tf_context_set_shared_tensorcore_min_tokens: ctx is NULL or tokens is 0");
     ctx->shared_tensorcore_min_tokens = tokens;
+    return TF_OK;
+}
+
+tf_status tf_context_set_router_tensorcore_min_rows(tf_context* ctx, uint32_t rows) {
+    TF_REQUIRE(ctx, ctx != nullptr && rows > 0, TF_ERR_INVALID_ARGUMENT, "tf_context_set_router_tensorcore_min_rows: ctx is NULL or rows is 0");
+    ctx->router_tensorcore_min_rows = rows;
     return TF_OK;
 }
 

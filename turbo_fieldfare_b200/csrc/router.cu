@@ -12,6 +12,7 @@
 // which is the reference kernel's per-lane element assignment with the
 // contraction and reduction order fixed.
 #include "router.cuh"
+#include "router_tensor.cuh"
 
 namespace tf {
 
@@ -620,6 +621,20 @@ static int tile_router_rows(uint32_t rows, uint32_t slots) {
     return best;
 }
 
+// Scratch of the two-launch router: (approximate logit, magnitude) per (row, expert), owned by the context and grown
+// on demand. Growing allocates, which a stream that is being captured must not do: the caller then takes the
+// one-launch kernel.
+static bool router_scratch(tf_context* ctx, cudaStream_t st, uint32_t rows, uint32_t num_experts) {
+    const size_t need = (size_t)rows * num_experts * sizeof(float2);
+    if (need <= ctx->router_approx_bytes) return true;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(st, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) { cudaGetLastError(); return false; }
+    if (ctx->router_approx) { cudaFree(ctx->router_approx); ctx->router_approx = nullptr; ctx->router_approx_bytes = 0; }
+    if (cudaMalloc(&ctx->router_approx, need) != cudaSuccess) { cudaGetLastError(); return false; }
+    ctx->router_approx_bytes = need;
+    return true;
+}
+
 static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, const uint8_t* S, const uint8_t* B,
                                const uint8_t* hidden, tf_dtype hidden_dtype, const uint8_t* eff, const uint8_t* pes,
                                const float* logit_bias, uint32_t* out_idx, uint8_t* out_w, float* out_logits,
@@ -679,6 +694,25 @@ static tf_status launch_router(tf_context* ctx, void* stream, const uint8_t* W, 
         launch_pdl(k, grid, dim3(kSplitThreads), smem_split, st, W, Sp, Bp, hp, stride, ep, pp, logit_bias, out_idx, wp, out_logits,
                    ctx->router_logits, ctx->router_tickets, grp, num_experts, d, top_k, a2);
         return check_launch(ctx, name);
+    } else if (rows >= ctx->router_tensorcore_min_rows && !out_logits && vec16 && d % kApxChunk == 0 && aligned(S, 8) && aligned(B, 8) &&
+               num_experts <= TF_MAX_ROUTER_EXPERTS && top_k <= (uint32_t)kWarp && top_k <= num_experts &&
+               router_recheck_smem_bytes(d, num_experts) <= 200 * 1024 && router_scratch(ctx, st, rows, num_experts)) {
+        // logits on the tensor cores, then the canonical logits of the few experts that can reach the top k
+        auto ka = bf ? router_approx_kernel<true> : router_approx_kernel<false>;
+        constexpr int kProductionGroups = 2816 / kGroup;          // the recheck keeps an expert's 44 code words in registers
+        const bool fixed = d / kGroup == (uint32_t)kProductionGroups;
+        auto kr = fixed ? (bf ? router_recheck_kernel<true, kProductionGroups> : router_recheck_kernel<false, kProductionGroups>)
+                        : (bf ? router_recheck_kernel<true, 0> : router_recheck_kernel<false, 0>);
+        static DeviceSmemCache configured_approx[2], configured_recheck[4];
+        const size_t smem_a = router_approx_smem_bytes(), smem_r = router_recheck_smem_bytes(d, num_experts);
+        if (tf_status s = ensure_dynamic_smem(ctx, ka, configured_approx[bf ? 1 : 0], smem_a)) return s;
+        if (tf_status s = ensure_dynamic_smem(ctx, kr, configured_recheck[(bf ? 1 : 0) + (fixed ? 2 : 0)], smem_r)) return s;
+        float2* approx = reinterpret_cast<float2*>(ctx->router_approx);
+        launch_pdl(ka, dim3((rows + kApxTokens - 1) / kApxTokens, (num_experts + kApxExperts - 1) / kApxExperts), dim3(kApxThreads),
+                   smem_a, st, W, Sp, Bp, hp, stride, ep, approx, rows, num_experts, d);
+        if (tf_status s = check_launch(ctx, name)) return s;
+        launch_pdl(kr, dim3((rows + kRecheckWarps - 1) / kRecheckWarps), dim3(kRecheckWarps * kWarp), smem_r, st, W, Sp, Bp, hp, stride,
+                   ep, pp, logit_bias, static_cast<const float2*>(approx), out_idx, wp, rows, num_experts, d, top_k);
     } else if (rows >= 256 && a2 && (size_t)kTileRouterRows * (d + num_experts) * 4 <= 100 * 1024) {
         const int R = tile_router_rows(rows, (uint32_t)ctx->sm_count * 2u);
         void (*k)(const uint8_t*, const uint16_t*, const uint16_t*, const uint16_t*, uint32_t, const uint16_t*, const uint16_t*, const float*,

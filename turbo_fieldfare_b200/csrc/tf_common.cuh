@@ -39,6 +39,11 @@ struct tf_context {
     // reference's MoE wrapper owns (Kernels/MoE/MoE.swift:92-106).
     float* router_logits = nullptr;        // [kRouterSplitRows, 256]
     unsigned int* router_tickets = nullptr;  // [kRouterSplitRows], self-resetting
+    // Prefill-sized router: (approximate logit, magnitude) per (row, expert) between its two launches; grown on demand.
+    void* router_approx = nullptr;
+    size_t router_approx_bytes = 0;
+    // Batches of at least this many rows take the two-launch router (tensor-core logits + canonical re-check).
+    uint32_t router_tensorcore_min_rows = 256;
     // One device word that kernels with bounded waits set when a wait gives up (0 = healthy).
     uint32_t* device_error = nullptr;
     // The same for the flag barriers of the peer exchange (peer.cu), kept apart so that a code from another kernel

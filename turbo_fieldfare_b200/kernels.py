@@ -80,6 +80,11 @@ class TurboContext:
         """The same threshold for a block's shared expert alone (default 256)."""
         self.check(self.lib.tf_context_set_shared_tensorcore_min_tokens(self.handle, tokens))
 
+    def set_router_tensorcore_min_rows(self, rows: int) -> None:
+        """Router calls over at least ``rows`` rows compute all logits on the tensor cores and re-check the candidates in
+        the canonical order (default 256; 0xFFFFFFFF keeps the one-launch kernel)."""
+        self.check(self.lib.tf_context_set_router_tensorcore_min_rows(self.handle, rows))
+
     def set_single_launch_step(self, enabled: bool) -> None:
         """One-token stack steps as one persistent launch (True) or layer by layer (False)."""
         self.check(self.lib.tf_context_set_single_launch_step(self.handle, 1 if enabled else 0))
