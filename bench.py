@@ -1,6 +1,6 @@
 #!/usr/bin/env python
 """Benchmark of the routed-expert hot path on B200: the synthetic 30-layer MoE stack of
-BASELINE.json (config 4): a 4096-token prefill followed by 256 decode steps at batch 1 and
+the benchmark specification (configuration 4): a 4096-token prefill followed by 256 decode steps at batch 1 and
 256 at batch 64, reported as whole-job tokens/s.
 
     python bench.py --gpus N --steps K --warmup W            # this library (CUDA, sm_100a)
@@ -135,7 +135,7 @@ def host_cores() -> int:
 
 
 def workload_name(layers, prefill_tokens, steps_dec, batch):
-    """The job both arms are quoted on (BASELINE config 4 at the default arguments)."""
+    """The job both arms are quoted on (benchmark configuration 4 at the default arguments)."""
     return (f"config4: {layers}-layer MoE stack (128 experts int4 g64, top-8, shared expert, RMSNorm between layers, "
             f"attention omitted): {prefill_tokens}-token prefill + {steps_dec} decode steps at batch 1 + {steps_dec} at batch {batch}")
 
@@ -458,7 +458,7 @@ def run_gpu(args):
 
 
 def measure_gemv(torch, ctx, peak, peak_src):
-    """BASELINE's first metric, "int4 expert GEMV HBM GB/s (% of peak)": the stand-alone GEMV (config-0 row shape, N = 2816)
+    """the benchmark's first metric, "int4 expert GEMV HBM GB/s (% of peak)": the stand-alone GEMV (config-0 row shape, N = 2816)
     on a matrix far larger than L2 (262144 rows, 415 MB: the reference's LM-head-sized instance), timed with CUDA events
     over back-to-back launches. Algorithmic bytes = packed codes + scale and bias planes."""
     from turbo_fieldfare_b200.kernels import DequantInt4GEMV
@@ -488,7 +488,7 @@ def measure_gemv(torch, ctx, peak, peak_src):
 
 
 def measure_gemv_sweep(torch, ctx, stack, peak, peak_src):
-    """BASELINE config 0 as its metric asks: single-token int4 GEMVs over DISTINCT 704 x 2816 expert matrices (the gate
+    """benchmark configuration 0 as its metric asks: single-token int4 GEMVs over DISTINCT 704 x 2816 expert matrices (the gate
     tensor of every expert blob of the pool: layers x 128 matrices, 3.8 GB at 30 layers, far beyond L2) in one launch.
     Algorithmic bytes per matrix = codes + scale and bias planes + x + y = 1 122 176."""
     from turbo_fieldfare_b200.kernels import DequantInt4GEMV
@@ -816,7 +816,7 @@ def case_qmm(args) -> None:
 
 
 def case_gemv_sweep(args) -> None:
-    """BASELINE config 0 as a sweep: one launch of single-token GEMVs over every expert's 704 x 2816 gate tensor of a
+    """benchmark configuration 0 as a sweep: one launch of single-token GEMVs over every expert's 704 x 2816 gate tensor of a
     --layers deep pool (430 MB per layer)."""
     import torch
     from turbo_fieldfare_b200.kernels import TurboContext

@@ -1,5 +1,5 @@
 """Shared fixtures-as-functions for the parity tests: seeded inputs (the
-reference's PRNG and quantisers through the oracle, or numpy for the BASELINE
+reference's PRNG and quantisers through the oracle, or numpy for the benchmark
 configurations) and upload helpers. Test infrastructure only."""
 from __future__ import annotations
 
@@ -31,7 +31,7 @@ def dev_zeros_u16(n, fill=0):
 
 
 def config0_matrix(o, m, n, rng, sb_dtype=0, bits=4):
-    """BASELINE config-0 distributions: uniform codes, scale=|N(0,1)|*0.004,
+    """benchmark configuration-0 distributions: uniform codes, scale=|N(0,1)|*0.004,
     bias=-8*scale+N(0,1e-4) (1e-4 read as the standard deviation), both rounded to the
     16-bit plane dtype; for 8-bit codes the recipe is scaled (scale/16, bias=-128*scale)."""
     if bits == 4:

@@ -1,12 +1,12 @@
 """GPU parity of the fused MoE block and the layer stack against the oracle applied per token
-(BASELINE configs 1 and 2, and a small-dimension stack)."""
+(benchmark configurations 1 and 2, and a small-dimension stack)."""
 import numpy as np
 import pytest
 
 from helpers import from_dev, to_dev
 
 pytestmark = pytest.mark.gpu
-TOL = 1e-2     # BASELINE: outputs within 1e-2 relative L2 of the fp32-dequantised oracle
+TOL = 1e-2     # benchmark bound: outputs within 1e-2 relative L2 of the fp32-dequantised oracle
 
 
 def _affine_from(o, tensor):
@@ -156,7 +156,7 @@ def _sample_rows(idx_ref, T, n_random, seed):
 def test_block_forward_prefill_sized_runs_on_tensor_cores(tf_ctx, oracle, production_layer, T, zipf):
     """From 256 tokens the block runs pack -> tcgen05 grouped GEMMs -> combine; same router decisions on EVERY row,
     outputs within the same 1e-2 relative L2 of the per-token oracle on at least 32 rows. T = 4096 with the
-    Zipf(1.1) logit bias is BASELINE config 3 on one GPU."""
+    Zipf(1.1) logit bias is benchmark configuration 3 on one GPU."""
     import torch
     from turbo_fieldfare_b200.stack import MoEBlock, Workspace
     o = oracle
@@ -197,7 +197,7 @@ def test_block_forward_prefill_sized_runs_on_tensor_cores(tf_ctx, oracle, produc
 
 @pytest.mark.parametrize("T", [5, 4096])
 def test_block_forward_bf16_rows(tf_ctx, oracle, production_layer, T):
-    """BASELINE config 3 names bf16 activations: the block takes bf16 rows, converts them to fp16 exactly (every bf16
+    """benchmark configuration 3 names bf16 activations: the block takes bf16 rows, converts them to fp16 exactly (every bf16
     value of normalised activations is an fp16 value), and rounds its result to bf16. Same router decisions as the oracle
     on every row; outputs within 1e-2 relative L2 plus the bf16 rounding of the result (2^-9)."""
     import torch

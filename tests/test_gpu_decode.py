@@ -1,6 +1,6 @@
 """GPU parity of the decode-path entry points against the CPU oracle, through the
 C ABI. Seeds, shapes and tolerances are the reference's own where it has a test
-(cited per case); BASELINE configurations use numpy-seeded inputs."""
+(cited per case); benchmark configurations use numpy-seeded inputs."""
 import numpy as np
 import pytest
 
@@ -10,7 +10,7 @@ from helpers import (blob_table, capi_offsets, config0_matrix, dev_zeros_u16, fr
 pytestmark = pytest.mark.gpu
 
 FP16_REDUCTION = 5e-3      # Tolerance.fp16Reduction
-FP16_CHAINED = 1e-2        # Tolerance.fp16ChainedReduction (also BASELINE's 1e-2 relative L2)
+FP16_CHAINED = 1e-2        # Tolerance.fp16ChainedReduction (also the benchmark's 1e-2 relative L2)
 
 
 def _run_gemv(tf_ctx, o, mat, x16, offset=0, bits=4):
@@ -75,7 +75,7 @@ def test_int8_gemv_reference_fixtures(tf_ctx, oracle, m, n, seed):
 
 @pytest.mark.parametrize("sb_dtype", [0, 1])
 def test_config0_gemv_704x2816(tf_ctx, oracle, sb_dtype):
-    """BASELINE config 0: 704 x 2816, uniform codes, scale/bias distributions, x ~ N(0,1) fp16."""
+    """benchmark configuration 0: 704 x 2816, uniform codes, scale/bias distributions, x ~ N(0,1) fp16."""
     o = oracle
     rng = np.random.default_rng(20260 + sb_dtype)
     mat = config0_matrix(o, 704, 2816, rng, sb_dtype=sb_dtype)
@@ -269,7 +269,7 @@ def test_block_router_strided_rows(tf_ctx, oracle, rows):
 
 
 def test_production_router_128x2816_with_bias(tf_ctx, oracle):
-    """BASELINE configs 1-3: 128 experts, D=2816, top-8; Zipf(1.1) logit bias; fp16 and bf16 rows."""
+    """benchmark configurations 1-3: 128 experts, D=2816, top-8; Zipf(1.1) logit bias; fp16 and bf16 rows."""
     o = oracle
     rng = np.random.default_rng(31)
     E, D, T = 128, 2816, 96
@@ -468,7 +468,7 @@ def test_routed_decode_reference_fixture(tf_ctx, oracle):
 
 
 def test_routed_decode_production_shape_with_device_table(tf_ctx, oracle):
-    """BASELINE config 1 routed half: D=2816, F=704, 8 of 16 pooled experts chosen by ids on the device."""
+    """benchmark configuration 1 routed half: D=2816, F=704, 8 of 16 pooled experts chosen by ids on the device."""
     import torch
     from turbo_fieldfare_b200.kernels import MoE
     o = oracle
