@@ -303,7 +303,7 @@ def test_production_router_128x2816_with_bias(tf_ctx, oracle):
 
 @pytest.mark.parametrize("T", [2, 7, 33, 64])
 def test_few_row_router_is_bit_exact(tf_ctx, oracle, T):
-    """2 to 64 aligned rows take the kernel that computes four rows per expert pass: logits bit for bit those of the
+    """2 to 64 aligned rows take the kernel that computes a block of rows per expert pass: logits bit for bit those of the
     oracle's canonical order, indices equal, ragged last group of rows (7, 33) included; bf16 rows against the truth."""
     o = oracle
     rng = np.random.default_rng(7000 + T)
